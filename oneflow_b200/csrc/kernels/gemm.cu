@@ -1,0 +1,105 @@
+// C entry points of the tcgen05 GEMM (see gemm_tcgen05.cuh for the kernel).
+#include "../common/host_utils.h"
+#include "gemm_tcgen05.cuh"
+#include "ofb_kernels.h"
+
+namespace ofb {
+
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shp, const GemmEpilogue& ep,
+                       int* status, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    OFB_CUDA_OK(cudaGetDevice(&dev));
+    OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int tiles = ((shp.M + 127) / 128) * ((shp.N + BN - 1) / BN);
+  int grid = tiles < sm_count ? tiles : sm_count;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, shp, ep, status);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t stream) {
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("gemm: empty problem");
+  if (a->N % 8 != 0) return fail("gemm: N must be a multiple of 8");
+  const int a_mn = a->a_mn_major, b_mn = a->b_mn_major;
+  // K-major: dims {K, rows}, row stride ld*2 bytes. MN-major: dims {rows, K}.
+  CUtensorMap tmA, tmB;
+  int bn = a->bn;
+  if (bn != 128 && bn != 256) {
+    // Small problems: prefer more, smaller tiles so that all SMs get work.
+    long long tiles256 = (long long)((a->M + 127) / 128) * ((a->N + 255) / 256);
+    bn = (tiles256 >= 120 && a->N >= 256) ? 256 : 128;
+  }
+  if (!a_mn) {
+    if (get_tensor_map(&tmA, a->A, 2, 2, a->K, a->M, 0, (uint64_t)a->lda * 2, 0, 64, 128, 0, 3)) return -1;
+  } else {
+    if (get_tensor_map(&tmA, a->A, 2, 2, a->M, a->K, 0, (uint64_t)a->lda * 2, 0, 64, 64, 0, 3)) return -1;
+  }
+  if (!b_mn) {
+    if (get_tensor_map(&tmB, a->B, 2, 2, a->K, a->N, 0, (uint64_t)a->ldb * 2, 0, 64, bn, 0, 3)) return -1;
+  } else {
+    if (get_tensor_map(&tmB, a->B, 2, 2, a->N, a->K, 0, (uint64_t)a->ldb * 2, 0, 64, 64, 0, 3)) return -1;
+  }
+  GemmShape shp{a->M, a->N, a->K};
+  int* status = device_status_ptr();
+#define OFB_GEMM_CASE(BN_, AM_, BM_) \
+  if (bn == BN_ && a_mn == AM_ && b_mn == BM_) return launch_gemm<BN_, AM_, BM_>(tmA, tmB, shp, ep, status, a->max_ctas, stream);
+  OFB_GEMM_CASE(256, 0, 0)
+  OFB_GEMM_CASE(256, 0, 1)
+  OFB_GEMM_CASE(256, 1, 0)
+  OFB_GEMM_CASE(256, 1, 1)
+  OFB_GEMM_CASE(128, 0, 0)
+  OFB_GEMM_CASE(128, 0, 1)
+  OFB_GEMM_CASE(128, 1, 0)
+  OFB_GEMM_CASE(128, 1, 1)
+#undef OFB_GEMM_CASE
+  return fail("gemm: unsupported configuration");
+}
+
+}  // namespace ofb
+
+OFB_API int ofb_gemm_bf16(const OfbGemmArgs* a, void* stream) {
+  using namespace ofb;
+  GemmEpilogue ep;
+  std::memset(&ep, 0, sizeof(ep));
+  ep.C = a->C;
+  ep.ldc = a->ldc;
+  ep.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  ep.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  ep.ldr = a->ldr;
+  ep.aux_in = reinterpret_cast<const __nv_bfloat16*>(a->aux_in);
+  ep.aux_out = reinterpret_cast<__nv_bfloat16*>(a->aux_out);
+  ep.ld_aux = a->ld_aux;
+  ep.alpha = a->alpha;
+  ep.act = a->act;
+  ep.out_fp32 = a->out_fp32;
+  ep.accumulate = a->accumulate;
+  ep.n_peers = 0;
+  return gemm_dispatch(a, ep, reinterpret_cast<cudaStream_t>(stream));
+}
+
+OFB_API const char* ofb_last_error() { return ofb::last_error().c_str(); }
+
+// Reads (and optionally clears) the device status block written by kernels whose bounded
+// waits gave up. Synchronises the device: call it at step boundaries, not per kernel.
+OFB_API int ofb_read_status(int clear, int* out_code, int* out_detail) {
+  int* p = ofb::device_status_ptr();
+  if (!p) return ofb::fail("no status block");
+  int h[2] = {0, 0};
+  OFB_CUDA_OK(cudaMemcpy(h, p, sizeof(h), cudaMemcpyDeviceToHost));
+  if (out_code) *out_code = h[0];
+  if (out_detail) *out_detail = h[1];
+  if (clear && (h[0] || h[1])) OFB_CUDA_OK(cudaMemset(p, 0, 64 * sizeof(int)));
+  return 0;
+}

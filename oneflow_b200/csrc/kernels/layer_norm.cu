@@ -1,0 +1,299 @@
+// LayerNorm forward / backward for bf16 activations (fp32 statistics), written for B200:
+// one CTA per row with the row held in registers as 16-byte vectors, so every element
+// is read from HBM exactly once per pass; the backward accumulates the gamma/beta
+// gradients of many rows in registers and leaves one partial row per CTA in a scratch
+// buffer that a second tiny kernel folds.
+//
+// Reference counterparts: oneflow/core/cuda/layer_norm.cuh (three-tier dispatch) and
+// oneflow/user/kernels/layer_norm_gpu_kernel.cu (layer_norm :330, layer_norm_grad :376,
+// layer_norm_param_grad :454).
+#include "../common/host_utils.h"
+#include "../common/ptx.cuh"
+#include "ofb_kernels.h"
+
+namespace ofb {
+
+constexpr int kLnMaxVecPerThread = 4;  // 4 x 8 elements x up to 1024 threads = 32768 columns
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Block-wide sum of two values at once; `red` holds 2*32 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
+  __syncthreads();
+  float x = lane < nw ? red[lane] : 0.f, y = lane < nw ? red[32 + lane] : 0.f;
+  a = warp_sum(x);
+  b = warp_sum(y);
+}
+
+template <int NV>
+__global__ void __launch_bounds__(NV == 4 ? 1024 : 256)
+layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                      const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                      float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols, float eps) {
+  __shared__ float red[64];
+  const int nvec = cols >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * cols);
+    float v[NV][8];
+    float s = 0.f, dummy = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        uint4 p = xr[vi];
+        const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          v[i][2 * j] = f.x; v[i][2 * j + 1] = f.y;
+          s += f.x + f.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      }
+    }
+    block_sum2(s, dummy, red);
+    const float mean = s / cols;
+    float q = 0.f;
+    dummy = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; q += d * d; }
+      }
+    }
+    block_sum2(q, dummy, red);
+    const float rstd = rsqrtf(q / cols + eps);
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<long long>(row) * cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float g[8], b[8];
+        if (gamma) {
+          uint4 p = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+          const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); g[2 * j] = f.x; g[2 * j + 1] = f.y; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = 1.f;
+        }
+        if (beta) {
+          uint4 p = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+          const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); b[2 * j] = f.x; b[2 * j + 1] = f.y; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) b[j] = 0.f;
+        }
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ow[j] = pack_bf16x2((v[i][2 * j] - mean) * rstd * g[2 * j] + b[2 * j],
+                              (v[i][2 * j + 1] - mean) * rstd * g[2 * j + 1] + b[2 * j + 1]);
+        yr[vi] = o;
+      }
+    }
+  }
+}
+
+// dx = rstd * (g*dy - mean_c(g*dy) - xhat * mean_c(g*dy*xhat)); each CTA also accumulates
+// sum_rows(dy*xhat) and sum_rows(dy) for its rows and writes them to partial[blockIdx.x].
+template <int NV>
+__global__ void __launch_bounds__(NV == 4 ? 1024 : 256)
+layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ add_to_dx,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ partial_dgamma,
+                      float* __restrict__ partial_dbeta, int rows, int cols) {
+  __shared__ float red[64];
+  const int nvec = cols >> 3;
+  float acc_g[NV][8], acc_b[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc_g[i][j] = 0.f; acc_b[i][j] = 0.f; }
+  float g[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (gamma && vi < nvec) {
+      uint4 p = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+      const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); g[i][2 * j] = f.x; g[i][2 * j + 1] = f.y; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[i][j] = 1.f;
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long off = static_cast<long long>(row) * cols;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + off);
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NV][8], gd[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        uint4 px = xr[vi], pd = dyr[vi];
+        const uint32_t wx[4] = {px.x, px.y, px.z, px.w};
+        const uint32_t wd[4] = {pd.x, pd.y, pd.z, pd.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 fx = unpack_bf16x2(wx[j]), fd = unpack_bf16x2(wd[j]);
+          float h0 = (fx.x - mu) * rs, h1 = (fx.y - mu) * rs;
+          xh[i][2 * j] = h0; xh[i][2 * j + 1] = h1;
+          acc_g[i][2 * j] += fd.x * h0; acc_g[i][2 * j + 1] += fd.y * h1;
+          acc_b[i][2 * j] += fd.x; acc_b[i][2 * j + 1] += fd.y;
+          float a0 = fd.x * g[i][2 * j], a1 = fd.y * g[i][2 * j + 1];
+          gd[i][2 * j] = a0; gd[i][2 * j + 1] = a1;
+          s1 += a0 + a1;
+          s2 += a0 * h0 + a1 * h1;
+        }
+      }
+    }
+    block_sum2(s1, s2, red);
+    const float m1 = s1 / cols, m2 = s2 / cols;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + off);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = rs * (gd[i][j] - m1 - xh[i][j] * m2);
+        if (add_to_dx) {
+          uint4 pa = reinterpret_cast<const uint4*>(add_to_dx + off)[vi];
+          const uint32_t wa[4] = {pa.x, pa.y, pa.z, pa.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(wa[j]); r[2 * j] += f.x; r[2 * j + 1] += f.y; }
+        }
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ow[j] = pack_bf16x2(r[2 * j], r[2 * j + 1]);
+        dxr[vi] = o;
+      }
+    }
+  }
+  if (partial_dgamma) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        float* pg = partial_dgamma + static_cast<long long>(blockIdx.x) * cols + vi * 8;
+        float* pb = partial_dbeta + static_cast<long long>(blockIdx.x) * cols + vi * 8;
+        *reinterpret_cast<float4*>(pg) = make_float4(acc_g[i][0], acc_g[i][1], acc_g[i][2], acc_g[i][3]);
+        *reinterpret_cast<float4*>(pg + 4) = make_float4(acc_g[i][4], acc_g[i][5], acc_g[i][6], acc_g[i][7]);
+        *reinterpret_cast<float4*>(pb) = make_float4(acc_b[i][0], acc_b[i][1], acc_b[i][2], acc_b[i][3]);
+        *reinterpret_cast<float4*>(pb + 4) = make_float4(acc_b[i][4], acc_b[i][5], acc_b[i][6], acc_b[i][7]);
+      }
+    }
+  }
+}
+
+// Folds partial[nparts, cols] into out[cols] (fp32, optionally accumulating) - one thread per column.
+__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb,
+                                     float* __restrict__ outa, float* __restrict__ outb, int nparts, int cols,
+                                     int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    a += pa[static_cast<long long>(p) * cols + c];
+    b += pb[static_cast<long long>(p) * cols + c];
+  }
+  if (accumulate) { a += outa[c]; b += outb[c]; }
+  outa[c] = a;
+  outb[c] = b;
+}
+
+static int ln_block_threads(int cols, int& nv) {
+  const int nvec = cols / 8;
+  nv = 1;
+  while (nv < kLnMaxVecPerThread && (nvec + nv - 1) / nv > 256) nv *= 2;  // aim for <=256 threads
+  int threads = (nvec + nv - 1) / nv;
+  if (threads > 1024) { nv = kLnMaxVecPerThread; threads = (nvec + nv - 1) / nv; }
+  threads = ((threads + 31) / 32) * 32;
+  return threads;
+}
+
+}  // namespace ofb
+
+using namespace ofb;
+
+OFB_API int ofb_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                               int rows, int cols, float eps, void* stream) {
+  if (cols % 8 != 0 || cols > 8 * kLnMaxVecPerThread * 1024) return fail("layer_norm: cols must be a multiple of 8 and <= 32768");
+  if (rows <= 0) return 0;
+  int nv;
+  const int threads = ln_block_threads(cols, nv);
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto B = reinterpret_cast<const __nv_bfloat16*>(beta);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  switch (nv) {
+    case 1: layer_norm_fwd_kernel<1><<<grid, threads, 0, s>>>(X, G, B, Y, mean, rstd, rows, cols, eps); break;
+    case 2: layer_norm_fwd_kernel<2><<<grid, threads, 0, s>>>(X, G, B, Y, mean, rstd, rows, cols, eps); break;
+    default: layer_norm_fwd_kernel<4><<<grid, threads, 0, s>>>(X, G, B, Y, mean, rstd, rows, cols, eps); break;
+  }
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Number of partial rows ofb_layer_norm_bwd writes: scratch must hold 2 * this * cols floats.
+OFB_API int ofb_layer_norm_bwd_parts(int rows) { return rows < 296 ? rows : 296; }
+
+OFB_API int ofb_layer_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                               const void* add_to_dx, void* dx, float* dgamma, float* dbeta, float* scratch,
+                               int accumulate_param_grads, int rows, int cols, void* stream) {
+  if (cols % 8 != 0 || cols > 8 * kLnMaxVecPerThread * 1024) return fail("layer_norm_bwd: cols must be a multiple of 8 and <= 32768");
+  if (rows <= 0) return 0;
+  if (dgamma && !scratch) return fail("layer_norm_bwd: scratch required for parameter gradients");
+  int nv;
+  const int threads = ln_block_threads(cols, nv);
+  const int grid = ofb_layer_norm_bwd_parts(rows);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  float* pg = dgamma ? scratch : nullptr;
+  float* pb = dgamma ? scratch + static_cast<long long>(grid) * cols : nullptr;
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto AD = reinterpret_cast<const __nv_bfloat16*>(add_to_dx);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  switch (nv) {
+    case 1: layer_norm_bwd_kernel<1><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+    case 2: layer_norm_bwd_kernel<2><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+    default: layer_norm_bwd_kernel<4><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+  }
+  OFB_CUDA_OK(cudaGetLastError());
+  if (dgamma) {
+    fold_partials_kernel<<<(cols + 127) / 128, 128, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
+    OFB_CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}
