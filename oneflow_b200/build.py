@@ -1,0 +1,102 @@
+"""Builds the native libraries in-tree (``oneflow_b200/lib``).
+
+``python -m oneflow_b200.build`` compiles every CUDA source for sm_100a with nvcc and the
+C++ runtime with g++. Objects are cached by source mtime so rebuilds are incremental.
+The libraries are plain shared objects with a C ABI bound through ctypes, so no PyTorch
+headers are needed and a full build takes about a minute.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(ROOT, "csrc")
+LIB = os.path.join(ROOT, "lib")
+OBJ = os.path.join(ROOT, "build")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+
+
+def _nvcc():
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found")
+    return exe
+
+
+def _newer(src, obj, deps):
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    return any(os.path.getmtime(d) > t for d in [src] + deps)
+
+
+def _run(cmd, log):
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    with open(log, "w") as f:
+        f.write(" ".join(cmd) + "\n" + p.stdout)
+    if p.returncode != 0:
+        raise RuntimeError(f"build failed: {' '.join(cmd)}\n{p.stdout[-4000:]}")
+    return p.stdout
+
+
+def build_kernels(verbose=False, jobs=None):
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")) + glob.glob(os.path.join(CSRC, "comm", "*.cu")))
+    headers = glob.glob(os.path.join(CSRC, "**", "*.h"), recursive=True) + glob.glob(
+        os.path.join(CSRC, "**", "*.cuh"), recursive=True)
+    nvcc = _nvcc()
+    objs, todo = [], []
+    for s in srcs:
+        o = os.path.join(OBJ, os.path.relpath(s, CSRC).replace(os.sep, "_") + ".o")
+        objs.append(o)
+        if _newer(s, o, headers):
+            todo.append((s, o))
+    def compile_one(so):
+        s, o = so
+        out = _run([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", s, "-o", o], o + ".log")
+        if verbose:
+            print(out)
+        return s
+    with concurrent.futures.ThreadPoolExecutor(max_workers=jobs or min(8, os.cpu_count() or 4)) as ex:
+        for s in ex.map(compile_one, todo):
+            print(f"[build] compiled {os.path.relpath(s, ROOT)}", flush=True)
+    lib = os.path.join(LIB, "libofb_kernels.so")
+    if todo or not os.path.exists(lib):
+        _run([nvcc, "-shared", "-o", lib] + objs + ["-lcudart"], os.path.join(OBJ, "link_kernels.log"))
+        print(f"[build] linked {os.path.relpath(lib, ROOT)}", flush=True)
+    return lib
+
+
+def build_core(verbose=False):
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "core", "*.cpp")))
+    if not srcs:
+        return None
+    headers = glob.glob(os.path.join(CSRC, "core", "*.h"))
+    lib = os.path.join(LIB, "libofb_core.so")
+    if os.path.exists(lib) and not any(_newer(s, lib, headers) for s in srcs):
+        return lib
+    cxx = shutil.which("g++") or "g++"
+    _run([cxx] + CXX_FLAGS + ["-shared", "-o", lib] + srcs + ["-lrt", "-ldl"], os.path.join(OBJ, "core.log"))
+    print(f"[build] built {os.path.relpath(lib, ROOT)}", flush=True)
+    return lib
+
+
+def build_all(verbose=False):
+    return [build_kernels(verbose), build_core(verbose)]
+
+
+if __name__ == "__main__":
+    build_all(verbose="-v" in sys.argv)

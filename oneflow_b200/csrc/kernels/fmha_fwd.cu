@@ -1,0 +1,358 @@
+// Fused multi-head attention forward for sm_100a (bf16, head dim 64 or 128, causal or
+// full, optional per-batch key length for padding).
+//
+// One CTA owns a 128-row query tile of one (batch, head). Roles:
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles through a 2-stage ring
+//   warp 1      tcgen05 issuer: S_j = Q K_j^T and O_j = P_j V_j, accumulators in TMEM
+//   warps 2..5  softmax: thread t owns query row t; it reads its S row with tcgen05.ld
+//               (no shuffles needed), keeps the running max / sum, writes P_j (bf16) to shared
+//               memory in the 128-byte-swizzled K-major layout the second MMA consumes, and
+//               folds O_j into its register accumulator with the usual rescaling.
+// S and O_j are double-buffered in TMEM (2 x 128 + 2 x D columns) so the tensor core works on
+// tile j+1 while the softmax warps are busy with tile j.
+//
+// Reference counterparts: oneflow/user/kernels/scaled_dot_product_attention_kernel.cu (flash
+// attention library call), fused_attention_kernels.cu :710 (CUTLASS fMHA, no sm_100 path) and the
+// unfused fused_tril_scale_softmax_mask_scale chain.
+#include "../common/host_utils.h"
+#include "../common/ptx.cuh"
+#include "ofb_kernels.h"
+
+namespace ofb {
+
+struct FmhaFwdParams {
+  __nv_bfloat16* out;   // [B, S, H, D] contiguous
+  float* lse;           // [B, H, S] natural-log sum-exp of the scaled scores
+  const int* kv_len;    // [B] number of valid keys per batch or null
+  int B, H, S, D;
+  int causal;
+  float scale_log2e;    // softmax scale * log2(e)
+  int* status;
+};
+
+template <int D>
+struct FmhaFwdCfg {
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int Q_BYTES = BM * D * 2;
+  static constexpr int KV_BYTES = BN * D * 2;
+  static constexpr int P_BYTES = BM * BN * 2;
+  static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, FmhaFwdParams p) {
+  using Cfg = FmhaFwdCfg<D>;
+  constexpr int BM = 128, BN = 128, DCH = D / 64;  // 64-element chunks along the head dimension
+  constexpr uint32_t IDESC_S = make_idesc_bf16(BM, BN, 0, 0);
+  constexpr uint32_t IDESC_O = make_idesc_bf16(BM, D, 0, 1);
+  constexpr int CH_BYTES = 128 * 128;  // one [128 rows x 64 elements] swizzled chunk
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::Q_BYTES;            // 2 stages
+  uint8_t* sV = sK + 2 * Cfg::KV_BYTES;       // 2 stages
+  uint8_t* sP = sV + 2 * Cfg::KV_BYTES;       // 2 buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * Cfg::P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* v_full = bars + 3;     // [2]
+  uint64_t* kv_empty = bars + 5;   // [2]
+  uint64_t* s_full = bars + 7;     // [2]
+  uint64_t* p_full = bars + 9;     // [2]
+  uint64_t* o_full = bars + 11;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Heavier (later) causal tiles first.
+  const int n_qt = (p.S + BM - 1) / BM;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * BM;
+  int kv_limit = p.S;
+  if (p.kv_len) kv_limit = min(kv_limit, p.kv_len[b]);
+  int kv_end = kv_limit;
+  if (p.causal) kv_end = min(kv_end, q0 + BM);
+  const int n_kv = (kv_end + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_full[s], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;            // S[0], S[1] at +0, +128
+  const uint32_t tO = tmem_base + 256;      // O[0], O[1] at +0, +D
+
+  if (warp == 0) {
+    if (elect_one() && n_kv > 0) {
+      mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) tma_load_4d(sQ + c * CH_BYTES, &tmQ, q_full, c * 64, h, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&k_full[s], Cfg::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sK + s * Cfg::KV_BYTES + c * CH_BYTES, &tmK, &k_full[s], c * 64, h, j * BN, b);
+        mbar_arrive_expect_tx(&v_full[s], Cfg::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sV + s * Cfg::KV_BYTES + c * CH_BYTES, &tmV, &v_full[s], c * 64, h, j * BN, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one() && n_kv > 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      const uint32_t q_base = smem_u32(sQ);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t k_base = smem_u32(sK + s * Cfg::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * CH_BYTES + (kk & 3) * 32;
+          umma_bf16_ss(tS + s * BN, make_smem_desc_sw128(q_base + off, 16, 1024),
+                       make_smem_desc_sw128(k_base + off, 16, 1024), IDESC_S, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+      };
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+      if (ok) { tc_fence_after(); issue_s(0); }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_kv) {
+          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(&p_full[s], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t p_base = smem_u32(sP + s * Cfg::P_BYTES);
+        const uint32_t v_base = smem_u32(sV + s * Cfg::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(p_base + (kk >> 2) * CH_BYTES + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(v_base + kk * 2048, CH_BYTES, 1024);
+          umma_bf16_ss(tO + s * D, da, db, IDESC_O, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[s]);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+    __syncwarp();
+  } else if (n_kv > 0) {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
+    const int row_g = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[s], ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int col_base = j * BN;
+      // A tile needs element-wise masking if it crosses the causal diagonal or the key-length limit.
+      const bool need_mask = (p.causal && col_base + BN - 1 > q0) || (col_base + BN > kv_limit);
+      const int col_max = p.causal ? min(row_g, kv_limit - 1) : kv_limit - 1;  // last visible column
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = __uint_as_float(v[i]);
+          if (need_mask && col_base + c * 32 + i > col_max) e = -INFINITY;
+          mx = fmaxf(mx, e);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * p.scale_log2e);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);  // m_run = -inf gives 0
+      float rowsum = 0.f;
+      uint8_t* p_row = sP + s * Cfg::P_BYTES + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, v);
+        tmem_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = __uint_as_float(v[i]) * p.scale_log2e - m_use;
+          float e1 = __uint_as_float(v[i + 1]) * p.scale_log2e - m_use;
+          float p0 = exp2f(e0), p1 = exp2f(e1);
+          if (need_mask) {
+            if (col_base + c * 32 + i > col_max) p0 = 0.f;
+            if (col_base + c * 32 + i + 1 > col_max) p1 = 0.f;
+          }
+          rowsum += p0 + p1;
+          packed[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        // 32 columns = four 16-byte groups inside the 64-column chunk (c >> 1)
+        uint8_t* chunk = p_row + (c >> 1) * CH_BYTES;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int grp = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(chunk + ((grp ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
+      }
+      l_run = l_run * alpha + rowsum;
+      m_run = m_new;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full[s]);
+      if (j > 0) {
+        const int so = (j - 1) & 1;
+        if (!mbar_wait(&o_full[so], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(tO + lane_addr + so * D + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+      }
+      alpha_prev = alpha;
+    }
+    if (ok) {
+      const int so = (n_kv - 1) & 1;
+      ok = mbar_wait(&o_full[so], ((n_kv - 1) >> 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(tO + lane_addr + so * D + c * 32, v);
+          tmem_wait_ld();
+          if (row_g < p.S) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                f[i] = (o_acc[c * 32 + g * 8 + i] * alpha_prev + __uint_as_float(v[g * 8 + i])) * inv;
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
+                  make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                             pack_bf16x2(f[6], f[7]));
+            }
+          }
+        }
+        if (row_g < p.S && p.lse)
+          p.lse[(static_cast<long long>(b) * p.H + h) * p.S + row_g] =
+              l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  } else {
+    // No visible keys at all (kv_len == 0): the output rows are zero.
+    const int r = (warp & 3) * 32 + lane;
+    const int row_g = q0 + r;
+    if (row_g < p.S) {
+      __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
+      for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
+      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.S + row_g] = -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, (int)kStatusMbarTimeout);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+template <int D>
+static int launch_fmha_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FmhaFwdParams& p,
+                           cudaStream_t stream) {
+  using Cfg = FmhaFwdCfg<D>;
+  auto kern = fmha_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid((p.S + 127) / 128, p.H, p.B);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// 4-D map over a [B, S, H, D] view with a token stride of `row_stride` elements.
+int fmha_tensor_map(CUtensorMap* out, const void* ptr, int B, int S, int H, int D, long long row_stride) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail("cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride * 2) % 16) return fail("fmha: operands must be 16-byte aligned");
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride * 2, (cuuint64_t)row_stride * 2 * S};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("fmha: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return 0;
+}
+
+}  // namespace ofb
+
+using namespace ofb;
+
+// q, k, v: bf16 views [B, S, H, D] whose element (b, s, h, d) sits at ((b*S + s) * row_stride + h*D + d).
+OFB_API int ofb_fmha_fwd(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
+                         void* out, float* lse, const int* kv_len, int B, int S, int H, int D, int causal, float scale,
+                         void* stream) {
+  if (D != 64 && D != 128) return fail("fmha: head dim must be 64 or 128");
+  CUtensorMap tq, tk, tv;
+  if (fmha_tensor_map(&tq, q, B, S, H, D, q_row_stride)) return -1;
+  if (fmha_tensor_map(&tk, k, B, S, H, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tv, v, B, S, H, D, kv_row_stride)) return -1;
+  FmhaFwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse; p.kv_len = kv_len; p.B = B; p.H = H; p.S = S; p.D = D; p.causal = causal;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = device_status_ptr();
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  return D == 64 ? launch_fmha_fwd<64>(tq, tk, tv, p, s) : launch_fmha_fwd<128>(tq, tk, tv, p, s);
+}

@@ -1,0 +1,225 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 statement of the op."""
+import math
+
+import pytest
+import torch
+
+from oneflow_b200.ops import gemm as G
+from oneflow_b200.ops import kernels as K
+from oneflow_b200.ops import _native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    scale = b.abs().max().item() + 1e-6
+    err = (a - b).abs().max().item()
+    assert err <= atol * max(1.0, scale) + rtol * scale * 0.5, f"max err {err} (scale {scale})"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    torch.cuda.synchronize()
+    assert _native.read_status() == (0, 0)
+
+
+@pytest.mark.parametrize("al,bl", [("mk", "nk"), ("mk", "kn"), ("km", "nk"), ("km", "kn")])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (520, 392, 264), (2048, 1024, 512)])
+def test_gemm_layouts(al, bl, shape):
+    M, N, K_ = shape
+    torch.manual_seed(1)
+    a = torch.randn((M, K_) if al == "mk" else (K_, M), device=DEV, dtype=BF)
+    b = torch.randn((N, K_) if bl == "nk" else (K_, N), device=DEV, dtype=BF)
+    out = G.gemm(a, b, a_layout=al, b_layout=bl)
+    ref = G.gemm_reference(a.cpu(), b.cpu(), al, bl)
+    close(out, ref)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_epilogues(bn):
+    torch.manual_seed(2)
+    M, N, K_ = 384, 512, 256
+    a = torch.randn(M, K_, device=DEV, dtype=BF)
+    b = torch.randn(N, K_, device=DEV, dtype=BF)
+    bias = torch.randn(N, device=DEV, dtype=BF)
+    res = torch.randn(M, N, device=DEV, dtype=BF)
+    for act in (1, 2, 3):
+        out, aux = G.gemm(a, b, bias=bias, act=act, residual=res, want_aux=True, bn=bn)
+        ref, raux = G.gemm_reference(a.cpu(), b.cpu(), bias=bias.cpu(), act=act, residual=res.cpu(), want_aux=True)
+        close(out, ref)
+        close(aux, raux)
+        out = G.gemm(a, b, aux_in=res, act=act, bn=bn)
+        close(out, G.gemm_reference(a.cpu(), b.cpu(), aux_in=res.cpu(), act=act))
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref = G.gemm_reference(a.cpu(), b.cpu(), out=acc.cpu().clone(), accumulate=True, out_dtype=torch.float32, alpha=0.5)
+    out = G.gemm(a, b, out=acc, accumulate=True, alpha=0.5, bn=bn)
+    close(out, ref)
+
+
+@pytest.mark.parametrize("cols", [64, 1024, 4096, 8192])
+def test_layer_norm(cols):
+    torch.manual_seed(3)
+    rows = 515
+    x = torch.randn(rows, cols, device=DEV, dtype=BF) * 2 + 0.5
+    g = torch.randn(cols, device=DEV, dtype=BF)
+    b = torch.randn(cols, device=DEV, dtype=BF)
+    y, mean, rstd = K.layer_norm_fwd(x, g, b, 1e-5)
+    ry, rmean, rrstd = K.layer_norm_fwd(x.cpu(), g.cpu(), b.cpu(), 1e-5)
+    close(y, ry)
+    close(mean, rmean, 1e-3, 1e-3)
+    close(rstd, rrstd, 1e-3, 1e-3)
+    ref = torch.nn.functional.layer_norm(x.float().cpu(), (cols,), g.float().cpu(), b.float().cpu(), 1e-5)
+    close(y, ref)
+    dy = torch.randn(rows, cols, device=DEV, dtype=BF)
+    add = torch.randn(rows, cols, device=DEV, dtype=BF)
+    dx, dg, db = K.layer_norm_bwd(dy, x, g, mean, rstd, add_to_dx=add)
+    rdx, rdg, rdb = K.layer_norm_bwd(dy.cpu(), x.cpu(), g.cpu(), rmean, rrstd, add_to_dx=add.cpu())
+    close(dx, rdx)
+    close(dg, rdg, 2e-2, 5e-2)
+    close(db, rdb, 2e-2, 5e-2)
+
+
+@pytest.mark.parametrize("act", [1, 2, 3])
+def test_bias_act(act):
+    torch.manual_seed(4)
+    x = torch.randn(300, 1024, device=DEV, dtype=BF)
+    b = torch.randn(1024, device=DEV, dtype=BF)
+    dy = torch.randn(300, 1024, device=DEV, dtype=BF)
+    close(K.bias_act_fwd(x, b, act), K.bias_act_fwd(x.cpu(), b.cpu(), act))
+    close(K.bias_act_bwd(x, b, dy, act), K.bias_act_bwd(x.cpu(), b.cpu(), dy.cpu(), act))
+
+
+def test_bias_mask_scale_and_dropout_mask():
+    torch.manual_seed(5)
+    x = torch.randn(257, 512, device=DEV, dtype=BF)
+    b = torch.randn(512, device=DEV, dtype=BF)
+    add = torch.randn(257, 512, device=DEV, dtype=BF)
+    mask = K.dropout_mask(x.shape, 0.1, seed=1234, device=DEV)
+    keep = mask.float().mean().item()
+    assert abs(keep - 0.9) < 0.01
+    mask2 = K.dropout_mask(x.shape, 0.1, seed=1234, device=DEV)
+    assert torch.equal(mask, mask2)
+    y = K.bias_mask_scale(x, b, mask, 1 / 0.9, add)
+    close(y, K.bias_mask_scale(x.cpu(), b.cpu(), mask.cpu(), 1 / 0.9, add.cpu()))
+
+
+def test_cast_scale_column_sum():
+    torch.manual_seed(6)
+    x = torch.randn(1000, 776, device=DEV, dtype=BF)
+    st = torch.tensor([0.25], device=DEV)
+    y = K.cast_scale(x, 2.0, torch.float32, st)
+    close(y, x.float().cpu() * 0.5, 1e-3, 1e-3)
+    close(K.column_sum(x), x.float().cpu().sum(0), 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("cols", [128, 512, 2048])
+def test_softmax_tril(cols):
+    torch.manual_seed(7)
+    x = torch.randn(2, 3, cols, cols, device=DEV, dtype=BF)
+    mask = K.dropout_mask(x.shape, 0.1, seed=7, device=DEV)
+    y, sm = K.softmax_fwd(x, scale=0.125, tril=True, dropout_mask=mask, dropout_scale=1 / 0.9, want_softmax=True)
+    ry, rsm = K.softmax_fwd(x.cpu(), scale=0.125, tril=True, dropout_mask=mask.cpu(), dropout_scale=1 / 0.9,
+                            want_softmax=True)
+    close(y, ry)
+    close(sm, rsm)
+    dy = torch.randn_like(x)
+    dx = K.softmax_bwd(sm, dy, scale=0.125, tril=True, dropout_mask=mask, dropout_scale=1 / 0.9)
+    rdx = K.softmax_bwd(rsm, dy.cpu(), scale=0.125, tril=True, dropout_mask=mask.cpu(), dropout_scale=1 / 0.9)
+    close(dx, rdx, 2e-2, 1e-3)
+
+
+def test_softmax_attn_mask():
+    torch.manual_seed(8)
+    B, H, S = 2, 4, 256
+    x = torch.randn(B, H, S, S, device=DEV, dtype=BF)
+    am = (torch.rand(S, S, device=DEV) > 0.2)
+    y = K.softmax_fwd(x, scale=0.5, attn_mask=am)
+    ry = K.softmax_fwd(x.cpu(), scale=0.5, attn_mask=am.cpu())
+    close(y, ry)
+
+
+@pytest.mark.parametrize("vocab", [1024, 50304])
+def test_xent(vocab):
+    torch.manual_seed(9)
+    rows = 300
+    logits = torch.randn(rows, vocab, device=DEV, dtype=BF) * 3
+    labels = torch.randint(0, vocab, (rows,), device=DEV)
+    labels[5] = -100
+    st = K.xent_stats(logits, labels)
+    loss, d = K.xent_grad(logits, labels, st, grad_scale=0.5)
+    ref = torch.nn.functional.cross_entropy(logits.float().cpu(), labels.cpu(), reduction="none", ignore_index=-100)
+    close(loss, ref, 1e-3, 1e-3)
+    lf = logits.float().cpu().requires_grad_(True)
+    torch.nn.functional.cross_entropy(lf, labels.cpu(), reduction="sum", ignore_index=-100).mul(0.5).backward()
+    close(d, lf.grad, 2e-2, 1e-3)
+    # vocabulary-sharded path: two shards merged
+    half = vocab // 2
+    p0 = K.xent_stats(logits[:, :half].contiguous(), labels, 0)
+    p1 = K.xent_stats(logits[:, half:].contiguous(), labels, half)
+    merged = K.xent_merge(torch.stack([p0, p1]))
+    close(merged[:, 2], st[:, 2], 1e-3, 1e-3)
+    l2, _ = K.xent_grad(logits[:, half:].contiguous(), labels, merged, vocab_start=half)
+    close(l2, ref, 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fmha_fwd(D, causal):
+    torch.manual_seed(10)
+    B, S, H = 2, 384, 3
+    qkv = torch.randn(B, S, 3, H, D, device=DEV, dtype=BF)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    out, lse = K.fmha_fwd(q, k, v, causal=causal)
+    ro, rl = K.fmha_reference(q.cpu(), k.cpu(), v.cpu(), causal, 1 / math.sqrt(D))
+    close(out, ro)
+    close(lse, rl, 1e-2, 1e-2)
+
+
+def test_fmha_fwd_padding_and_ragged():
+    torch.manual_seed(11)
+    B, S, H, D = 3, 200, 2, 64
+    q = torch.randn(B, S, H, D, device=DEV, dtype=BF)
+    k = torch.randn(B, S, H, D, device=DEV, dtype=BF)
+    v = torch.randn(B, S, H, D, device=DEV, dtype=BF)
+    kv_len = torch.tensor([200, 77, 130], dtype=torch.int32)
+    out, lse = K.fmha_fwd(q, k, v, causal=False, kv_len=kv_len)
+    ro, rl = K.fmha_reference(q.cpu(), k.cpu(), v.cpu(), False, 1 / math.sqrt(D), kv_len)
+    close(out, ro)
+    close(lse, rl, 1e-2, 1e-2)
+
+
+def test_multi_tensor_adamw_sgd_and_norm():
+    torch.manual_seed(12)
+    sizes = [1000, 65536 + 8, 300000, 16]
+    def mk(dt=torch.float32):
+        return [torch.randn(n, device=DEV, dtype=dt) for n in sizes]
+    w, g, m, v = mk(), mk(BF), [t.abs() * 0 for t in mk()], [t.abs() * 0 for t in mk()]
+    c = [torch.empty(n, device=DEV, dtype=BF) for n in sizes]
+    wc, gc, mc, vc = [[t.cpu().clone() for t in L] for L in (w, g, m, v)]
+    cc = [t.cpu().clone() for t in c]
+    kw = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, scale=0.5, step=3)
+    K.multi_tensor_adamw(g, w, c, m, v, **kw)
+    K.multi_tensor_adamw(gc, wc, cc, mc, vc, **kw)
+    for a, b in zip(w + m + v, wc + mc + vc):
+        close(a, b, 1e-3, 1e-4)
+    for a, b in zip(c, cc):  # bf16 copies: one rounding step apart at most
+        close(a, b, 1e-2, 1e-2)
+    # SGD momentum
+    w, g, m = mk(), mk(), [t * 0 for t in mk()]
+    wc, gc, mc = [[t.cpu().clone() for t in L] for L in (w, g, m)]
+    kw = dict(lr=0.1, momentum=0.9, nesterov=True, weight_decay=1e-4, l2=1e-3, scale=2.0)
+    K.multi_tensor_sgd(g, w, None, m, **kw)
+    K.multi_tensor_sgd(gc, wc, None, mc, **kw)
+    for a, b in zip(w + m, wc + mc):
+        close(a, b, 1e-3, 1e-4)
+    g[1][7] = float("inf")
+    out = K.multi_tensor_sqsum(g)
+    ref = K.multi_tensor_sqsum([t.cpu() for t in g])
+    close(out[:1], ref[:1], 1e-3, 1e-3)
+    assert int(out[1].item()) == 1
+    f, found, norm = K.clip_factor(out, 1.0)
+    assert int(found.item()) == 1 and f.item() <= 1.0
