@@ -1,0 +1,474 @@
+// Fused multi-head attention backward for sm_100a (bf16, head dim 64 or 128).
+//
+// One CTA owns a 128-key tile (K_j, V_j stay resident in shared memory) of one (batch, head)
+// and walks over the query tiles i that see it. Per (i, j) pair five tcgen05 products run,
+// all fed from the same shared-memory tiles without any transposition pass:
+//     S   = Q_i K_j^T            (K-major  x K-major)       -> TMEM
+//     dP  = dO_i V_j^T           (K-major  x K-major)       -> TMEM
+//     dV += P^T dO_i             (MN-major x MN-major)      -> TMEM accumulator
+//     dK += dS^T Q_i             (MN-major x MN-major)      -> TMEM accumulator
+//     dQ_i partial = dS K_j      (K-major  x MN-major)      -> TMEM, then fp32 red.add to HBM
+// The 128 compute threads own one query row each: they rebuild P from S and the saved
+// log-sum-exp, form dS = P * (dP - delta) * scale, and publish P / dS (bf16) through one
+// shared buffer in the 128-byte swizzled layout that serves both as K-major and MN-major
+// operand. TMEM: S | dP (reused for the dQ partial) | dV | dK = 512 columns at D = 128.
+//
+// Reference counterpart: oneflow/user/kernels/scaled_dot_product_attention_grad_kernel.cu
+// (flash-attention library call).
+#include "../common/host_utils.h"
+#include "../common/ptx.cuh"
+#include "ofb_kernels.h"
+
+namespace ofb {
+
+int fmha_tensor_map(CUtensorMap* out, const void* ptr, int B, int S, int H, int D, long long row_stride);
+
+struct FmhaBwdParams {
+  const float* lse;     // [B, H, S]
+  const float* delta;   // [B, H, S] rowsum(dO * O)
+  float* dq_acc;        // [B, S, H, D] fp32, zero-initialised, receives red.add
+  __nv_bfloat16* dk;    // element (b,s,h,d) at ((b*S+s)*dkv_row_stride + h*D + d)
+  __nv_bfloat16* dv;
+  long long dkv_row_stride;
+  const int* kv_len;
+  int B, H, S, D;
+  int causal;
+  float scale;          // softmax scale
+  float scale_log2e;
+  int* status;
+};
+
+template <int D>
+struct FmhaBwdCfg {
+  static constexpr int T_BYTES = 128 * D * 2;       // one [128 x D] tile
+  static constexpr int PDS_BYTES = 128 * 128 * 2;
+  static constexpr int SMEM_BYTES = 6 * T_BYTES + PDS_BYTES + 256 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, FmhaBwdParams p) {
+  using Cfg = FmhaBwdCfg<D>;
+  constexpr int DCH = D / 64;
+  constexpr int CH_BYTES = 128 * 128;
+  constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);   // S, dP
+  constexpr uint32_t IDESC_TT = make_idesc_bf16(128, D, 1, 1);    // dV, dK (both operands MN-major)
+  constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, D, 0, 1);    // dQ (A K-major, B MN-major)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::T_BYTES;
+  uint8_t* sQ = sV + Cfg::T_BYTES;          // 2 stages
+  uint8_t* sdO = sQ + 2 * Cfg::T_BYTES;     // 2 stages
+  uint8_t* sPdS = sdO + 2 * Cfg::T_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sPdS + Cfg::PDS_BYTES);
+  uint64_t* kv_full = bars;         // 1
+  uint64_t* q_full = bars + 1;      // [2]
+  uint64_t* q_empty = bars + 3;     // [2]
+  uint64_t* do_full = bars + 5;     // [2]
+  uint64_t* do_empty = bars + 7;    // [2]
+  uint64_t* s_full = bars + 9;
+  uint64_t* dp_full = bars + 10;
+  uint64_t* p_ready = bars + 11;    // count 128
+  uint64_t* dv_done = bars + 12;
+  uint64_t* ds_ready = bars + 13;   // count 128
+  uint64_t* dq_full = bars + 14;
+  uint64_t* dq_drained = bars + 15; // count 128
+  uint64_t* all_done = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int k0 = jt * 128;
+  const int n_qt = (p.S + 127) / 128;
+  int kv_limit = p.S;
+  if (p.kv_len) kv_limit = min(kv_limit, p.kv_len[b]);
+  const int i_start = p.causal ? jt : 0;
+  const bool tile_visible = k0 < kv_limit;
+  const int n_iter = tile_visible ? n_qt - i_start : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(dv_done, 1);
+    mbar_init(ds_ready, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 128);
+    mbar_init(all_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;
+  const uint32_t tdP = tmem_base + 128;   // also receives the dQ partial (first D columns)
+  const uint32_t tdV = tmem_base + 256;
+  const uint32_t tdK = tmem_base + 256 + D;
+
+  if (warp == 0) {
+    if (elect_one() && n_iter > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * Cfg::T_BYTES);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_4d(sK + c * CH_BYTES, &tmK, kv_full, c * 64, h, k0, b);
+        tma_load_4d(sV + c * CH_BYTES, &tmV, kv_full, c * 64, h, k0, b);
+      }
+      for (int t = 0; t < n_iter; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = ((t >> 1) & 1) ^ 1;
+        const int qrow = (i_start + t) * 128;
+        if (!mbar_wait(&q_empty[st], ph, abort_flag)) break;
+        mbar_arrive_expect_tx(&q_full[st], Cfg::T_BYTES);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sQ + st * Cfg::T_BYTES + c * CH_BYTES, &tmQ, &q_full[st], c * 64, h, qrow, b);
+        if (!mbar_wait(&do_empty[st], ph, abort_flag)) break;
+        mbar_arrive_expect_tx(&do_full[st], Cfg::T_BYTES);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sdO + st * Cfg::T_BYTES + c * CH_BYTES, &tmdO, &do_full[st], c * 64, h, qrow, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one() && n_iter > 0) {
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), pds_base = smem_u32(sPdS);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        const int st = t & 1;
+        const uint32_t ph2 = (t >> 1) & 1;  // phase of the 2-stage rings
+        const uint32_t ph1 = t & 1;         // phase of the once-per-iteration barriers
+        const uint32_t q_base = smem_u32(sQ + st * Cfg::T_BYTES);
+        const uint32_t do_base = smem_u32(sdO + st * Cfg::T_BYTES);
+        // S = Q_i K_j^T
+        if (!mbar_wait(&q_full[st], ph2, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * CH_BYTES + (kk & 3) * 32;
+          umma_bf16_ss(tS, make_smem_desc_sw128(q_base + off, 16, 1024), make_smem_desc_sw128(k_base + off, 16, 1024),
+                       IDESC_S, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+        // dP = dO_i V_j^T (its TMEM region held the previous dQ partial: wait until that was drained)
+        if (!mbar_wait(&do_full[st], ph2, abort_flag)) { ok = false; break; }
+        if (t > 0 && !mbar_wait(dq_drained, (t - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * CH_BYTES + (kk & 3) * 32;
+          umma_bf16_ss(tdP, make_smem_desc_sw128(do_base + off, 16, 1024), make_smem_desc_sw128(v_base + off, 16, 1024),
+                       IDESC_S, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(dp_full);
+        // dV += P^T dO_i : A = P as MN-major (M = keys, K = query rows), B = dO_i as MN-major (N = d)
+        if (!mbar_wait(p_ready, ph1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          umma_bf16_ss(tdV, make_smem_desc_sw128(pds_base + kk * 2048, CH_BYTES, 1024),
+                       make_smem_desc_sw128(do_base + kk * 2048, CH_BYTES, 1024), IDESC_TT, (t | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(dv_done);
+        umma_commit(&do_empty[st]);
+        // dK += dS^T Q_i ; dQ partial = dS K_j
+        if (!mbar_wait(ds_ready, ph1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          umma_bf16_ss(tdK, make_smem_desc_sw128(pds_base + kk * 2048, CH_BYTES, 1024),
+                       make_smem_desc_sw128(q_base + kk * 2048, CH_BYTES, 1024), IDESC_TT, (t | kk) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          umma_bf16_ss(tdP, make_smem_desc_sw128(pds_base + (kk >> 2) * CH_BYTES + (kk & 3) * 32, 16, 1024),
+                       make_smem_desc_sw128(k_base + kk * 2048, CH_BYTES, 1024), IDESC_DQ, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(dq_full);
+        umma_commit(&q_empty[st]);
+      }
+      if (ok) umma_commit(all_done);
+    }
+    __syncwarp();
+  } else if (n_iter > 0) {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* pds_row = sPdS + r * 128;
+    const float kLog2e = 1.4426950408889634f;
+    bool ok = true;
+    for (int t = 0; t < n_iter; ++t) {
+      const uint32_t ph1 = t & 1;
+      const int q0 = (i_start + t) * 128;
+      const int row_g = q0 + r;
+      const bool row_ok = row_g < p.S;
+      const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.S + row_g;
+      const float lse = row_ok ? p.lse[stat_idx] : -INFINITY;
+      const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+      const float lse2 = lse * kLog2e;
+      const bool dead_row = !row_ok || lse == -INFINITY;
+      const bool need_mask = (p.causal && k0 + 127 > q0) || (k0 + 128 > kv_limit);
+      const int col_max = p.causal ? min(row_g, kv_limit - 1) : kv_limit - 1;
+      uint32_t pk[64];  // P, later dS, as packed bf16 pairs for this row
+      if (!mbar_wait(s_full, ph1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(tS + lane_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2e - lse2);
+          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2e - lse2);
+          if (dead_row || (need_mask && k0 + c * 32 + i > col_max)) p0 = 0.f;
+          if (dead_row || (need_mask && k0 + c * 32 + i + 1 > col_max)) p1 = 0.f;
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+        }
+      }
+      // Publish P. The buffer is free: the MMAs that read dS of the previous iteration were
+      // covered by the dq_full wait below in that iteration.
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        uint8_t* chunk = pds_row + (g >> 3) * CH_BYTES;
+        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) =
+            make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+      // dS = P * (dP - delta) * scale
+      if (!mbar_wait(dp_full, ph1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(tdP + lane_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float2 pp = unpack_bf16x2(pk[c * 16 + (i >> 1)]);
+          float d0 = pp.x * (__uint_as_float(v[i]) - delta) * p.scale;
+          float d1 = pp.y * (__uint_as_float(v[i + 1]) - delta) * p.scale;
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(d0, d1);
+        }
+      }
+      tc_fence_before();
+      if (!mbar_wait(dv_done, ph1, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        uint8_t* chunk = pds_row + (g >> 3) * CH_BYTES;
+        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) =
+            make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_ready);
+      // Drain the dQ partial of this pair into the fp32 accumulator.
+      if (!mbar_wait(dq_full, ph1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(tdP + lane_addr + c * 32, v);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(dq_row + c * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                       __uint_as_float(v[i + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_drained);
+    }
+    // dK, dV of this key tile: TMEM lane = key row
+    if (ok) ok = mbar_wait(all_done, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int krow = k0 + r;
+      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = which == 0 ? tdK : tdV;
+        __nv_bfloat16* dst = which == 0 ? dk_row : dv_row;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(src + lane_addr + c * 32, v);
+          tmem_wait_ld();
+          if (krow < p.S) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(
+                  pack_bf16x2(__uint_as_float(v[g * 8]), __uint_as_float(v[g * 8 + 1])),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+          }
+        }
+      }
+    }
+  } else {
+    // Key tile invisible to every query (beyond kv_len): zero gradients.
+    const int r = (warp & 3) * 32 + lane;
+    const int krow = k0 + r;
+    if (krow < p.S) {
+      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+      for (int i = 0; i < D; i += 8) {
+        *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, (int)kStatusMbarTimeout);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row.
+__global__ void fmha_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int S, int H, int D) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * H;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % H);
+  const long long bs = w / H;
+  const int s = static_cast<int>(bs % S);
+  const int b = static_cast<int>(bs / S);
+  const __nv_bfloat16* po = o + w * D;
+  const __nv_bfloat16* pd = d_o + w * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + i));
+    float2 c = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + i));
+    acc += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+}
+
+// dq (bf16, strided rows) = cast(dq_acc fp32 [B*S, H*D])
+__global__ void fmha_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int hd,
+                                    long long row_stride) {
+  const int vec_per_row = hd >> 3;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(acc + row * hd + c);
+    const float4 bb = *reinterpret_cast<const float4*>(acc + row * hd + c + 4);
+    *reinterpret_cast<uint4*>(dq + row * row_stride + c) =
+        make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(bb.x, bb.y), pack_bf16x2(bb.z, bb.w));
+  }
+}
+
+template <int D>
+static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                           const FmhaBwdParams& p, cudaStream_t stream) {
+  using Cfg = FmhaBwdCfg<D>;
+  auto kern = fmha_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid((p.S + 127) / 128, p.H, p.B);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace ofb
+
+using namespace ofb;
+
+// Floats of scratch the backward needs: B*S*H*D for the fp32 dQ accumulator + B*H*S for delta.
+OFB_API long long ofb_fmha_bwd_scratch_floats(int B, int S, int H, int D) {
+  return static_cast<long long>(B) * S * H * D + static_cast<long long>(B) * H * S;
+}
+
+// q,k,v: [B,S,H,D] views (token strides q_row_stride / kv_row_stride); o, d_o: contiguous [B,S,H,D];
+// dq,dk,dv: [B,S,H,D] views with token stride dqkv_row_stride (e.g. slices of one packed buffer).
+OFB_API int ofb_fmha_bwd(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
+                         const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                         long long dqkv_row_stride, float* scratch, const int* kv_len, int B, int S, int H, int D,
+                         int causal, float scale, void* stream) {
+  if (D != 64 && D != 128) return fail("fmha_bwd: head dim must be 64 or 128");
+  if (dqkv_row_stride % 8) return fail("fmha_bwd: gradient row stride must be a multiple of 8");
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv, tdo;
+  if (fmha_tensor_map(&tq, q, B, S, H, D, q_row_stride)) return -1;
+  if (fmha_tensor_map(&tk, k, B, S, H, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tv, v, B, S, H, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tdo, d_o, B, S, H, D, static_cast<long long>(H) * D)) return -1;
+  const long long n_acc = static_cast<long long>(B) * S * H * D;
+  float* dq_acc = scratch;
+  float* delta = scratch + n_acc;
+  OFB_CUDA_OK(cudaMemsetAsync(dq_acc, 0, n_acc * sizeof(float), s));
+  {
+    const long long rows = static_cast<long long>(B) * S * H;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    fmha_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
+    OFB_CUDA_OK(cudaGetLastError());
+  }
+  FmhaBwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk); p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.dkv_row_stride = dqkv_row_stride; p.kv_len = kv_len;
+  p.B = B; p.H = H; p.S = S; p.D = D; p.causal = causal; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = device_status_ptr();
+  int rc = D == 64 ? launch_fmha_bwd<64>(tq, tk, tv, tdo, p, s) : launch_fmha_bwd<128>(tq, tk, tv, tdo, p, s);
+  if (rc) return rc;
+  {
+    const long long rows = static_cast<long long>(B) * S;
+    const long long total = rows * (H * D / 8);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    fmha_dq_cast_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), rows,
+                                                                     H * D, dqkv_row_stride);
+    OFB_CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}

@@ -517,3 +517,44 @@ def clip_factor(sq_and_bad, max_norm):
           "clip_factor")
     _count()
     return factor, found, norm
+
+
+def fmha_bwd_reference(q, k, v, o, d_o, lse, causal, scale, kv_len=None):
+    """fp32 PyTorch attention backward on [B,S,H,D] tensors -> (dq, dk, dv)."""
+    B, S, H, D = q.shape
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    with torch.enable_grad():
+        out, _ = fmha_reference(qf, kf, vf, causal, scale, kv_len)
+        out.backward(d_o.float())
+    return qf.grad.to(q.dtype), kf.grad.to(q.dtype), vf.grad.to(q.dtype)
+
+
+def fmha_bwd(q, k, v, o, d_o, lse, causal=False, scale=None, kv_len=None, dqkv=None):
+    """Fused attention backward. Returns (dq, dk, dv) as [B,S,H,D] views of one packed [B,S,3,H,D] buffer
+    (``dqkv`` if given), so that the QKV projection's backward consumes a single matrix."""
+    B, S, H, D = q.shape
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        dq, dk, dv = fmha_bwd_reference(q, k, v, o, d_o, lse, causal, scale, kv_len)
+        if dqkv is None:
+            dqkv = torch.empty((B, S, 3, H, D), dtype=q.dtype)
+        dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2] = dq, dk, dv
+        return dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    qs, ks, vs = _bshd_stride(q, "q"), _bshd_stride(k, "k"), _bshd_stride(v, "v")
+    if ks != vs:
+        raise ValueError("fmha: k and v must share their token stride")
+    _need_bf16(o, d_o)
+    if dqkv is None:
+        dqkv = torch.empty((B, S, 3, H, D), dtype=torch.bfloat16, device=q.device)
+    dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    _lib().ofb_fmha_bwd_scratch_floats.restype = c_longlong
+    n = _lib().ofb_fmha_bwd_scratch_floats(c_int(B), c_int(S), c_int(H), c_int(D))
+    scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+    if kv_len is not None:
+        kv_len = kv_len.to(device=q.device, dtype=torch.int32).contiguous()
+    check(_lib().ofb_fmha_bwd(ptr(q), ptr(k), ptr(v), c_longlong(qs), c_longlong(ks), ptr(o), ptr(d_o), ptr(lse),
+                              ptr(dq), ptr(dk), ptr(dv), c_longlong(3 * H * D), ptr(scratch), ptr(kv_len), c_int(B),
+                              c_int(S), c_int(H), c_int(D), c_int(int(causal)), c_float(scale), stream_ptr()),
+          "fmha_bwd")
+    _count(4)
+    return dq, dk, dv

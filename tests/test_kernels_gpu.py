@@ -223,3 +223,36 @@ def test_multi_tensor_adamw_sgd_and_norm():
     assert int(out[1].item()) == 1
     f, found, norm = K.clip_factor(out, 1.0)
     assert int(found.item()) == 1 and f.item() <= 1.0
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fmha_bwd(D, causal):
+    torch.manual_seed(13)
+    B, S, H = 2, 384, 2
+    qkv = torch.randn(B, S, 3, H, D, device=DEV, dtype=BF)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    out, lse = K.fmha_fwd(q, k, v, causal=causal)
+    d_o = torch.randn_like(out)
+    dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o, lse, causal=causal)
+    rq, rk, rv = K.fmha_bwd_reference(q.cpu(), k.cpu(), v.cpu(), out.cpu(), d_o.cpu(), lse.cpu(), causal,
+                                      1 / math.sqrt(D))
+    close(dq, rq, 3e-2, 2e-2)
+    close(dk, rk, 3e-2, 2e-2)
+    close(dv, rv, 3e-2, 2e-2)
+
+
+def test_fmha_bwd_padding_ragged():
+    torch.manual_seed(14)
+    B, S, H, D = 2, 200, 2, 64
+    qkv = torch.randn(B, S, 3, H, D, device=DEV, dtype=BF)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    kv_len = torch.tensor([200, 90], dtype=torch.int32)
+    out, lse = K.fmha_fwd(q, k, v, causal=False, kv_len=kv_len)
+    d_o = torch.randn_like(out)
+    dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o, lse, causal=False, kv_len=kv_len)
+    rq, rk, rv = K.fmha_bwd_reference(q.cpu(), k.cpu(), v.cpu(), out.cpu(), d_o.cpu(), lse.cpu(), False,
+                                      1 / math.sqrt(D), kv_len)
+    close(dq, rq, 3e-2, 2e-2)
+    close(dk, rk, 3e-2, 2e-2)
+    close(dv, rv, 3e-2, 2e-2)
