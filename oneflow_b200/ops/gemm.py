@@ -125,4 +125,6 @@ def gemm(a, b, *, a_layout="mk", b_layout="nk", bias=None, act=0, residual=None,
             raise TypeError(f"gemm: {nm} must be 16-byte aligned bfloat16")
     lib = _native.kernels()
     _native.check(lib.ofb_gemm_bf16(args, _native.stream_ptr()), "ofb_gemm_bf16")
+    from . import kernels as _k
+    _k._count()
     return (out, aux) if want_aux else out

@@ -371,7 +371,7 @@ def fmha_reference(q, k, v, causal, scale, kv_len=None):
     lse = torch.logsumexp(s, -1)
     p = torch.exp(s - lse[..., None])
     p = torch.nan_to_num(p, nan=0.0)
-    o = torch.matmul(p, vf).permute(0, 2, 1, 3)
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).contiguous()
     return o.to(q.dtype), lse
 
 
