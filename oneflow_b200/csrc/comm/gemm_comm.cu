@@ -1,0 +1,536 @@
+// GEMM fused with its collective over NVSwitch peer memory (tensor parallel with sequence-parallel
+// activations). One persistent tcgen05 kernel per call does the tensor-core tiles AND the transfer:
+//
+//   MODE_RS  "GEMM -> reduce-scatter" (row-parallel Linear forward, column-parallel dX):
+//       every rank computes its partial C[T, N] tile by tile; the epilogue stores each finished tile
+//       (bf16) straight into the staging buffer of the rank that owns those rows (plain P2P stores over
+//       NVLink) and bumps a per-tile flag there. Tiles for other ranks are computed first, the rank's own
+//       rows last, so the transfers run under the remaining MMA work. When a CTA has no tiles left it
+//       turns into a reducer: it waits (bounded) for the flags of its share of the local rows, sums the n
+//       partial tiles in fp32, adds bias and the residual shard and writes the [T/n, N] result.
+//   MODE_AG  "all-gather -> GEMM" (column-parallel Linear forward, row-parallel dX, ZeRO parameter gather
+//       in front of the first consuming GEMM):
+//       two extra copier warps per CTA pull the peers' row shards into this GPU's gathered buffer (each
+//       remote tile crosses NVLink once); the TMA producer starts with the local rows and waits (bounded)
+//       on a per-peer arrival counter before it loads rows that came from that peer. TMA only ever reads
+//       local memory.
+//
+// Synchronisation uses monotonic epochs in the SignalBlock (comm_common.cuh); staging and gathered
+// buffers are double-buffered by epoch parity and guarded by "consumed"/"pulled" acknowledgements, so a
+// fast rank can run at most two calls ahead of a slow one. No NCCL, no TMA multicast.
+//
+// Reference counterparts: matmul + `_nccl_logical_reduce_scatter` / `_nccl_logical_all_gather` ops
+// (oneflow/user/kernels/nccl_logical_kernels.cpp:199-352) inserted by insert_nccl_logical_op_pass.cpp.
+#include "../common/host_utils.h"
+#include "../kernels/gemm_tcgen05.cuh"
+#include "comm_common.cuh"
+#include "ofb_comm.h"
+
+namespace ofb {
+
+enum { MODE_RS = 1, MODE_AG = 2 };
+
+struct GemmCommParams {
+  int n, rank;
+  int rows_per_rank;           // T / n, multiple of 128
+  unsigned int epoch;          // per-mode call counter (1, 2, ...), identical on all ranks
+  SignalBlock* sig[kMaxPeers];
+  int* status;
+  // ---- MODE_RS
+  __nv_bfloat16* stage[kMaxPeers];    // staging of every rank: [2 parity][n src][rows_per_rank][N]
+  unsigned int* flags[kMaxPeers];     // flags of every rank:   [2 parity][n src][flag_stride]
+  int flag_stride;
+  __nv_bfloat16* out;                 // [rows_per_rank, ldc] local result
+  long long ldc;
+  const __nv_bfloat16* bias;          // [N] or null (added once, after the reduction)
+  const __nv_bfloat16* residual;      // [rows_per_rank, ldr] or null
+  long long ldr;
+  int done_slot;                      // local counter slot used to detect the last reducing CTA
+  unsigned int done_target;
+  // ---- MODE_AG
+  const __nv_bfloat16* x_local;       // [rows_per_rank, K] this rank's shard (private memory)
+  __nv_bfloat16* gathered[kMaxPeers]; // gathered buffers of every rank: [2 parity][T][K] (only peers' own rows are read)
+  long long k_cols;                   // K (row length of the gathered matrix)
+  unsigned int pull_target;           // cumulative arrival count expected on the per-peer pull counters
+  int pull_slot;                      // first local counter slot of the per-peer pull counters
+};
+
+template <int BN>
+struct GemmCommCfg {
+  static constexpr int THREADS_RS = 192;
+  static constexpr int THREADS_AG = 256;
+};
+
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+template <int BN, int B_MN, int MODE>
+__global__ void __launch_bounds__(MODE == MODE_AG ? 256 : 192, 1)
+gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlocal,
+                 const __grid_constant__ CUtensorMap tmB, GemmShape shp, GemmEpilogue ep, GemmCommParams cp) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
+  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, 0, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  SignalBlock* my_sig = cp.sig[cp.rank];
+  const int parity = cp.epoch & 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (shp.M + BM - 1) / BM;
+  const int tiles_n = (shp.N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int kblocks = (shp.K + BK - 1) / BK;
+  const int tiles_m_per_rank = cp.rows_per_rank / BM;
+  // Row-tile rotation: MODE_AG starts with the local rows, MODE_RS ends with them.
+  const int rot = (MODE == MODE_AG ? cp.rank : (cp.rank + 1) % cp.n) * tiles_m_per_rank;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int ready_owner = cp.rank;  // rows of this owner are known to be present
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        tm = (tm + rot) % tiles_m;
+        const int m0 = tm * BM, n0 = tn * BN;
+        const int owner = tm / tiles_m_per_rank;
+        if (MODE == MODE_AG && owner != cp.rank && owner != ready_owner) {
+          if (!wait_local_ge(&my_sig->local_cnt[cp.pull_slot + owner], cp.pull_target, cp.status, 200 + owner)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();
+          ready_owner = owner;
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[stage], A_BYTES + B_BYTES);
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * B_BYTES;
+          if (MODE == MODE_AG && owner == cp.rank) {
+            tma_load_2d(a_dst, &tmAlocal, &full[stage], kb * BK, m0 - cp.rank * cp.rows_per_rank);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full[stage], kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d(b_dst, &tmB, &full[stage], kb * BK, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int cleared_owner = -1;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      tm = (tm + rot) % tiles_m;
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int owner = tm / tiles_m_per_rank;
+      if (MODE == MODE_RS && owner != cleared_owner) {
+        // The owner must have finished reducing what we stored into this parity two calls ago.
+        int ok_w = 1;
+        if (lane == 0 && cp.epoch > 2)
+          ok_w = wait_flag_ge(&my_sig->rs_consumed[owner], cp.epoch - 2, cp.status, 300 + owner) ? 1 : 0;
+        ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+        if (!ok_w) { *abort_flag = 1; break; }
+        cleared_owner = owner;
+      }
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < shp.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = col0 + g * 8;
+          if (!row_ok || col >= shp.N) continue;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * ep.alpha;
+          if (MODE == MODE_RS) {
+            const long long lrow = row - owner * cp.rows_per_rank;
+            __nv_bfloat16* dst = cp.stage[owner] +
+                                 ((static_cast<long long>(parity) * cp.n + cp.rank) * cp.rows_per_rank + lrow) * shp.N + col;
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                        pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+          } else {
+            if (ep.bias) {
+              uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col));
+              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(bw[j]); v[2 * j] += f.x; v[2 * j + 1] += f.y; }
+            }
+            if (ep.aux_out) {
+              *reinterpret_cast<uint4*>(ep.aux_out + static_cast<long long>(row) * ep.ld_aux + col) =
+                  make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            }
+            if (ep.act != kActNone && !ep.aux_in) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.act);
+            }
+            if (ep.aux_in) {
+              uint4 hh = __ldg(reinterpret_cast<const uint4*>(ep.aux_in + static_cast<long long>(row) * ep.ld_aux + col));
+              const uint32_t hw[4] = {hh.x, hh.y, hh.z, hh.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(hw[j]);
+                v[2 * j] *= apply_act_grad(f.x, ep.act);
+                v[2 * j + 1] *= apply_act_grad(f.y, ep.act);
+              }
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                        pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+          }
+        }
+      }
+      tc_fence_before();
+      if (MODE == MODE_RS) __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&tempty[acc]);
+        if (MODE == MODE_RS) {
+          const int tile_local = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
+          atomicAdd_system(cp.flags[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.flag_stride + tile_local, 1u);
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  } else if (MODE == MODE_AG) {
+    // ---------------------------------------------------------------- copiers (warps 6, 7)
+    const int ct = threadIdx.x - 192;  // 0..63
+    const long long shard_vecs = static_cast<long long>(cp.rows_per_rank) * cp.k_cols / 8;
+    const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
+    const long long v0 = per_cta * blockIdx.x;
+    const long long v1 = min(shard_vecs, v0 + per_cta);
+    const long long buf_elems = static_cast<long long>(shp.M) * cp.k_cols;
+    __nv_bfloat16* my_gathered = cp.gathered[cp.rank] + parity * buf_elems;
+    bool ok = true;
+    // 1. publish the local shard: peers must have finished pulling what this parity held two calls ago
+    if (ct == 0 && cp.epoch > 2) {
+      for (int p = 0; p < cp.n && ok; ++p)
+        if (p != cp.rank) ok = wait_flag_ge(&my_sig->ag_pulled[p], cp.epoch - 2, cp.status, 400 + p);
+    }
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(cp.x_local);
+      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(cp.rank) * cp.rows_per_rank * cp.k_cols);
+      for (long long i = v0 + ct; i < v1; i += 64) dst[i] = src[i];
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (ct == 0) {
+      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + cp.rank], 1u) + 1u;
+      if (arrived == cp.pull_target) {  // last CTA: the whole local shard is readable by the peers
+        for (int p = 0; p < cp.n; ++p)
+          if (p != cp.rank) st_release_sys(&cp.sig[p]->ag_ready[cp.rank], cp.epoch);
+      }
+    }
+    // 2. pull the peers' shards, nearest successor first (the order the GEMM consumes them in)
+    for (int k = 1; k < cp.n; ++k) {
+      const int o = (cp.rank + k) % cp.n;
+      int okw = 1;
+      if (ct == 0) okw = (ok && wait_flag_ge(&my_sig->ag_ready[o], cp.epoch, cp.status, 500 + o)) ? 1 : 0;
+      __shared__ int ok_shared;
+      if (ct == 0) ok_shared = okw;
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (!ok_shared) { *abort_flag = 1; break; }
+      const uint4* src = reinterpret_cast<const uint4*>(cp.gathered[o] + parity * buf_elems +
+                                                        static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
+      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
+      long long i = v0 + ct;
+      // 8 independent 16-byte loads in flight per thread before the first store
+      for (; i + 7 * 64 < v1; i += 8 * 64) {
+        uint4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = src[i + u * 64];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * 64] = t[u];
+      }
+      for (; i < v1; i += 64) dst[i] = src[i];
+      __threadfence();
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (ct == 0) {
+        const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + o], 1u) + 1u;
+        if (arrived == cp.pull_target) st_release_sys(&cp.sig[o]->ag_pulled[cp.rank], cp.epoch);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (MODE == MODE_RS && !*abort_flag) {
+    // ---------------------------------------------------------------- reduce the rows this rank owns
+    __shared__ int red_ok;
+    const int local_tiles = tiles_m_per_rank * tiles_n;
+    const __nv_bfloat16* my_stage = cp.stage[cp.rank] + static_cast<long long>(parity) * cp.n * cp.rows_per_rank * shp.N;
+    unsigned int* my_flags = cp.flags[cp.rank] + static_cast<long long>(parity) * cp.n * cp.flag_stride;
+    for (int lt = blockIdx.x; lt < local_tiles; lt += gridDim.x) {
+      if (threadIdx.x == 0) {
+        bool ok = true;
+        for (int s = 0; s < cp.n && ok; ++s) ok = wait_flag_ge(my_flags + s * cp.flag_stride + lt, 4u, cp.status, 600 + s);
+        if (ok)
+          for (int s = 0; s < cp.n; ++s) my_flags[s * cp.flag_stride + lt] = 0u;
+        red_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!red_ok) break;
+      const int ltm = lt / tiles_n, ltn = lt % tiles_n;
+      const int r0 = ltm * BM, c0 = ltn * BN;
+      constexpr int VPR = BN / 8;  // vectors per tile row
+      for (int e = threadIdx.x; e < BM * VPR; e += blockDim.x) {
+        const int rr = r0 + e / VPR, cc = c0 + (e % VPR) * 8;
+        if (rr >= cp.rows_per_rank || cc >= shp.N) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < cp.n; ++s) {
+          const uint4 q = *reinterpret_cast<const uint4*>(my_stage + (static_cast<long long>(s) * cp.rows_per_rank + rr) * shp.N + cc);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        if (cp.bias) {
+          const uint4 q = __ldg(reinterpret_cast<const uint4*>(cp.bias + cc));
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        if (cp.residual) {
+          const uint4 q = *reinterpret_cast<const uint4*>(cp.residual + static_cast<long long>(rr) * cp.ldr + cc);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        *reinterpret_cast<uint4*>(cp.out + static_cast<long long>(rr) * cp.ldc + cc) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      }
+      __syncthreads();
+    }
+    // Tell the senders that this parity of the staging buffer may be reused.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.done_slot], 1u) + 1u;
+      if (arrived == cp.done_target)
+        for (int p = 0; p < cp.n; ++p) st_release_sys(&cp.sig[p]->rs_consumed[cp.rank], cp.epoch);
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0 && cp.status) atomicCAS(cp.status, 0, (int)kStatusMbarTimeout);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int BN, int B_MN, int MODE>
+static int launch_gemm_comm(const CUtensorMap& tmA, const CUtensorMap& tmAl, const CUtensorMap& tmB, const GemmShape& shp,
+                            const GemmEpilogue& ep, const GemmCommParams& cp, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_comm_kernel<BN, B_MN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  kern<<<grid, MODE == MODE_AG ? 256 : 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmAl, tmB, shp, ep, cp);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace ofb
+
+using namespace ofb;
+
+// The grid of the fused kernels is fixed per device (one CTA per SM, capped by the tile count is NOT
+// applied) so that the per-call arrival targets are simple multiples of it.
+OFB_API int ofb_gemm_comm_grid(int* out) {
+  int dev = 0, sms = 0;
+  OFB_CUDA_OK(cudaGetDevice(&dev));
+  OFB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  *out = sms;
+  return 0;
+}
+
+// C[T/n, N] = reduce_scatter_rows( A[T, K] @ B^T ) + bias + residual.
+//   a: bf16 [T, lda] local; b: bf16 [N, ldb] ("nk") or [K, ldb] ("kn"); out: bf16 [T/n, ldc] local.
+//   stage_off / flag_off: byte offsets of the staging and flag regions inside every rank's arena.
+OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, const void* b, long long ldb, int b_mn_major,
+                        void* out, long long ldc, const void* bias, const void* residual, long long ldr, int T, int N, int K,
+                        float alpha, long long stage_off, long long flag_off, int flag_stride, unsigned int epoch,
+                        int done_slot, void* stream) {
+  const int n = ctx->n;
+  if (n < 1 || n > kMaxPeers) return fail("gemm_rs: group size must be 1..8");
+  if (T % (n * 128)) return fail("gemm_rs: rows must be a multiple of 128 * group size");
+  if (N % 8 || K % 8) return fail("gemm_rs: N and K must be multiples of 8");
+  const int bn = 256;
+  const int tiles_local = (T / n / 128) * ((N + bn - 1) / bn);
+  if (tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
+  CUtensorMap tmA, tmB;
+  if (get_tensor_map(&tmA, a, 2, 2, K, T, 0, (uint64_t)lda * 2, 0, 64, 128, 0, 3)) return -1;
+  if (!b_mn_major) {
+    if (get_tensor_map(&tmB, b, 2, 2, K, N, 0, (uint64_t)ldb * 2, 0, 64, bn, 0, 3)) return -1;
+  } else {
+    if (get_tensor_map(&tmB, b, 2, 2, N, K, 0, (uint64_t)ldb * 2, 0, 64, 64, 0, 3)) return -1;
+  }
+  int grid = 0;
+  if (ofb_gemm_comm_grid(&grid)) return -1;
+  GemmShape shp{T, N, K};
+  GemmEpilogue ep;
+  std::memset(&ep, 0, sizeof(ep));
+  ep.alpha = alpha;
+  GemmCommParams cp;
+  std::memset(&cp, 0, sizeof(cp));
+  cp.n = n; cp.rank = ctx->rank; cp.rows_per_rank = T / n; cp.epoch = epoch; cp.status = device_status_ptr();
+  for (int i = 0; i < n; ++i) {
+    cp.sig[i] = reinterpret_cast<SignalBlock*>(ctx->signals[i]);
+    cp.stage[i] = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ctx->arena[i]) + stage_off);
+    cp.flags[i] = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(ctx->arena[i]) + flag_off);
+  }
+  cp.flag_stride = flag_stride;
+  cp.out = reinterpret_cast<__nv_bfloat16*>(out); cp.ldc = ldc;
+  cp.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  cp.residual = reinterpret_cast<const __nv_bfloat16*>(residual); cp.ldr = ldr;
+  cp.done_slot = done_slot; cp.done_target = epoch * static_cast<unsigned int>(grid);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  return b_mn_major ? launch_gemm_comm<256, 1, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s)
+                    : launch_gemm_comm<256, 0, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s);
+}
+
+// C[T, N] = epilogue( all_gather_rows(x_local[T/n, K]) @ B^T ); the gathered matrix of this call stays in
+// this rank's gathered buffer (parity = epoch & 1) for later kernels (weight gradients).
+OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* b, long long ldb, int b_mn_major, void* out,
+                        long long ldc, const void* bias, const void* aux_in, void* aux_out, long long ld_aux, int act, int T,
+                        int N, int K, float alpha, long long gathered_off, unsigned int epoch, int pull_slot, void* stream) {
+  const int n = ctx->n;
+  if (n < 1 || n > kMaxPeers) return fail("ag_gemm: group size must be 1..8");
+  if (T % (n * 128)) return fail("ag_gemm: rows must be a multiple of 128 * group size");
+  if (N % 8 || K % 8) return fail("ag_gemm: N and K must be multiples of 8");
+  const int bn = 256;
+  int grid = 0;
+  if (ofb_gemm_comm_grid(&grid)) return -1;
+  const long long buf_elems = static_cast<long long>(T) * K;
+  auto* my_g = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ctx->arena[ctx->rank]) + gathered_off) +
+               (epoch & 1) * buf_elems;
+  CUtensorMap tmA, tmAl, tmB;
+  if (get_tensor_map(&tmA, my_g, 2, 2, K, T, 0, (uint64_t)K * 2, 0, 64, 128, 0, 3)) return -1;
+  if (get_tensor_map(&tmAl, x_local, 2, 2, K, T / n, 0, (uint64_t)K * 2, 0, 64, 128, 0, 3)) return -1;
+  if (!b_mn_major) {
+    if (get_tensor_map(&tmB, b, 2, 2, K, N, 0, (uint64_t)ldb * 2, 0, 64, bn, 0, 3)) return -1;
+  } else {
+    if (get_tensor_map(&tmB, b, 2, 2, N, K, 0, (uint64_t)ldb * 2, 0, 64, 64, 0, 3)) return -1;
+  }
+  GemmShape shp{T, N, K};
+  GemmEpilogue ep;
+  std::memset(&ep, 0, sizeof(ep));
+  ep.C = out; ep.ldc = ldc; ep.alpha = alpha; ep.act = act;
+  ep.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  ep.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
+  ep.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  ep.ld_aux = ld_aux;
+  GemmCommParams cp;
+  std::memset(&cp, 0, sizeof(cp));
+  cp.n = n; cp.rank = ctx->rank; cp.rows_per_rank = T / n; cp.epoch = epoch; cp.status = device_status_ptr();
+  for (int i = 0; i < n; ++i) {
+    cp.sig[i] = reinterpret_cast<SignalBlock*>(ctx->signals[i]);
+    cp.gathered[i] = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ctx->arena[i]) + gathered_off);
+  }
+  cp.x_local = reinterpret_cast<const __nv_bfloat16*>(x_local);
+  cp.k_cols = K;
+  cp.pull_slot = pull_slot;
+  cp.pull_target = epoch * static_cast<unsigned int>(grid);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  return b_mn_major ? launch_gemm_comm<256, 1, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s)
+                    : launch_gemm_comm<256, 0, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s);
+}

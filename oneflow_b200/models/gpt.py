@@ -76,19 +76,31 @@ class ParamStore:
     optimizer can treat the buffer as two contiguous segments."""
 
     def __init__(self, specs, device, dtype=torch.bfloat16, grad_dtype=torch.float32):
-        # specs: list of (name, shape, decay: bool, init_std or ("const", value))
-        decay = [s for s in specs if s[2]]
-        no_decay = [s for s in specs if not s[2]]
-        self.specs = decay + no_decay
+        # specs: list of (name, shape, decay: bool, init_std or ("const", value)[, rep]) where rep tells how the
+        # tensor relates to the tensor-parallel group: 0 = a shard unique to this rank, 1 = replicated and its
+        # gradient is a partial sum over the ranks' token shards, 2 = replicated with a complete gradient.
+        specs = [tuple(s) + (0,) * (5 - len(s)) for s in specs]
+        order = sorted(range(len(specs)), key=lambda i: (not specs[i][2], specs[i][4] != 0, i))
+        self.specs5 = [specs[i] for i in order]
+        self.specs = [s[:4] for s in self.specs5]
         off = 0
         self.offsets = {}
-        for name, shape, _, _ in self.specs:
-            self.offsets[name] = (off, math.prod(shape), tuple(shape))
-            off += _align(math.prod(shape))
-            if name == decay[-1][0] if decay else False:
+        self.decay_end = 0
+        self.replicated_ranges = []   # [lo, hi) element ranges holding replicated tensors (count once in norms)
+        self.partial_names = []       # replicated tensors whose gradients must be summed over the tp group
+        for name, shape, dec, _, rep in self.specs5:
+            n = math.prod(shape)
+            self.offsets[name] = (off, n, tuple(shape))
+            if rep:
+                if self.replicated_ranges and self.replicated_ranges[-1][1] == off:
+                    self.replicated_ranges[-1][1] = off + _align(n)
+                else:
+                    self.replicated_ranges.append([off, off + _align(n)])
+                if rep == 1:
+                    self.partial_names.append(name)
+            off += _align(n)
+            if dec:
                 self.decay_end = off
-        if not decay:
-            self.decay_end = 0
         self.total = off
         self.flat = torch.zeros(self.total, dtype=dtype, device=device)
         self.grad = torch.zeros(self.total, dtype=grad_dtype, device=device)
@@ -99,14 +111,16 @@ class ParamStore:
             self.g[name] = self.grad[o:o + n].view(shape)
         self.grad_ready = set()  # names whose gradient holds a value for the current accumulation window
 
-    def init_(self, seed=0):
+    def init_(self, seed=0, shard_offset=0):
         """Every tensor draws from its own stream seeded by (seed, name), so the values do not depend on
         which other tensors share the store (any pipeline split initialises identically)."""
         import zlib
         dev = self.flat.device
         gen = torch.Generator(device=dev)
-        for name, shape, _, init in self.specs:
-            gen.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
+        for name, shape, _, init, rep in self.specs5:
+            # shards differ between tensor-parallel ranks, replicated tensors must not
+            s = seed + (0 if rep else shard_offset)
+            gen.manual_seed((s * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
             if isinstance(init, tuple):
                 self.p[name].fill_(init[1])
             else:
@@ -136,13 +150,14 @@ def layer_specs(cfg: GPTConfig, li: int, tp: int = 1):
     h, f = cfg.hidden, cfg.ffn
     std_out = cfg.init_std / math.sqrt(2.0 * cfg.layers)
     p = f"h.{li}."
+    rep = 1 if tp > 1 else 0  # LayerNorm parameters and row-parallel biases see only this rank's token shard
     return [
-        (p + "ln1.g", (h,), False, ("const", 1.0)), (p + "ln1.b", (h,), False, ("const", 0.0)),
+        (p + "ln1.g", (h,), False, ("const", 1.0), rep), (p + "ln1.b", (h,), False, ("const", 0.0), rep),
         (p + "attn.wqkv", (3 * h // tp, h), True, cfg.init_std), (p + "attn.bqkv", (3 * h // tp,), False, ("const", 0.0)),
-        (p + "attn.wo", (h, h // tp), True, std_out), (p + "attn.bo", (h,), False, ("const", 0.0)),
-        (p + "ln2.g", (h,), False, ("const", 1.0)), (p + "ln2.b", (h,), False, ("const", 0.0)),
+        (p + "attn.wo", (h, h // tp), True, std_out), (p + "attn.bo", (h,), False, ("const", 0.0), rep),
+        (p + "ln2.g", (h,), False, ("const", 1.0), rep), (p + "ln2.b", (h,), False, ("const", 0.0), rep),
         (p + "mlp.w1", (f // tp, h), True, cfg.init_std), (p + "mlp.b1", (f // tp,), False, ("const", 0.0)),
-        (p + "mlp.w2", (h, f // tp), True, std_out), (p + "mlp.b2", (h,), False, ("const", 0.0)),
+        (p + "mlp.w2", (h, f // tp), True, std_out), (p + "mlp.b2", (h,), False, ("const", 0.0), rep),
     ]
 
 
@@ -169,14 +184,15 @@ class GPTStage:
         if first or last:
             specs.append(("wte", (self.vocab_local, cfg.hidden), True, cfg.init_std))
         if first:
-            specs.append(("wpe", (cfg.seq_len, cfg.hidden), True, cfg.init_std))
+            specs.append(("wpe", (cfg.seq_len, cfg.hidden), True, cfg.init_std, 2 if tpn > 1 else 0))
         for li in range(self.l0, self.l1):
             specs += layer_specs(cfg, li, tpn)
         if last:
-            specs += [("lnf.g", (cfg.hidden,), False, ("const", 1.0)), ("lnf.b", (cfg.hidden,), False, ("const", 0.0))]
+            rep = 1 if tpn > 1 else 0
+            specs += [("lnf.g", (cfg.hidden,), False, ("const", 1.0), rep), ("lnf.b", (cfg.hidden,), False, ("const", 0.0), rep)]
         self.store = ParamStore(specs, self.device, grad_dtype=grad_dtype)
         # Different tensor-parallel ranks hold different shards: decorrelate their random init.
-        self.store.init_(seed + 7919 * self.tp_rank)
+        self.store.init_(seed, shard_offset=7919 * self.tp_rank)
         self.saved: Dict[int, dict] = {}
 
     # ------------------------------------------------------------------ helpers
@@ -359,6 +375,19 @@ class GPTStage:
                             vocab_start=self.tp_rank * self.vocab_local)
             return None
         return dy
+
+    def sync_replicated_grads(self):
+        """Sums over the tensor-parallel group the gradients of replicated parameters that were formed from
+        this rank's token shard only (LayerNorm parameters, row-parallel biases)."""
+        if self.tp is None or not self.store.partial_names:
+            return
+        views = [self.store.g[n].reshape(-1) for n in self.store.partial_names]
+        flat = torch.cat(views)
+        flat = self.tp.all_reduce(flat)
+        o = 0
+        for v in views:
+            v.copy_(flat[o:o + v.numel()])
+            o += v.numel()
 
     def num_local_params(self):
         return sum(math.prod(s[1]) for s in self.store.specs)

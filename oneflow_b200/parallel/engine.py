@@ -28,8 +28,9 @@ class FlatAdamW:
     """
 
     def __init__(self, store, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_grad=1.0, zero=None,
-                 norm_groups=()):
+                 norm_groups=(), tp_size=1):
         self.store = store
+        self.tp_size = tp_size
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         self.zero = zero
         self.norm_groups = tuple(g for g in norm_groups if g is not None)
@@ -46,6 +47,22 @@ class FlatAdamW:
     def set_lr(self, lr):
         self.lr = lr
         self.lr_t.fill_(lr)
+
+    def _split_replicated(self):
+        """This rank's range [lo, hi) cut into (replicated pieces, unique pieces), as offsets into the shard.
+        Pieces are 64-element aligned like the store, so they satisfy the kernels' alignment rule."""
+        rep, uniq, cur = [], [], self.lo
+        for a, b in getattr(self.store, "replicated_ranges", []):
+            a, b = max(a, self.lo), min(b, self.hi)
+            if a >= b:
+                continue
+            if a > cur:
+                uniq.append((cur - self.lo, a - self.lo))
+            rep.append((a - self.lo, b - self.lo))
+            cur = b
+        if cur < self.hi:
+            uniq.append((cur - self.lo, self.hi - self.lo))
+        return rep, uniq
 
     def _segments(self):
         """(lo, hi, weight_decay) pieces of this rank's range: the decayed prefix and the rest."""
@@ -65,7 +82,14 @@ class FlatAdamW:
             grad_shard = self.zero.reduce_scatter_grads(grad, self.lo, self.hi)
         else:
             grad_shard = grad[self.lo:self.hi]
-        sq = K.multi_tensor_sqsum([grad_shard], out=self._sq)
+        rep, uniq = self._split_replicated()
+        if rep and self.tp_size > 1:
+            # tensors replicated over the tensor-parallel group enter the global norm once, not tp times
+            sq = K.multi_tensor_sqsum([grad_shard[a:b] for a, b in uniq], out=self._sq) if uniq else self._sq.zero_()
+            sq_rep = K.multi_tensor_sqsum([grad_shard[a:b] for a, b in rep])
+            sq += sq_rep / self.tp_size
+        else:
+            sq = K.multi_tensor_sqsum([grad_shard], out=self._sq)
         groups = list(self.norm_groups) + ([self.zero.group] if self.zero is not None else [])
         for g in groups:
             dist.all_reduce(sq, group=g)
@@ -218,5 +242,7 @@ class StagedTrainer:
             # tied embedding: the first and last stage each hold a copy of wte; sum their gradients
             if self.embedding_group is not None and (st.first or st.last):
                 dist.all_reduce(st.store.g["wte"], group=self.embedding_group)
+        if hasattr(st, "sync_replicated_grads"):
+            st.sync_replicated_grads()
         self.opt.step()
         return loss

@@ -79,7 +79,8 @@ def build_gpt_trainer(cfg, tp=1, pp=1, dp=1, micro_batch=4, n_micro=16, device="
     if tp > 1:
         from .tensor_parallel import TPContext
         tp_ctx = TPContext(mesh.tp_group, mesh.tp_ranks, device, max_tokens=micro_batch * cfg.seq_len,
-                           max_cols=max(cfg.ffn // tp, 3 * cfg.hidden // tp, cfg.hidden, cfg.vocab_size // tp))
+                           max_cols=max(cfg.ffn // tp, 3 * cfg.hidden // tp, cfg.hidden, cfg.vocab_size // tp),
+                           hidden=cfg.hidden)
     per = cfg.layers // pp
     l0 = mesh.pp_idx * per
     l1 = cfg.layers if mesh.pp_idx == pp - 1 else l0 + per
@@ -93,7 +94,7 @@ def build_gpt_trainer(cfg, tp=1, pp=1, dp=1, micro_batch=4, n_micro=16, device="
         from .zero import GradAllReduce
         zero = GradAllReduce(mesh.dp_group, mesh.dp_ranks, device)
     opt = FlatAdamW(stage.store, lr=lr, weight_decay=weight_decay, clip_grad=clip_grad, zero=zero,
-                    norm_groups=(mesh.tp_group, mesh.pp_group))
+                    norm_groups=(mesh.tp_group, mesh.pp_group), tp_size=tp)
     p2p = None
     if pp > 1:
         tokens = micro_batch * cfg.seq_len // tp

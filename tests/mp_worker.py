@@ -1,0 +1,231 @@
+"""Worker run under torch.distributed.run by the multi-process tests:
+    python -m torch.distributed.run --nproc-per-node N tests/mp_worker.py <case> <cpu|cuda>
+Each case checks a multi-rank code path against a single-process statement of the same computation and
+exits non-zero on mismatch."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def close(a, b, tol=3e-2, what=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    scale = b.abs().max().item() + 1e-6
+    err = (a - b).abs().max().item()
+    assert err <= tol * max(1.0, scale), f"{what}: max err {err} (scale {scale})"
+
+
+def setup(devkind):
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if devkind == "cuda":
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    return rank, world, dev
+
+
+def case_collectives(rank, world, dev):
+    from oneflow_b200.comm.symmetric import DeviceCollectives, SymmetricArena
+    arena = SymmetricArena(None, list(range(world)), dev, 64 << 20)
+    coll = DeviceCollectives(arena, io_bytes=16 << 20)
+    torch.manual_seed(0)
+    full = [torch.randn(world * 1024, 96) for _ in range(world)]  # rank r's input = full[r]
+    x = full[rank].to(dev)
+    for _ in range(3):  # repeated calls exercise the epoch protocol
+        out = coll.all_reduce(x, scale=0.5)
+        close(out, sum(full) * 0.5, 1e-4, "all_reduce fp32")
+    xb = x.bfloat16()
+    out = coll.all_reduce(xb, scale=1.0, out_dtype=torch.float32)
+    close(out, sum(f.bfloat16().float() for f in full), 1e-2, "all_reduce bf16->fp32")
+    rs = coll.reduce_scatter(x)
+    m = x.shape[0] // world
+    close(rs, sum(full)[rank * m:(rank + 1) * m], 1e-4, "reduce_scatter")
+    ag = coll.all_gather(x[:256].contiguous())
+    close(ag, torch.cat([f[:256] for f in full]), 1e-6, "all_gather")
+    # S(0) -> S(1) on a [8*world, 6*world, 16] tensor
+    logical = torch.arange(8 * world * 6 * world * 16, dtype=torch.float32).view(8 * world, 6 * world, 16)
+    shard0 = logical.chunk(world, 0)[rank].contiguous().to(dev)
+    got = coll.all_to_all(shard0, 0, 1, logical.shape)
+    close(got, logical.chunk(world, 1)[rank], 1e-6, "all_to_all 0->1")
+    shard1 = logical.chunk(world, 1)[rank].contiguous().to(dev)
+    got = coll.all_to_all(shard1, 1, 0, logical.shape)
+    close(got, logical.chunk(world, 0)[rank], 1e-6, "all_to_all 1->0")
+    coll.barrier()
+    odd = torch.randn(1001, device=dev)
+    ref = odd.clone()
+    dist.all_reduce(ref)
+    close(coll.all_reduce(odd), ref, 1e-4, "all_reduce odd size")
+
+
+def case_fused_gemm(rank, world, dev):
+    from oneflow_b200.parallel.tensor_parallel import TPContext
+    T, H, F = 256 * world, 256, 512
+    tp = TPContext(None, list(range(world)), dev, max_tokens=T, max_cols=max(H, F), hidden=max(H, F))
+    torch.manual_seed(1)
+    dt = torch.bfloat16
+    x_full = torch.randn(T, H).to(dt)
+    w1_full = (torch.randn(F, H) * 0.05).to(dt)       # column parallel: rows of w1 sharded
+    b1_full = torch.randn(F).to(dt)
+    w2_full = (torch.randn(H, F) * 0.05).to(dt)       # row parallel: columns of w2 sharded
+    b2 = torch.randn(H).to(dt)
+    res_full = torch.randn(T, H).to(dt)
+    Fl, Tl = F // world, T // world
+    x_sh = x_full[rank * Tl:(rank + 1) * Tl].contiguous().to(dev)
+    w1 = w1_full[rank * Fl:(rank + 1) * Fl].contiguous().to(dev)
+    b1 = b1_full[rank * Fl:(rank + 1) * Fl].contiguous().to(dev)
+    w2 = w2_full[:, rank * Fl:(rank + 1) * Fl].contiguous().to(dev)
+    res_sh = res_full[rank * Tl:(rank + 1) * Tl].contiguous().to(dev)
+    for it in range(4):  # several rounds: parity double-buffering and acknowledgements
+        gathered, a, h1 = tp.ag_gemm(x_sh, w1, bias=b1, act=2, want_aux=True, return_gathered=True)
+        ref_h1 = x_full.float() @ w1_full.float().t()[:, rank * Fl:(rank + 1) * Fl] + b1_full.float()[rank * Fl:(rank + 1) * Fl]
+        close(gathered, x_full, 1e-6, f"gathered rows (round {it})")
+        close(h1, ref_h1, 3e-2, f"ag_gemm pre-activation (round {it})")
+        close(a, torch.nn.functional.gelu(ref_h1, approximate="tanh"), 3e-2, f"ag_gemm activation (round {it})")
+        y = tp.gemm_rs(a, w2, bias=b2.to(dev), residual=res_sh)
+        a_full = torch.nn.functional.gelu(x_full.float() @ w1_full.float().t() + b1_full.float(), approximate="tanh")
+        ref_y = (a_full.to(dt).float() @ w2_full.float().t() + b2.float() + res_full.float())[rank * Tl:(rank + 1) * Tl]
+        close(y, ref_y, 4e-2, f"gemm_rs (round {it})")
+        # data-gradient forms ("kn" weights)
+        dy_sh = y
+        dyf, dh = tp.ag_gemm(dy_sh, w2, b_layout="kn", aux_in=h1, act=2, return_gathered=True)
+        dln = tp.gemm_rs(dh, w1, b_layout="kn")
+        assert dln.shape == (Tl, H) and dyf.shape == (T, H)
+        assert torch.isfinite(dln.float()).all()
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+
+
+def _train_losses(cfg, tp, pp, dp, dev, steps, micro_batch, n_micro, tokens):
+    from oneflow_b200.parallel.setup import build_gpt_trainer
+    tr = build_gpt_trainer(cfg, tp=tp, pp=pp, dp=dp, micro_batch=micro_batch, n_micro=n_micro, device=dev, lr=2e-3,
+                           weight_decay=0.01, seed=11)
+    losses = []
+    for _ in range(steps):
+        loss = tr.train_step(tokens)
+        losses.append(float(loss.item()) if tr.has_loss else float("nan"))
+    return tr, losses
+
+
+def case_gpt_parallel(rank, world, dev, tp, pp, dp):
+    """The same tiny GPT trained with (tp, pp, dp) must follow the loss curve of the single-process run."""
+    from oneflow_b200.models.gpt import GPTConfig
+    D = 64 if dev.type == "cuda" else 16
+    cfg = GPTConfig(vocab_size=256, hidden=2 * D * max(tp, 1), layers=4, heads=2 * max(tp, 1), ffn=512,
+                    seq_len=128 * tp if dev.type == "cuda" else 32)
+    micro_batch, n_micro = 2, 4
+    g = torch.Generator().manual_seed(5)
+    tokens_all = torch.randint(0, cfg.vocab_size, (dp * micro_batch * n_micro, cfg.seq_len + 1), generator=g)
+    dp_idx = rank // (tp * pp)
+    per = micro_batch * n_micro
+    tokens = tokens_all[dp_idx * per:(dp_idx + 1) * per].to(dev)
+    tr, losses = _train_losses(cfg, tp, pp, dp, dev, 4, micro_batch, n_micro, tokens)
+    # single-process oracle on CPU with the full (unsharded) model is not bit-identical (different init
+    # streams per shard), so the check is behavioural: finite, decreasing, and equal across the ranks that
+    # report a loss.
+    if tr.has_loss:
+        assert all(l == l for l in losses), losses
+        assert losses[-1] < losses[0], losses
+    t = torch.tensor([losses[-1] if tr.has_loss else 0.0, 1.0 if tr.has_loss else 0.0], dtype=torch.float64, device=dev)
+    dist.all_reduce(t)
+    mean = (t[0] / t[1]).item()
+    if tr.has_loss and dp == 1:
+        assert abs(losses[-1] - mean) < 1e-3 * max(1.0, abs(mean)), (losses[-1], mean)
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+
+
+def case_tp_matches_single(rank, world, dev):
+    """Tensor-parallel forward/backward of one stage equals the unsharded stage when the shards are cut from
+    the same full weights."""
+    from oneflow_b200.models.gpt import GPTConfig, GPTStage
+    from oneflow_b200.parallel.tensor_parallel import TPContext
+    tpn = world
+    D = 64 if dev.type == "cuda" else 16
+    cfg = GPTConfig(vocab_size=128 * tpn, hidden=2 * D * tpn, layers=2, heads=2 * tpn, ffn=256 * tpn,
+                    seq_len=128 * tpn if dev.type == "cuda" else 16 * tpn)
+    B, S, h = 2, cfg.seq_len, cfg.hidden
+    full = GPTStage(cfg, device="cpu", seed=3)
+    for n, p in full.store.named_parameters():
+        if p.dim() == 1:
+            p.copy_((torch.randn(p.shape, generator=torch.Generator().manual_seed(len(n))) * 0.1 + (1 if n.endswith(".g") else 0)))
+    tp = TPContext(None, list(range(world)), dev, max_tokens=B * S, max_cols=max(cfg.ffn, 3 * h, cfg.vocab_size), hidden=h)
+    sh = GPTStage(cfg, device=dev, tp=tp, seed=3)
+    Hl, Dh, r = cfg.heads // tpn, cfg.head_dim, rank
+    for n, p in sh.store.named_parameters():
+        f = full.store.p[n]
+        if n.endswith("attn.wqkv") or n.endswith("attn.bqkv"):
+            f3 = f.view(3, cfg.heads, Dh, *f.shape[1:])[:, r * Hl:(r + 1) * Hl]
+            p.copy_(f3.reshape(p.shape))
+        elif n.endswith("attn.wo") or n.endswith("mlp.w2"):
+            c = f.shape[1] // tpn
+            p.copy_(f[:, r * c:(r + 1) * c])
+        elif n.endswith("mlp.w1") or n.endswith("mlp.b1") or n == "wte":
+            c = f.shape[0] // tpn
+            p.copy_(f[r * c:(r + 1) * c])
+        else:
+            p.copy_(f)
+    g = torch.Generator().manual_seed(9)
+    tok = torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g)
+    inp, lab = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    full.store.start_accumulation()
+    ref_loss = full.forward(0, inp, lab)
+    full.backward(0)
+    sh.store.start_accumulation()
+    loss = sh.forward(0, inp.to(dev), lab.to(dev))
+    sh.backward(0)
+    sh.sync_replicated_grads()
+    close(loss, ref_loss, 2e-2, "tp loss")
+    for n, gsh in sh.store.g.items():
+        f = full.store.g[n]
+        if n.endswith("attn.wqkv") or n.endswith("attn.bqkv"):
+            ref = f.view(3, cfg.heads, Dh, *f.shape[1:])[:, r * Hl:(r + 1) * Hl].reshape(gsh.shape)
+        elif n.endswith("attn.wo") or n.endswith("mlp.w2"):
+            c = f.shape[1] // tpn
+            ref = f[:, r * c:(r + 1) * c]
+        elif n.endswith("mlp.w1") or n.endswith("mlp.b1") or n == "wte":
+            c = f.shape[0] // tpn
+            ref = f[r * c:(r + 1) * c]
+        else:
+            ref = f
+        close(gsh, ref, 8e-2, f"tp grad {n}")
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+
+
+def main():
+    case, devkind = sys.argv[1], sys.argv[2]
+    rank, world, dev = setup(devkind)
+    try:
+        if case == "collectives":
+            case_collectives(rank, world, dev)
+        elif case == "fused_gemm":
+            case_fused_gemm(rank, world, dev)
+        elif case == "tp_matches_single":
+            case_tp_matches_single(rank, world, dev)
+        elif case.startswith("gpt_"):
+            tp, pp, dp = (int(v) for v in case.split("_")[1:4])
+            case_gpt_parallel(rank, world, dev, tp, pp, dp)
+        else:
+            raise SystemExit(f"unknown case {case}")
+        dist.barrier()
+        if rank == 0:
+            print(f"CASE {case} OK")
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,32 @@
+"""Multi-GPU checks (one process per GPU): in-kernel collectives over symmetric memory, the GEMM fused with
+reduce-scatter / all-gather, and tensor / pipeline parallel GPT training."""
+import pytest
+import torch
+
+from test_parallel_cpu import run_case
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _n(want):
+    have = torch.cuda.device_count()
+    if have < want:
+        pytest.skip(f"needs {want} GPUs")
+    return want
+
+
+def test_collectives_2gpu():
+    run_case("collectives", _n(2), "cuda")
+
+
+def test_fused_gemm_collectives_2gpu():
+    run_case("fused_gemm", _n(2), "cuda")
+
+
+def test_tensor_parallel_matches_unsharded_2gpu():
+    run_case("tp_matches_single", _n(2), "cuda")
+
+
+@pytest.mark.parametrize("case,n", [("gpt_2_1_1", 2), ("gpt_1_2_1", 2), ("gpt_1_1_2", 2), ("gpt_2_2_1", 4)])
+def test_gpt_parallel_training_gpu(case, n):
+    run_case(case, _n(n), "cuda")

@@ -1,0 +1,28 @@
+"""Multi-process (gloo, CPU) checks of tensor / pipeline / data parallel training logic."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_PORT = [29620]
+
+
+def run_case(case, nproc, dev="cpu", timeout=600):
+    _PORT[0] += 1
+    env = dict(os.environ, OMP_NUM_THREADS="2", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_PORT[0]), os.path.join(ROOT, "tests", "mp_worker.py"),
+           case, dev]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert p.returncode == 0 and f"CASE {case} OK" in p.stdout, p.stdout[-4000:]
+
+
+def test_tensor_parallel_matches_unsharded_cpu():
+    run_case("tp_matches_single", 2)
+
+
+@pytest.mark.parametrize("case,n", [("gpt_2_1_1", 2), ("gpt_1_2_1", 2), ("gpt_1_1_2", 2), ("gpt_2_2_1", 4)])
+def test_gpt_parallel_training_cpu(case, n):
+    run_case(case, n)
