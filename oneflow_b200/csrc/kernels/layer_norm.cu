@@ -297,3 +297,89 @@ OFB_API int ofb_layer_norm_bwd(const void* dy, const void* x, const void* gamma,
   }
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// LayerNorm backward for callers that must not allocate (declared in ofb_noalloc.h).
+//
+// The regular entry point above takes its partial-sum scratch from the caller, who normally gets it
+// from an allocator. Some callers have none they may touch at that moment: code running inside a
+// latency-critical serving loop that has frozen its memory pool, a plug-in that is handed raw device
+// pointers by a host application and is forbidden to call cudaMalloc, or a step replayed under a
+// memory budget that is already spoken for. For them the scratch lives in the library image itself.
+//
+// The array below is ordinary device memory reserved when the library is loaded: every GPU that loads
+// libofb_kernels.so keeps kNoAllocScratchFloats * 4 bytes (9.25 MiB) until the process exits.
+// Its size bounds the problem: cols <= kNoAllocMaxCols (rows are unlimited - the number of partial rows
+// is capped at 296 whatever the row count).
+//
+// All calls share the one array and it keeps whatever the last call left in it. Nothing in it has to
+// start at zero (each CTA overwrites its whole partial row before the fold reads it), so no clearing
+// pass runs; but two calls that overlap on the GPU (different streams, or different threads launching
+// at once) would write the same partial rows and race. Issue the calls on one stream, or order them
+// with events.
+//
+// The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that
+// device current) and remembers it; that first call should therefore happen before any stream capture
+// begins. No call here allocates or frees memory.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxCols = 4096;
+constexpr int kNoAllocMaxParts = 296;
+constexpr long long kNoAllocScratchFloats = 2ll * kNoAllocMaxParts * kNoAllocMaxCols;
+static __device__ __align__(256) float g_ln_bwd_scratch[kNoAllocScratchFloats];
+
+// In host code `g_ln_bwd_scratch` only names the symbol; the device address has to be asked for,
+// once per device, while that device is current.
+int noalloc_scratch_ptr(float** out) {
+  static float* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  OFB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ::ofb::fail("layer_norm_bwd_noalloc: unsupported device ordinal");
+  std::lock_guard<std::mutex> g(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_ln_bwd_scratch);
+    if (e != cudaSuccess) return ::ofb::fail(std::string("cudaGetSymbolAddress(g_ln_bwd_scratch): ") + cudaGetErrorString(e));
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+}  // namespace
+
+OFB_API int ofb_layer_norm_bwd_noalloc_max_cols(void) { return kNoAllocMaxCols; }
+
+OFB_API int ofb_layer_norm_bwd_noalloc(const void* dy, const void* x, const void* gamma, const float* mean,
+                                       const float* rstd, const void* add_to_dx, void* dx, float* dgamma, float* dbeta,
+                                       int accumulate_param_grads, int rows, int cols, void* stream) {
+  if (cols > kNoAllocMaxCols)
+    return fail("layer_norm_bwd_noalloc: cols = " + std::to_string(cols) + " exceeds the built-in scratch (max " +
+                std::to_string(kNoAllocMaxCols) + " columns); use ofb_layer_norm_bwd with caller-provided scratch");
+  if (cols % 8 != 0) return fail("layer_norm_bwd_noalloc: cols must be a multiple of 8");
+  if (rows <= 0) return 0;
+  float* scratch = nullptr;
+  if (noalloc_scratch_ptr(&scratch)) return -1;
+  int nv;
+  const int threads = ln_block_threads(cols, nv);
+  const int grid = rows < kNoAllocMaxParts ? rows : kNoAllocMaxParts;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  float* pg = dgamma ? scratch : nullptr;
+  float* pb = dgamma ? scratch + static_cast<long long>(grid) * cols : nullptr;
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto AD = reinterpret_cast<const __nv_bfloat16*>(add_to_dx);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  switch (nv) {
+    case 1: layer_norm_bwd_kernel<1><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+    case 2: layer_norm_bwd_kernel<2><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+    default: layer_norm_bwd_kernel<4><<<grid, threads, 0, s>>>(DY, X, G, mean, rstd, AD, DX, pg, pb, rows, cols); break;
+  }
+  OFB_CUDA_OK(cudaGetLastError());
+  if (dgamma) {
+    fold_partials_kernel<<<(cols + 127) / 128, 128, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
+    OFB_CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}
