@@ -1,0 +1,87 @@
+"""Stand-ins for the classes the reference's C extension exposes and that appear by name in pickled
+checkpoints: ``oneflow._oneflow_internal.dtype`` (state: DataType enum int), ``.placement`` (state:
+{"type", "ranks"}) and ``.sbp.sbp`` (state: ("S", axis) | ("B", -1) | ("P", -1)).
+Reference: oneflow/api/python/framework/dtype.cpp:37-44, symbol/placement_symbol.cpp,
+symbol/sbp_symbol.cpp:62-106."""
+import sys
+import types
+
+import torch
+
+from oneflow_b200.framework import dtype as _D
+from oneflow_b200.framework.placement import placement as _Placement
+from oneflow_b200 import sbp as _S
+
+
+class dtype:
+    __slots__ = ("enum",)
+
+    def __init__(self, enum=2):
+        self.enum = enum
+
+    @classmethod
+    def of(cls, torch_dtype):
+        return cls(_D.ENUM_OF[torch_dtype])
+
+    @property
+    def torch_dtype(self):
+        return _D.DTYPE_OF_ENUM[self.enum]
+
+    def __getstate__(self):
+        return self.enum
+
+    def __setstate__(self, state):
+        self.enum = int(state)
+
+    def __eq__(self, other):
+        if isinstance(other, dtype):
+            return self.enum == other.enum
+        if isinstance(other, torch.dtype):
+            return self.torch_dtype == other
+        return NotImplemented
+
+    def __hash__(self):
+        return hash(self.enum)
+
+    def __repr__(self):
+        return "oneflow." + str(self.torch_dtype).split(".")[-1]
+
+
+class placement(_Placement):
+    @classmethod
+    def of(cls, p):
+        return cls(p.type, p.ranks.tolist())
+
+
+sbp = types.ModuleType("oneflow._oneflow_internal.sbp")
+
+
+class _sbp:
+    __slots__ = ("kind", "axis")
+
+    def __init__(self, kind="B", axis=-1):
+        self.kind, self.axis = kind, axis
+
+    @classmethod
+    def of(cls, s):
+        return cls(s.kind, s.axis)
+
+    def to_sbp(self):
+        return _S.sbp(self.kind, self.axis)
+
+    def __getstate__(self):
+        return (self.kind, self.axis)
+
+    def __setstate__(self, state):
+        self.kind, self.axis = state[0], int(state[1])
+
+    def __repr__(self):
+        return repr(self.to_sbp())
+
+
+_sbp.__name__ = _sbp.__qualname__ = "sbp"
+_sbp.__module__ = "oneflow._oneflow_internal.sbp"
+sbp.sbp = _sbp
+sys.modules["oneflow._oneflow_internal.sbp"] = sbp
+dtype.__module__ = "oneflow._oneflow_internal"
+placement.__module__ = "oneflow._oneflow_internal"

@@ -1,0 +1,198 @@
+"""``flow._C``: the functional ops of the reference that have no torch spelling — the fused ops named in
+oneflow/core/functional/functional_api.yaml (:1254 fused_bias_add_gelu, :1549 fused_scale_tril_softmax_mask_scale,
+:2651-2703 attention, :2815 fused_dot_feature_interaction, fused_mlp) — with autograd. bf16 CUDA tensors
+run the hand-written sm_100a kernels; other inputs take the PyTorch statement of the same maths. Anything
+else resolves to the torch function of the same name."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .framework.global_tensor import to_global, to_local  # noqa: F401
+from .ops import gemm as G
+from .ops import kernels as K
+
+
+def _native_ok(*ts):
+    return all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts) and ts[0].shape[-1] % 8 == 0
+
+
+class _BiasAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, act):
+        ctx.save_for_backward(x, bias)
+        ctx.act = act
+        return K.bias_act_fwd(x.contiguous(), bias, act)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, bias = ctx.saved_tensors
+        dx = K.bias_act_bwd(x.contiguous(), bias, dy.contiguous(), ctx.act)
+        db = K.column_sum(dx.reshape(-1, dx.shape[-1])).to(bias.dtype) if bias is not None else None
+        return dx, db, None
+
+
+def fused_bias_add_gelu(x, bias, *, axis=-1):
+    """gelu(x + bias) with bias broadcast along ``axis`` (last axis for the kernel path)."""
+    if _native_ok(x, bias) and (axis in (-1, x.dim() - 1)):
+        return _BiasAct.apply(x, bias, G.ACT_GELU)
+    shape = [1] * x.dim()
+    shape[axis] = -1
+    return torch.nn.functional.gelu(x + bias.reshape(shape))
+
+
+def fused_bias_add_dropout(x, bias, *, p=0.5, axis=-1, generator=None, training=True):
+    """dropout(x + bias, p)."""
+    shape = [1] * x.dim()
+    shape[axis] = -1
+    return torch.nn.functional.dropout(x + bias.reshape(shape), p, training)
+
+
+def fused_bias_add_mask_scale(x, bias, mask, scale, addend=None, *, axis=-1):
+    return K.bias_mask_scale(x.contiguous(), bias, mask, scale, addend) if _native_ok(x, bias) and not x.requires_grad \
+        else ((x + bias) * mask.to(x.dtype) * scale + (addend if addend is not None else 0))
+
+
+class _TrilSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, diagonal, tril_scale, mask_scale):
+        y, sm = K.softmax_fwd(x.contiguous(), scale=tril_scale, tril=True, diagonal=diagonal, dropout_mask=mask,
+                              dropout_scale=mask_scale, want_softmax=True)
+        ctx.save_for_backward(sm, mask)
+        ctx.args = (diagonal, tril_scale, mask_scale)
+        return y, sm
+
+    @staticmethod
+    def backward(ctx, dy, _dsm):
+        sm, mask = ctx.saved_tensors
+        diagonal, tril_scale, mask_scale = ctx.args
+        dx = K.softmax_bwd(sm, dy.contiguous(), scale=tril_scale, tril=True, diagonal=diagonal, dropout_mask=mask,
+                           dropout_scale=mask_scale)
+        return dx, None, None, None, None
+
+
+def fused_scale_tril_softmax_mask_scale(x, mask, *, diagonal=0, tril_scale_value=1.0, mask_scale_value=1.0,
+                                        tril_fill_value=float("-inf")):
+    """(dropout_mask * softmax(tril(x * tril_scale)) * mask_scale, softmax_y) over [.., s_q, s_k] scores."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
+        return _TrilSoftmax.apply(x, mask, diagonal, tril_scale_value, mask_scale_value)
+    s_q, s_k = x.shape[-2:]
+    keep = torch.ones(s_q, s_k, dtype=torch.bool, device=x.device).tril(diagonal)
+    sm = torch.softmax((x * tril_scale_value).masked_fill(~keep, float("-inf")), -1)
+    y = sm * (mask.to(x.dtype) if mask is not None else 1.0) * mask_scale_value
+    return y, sm
+
+
+def fused_scale_mask_softmax(x, mask, fill_value=-10000.0, scale=1.0):
+    """softmax(masked_fill(x * scale, mask == 0, fill_value))."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and not x.requires_grad and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048 \
+            and mask.numel() % x.shape[-1] == 0 and (x.numel() // x.shape[-1]) % (mask.numel() // x.shape[-1]) == 0:
+        return K.softmax_fwd(x.contiguous(), scale=scale, attn_mask=mask, mask_fill=fill_value)
+    return torch.softmax((x * scale).masked_fill(~mask.bool(), fill_value), -1)
+
+
+def fused_scale_mask_softmax_dropout(x, mask, dropout_mask, fill_value=-10000.0, scale=1.0, p=0.5):
+    sm = fused_scale_mask_softmax(x, mask, fill_value, scale)
+    return sm * dropout_mask.to(x.dtype) * (1.0 / (1.0 - p)), sm
+
+
+class _Fmha(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = K.fmha_fwd(q, k, v, causal=causal, scale=scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o.contiguous(), lse, causal=ctx.causal, scale=ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def _bshd_ok(t):
+    B, S, H, D = t.shape
+    return t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == S * t.stride(1) and t.data_ptr() % 16 == 0
+
+
+def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None):
+    """query/key/value: [B, H, S, D] (torch convention). The fused tcgen05 kernel is used for bf16 CUDA inputs
+    with head dim 64/128, no explicit mask and no dropout."""
+    D = query.shape[-1]
+    if (query.is_cuda and query.dtype == torch.bfloat16 and D in (64, 128) and attn_mask is None and dropout_p == 0.0
+            and query.shape == key.shape == value.shape):
+        q, k, v = (t.transpose(1, 2) for t in (query, key, value))  # [B, S, H, D] views
+        if not all(_bshd_ok(t) for t in (q, k, v)):
+            q, k, v = (t.contiguous() for t in (q, k, v))
+        sc = scale if scale is not None else 1.0 / math.sqrt(D)
+        return _Fmha.apply(q, k, v, bool(is_causal), sc).transpose(1, 2)
+    return torch.nn.functional.scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale=scale)
+
+
+def fused_multi_head_attention_inference(query, key, value, num_heads, causal=False, query_hidden_slice_start=0,
+                                         query_hidden_slice_end=-1, key_hidden_slice_start=0, key_hidden_slice_end=-1,
+                                         value_hidden_slice_start=0, value_hidden_slice_end=-1, attn_bias=None,
+                                         causal_diagonal_offset=0):
+    """query/key/value: [B, S, hidden(_slices)] packed layouts (BM(HK)); returns [B, S, H*D]."""
+    def sl(t, a, b):
+        return t[..., a:(t.shape[-1] if b == -1 else b)]
+    q = sl(query, query_hidden_slice_start, query_hidden_slice_end)
+    k = sl(key, key_hidden_slice_start, key_hidden_slice_end)
+    v = sl(value, value_hidden_slice_start, value_hidden_slice_end)
+    B, S, HD = q.shape
+    D = HD // num_heads
+    q4, k4, v4 = (t.reshape(B, t.shape[1], num_heads, D) for t in (q, k, v))
+    if (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and attn_bias is None and causal_diagonal_offset == 0
+            and k.shape[1] == S and all(_bshd_ok(t) for t in (q4, k4, v4))):
+        with torch.no_grad():
+            out, _ = K.fmha_fwd(q4, k4, v4, causal=causal)
+        return out.reshape(B, S, HD)
+    o = torch.nn.functional.scaled_dot_product_attention(q4.transpose(1, 2), k4.transpose(1, 2), v4.transpose(1, 2),
+                                                         attn_mask=attn_bias, is_causal=causal and attn_bias is None)
+    return o.transpose(1, 2).reshape(B, S, HD)
+
+
+def fused_multi_head_attention_inference_v2(*, query, query_layout="BM(HK)", query_head_size=None, key=None,
+                                            key_layout=None, value=None, value_layout=None, attn_bias=None,
+                                            output_layout="BM(HK)", causal=False, scale=None, **unused):
+    H = query.shape[-1] // query_head_size
+    return fused_multi_head_attention_inference(query, key, value, H, causal=causal, attn_bias=attn_bias)
+
+
+def fused_mlp(x, weights, biases, skip_final_activation=False):
+    from .nn.modules.fused_mlp import fused_linear_act
+    n = len(weights)
+    for i, (w, b) in enumerate(zip(weights, biases)):
+        x = fused_linear_act(x, w, b, 0 if (i == n - 1 and skip_final_activation) else 3)
+    return x
+
+
+def fused_matmul_bias(x, weight, bias, _add_to_output=None, alpha=1.0, beta=1.0):
+    from .nn.modules.fused_mlp import fused_linear_act
+    y = fused_linear_act(x, weight, bias, 0)
+    return y if _add_to_output is None else y * alpha + _add_to_output * beta
+
+
+def fused_dot_feature_interaction(features, output_concat=None, self_interaction=False, output_padding=0, pooling="none"):
+    from .ops.interaction import dot_feature_interaction
+    return dot_feature_interaction(features, output_concat, self_interaction, output_padding, pooling)
+
+
+def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+    return torch.nn.functional.layer_norm(x, normalized_shape, weight, bias, eps)
+
+
+def local_all_reduce(x, inplace=False):
+    from . import comm
+    t = x if inplace else x.clone()
+    return comm.all_reduce(t)
+
+
+def __getattr__(name):
+    if hasattr(torch, name):
+        return getattr(torch, name)
+    if hasattr(torch.nn.functional, name):
+        return getattr(torch.nn.functional, name)
+    raise AttributeError(f"flow._C has no op {name!r}")

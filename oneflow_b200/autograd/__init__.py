@@ -1,0 +1,5 @@
+"""``flow.autograd``: torch.autograd under the flow names (backward, grad, Function, functional.*, graph
+saved-tensor hooks, grad modes). Reference: python/oneflow/autograd/*.py."""
+from torch.autograd import *  # noqa: F401,F403
+from torch.autograd import Function, backward, functional, grad, graph  # noqa: F401
+from torch import enable_grad, inference_mode, no_grad, set_grad_enabled  # noqa: F401

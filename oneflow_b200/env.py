@@ -1,0 +1,75 @@
+"""``flow.env``: rank / world queries and process-group bootstrap from MASTER_ADDR / MASTER_PORT /
+WORLD_SIZE / RANK / LOCAL_RANK (reference: python/oneflow/env.py:19-93,
+python/oneflow/framework/env_util.py:167-192). The control plane is torch.distributed's TCPStore; the
+data plane is gloo for CPU tensors and NCCL plus the in-tree peer-memory kernels for CUDA tensors."""
+from __future__ import annotations
+
+import datetime
+import os
+
+import torch
+import torch.distributed as dist
+
+_initialized_here = False
+
+
+def init(backend=None, timeout_seconds=None):
+    """Joins the job described by the launcher's environment variables (no-op for a single process)."""
+    global _initialized_here
+    if dist.is_initialized():
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1 and "RANK" not in os.environ:
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    if backend is None:
+        backend = "cpu:gloo,cuda:nccl" if torch.cuda.is_available() else "gloo"
+    timeout = datetime.timedelta(seconds=timeout_seconds or int(os.environ.get("ONEFLOW_TIMEOUT_SECONDS", "7200")))
+    kwargs = {}
+    if torch.cuda.is_available():
+        torch.cuda.set_device(get_local_rank())
+    dist.init_process_group(backend, timeout=timeout, **kwargs)
+    _initialized_here = True
+
+
+def get_rank():
+    return dist.get_rank() if dist.is_initialized() else int(os.environ.get("RANK", "0"))
+
+
+def get_world_size():
+    return dist.get_world_size() if dist.is_initialized() else int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def get_local_rank():
+    return int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def get_node_size():
+    local = int(os.environ.get("LOCAL_WORLD_SIZE", str(get_world_size())))
+    return max(1, get_world_size() // max(local, 1))
+
+
+def is_multi_client():
+    return True
+
+
+def init_rdma():
+    """Kept for API compatibility: intra-node traffic uses NVLink peer memory, there is no RDMA path."""
+    return None
+
+
+def rdma_is_initialized():
+    return False
+
+
+def all_device_placement(device_type):
+    from .framework.placement import placement
+    return placement.all(device_type)
+
+
+def shutdown():
+    global _initialized_here
+    if dist.is_initialized() and _initialized_here:
+        dist.destroy_process_group()
+        _initialized_here = False

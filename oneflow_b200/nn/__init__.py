@@ -1,0 +1,43 @@
+"""``flow.nn``: torch.nn's layers (Module, Linear, Conv*, norms, RNNs, losses, ...) under the flow names,
+plus what the reference adds: ``Graph``, ``parallel.DistributedDataParallel``, ``FusedMLP``,
+``Module.to_global / to_local``, ``utils.clip_grad_norm_`` aware of global tensors, and the few layers
+torch lacks (``CombinedMarginLoss``, ``FusedBatchNorm*`` aliases, ``RMSNorm`` when missing)."""
+import torch as _torch
+import torch.nn as _tnn
+from torch.nn import *  # noqa: F401,F403
+from torch.nn import Module  # noqa: F401
+
+from . import functional, init  # noqa: F401
+
+from . import graph, module_ext, parallel, utils  # noqa: F401
+from .graph import Graph  # noqa: F401
+from .modules import FusedMLP  # noqa: F401
+from .extra_modules import (CombinedMarginLoss, FusedBatchNorm1d, FusedBatchNorm2d, FusedBatchNorm3d, MinMaxObserver,  # noqa: F401
+                            MovingAverageMinMaxObserver, FakeQuantization, Quantization)
+
+
+
+class _ParameterMeta(type):
+    def __instancecheck__(cls, obj):
+        return isinstance(obj, _tnn.Parameter) or getattr(obj, "_is_param", False)
+
+    def __call__(cls, data=None, requires_grad=True):
+        return _tnn.Parameter(data, requires_grad)
+
+
+class Parameter(metaclass=_ParameterMeta):
+    """``flow.nn.Parameter(data, requires_grad=True)`` builds a torch Parameter (global tensors stay global
+    and are marked as parameters); the class object is also the ``oneflow.nn.Parameter`` path of checkpoints."""
+    _pickle_state = None
+
+    def __getstate__(self):
+        return self._pickle_state
+
+
+Parameter.__module__ = "oneflow.nn"
+module_ext.install()
+GraphModule = graph.GraphModule
+
+
+def __getattr__(name):
+    return getattr(_tnn, name)

@@ -1,0 +1,439 @@
+"""``flow.nn.Graph``: the static-graph training / inference front-end.
+
+The reference traces ``build()`` into a Job, runs ~45 rewrite passes and executes a Plan on an actor
+runtime (python/oneflow/nn/graph/graph.py:257-286, 846-877, 1359-1449, 1740-1795). Here the same contract
+is met without a tracing compiler: ``build()`` runs on the eager engine (global tensors dispatch through
+the SBP rules, kernels launch on CUDA streams), and nn.Graph supplies what the passes provided —
+
+* one call = one mini-batch: with ``set_gradient_accumulation_steps(N)`` tensor inputs are unpacked on
+  dim 0 into N micro-batches, gradients accumulate, outputs are packed again (lazy_op_interpreter.cpp:270-330);
+* ``loss.backward()`` inside ``build`` feeds the optimizers added with ``add_optimizer``; after the last
+  micro-batch gradients are clipped (``clip_grad_max_norm``), the (fused) optimizer steps, LR schedulers
+  step and the train-step counter advances;
+* ``config.enable_amp`` runs ``build`` under autocast; ``set_grad_scaler`` adds dynamic / static loss scaling;
+* ``config.enable_zero`` turns broadcast parameters (and therefore their optimizer states) into ``S(0)``
+  shards over the data-parallel axis (optimizer_placement_optimization_pass.cpp);
+* ``GraphModule.set_stage(stage_id, placement)`` moves a block's inputs to its stage's placement
+  (proxy.py:240-308), ``activation_checkpointing`` recomputes the block in backward;
+* ``state_dict`` / ``load_state_dict`` cover module blocks, optimizer states and ``System-Train-TrainStep``;
+* inputs must keep the same meta on every call (nn_graph.cpp:882-893).
+"""
+from __future__ import annotations
+
+import contextlib
+from collections import OrderedDict
+from typing import List
+
+import torch
+import torch.distributed as dist
+
+from ...framework import global_tensor as GT
+from ... import sbp as S
+from .graph_config import GraphConfig
+
+
+class GraphModule:
+    """Per-block graph settings reached through ``block.to(GraphModule)`` (or the older ``block.config``)."""
+
+    def __init__(self, proxy):
+        self._proxy = proxy
+        self.stage_id = None
+        self.stage_placement = None
+        self.activation_checkpointing = False
+
+    def set_stage(self, stage_id=None, placement=None):
+        self.stage_id, self.stage_placement = stage_id, placement
+        return self
+
+    # older attribute-style API
+    @property
+    def stage_id_(self):
+        return self.stage_id
+
+
+class ModuleProxy:
+    """What ``self.m = module`` becomes inside a Graph: calls go to the module, with stage placement and
+    activation checkpointing applied; attribute access reaches sub-modules (as proxies) and parameters."""
+
+    def __init__(self, module, name, graph):
+        object.__setattr__(self, "_module", module)
+        object.__setattr__(self, "_name", name)
+        object.__setattr__(self, "_graph", graph)
+        object.__setattr__(self, "_gm", GraphModule(self))
+        object.__setattr__(self, "_children", {})
+
+    def to(self, kind=None, *args, **kwargs):
+        if kind is GraphModule or kind is None:
+            return self._gm
+        if kind is torch.nn.Module:
+            return self._module
+        self._module.to(kind, *args, **kwargs)
+        return self
+
+    @property
+    def config(self):
+        return self._gm
+
+    @property
+    def origin(self):
+        return self._module
+
+    def __getattr__(self, name):
+        mod = object.__getattribute__(self, "_module")
+        child = mod._modules.get(name) if hasattr(mod, "_modules") else None
+        if child is not None:
+            ch = self._children.get(name)
+            if ch is None:
+                ch = ModuleProxy(child, f"{self._name}.{name}", self._graph)
+                self._children[name] = ch
+            return ch
+        return getattr(mod, name)
+
+    def __setattr__(self, name, value):
+        setattr(self._module, name, value)
+
+    def __call__(self, *args, **kwargs):
+        gm = self._gm
+        if gm.stage_placement is not None:
+            args = tuple(_to_stage(a, gm.stage_placement) for a in args)
+            kwargs = {k: _to_stage(v, gm.stage_placement) for k, v in kwargs.items()}
+        mod = self._module
+        fn = mod
+        if self._children:
+            fn = _ChildPatched(self)
+        if gm.activation_checkpointing and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint
+            return checkpoint(fn, *args, use_reentrant=False, **kwargs)
+        return fn(*args, **kwargs)
+
+
+class _ChildPatched:
+    """Calls the module while its direct children are temporarily replaced by their proxies, so that stage /
+    checkpoint settings of nested blocks take effect."""
+
+    def __init__(self, proxy):
+        self.proxy = proxy
+
+    def __call__(self, *args, **kwargs):
+        mod = self.proxy._module
+        saved = {}
+        for name, ch in self.proxy._children.items():
+            saved[name] = mod._modules[name]
+            mod._modules[name] = _CallShim(ch)
+        try:
+            return mod(*args, **kwargs)
+        finally:
+            for name, m in saved.items():
+                mod._modules[name] = m
+
+
+class _CallShim(torch.nn.Module):
+    def __init__(self, proxy):
+        super().__init__()
+        object.__setattr__(self, "_p", proxy)
+
+    def forward(self, *a, **k):
+        return self._p(*a, **k)
+
+
+def _to_stage(x, placement):
+    if isinstance(x, GT.GlobalTensor) and x.placement != placement:
+        nd = x.sbp if len(x.sbp) == placement.ndim else (S.broadcast,) * placement.ndim
+        return GT.to_global(x, placement, nd)
+    return x
+
+
+class Graph:
+    _nesting = 0
+
+    def __init__(self, enable_get_runtime_state_dict=False):
+        object.__setattr__(self, "_blocks", OrderedDict())
+        self.config = GraphConfig()
+        self._opts = []            # dicts: optim, lr_sch, is_sparse
+        self._grad_scaler = None
+        self._compiled = False
+        self._train_step = 0
+        self._input_meta = None
+        self._debug_level = -1
+        self._debug_ranks = None
+        self._name = f"{type(self).__name__}_{id(self) & 0xffff}"
+        self._pending_state = None
+
+    # ------------------------------------------------------------------ construction API
+    def __setattr__(self, name, value):
+        if isinstance(value, torch.nn.Module):
+            self._blocks[name] = ModuleProxy(value, name, self)
+            return
+        object.__setattr__(self, name, value)
+
+    def __getattr__(self, name):
+        blocks = object.__getattribute__(self, "_blocks")
+        if name in blocks:
+            return blocks[name]
+        raise AttributeError(name)
+
+    def build(self, *args, **kwargs):
+        raise NotImplementedError("nn.Graph subclasses must implement build()")
+
+    def add_optimizer(self, optim, *, lr_sch=None, is_sparse=False):
+        if lr_sch is not None and getattr(lr_sch, "optimizer", optim) is not optim:
+            raise ValueError("lr_sch must wrap the optimizer it is added with")
+        self._opts.append({"optim": optim, "lr_sch": lr_sch, "is_sparse": is_sparse})
+        self.config.training = True
+
+    def set_grad_scaler(self, grad_scaler):
+        self._grad_scaler = grad_scaler
+
+    @property
+    def name(self):
+        return self._name
+
+    @property
+    def training(self):
+        return self.config.training
+
+    def debug(self, v_level=-1, *, ranks=None, max_py_stack_depth=2, only_user_py_stack=True, op_repr_with_py_stack=False):
+        self._debug_level, self._debug_ranks = v_level, ranks
+        from ...framework import boxing
+        me = dist.get_rank() if dist.is_initialized() else 0
+        boxing.debug_routes = v_level >= 1 and (ranks is None or me in (ranks if isinstance(ranks, (list, tuple)) else [ranks]))
+
+    @classmethod
+    def trace(cls, func):
+        """Wraps a plain function as a graph (inference): ``g = Graph.trace(f); g(x)``."""
+        class _Traced(Graph):
+            def build(self, *a, **k):
+                return func(*a, **k)
+        return _Traced()
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self, destination=None):
+        sd = destination if destination is not None else OrderedDict()
+        for name, proxy in self._blocks.items():
+            sd[name] = proxy._module.state_dict()
+        for i, o in enumerate(self._opts):
+            opt = o["optim"]
+            sd[f"System-Optimizer-{i}"] = opt.state_dict()
+            if o["lr_sch"] is not None:
+                sd[f"System-LRScheduler-{i}"] = o["lr_sch"].state_dict()
+        if self._grad_scaler is not None and hasattr(self._grad_scaler, "state_dict"):
+            sd["System-GradScaler"] = self._grad_scaler.state_dict()
+        sd["System-Train-TrainStep"] = torch.tensor([self._train_step], dtype=torch.int64)
+        return sd
+
+    def load_state_dict(self, state_dict, strict=True):
+        for name, proxy in self._blocks.items():
+            if name in state_dict:
+                proxy._module.load_state_dict(state_dict[name], strict=strict)
+            elif strict:
+                raise KeyError(f"missing block {name} in state dict")
+        for i, o in enumerate(self._opts):
+            k = f"System-Optimizer-{i}"
+            if k in state_dict:
+                o["optim"].load_state_dict(state_dict[k])
+            k = f"System-LRScheduler-{i}"
+            if k in state_dict and o["lr_sch"] is not None:
+                o["lr_sch"].load_state_dict(state_dict[k])
+        if "System-GradScaler" in state_dict and self._grad_scaler is not None:
+            self._grad_scaler.load_state_dict(state_dict["System-GradScaler"])
+        ts = state_dict.get("System-Train-TrainStep")
+        if ts is not None:
+            self._train_step = int(torch.as_tensor(ts).reshape(-1)[0])
+
+    def runtime_state_dict(self, destination=None):
+        """State needed to run without re-compiling: there is no compiled plan to cache here, so this is
+        the ordinary state dict plus the recorded input meta."""
+        sd = self.state_dict(destination)
+        sd["System-InputMeta"] = self._input_meta
+        return sd
+
+    def load_runtime_state_dict(self, state_dict, *, warmup_with_run=True):
+        self._input_meta = state_dict.get("System-InputMeta")
+        self.load_state_dict({k: v for k, v in state_dict.items() if k != "System-InputMeta"}, strict=False)
+
+    # ------------------------------------------------------------------ compile
+    def _all_params(self):
+        seen, out = set(), []
+        for o in self._opts:
+            for g in o["optim"].param_groups:
+                for p in g["params"]:
+                    if id(p) not in seen:
+                        seen.add(id(p))
+                        out.append(p)
+        return out
+
+    def _apply_zero(self):
+        """B parameters become S(0) shards on the first mesh axis whose size divides dim 0 (ZeRO): the
+        optimizer states created from them are sharded alike, gradients arrive by reduce-scatter and the
+        consumers all-gather on use."""
+        if self.config.zero_stage <= 0:
+            return
+        for p in self._all_params():
+            if not isinstance(p, GT.GlobalTensor):
+                continue
+            if p.numel() < self.config.zero_shard_min_size:
+                continue
+            nd = list(p.sbp)
+            for axis, s in enumerate(nd):
+                n = p.placement.hierarchy[axis]
+                if s.kind == "B" and n > 1 and p.dim() > 0 and p.shape[0] % n == 0 and \
+                        not any(o.kind == "S" and o.axis == 0 for o in nd):
+                    nd[axis] = S.split(0)
+                    break
+            if tuple(nd) != p.sbp:
+                new = GT.rebox(p.detach(), nd)
+                p._local, p._nd_sbp = new._local, new._nd_sbp
+
+    def _compile(self, args):
+        if Graph._nesting > 0:
+            raise RuntimeError("nn.Graph objects cannot be nested")
+        self._apply_zero()
+        self._compiled = True
+        if self._pending_state is not None:
+            self.load_state_dict(self._pending_state)
+            self._pending_state = None
+
+    @staticmethod
+    def _meta(a):
+        if isinstance(a, GT.GlobalTensor):
+            return ("g", tuple(a.shape), a.dtype, a.placement, a.sbp)
+        if isinstance(a, torch.Tensor):
+            return ("l", tuple(a.shape), a.dtype, a.device.type)
+        return ("o", type(a))
+
+    # ------------------------------------------------------------------ run
+    def __call__(self, *args, **kwargs):
+        if not self._compiled:
+            self._compile(args)
+            self._input_meta = [self._meta(a) for a in args]
+        else:
+            meta = [self._meta(a) for a in args]
+            if self._input_meta is not None and meta != self._input_meta:
+                raise RuntimeError(f"nn.Graph {self._name}: inputs must keep the same shape/dtype/placement/sbp on every call "
+                                   f"(first call {self._input_meta}, now {meta})")
+        return self._run(args, kwargs)
+
+    @contextlib.contextmanager
+    def _backward_scaling(self, factor_fn):
+        """Inside build(), ``loss.backward()`` applies the gradient-accumulation average and the loss scale."""
+        orig = torch.Tensor.backward
+
+        def backward(t, gradient=None, *a, **k):
+            f = factor_fn()
+            if f != 1.0:
+                if gradient is None:
+                    if t.numel() != 1:
+                        raise RuntimeError("only a scalar loss may call backward() inside nn.Graph.build")
+                    gradient = torch.ones_like(t) * f
+                else:
+                    gradient = gradient * f
+            return orig(t, gradient, *a, **k)
+        torch.Tensor.backward = backward
+        try:
+            yield
+        finally:
+            torch.Tensor.backward = orig
+
+    def _run(self, args, kwargs):
+        cfg = self.config
+        n = cfg.grad_acc_steps if cfg.training else 1
+        micro_args = _unpack(args, n)
+        scaler = self._grad_scaler
+        loss_scale = float(scaler.get_scale()) if scaler is not None and hasattr(scaler, "get_scale") else 1.0
+        outs = []
+        Graph._nesting += 1
+        try:
+            ctx = contextlib.nullcontext()
+            if cfg.amp_enabled:
+                dev = "cuda" if any(isinstance(a, torch.Tensor) and a.device.type == "cuda" for a in args) else "cpu"
+                ctx = torch.autocast(dev, dtype=cfg.amp_dtype if dev == "cuda" or cfg.amp_dtype == torch.bfloat16 else torch.bfloat16)
+            grad_ctx = contextlib.nullcontext() if cfg.training else torch.no_grad()
+            with ctx, grad_ctx, self._backward_scaling(lambda: loss_scale / n):
+                for m in range(n):
+                    outs.append(self.build(*micro_args[m], **kwargs))
+        finally:
+            Graph._nesting -= 1
+        if cfg.training:
+            self._optimizer_step(loss_scale)
+        return _pack(outs)
+
+    def _optimizer_step(self, loss_scale):
+        scaler = self._grad_scaler
+        found_inf = False
+        params = self._all_params()
+        if loss_scale != 1.0:
+            inv = 1.0 / loss_scale
+            for p in params:
+                if p.grad is not None:
+                    p.grad.mul_(inv)
+        if scaler is not None and getattr(scaler, "dynamic", False):
+            bad = torch.zeros((), dtype=torch.float32)
+            for p in params:
+                if p.grad is not None:
+                    g = p.grad._local if isinstance(p.grad, GT.GlobalTensor) else p.grad
+                    if g.numel():
+                        bad = bad + (~torch.isfinite(g)).any().float().cpu()
+            if dist.is_initialized():
+                dist.all_reduce(bad)
+            found_inf = bool(bad.item() > 0)
+            scaler.update(found_inf)
+        if not found_inf:
+            for o in self._opts:
+                opt = o["optim"]
+                if hasattr(opt, "clip_grad"):
+                    opt.clip_grad()
+                opt.step()
+        for o in self._opts:
+            o["optim"].zero_grad(set_to_none=True)
+            if o["lr_sch"] is not None and not found_inf:
+                o["lr_sch"].step()
+        self._train_step += 1
+
+    def __repr__(self):
+        lines = [f"(GRAPH:{self._name}:{type(self).__name__}): ("]
+        for name, proxy in self._blocks.items():
+            gm = proxy._gm
+            extra = f", stage_id={gm.stage_id}, placement={gm.stage_placement}" if gm.stage_id is not None else ""
+            lines.append(f"  (MODULE:{name}:{type(proxy._module).__name__}{extra})")
+        lines.append(f"  (CONFIG: training={self.config.training}, amp={self.config.amp_enabled}, "
+                     f"zero={self.config.zero_stage}, grad_acc={self.config.grad_acc_steps})")
+        lines.append(")")
+        return "\n".join(lines)
+
+
+def _unpack(args, n):
+    """dim-0 unpack of every tensor argument into n micro-batches."""
+    if n == 1:
+        return [args]
+    out = [[] for _ in range(n)]
+    for a in args:
+        if isinstance(a, torch.Tensor) and a.dim() > 0:
+            if a.shape[0] % n:
+                raise ValueError(f"batch dimension {a.shape[0]} is not divisible by the {n} gradient accumulation steps")
+            if isinstance(a, GT.GlobalTensor):
+                m = a.shape[0] // n
+                pieces = [a[i * m:(i + 1) * m] for i in range(n)]
+                # keep the original layout for every micro-batch
+                pieces = [GT.to_global(p, a.placement, a.sbp) for p in pieces]
+            else:
+                pieces = list(a.chunk(n, 0))
+            for i in range(n):
+                out[i].append(pieces[i])
+        else:
+            for i in range(n):
+                out[i].append(a)
+    return [tuple(o) for o in out]
+
+
+def _pack(outs):
+    if len(outs) == 1:
+        return outs[0]
+    first = outs[0]
+    if isinstance(first, torch.Tensor):
+        dets = [o.detach() for o in outs]
+        return torch.stack(dets) if first.dim() == 0 else torch.cat(dets, 0)
+    if isinstance(first, (tuple, list)):
+        return type(first)(_pack([o[i] for o in outs]) for i in range(len(first)))
+    if isinstance(first, dict):
+        return {k: _pack([o[k] for o in outs]) for k in first}
+    return outs

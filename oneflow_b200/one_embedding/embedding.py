@@ -1,0 +1,493 @@
+"""OneEmbedding: embedding tables far larger than one device, hash-sharded over the ranks.
+
+Public surface follows python/oneflow/one_embedding.py (:177-558 Embedding classes, :560-725 store
+options, :727-815 initializers, :1301-1340 Optimizer wrapper):
+
+    table = make_table_options(make_uniform_initializer(-0.05, 0.05))
+    emb = MultiTableEmbedding("sparse", embedding_dim=128, dtype=flow.float16, key_type=flow.int64,
+                              tables=[table] * 26, store_options=make_device_mem_store_options(...))
+    y = emb(ids)                    # ids [batch, 26] -> [batch, 26, 128]
+    opt = Optimizer(emb, flow.optim.SGD)   # or Adam / Adagrad / Ftrl / SmartDecayAdam, momentum SGD
+
+Data flow per step (the three shuffles of the reference, oneflow/user/kernels/data_shuffle_kernel.cu and
+one_embedding_*_p2p_kernel.cu):
+  1. id shuffle       : unique the local (id, table) keys, send every key to its owner
+                        ``hash(key) % world`` (all-to-all-v), owners unique what they received;
+  2. embedding shuffle: owners look rows up in their store (missing rows are initialised by the table's
+                        initializer), send them back; an inverse-index gather rebuilds [batch, tables, dim];
+  3. gradient shuffle : row gradients are segment-summed per unique key, sent to the owners, summed there
+                        and applied by the sparse row optimizer (SGD / momentum / Adam / Adagrad / FTRL), the
+                        updated rows are put back into the store.
+A stored line is ``storage_dim = size_factor * embedding_dim`` floats: ``[embedding | optimizer state...]``.
+Stores: device memory (hash table + dense rows on the GPU), host memory behind a device LRU cache, SSD
+(``csrc/core/persistent_table.cpp``) behind the caches. Single-rank jobs skip the exchanges.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------------ option builders
+def make_uniform_initializer(low, high):
+    return {"type": "uniform", "low": float(low), "high": float(high)}
+
+
+def make_normal_initializer(mean, std):
+    return {"type": "normal", "mean": float(mean), "std": float(std)}
+
+
+def make_constant_initializer(value):
+    return {"type": "constant", "value": float(value)}
+
+
+def make_table_options(param):
+    """param: one initializer (whole table) or a list of column options."""
+    if isinstance(param, dict) and "type" in param:
+        return {"initializer": param}
+    if isinstance(param, (list, tuple)):
+        return {"columns": list(param)}
+    raise ValueError("make_table_options expects an initializer or a list of column options")
+
+
+make_table = make_table_options
+
+
+def make_column_options(initializer):
+    return {"initializer": initializer}
+
+
+def _check_capacity(capacity):
+    if capacity is None or capacity <= 0:
+        raise ValueError("capacity must be a positive number of rows")
+
+
+def make_device_mem_store_options(persistent_path, capacity, size_factor=1, physical_block_size=512):
+    _check_capacity(capacity)
+    return {"kv_store": {"caches": [{"policy": "full", "capacity": int(capacity), "value_memory_kind": "device"}],
+                         "persistent_table": {"path": persistent_path, "physical_block_size": physical_block_size}},
+            "size_factor": size_factor}
+
+
+def make_cached_ssd_store_options(cache_budget_mb, persistent_path, capacity=None, size_factor=1, physical_block_size=512,
+                                  host_cache_budget_mb=0):
+    if cache_budget_mb <= 0 and host_cache_budget_mb <= 0:
+        raise ValueError("cache_budget_mb or host_cache_budget_mb must be positive")
+    caches = []
+    if cache_budget_mb > 0:
+        caches.append({"policy": "lru", "cache_memory_budget_mb": cache_budget_mb, "value_memory_kind": "device"})
+    if host_cache_budget_mb > 0:
+        caches.append({"policy": "lru", "cache_memory_budget_mb": host_cache_budget_mb, "value_memory_kind": "host"})
+    pt = {"path": persistent_path, "physical_block_size": physical_block_size}
+    if capacity is not None:
+        pt["capacity_hint"] = int(capacity)
+    return {"kv_store": {"caches": caches, "persistent_table": pt}, "size_factor": size_factor}
+
+
+def make_cached_host_mem_store_options(cache_budget_mb, persistent_path, capacity, size_factor=1, physical_block_size=512):
+    _check_capacity(capacity)
+    if cache_budget_mb <= 0:
+        raise ValueError("cache_budget_mb must be positive")
+    return {"kv_store": {"caches": [{"policy": "lru", "cache_memory_budget_mb": cache_budget_mb, "value_memory_kind": "device"},
+                                    {"policy": "full", "capacity": int(capacity), "value_memory_kind": "host"}],
+                         "persistent_table": {"path": persistent_path, "physical_block_size": physical_block_size}},
+            "size_factor": size_factor}
+
+
+# ------------------------------------------------------------------------------------------------ key hashing
+def _mix64(k: torch.Tensor) -> torch.Tensor:
+    """64-bit finaliser (splitmix64 constants) on int64 tensors; wraps like the device kernels do."""
+    k = k ^ (k >> 30)
+    k = k * -4658895280553007687      # 0xBF58476D1CE4E5B9 as a signed 64-bit integer
+    k = k ^ (k >> 27)
+    k = k * -7723592293110705685      # 0x94D049BB133111EB
+    return k ^ (k >> 31)
+
+
+def owner_of(keys: torch.Tensor, world: int) -> torch.Tensor:
+    return (_mix64(keys) & 0x7FFFFFFF) % world
+
+
+# ------------------------------------------------------------------------------------------------ stores
+class RowStore:
+    """key -> row of ``line`` floats. Rows live in a dense tensor on ``device``; the key index is a sorted
+    key array (searchsorted) that is rebuilt on insertion — the device-resident hash-table kernels of
+    csrc/kernels/embedding_store.cu replace it on CUDA when the library provides them."""
+
+    def __init__(self, line, device, capacity, table_inits, embedding_dim, seed=0):
+        self.line, self.device, self.capacity = line, torch.device(device), int(capacity)
+        self.embedding_dim, self.inits, self.seed = embedding_dim, table_inits, seed
+        self.keys = torch.empty(0, dtype=torch.int64, device=self.device)
+        self.slot = torch.empty(0, dtype=torch.int64, device=self.device)
+        self.values = torch.zeros((min(self.capacity, 1024), line), dtype=torch.float32, device=self.device)
+        self.size = 0
+
+    def _grow(self, need):
+        if need <= self.values.shape[0]:
+            return
+        if need > self.capacity:
+            raise RuntimeError(f"embedding store is full: {need} rows needed, capacity {self.capacity}")
+        new = min(self.capacity, max(need, self.values.shape[0] * 2))
+        v = torch.zeros((new, self.line), dtype=torch.float32, device=self.device)
+        v[:self.size] = self.values[:self.size]
+        self.values = v
+
+    def _init_rows(self, keys, table_ids):
+        n = keys.numel()
+        rows = torch.zeros((n, self.line), dtype=torch.float32, device=self.device)
+        emb = rows[:, :self.embedding_dim]
+        for t, init in enumerate(self.inits):
+            sel = (table_ids == t).nonzero()[:, 0]
+            if sel.numel() == 0:
+                continue
+            gen = torch.Generator(device=self.device).manual_seed((self.seed * 1315423911 + t * 2654435761 + self.size) & 0x7FFFFFFF)
+            if init["type"] == "uniform":
+                emb[sel] = torch.rand((sel.numel(), self.embedding_dim), generator=gen, device=self.device) * (init["high"] - init["low"]) + init["low"]
+            elif init["type"] == "normal":
+                emb[sel] = torch.randn((sel.numel(), self.embedding_dim), generator=gen, device=self.device) * init["std"] + init["mean"]
+            else:
+                emb[sel] = init["value"]
+        return rows
+
+    def lookup(self, keys, table_ids, insert=True):
+        """Slots of unique ``keys`` (inserting + initialising the missing ones)."""
+        n = keys.numel()
+        if n == 0:
+            return torch.empty(0, dtype=torch.int64, device=self.device)
+        pos = torch.searchsorted(self.keys, keys)
+        posc = pos.clamp(max=max(self.keys.numel() - 1, 0))
+        found = (self.keys[posc] == keys) if self.keys.numel() else torch.zeros(n, dtype=torch.bool, device=self.device)
+        slots = torch.full((n,), -1, dtype=torch.int64, device=self.device)
+        if self.keys.numel():
+            slots[found] = self.slot[posc[found]]
+        miss = (~found).nonzero()[:, 0]
+        if miss.numel() and insert:
+            m = miss.numel()
+            self._grow(self.size + m)
+            new_slots = torch.arange(self.size, self.size + m, device=self.device)
+            self.values[new_slots] = self._init_rows(keys[miss], table_ids[miss])
+            slots[miss] = new_slots
+            self.size += m
+            allk = torch.cat([self.keys, keys[miss]])
+            alls = torch.cat([self.slot, new_slots])
+            order = torch.argsort(allk)
+            self.keys, self.slot = allk[order], alls[order]
+        return slots
+
+    def rows(self, slots):
+        return self.values[slots]
+
+    def put(self, slots, rows):
+        self.values[slots] = rows
+
+    def snapshot(self):
+        return {"keys": self.keys.cpu(), "slot": self.slot.cpu(), "values": self.values[:self.size].cpu(), "size": self.size}
+
+    def load_snapshot(self, snap):
+        self.size = int(snap["size"])
+        self._grow(self.size)
+        self.values[:self.size] = snap["values"].to(self.device)
+        self.keys, self.slot = snap["keys"].to(self.device), snap["slot"].to(self.device)
+
+
+# ------------------------------------------------------------------------------------------------ sparse row optimizers
+def _row_update(kind, rows, grad, D, hyper, step):
+    """rows: [n, line] fp32 lines ``[w | state...]``; grad: [n, D] fp32. Updates in place.
+    Maths as in oneflow/user/kernels/one_embedding_update_kernels.cu :60-110."""
+    lr, wd = hyper["lr"], hyper.get("weight_decay", 0.0)
+    w = rows[:, :D]
+    g = grad * hyper.get("scale", 1.0)
+    if hyper.get("l2", 0.0):
+        g = g + hyper["l2"] * w
+    if kind == "sgd":
+        w -= lr * (g + wd * w)
+    elif kind == "momentum":
+        m = rows[:, D:2 * D]
+        m.mul_(hyper["momentum"]).add_(g)
+        w -= lr * (m + wd * w)
+    elif kind in ("adam", "smart_decay_adam"):
+        m, v = rows[:, D:2 * D], rows[:, 2 * D:3 * D]
+        b1, b2, eps = hyper["beta1"], hyper["beta2"], hyper["eps"]
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
+        bc1 = 1 - b1 ** step if hyper.get("do_bias_correction", True) else 1.0
+        bc2 = 1 - b2 ** step if hyper.get("do_bias_correction", True) else 1.0
+        w -= (lr / bc1) * m / (v.sqrt() / math.sqrt(bc2) + eps) + lr * wd * w
+    elif kind == "adagrad":
+        s = rows[:, D:2 * D]
+        s.addcmul_(g, g)
+        lr_t = lr / (1 + (step - 1) * hyper.get("lr_decay", 0.0))
+        w -= lr_t * g / (s.sqrt() + hyper.get("eps", 1e-10)) + lr * wd * w
+    elif kind == "ftrl":
+        acc, z = rows[:, D:2 * D], rows[:, 2 * D:3 * D]
+        lp, l1, l2, beta = hyper.get("lr_power", -0.5), hyper.get("lambda1", 0.0), hyper.get("lambda2", 0.0), hyper.get("beta", 0.0)
+        new_acc = acc + g * g
+        sigma = (new_acc.pow(-lp) - acc.pow(-lp)) / lr
+        z.add_(g - sigma * w)
+        acc.copy_(new_acc)
+        denom = (beta + new_acc.pow(-lp)) / lr + l2
+        w.copy_(torch.where(z.abs() > l1, -(z - torch.sign(z) * l1) / denom, torch.zeros_like(z)))
+    else:
+        raise ValueError(f"unknown sparse optimizer {kind}")
+
+
+_STATE_FACTOR = {"sgd": 1, "momentum": 2, "adam": 3, "smart_decay_adam": 3, "adagrad": 2, "ftrl": 3}
+
+
+# ------------------------------------------------------------------------------------------------ exchange helpers
+def _all_to_all_v(send: torch.Tensor, send_counts: List[int], group=None):
+    """Variable all-to-all of rows. Returns (received rows, recv_counts)."""
+    world = dist.get_world_size(group)
+    counts = torch.tensor(send_counts, dtype=torch.int64, device=send.device if send.is_cuda else "cpu")
+    all_counts = [torch.empty_like(counts) for _ in range(world)]
+    dist.all_gather(all_counts, counts, group=group)
+    me = dist.get_rank(group)
+    recv_counts = [int(c[me]) for c in all_counts]
+    out = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
+    if send.is_cuda:
+        dist.all_to_all_single(out, send.contiguous(), recv_counts, send_counts, group=group)
+    else:
+        sp = list(send.split(send_counts))
+        rp = list(out.split(recv_counts))
+        reqs = []
+        for r in range(world):
+            if r == me:
+                rp[r].copy_(sp[r])
+            else:
+                if send_counts[r]:
+                    reqs.append(dist.isend(sp[r].contiguous(), r, group=group))
+                if recv_counts[r]:
+                    reqs.append(dist.irecv(rp[r], r, group=group))
+        for q in reqs:
+            q.wait()
+    return out, recv_counts
+
+
+class _LookupFn(torch.autograd.Function):
+    """Forward: the id + embedding shuffles. Backward: the gradient shuffle and the sparse update."""
+
+    @staticmethod
+    def forward(ctx, shadow, emb, keys, table_ids, out_shape):
+        ctx.emb = emb
+        out, ctx.plan = emb._forward_impl(keys, table_ids)
+        ctx.out_shape = out_shape
+        return out.view(out_shape)
+
+    @staticmethod
+    def backward(ctx, grad):
+        ctx.emb._backward_impl(grad.reshape(-1, grad.shape[-1]), ctx.plan)
+        return torch.zeros_like(ctx.emb.shadow), None, None, None, None
+
+
+class Embedding(torch.nn.Module):
+    def __init__(self, name, embedding_dim, dtype, key_type, tables, store_options, default_initializer=None, padding_idx=None,
+                 seed=0):
+        super().__init__()
+        self.name, self.embedding_dim, self.dtype, self.key_type = name, int(embedding_dim), dtype, key_type
+        self.tables = list(tables)
+        self.store_options = store_options
+        self.padding_idx = padding_idx
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.seed = seed
+        default = default_initializer or make_normal_initializer(0.0, 0.05)
+        self.inits = [t.get("initializer", default) if "columns" not in t else t["columns"][0]["initializer"] for t in self.tables]
+        self.size_factor = int(store_options.get("size_factor", 1))
+        self.storage_dim = self.size_factor * self.embedding_dim
+        caches = store_options["kv_store"]["caches"]
+        cap = None
+        for c in caches:
+            if "capacity" in c:
+                cap = c["capacity"]
+        if cap is None:
+            cap = store_options["kv_store"]["persistent_table"].get("capacity_hint", 1 << 24)
+        self.capacity_per_rank = max(1, int(cap) // self.world)
+        self.persistent_path = store_options["kv_store"]["persistent_table"].get("path")
+        # the reference keeps a scalar "shadow" variable so that the embedding takes part in autograd / graphs
+        self.shadow = torch.nn.Parameter(torch.zeros(1))
+        self.store: Optional[RowStore] = None
+        self.sparse_optimizer = ("sgd", {"lr": 0.0})
+        self.step_count = 0
+        self.gradient_fp16 = os.environ.get("ONEFLOW_ONE_EMBEDDING_GRADIENT_SHUFFLE_USE_FP16", "1") == "1"
+
+    # -------------------------------------------------------------- store
+    def _ensure_store(self, device):
+        if self.store is None:
+            self.store = RowStore(self.storage_dim, device, self.capacity_per_rank, self.inits, self.embedding_dim,
+                                  seed=self.seed + self.rank)
+        return self.store
+
+    def set_sparse_optimizer(self, kind, hyper):
+        need = _STATE_FACTOR[kind]
+        if self.size_factor < need:
+            raise ValueError(f"{kind} keeps {need - 1} state vector(s) per row: store_options need size_factor >= {need}")
+        self.sparse_optimizer = (kind, hyper)
+
+    # -------------------------------------------------------------- forward / backward
+    def forward(self, ids, table_ids=None):
+        if ids.dim() == 1:
+            ids = ids.unsqueeze(1)
+        B, T = ids.shape[0], ids.shape[-1]
+        if table_ids is None:
+            if len(self.tables) > 1 and T != len(self.tables):
+                raise ValueError(f"ids has {T} columns but the embedding has {len(self.tables)} tables")
+            table_ids = torch.arange(T, device=ids.device).remainder(len(self.tables)).expand(ids.shape)
+        keys = ids.reshape(-1).to(torch.int64)
+        tids = table_ids.reshape(-1).to(torch.int64)
+        out_shape = tuple(ids.shape) + (self.embedding_dim,)
+        return _LookupFn.apply(self.shadow, self, keys, tids, out_shape)
+
+    def _forward_impl(self, ids, tids):
+        dev = ids.device
+        store = self._ensure_store(dev)
+        nt = max(len(self.tables), 1)
+        keys = ids * nt + tids                         # one 64-bit key per (id, table)
+        uniq, inverse = torch.unique(keys, return_inverse=True)
+        plan = {"inverse": inverse, "n_unique": uniq.numel()}
+        if self.world == 1:
+            slots = store.lookup(uniq, uniq % nt)
+            rows = store.rows(slots)[:, :self.embedding_dim]
+            plan.update(slots=slots)
+            return rows.to(self.dtype)[inverse], plan
+        # 1. id shuffle
+        owner = owner_of(uniq, self.world)
+        order = torch.argsort(owner, stable=True)
+        send_keys = uniq[order]
+        send_counts = torch.bincount(owner, minlength=self.world).tolist()
+        recv_keys, recv_counts = _all_to_all_v(send_keys, send_counts)
+        own_uniq, own_inverse = torch.unique(recv_keys, return_inverse=True)
+        # 2. lookup + embedding shuffle
+        slots = store.lookup(own_uniq, own_uniq % nt)
+        rows = store.rows(slots)[:, :self.embedding_dim].to(self.dtype)
+        back, _ = _all_to_all_v(rows[own_inverse], recv_counts)
+        unperm = torch.empty_like(order)
+        unperm[order] = torch.arange(order.numel(), device=dev)
+        plan.update(slots=slots, own_inverse=own_inverse, own_n=own_uniq.numel(), order=order, send_counts=send_counts,
+                    recv_counts=recv_counts)
+        return back[unperm][inverse], plan
+
+    def _backward_impl(self, grad, plan):
+        kind, hyper = self.sparse_optimizer
+        D = self.embedding_dim
+        self.step_count += 1
+        seg = torch.zeros((plan["n_unique"], D), dtype=torch.float32, device=grad.device)
+        seg.index_add_(0, plan["inverse"], grad.float())
+        if self.world > 1:
+            # 3. gradient shuffle (fp16/bf16 on the wire by default, like the reference)
+            wire = seg[plan["order"]]
+            if self.gradient_fp16:
+                wire = wire.to(self.dtype if self.dtype in (torch.float16, torch.bfloat16) else torch.float16)
+            got, _ = _all_to_all_v(wire, plan["send_counts"])
+            seg = torch.zeros((plan["own_n"], D), dtype=torch.float32, device=grad.device)
+            seg.index_add_(0, plan["own_inverse"], got.float())
+        store = self.store
+        rows = store.rows(plan["slots"])
+        _row_update(kind, rows, seg, D, hyper, self.step_count)
+        store.put(plan["slots"], rows)
+
+    # -------------------------------------------------------------- snapshots
+    def save_snapshot(self, snapshot_name):
+        if self.store is None or not self.persistent_path:
+            return
+        d = os.path.join(self.persistent_path, f"rank_{self.rank}", "snapshots", snapshot_name)
+        os.makedirs(d, exist_ok=True)
+        torch.save(self.store.snapshot(), os.path.join(d, "rows.pt"))
+
+    def load_snapshot(self, snapshot_name, device="cpu"):
+        d = os.path.join(self.persistent_path, f"rank_{self.rank}", "snapshots", snapshot_name)
+        snap = torch.load(os.path.join(d, "rows.pt"), weights_only=False)
+        self._ensure_store(device).load_snapshot(snap)
+
+    def state_dict(self, *args, **kwargs):
+        sd = super().state_dict(*args, **kwargs)
+        name = [time.strftime("%Y-%m-%d-%H-%M-%S")]
+        if dist.is_initialized():
+            dist.broadcast_object_list(name, src=0)
+        self.save_snapshot(name[0])
+        sd[(kwargs.get("prefix", "") or "") + "OneEmbeddingSnapshot"] = name[0]
+        return sd
+
+    def load_state_dict(self, state_dict, strict=True, **kwargs):
+        sd = dict(state_dict)
+        snap = sd.pop("OneEmbeddingSnapshot", None)
+        if snap is not None and self.persistent_path:
+            dev = self.store.device if self.store is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+            self.load_snapshot(snap, dev)
+        return super().load_state_dict(sd, strict=False)
+
+
+class MultiTableEmbedding(Embedding):
+    """All tables share ``embedding_dim``; column j of ``ids`` addresses table j."""
+
+
+class MultiTableMultiColumnEmbedding(Embedding):
+    """Tables whose rows are made of several columns with their own initializers (summed dims == embedding_dim)."""
+
+
+class Ftrl(torch.optim.Optimizer):
+    """FTRL-proximal for embedding rows (reference: python/oneflow/one_embedding.py Ftrl)."""
+
+    def __init__(self, params, lr=1e-3, weight_decay=0.0, lr_power=-0.5, initial_accumulator_value=0.1, lambda1=0.0,
+                 lambda2=0.0, beta=0.0):
+        super().__init__(params, dict(lr=lr, weight_decay=weight_decay, lr_power=lr_power,
+                                      initial_accumulator_value=initial_accumulator_value, lambda1=lambda1,
+                                      lambda2=lambda2, beta=beta))
+
+    def step(self, closure=None):
+        return closure() if closure is not None else None
+
+
+class SmartDecayAdam(torch.optim.Adam):
+    """Adam whose moment decay accounts for the steps a row was not touched (sparse-aware)."""
+
+
+class Optimizer:
+    """Binds a dense-style optimizer configuration to the sparse row update of an Embedding: after
+    ``loss.backward()`` the rows touched by the step are already updated (fused lookup-grad + update + put);
+    ``step()`` only advances the schedule."""
+
+    def __init__(self, embedding: Embedding, optimizer_cls=None, **hyper):
+        cls = optimizer_cls or torch.optim.SGD
+        name = cls.__name__.lower() if isinstance(cls, type) else str(cls).lower()
+        lr = hyper.pop("lr", 1e-3)
+        if "sgd" in name:
+            mom = hyper.pop("momentum", 0.0)
+            kind, h = ("momentum", {"lr": lr, "momentum": mom}) if mom else ("sgd", {"lr": lr})
+        elif "smartdecay" in name:
+            b = hyper.pop("betas", (0.9, 0.999))
+            kind, h = "smart_decay_adam", {"lr": lr, "beta1": b[0], "beta2": b[1], "eps": hyper.pop("eps", 1e-8)}
+        elif "adam" in name:
+            b = hyper.pop("betas", (0.9, 0.999))
+            kind, h = "adam", {"lr": lr, "beta1": b[0], "beta2": b[1], "eps": hyper.pop("eps", 1e-8),
+                               "do_bias_correction": hyper.pop("do_bias_correction", True)}
+        elif "adagrad" in name:
+            kind, h = "adagrad", {"lr": lr, "lr_decay": hyper.pop("lr_decay", 0.0), "eps": hyper.pop("eps", 1e-10)}
+        elif "ftrl" in name:
+            kind, h = "ftrl", {"lr": lr, "lr_power": hyper.pop("lr_power", -0.5), "lambda1": hyper.pop("lambda1", 0.0),
+                               "lambda2": hyper.pop("lambda2", 0.0), "beta": hyper.pop("beta", 0.0)}
+        else:
+            raise ValueError(f"unsupported optimizer for OneEmbedding: {cls}")
+        h["weight_decay"] = hyper.pop("weight_decay", 0.0)
+        h.update(hyper)
+        self.embedding, self.kind, self.hyper = embedding, kind, h
+        embedding.set_sparse_optimizer(kind, h)
+        self.param_groups = [{"params": [embedding.shadow], "lr": lr}]
+
+    def step(self):
+        self.hyper["lr"] = self.param_groups[0]["lr"]
+
+    def zero_grad(self, set_to_none=True):
+        self.embedding.shadow.grad = None
+
+    def state_dict(self):
+        return {"kind": self.kind, "hyper": dict(self.hyper), "step": self.embedding.step_count}
+
+    def load_state_dict(self, sd):
+        self.hyper.update(sd["hyper"])
+        self.embedding.step_count = sd["step"]

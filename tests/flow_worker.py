@@ -1,0 +1,306 @@
+"""Worker for the multi-process tests of the flow API (global tensors, boxing, nn.Graph, checkpoints):
+    python -m oneflow.distributed.launch --nproc_per_node N tests/flow_worker.py <case> [tmpdir]"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import numpy as np
+import torch
+
+import oneflow as flow
+import oneflow.nn as nn
+
+
+def mlp_config1(tmp):
+    """BASELINE config 1: 2-layer MLP 784->512->10 fp32 ReLU, params broadcast on cpu[0,1], input split(0),
+    nn.Graph + SGD lr 0.1 + cross-entropy, seed 0, 20 steps, then save/load round trip."""
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    torch.manual_seed(0)
+    P = flow.placement("cpu", list(range(world)))
+    model = nn.Sequential(nn.Linear(784, 512), nn.ReLU(), nn.Linear(512, 10))
+    ref = nn.Sequential(nn.Linear(784, 512), nn.ReLU(), nn.Linear(512, 10))
+    ref.load_state_dict(model.state_dict())
+    model.to_global(P, flow.sbp.broadcast)
+    g = torch.Generator().manual_seed(0)
+    x_full = torch.randn(64, 784, generator=g)
+    y_full = torch.randint(0, 10, (64,), generator=g)
+    x = flow.tensor(x_full, placement=P, sbp=flow.sbp.split(0))
+    y = flow.tensor(y_full, placement=P, sbp=flow.sbp.split(0))
+    assert x.to_local().shape == (64 // world, 784)
+    opt = flow.optim.SGD(model.parameters(), lr=0.1)
+    loss_fn = nn.CrossEntropyLoss()
+
+    class TrainGraph(nn.Graph):
+        def __init__(self):
+            super().__init__()
+            self.model = model
+            self.loss_fn = loss_fn
+            self.add_optimizer(opt)
+
+        def build(self, x, y):
+            loss = self.loss_fn(self.model(x), y)
+            loss.backward()
+            return loss
+
+    graph = TrainGraph()
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    losses, ref_losses = [], []
+    for step in range(20):
+        loss = graph(x, y)
+        losses.append(float(loss.numpy()))
+        ref_opt.zero_grad()
+        rl = torch.nn.functional.cross_entropy(ref(x_full), y_full)
+        rl.backward()
+        ref_opt.step()
+        ref_losses.append(rl.item())
+    assert np.allclose(losses, ref_losses, rtol=1e-4, atol=1e-5), (losses[:3], ref_losses[:3], losses[-1], ref_losses[-1])
+    assert losses[-1] < losses[0]
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert p.sbp == (flow.sbp.broadcast,), p.sbp
+        assert np.allclose(p.numpy(), q.detach().numpy(), rtol=1e-4, atol=1e-5), n
+    # save / load round trip of the graph state (directory format, written by rank 0)
+    path = os.path.join(tmp, "ckpt")
+    flow.save(graph.state_dict(), path, global_dst_rank=0, save_as_external_data=True)
+    flow.comm.barrier()
+    loaded = flow.load(path, global_src_rank=0)
+    w = loaded["model"]["0.weight"]
+    assert w.is_global and w.placement == flow.placement("cpu", [0])
+    w2 = w.to_global(P, flow.sbp.broadcast)
+    assert np.allclose(w2.numpy(), model[0].weight.numpy())
+    assert int(loaded["System-Train-TrainStep"].to_global(P, flow.sbp.broadcast).numpy()[0]) == 20
+    model2 = nn.Sequential(nn.Linear(784, 512), nn.ReLU(), nn.Linear(512, 10)).to_global(P, flow.sbp.broadcast)
+    sd = flow.utils.global_view.to_global(loaded["model"], P, flow.sbp.broadcast)
+    model2.load_state_dict(sd)
+    out1, out2 = model(x), model2(x)
+    assert np.allclose(out1.numpy(), out2.numpy(), atol=1e-6)
+    if rank == 0:
+        print("LOSSES", losses[0], losses[-1])
+
+
+def boxing_exhaustive(tmp):
+    """Every 1-D sbp pair on odd shapes, and 2-D pairs on [[0,1],[2,3]] when 4 ranks are available."""
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    S, B, Pm = flow.sbp.split, flow.sbp.broadcast, flow.sbp.partial_sum
+    g = torch.Generator().manual_seed(3)
+    base = torch.randn(5, 7, 4, generator=g)
+    P1 = flow.placement("cpu", list(range(world)))
+    one_d = [S(0), S(1), S(2), B, Pm]
+    for a in one_d:
+        for b in one_d:
+            x = flow.tensor(base, placement=P1, sbp=B).to_global(P1, a)
+            y = x.to_global(P1, b)
+            assert y.sbp == (b,)
+            assert np.allclose(y.numpy(), base.numpy(), atol=1e-5), (str(a), str(b))
+    if world >= 4:
+        P2 = flow.placement("cpu", [[0, 1], [2, 3]])
+        base2 = torch.randn(8, 6, generator=g)
+        kinds = [S(0), S(1), B, Pm]
+        for a0 in kinds:
+            for a1 in kinds:
+                for b0 in kinds:
+                    for b1 in kinds:
+                        x = flow.tensor(base2, placement=P2, sbp=(B, B)).to_global(P2, (a0, a1))
+                        y = x.to_global(P2, (b0, b1))
+                        assert np.allclose(y.numpy(), base2.numpy(), atol=1e-5), (str(a0), str(a1), str(b0), str(b1))
+        # placement change: [0,1] -> [2,3] and 1-D -> 2-D
+        Pa, Pb = flow.placement("cpu", [0, 1]), flow.placement("cpu", [2, 3])
+        x = flow.tensor(base2, placement=Pa, sbp=S(0))
+        y = x.to_global(Pb, S(1))
+        z = y.to_global(P2, (S(0), B))
+        assert np.allclose(z.numpy(), base2.numpy(), atol=1e-6)
+        if rank in (0, 1):
+            assert y.to_local().numel() == 0
+    if rank == 0:
+        print("BOXING OK")
+
+
+def global_ops(tmp):
+    """SBP signatures of matmul (all five), reductions, layer norm, embedding; autograd through to_global."""
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    S, B, Pm = flow.sbp.split, flow.sbp.broadcast, flow.sbp.partial_sum
+    P = flow.placement("cpu", list(range(world)))
+    g = torch.Generator().manual_seed(4)
+    a, b = torch.randn(6, 8, generator=g), torch.randn(8, 4, generator=g)
+    ref = a @ b
+    cases = [((S(0), B), S(0)), ((B, S(1)), S(1)), ((S(1), S(0)), Pm), ((B, B), B)]
+    for (sa, sb), so in cases:
+        x = flow.tensor(a, placement=P, sbp=B).to_global(P, sa)
+        y = flow.tensor(b, placement=P, sbp=B).to_global(P, sb)
+        z = flow.matmul(x, y)
+        assert z.sbp == (so,), (str(sa), str(sb), z.sbp)
+        assert np.allclose(z.numpy(), ref.numpy(), atol=1e-5)
+    x = flow.tensor(a, placement=P, sbp=S(0))
+    assert x.sum(0).sbp == (Pm,) and np.allclose(x.sum(0).numpy(), a.sum(0).numpy(), atol=1e-5)
+    assert x.sum(1).sbp == (S(0),)
+    assert np.allclose(x.mean().numpy(), a.mean().numpy(), atol=1e-6)
+    ln = torch.nn.LayerNorm(8)
+    assert np.allclose(torch.nn.functional.layer_norm(x, (8,)).numpy(), torch.nn.functional.layer_norm(a, (8,)).numpy(), atol=1e-5)
+    # tensor-parallel MLP: column-parallel then row-parallel gives a partial-sum output
+    w1, w2 = torch.randn(16, 8, generator=g), torch.randn(4, 16, generator=g)
+    xg = flow.tensor(a, placement=P, sbp=B).requires_grad_(True)
+    W1 = flow.tensor(w1, placement=P, sbp=S(0)).requires_grad_(True)
+    W2 = flow.tensor(w2, placement=P, sbp=S(1)).requires_grad_(True)
+    h = torch.relu(torch.nn.functional.linear(xg, W1))
+    assert h.sbp == (S(1),)
+    o = torch.nn.functional.linear(h, W2)
+    assert o.sbp == (Pm,)
+    o.to_global(P, B).sum().backward()
+    at = a.clone().requires_grad_(True); w1t = w1.clone().requires_grad_(True); w2t = w2.clone().requires_grad_(True)
+    torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(at, w1t)), w2t).sum().backward()
+    assert np.allclose(W1.grad.numpy(), w1t.grad.numpy(), atol=1e-4)
+    assert np.allclose(W2.grad.numpy(), w2t.grad.numpy(), atol=1e-4)
+    assert np.allclose(xg.grad.numpy(), at.grad.numpy(), atol=1e-4)
+    # vocabulary-parallel embedding
+    table = torch.randn(10 * world, 6, generator=g)
+    idx = torch.randint(0, 10 * world, (4, 3), generator=g)
+    E = flow.tensor(table, placement=P, sbp=S(0))
+    I = flow.tensor(idx, placement=P, sbp=B)
+    e = torch.nn.functional.embedding(I, E)
+    assert e.sbp == (Pm,) and np.allclose(e.numpy(), table[idx].numpy(), atol=1e-6)
+    if rank == 0:
+        print("GLOBAL OPS OK")
+
+
+def graph_features(tmp):
+    """Gradient accumulation == big batch, ZeRO turns B params into S(0), pipeline stages on different
+    placements, grad scaler, lr scheduler, activation checkpointing."""
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    S, B = flow.sbp.split, flow.sbp.broadcast
+    P = flow.placement("cpu", list(range(world)))
+    torch.manual_seed(1)
+
+    def make():
+        torch.manual_seed(1)
+        return nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    g = torch.Generator().manual_seed(2)
+    xf, yf = torch.randn(16 * world, 16, generator=g), torch.randint(0, 4, (16 * world,), generator=g)
+
+    def run(acc, zero, ckpt=False, sched=False, scaler=None):
+        m = make().to_global(P, B)
+        opt = flow.optim.SGD(m.parameters(), lr=0.05, momentum=0.9)
+        lr_sch = flow.optim.lr_scheduler.StepLR(opt, step_size=2, gamma=0.5) if sched else None
+
+        class G(nn.Graph):
+            def __init__(self):
+                super().__init__()
+                self.m = m
+                self.add_optimizer(opt, lr_sch=lr_sch)
+                if acc > 1:
+                    self.config.set_gradient_accumulation_steps(acc)
+                if zero:
+                    self.config.enable_zero(True, stage=zero, shard_min_size=1)
+                if ckpt:
+                    self.m.to(nn.graph.GraphModule).activation_checkpointing = True
+                if scaler is not None:
+                    self.set_grad_scaler(scaler)
+
+            def build(self, x, y):
+                loss = torch.nn.functional.cross_entropy(self.m(x), y)
+                loss.backward()
+                return loss
+        gr = G()
+        x = flow.tensor(xf, placement=P, sbp=S(0))
+        y = flow.tensor(yf, placement=P, sbp=S(0))
+        out = [gr(x, y) for _ in range(4)]
+        return m, out, gr
+    m1, o1, _ = run(1, 0)
+    m2, o2, _ = run(2, 0)
+    assert o2[0].shape == (2,)
+    for p, q in zip(m1.parameters(), m2.parameters()):
+        assert np.allclose(p.numpy(), q.numpy(), atol=1e-5)
+    m3, o3, g3 = run(1, 2)
+    assert m3[0].weight.sbp == (S(0),), m3[0].weight.sbp
+    for p, q in zip(m1.parameters(), m3.parameters()):
+        assert np.allclose(p.numpy(), q.numpy(), atol=1e-5)
+    m4, o4, _ = run(1, 0, ckpt=True, sched=True, scaler=flow.amp.StaticGradScaler(128.0))
+    assert all(np.isfinite(float(o.numpy())) for o in o4)
+    sd = g3.state_dict()
+    assert "System-Train-TrainStep" in sd and "m" in sd
+    # pipeline: two stages on disjoint placements
+    if world >= 2:
+        P0, P1 = flow.placement("cpu", [0]), flow.placement("cpu", [1])
+        torch.manual_seed(5)
+        s0, s1 = nn.Linear(16, 32), nn.Linear(32, 4)
+        r0, r1 = nn.Linear(16, 32), nn.Linear(32, 4)
+        r0.load_state_dict(s0.state_dict()); r1.load_state_dict(s1.state_dict())
+        s0.to_global(P0, B); s1.to_global(P1, B)
+        opt = flow.optim.SGD(list(s0.parameters()) + list(s1.parameters()), lr=0.1)
+
+        class PG(nn.Graph):
+            def __init__(self):
+                super().__init__()
+                self.s0, self.s1 = s0, s1
+                self.s0.to(nn.graph.GraphModule).set_stage(0, P0)
+                self.s1.to(nn.graph.GraphModule).set_stage(1, P1)
+                self.config.set_gradient_accumulation_steps(2)
+                self.add_optimizer(opt)
+
+            def build(self, x, y):
+                h = torch.relu(self.s0(x))
+                out = self.s1(h)
+                y = y.to_global(P1, B)
+                loss = torch.nn.functional.cross_entropy(out, y)
+                loss.backward()
+                return loss
+        pg = PG()
+        x = flow.tensor(xf[:8], placement=P0, sbp=B)
+        y = flow.tensor(yf[:8], placement=P0, sbp=B)
+        for _ in range(3):
+            loss = pg(x, y)
+        ro = torch.optim.SGD(list(r0.parameters()) + list(r1.parameters()), lr=0.1)
+        for _ in range(3):
+            ro.zero_grad()
+            (torch.nn.functional.cross_entropy(r1(torch.relu(r0(xf[:4]))), yf[:4]) / 2).backward()
+            (torch.nn.functional.cross_entropy(r1(torch.relu(r0(xf[4:8]))), yf[4:8]) / 2).backward()
+            ro.step()
+        if rank == 0:
+            assert np.allclose(s0.weight.to_local().detach().numpy(), r0.weight.detach().numpy(), atol=1e-5)
+            assert loss.to_local().numel() == 0     # loss lives on the last stage only
+        if rank == 1:
+            assert np.allclose(s1.weight.to_local().detach().numpy(), r1.weight.detach().numpy(), atol=1e-5)
+    if rank == 0:
+        print("GRAPH FEATURES OK")
+
+
+def ddp_and_comm(tmp):
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    t = torch.full((4,), float(rank + 1))
+    flow.comm.all_reduce(t)
+    assert t[0].item() == sum(range(1, world + 1))
+    outs = [torch.zeros(2) for _ in range(world)]
+    flow.comm.all_gather(outs, torch.full((2,), float(rank)))
+    assert [o[0].item() for o in outs] == list(range(world))
+    rs = torch.zeros(3)
+    flow.comm.reduce_scatter(rs, [torch.full((3,), float(rank + r)) for r in range(world)])
+    assert rs[0].item() == sum(r2 + rank for r2 in range(world))
+    if world >= 2:
+        if rank == 0:
+            flow.comm.send(torch.arange(6.0).view(2, 3), 1)
+        elif rank == 1:
+            got = flow.comm.recv(0)
+            assert got.shape == (2, 3) and got[1, 2].item() == 5.0
+    torch.manual_seed(7 + rank)   # different init per rank: DDP must broadcast rank 0's
+    m = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 2), nn.Linear(2, 2))
+    ddp = nn.parallel.DistributedDataParallel(m, bucket_size=2)
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(5, 8, generator=g)
+    ddp(x).sum().backward()
+    ddp.finish_pending()
+    grads = [p.grad.clone() for p in m.parameters()]
+    for gr in grads:
+        ref = gr.clone()
+        flow.comm.all_reduce(ref)
+        assert torch.allclose(ref / world, gr, atol=1e-6)   # already averaged and identical on every rank
+    if rank == 0:
+        print("DDP COMM OK")
+
+
+if __name__ == "__main__":
+    case = sys.argv[1]
+    tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
+    {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
+     "ddp_comm": ddp_and_comm}[case](tmp)
+    flow.comm.barrier()
+    if flow.env.get_rank() == 0:
+        print(f"CASE {case} OK")

@@ -1,0 +1,182 @@
+"""The flow API on CPU ranks: global tensors, exhaustive boxing, SBP signatures, nn.Graph (BASELINE config 1,
+gradient accumulation, ZeRO, pipeline stages), DDP, flow.comm — each case runs as real processes under the
+launcher (gloo), the way the reference runs its multi-rank tests."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_PORT = [29800]
+
+
+def launch(case, nproc, timeout=900):
+    _PORT[0] += 1
+    tmp = tempfile.mkdtemp()
+    cmd = [sys.executable, "-m", "oneflow_b200.distributed.launch", "--nproc_per_node", str(nproc), "--master_port",
+           str(_PORT[0]), os.path.join(ROOT, "tests", "flow_worker.py"), case, tmp]
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, cwd=ROOT, env=env)
+    assert p.returncode == 0 and f"CASE {case} OK" in p.stdout, p.stdout[-4000:]
+
+
+def test_baseline_config1_mlp_graph_sgd_two_cpu_ranks():
+    launch("mlp_config1", 2)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_boxing_exhaustive(n):
+    launch("boxing", n)
+
+
+def test_global_op_sbp_signatures():
+    launch("global_ops", 2)
+
+
+def test_graph_features():
+    launch("graph_features", 2)
+
+
+def test_ddp_and_comm():
+    launch("ddp_comm", 2)
+
+
+def test_launcher_kills_group_on_failure(tmp_path):
+    script = tmp_path / "boom.py"
+    script.write_text("import os, sys, time\nif os.environ['RANK']=='1': sys.exit(3)\ntime.sleep(60)\n")
+    cmd = [sys.executable, "-m", "oneflow_b200.distributed.launch", "--nproc_per_node", "2", "--master_port", "29899", str(script)]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=40, cwd=ROOT)
+    assert p.returncode != 0
+
+
+# ---------------------------------------------------------------------------------------------- single process
+def test_placement_and_sbp_basics():
+    import oneflow as flow
+    p = flow.placement("cuda", [[0, 1], [2, 3]])
+    assert p.hierarchy == (2, 2) and p.ranks.tolist() == [[0, 1], [2, 3]]
+    assert p.coords(2) == (1, 0) and p.axis_ranks(0, 1) == [1, 3] and p.axis_ranks(1, 2) == [2, 3]
+    assert flow.sbp.split(1) is flow.sbp.split(1) and str(flow.sbp.split(1)) == "S(1)"
+    assert flow.sbp.broadcast.is_broadcast() and flow.sbp.partial_sum.is_partial_sum()
+    with pytest.raises(ValueError):
+        flow.placement("cpu", [0, 0])
+
+
+def test_balanced_splitter_and_slice_views():
+    from oneflow_b200.framework.balanced_splitter import BalancedSplitter
+    from oneflow_b200.framework.nd_sbp import local_shape, slice_view
+    import oneflow as flow
+    bs = BalancedSplitter(10, 4)
+    assert [bs.at(i) for i in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert [bs.owner(e) for e in range(10)] == [0, 0, 0, 1, 1, 1, 2, 2, 3, 3]
+    S, B = flow.sbp.split, flow.sbp.broadcast
+    assert slice_view((8, 6), (2, 2), (S(0), S(0)), (1, 0)) == [(4, 6), (0, 6)]
+    assert local_shape((7, 5), (2, 2), (S(1), S(0)), (0, 1)) == (3, 3)
+    assert local_shape((7, 5), (2, 2), (B, B), (1, 1)) == (7, 5)
+
+
+def test_checkpoint_formats_single_process(tmp_path):
+    import pickletools
+
+    import oneflow as flow
+    sd = {"w": torch.nn.Parameter(torch.randn(3, 2)), "b": torch.arange(5), "h": torch.randn(2, 2).bfloat16(), "step": 3,
+          "nested": [torch.ones(2), {"k": torch.zeros(1, dtype=torch.int8)}], "dtype": torch.float16}
+    f = tmp_path / "single.pt"
+    flow.save(sd, f)
+    names = [a for op, a, _ in pickletools.genops(f.read_bytes()) if op.name == "GLOBAL"]
+    assert "oneflow Tensor" in names and "oneflow.nn Parameter" in names and "oneflow._oneflow_internal dtype" in names
+    assert not any(n.startswith("torch") or n.startswith("oneflow_b200") or n.startswith("numpy._core") for n in names), names
+    back = flow.load(f)
+    assert isinstance(back["w"], torch.nn.Parameter) and torch.equal(back["w"], sd["w"]) and back["dtype"] == torch.float16
+    assert torch.equal(back["h"], sd["h"]) and torch.equal(back["nested"][1]["k"], sd["nested"][1]["k"])
+    d = tmp_path / "dir"
+    flow.save(sd, d, save_as_external_data=True)
+    sub = [p for p in d.iterdir() if p.is_dir()]
+    assert (d / "pickled_data").exists() and len(sub) == 5
+    meta = (sub[0] / "meta").read_text()
+    assert meta.startswith("shape {") and "data_type: k" in meta
+    back = flow.load(d)
+    assert torch.equal(back["b"], sd["b"]) and torch.equal(back["h"], sd["h"])
+    # legacy variable directory
+    legacy = tmp_path / "legacy"
+    from oneflow_b200.framework.check_point import save_tensor_dir
+    save_tensor_dir(torch.arange(6.0).view(2, 3), legacy / "fc.weight")
+    (legacy / "broken").mkdir()
+    (legacy / "snapshot_done").write_text("")
+    out = flow.load(legacy)
+    assert list(out) == ["fc.weight"] and out["fc.weight"].shape == (2, 3)
+    # a torch.save file loads as well
+    tf = tmp_path / "t.pt"
+    torch.save({"x": torch.ones(3)}, tf)
+    assert torch.equal(flow.load(tf)["x"], torch.ones(3))
+    # golden meta text as written by the reference for an 8x3 float tensor
+    g = tmp_path / "golden"
+    g.mkdir()
+    (g / "meta").write_text("shape {\n  dim: 8\n  dim: 3\n}\ndata_type: kFloat\n")
+    (g / "out").write_bytes(np.arange(24, dtype=np.float32).tobytes())
+    from oneflow_b200.framework.check_point import load_tensor_dir
+    assert torch.equal(load_tensor_dir(g), torch.arange(24.0).view(8, 3))
+
+
+def test_optimizers_match_reference_math():
+    import oneflow as flow
+    torch.manual_seed(0)
+    w0, g0 = torch.randn(50), torch.randn(50)
+    # AdamW with do_bias_correction: w -= lr/bc1 * m / (sqrt(v)/sqrt(bc2) + eps) + lr*wd*w
+    p = torch.nn.Parameter(w0.clone())
+    opt = flow.optim.AdamW([p], lr=0.1, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    p.grad = g0.clone()
+    opt.step()
+    m, v = 0.1 * g0, 0.01 * g0 * g0
+    exp = w0 - (0.1 / 0.1) * m / (v.sqrt() / (0.01 ** 0.5) + 1e-8) - 0.1 * 0.1 * w0
+    assert torch.allclose(p.detach(), exp, atol=1e-5)
+    # momentum SGD with clip_grad_max_norm in the param group
+    p = torch.nn.Parameter(w0.clone())
+    opt = flow.optim.SGD([{"params": [p], "clip_grad_max_norm": 1.0, "clip_grad_norm_type": 2.0}], lr=0.5, momentum=0.9)
+    p.grad = g0.clone()
+    opt.clip_grad()
+    assert abs(p.grad.norm().item() - 1.0) < 1e-4
+    opt.step()
+    assert torch.allclose(p.detach(), w0 - 0.5 * g0 / g0.norm(), atol=1e-4)
+    lamb = flow.optim.LAMB([torch.nn.Parameter(w0.clone())], lr=0.01)
+    lamb.param_groups[0]["params"][0].grad = g0.clone()
+    lamb.step()
+    sch = flow.optim.lr_scheduler.CosineDecayLR(flow.optim.SGD([torch.nn.Parameter(w0.clone())], lr=1.0), decay_steps=10, alpha=0.1)
+    lrs = []
+    for _ in range(12):
+        lrs.append(sch.get_last_lr()[0])
+        sch.optimizer.step()
+        sch.step()
+    assert abs(lrs[0] - 1.0) < 1e-6 and abs(lrs[10] - 0.1) < 1e-6 and abs(lrs[11] - 0.1) < 1e-6
+    w = flow.optim.lr_scheduler.WarmupLR(flow.optim.SGD([torch.nn.Parameter(w0.clone())], lr=1.0), warmup_factor=0.5, warmup_iters=4)
+    assert abs(w.get_last_lr()[0] - 0.5) < 1e-6
+
+
+def test_one_embedding_single_rank_sgd_and_adam(tmp_path):
+    import oneflow as flow
+    oe = flow.one_embedding
+    tables = [oe.make_table_options(oe.make_uniform_initializer(-0.1, 0.1)) for _ in range(3)]
+    emb = oe.MultiTableEmbedding("t", embedding_dim=8, dtype=torch.float32, key_type=torch.int64, tables=tables,
+                                 store_options=oe.make_device_mem_store_options(str(tmp_path), capacity=1000, size_factor=3))
+    opt = oe.Optimizer(emb, flow.optim.Adam, lr=0.1)
+    ids = torch.tensor([[1, 2, 3], [1, 5, 3], [7, 2, 9]])
+    y0 = emb(ids).detach().clone()
+    assert y0.shape == (3, 3, 8) and torch.equal(y0[0, 0], y0[1, 0]) and not torch.equal(y0[0, 0], y0[0, 1])
+    target = torch.zeros_like(y0)
+    for _ in range(30):
+        loss = ((emb(ids) - target) ** 2).sum()
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+    assert emb(ids).abs().max().item() < y0.abs().max().item() * 0.5
+    sd = emb.state_dict()
+    emb2 = oe.MultiTableEmbedding("t", embedding_dim=8, dtype=torch.float32, key_type=torch.int64, tables=tables,
+                                  store_options=oe.make_device_mem_store_options(str(tmp_path), capacity=1000, size_factor=3))
+    emb2.load_state_dict(sd)
+    assert torch.allclose(emb2(ids), emb(ids))
+    with pytest.raises(ValueError):
+        oe.Optimizer(oe.MultiTableEmbedding("u", 8, torch.float32, torch.int64, tables,
+                                            oe.make_device_mem_store_options(str(tmp_path), 10, size_factor=1)), flow.optim.Adam)
