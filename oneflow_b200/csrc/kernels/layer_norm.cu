@@ -214,20 +214,31 @@ layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   }
 }
 
-// Folds partial[nparts, cols] into out[cols] (fp32, optionally accumulating) - one thread per column.
-__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb,
-                                     float* __restrict__ outa, float* __restrict__ outb, int nparts, int cols,
-                                     int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// Folds partial[nparts, cols] into out[cols] (fp32, optionally accumulating). Block = 32 columns x 8 part
+// lanes: the 8 lanes of a column stride over the parts, then a shared-memory step adds them.
+__global__ void __launch_bounds__(256)
+fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ outa,
+                     float* __restrict__ outb, int nparts, int cols, int accumulate) {
+  __shared__ float sa[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    a += pa[static_cast<long long>(p) * cols + c];
-    b += pb[static_cast<long long>(p) * cols + c];
+  if (c < cols) {
+    for (int p = ty; p < nparts; p += 8) {
+      a += pa[static_cast<long long>(p) * cols + c];
+      b += pb[static_cast<long long>(p) * cols + c];
+    }
   }
-  if (accumulate) { a += outa[c]; b += outb[c]; }
-  outa[c] = a;
-  outb[c] = b;
+  sa[ty][tx] = a;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { a += sa[k][tx]; b += sb[k][tx]; }
+    if (accumulate) { a += outa[c]; b += outb[c]; }
+    outa[c] = a;
+    outb[c] = b;
+  }
 }
 
 static int ln_block_threads(int cols, int& nv) {
@@ -292,7 +303,7 @@ OFB_API int ofb_layer_norm_bwd(const void* dy, const void* x, const void* gamma,
   }
   OFB_CUDA_OK(cudaGetLastError());
   if (dgamma) {
-    fold_partials_kernel<<<(cols + 127) / 128, 128, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
+    fold_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
     OFB_CUDA_OK(cudaGetLastError());
   }
   return 0;
@@ -378,7 +389,7 @@ OFB_API int ofb_layer_norm_bwd_noalloc(const void* dy, const void* x, const void
   }
   OFB_CUDA_OK(cudaGetLastError());
   if (dgamma) {
-    fold_partials_kernel<<<(cols + 127) / 128, 128, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
+    fold_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(pg, pb, dgamma, dbeta, grid, cols, accumulate_param_grads);
     OFB_CUDA_OK(cudaGetLastError());
   }
   return 0;
