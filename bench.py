@@ -149,14 +149,27 @@ def main():
     if tp == 0 or pp == 0:
         # BASELINE config: TP=4 x PP=2 at 8 GPUs; smaller degrees below that.
         tp, pp = {1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (4, 2)}.get(world, (world, 1))
+    is_bert = args.workload == "bert-large"
+    if is_bert:
+        # BASELINE config: 2-D placement DP=2 x TP=4 at 8 GPUs, micro-batch 32 per data-parallel rank
+        tp, pp = (args.tp or min(world, 4)), 1
+        args.micro_batch = 32
     dp = world // (tp * pp)
+    if is_bert:
+        args.global_batch = args.micro_batch * dp
     n_micro = args.global_batch // (args.micro_batch * dp)
+    stage_kw = {}
+    if is_bert:
+        stage_kw["stage_cls"] = bert_mod.BertStage
     trainer = build_gpt_trainer(cfg, tp=tp, pp=pp, dp=dp, micro_batch=args.micro_batch, n_micro=n_micro,
-                                device=device, lr=1e-4, zero_stage=1)
+                                device=device, lr=1e-4, zero_stage=1, **stage_kw)
     local_batch = args.micro_batch * n_micro
     seq = cfg.seq_len
     gen = torch.Generator().manual_seed(1234 + (rank // (tp * pp)))
-    host_tokens = torch.randint(0, cfg.vocab_size, (local_batch, seq + 1), generator=gen).pin_memory()
+    if is_bert:
+        host_tokens = bert_mod.make_batch(cfg, local_batch, generator=gen).pin_memory()
+    else:
+        host_tokens = torch.randint(0, cfg.vocab_size, (local_batch, seq + 1), generator=gen).pin_memory()
     dev_tokens = host_tokens.to(device, non_blocking=True)
 
     def barrier():
@@ -218,7 +231,8 @@ def main():
             "metric": "gpt_6.7b_train_tokens_per_s" if args.workload == "gpt-6.7b" else f"{args.workload}_train_tokens_per_s",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens (uniform in vocab), random-init weights",
+            "vs_baseline": None, "dtype": "bf16", "data": ("synthetic tokens (uniform in vocab), 76 masked positions per sequence, Bernoulli(0.5) NSP labels, random-init weights"
+                                      if is_bert else "synthetic tokens (uniform in vocab), random-init weights"),
             "config": {"model": args.workload, "layers": cfg.layers, "hidden": cfg.hidden, "heads": cfg.heads,
                        "ffn": cfg.ffn, "vocab": cfg.vocab_size, "global_batch": args.global_batch, "seq_len": seq,
                        "micro_batch": args.micro_batch, "grad_accum_steps": n_micro,

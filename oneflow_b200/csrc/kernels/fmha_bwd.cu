@@ -7,7 +7,7 @@
 //     dP  = dO_i V_j^T           (K-major  x K-major)       -> TMEM
 //     dV += P^T dO_i             (MN-major x MN-major)      -> TMEM accumulator
 //     dK += dS^T Q_i             (MN-major x MN-major)      -> TMEM accumulator
-//     dQ_i partial = dS K_j      (K-major  x MN-major)      -> TMEM, then fp32 red.add to HBM
+//     dQ_i partial = dS K_j      (K-major  x MN-major)      -> TMEM, then staged in shared memory and added to HBM by TMA (cp.reduce.async.bulk)
 // The 128 compute threads own one query row each: they rebuild P from S and the saved
 // log-sum-exp, form dS = P * (dP - delta) * scale, and publish P / dS (bf16) through one
 // shared buffer in the 128-byte swizzled layout that serves both as K-major and MN-major
@@ -45,14 +45,33 @@ struct FmhaBwdCfg {
   static constexpr int SMEM_BYTES = 6 * T_BYTES + PDS_BYTES + 256 + 1024;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ float fast_exp2_b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// fp32 add-reduction of a shared-memory tile into global memory through TMA (one bulk operation instead of
+// thousands of per-thread red instructions; L2 sees whole 128-byte lines).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* smem_src, int x, int y, int z, int w) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+// Rendezvous of the 128 compute threads on an mbarrier (bounded, unlike bar.sync: a thread that gave up on
+// another wait can never leave its peers stuck here).
+__device__ __forceinline__ bool compute_sync(uint64_t* bar, uint32_t& parity, volatile int* abort_flag) {
+  mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  parity ^= 1;
+  return ok;
 }
 
 template <int D>
 __global__ void __launch_bounds__(192, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, FmhaBwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmdQ, FmhaBwdParams p) {
   using Cfg = FmhaBwdCfg<D>;
   constexpr int DCH = D / 64;
   constexpr int CH_BYTES = 128 * 128;
@@ -81,7 +100,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* dq_full = bars + 14;
   uint64_t* dq_drained = bars + 15; // count 128
   uint64_t* all_done = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* stg_bar = bars + 17;    // count 128: rendezvous of the compute threads around the dQ staging area
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,6 +130,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(dq_full, 1);
     mbar_init(dq_drained, 128);
     mbar_init(all_done, 1);
+    mbar_init(stg_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -220,6 +241,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* pds_row = sPdS + r * 128;
     const float kLog2e = 1.4426950408889634f;
     bool ok = true;
+    uint32_t stg_parity = 0;
     for (int t = 0; t < n_iter; ++t) {
       const uint32_t ph1 = t & 1;
       const int q0 = (i_start + t) * 128;
@@ -235,20 +257,27 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t pk[64];  // P, later dS, as packed bf16 pairs for this row
       if (!mbar_wait(s_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
+      // the previous pair's dQ reduction must have finished reading the staging area (= this P buffer)
+      if (t > 0) {
+        if (r == 0) tma_store_wait_read<0>();
+        if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
+      }
+      {
+        uint32_t v[4][32];
         __syncwarp();
-        tmem_ld_32x32(tS + lane_addr + c * 32, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_addr + c * 32, v[c]);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2e - lse2);
-          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2e - lse2);
-          if (dead_row || (need_mask && k0 + c * 32 + i > col_max)) p0 = 0.f;
-          if (dead_row || (need_mask && k0 + c * 32 + i + 1 > col_max)) p1 = 0.f;
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = fast_exp2_b(__uint_as_float(v[c][i]) * p.scale_log2e - lse2);
+            float p1 = fast_exp2_b(__uint_as_float(v[c][i + 1]) * p.scale_log2e - lse2);
+            if (dead_row || (need_mask && k0 + c * 32 + i > col_max)) p0 = 0.f;
+            if (dead_row || (need_mask && k0 + c * 32 + i + 1 > col_max)) p1 = 0.f;
+            pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          }
       }
       // Publish P. The buffer is free: the MMAs that read dS of the previous iteration were
       // covered by the dq_full wait below in that iteration.
@@ -265,18 +294,22 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(dp_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t v[2][32];
         __syncwarp();
-        tmem_ld_32x32(tdP + lane_addr + c * 32, v);
+        tmem_ld_32x32(tdP + lane_addr + hh * 64, v[0]);
+        tmem_ld_32x32(tdP + lane_addr + hh * 64 + 32, v[1]);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float2 pp = unpack_bf16x2(pk[c * 16 + (i >> 1)]);
-          float d0 = pp.x * (__uint_as_float(v[i]) - delta) * p.scale;
-          float d1 = pp.y * (__uint_as_float(v[i + 1]) - delta) * p.scale;
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(d0, d1);
-        }
+        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int c = hh * 2 + cc;
+            float2 pp = unpack_bf16x2(pk[c * 16 + (i >> 1)]);
+            float d0 = pp.x * (__uint_as_float(v[cc][i]) - delta) * p.scale;
+            float d1 = pp.y * (__uint_as_float(v[cc][i + 1]) - delta) * p.scale;
+            pk[c * 16 + (i >> 1)] = pack_bf16x2(d0, d1);
+          }
       }
       tc_fence_before();
       if (!mbar_wait(dv_done, ph1, abort_flag)) { ok = false; break; }
@@ -289,26 +322,44 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
-      // Drain the dQ partial of this pair into the fp32 accumulator.
+      // Drain the dQ partial of this pair: TMEM -> swizzled fp32 staging in shared memory (the P/dS buffer,
+      // idle until the next pair's P) -> one TMA add-reduction per 32-column slab into the fp32 accumulator.
       if (!mbar_wait(dq_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
+      for (int hh = 0; hh < D / 64; ++hh) {
+        if (hh > 0) {
+          if (r == 0) tma_store_wait_read<0>();
+          if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
+        }
+        uint32_t v[2][32];
         __syncwarp();
-        tmem_ld_32x32(tdP + lane_addr + c * 32, v);
+        tmem_ld_32x32(tdP + lane_addr + hh * 64, v[0]);
+        tmem_ld_32x32(tdP + lane_addr + hh * 64 + 32, v[1]);
         tmem_wait_ld();
-        if (row_ok) {
+        if (hh == D / 64 - 1) {
+          // every column of the dQ partial has left TMEM: the dP region may be overwritten
+          tc_fence_before();
+          mbar_arrive(dq_drained);
+        }
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(dq_row + c * 32 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                       __uint_as_float(v[i + 3]));
+        for (int cc = 0; cc < 2; ++cc) {
+          uint8_t* st = sPdS + cc * (128 * 128) + r * 128;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<uint4*>(st + ((g ^ (r & 7)) << 4)) = make_uint4(v[cc][4 * g], v[cc][4 * g + 1], v[cc][4 * g + 2], v[cc][4 * g + 3]);
+        }
+        fence_proxy_async_smem();
+        if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
+        if (r == 0) {
+          tma_reduce_add_4d(&tmdQ, sPdS, hh * 64, h, q0, b);
+          tma_reduce_add_4d(&tmdQ, sPdS + 128 * 128, hh * 64 + 32, h, q0, b);
+          tma_store_commit();
         }
       }
-      tc_fence_before();
-      mbar_arrive(dq_drained);
+      if (!ok) break;
     }
+    if (r == 0) tma_store_wait<0>();
     // dK, dV of this key tile: TMEM lane = key row
     if (ok) ok = mbar_wait(all_done, 0, abort_flag);
     if (ok) {
@@ -404,7 +455,7 @@ __global__ void fmha_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16
 
 template <int D>
 static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                           const FmhaBwdParams& p, cudaStream_t stream) {
+                           const CUtensorMap& tdq, const FmhaBwdParams& p, cudaStream_t stream) {
   using Cfg = FmhaBwdCfg<D>;
   auto kern = fmha_bwd_kernel<D>;
   static bool configured = false;
@@ -413,7 +464,7 @@ static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   dim3 grid((p.S + 127) / 128, p.H, p.B);
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -459,7 +510,19 @@ OFB_API int ofb_fmha_bwd(const void* q, const void* k, const void* v, long long 
   p.dkv_row_stride = dqkv_row_stride; p.kv_len = kv_len;
   p.B = B; p.H = H; p.S = S; p.D = D; p.causal = causal; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
   p.status = device_status_ptr();
-  int rc = D == 64 ? launch_fmha_bwd<64>(tq, tk, tv, tdo, p, s) : launch_fmha_bwd<128>(tq, tk, tv, tdo, p, s);
+  CUtensorMap tdq;
+  {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail("cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)H * D * 4, (cuuint64_t)S * H * D * 4};
+    cuuint32_t box[4] = {32, 1, 128, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("fmha_bwd: cuTensorMapEncodeTiled(dq) failed with code " + std::to_string((int)r));
+  }
+  int rc = D == 64 ? launch_fmha_bwd<64>(tq, tk, tv, tdo, tdq, p, s) : launch_fmha_bwd<128>(tq, tk, tv, tdo, tdq, p, s);
   if (rc) return rc;
   {
     const long long rows = static_cast<long long>(B) * S;

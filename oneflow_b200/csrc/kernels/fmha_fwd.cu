@@ -4,12 +4,13 @@
 // One CTA owns a 128-row query tile of one (batch, head). Roles:
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles through a 2-stage ring
 //   warp 1      tcgen05 issuer: S_j = Q K_j^T and O_j = P_j V_j, accumulators in TMEM
-//   warps 2..5  softmax: thread t owns query row t; it reads its S row with tcgen05.ld
-//               (no shuffles needed), keeps the running max / sum, writes P_j (bf16) to shared
-//               memory in the 128-byte-swizzled K-major layout the second MMA consumes, and
-//               folds O_j into its register accumulator with the usual rescaling.
-// S and O_j are double-buffered in TMEM (2 x 128 + 2 x D columns) so the tensor core works on
-// tile j+1 while the softmax warps are busy with tile j.
+//   warps 2..5  softmax: thread t owns query row t; it reads its whole S row with tcgen05.ld
+//               (no shuffles needed), keeps the running max / sum and writes P_j (bf16) to shared
+//               memory in the 128-byte-swizzled K-major layout the second MMA consumes.
+// O accumulates in TMEM across all key tiles (the PV product runs with accumulate on); the exponent
+// reference trails the true running maximum by up to 2^8, so O is only rescaled in TMEM
+// (tcgen05.ld / st) on the rare tiles where a row maximum jumps. S is double-buffered in TMEM so the
+// tensor core computes tile j+1 while the softmax warps work on tile j.
 //
 // Reference counterparts: oneflow/user/kernels/scaled_dot_product_attention_kernel.cu (flash
 // attention library call), fused_attention_kernels.cu :710 (CUTLASS fMHA, no sm_100 path) and the
@@ -39,6 +40,13 @@ struct FmhaFwdCfg {
   static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 256 + 1024;
 };
 
+// ex2.approx: one MUFU op (inputs here are <= ~8, -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(192, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -62,7 +70,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* kv_empty = bars + 5;   // [2]
   uint64_t* s_full = bars + 7;     // [2]
   uint64_t* p_full = bars + 9;     // [2]
-  uint64_t* o_full = bars + 11;    // [2]
+  uint64_t* pv_done = bars + 11;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -86,7 +94,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 128);
-      mbar_init(&o_full[s], 1);
+      mbar_init(&pv_done[s], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -103,7 +111,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;            // S[0], S[1] at +0, +128
-  const uint32_t tO = tmem_base + 256;      // O[0], O[1] at +0, +D
+  const uint32_t tO = tmem_base + 256;      // running O accumulator, D columns
 
   if (warp == 0) {
     if (elect_one() && n_kv > 0) {
@@ -156,9 +164,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(p_base + (kk >> 2) * CH_BYTES + (kk & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(v_base + kk * 2048, CH_BYTES, 1024);
-          umma_bf16_ss(tO + s * D, da, db, IDESC_O, kk != 0 ? 1u : 0u);
+          umma_bf16_ss(tO, da, db, IDESC_O, (j | kk) != 0 ? 1u : 0u);   // O accumulates in TMEM over all key tiles
         }
-        umma_commit(&o_full[s]);
+        umma_commit(&pv_done[s]);
         umma_commit(&kv_empty[s]);
       }
     }
@@ -168,10 +176,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
     const int row_g = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    // m_ref is the exponent reference actually used for P and l; it trails the true running maximum by at
+    // most kLazy (log2 units) so that the TMEM-resident O only has to be rescaled when the maximum jumps.
+    constexpr float kLazy = 8.0f;
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
@@ -179,48 +187,63 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&s_full[s], ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int col_base = j * BN;
-      // A tile needs element-wise masking if it crosses the causal diagonal or the key-length limit.
       const bool need_mask = (p.causal && col_base + BN - 1 > q0) || (col_base + BN > kv_limit);
       const int col_max = p.causal ? min(row_g, kv_limit - 1) : kv_limit - 1;  // last visible column
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, v);
-        tmem_wait_ld();
+      uint32_t sv[4][32];
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, sv[c]);
+      tmem_wait_ld();
+      // eight independent max chains: a single warp per scheduler cannot hide a 128-long dependent chain
+      float mxs[8] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = __uint_as_float(v[i]);
+          float e = __uint_as_float(sv[c][i]) * p.scale_log2e;
           if (need_mask && col_base + c * 32 + i > col_max) e = -INFINITY;
-          mx = fmaxf(mx, e);
+          sv[c][i] = __float_as_uint(e);
+          mxs[i & 7] = fmaxf(mxs[i & 7], e);
         }
+      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      // Rescale O (and l) only when some row of the warp moved its maximum by more than kLazy.
+      const bool jump = mx > m_ref + kLazy;
+      if (__any_sync(0xffffffffu, jump)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);  // m_new is finite here or equals m_ref
+        if (j > 0) {
+          if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(tO + lane_addr + c * 16, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(tO + lane_addr + c * 16, o);
+          }
+          tmem_wait_st();
+        }
+        l_run *= alpha;
+        m_ref = m_new;
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2e);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);  // m_run = -inf gives 0
-      float rowsum = 0.f;
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      if (j >= 2) {  // the P buffer of parity s was last read by the PV product of tile j-2
+        if (!mbar_wait(&pv_done[s], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+      }
+      float rs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       uint8_t* p_row = sP + s * Cfg::P_BYTES + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, v);
-        tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0 = __uint_as_float(v[i]) * p.scale_log2e - m_use;
-          float e1 = __uint_as_float(v[i + 1]) * p.scale_log2e - m_use;
-          float p0 = exp2f(e0), p1 = exp2f(e1);
-          if (need_mask) {
-            if (col_base + c * 32 + i > col_max) p0 = 0.f;
-            if (col_base + c * 32 + i + 1 > col_max) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
+          const float p0 = fast_exp2(__uint_as_float(sv[c][i]) - m_use);       // masked entries are -inf -> 0
+          const float p1 = fast_exp2(__uint_as_float(sv[c][i + 1]) - m_use);
+          rs[(i >> 1) & 7] += p0 + p1;
           packed[i >> 1] = pack_bf16x2(p0, p1);
         }
-        // 32 columns = four 16-byte groups inside the 64-column chunk (c >> 1)
         uint8_t* chunk = p_row + (c >> 1) * CH_BYTES;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -229,30 +252,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
       }
-      l_run = l_run * alpha + rowsum;
-      m_run = m_new;
+      l_run += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full[s]);
-      if (j > 0) {
-        const int so = (j - 1) & 1;
-        if (!mbar_wait(&o_full[so], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          __syncwarp();
-          tmem_ld_32x32(tO + lane_addr + so * D + c * 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-        }
-      }
-      alpha_prev = alpha;
     }
     if (ok) {
       const int so = (n_kv - 1) & 1;
-      ok = mbar_wait(&o_full[so], ((n_kv - 1) >> 1) & 1, abort_flag);
+      ok = mbar_wait(&pv_done[so], ((n_kv - 1) >> 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -261,15 +268,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
           __syncwarp();
-          tmem_ld_32x32(tO + lane_addr + so * D + c * 32, v);
+          tmem_ld_32x32(tO + lane_addr + c * 32, v);
           tmem_wait_ld();
           if (row_g < p.S) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float f[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                f[i] = (o_acc[c * 32 + g * 8 + i] * alpha_prev + __uint_as_float(v[g * 8 + i])) * inv;
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv;
               *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
                   make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
                              pack_bf16x2(f[6], f[7]));
@@ -278,7 +284,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         if (row_g < p.S && p.lse)
           p.lse[(static_cast<long long>(b) * p.H + h) * p.S + row_g] =
-              l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+              l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       }
     }
   } else {

@@ -1,9 +1,15 @@
 // C entry points of the tcgen05 GEMM (see gemm_tcgen05.cuh for the kernel).
+#include <cstdlib>
+
 #include "../common/host_utils.h"
 #include "gemm_tcgen05.cuh"
+#include "gemm_2cta.cuh"
 #include "ofb_kernels.h"
 
 namespace ofb {
+
+// Whether shapes that fill the machine use the two-SM kernel unless told otherwise.
+constexpr bool kDefault2Cta = true;
 
 template <int BN, int A_MN, int B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shp, const GemmEpilogue& ep,
@@ -29,6 +35,39 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return 0;
 }
 
+template <int A_MN, int B_MN>
+static int launch_gemm_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shp, const GemmEpilogue& ep,
+                            int* status, int max_ctas, cudaStream_t stream) {
+  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    OFB_CUDA_OK(cudaGetDevice(&dev));
+    OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int tiles = ((shp.M + 255) / 256) * ((shp.N + 255) / 256);
+  int grid = 2 * tiles < sm_count ? 2 * tiles : (sm_count & ~1);
+  if (max_ctas > 1 && grid > (max_ctas & ~1)) grid = max_ctas & ~1;
+  kern<<<grid, 192, Gemm2Cfg::SMEM_BYTES, stream>>>(tmA, tmB, shp, ep, status);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+static int gemm_mode_2cta() {
+  // OFB_GEMM_2CTA=0 turns the two-SM kernel off, =1 forces it for every shape it supports.
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = std::getenv("OFB_GEMM_2CTA");
+    mode = e ? std::atoi(e) : -1;
+  }
+  return mode;
+}
+
 int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("gemm: empty problem");
   if (a->N % 8 != 0) return fail("gemm: N must be a multiple of 8");
@@ -36,6 +75,32 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
   // K-major: dims {K, rows}, row stride ld*2 bytes. MN-major: dims {rows, K}.
   CUtensorMap tmA, tmB;
   int bn = a->bn;
+  const int mode2 = gemm_mode_2cta();
+  bool two = bn == 512 || (mode2 == 1 && bn == 0);
+  if (mode2 == -1 && bn == 0) {
+    // default: the two-SM kernel for problems that fill the machine with 256 x 256 tiles
+    const long long tiles2 = (long long)((a->M + 255) / 256) * ((a->N + 255) / 256);
+    two = kDefault2Cta && tiles2 >= 74 && a->N >= 256 && a->M >= 256;
+  }
+  if (mode2 == 0) two = bn == 512;
+  if (two) {
+    if (!a_mn) {
+      if (get_tensor_map(&tmA, a->A, 2, 2, a->K, a->M, 0, (uint64_t)a->lda * 2, 0, 64, 128, 0, 3)) return -1;
+    } else {
+      if (get_tensor_map(&tmA, a->A, 2, 2, a->M, a->K, 0, (uint64_t)a->lda * 2, 0, 64, 64, 0, 3)) return -1;
+    }
+    if (!b_mn) {
+      if (get_tensor_map(&tmB, a->B, 2, 2, a->K, a->N, 0, (uint64_t)a->ldb * 2, 0, 64, 128, 0, 3)) return -1;
+    } else {
+      if (get_tensor_map(&tmB, a->B, 2, 2, a->N, a->K, 0, (uint64_t)a->ldb * 2, 0, 64, 64, 0, 3)) return -1;
+    }
+    GemmShape shp2{a->M, a->N, a->K};
+    int* st2 = device_status_ptr();
+    if (!a_mn && !b_mn) return launch_gemm_2cta<0, 0>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
+    if (!a_mn && b_mn) return launch_gemm_2cta<0, 1>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
+    if (a_mn && !b_mn) return launch_gemm_2cta<1, 0>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
+    return launch_gemm_2cta<1, 1>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
+  }
   if (bn != 128 && bn != 256) {
     // Small problems: prefer more, smaller tiles so that all SMs get work.
     long long tiles256 = (long long)((a->M + 127) / 128) * ((a->N + 255) / 256);

@@ -191,8 +191,11 @@ class StagedTrainer:
         Returns the mean loss over the step as a 0-d device tensor (valid on the last stage)."""
         st, n = self.stage, self.n_micro
         mb = tokens.shape[0] // n
-        inputs = [tokens[i * mb:(i + 1) * mb, :-1].contiguous() for i in range(n)]
-        labels = [tokens[i * mb:(i + 1) * mb, 1:].contiguous() for i in range(n)]
+        if hasattr(st, "split_batch"):
+            inputs, labels = st.split_batch(tokens, n)     # model-specific batch layout
+        else:
+            inputs = [tokens[i * mb:(i + 1) * mb, :-1].contiguous() for i in range(n)]
+            labels = [tokens[i * mb:(i + 1) * mb, 1:].contiguous() for i in range(n)]
         st.store.start_accumulation()
         loss = torch.zeros((), dtype=torch.float32, device=tokens.device)
         if self.pp_size == 1:
