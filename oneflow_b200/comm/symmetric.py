@@ -46,7 +46,7 @@ class SymmetricArena:
         lib = _native.kernels()
         self.group, self.ranks, self.device = group, list(ranks), torch.device(device)
         self.n = len(self.ranks)
-        self.rank = self.ranks.index(dist.get_rank()) if dist.is_initialized() else 0
+        self.rank = self.ranks.index(dist.get_rank()) if dist.is_initialized() and self.n > 1 else 0
         self.nbytes = _align(int(nbytes) + _SIGNAL_BYTES, 1 << 21)
         ptr = c_void_p()
         handle = (c_ubyte * 64)()

@@ -80,6 +80,9 @@ struct SignalBlock {
   unsigned int ag_ready[kMaxPeers];      // ag_ready[r] = last all-gather epoch for which rank r's shard is readable
   unsigned int ag_pulled[kMaxPeers];     // ag_pulled[r] = last all-gather epoch whose shard rank r finished pulling from me
   unsigned int local_cnt[32];            // scratch counters used only by this GPU's own CTAs
+  unsigned int emb_ids[kMaxPeers];       // emb_ids[r] = last embedding step whose unique ids rank r stored into my key buffer
+  unsigned int emb_rows[kMaxPeers];      // emb_rows[r] = last embedding step whose rows owner r stored into my row buffer
+  unsigned int emb_grads[kMaxPeers];     // emb_grads[r] = last embedding step whose gradients rank r stored into my buffer
 };
 
 }  // namespace ofb

@@ -1,0 +1,601 @@
+// OneEmbedding on device: the id shuffle, the table lookup fused with the embedding shuffle, and the
+// gradient shuffle fused with the sparse row update, all over peer-mapped memory (no NCCL, no host sync).
+//
+// One training step of a model-parallel embedding with N ranks (every rank owns the keys whose hash maps to it):
+//
+//   forward  (requester)  partition : dedupe this rank's ids in a per-step hash table, number the unique keys per
+//                                     owner, and store every unique key straight into the owner's receive buffer
+//                         publish   : translate every id position to (owner, index), push the per-owner counts,
+//                                     raise the "ids ready" flag at every owner
+//            (owner)      resolve   : wait for the flags, find-or-insert every received key in the persistent
+//                                     table (new rows are initialised in place from a counter-based generator,
+//                                     so a row's initial value depends only on its key and the seed)
+//                         serve     : read each row (fp32), convert, and store it into the requester's receive
+//                                     buffer; raise "rows ready" at every requester
+//            (requester)  gather    : wait for the flags, expand unique rows to [ids, dim] by the inverse index
+//   backward (requester)  reduce    : segment-sum the output gradient per unique key (fp32 vector atomics in L2)
+//                         push      : convert each summed row and store it into the owner's gradient buffer,
+//                                     clear the sum, raise "grads ready" at every owner
+//            (owner)      combine   : wait for the flags, add the rows of all requesters per touched table row
+//                         update    : apply SGD / momentum / Adam / Adagrad / FTRL to each touched row once
+//
+// All capacities are worst case (every id of a rank unique and owned by one peer), so no count ever has to
+// reach the host. Flags are monotonic step numbers; every wait is bounded and reports through the status
+// block. Buffer reuse across steps is safe without extra flags: a requester cannot publish step t+1 before it
+// gathered step t, which needs every owner's serve(t), and the counts are double-buffered by step parity
+// because the owner still reads them in combine(t) while a fast requester publishes step t+1.
+//
+// Reference counterparts: oneflow/user/kernels/one_embedding_kernels.cu (lookup / put),
+// one_embedding_id_shuffle_p2p_kernel.cu, one_embedding_embedding_shuffle_p2p_kernel.cu,
+// one_embedding_embedding_gradient_shuffle_p2p_kernel.cu, one_embedding_update_kernels.cu:60-110,
+// oneflow/core/embedding/hash_functions.cuh, full_cache.cu.
+#include <cuda_fp16.h>
+
+#include "../common/host_utils.h"
+#include "comm_common.cuh"
+#include "ofb_comm.h"
+
+namespace ofb {
+
+constexpr unsigned long long kEmptyKey = ~0ull;
+constexpr int kOwnerShift = 28;
+constexpr unsigned int kIndexMask = (1u << kOwnerShift) - 1u;
+
+struct EmbCtx {
+  int rank, n;
+  unsigned char* arena[kMaxPeers];
+  SignalBlock* sig[kMaxPeers];
+  int* status;
+};
+
+static EmbCtx to_emb_ctx(const OfbCommCtx* c) {
+  EmbCtx x;
+  x.rank = c->rank;
+  x.n = c->n;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    x.arena[i] = reinterpret_cast<unsigned char*>(c->arena[i]);
+    x.sig[i] = reinterpret_cast<SignalBlock*>(c->signals[i]);
+  }
+  x.status = device_status_ptr();
+  return x;
+}
+
+// splitmix64 finaliser on a signed value with arithmetic shifts: bit-identical to the int64 tensor version
+// that the host side uses to compute owners.
+__device__ __forceinline__ long long mix64s(long long k) {
+  k = k ^ (k >> 30);
+  k = k * static_cast<long long>(0xBF58476D1CE4E5B9ull);
+  k = k ^ (k >> 27);
+  k = k * static_cast<long long>(0x94D049BB133111EBull);
+  return k ^ (k >> 31);
+}
+__device__ __forceinline__ int owner_of(long long key, int world) {
+  return static_cast<int>((mix64s(key) & 0x7FFFFFFFll) % world);
+}
+// table position: a second, independent mix (the owner hash fixes some bits of the first one)
+__device__ __forceinline__ unsigned long long slot_hash(long long key) {
+  return static_cast<unsigned long long>(mix64s(key + static_cast<long long>(0x9E3779B97F4A7C15ull))) >> 17;
+}
+__device__ __forceinline__ float unit_uniform(unsigned long long key, unsigned int c, unsigned long long seed) {
+  const unsigned long long h =
+      static_cast<unsigned long long>(mix64s(static_cast<long long>(key * 0x9E3779B97F4A7C15ull + c * 0xD6E8FEB86659FD93ull + seed)));
+  // bits 8..31: the arithmetic shifts of the signed mix leave the top bit constant
+  return (static_cast<float>((h >> 8) & 0xFFFFFFull) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1)
+}
+
+__device__ __forceinline__ void record(int* status, int code, int detail) {
+  if (status && atomicCAS(status, 0, code) == 0) status[1] = detail;
+}
+
+// --------------------------------------------------------------------------------------------- requester: ids
+__global__ void __launch_bounds__(256)
+emb_partition_kernel(const long long* __restrict__ ids, const int* __restrict__ tids, long long n, int num_tables, int columns,
+                     unsigned long long* dkeys, unsigned int* dval, long long dmask, int* cnt, unsigned int* inv, EmbCtx c,
+                     long long keys_off, long long cap) {
+  for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x; p < n; p += (long long)gridDim.x * blockDim.x) {
+    const int t = tids ? tids[p] : static_cast<int>(p % columns) % num_tables;
+    const long long key = ids[p] * num_tables + t;
+    const unsigned long long ukey = static_cast<unsigned long long>(key);
+    long long s = static_cast<long long>(slot_hash(key)) & dmask;
+    unsigned int found = 0xFFFFFFFFu;
+    for (long long probe = 0; probe <= dmask; ++probe) {
+      const unsigned long long prev = atomicCAS(&dkeys[s], kEmptyKey, ukey);
+      if (prev == kEmptyKey) {
+        const int owner = owner_of(key, c.n);
+        const int idx = atomicAdd(&cnt[owner], 1);
+        dval[s] = (static_cast<unsigned int>(owner) << kOwnerShift) | static_cast<unsigned int>(idx);
+        if (idx < cap)
+          reinterpret_cast<unsigned long long*>(c.arena[owner] + keys_off)[c.rank * cap + idx] = ukey;
+        found = static_cast<unsigned int>(s);
+        break;
+      }
+      if (prev == ukey) {
+        found = static_cast<unsigned int>(s);
+        break;
+      }
+      s = (s + 1) & dmask;
+    }
+    if (found == 0xFFFFFFFFu) record(c.status, kStatusHashTableFull, 1);
+    inv[p] = found;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+emb_publish_kernel(long long n, const unsigned int* __restrict__ dval, const int* __restrict__ cnt, unsigned int* inv, EmbCtx c,
+                   long long cnt_off, unsigned int epoch) {
+  if (blockIdx.x == 0 && threadIdx.x < c.n) {
+    const int r = threadIdx.x;
+    int* peer_cnt = reinterpret_cast<int*>(c.arena[r] + cnt_off) + (epoch & 1u) * kMaxPeers;
+    peer_cnt[c.rank] = cnt[r];
+    __threadfence_system();
+    st_release_sys(&c.sig[r]->emb_ids[c.rank], epoch);
+  }
+  for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x; p < n; p += (long long)gridDim.x * blockDim.x) {
+    const unsigned int s = inv[p];
+    inv[p] = s == 0xFFFFFFFFu ? s : dval[s];
+  }
+}
+
+// Waits (thread r for peer r) until every peer's flag reached `epoch`, then loads the per-source counts into
+// shared memory as an exclusive prefix. Returns false for the whole block when a wait ran out.
+__device__ bool wait_and_prefix(const unsigned int* flags, const int* counts, int n, long long cap, unsigned int epoch, int* status,
+                                int detail, long long* pre /* [kMaxPeers + 1] shared */) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < n) {
+    if (!wait_flag_ge(&flags[threadIdx.x], epoch, status, detail + threadIdx.x)) ok_s = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && ok_s) {
+    long long acc = 0;
+    for (int r = 0; r < n; ++r) {
+      pre[r] = acc;
+      long long v = counts ? reinterpret_cast<const volatile int*>(counts)[r] : 0;
+      if (v < 0) v = 0;
+      if (v > cap) v = cap;
+      acc += v;
+    }
+    pre[n] = acc;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__device__ __forceinline__ void locate(const long long* pre, int n, long long w, int* r, long long* idx) {
+  int q = 0;
+  while (q + 1 < n && w >= pre[q + 1]) ++q;
+  *r = q;
+  *idx = w - pre[q];
+}
+
+// Raises `flag[c.rank] = epoch` at every peer once all CTAs of the grid have finished their stores.
+__device__ void signal_when_grid_done(const EmbCtx& c, int* done_cnt, unsigned int epoch, int which) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int old = atomicAdd(done_cnt, 1);
+    if (old == static_cast<int>(gridDim.x) - 1) {
+      *done_cnt = 0;
+      __threadfence_system();
+      for (int r = 0; r < c.n; ++r) {
+        unsigned int* f = which == 0 ? &c.sig[r]->emb_rows[c.rank] : &c.sig[r]->emb_grads[c.rank];
+        st_release_sys(f, epoch);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------- owner: lookup
+__global__ void __launch_bounds__(256)
+emb_resolve_kernel(OfbEmbStore st, EmbCtx c, long long keys_off, long long cnt_off, long long cap, int* slot_tmp, int* n_uo,
+                   unsigned int epoch, int insert) {
+  __shared__ long long pre[kMaxPeers + 1];
+  const int* counts = reinterpret_cast<const int*>(c.arena[c.rank] + cnt_off) + (epoch & 1u) * kMaxPeers;
+  if (!wait_and_prefix(c.sig[c.rank]->emb_ids, counts, c.n, cap, epoch, c.status, 200, pre)) return;
+  const unsigned long long* keys = reinterpret_cast<const unsigned long long*>(c.arena[c.rank] + keys_off);
+  const long long tmask = st.tcap - 1;
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = warp; w < pre[c.n]; w += nwarps) {
+    int r;
+    long long idx;
+    locate(pre, c.n, w, &r, &idx);
+    const unsigned long long ukey = keys[r * cap + idx];
+    const long long key = static_cast<long long>(ukey);
+    int s_found = -1, new_row = -1;
+    if (lane == 0) {
+      long long s = static_cast<long long>(slot_hash(key)) & tmask;
+      for (long long probe = 0; probe <= tmask; ++probe) {
+        unsigned long long prev = st.tkeys[s];
+        if (prev == kEmptyKey && insert) prev = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
+        if (prev == kEmptyKey) {
+          if (!insert) break;  // absent and not inserting: the row reads as zeros
+          const int row = atomicAdd(&st.counters[0], 1);
+          if (row < st.row_cap) {
+            st.trow[s] = row;
+            st.row_key[row] = ukey;
+            new_row = row;
+          } else {
+            st.trow[s] = -1;
+            record(c.status, kStatusHashTableFull, 2);
+          }
+          s_found = static_cast<int>(s);
+          break;
+        }
+        if (prev == ukey) {
+          s_found = static_cast<int>(s);
+          break;
+        }
+        s = (s + 1) & tmask;
+      }
+      if (s_found < 0 && insert) record(c.status, kStatusHashTableFull, 3);
+      if (s_found >= 0) {
+        if (atomicExch(&st.stamp[s_found], epoch) != epoch) st.uo_of[s_found] = atomicAdd(n_uo, 1);
+      }
+      slot_tmp[r * cap + idx] = s_found;
+    }
+    new_row = __shfl_sync(0xffffffffu, new_row, 0);
+    if (new_row >= 0) {
+      const int table = static_cast<int>(ukey % static_cast<unsigned long long>(st.num_tables));
+      const int kind = st.init_kind[table];
+      const float a = st.init_a[table], b = st.init_b[table];
+      float* row = st.rows + static_cast<long long>(new_row) * st.line;
+      for (int col = lane; col < st.line; col += 32) {
+        float v;
+        if (col >= st.dim) {
+          v = col < 2 * st.dim ? st.state_init : 0.f;  // first state vector (accumulator) only
+        } else if (kind == 0) {  // uniform(a, b)
+          v = a + (b - a) * unit_uniform(ukey, col, st.seed);
+        } else if (kind == 1) {  // normal(mean a, std b), Box-Muller on a column pair
+          const float u1 = unit_uniform(ukey, 2 * (col >> 1), st.seed);
+          const float u2 = unit_uniform(ukey, 2 * (col >> 1) + 1, st.seed ^ 0x5851F42D4C957F2Dull);
+          const float rad = sqrtf(-2.f * __logf(u1));
+          float sn, cs;
+          __sincosf(6.283185307179586f * u2, &sn, &cs);
+          v = a + b * rad * ((col & 1) ? sn : cs);
+        } else {  // constant a
+          v = a;
+        }
+        row[col] = v;
+      }
+    }
+  }
+}
+
+template <bool kHalf>
+__device__ __forceinline__ uint2 pack4(float4 v) {
+  uint2 o;
+  if (kHalf) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    o.x = *reinterpret_cast<const unsigned int*>(&lo);
+    o.y = *reinterpret_cast<const unsigned int*>(&hi);
+  } else {
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+  }
+  return o;
+}
+template <bool kHalf>
+__device__ __forceinline__ float4 unpack4(uint2 q) {
+  if (kHalf) {
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+  const float2 lo = unpack_bf16x2(q.x), hi = unpack_bf16x2(q.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+emb_serve_kernel(OfbEmbStore st, EmbCtx c, long long cnt_off, long long emb_off, long long cap, const int* __restrict__ slot_tmp,
+                 int* rowidx, int* uoidx, int* u_row, int* done_cnt, unsigned int epoch) {
+  __shared__ long long pre[kMaxPeers + 1];
+  const int* counts = reinterpret_cast<const int*>(c.arena[c.rank] + cnt_off) + (epoch & 1u) * kMaxPeers;
+  const bool ok = wait_and_prefix(c.sig[c.rank]->emb_ids, counts, c.n, cap, epoch, c.status, 210, pre);
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int D = st.dim;
+  for (long long w = warp; ok && w < pre[c.n]; w += nwarps) {
+    int r;
+    long long idx;
+    locate(pre, c.n, w, &r, &idx);
+    const int s = slot_tmp[r * cap + idx];
+    const int row = s >= 0 ? st.trow[s] : -1;
+    if (lane == 0) {
+      const int uo = s >= 0 ? st.uo_of[s] : -1;
+      rowidx[r * cap + idx] = row;
+      uoidx[r * cap + idx] = uo;
+      if (uo >= 0) u_row[uo] = row;
+    }
+    uint2* dst = reinterpret_cast<uint2*>(c.arena[r] + emb_off) + (c.rank * cap + idx) * (D >> 2);
+    const float4* src = reinterpret_cast<const float4*>(st.rows + static_cast<long long>(row < 0 ? 0 : row) * st.line);
+    for (int q = lane; q < (D >> 2); q += 32) {
+      const float4 v = row >= 0 ? src[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+      dst[q] = pack4<kHalf>(v);
+    }
+  }
+  signal_when_grid_done(c, done_cnt, epoch, 0);
+}
+
+// --------------------------------------------------------------------------------------------- requester: gather
+__global__ void __launch_bounds__(256)
+emb_gather_kernel(EmbCtx c, long long emb_off, long long cap, const unsigned int* __restrict__ inv, long long n, int D, uint2* out,
+                  unsigned int epoch) {
+  __shared__ long long pre[kMaxPeers + 1];
+  if (!wait_and_prefix(c.sig[c.rank]->emb_rows, nullptr, c.n, cap, epoch, c.status, 220, pre)) return;
+  const uint2* src = reinterpret_cast<const uint2*>(c.arena[c.rank] + emb_off);
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int vec = D >> 2;
+  for (long long p = warp; p < n; p += nwarps) {
+    const unsigned int v = inv[p];
+    const bool valid = v != 0xFFFFFFFFu;
+    const long long u = valid ? (long long)(v >> kOwnerShift) * cap + (v & kIndexMask) : 0;
+    for (int q = lane; q < vec; q += 32) out[p * vec + q] = valid ? src[u * vec + q] : make_uint2(0u, 0u);
+  }
+}
+
+// --------------------------------------------------------------------------------------------- requester: gradients
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+emb_grad_reduce_kernel(const uint2* __restrict__ grad, const unsigned int* __restrict__ inv, long long n, int D, long long cap,
+                       float* gsum) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int vec = D >> 2;
+  for (long long p = warp; p < n; p += nwarps) {
+    const unsigned int v = inv[p];
+    if (v == 0xFFFFFFFFu) continue;
+    const long long u = (long long)(v >> kOwnerShift) * cap + (v & kIndexMask);
+    float4* dst = reinterpret_cast<float4*>(gsum + u * D);
+    for (int q = lane; q < vec; q += 32) atomicAdd(&dst[q], unpack4<kHalf>(grad[p * vec + q]));
+  }
+}
+
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+emb_grad_push_kernel(EmbCtx c, const int* __restrict__ cnt, long long grad_off, long long cap, int D, float* gsum, int* done_cnt,
+                     unsigned int epoch) {
+  __shared__ long long pre[kMaxPeers + 1];
+  if (threadIdx.x == 0) {
+    long long acc = 0;
+    for (int r = 0; r < c.n; ++r) {
+      pre[r] = acc;
+      long long v = cnt[r];
+      acc += v > cap ? cap : v;
+    }
+    pre[c.n] = acc;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int vec = D >> 2;
+  for (long long w = warp; w < pre[c.n]; w += nwarps) {
+    int o;
+    long long idx;
+    locate(pre, c.n, w, &o, &idx);
+    float4* src = reinterpret_cast<float4*>(gsum + (o * cap + idx) * D);
+    uint2* dst = reinterpret_cast<uint2*>(c.arena[o] + grad_off) + (c.rank * cap + idx) * vec;
+    for (int q = lane; q < vec; q += 32) {
+      dst[q] = pack4<kHalf>(src[q]);
+      src[q] = make_float4(0.f, 0.f, 0.f, 0.f);  // the sums stay zero between steps
+    }
+  }
+  signal_when_grid_done(c, done_cnt, epoch, 1);
+}
+
+// --------------------------------------------------------------------------------------------- owner: update
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+emb_grad_combine_kernel(EmbCtx c, long long cnt_off, long long grad_off, long long cap, int D, const int* __restrict__ uoidx,
+                        float* gacc, unsigned int epoch) {
+  __shared__ long long pre[kMaxPeers + 1];
+  const int* counts = reinterpret_cast<const int*>(c.arena[c.rank] + cnt_off) + (epoch & 1u) * kMaxPeers;
+  if (!wait_and_prefix(c.sig[c.rank]->emb_grads, counts, c.n, cap, epoch, c.status, 230, pre)) return;
+  const uint2* src = reinterpret_cast<const uint2*>(c.arena[c.rank] + grad_off);
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int vec = D >> 2;
+  for (long long w = warp; w < pre[c.n]; w += nwarps) {
+    int r;
+    long long idx;
+    locate(pre, c.n, w, &r, &idx);
+    const int uo = uoidx[r * cap + idx];
+    if (uo < 0) continue;
+    float4* dst = reinterpret_cast<float4*>(gacc + static_cast<long long>(uo) * D);
+    for (int q = lane; q < vec; q += 32) atomicAdd(&dst[q], unpack4<kHalf>(src[(r * cap + idx) * vec + q]));
+  }
+}
+
+// Row layout: [w (D) | state 1 (D) | state 2 (D)] as far as the optimizer needs.
+__global__ void __launch_bounds__(256)
+emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __restrict__ n_uo, float* gacc, OfbEmbUpdate h) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int D = st.dim;
+  const int total = *n_uo;
+  for (long long u = warp; u < total; u += nwarps) {
+    const int row = u_row[u];
+    float* g_row = gacc + u * D;
+    if (row < 0) {
+      for (int col = lane; col < D; col += 32) g_row[col] = 0.f;
+      continue;
+    }
+    float* w = st.rows + static_cast<long long>(row) * st.line;
+    for (int col = lane; col < D; col += 32) {
+      float g = g_row[col] * h.scale;
+      g_row[col] = 0.f;  // the accumulators stay zero between steps
+      float x = w[col];
+      if (h.l2 != 0.f) g += h.l2 * x;
+      switch (h.kind) {
+        case 0:  // sgd
+          x -= h.lr * (g + h.weight_decay * x);
+          break;
+        case 1: {  // momentum
+          const float m = h.momentum * w[D + col] + g;
+          w[D + col] = m;
+          x -= h.lr * (m + h.weight_decay * x);
+          break;
+        }
+        case 2: {  // adam
+          const float m = h.beta1 * w[D + col] + (1.f - h.beta1) * g;
+          const float v = h.beta2 * w[2 * D + col] + (1.f - h.beta2) * g * g;
+          w[D + col] = m;
+          w[2 * D + col] = v;
+          x -= (h.lr / h.bias_corr1) * m / (sqrtf(v) / sqrtf(h.bias_corr2) + h.eps) + h.lr * h.weight_decay * x;
+          break;
+        }
+        case 3: {  // adagrad
+          const float s = w[D + col] + g * g;
+          w[D + col] = s;
+          x -= h.lr_eff * g / (sqrtf(s) + h.eps) + h.lr * h.weight_decay * x;
+          break;
+        }
+        default: {  // ftrl
+          const float acc = w[D + col];
+          const float nacc = acc + g * g;
+          const float sigma = (powf(nacc, -h.lr_power) - powf(acc, -h.lr_power)) / h.lr;
+          const float z = w[2 * D + col] + g - sigma * x;
+          w[2 * D + col] = z;
+          w[D + col] = nacc;
+          const float denom = (h.beta + powf(nacc, -h.lr_power)) / h.lr + h.lambda2;
+          x = fabsf(z) > h.lambda1 ? -(z - copysignf(h.lambda1, z)) / denom : 0.f;
+          break;
+        }
+      }
+      w[col] = x;
+    }
+  }
+}
+
+// Finds (optionally inserts, without initialising) keys in the table of one rank: rows[i] = row index or -1.
+__global__ void __launch_bounds__(256)
+emb_find_kernel(OfbEmbStore st, const long long* __restrict__ keys, long long n, int insert, int* rows, int* status) {
+  const long long tmask = st.tcap - 1;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long key = keys[i];
+    const unsigned long long ukey = static_cast<unsigned long long>(key);
+    long long s = static_cast<long long>(slot_hash(key)) & tmask;
+    int row = -1;
+    for (long long probe = 0; probe <= tmask; ++probe) {
+      unsigned long long prev = st.tkeys[s];
+      if (prev == kEmptyKey && insert) prev = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
+      if (prev == kEmptyKey) {
+        if (insert) {
+          row = atomicAdd(&st.counters[0], 1);
+          if (row < st.row_cap) {
+            st.row_key[row] = ukey;
+          } else {
+            row = -1;
+            record(status, kStatusHashTableFull, 4);
+          }
+          st.trow[s] = row;
+        }
+        break;
+      }
+      if (prev == ukey) {
+        // a concurrent inserter of the same key may not have published the row yet: callers pass unique keys
+        row = st.trow[s];
+        break;
+      }
+      s = (s + 1) & tmask;
+    }
+    rows[i] = row;
+  }
+}
+
+}  // namespace ofb
+
+using namespace ofb;
+
+static int emb_grid(long long items, int per_block) {
+  long long b = (items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  return static_cast<int>(b);
+}
+
+static int emb_check(const OfbCommCtx* ctx, const OfbEmbStore* st, const OfbEmbShuffle* sh, long long n) {
+  if (!ctx || !st || !sh) return fail("embedding: null argument");
+  if (ctx->n < 1 || ctx->n > kMaxPeers) return fail("embedding: 1..8 ranks");
+  if (st->dim % 4 || st->line < st->dim) return fail("embedding: dim must be a multiple of 4 and fit the row");
+  if (n > sh->cap || sh->cap > (1ll << kOwnerShift)) return fail("embedding: more ids than the exchange buffers hold");
+  if (sh->dcap & (sh->dcap - 1) || st->tcap & (st->tcap - 1)) return fail("embedding: table sizes must be powers of two");
+  if (sh->dcap < 2 * n || sh->dcap > (1ll << 32) - 2) return fail("embedding: dedupe table too small for this many ids");
+  if (st->tcap > (1ll << 31)) return fail("embedding: table too large");
+  return 0;
+}
+
+// Forward: ids [n] (row-major [batch, columns]) -> out [n, dim] in `out_half ? fp16 : bf16`. `epoch` is this
+// arena's embedding step number (same on every rank, starting at 1).
+OFB_API int ofb_emb_forward(const OfbCommCtx* cctx, const OfbEmbStore* st, const OfbEmbShuffle* sh, const long long* ids,
+                            const int* tids, long long n, int columns, int insert, unsigned int epoch, void* out, int out_half,
+                            void* stream_) {
+  if (emb_check(cctx, st, sh, n)) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  EmbCtx c = to_emb_ctx(cctx);
+  OFB_CUDA_OK(cudaMemsetAsync(sh->dkeys, 0xFF, sh->dcap * sizeof(unsigned long long), stream));
+  OFB_CUDA_OK(cudaMemsetAsync(sh->cnt, 0, kMaxPeers * sizeof(int), stream));
+  OFB_CUDA_OK(cudaMemsetAsync(sh->n_uo, 0, sizeof(int), stream));
+  emb_partition_kernel<<<emb_grid(n, 256), 256, 0, stream>>>(ids, tids, n, st->num_tables, columns < 1 ? 1 : columns, sh->dkeys, sh->dval,
+                                                            sh->dcap - 1, sh->cnt, sh->inv, c, sh->keys_off, sh->cap);
+  emb_publish_kernel<<<emb_grid(n, 256), 256, 0, stream>>>(n, sh->dval, sh->cnt, sh->inv, c, sh->cnt_off, epoch);
+  const long long worst = sh->cap * c.n;
+  emb_resolve_kernel<<<emb_grid(worst, 8), 256, 0, stream>>>(*st, c, sh->keys_off, sh->cnt_off, sh->cap, sh->slot_tmp, sh->n_uo, epoch,
+                                                            insert);
+  if (out_half)
+    emb_serve_kernel<true><<<emb_grid(worst, 8), 256, 0, stream>>>(*st, c, sh->cnt_off, sh->emb_off, sh->cap, sh->slot_tmp, sh->rowidx,
+                                                                   sh->uoidx, sh->u_row, sh->done + 0, epoch);
+  else
+    emb_serve_kernel<false><<<emb_grid(worst, 8), 256, 0, stream>>>(*st, c, sh->cnt_off, sh->emb_off, sh->cap, sh->slot_tmp, sh->rowidx,
+                                                                    sh->uoidx, sh->u_row, sh->done + 0, epoch);
+  emb_gather_kernel<<<emb_grid(n, 8), 256, 0, stream>>>(c, sh->emb_off, sh->cap, sh->inv, n, st->dim, reinterpret_cast<uint2*>(out), epoch);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Backward of the forward with the same `epoch`: grad [n, dim] (same 16-bit type as the forward output).
+OFB_API int ofb_emb_backward(const OfbCommCtx* cctx, const OfbEmbStore* st, const OfbEmbShuffle* sh, const void* grad, long long n,
+                             int grad_half, unsigned int epoch, const OfbEmbUpdate* upd, void* stream_) {
+  if (emb_check(cctx, st, sh, n)) return -1;
+  if (!upd) return fail("embedding: no update rule");
+  const int need = upd->kind == 0 ? 1 : (upd->kind == 1 || upd->kind == 3) ? 2 : 3;
+  if (st->line < need * st->dim) return fail("embedding: rows too short for this optimizer's state");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  EmbCtx c = to_emb_ctx(cctx);
+  const long long worst = sh->cap * c.n;
+  const uint2* g = reinterpret_cast<const uint2*>(grad);
+  if (grad_half) {
+    emb_grad_reduce_kernel<true><<<emb_grid(n, 8), 256, 0, stream>>>(g, sh->inv, n, st->dim, sh->cap, sh->gsum);
+    emb_grad_push_kernel<true><<<emb_grid(n, 8), 256, 0, stream>>>(c, sh->cnt, sh->grad_off, sh->cap, st->dim, sh->gsum, sh->done + 1, epoch);
+    emb_grad_combine_kernel<true><<<emb_grid(worst, 8), 256, 0, stream>>>(c, sh->cnt_off, sh->grad_off, sh->cap, st->dim, sh->uoidx, sh->gacc,
+                                                                          epoch);
+  } else {
+    emb_grad_reduce_kernel<false><<<emb_grid(n, 8), 256, 0, stream>>>(g, sh->inv, n, st->dim, sh->cap, sh->gsum);
+    emb_grad_push_kernel<false><<<emb_grid(n, 8), 256, 0, stream>>>(c, sh->cnt, sh->grad_off, sh->cap, st->dim, sh->gsum, sh->done + 1, epoch);
+    emb_grad_combine_kernel<false><<<emb_grid(worst, 8), 256, 0, stream>>>(c, sh->cnt_off, sh->grad_off, sh->cap, st->dim, sh->uoidx,
+                                                                           sh->gacc, epoch);
+  }
+  emb_update_kernel<<<emb_grid(worst, 8), 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// rows[i] = row index of keys[i] in this rank's table (-1 when absent and not inserting). Keys must be unique
+// when inserting. Used by snapshot loading and by tests.
+OFB_API int ofb_emb_find(const OfbEmbStore* st, const long long* keys, long long n, int insert, int* rows, void* stream_) {
+  if (!st || (st->tcap & (st->tcap - 1))) return fail("embedding: bad table");
+  if (n == 0) return 0;
+  emb_find_kernel<<<emb_grid(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(*st, keys, n, insert, rows, device_status_ptr());
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

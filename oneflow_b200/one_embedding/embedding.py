@@ -312,6 +312,8 @@ class Embedding(torch.nn.Module):
         # the reference keeps a scalar "shadow" variable so that the embedding takes part in autograd / graphs
         self.shadow = torch.nn.Parameter(torch.zeros(1))
         self.store: Optional[RowStore] = None
+        self.engine = None          # device engine (one_embedding/native.py) once a CUDA batch arrived
+        self.max_ids_per_step = int(os.environ.get("ONEFLOW_ONE_EMBEDDING_MAX_IDS_PER_STEP", "0"))
         self.sparse_optimizer = ("sgd", {"lr": 0.0})
         self.step_count = 0
         self.gradient_fp16 = os.environ.get("ONEFLOW_ONE_EMBEDDING_GRADIENT_SHUFFLE_USE_FP16", "1") == "1"
@@ -343,8 +345,31 @@ class Embedding(torch.nn.Module):
         out_shape = tuple(ids.shape) + (self.embedding_dim,)
         return _LookupFn.apply(self.shadow, self, keys, tids, out_shape)
 
+    def _use_engine(self, ids):
+        """The device engine serves 16-bit embeddings on CUDA within one node; everything else (CPU tensors,
+        fp32 outputs, more than 8 ranks) takes the tensor-op path below."""
+        if self.engine is not None:
+            return True
+        if self.store is not None or self.dtype not in (torch.float16, torch.bfloat16) or self.world > 8:
+            return False
+        if self.embedding_dim % 4 or os.environ.get("ONEFLOW_B200_EMBEDDING_ENGINE", "1") == "0":
+            return False
+        from . import native
+        if not native.available(ids.device):
+            return False
+        kind = self.sparse_optimizer[0]
+        state_init = float(self.sparse_optimizer[1].get("initial_accumulator_value", 0.0)) if kind in ("adagrad", "ftrl") else 0.0
+        self.engine = native.NativeEmbeddingEngine(
+            ids.device, max(ids.numel(), self.max_ids_per_step), self.embedding_dim, self.storage_dim, self.inits,
+            self.capacity_per_rank, seed=self.seed, half=self.dtype == torch.float16, state_init=state_init)
+        return True
+
     def _forward_impl(self, ids, tids):
         dev = ids.device
+        if ids.is_cuda and self._use_engine(ids):
+            nt = max(len(self.tables), 1)
+            out = self.engine.forward(ids, tids if nt > 1 else None, insert=True)
+            return out.view(-1, self.embedding_dim), {"engine": True}
         store = self._ensure_store(dev)
         nt = max(len(self.tables), 1)
         keys = ids * nt + tids                         # one 64-bit key per (id, table)
@@ -376,6 +401,9 @@ class Embedding(torch.nn.Module):
         kind, hyper = self.sparse_optimizer
         D = self.embedding_dim
         self.step_count += 1
+        if plan.get("engine"):
+            self.engine.backward(grad, kind, hyper, self.step_count)
+            return
         seg = torch.zeros((plan["n_unique"], D), dtype=torch.float32, device=grad.device)
         seg.index_add_(0, plan["inverse"], grad.float())
         if self.world > 1:
@@ -393,16 +421,20 @@ class Embedding(torch.nn.Module):
 
     # -------------------------------------------------------------- snapshots
     def save_snapshot(self, snapshot_name):
-        if self.store is None or not self.persistent_path:
+        store = self.engine if self.engine is not None else self.store
+        if store is None or not self.persistent_path:
             return
         d = os.path.join(self.persistent_path, f"rank_{self.rank}", "snapshots", snapshot_name)
         os.makedirs(d, exist_ok=True)
-        torch.save(self.store.snapshot(), os.path.join(d, "rows.pt"))
+        torch.save(store.snapshot(), os.path.join(d, "rows.pt"))
 
     def load_snapshot(self, snapshot_name, device="cpu"):
         d = os.path.join(self.persistent_path, f"rank_{self.rank}", "snapshots", snapshot_name)
         snap = torch.load(os.path.join(d, "rows.pt"), weights_only=False)
-        self._ensure_store(device).load_snapshot(snap)
+        if self.engine is not None:
+            self.engine.load_snapshot(snap)
+        else:
+            self._ensure_store(device).load_snapshot(snap)
 
     def state_dict(self, *args, **kwargs):
         sd = super().state_dict(*args, **kwargs)

@@ -204,6 +204,39 @@ def case_tp_matches_single(rank, world, dev):
         assert _native.read_status() == (0, 0), _native.read_status()
 
 
+def case_embedding_engine(rank, world, dev):
+    """Model-parallel embedding over peer memory against a single-rank engine fed the global batch."""
+    from oneflow_b200.one_embedding.native import NativeEmbeddingEngine
+    from oneflow_b200.ops import _native
+    D, T, B = 128, 5, 4096
+    inits = [{"type": "normal", "mean": 0.0, "std": 0.05}, {"type": "uniform", "low": -0.1, "high": 0.1}] * 2 + \
+            [{"type": "constant", "value": 0.125}]
+    eng = NativeEmbeddingEngine(dev, B * T, D, D, inits, 1 << 16, seed=7)
+    ref = NativeEmbeddingEngine(dev, world * B * T, D, D, inits, 1 << 17, seed=7, solo=True)
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    hyper = {"lr": 0.5}
+    for step in range(1, 4):
+        ids = (torch.randint(0, 3000, (B, T), generator=g) ** 2 // 3000).to(dev)       # skewed, many duplicates
+        grad = (torch.randn(B, T, D, generator=g) * 0.1).bfloat16().to(dev)
+        all_ids = [torch.empty_like(ids) for _ in range(world)]
+        all_grad = [torch.empty_like(grad) for _ in range(world)]
+        dist.all_gather(all_ids, ids)
+        dist.all_gather(all_grad, grad)
+        out = eng.forward(ids)
+        out_ref = ref.forward(torch.cat(all_ids))[rank * B:(rank + 1) * B]
+        if step == 1:
+            assert torch.equal(out, out_ref), "initial rows differ between sharded and single-rank engines"
+        else:
+            close(out, out_ref, 2e-2, f"embedding rows step {step}")
+        eng.backward(grad, "sgd", hyper, step)
+        ref.backward(torch.cat(all_grad), "sgd", hyper, step)
+    torch.cuda.synchronize()
+    total = torch.tensor([eng.size], device=dev)
+    dist.all_reduce(total)
+    assert int(total) == ref.size, (int(total), ref.size)
+    assert _native.read_status() == (0, 0), _native.read_status()
+
+
 def main():
     case, devkind = sys.argv[1], sys.argv[2]
     rank, world, dev = setup(devkind)
@@ -214,6 +247,8 @@ def main():
             case_fused_gemm(rank, world, dev)
         elif case == "tp_matches_single":
             case_tp_matches_single(rank, world, dev)
+        elif case == "embedding_engine":
+            case_embedding_engine(rank, world, dev)
         elif case.startswith("gpt_"):
             tp, pp, dp = (int(v) for v in case.split("_")[1:4])
             case_gpt_parallel(rank, world, dev, tp, pp, dp)

@@ -256,3 +256,27 @@ def test_fmha_bwd_padding_ragged():
     close(dq, rq, 3e-2, 2e-2)
     close(dk, rk, 3e-2, 2e-2)
     close(dv, rv, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("self_inter,T,D", [(False, 26, 128), (True, 26, 128), (False, 7, 64), (False, 31, 32)])
+def test_dot_feature_interaction(self_inter, T, D):
+    from oneflow_b200.ops.interaction import dot_feature_interaction, dot_feature_interaction_reference
+    torch.manual_seed(3)
+    B = 517
+    dense = (torch.randn(B, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    sparse = (torch.randn(B, T, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    F = T + 1
+    npairs = F * (F + 1) // 2 if self_inter else F * (F - 1) // 2
+    pad = (-(D + npairs)) % 8 or 8
+    n0 = K.launch_count
+    out = dot_feature_interaction([dense, sparse], output_concat=dense, self_interaction=self_inter, output_padding=pad)
+    assert K.launch_count == n0 + 1, "native interaction kernel did not run"
+    d32, s32 = dense.detach().float().requires_grad_(), sparse.detach().float().requires_grad_()
+    ref = dot_feature_interaction_reference([d32, s32], output_concat=d32, self_interaction=self_inter, output_padding=pad)
+    assert out.shape == ref.shape
+    torch.testing.assert_close(out.float(), ref, atol=0.06, rtol=0.02)
+    g = (torch.randn_like(ref) * 0.5).bfloat16()
+    out.backward(g)
+    ref.backward(g.float())
+    torch.testing.assert_close(dense.grad.float(), d32.grad, atol=0.15, rtol=0.03)
+    torch.testing.assert_close(sparse.grad.float(), s32.grad, atol=0.15, rtol=0.03)

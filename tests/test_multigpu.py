@@ -30,3 +30,8 @@ def test_tensor_parallel_matches_unsharded_2gpu():
 @pytest.mark.parametrize("case,n", [("gpt_2_1_1", 2), ("gpt_1_2_1", 2), ("gpt_1_1_2", 2), ("gpt_2_2_1", 4)])
 def test_gpt_parallel_training_gpu(case, n):
     run_case(case, _n(n), "cuda")
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_embedding_engine_matches_single_rank(n):
+    run_case("embedding_engine", _n(n), "cuda")
