@@ -88,35 +88,60 @@ __device__ __forceinline__ void record(int* status, int code, int detail) {
 }
 
 // --------------------------------------------------------------------------------------------- requester: ids
+// Lanes of `mask` (all of them call this) that hold the same `bucket` share one atomicAdd on counter[bucket]:
+// returns each lane's own index. Same-address atomics from every thread would serialise in L2.
+__device__ __forceinline__ int grouped_count(unsigned int mask, int bucket, int* counters) {
+  const unsigned int lane = threadIdx.x & 31;
+  const unsigned int peers = __match_any_sync(mask, bucket);
+  const int leader = __ffs(peers) - 1;
+  int base = 0;
+  if (static_cast<int>(lane) == leader) base = atomicAdd(&counters[bucket], __popc(peers));
+  base = __shfl_sync(peers, base, leader);
+  return base + __popc(peers & ((1u << lane) - 1u));
+}
+
 __global__ void __launch_bounds__(256)
 emb_partition_kernel(const long long* __restrict__ ids, const int* __restrict__ tids, long long n, int num_tables, int columns,
                      unsigned long long* dkeys, unsigned int* dval, long long dmask, int* cnt, unsigned int* inv, EmbCtx c,
                      long long keys_off, long long cap) {
-  for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x; p < n; p += (long long)gridDim.x * blockDim.x) {
-    const int t = tids ? tids[p] : static_cast<int>(p % columns) % num_tables;
-    const long long key = ids[p] * num_tables + t;
-    const unsigned long long ukey = static_cast<unsigned long long>(key);
-    long long s = static_cast<long long>(slot_hash(key)) & dmask;
+  for (long long base = blockIdx.x * (long long)blockDim.x; base < n; base += (long long)gridDim.x * blockDim.x) {
+    const long long p = base + threadIdx.x;
+    const bool active = p < n;
     unsigned int found = 0xFFFFFFFFu;
-    for (long long probe = 0; probe <= dmask; ++probe) {
-      const unsigned long long prev = atomicCAS(&dkeys[s], kEmptyKey, ukey);
-      if (prev == kEmptyKey) {
-        const int owner = owner_of(key, c.n);
-        const int idx = atomicAdd(&cnt[owner], 1);
-        dval[s] = (static_cast<unsigned int>(owner) << kOwnerShift) | static_cast<unsigned int>(idx);
-        if (idx < cap)
-          reinterpret_cast<unsigned long long*>(c.arena[owner] + keys_off)[c.rank * cap + idx] = ukey;
-        found = static_cast<unsigned int>(s);
-        break;
+    bool first = false;
+    long long key = 0;
+    if (active) {
+      const int t = tids ? tids[p] : static_cast<int>(p % columns) % num_tables;
+      key = ids[p] * num_tables + t;
+      const unsigned long long ukey = static_cast<unsigned long long>(key);
+      long long s = static_cast<long long>(slot_hash(key)) & dmask;
+      for (long long probe = 0; probe <= dmask; ++probe) {
+        // plain read first: repeated ids (the head of a Zipf distribution) never reach the atomic
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&dkeys[s]);
+        if (cur == kEmptyKey) {
+          cur = atomicCAS(&dkeys[s], kEmptyKey, ukey);
+          if (cur == kEmptyKey) {
+            first = true;
+            cur = ukey;
+          }
+        }
+        if (cur == ukey) {
+          found = static_cast<unsigned int>(s);
+          break;
+        }
+        s = (s + 1) & dmask;
       }
-      if (prev == ukey) {
-        found = static_cast<unsigned int>(s);
-        break;
-      }
-      s = (s + 1) & dmask;
+      if (found == 0xFFFFFFFFu) record(c.status, kStatusHashTableFull, 1);
     }
-    if (found == 0xFFFFFFFFu) record(c.status, kStatusHashTableFull, 1);
-    inv[p] = found;
+    const unsigned int fmask = __ballot_sync(0xffffffffu, first);
+    if (first) {
+      const int owner = owner_of(key, c.n);
+      const int idx = grouped_count(fmask, owner, cnt);
+      dval[found] = (static_cast<unsigned int>(owner) << kOwnerShift) | static_cast<unsigned int>(idx);
+      if (idx < cap)
+        reinterpret_cast<unsigned long long*>(c.arena[owner] + keys_off)[c.rank * cap + idx] = static_cast<unsigned long long>(key);
+    }
+    if (active) inv[p] = found;
   }
 }
 
@@ -196,61 +221,79 @@ emb_resolve_kernel(OfbEmbStore st, EmbCtx c, long long keys_off, long long cnt_o
   const unsigned long long* keys = reinterpret_cast<const unsigned long long*>(c.arena[c.rank] + keys_off);
   const long long tmask = st.tcap - 1;
   const int lane = threadIdx.x & 31;
-  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long w = warp; w < pre[c.n]; w += nwarps) {
-    int r;
-    long long idx;
-    locate(pre, c.n, w, &r, &idx);
-    const unsigned long long ukey = keys[r * cap + idx];
-    const long long key = static_cast<long long>(ukey);
-    int s_found = -1, new_row = -1;
-    if (lane == 0) {
-      long long s = static_cast<long long>(slot_hash(key)) & tmask;
+  const long long total = pre[c.n];
+  // one key per thread for the probe (32 independent probes per warp in flight), then the warp fills new rows together
+  for (long long base = blockIdx.x * (long long)blockDim.x; base < total; base += (long long)gridDim.x * blockDim.x) {
+    const long long w = base + threadIdx.x;
+    const bool active = w < total;
+    int s_found = -1;
+    bool is_new = false;
+    unsigned long long ukey = 0;
+    long long where = 0;
+    if (active) {
+      int r;
+      long long idx;
+      locate(pre, c.n, w, &r, &idx);
+      where = r * cap + idx;
+      ukey = keys[where];
+      long long s = static_cast<long long>(slot_hash(static_cast<long long>(ukey))) & tmask;
       for (long long probe = 0; probe <= tmask; ++probe) {
-        unsigned long long prev = st.tkeys[s];
-        if (prev == kEmptyKey && insert) prev = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
-        if (prev == kEmptyKey) {
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&st.tkeys[s]);
+        if (cur == kEmptyKey) {
           if (!insert) break;  // absent and not inserting: the row reads as zeros
-          const int row = atomicAdd(&st.counters[0], 1);
-          if (row < st.row_cap) {
-            st.trow[s] = row;
-            st.row_key[row] = ukey;
-            new_row = row;
-          } else {
-            st.trow[s] = -1;
-            record(c.status, kStatusHashTableFull, 2);
+          cur = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
+          if (cur == kEmptyKey) {
+            is_new = true;
+            cur = ukey;
           }
-          s_found = static_cast<int>(s);
-          break;
         }
-        if (prev == ukey) {
+        if (cur == ukey) {
           s_found = static_cast<int>(s);
           break;
         }
         s = (s + 1) & tmask;
       }
       if (s_found < 0 && insert) record(c.status, kStatusHashTableFull, 3);
-      if (s_found >= 0) {
-        if (atomicExch(&st.stamp[s_found], epoch) != epoch) st.uo_of[s_found] = atomicAdd(n_uo, 1);
-      }
-      slot_tmp[r * cap + idx] = s_found;
     }
-    new_row = __shfl_sync(0xffffffffu, new_row, 0);
-    if (new_row >= 0) {
-      const int table = static_cast<int>(ukey % static_cast<unsigned long long>(st.num_tables));
+    // rows for the new keys: one atomic per warp
+    const unsigned int nmask = __ballot_sync(0xffffffffu, is_new);
+    int new_row = -1;
+    if (is_new) {
+      new_row = grouped_count(nmask, 0, st.counters);
+      if (new_row < st.row_cap) {
+        st.trow[s_found] = new_row;
+        st.row_key[new_row] = ukey;
+      } else {
+        st.trow[s_found] = -1;
+        new_row = -1;
+        record(c.status, kStatusHashTableFull, 2);
+      }
+    }
+    // number the rows touched in this step (a key can arrive from several ranks: the first stamp wins)
+    const bool fresh = s_found >= 0 && atomicExch(&st.stamp[s_found], epoch) != epoch;
+    const unsigned int umask = __ballot_sync(0xffffffffu, fresh);
+    if (fresh) st.uo_of[s_found] = grouped_count(umask, 0, n_uo);
+    if (active) slot_tmp[where] = s_found;
+    // initialise the new rows, one row per warp pass
+    unsigned int todo = __ballot_sync(0xffffffffu, new_row >= 0);
+    while (todo) {
+      const int src = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const int row_i = __shfl_sync(0xffffffffu, new_row, src);
+      const unsigned long long k = __shfl_sync(0xffffffffu, ukey, src);
+      const int table = static_cast<int>(k % static_cast<unsigned long long>(st.num_tables));
       const int kind = st.init_kind[table];
       const float a = st.init_a[table], b = st.init_b[table];
-      float* row = st.rows + static_cast<long long>(new_row) * st.line;
+      float* row = st.rows + static_cast<long long>(row_i) * st.line;
       for (int col = lane; col < st.line; col += 32) {
         float v;
         if (col >= st.dim) {
           v = col < 2 * st.dim ? st.state_init : 0.f;  // first state vector (accumulator) only
         } else if (kind == 0) {  // uniform(a, b)
-          v = a + (b - a) * unit_uniform(ukey, col, st.seed);
+          v = a + (b - a) * unit_uniform(k, col, st.seed);
         } else if (kind == 1) {  // normal(mean a, std b), Box-Muller on a column pair
-          const float u1 = unit_uniform(ukey, 2 * (col >> 1), st.seed);
-          const float u2 = unit_uniform(ukey, 2 * (col >> 1) + 1, st.seed ^ 0x5851F42D4C957F2Dull);
+          const float u1 = unit_uniform(k, 2 * (col >> 1), st.seed);
+          const float u2 = unit_uniform(k, 2 * (col >> 1) + 1, st.seed ^ 0x5851F42D4C957F2Dull);
           const float rad = sqrtf(-2.f * __logf(u1));
           float sn, cs;
           __sincosf(6.283185307179586f * u2, &sn, &cs);
@@ -415,64 +458,64 @@ emb_grad_combine_kernel(EmbCtx c, long long cnt_off, long long grad_off, long lo
   }
 }
 
-// Row layout: [w (D) | state 1 (D) | state 2 (D)] as far as the optimizer needs.
+// One element of the row update. Row layout: [w (D) | state 1 (D) | state 2 (D)] as far as the optimizer needs.
+template <int KIND>
+__device__ __forceinline__ void update_one(float& x, float g, float& s1, float& s2, const OfbEmbUpdate& h) {
+  g *= h.scale;
+  if (h.l2 != 0.f) g += h.l2 * x;
+  if (KIND == 0) {  // sgd
+    x -= h.lr * (g + h.weight_decay * x);
+  } else if (KIND == 1) {  // momentum
+    s1 = h.momentum * s1 + g;
+    x -= h.lr * (s1 + h.weight_decay * x);
+  } else if (KIND == 2) {  // adam
+    s1 = h.beta1 * s1 + (1.f - h.beta1) * g;
+    s2 = h.beta2 * s2 + (1.f - h.beta2) * g * g;
+    x -= (h.lr / h.bias_corr1) * s1 / (sqrtf(s2) / sqrtf(h.bias_corr2) + h.eps) + h.lr * h.weight_decay * x;
+  } else if (KIND == 3) {  // adagrad
+    s1 += g * g;
+    x -= h.lr_eff * g / (sqrtf(s1) + h.eps) + h.lr * h.weight_decay * x;
+  } else {  // ftrl: s1 = accumulator, s2 = z
+    const float nacc = s1 + g * g;
+    const float sigma = (powf(nacc, -h.lr_power) - powf(s1, -h.lr_power)) / h.lr;
+    s2 += g - sigma * x;
+    s1 = nacc;
+    const float denom = (h.beta + powf(nacc, -h.lr_power)) / h.lr + h.lambda2;
+    x = fabsf(s2) > h.lambda1 ? -(s2 - copysignf(h.lambda1, s2)) / denom : 0.f;
+  }
+}
+
+// One warp per touched row, 16 bytes per lane and access: reads the summed gradient (and clears it, so the
+// accumulators stay zero between steps), the weights and the state, writes them back.
+template <int KIND>
 __global__ void __launch_bounds__(256)
-emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __restrict__ n_uo, float* gacc, OfbEmbUpdate h) {
+emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __restrict__ n_uo, float* __restrict__ gacc,
+                  OfbEmbUpdate h) {
+  constexpr int kStates = KIND == 0 ? 0 : (KIND == 1 || KIND == 3) ? 1 : 2;
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  const int D = st.dim;
+  const int vec = st.dim >> 2;
   const int total = *n_uo;
   for (long long u = warp; u < total; u += nwarps) {
     const int row = u_row[u];
-    float* g_row = gacc + u * D;
-    if (row < 0) {
-      for (int col = lane; col < D; col += 32) g_row[col] = 0.f;
-      continue;
-    }
-    float* w = st.rows + static_cast<long long>(row) * st.line;
-    for (int col = lane; col < D; col += 32) {
-      float g = g_row[col] * h.scale;
-      g_row[col] = 0.f;  // the accumulators stay zero between steps
-      float x = w[col];
-      if (h.l2 != 0.f) g += h.l2 * x;
-      switch (h.kind) {
-        case 0:  // sgd
-          x -= h.lr * (g + h.weight_decay * x);
-          break;
-        case 1: {  // momentum
-          const float m = h.momentum * w[D + col] + g;
-          w[D + col] = m;
-          x -= h.lr * (m + h.weight_decay * x);
-          break;
-        }
-        case 2: {  // adam
-          const float m = h.beta1 * w[D + col] + (1.f - h.beta1) * g;
-          const float v = h.beta2 * w[2 * D + col] + (1.f - h.beta2) * g * g;
-          w[D + col] = m;
-          w[2 * D + col] = v;
-          x -= (h.lr / h.bias_corr1) * m / (sqrtf(v) / sqrtf(h.bias_corr2) + h.eps) + h.lr * h.weight_decay * x;
-          break;
-        }
-        case 3: {  // adagrad
-          const float s = w[D + col] + g * g;
-          w[D + col] = s;
-          x -= h.lr_eff * g / (sqrtf(s) + h.eps) + h.lr * h.weight_decay * x;
-          break;
-        }
-        default: {  // ftrl
-          const float acc = w[D + col];
-          const float nacc = acc + g * g;
-          const float sigma = (powf(nacc, -h.lr_power) - powf(acc, -h.lr_power)) / h.lr;
-          const float z = w[2 * D + col] + g - sigma * x;
-          w[2 * D + col] = z;
-          w[D + col] = nacc;
-          const float denom = (h.beta + powf(nacc, -h.lr_power)) / h.lr + h.lambda2;
-          x = fabsf(z) > h.lambda1 ? -(z - copysignf(h.lambda1, z)) / denom : 0.f;
-          break;
-        }
-      }
-      w[col] = x;
+    float4* g4 = reinterpret_cast<float4*>(gacc + u * st.dim);
+    float4* w4 = reinterpret_cast<float4*>(st.rows + static_cast<long long>(row < 0 ? 0 : row) * st.line);
+    for (int q = lane; q < vec; q += 32) {
+      const float4 g = g4[q];
+      g4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < 0) continue;
+      float4 x = w4[q];
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      if (kStates >= 1) a = w4[vec + q];
+      if (kStates >= 2) b = w4[2 * vec + q];
+      update_one<KIND>(x.x, g.x, a.x, b.x, h);
+      update_one<KIND>(x.y, g.y, a.y, b.y, h);
+      update_one<KIND>(x.z, g.z, a.z, b.z, h);
+      update_one<KIND>(x.w, g.w, a.w, b.w, h);
+      w4[q] = x;
+      if (kStates >= 1) w4[vec + q] = a;
+      if (kStates >= 2) w4[2 * vec + q] = b;
     }
   }
 }
@@ -527,7 +570,7 @@ static int emb_grid(long long items, int per_block) {
 static int emb_check(const OfbCommCtx* ctx, const OfbEmbStore* st, const OfbEmbShuffle* sh, long long n) {
   if (!ctx || !st || !sh) return fail("embedding: null argument");
   if (ctx->n < 1 || ctx->n > kMaxPeers) return fail("embedding: 1..8 ranks");
-  if (st->dim % 4 || st->line < st->dim) return fail("embedding: dim must be a multiple of 4 and fit the row");
+  if (st->dim % 4 || st->line < st->dim || st->line % 4) return fail("embedding: dim and row length must be multiples of 4, dim <= row length");
   if (n > sh->cap || sh->cap > (1ll << kOwnerShift)) return fail("embedding: more ids than the exchange buffers hold");
   if (sh->dcap & (sh->dcap - 1) || st->tcap & (st->tcap - 1)) return fail("embedding: table sizes must be powers of two");
   if (sh->dcap < 2 * n || sh->dcap > (1ll << 32) - 2) return fail("embedding: dedupe table too small for this many ids");
@@ -550,7 +593,7 @@ OFB_API int ofb_emb_forward(const OfbCommCtx* cctx, const OfbEmbStore* st, const
                                                             sh->dcap - 1, sh->cnt, sh->inv, c, sh->keys_off, sh->cap);
   emb_publish_kernel<<<emb_grid(n, 256), 256, 0, stream>>>(n, sh->dval, sh->cnt, sh->inv, c, sh->cnt_off, epoch);
   const long long worst = sh->cap * c.n;
-  emb_resolve_kernel<<<emb_grid(worst, 8), 256, 0, stream>>>(*st, c, sh->keys_off, sh->cnt_off, sh->cap, sh->slot_tmp, sh->n_uo, epoch,
+  emb_resolve_kernel<<<emb_grid(worst, 256), 256, 0, stream>>>(*st, c, sh->keys_off, sh->cnt_off, sh->cap, sh->slot_tmp, sh->n_uo, epoch,
                                                             insert);
   if (out_half)
     emb_serve_kernel<true><<<emb_grid(worst, 8), 256, 0, stream>>>(*st, c, sh->cnt_off, sh->emb_off, sh->cap, sh->slot_tmp, sh->rowidx,
@@ -585,7 +628,14 @@ OFB_API int ofb_emb_backward(const OfbCommCtx* cctx, const OfbEmbStore* st, cons
     emb_grad_combine_kernel<false><<<emb_grid(worst, 8), 256, 0, stream>>>(c, sh->cnt_off, sh->grad_off, sh->cap, st->dim, sh->uoidx,
                                                                            sh->gacc, epoch);
   }
-  emb_update_kernel<<<emb_grid(worst, 8), 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd);
+  const int ug = emb_grid(worst, 8);
+  switch (upd->kind) {
+    case 0: emb_update_kernel<0><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+    case 1: emb_update_kernel<1><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+    case 2: emb_update_kernel<2><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+    case 3: emb_update_kernel<3><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+    default: emb_update_kernel<4><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+  }
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

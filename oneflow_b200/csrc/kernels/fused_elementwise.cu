@@ -180,6 +180,33 @@ static inline int ew_grid(long long work_items, int threads) {
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
+// Binary cross entropy on logits, forward and backward in one pass (the loss head of click-through models;
+// reference: binary_cross_entropy_with_logits(_reduce_mean) kernels). Row r reads logits[r * ld], adds its loss to
+// *loss_sum (scaled) and writes grad_scale * (sigmoid(x) - y) to dlogits[r * ld], zeros to the ld - 1 columns beside it.
+__global__ void __launch_bounds__(256)
+bce_logits_kernel(const __nv_bfloat16* __restrict__ logits, int ld, const float* __restrict__ labels,
+                  __nv_bfloat16* __restrict__ dlogits, float* loss_sum, long long rows, float loss_scale, float grad_scale) {
+  float local = 0.f;
+  for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+    const float x = __bfloat162float(logits[r * ld]);
+    const float y = labels[r];
+    local += fmaxf(x, 0.f) - x * y + log1pf(__expf(-fabsf(x)));
+    const float sig = 1.f / (1.f + __expf(-x));
+    __nv_bfloat16* g = dlogits + r * ld;
+    g[0] = __float2bfloat16(grad_scale * (sig - y));
+    for (int c = 1; c < ld; ++c) g[c] = __float2bfloat16(0.f);
+  }
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += part[w];
+    atomicAdd(loss_sum, t * loss_scale);
+  }
+}
+
 }  // namespace ofb
 
 using namespace ofb;
@@ -247,6 +274,17 @@ OFB_API int ofb_column_sum(const void* x, float* out, int rows, int cols, void* 
   const int rows_per_cta = (rows + slabs - 1) / slabs;
   column_sum_kernel<<<dim3(panels, slabs), dim3(32, 8), 0, (cudaStream_t)stream>>>((const bf16*)x, out, rows, cols,
                                                                                  rows_per_cta);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// loss_sum must be zeroed by the caller (it accumulates, so micro-batches can share it).
+OFB_API int ofb_bce_logits(const void* logits, int ld, const float* labels, void* dlogits, float* loss_sum, long long rows,
+                           float loss_scale, float grad_scale, void* stream) {
+  if (rows == 0) return 0;
+  if (ld < 1) return fail("bce_logits: bad leading dimension");
+  bce_logits_kernel<<<ew_grid(rows, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)logits, ld, labels, (bf16*)dlogits, loss_sum,
+                                                                          rows, loss_scale, grad_scale);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -27,7 +27,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     OFB_CUDA_OK(cudaGetDevice(&dev));
     OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const int tiles = ((shp.M + 127) / 128) * ((shp.N + BN - 1) / BN);
+  const int tiles = ((shp.M + 127) / 128) * ((shp.N + BN - 1) / BN) * (shp.splits > 1 ? shp.splits : 1);
   int grid = tiles < sm_count ? tiles : sm_count;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, shp, ep, status);
@@ -94,7 +94,7 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
     } else {
       if (get_tensor_map(&tmB, a->B, 2, 2, a->N, a->K, 0, (uint64_t)a->ldb * 2, 0, 64, 64, 0, 3)) return -1;
     }
-    GemmShape shp2{a->M, a->N, a->K};
+    GemmShape shp2{a->M, a->N, a->K, 1};
     int* st2 = device_status_ptr();
     if (!a_mn && !b_mn) return launch_gemm_2cta<0, 0>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
     if (!a_mn && b_mn) return launch_gemm_2cta<0, 1>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
@@ -116,7 +116,35 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
   } else {
     if (get_tensor_map(&tmB, a->B, 2, 2, a->N, a->K, 0, (uint64_t)a->ldb * 2, 0, 64, 64, 0, 3)) return -1;
   }
-  GemmShape shp{a->M, a->N, a->K};
+  GemmShape shp{a->M, a->N, a->K, 1};
+  // Split-K: few output tiles but a long K (weight gradients: [out, in] = dY^T X over all tokens) would leave most
+  // SMs idle. The K range is cut so that about one work unit per SM exists; partial sums are added atomically into
+  // the fp32 output, which is cleared first unless the call accumulates anyway.
+  {
+    static int sm_count = 0, allow = -1;
+    if (sm_count == 0) {
+      int dev = 0;
+      OFB_CUDA_OK(cudaGetDevice(&dev));
+      OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (allow < 0) {
+      const char* e = std::getenv("OFB_GEMM_SPLITK");
+      allow = e ? std::atoi(e) : 1;
+    }
+    const bool plain = !ep.bias && !ep.aux_in && !ep.aux_out && !ep.residual && ep.act == 0 && ep.out_fp32;
+    const int tiles = ((a->M + 127) / 128) * ((a->N + bn - 1) / bn);
+    const int kblocks = (a->K + 63) / 64;
+    int cap = a->max_ctas > 0 && a->max_ctas < sm_count ? a->max_ctas : sm_count;
+    if (allow && plain && tiles * 2 <= cap && kblocks >= 16) {
+      int splits = cap / tiles;
+      if (splits > kblocks / 4) splits = kblocks / 4;
+      if (splits > 1) {
+        shp.splits = splits;
+        if (!ep.accumulate)
+          OFB_CUDA_OK(cudaMemset2DAsync(ep.C, static_cast<size_t>(ep.ldc) * 4, 0, static_cast<size_t>(a->N) * 4, a->M, stream));
+      }
+    }
+  }
   int* status = device_status_ptr();
 #define OFB_GEMM_CASE(BN_, AM_, BM_) \
   if (bn == BN_ && a_mn == AM_ && b_mn == BM_) return launch_gemm<BN_, AM_, BM_>(tmA, tmB, shp, ep, status, a->max_ctas, stream);
@@ -150,7 +178,6 @@ OFB_API int ofb_gemm_bf16(const OfbGemmArgs* a, void* stream) {
   ep.act = a->act;
   ep.out_fp32 = a->out_fp32;
   ep.accumulate = a->accumulate;
-  ep.n_peers = 0;
   return gemm_dispatch(a, ep, reinterpret_cast<cudaStream_t>(stream));
 }
 

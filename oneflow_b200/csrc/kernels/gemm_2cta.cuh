@@ -21,7 +21,8 @@ struct Gemm2Cfg {
   static constexpr int STAGES = 6;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BNH * BK * 2;
-  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+  static constexpr int EPI_BYTES = 4 * 32 * 128;  // staging tile of each epilogue warp (gemm_epilogue.cuh)
+  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 256 + 1024;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -92,7 +93,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Gemm2Cfg::EPI_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -206,6 +208,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
+    const uint32_t stage = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair; t < total_tiles; t += n_pairs) {
@@ -214,75 +217,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM, n0 = tn * BN;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < shp.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int col = col0 + g * 8;
-          if (!row_ok || col >= shp.N) continue;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * ep.alpha;
-          if (ep.bias) {
-            uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col));
-            const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(bw[j]); v[2 * j] += f.x; v[2 * j + 1] += f.y; }
-          }
-          if (ep.aux_out) {
-            *reinterpret_cast<uint4*>(ep.aux_out + static_cast<long long>(row) * ep.ld_aux + col) =
-                make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-          }
-          if (ep.act != kActNone && !ep.aux_in) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.act);
-          }
-          if (ep.aux_in) {
-            uint4 hh = __ldg(reinterpret_cast<const uint4*>(ep.aux_in + static_cast<long long>(row) * ep.ld_aux + col));
-            const uint32_t hw[4] = {hh.x, hh.y, hh.z, hh.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(hw[j]);
-              v[2 * j] *= apply_act_grad(f.x, ep.act);
-              v[2 * j + 1] *= apply_act_grad(f.y, ep.act);
-            }
-          }
-          if (ep.residual) {
-            uint4 rr = __ldg(reinterpret_cast<const uint4*>(ep.residual + static_cast<long long>(row) * ep.ldr + col));
-            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(rw[j]); v[2 * j] += f.x; v[2 * j + 1] += f.y; }
-          }
-          if (ep.out_fp32) {
-            float* dst = reinterpret_cast<float*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
-            float4 lo = make_float4(v[0], v[1], v[2], v[3]), hi = make_float4(v[4], v[5], v[6], v[7]);
-            if (ep.accumulate) {
-              float4 a = *reinterpret_cast<float4*>(dst), b = *reinterpret_cast<float4*>(dst + 4);
-              lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-              hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
-            }
-            *reinterpret_cast<float4*>(dst) = lo;
-            *reinterpret_cast<float4*>(dst + 4) = hi;
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
-            if (ep.accumulate) {
-              uint4 cc = *reinterpret_cast<uint4*>(dst);
-              const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(cw[j]); v[2 * j] += f.x; v[2 * j + 1] += f.y; }
-            }
-            *reinterpret_cast<uint4*>(dst) =
-                make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-          }
-        }
-      }
+      gemm_epilogue_warp<BN>(ep, shp, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, m0 + quad * 32, n0, lane, stage,
+                             false);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));   // the leader owns the accumulator hand-off

@@ -40,19 +40,16 @@ struct GemmEpilogue {
   int act;                        // GemmAct applied to (alpha*acc + bias)
   int out_fp32;                   // C is fp32
   int accumulate;                 // C += result
-  // Fused collective (see comm/fused_gemm_collective.cu): when n_peers > 0 the tile is
-  // stored to peer_out[owner] instead of C, and a per-tile flag is published.
-  int n_peers;
-  int my_rank;
-  int rows_per_rank;              // reduce-scatter row ownership (M / n_peers)
-  void* peer_out[8];              // staging buffer of each rank: [n_peers, rows_per_rank, ldc]
-  unsigned int* peer_flags[8];    // flag array of each rank: [n_peers, tiles]
-  unsigned int flag_value;        // value published for this launch (monotonic epoch)
 };
 
 struct GemmShape {
   int M, N, K;
+  int splits;  // > 1: the K range is cut into this many pieces whose partial sums are added atomically into an fp32 C
 };
+
+}  // namespace ofb
+#include "gemm_epilogue.cuh"
+namespace ofb {
 
 template <int BN>
 struct GemmCfg {
@@ -62,7 +59,8 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
-  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 256 /*barriers*/ + 1024 /*alignment*/;
+  static constexpr int EPI_BYTES = 4 * 32 * 128;  // staging tile of each epilogue warp (gemm_epilogue.cuh)
+  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
   static constexpr int THREADS = 192;
 };
 
@@ -109,7 +107,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -146,6 +145,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int tiles_n = (shp.N + BN - 1) / BN;
   const int total_tiles = tiles_m * tiles_n;
   const int kblocks = (shp.K + BK - 1) / BK;
+  // split-K: unit u = (tile u % total_tiles, K piece u / total_tiles); no piece is empty
+  const int kb_per = (kblocks + max(shp.splits, 1) - 1) / max(shp.splits, 1);
+  const int splits = (kblocks + kb_per - 1) / kb_per;
+  const int total_units = total_tiles * splits;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -153,11 +156,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tm, tn;
-        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        tile_coords(u % total_tiles, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kb0 = (u / total_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[stage], A_BYTES + B_BYTES);
           uint8_t* a_dst = sA + stage * A_BYTES;
@@ -187,11 +191,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kb0 = (u / total_tiles) * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
@@ -202,7 +207,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                      : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, BK * 128, 1024)
                                      : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, IDESC, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(d_tmem, da, db, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -216,124 +221,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const uint32_t stage = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
       int tm, tn;
-      tile_coords(t, tiles_m, tiles_n, tm, tn);
-      const int m0 = tm * BM, n0 = tn * BN;
+      tile_coords(u % total_tiles, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < shp.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();  // tcgen05.ld is warp-collective: re-converge after the predicated stores
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {  // groups of 8 columns = one 16-byte bf16 vector
-          const int col = col0 + g * 8;
-          if (!row_ok || col >= shp.N) continue;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * ep.alpha;
-          if (ep.bias) {
-            uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col));
-            const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(bw[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
-            }
-          }
-          if (ep.aux_out) {
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(ep.aux_out + static_cast<long long>(row) * ep.ld_aux + col) = o;
-          }
-          if (ep.act != kActNone && !ep.aux_in) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.act);
-          }
-          if (ep.aux_in) {
-            uint4 hh = __ldg(reinterpret_cast<const uint4*>(ep.aux_in + static_cast<long long>(row) * ep.ld_aux + col));
-            const uint32_t hw[4] = {hh.x, hh.y, hh.z, hh.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(hw[j]);
-              v[2 * j] *= apply_act_grad(f.x, ep.act);
-              v[2 * j + 1] *= apply_act_grad(f.y, ep.act);
-            }
-          }
-          if (ep.residual) {
-            uint4 rr = __ldg(reinterpret_cast<const uint4*>(ep.residual + static_cast<long long>(row) * ep.ldr + col));
-            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(rw[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
-            }
-          }
-          if (ep.out_fp32) {
-            float* dst = reinterpret_cast<float*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
-            float4 lo = make_float4(v[0], v[1], v[2], v[3]), hi = make_float4(v[4], v[5], v[6], v[7]);
-            if (ep.accumulate) {
-              float4 a = *reinterpret_cast<float4*>(dst), b = *reinterpret_cast<float4*>(dst + 4);
-              lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-              hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
-            }
-            *reinterpret_cast<float4*>(dst) = lo;
-            *reinterpret_cast<float4*>(dst + 4) = hi;
-          } else {
-            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(ep.C);
-            long long off = static_cast<long long>(row) * ep.ldc + col;
-            if (ep.n_peers > 0) {
-              // Reduce-scatter staging: rows [o*rows_per_rank, (o+1)*rows_per_rank) belong to rank o;
-              // this rank's partial goes to slot `my_rank` of the owner's staging buffer.
-              const int owner = row / ep.rows_per_rank;
-              const long long lrow = row - owner * ep.rows_per_rank;
-              base = reinterpret_cast<__nv_bfloat16*>(ep.peer_out[owner]);
-              off = (static_cast<long long>(ep.my_rank) * ep.rows_per_rank + lrow) * ep.ldc + col;
-            }
-            __nv_bfloat16* dst = base + off;
-            if (ep.accumulate) {
-              uint4 cc = *reinterpret_cast<uint4*>(dst);
-              const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(cw[j]);
-                v[2 * j] += f.x;
-                v[2 * j + 1] += f.y;
-              }
-            }
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(dst) = o;
-          }
-        }
-      }
+      gemm_epilogue_warp<BN>(ep, shp, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, tm * BM + quad * 32, tn * BN,
+                             lane, stage, splits > 1);
       tc_fence_before();
-      if (ep.n_peers > 0) {
-        // Publish "tile t of rank my_rank has landed" to the owner(s) of its rows. A 128-row tile
-        // never straddles two owners because rows_per_rank is a multiple of 128 (checked on the host).
-        __threadfence_system();
-      }
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&tempty[acc]);
-        if (ep.n_peers > 0) {
-          const int owner = min(m0 / ep.rows_per_rank, ep.n_peers - 1);
-          // four epilogue warps each add 1; the consumer waits for 4 * (number of launches so far)
-          atomicAdd_system(ep.peer_flags[owner] + static_cast<long long>(ep.my_rank) * total_tiles + t, 1u);
-        }
-      }
+      if (lane == 0) mbar_arrive(&tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }

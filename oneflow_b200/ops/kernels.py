@@ -558,3 +558,60 @@ def fmha_bwd(q, k, v, o, d_o, lse, causal=False, scale=None, kv_len=None, dqkv=N
           "fmha_bwd")
     _count(4)
     return dq, dk, dv
+
+
+def bce_logits(logits, labels, loss_scale=1.0, grad_scale=1.0, loss_sum=None):
+    """Binary cross entropy on ``logits[:, 0]`` against fp32 ``labels``: returns (loss_sum [1] fp32, dlogits like
+    logits with the gradient in column 0 and zeros elsewhere). ``loss_sum`` accumulates when passed in."""
+    rows, ld = logits.shape
+    if not logits.is_cuda:
+        x = logits[:, 0].float()
+        loss = (torch.clamp(x, min=0) - x * labels + torch.log1p(torch.exp(-x.abs()))).sum() * loss_scale
+        d = torch.zeros_like(logits)
+        d[:, 0] = (grad_scale * (torch.sigmoid(x) - labels)).to(logits.dtype)
+        out = loss.reshape(1) if loss_sum is None else loss_sum.add_(loss)
+        return out, d
+    _need_bf16(logits)
+    if loss_sum is None:
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=logits.device)
+    d = torch.empty_like(logits)
+    check(_lib().ofb_bce_logits(ptr(logits), c_int(ld), ptr(labels), ptr(d), ptr(loss_sum), c_longlong(rows),
+                                c_float(loss_scale), c_float(grad_scale), stream_ptr()), "bce_logits")
+    _count()
+    return loss_sum, d
+
+
+def interaction_fwd(dense, sparse, self_interaction=False, out_dim=None):
+    """[dense | lower triangle of X X^T | zero pad] with X = [dense; sparse] per sample (no autograd)."""
+    B, D = dense.shape
+    T = sparse.shape[1]
+    F = T + 1
+    npairs = F * (F + 1) // 2 if self_interaction else F * (F - 1) // 2
+    out_dim = out_dim or (D + npairs + 7) // 8 * 8
+    if not dense.is_cuda:
+        from .interaction import dot_feature_interaction_reference
+        return dot_feature_interaction_reference([dense, sparse], dense, self_interaction, out_dim - D - npairs)
+    out = torch.empty((B, out_dim), dtype=dense.dtype, device=dense.device)
+    check(_lib().ofb_interaction_fwd(ptr(dense), ptr(sparse), ptr(out), c_longlong(B), c_int(T), c_int(D), c_int(int(self_interaction)),
+                                     c_int(out_dim), stream_ptr()), "interaction_fwd")
+    _count()
+    return out
+
+
+def interaction_bwd(dense, sparse, dout, self_interaction=False):
+    """Gradients of interaction_fwd wrt (dense, sparse)."""
+    B, D = dense.shape
+    T = sparse.shape[1]
+    if not dense.is_cuda:
+        from .interaction import dot_feature_interaction_reference
+        d32, s32 = dense.float().requires_grad_(), sparse.float().requires_grad_()
+        F = T + 1
+        npairs = F * (F + 1) // 2 if self_interaction else F * (F - 1) // 2
+        ref = dot_feature_interaction_reference([d32, s32], d32, self_interaction, dout.shape[1] - D - npairs)
+        ref.backward(dout.float())
+        return d32.grad.to(dense.dtype), s32.grad.to(sparse.dtype)
+    dd, ds = torch.empty_like(dense), torch.empty_like(sparse)
+    check(_lib().ofb_interaction_bwd(ptr(dense), ptr(sparse), ptr(dout.contiguous()), ptr(dd), ptr(ds), c_longlong(B), c_int(T), c_int(D),
+                                     c_int(int(self_interaction)), c_int(dout.shape[1]), stream_ptr()), "interaction_bwd")
+    _count()
+    return dd, ds
