@@ -15,10 +15,7 @@ class _Interaction(torch.autograd.Function):
     def forward(ctx, dense, sparse, self_interaction, out_dim):
         B, D = dense.shape
         T = sparse.shape[1]
-        out = torch.empty((B, out_dim), dtype=dense.dtype, device=dense.device)
-        check(_native.kernels().ofb_interaction_fwd(ptr(dense), ptr(sparse), ptr(out), c_longlong(B), c_int(T), c_int(D),
-                                                    c_int(int(self_interaction)), c_int(out_dim), stream_ptr()), "interaction_fwd")
-        _k._count()
+        out = _k.interaction_fwd(dense, sparse, self_interaction, out_dim)
         ctx.save_for_backward(dense, sparse)
         ctx.args = (self_interaction, out_dim)
         return out
@@ -29,11 +26,7 @@ class _Interaction(torch.autograd.Function):
         self_interaction, out_dim = ctx.args
         B, D = dense.shape
         T = sparse.shape[1]
-        dd, ds = torch.empty_like(dense), torch.empty_like(sparse)
-        check(_native.kernels().ofb_interaction_bwd(ptr(dense), ptr(sparse), ptr(dout.contiguous()), ptr(dd), ptr(ds),
-                                                    c_longlong(B), c_int(T), c_int(D), c_int(int(self_interaction)),
-                                                    c_int(out_dim), stream_ptr()), "interaction_bwd")
-        _k._count()
+        dd, ds = _k.interaction_bwd(dense, sparse, dout, self_interaction)
         return dd, ds, None, None
 
 

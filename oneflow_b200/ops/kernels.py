@@ -581,6 +581,13 @@ def bce_logits(logits, labels, loss_scale=1.0, grad_scale=1.0, loss_sum=None):
     return loss_sum, d
 
 
+def _interaction_on_tensor_cores(D, T, self_interaction, out_dim):
+    """The tcgen05 kernels cover the DLRM shape class: dim 128, up to 31 sparse features, strict lower triangle."""
+    import os
+    return (D == 128 and 1 <= T <= 31 and not self_interaction and out_dim % 8 == 0 and out_dim - D <= 512
+            and os.environ.get("OFB_INTERACTION_TC", "1") != "0")
+
+
 def interaction_fwd(dense, sparse, self_interaction=False, out_dim=None):
     """[dense | lower triangle of X X^T | zero pad] with X = [dense; sparse] per sample (no autograd)."""
     B, D = dense.shape
@@ -592,6 +599,11 @@ def interaction_fwd(dense, sparse, self_interaction=False, out_dim=None):
         from .interaction import dot_feature_interaction_reference
         return dot_feature_interaction_reference([dense, sparse], dense, self_interaction, out_dim - D - npairs)
     out = torch.empty((B, out_dim), dtype=dense.dtype, device=dense.device)
+    if _interaction_on_tensor_cores(D, T, self_interaction, out_dim):
+        check(_lib().ofb_interaction_tc_fwd(ptr(dense), ptr(sparse), ptr(out), c_longlong(B), c_int(T), c_int(D), c_int(out_dim),
+                                            stream_ptr()), "interaction_tc_fwd")
+        _count()
+        return out
     check(_lib().ofb_interaction_fwd(ptr(dense), ptr(sparse), ptr(out), c_longlong(B), c_int(T), c_int(D), c_int(int(self_interaction)),
                                      c_int(out_dim), stream_ptr()), "interaction_fwd")
     _count()
@@ -611,6 +623,11 @@ def interaction_bwd(dense, sparse, dout, self_interaction=False):
         ref.backward(dout.float())
         return d32.grad.to(dense.dtype), s32.grad.to(sparse.dtype)
     dd, ds = torch.empty_like(dense), torch.empty_like(sparse)
+    if _interaction_on_tensor_cores(D, T, self_interaction, dout.shape[1]):
+        check(_lib().ofb_interaction_tc_bwd(ptr(dense), ptr(sparse), ptr(dout.contiguous()), ptr(dd), ptr(ds), c_longlong(B), c_int(T),
+                                            c_int(D), c_int(dout.shape[1]), stream_ptr()), "interaction_tc_bwd")
+        _count()
+        return dd, ds
     check(_lib().ofb_interaction_bwd(ptr(dense), ptr(sparse), ptr(dout.contiguous()), ptr(dd), ptr(ds), c_longlong(B), c_int(T), c_int(D),
                                      c_int(int(self_interaction)), c_int(dout.shape[1]), stream_ptr()), "interaction_bwd")
     _count()
