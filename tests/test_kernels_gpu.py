@@ -280,3 +280,28 @@ def test_dot_feature_interaction(self_inter, T, D):
     ref.backward(g.float())
     torch.testing.assert_close(dense.grad.float(), d32.grad, atol=0.15, rtol=0.03)
     torch.testing.assert_close(sparse.grad.float(), s32.grad, atol=0.15, rtol=0.03)
+
+
+@pytest.mark.parametrize("N,H,W,Cin,Cout,R", [(4, 56, 56, 64, 64, 3), (3, 28, 28, 128, 128, 3), (5, 14, 14, 256, 256, 3),
+                                              (6, 7, 7, 512, 512, 3), (2, 19, 13, 64, 128, 3), (2, 16, 16, 64, 64, 5)])
+def test_conv_implicit_gemm(N, H, W, Cin, Cout, R):
+    from oneflow_b200.ops import conv as C
+    torch.manual_seed(0)
+    x = torch.randn(N, H, W, Cin, device="cuda").bfloat16()
+    w = (torch.randn(Cout, R, R, Cin, device="cuda") / math.sqrt(R * R * Cin)).bfloat16()
+    dy = torch.randn(N, H, W, Cout, device="cuda").bfloat16()
+    x32 = x.float().requires_grad_()
+    w32 = w.float().requires_grad_()
+    ref = C._ref_conv(x32, w32)
+    ref.backward(dy.float())
+    y = C.conv_fprop(x, w)
+    torch.testing.assert_close(y.float(), ref.detach(), atol=3e-2, rtol=2e-2)
+    dx = C.conv_dgrad(dy, w)
+    torch.testing.assert_close(dx.float(), x32.grad, atol=3e-2, rtol=2e-2)
+    dw = C.conv_wgrad(x, dy, (R, R))
+    scale = w32.grad.abs().max().item()
+    assert (dw - w32.grad).abs().max().item() <= 1e-2 * scale + 1e-3
+    dw2 = C.conv_wgrad(x, dy, (R, R), out=dw.clone(), accumulate=True)
+    assert (dw2 - 2 * w32.grad).abs().max().item() <= 2e-2 * scale + 2e-3
+    torch.cuda.synchronize()
+    assert _native.read_status() == (0, 0)
