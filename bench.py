@@ -34,7 +34,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "bert-large", "dlrm", "dlrm-tiny"])
+    ap.add_argument("--workload", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "bert-large", "dlrm", "dlrm-tiny", "resnet50", "resnet-tiny"])
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0 = choose from --gpus)")
@@ -107,6 +107,96 @@ def reference_arm(args):
     if os.path.isdir(os.path.join(ref_dir, "oneflow")):
         line["unavailable"] = "baseline/_ref holds no runnable build of the reference for sm_100"
     print(json.dumps(line))
+    return 0
+
+
+def run_resnet(args, world, rank, local_rank, device):
+    """ResNet-50 data parallel, 256 images of 224 x 224 x 3 (bf16, channels last) per GPU, SGD momentum: images/s."""
+    import torch
+    import torch.distributed as dist
+
+    from oneflow_b200.models import resnet as rn
+    from oneflow_b200.ops import _native
+    from oneflow_b200.ops import kernels as K
+
+    cfg = rn.RESNET50 if args.workload == "resnet50" else rn.tiny_config(image_size=64)
+    per_gpu = 256 if args.workload == "resnet50" else 32
+    trainer = rn.ResNetTrainer(cfg, device, lr=0.1, momentum=0.9, weight_decay=1e-4, seed=0)
+    pool = 2
+    g = torch.Generator().manual_seed(77 + rank)
+    host = [(torch.randn(per_gpu, cfg.image_size, cfg.image_size, 3, generator=g).bfloat16().pin_memory(),
+             torch.randint(0, cfg.num_classes, (per_gpu,), generator=g).pin_memory()) for _ in range(pool)]
+    dev = [tuple(t.to(device, non_blocking=True) for t in b) for b in host]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    k = 0
+    for _ in range(args.warmup):
+        loss = trainer.train_step(*dev[k % pool])
+        k += 1
+    barrier()
+    if _native.read_status() != (0, 0):
+        raise SystemExit(f"a kernel reported a failure during warm-up: {_native.read_status(False)}")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = K.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = trainer.train_step(*dev[k % pool])
+        k += 1
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = K.launch_count - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    final_loss = float(loss.item())
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    wall0 = time.perf_counter()
+    h2d = d2h = 0
+    for _ in range(args.steps):
+        batch = tuple(t.to(device, non_blocking=True) for t in host[k % pool])
+        k += 1
+        loss = trainer.train_step(*batch)
+        host_loss = loss.to("cpu")
+        h2d = sum(t.numel() * t.element_size() for t in batch)
+        d2h = host_loss.numel() * host_loss.element_size()
+    t1.record()
+    barrier()
+    e2e_ms = max(t0.elapsed_time(t1), (time.perf_counter() - wall0) * 1e3)
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+    status = _native.read_status()
+    if rank == 0:
+        images = per_gpu * world
+        line = {
+            "metric": f"{args.workload}_train_images_per_s", "value": images * args.steps / (ms / 1e3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic images ~N(0,1) bf16 channels-last, labels uniform in [0,1000); random-init weights",
+            "config": {"model": args.workload, "batch_per_gpu": per_gpu, "global_batch": images, "image": cfg.image_size,
+                       "parallelism": f"dp{world}", "optimizer": "SGD momentum 0.9, fp32 master weights",
+                       "l2": "activations of a 256-image batch (several GB) far exceed the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": images * args.steps / (e2e_ms / 1e3), "unit": "images/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "final_loss": final_loss,
+            "model_tflops_per_gpu": cfg.flops_per_image() * per_gpu * args.steps / (ms / 1e3) / 1e12,
+            "kernel_status": list(status),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 
@@ -225,6 +315,8 @@ def main():
 
     if args.workload.startswith("dlrm"):
         return run_dlrm(args, world, rank, local_rank, device)
+    if args.workload.startswith("resnet"):
+        return run_resnet(args, world, rank, local_rank, device)
 
     from oneflow_b200.models import gpt as gpt_mod
     from oneflow_b200.ops import _native

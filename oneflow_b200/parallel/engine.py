@@ -114,6 +114,45 @@ class FlatAdamW:
         self.set_lr(sd["lr"])
 
 
+class FlatSGD:
+    """SGD with momentum over a ParamStore: fp32 master weights and momentum in flat buffers, the bf16 model copy
+    written by the same kernel; weight decay (L2 form, as torch.optim.SGD) only on the store's decayed prefix.
+    Gradients must already be reduced over the data-parallel ranks."""
+
+    def __init__(self, store, lr=0.1, momentum=0.9, weight_decay=1e-4, nesterov=False):
+        self.store, self.lr, self.momentum, self.wd, self.nesterov = store, lr, momentum, weight_decay, nesterov
+        dev = store.flat.device
+        self.master = store.flat.float()
+        self.m = torch.zeros(store.total, dtype=torch.float32, device=dev) if momentum else None
+        self.lr_t = torch.full((1,), lr, dtype=torch.float32, device=dev)
+        self.step_count = 0
+
+    def set_lr(self, lr):
+        self.lr = lr
+        self.lr_t.fill_(lr)
+
+    def step(self, grad_scale=1.0):
+        st = self.store
+        self.step_count += 1
+        d = st.decay_end
+        for lo, hi, wd in ((0, d, self.wd), (d, st.total, 0.0)):
+            if hi <= lo:
+                continue
+            K.multi_tensor_sgd([st.grad[lo:hi]], [self.master[lo:hi]], [st.flat[lo:hi]], [self.m[lo:hi]] if self.m is not None else None,
+                               lr=self.lr, momentum=self.momentum, nesterov=self.nesterov, l2=wd, scale=grad_scale,
+                               lr_tensor=self.lr_t)
+
+    def state_dict(self):
+        return {"step": self.step_count, "master": self.master, "m": self.m, "lr": self.lr}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        self.master.copy_(sd["master"])
+        if self.m is not None and sd.get("m") is not None:
+            self.m.copy_(sd["m"])
+        self.set_lr(sd["lr"])
+
+
 class PipelineP2P:
     """Activations / activation-gradients between neighbouring pipeline stages over NCCL (or gloo)
     send/recv. A send and the matching receive of the opposite direction are posted as one batch so the
