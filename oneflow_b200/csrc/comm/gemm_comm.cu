@@ -76,7 +76,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -218,58 +219,21 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < shp.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int col = col0 + g * 8;
-          if (!row_ok || col >= shp.N) continue;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * ep.alpha;
-          if (MODE == MODE_RS) {
-            const long long lrow = row - owner * cp.rows_per_rank;
-            __nv_bfloat16* dst = cp.stage[owner] +
-                                 ((static_cast<long long>(parity) * cp.n + cp.rank) * cp.rows_per_rank + lrow) * shp.N + col;
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                        pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-          } else {
-            if (ep.bias) {
-              uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col));
-              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(bw[j]); v[2 * j] += f.x; v[2 * j + 1] += f.y; }
-            }
-            if (ep.aux_out) {
-              *reinterpret_cast<uint4*>(ep.aux_out + static_cast<long long>(row) * ep.ld_aux + col) =
-                  make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-            }
-            if (ep.act != kActNone && !ep.aux_in) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.act);
-            }
-            if (ep.aux_in) {
-              uint4 hh = __ldg(reinterpret_cast<const uint4*>(ep.aux_in + static_cast<long long>(row) * ep.ld_aux + col));
-              const uint32_t hw[4] = {hh.x, hh.y, hh.z, hh.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(hw[j]);
-                v[2 * j] *= apply_act_grad(f.x, ep.act);
-                v[2 * j + 1] *= apply_act_grad(f.y, ep.act);
-              }
-            }
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                        pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-          }
-        }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      const uint32_t stage_sm = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
+      if (MODE == MODE_RS) {
+        // The raw partial tile goes to the slab this rank owns in the staging buffer of the rows' owner (plain P2P
+        // stores over NVLink, full 64-byte row segments); bias and residual are added once, after the reduction.
+        GemmEpilogue pe;
+        pe.C = cp.stage[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.rows_per_rank * shp.N;
+        pe.ldc = shp.N;
+        pe.bias = nullptr; pe.residual = nullptr; pe.aux_in = nullptr; pe.aux_out = nullptr;
+        pe.ldr = 0; pe.ld_aux = 0;
+        pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+        GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
+        gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false);
+      } else {
+        gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
       }
       tc_fence_before();
       if (MODE == MODE_RS) __threadfence_system();
@@ -368,31 +332,58 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ltm = lt / tiles_n, ltn = lt % tiles_n;
       const int r0 = ltm * BM, c0 = ltn * BN;
       constexpr int VPR = BN / 8;  // vectors per tile row
-      for (int e = threadIdx.x; e < BM * VPR; e += blockDim.x) {
-        const int rr = r0 + e / VPR, cc = c0 + (e % VPR) * 8;
-        if (rr >= cp.rows_per_rank || cc >= shp.N) continue;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      constexpr int UNR = 4;       // independent vectors per thread and pass: their loads are all in flight together
+      for (int e0 = threadIdx.x; e0 < BM * VPR; e0 += blockDim.x * UNR) {
+        float acc[UNR][8];
+        int rr[UNR], cc[UNR];
+        bool okv[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const int e = e0 + u * blockDim.x;
+          rr[u] = r0 + e / VPR;
+          cc[u] = c0 + (e % VPR) * 8;
+          okv[u] = e < BM * VPR && rr[u] < cp.rows_per_rank && cc[u] < shp.N;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+        }
+        uint4 rq[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          rq[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (okv[u] && cp.residual) rq[u] = *reinterpret_cast<const uint4*>(cp.residual + static_cast<long long>(rr[u]) * cp.ldr + cc[u]);
+        }
         for (int s = 0; s < cp.n; ++s) {
-          const uint4 q = *reinterpret_cast<const uint4*>(my_stage + (static_cast<long long>(s) * cp.rows_per_rank + rr) * shp.N + cc);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+          uint4 q[UNR];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
-        }
-        if (cp.bias) {
-          const uint4 q = __ldg(reinterpret_cast<const uint4*>(cp.bias + cc));
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+          for (int u = 0; u < UNR; ++u) {
+            q[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (okv[u]) q[u] = *reinterpret_cast<const uint4*>(my_stage + (static_cast<long long>(s) * cp.rows_per_rank + rr[u]) * shp.N + cc[u]);
+          }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
-        }
-        if (cp.residual) {
-          const uint4 q = *reinterpret_cast<const uint4*>(cp.residual + static_cast<long long>(rr) * cp.ldr + cc);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+          for (int u = 0; u < UNR; ++u) {
+            const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
+          }
         }
-        *reinterpret_cast<uint4*>(cp.out + static_cast<long long>(rr) * cp.ldc + cc) =
-            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          if (!okv[u]) continue;
+          if (cp.bias) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(cp.bias + cc[u]));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
+          }
+          if (cp.residual) {
+            const uint32_t w[4] = {rq[u].x, rq[u].y, rq[u].z, rq[u].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
+          }
+          *reinterpret_cast<uint4*>(cp.out + static_cast<long long>(rr[u]) * cp.ldc + cc[u]) =
+              make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]), pack_bf16x2(acc[u][4], acc[u][5]),
+                         pack_bf16x2(acc[u][6], acc[u][7]));
+        }
       }
       __syncthreads();
     }

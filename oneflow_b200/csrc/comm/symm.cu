@@ -86,6 +86,25 @@ struct alignas(sizeof(T) * VEC) Pack {
   T v[VEC];
 };
 
+
+// dst[0..VEC) = v as TOut, written with the widest aligned stores (dst is aligned to VEC * sizeof(TOut) bytes).
+template <typename TOut, int VEC>
+__device__ __forceinline__ void store_vec(TOut* dst, const float (&v)[VEC]) {
+  if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+    uint32_t w[VEC / 2];
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    if constexpr (VEC == 8) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
 // mode 0: all-reduce, 1: reduce-scatter, 2: all-gather.
 // Input of every rank sits in its arena at `in_off` (count elements of TIn for reduce modes, count/n for
 // all-gather); the result goes to `out` (local memory, TOut), count elements for all-reduce / all-gather,
@@ -105,31 +124,52 @@ __global__ void __launch_bounds__(512) collective_kernel(CommCtx c, int mode, lo
     grid_peer_barrier(c, 2 * epoch, 0);
     return;
   }
+  constexpr int UNR = 4;  // independent 16-byte accesses per thread and pass: NVLink latency needs megabytes in flight
   if (mode == 0 || mode == 1) {
     const long long base = slice * c.rank;
-    for (long long i = tid * VEC; i < slice; i += nth * VEC) {
-      float acc[VEC];
+    for (long long i0 = tid * VEC; i0 < slice; i0 += nth * VEC * UNR) {
+      float acc[UNR][VEC];
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[u][j] = 0.f;
 #pragma unroll 1
       for (int k = 0; k < c.n; ++k) {
         const int p = (c.rank + k) % c.n;  // spread the peers' load
-        const PIn v = *reinterpret_cast<const PIn*>(c.arena[p] + in_off + (base + i) * sizeof(TIn));
+        PIn v[UNR];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) acc[j] += to_f<TIn>(v.v[j]);
+        for (int u = 0; u < UNR; ++u) {
+          const long long i = i0 + u * nth * VEC;
+          if (i < slice) v[u] = *reinterpret_cast<const PIn*>(c.arena[p] + in_off + (base + i) * sizeof(TIn));
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          if (i0 + u * nth * VEC < slice) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[u][j] += to_f<TIn>(v[u].v[j]);
+          }
+        }
       }
-      if (mode == 1) {
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) out[i + j] = from_f<TOut>(acc[j] * scale);
-      } else {
-        // push the reduced slice (fp32) into every rank's staging area
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * nth * VEC;
+        if (i >= slice) continue;
+        if (mode == 1) {
+          float o[VEC];
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) o[j] = acc[u][j] * scale;
+          store_vec<TOut, VEC>(out + i, o);
+        } else {
+          // push the reduced slice (fp32) into every rank's staging area
 #pragma unroll 1
-        for (int k = 0; k < c.n; ++k) {
-          const int p = (c.rank + k) % c.n;
-          float* dst = reinterpret_cast<float*>(c.arena[p] + stage_off) + base + i;
+          for (int k = 0; k < c.n; ++k) {
+            const int p = (c.rank + k) % c.n;
+            float* dst = reinterpret_cast<float*>(c.arena[p] + stage_off) + base + i;
 #pragma unroll
-          for (int j = 0; j < VEC; j += 4)
-            *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j] * scale, acc[j + 1] * scale, acc[j + 2] * scale, acc[j + 3] * scale);
+            for (int j = 0; j < VEC; j += 4)
+              *reinterpret_cast<float4*>(dst + j) =
+                  make_float4(acc[u][j] * scale, acc[u][j + 1] * scale, acc[u][j + 2] * scale, acc[u][j + 3] * scale);
+          }
         }
       }
     }
@@ -138,7 +178,8 @@ __global__ void __launch_bounds__(512) collective_kernel(CommCtx c, int mode, lo
       const float* st = reinterpret_cast<const float*>(c.arena[c.rank] + stage_off);
       for (long long i = tid * 4; i < count; i += nth * 4) {
         const float4 v = *reinterpret_cast<const float4*>(st + i);
-        out[i] = from_f<TOut>(v.x); out[i + 1] = from_f<TOut>(v.y); out[i + 2] = from_f<TOut>(v.z); out[i + 3] = from_f<TOut>(v.w);
+        const float o[4] = {v.x, v.y, v.z, v.w};
+        store_vec<TOut, 4>(out + i, o);
       }
       return;  // the staging area is rewritten only after the next call's first barrier
     }
@@ -146,10 +187,22 @@ __global__ void __launch_bounds__(512) collective_kernel(CommCtx c, int mode, lo
     for (int k = 0; k < c.n; ++k) {
       const int p = (c.rank + k) % c.n;
       const TIn* src = reinterpret_cast<const TIn*>(c.arena[p] + in_off);
-      for (long long i = tid * VEC; i < slice; i += nth * VEC) {
-        const PIn v = *reinterpret_cast<const PIn*>(src + i);
+      for (long long i0 = tid * VEC; i0 < slice; i0 += nth * VEC * UNR) {
+        PIn v[UNR];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) out[slice * p + i + j] = from_f<TOut>(to_f<TIn>(v.v[j]) * scale);
+        for (int u = 0; u < UNR; ++u) {
+          const long long i = i0 + u * nth * VEC;
+          if (i < slice) v[u] = *reinterpret_cast<const PIn*>(src + i);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const long long i = i0 + u * nth * VEC;
+          if (i >= slice) continue;
+          float o[VEC];
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) o[j] = to_f<TIn>(v[u].v[j]) * scale;
+          store_vec<TOut, VEC>(out + slice * p + i, o);
+        }
       }
     }
   }

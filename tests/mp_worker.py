@@ -237,6 +237,59 @@ def case_embedding_engine(rank, world, dev):
     assert _native.read_status() == (0, 0), _native.read_status()
 
 
+def case_dlrm_parallel(rank, world, dev):
+    """Model-parallel embedding + data-parallel MLPs: the loss curve must match a single-rank run on the global batch."""
+    from oneflow_b200.models import dlrm as M
+    cfg = M.tiny_config(global_batch=128)
+    tr = M.DLRMTrainer(cfg, dev, seed=4)
+    full = [M.make_batch(cfg, cfg.global_batch, seed=10 + s) for s in range(4)]
+    B = tr.local_batch
+    losses = []
+    for dense, ids, labels in full:
+        sl = slice(rank * B, (rank + 1) * B)
+        loss = tr.train_step(dense[sl].to(dev), ids[sl].to(dev), labels[sl].to(dev))
+        t = loss.detach().float().reshape(1).clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / world)
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+    assert losses[-1] == losses[-1] and all(abs(l) < 10 for l in losses), losses
+    # parameters stay identical on all ranks
+    flat = tr.store.flat.float().clone()
+    ref = flat.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(flat, ref), "MLP replicas diverged"
+    if rank == 0:
+        print("DLRM_LOSSES " + ",".join(f"{l:.6f}" for l in losses))
+
+
+def case_resnet_parallel(rank, world, dev):
+    from oneflow_b200.models import resnet as R
+    cfg = R.tiny_config()
+    tr = R.ResNetTrainer(cfg, dev, lr=0.05, seed=2)
+    g = torch.Generator().manual_seed(50 + rank)
+    images = torch.randn(8, cfg.image_size, cfg.image_size, 3, generator=g).bfloat16().to(dev)
+    labels = torch.randint(0, cfg.num_classes, (8,), generator=g).to(dev)
+    first = last = None
+    for step in range(6):
+        loss = tr.train_step(images, labels)
+        t = loss.detach().float().reshape(1).clone()
+        dist.all_reduce(t)
+        last = float(t) / world
+        first = last if first is None else first
+    assert last < first, (first, last)
+    flat = tr.net.store.flat.float().clone()
+    ref = flat.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(flat, ref), "replicas diverged"
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+
+
 def main():
     case, devkind = sys.argv[1], sys.argv[2]
     rank, world, dev = setup(devkind)
@@ -247,6 +300,10 @@ def main():
             case_fused_gemm(rank, world, dev)
         elif case == "tp_matches_single":
             case_tp_matches_single(rank, world, dev)
+        elif case == "dlrm_parallel":
+            case_dlrm_parallel(rank, world, dev)
+        elif case == "resnet_parallel":
+            case_resnet_parallel(rank, world, dev)
         elif case == "embedding_engine":
             case_embedding_engine(rank, world, dev)
         elif case.startswith("gpt_"):

@@ -35,3 +35,16 @@ def test_gpt_parallel_training_gpu(case, n):
 @pytest.mark.parametrize("n", [2, 4])
 def test_embedding_engine_matches_single_rank(n):
     run_case("embedding_engine", _n(n), "cuda")
+
+
+def test_dlrm_two_gpus_match_one_gpu():
+    from test_parallel_cpu import _dlrm_losses
+    _n(2)
+    one = _dlrm_losses(run_case("dlrm_parallel", 1, "cuda"))
+    two = _dlrm_losses(run_case("dlrm_parallel", 2, "cuda"))
+    for a, b in zip(one, two):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (one, two)
+
+
+def test_resnet_data_parallel_2gpu():
+    run_case("resnet_parallel", _n(2), "cuda")

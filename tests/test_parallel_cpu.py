@@ -17,6 +17,7 @@ def run_case(case, nproc, dev="cpu", timeout=600):
            case, dev]
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env, cwd=ROOT)
     assert p.returncode == 0 and f"CASE {case} OK" in p.stdout, p.stdout[-4000:]
+    return p.stdout
 
 
 def test_tensor_parallel_matches_unsharded_cpu():
@@ -26,3 +27,20 @@ def test_tensor_parallel_matches_unsharded_cpu():
 @pytest.mark.parametrize("case,n", [("gpt_2_1_1", 2), ("gpt_1_2_1", 2), ("gpt_1_1_2", 2), ("gpt_2_2_1", 4)])
 def test_gpt_parallel_training_cpu(case, n):
     run_case(case, n)
+
+
+def _dlrm_losses(out):
+    line = [l for l in out.splitlines() if l.startswith("DLRM_LOSSES ")][-1]
+    return [float(v) for v in line.split()[1].split(",")]
+
+
+def test_dlrm_two_ranks_match_one_rank_cpu():
+    one = _dlrm_losses(run_case("dlrm_parallel", 1))
+    two = _dlrm_losses(run_case("dlrm_parallel", 2))
+    assert len(one) == len(two) == 4
+    for a, b in zip(one, two):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (one, two)
+
+
+def test_resnet_data_parallel_cpu():
+    run_case("resnet_parallel", 2)
