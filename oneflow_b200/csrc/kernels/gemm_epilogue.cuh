@@ -129,93 +129,109 @@ __device__ __forceinline__ void epi_store_f32(uint32_t stage, int lane, const fl
   __syncwarp();
 }
 
+// Elementwise part and stores of one 32-column chunk whose accumulator values are already in `r`.
+__device__ __forceinline__ void gemm_epilogue_chunk(const GemmEpilogue& ep, const uint32_t (&r)[32], int row0, int col0, int rows_valid,
+                                                    int cols_valid, int lane, uint32_t stage, bool atomic_out) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+  if (ep.bias) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < cols_valid) {
+        const uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0 + g * 8));  // same address in every lane
+        const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(bw[j]);
+          v[g * 8 + 2 * j] += f.x;
+          v[g * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
+  }
+  const long long tile_off_aux = static_cast<long long>(row0) * ep.ld_aux + col0;
+  if (ep.aux_out) epi_store_bf16(stage, lane, v, ep.aux_out + tile_off_aux, ep.ld_aux, rows_valid, cols_valid, false);
+  if (ep.aux_in) {
+    float h[32];
+    epi_load_bf16(stage, lane, ep.aux_in + tile_off_aux, ep.ld_aux, rows_valid, cols_valid, h);
+    switch (ep.act) {
+      case kActGeluErf:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= gelu_erf_grad(h[j]);
+        break;
+      case kActGeluTanh:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(h[j]);
+        break;
+      case kActRelu:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = h[j] > 0.f ? v[j] : 0.f;
+        break;
+      default:
+        break;
+    }
+  } else {
+    switch (ep.act) {
+      case kActGeluErf:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        break;
+      case kActGeluTanh:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        break;
+      case kActRelu:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        break;
+      default:
+        break;
+    }
+  }
+  if (ep.residual) {
+    float h[32];
+    epi_load_bf16(stage, lane, ep.residual + static_cast<long long>(row0) * ep.ldr + col0, ep.ldr, rows_valid, cols_valid, h);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += h[j];
+  }
+  const long long tile_off = static_cast<long long>(row0) * ep.ldc + col0;
+  if (ep.out_fp32) {
+    epi_store_f32(stage, lane, v, reinterpret_cast<float*>(ep.C) + tile_off, ep.ldc, rows_valid, cols_valid,
+                  atomic_out ? 2 : (ep.accumulate ? 1 : 0));
+  } else {
+    epi_store_bf16(stage, lane, v, reinterpret_cast<__nv_bfloat16*>(ep.C) + tile_off, ep.ldc, rows_valid, cols_valid,
+                   ep.accumulate != 0);
+  }
+}
+
 // Epilogue of one accumulator tile for one warp: rows [row0, row0 + 32) x columns [n0, n0 + BN) of the problem,
 // accumulator at TMEM address `taddr` (lane quadrant and column base already applied). `atomic_out` selects
 // atomic accumulation into an fp32 C (split-K); the fused elementwise options are not combined with it.
+// The TMEM load of chunk c + 1 is in flight while chunk c is processed (two register buffers; tcgen05.wait::ld
+// is only issued right before a buffer is read, and nothing touches a buffer between its load and that wait).
 template <int BN>
 __device__ __forceinline__ void gemm_epilogue_warp(const GemmEpilogue& ep, const GemmShape& shp, uint32_t taddr, int row0, int n0,
                                                    int lane, uint32_t stage, bool atomic_out) {
   const int rows_valid = shp.M - row0;
+  int nchunks = (shp.N - n0 + 31) / 32;
+  if (nchunks > BN / 32) nchunks = BN / 32;
+  if (nchunks <= 0) return;
+  uint32_t ra[32], rb[32];
+  __syncwarp();  // tcgen05.ld is warp-collective
+  tmem_ld_32x32(taddr, ra);
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
-    const int col0 = n0 + c * 32;
-    const int cols_valid = shp.N - col0;
-    if (cols_valid <= 0) break;
-    uint32_t r[32];
-    __syncwarp();  // tcgen05.ld is warp-collective
-    tmem_ld_32x32(taddr + c * 32, r);
+  for (int c = 0; c < nchunks; c += 2) {
     tmem_wait_ld();
-    if (rows_valid <= 0) continue;
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
-    if (ep.bias) {
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (g * 8 < cols_valid) {
-          const uint4 bb = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0 + g * 8));  // same address in every lane
-          const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = unpack_bf16x2(bw[j]);
-            v[g * 8 + 2 * j] += f.x;
-            v[g * 8 + 2 * j + 1] += f.y;
-          }
-        }
-      }
-    }
-    const long long tile_off_aux = static_cast<long long>(row0) * ep.ld_aux + col0;
-    if (ep.aux_out) epi_store_bf16(stage, lane, v, ep.aux_out + tile_off_aux, ep.ld_aux, rows_valid, cols_valid, false);
-    if (ep.aux_in) {
-      float h[32];
-      epi_load_bf16(stage, lane, ep.aux_in + tile_off_aux, ep.ld_aux, rows_valid, cols_valid, h);
-      switch (ep.act) {
-        case kActGeluErf:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= gelu_erf_grad(h[j]);
-          break;
-        case kActGeluTanh:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(h[j]);
-          break;
-        case kActRelu:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = h[j] > 0.f ? v[j] : 0.f;
-          break;
-        default:
-          break;
-      }
-    } else {
-      switch (ep.act) {
-        case kActGeluErf:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-          break;
-        case kActGeluTanh:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-          break;
-        case kActRelu:
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-          break;
-        default:
-          break;
-      }
-    }
-    if (ep.residual) {
-      float h[32];
-      epi_load_bf16(stage, lane, ep.residual + static_cast<long long>(row0) * ep.ldr + col0, ep.ldr, rows_valid, cols_valid, h);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] += h[j];
-    }
-    const long long tile_off = static_cast<long long>(row0) * ep.ldc + col0;
-    if (ep.out_fp32) {
-      epi_store_f32(stage, lane, v, reinterpret_cast<float*>(ep.C) + tile_off, ep.ldc, rows_valid, cols_valid,
-                    atomic_out ? 2 : (ep.accumulate ? 1 : 0));
-    } else {
-      epi_store_bf16(stage, lane, v, reinterpret_cast<__nv_bfloat16*>(ep.C) + tile_off, ep.ldc, rows_valid, cols_valid,
-                     ep.accumulate != 0);
+    __syncwarp();
+    if (c + 1 < nchunks) tmem_ld_32x32(taddr + (c + 1) * 32, rb);
+    if (rows_valid > 0) gemm_epilogue_chunk(ep, ra, row0, n0 + c * 32, rows_valid, shp.N - (n0 + c * 32), lane, stage, atomic_out);
+    if (c + 1 < nchunks) {
+      tmem_wait_ld();
+      __syncwarp();
+      if (c + 2 < nchunks) tmem_ld_32x32(taddr + (c + 2) * 32, ra);
+      if (rows_valid > 0)
+        gemm_epilogue_chunk(ep, rb, row0, n0 + (c + 1) * 32, rows_valid, shp.N - (n0 + (c + 1) * 32), lane, stage, atomic_out);
     }
   }
 }
