@@ -342,23 +342,50 @@ emb_serve_kernel(OfbEmbStore st, EmbCtx c, long long cnt_off, long long emb_off,
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int D = st.dim;
-  for (long long w = warp; ok && w < pre[c.n]; w += nwarps) {
-    int r;
-    long long idx;
-    locate(pre, c.n, w, &r, &idx);
-    const int s = slot_tmp[r * cap + idx];
-    const int row = s >= 0 ? st.trow[s] : -1;
-    if (lane == 0) {
-      const int uo = s >= 0 ? st.uo_of[s] : -1;
-      rowidx[r * cap + idx] = row;
-      uoidx[r * cap + idx] = uo;
-      if (uo >= 0) u_row[uo] = row;
+  constexpr int UNR = 4;  // rows per warp and pass: their dependent index loads and row loads overlap
+  const long long total = ok ? pre[c.n] : 0;
+  for (long long w0 = warp * UNR; w0 < total; w0 += nwarps * UNR) {
+    int rr[UNR], row[UNR], sl[UNR];
+    long long where[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      rr[u] = 0;
+      where[u] = -1;
+      sl[u] = -1;
+      if (w0 + u < total) {
+        long long idx;
+        locate(pre, c.n, w0 + u, &rr[u], &idx);
+        where[u] = rr[u] * cap + idx;
+        sl[u] = slot_tmp[where[u]];
+      }
     }
-    uint2* dst = reinterpret_cast<uint2*>(c.arena[r] + emb_off) + (c.rank * cap + idx) * (D >> 2);
-    const float4* src = reinterpret_cast<const float4*>(st.rows + static_cast<long long>(row < 0 ? 0 : row) * st.line);
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) row[u] = sl[u] >= 0 ? st.trow[sl[u]] : -1;
+    if (lane < UNR) {
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        if (lane == u && where[u] >= 0) {
+          const int uo = sl[u] >= 0 ? st.uo_of[sl[u]] : -1;
+          rowidx[where[u]] = row[u];
+          uoidx[where[u]] = uo;
+          if (uo >= 0) u_row[uo] = row[u];
+        }
+      }
+    }
     for (int q = lane; q < (D >> 2); q += 32) {
-      const float4 v = row >= 0 ? src[q] : make_float4(0.f, 0.f, 0.f, 0.f);
-      dst[q] = pack4<kHalf>(v);
+      float4 v[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row[u] >= 0) v[u] = reinterpret_cast<const float4*>(st.rows + static_cast<long long>(row[u]) * st.line)[q];
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        if (where[u] < 0) continue;
+        const long long idx = where[u] - rr[u] * cap;
+        uint2* dst = reinterpret_cast<uint2*>(c.arena[rr[u]] + emb_off) + (c.rank * cap + idx) * (D >> 2);
+        dst[q] = pack4<kHalf>(v[u]);
+      }
     }
   }
   signal_when_grid_done(c, done_cnt, epoch, 0);
@@ -375,11 +402,25 @@ emb_gather_kernel(EmbCtx c, long long emb_off, long long cap, const unsigned int
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int vec = D >> 2;
-  for (long long p = warp; p < n; p += nwarps) {
-    const unsigned int v = inv[p];
-    const bool valid = v != 0xFFFFFFFFu;
-    const long long u = valid ? (long long)(v >> kOwnerShift) * cap + (v & kIndexMask) : 0;
-    for (int q = lane; q < vec; q += 32) out[p * vec + q] = valid ? src[u * vec + q] : make_uint2(0u, 0u);
+  constexpr int UNR = 4;
+  for (long long p0 = warp * UNR; p0 < n; p0 += nwarps * UNR) {
+    long long u[UNR];
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) {
+      u[k] = -1;
+      if (p0 + k < n) {
+        const unsigned int v = inv[p0 + k];
+        if (v != 0xFFFFFFFFu) u[k] = (long long)(v >> kOwnerShift) * cap + (v & kIndexMask);
+      }
+    }
+    for (int q = lane; q < vec; q += 32) {
+      uint2 t[UNR];
+#pragma unroll
+      for (int k = 0; k < UNR; ++k) t[k] = u[k] >= 0 ? src[u[k] * vec + q] : make_uint2(0u, 0u);
+#pragma unroll
+      for (int k = 0; k < UNR; ++k)
+        if (p0 + k < n) out[(p0 + k) * vec + q] = t[k];
+    }
   }
 }
 
@@ -392,12 +433,25 @@ emb_grad_reduce_kernel(const uint2* __restrict__ grad, const unsigned int* __res
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int vec = D >> 2;
-  for (long long p = warp; p < n; p += nwarps) {
-    const unsigned int v = inv[p];
-    if (v == 0xFFFFFFFFu) continue;
-    const long long u = (long long)(v >> kOwnerShift) * cap + (v & kIndexMask);
-    float4* dst = reinterpret_cast<float4*>(gsum + u * D);
-    for (int q = lane; q < vec; q += 32) atomicAdd(&dst[q], unpack4<kHalf>(grad[p * vec + q]));
+  constexpr int UNR = 4;
+  for (long long p0 = warp * UNR; p0 < n; p0 += nwarps * UNR) {
+    long long u[UNR];
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) {
+      u[k] = -1;
+      if (p0 + k < n) {
+        const unsigned int v = inv[p0 + k];
+        if (v != 0xFFFFFFFFu) u[k] = (long long)(v >> kOwnerShift) * cap + (v & kIndexMask);
+      }
+    }
+    for (int q = lane; q < vec; q += 32) {
+      uint2 t[UNR];
+#pragma unroll
+      for (int k = 0; k < UNR; ++k) t[k] = u[k] >= 0 ? grad[(p0 + k) * vec + q] : make_uint2(0u, 0u);
+#pragma unroll
+      for (int k = 0; k < UNR; ++k)
+        if (u[k] >= 0) atomicAdd(reinterpret_cast<float4*>(gsum + u[k] * D) + q, unpack4<kHalf>(t[k]));
+    }
   }
 }
 
@@ -447,14 +501,31 @@ emb_grad_combine_kernel(EmbCtx c, long long cnt_off, long long grad_off, long lo
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int vec = D >> 2;
-  for (long long w = warp; w < pre[c.n]; w += nwarps) {
-    int r;
-    long long idx;
-    locate(pre, c.n, w, &r, &idx);
-    const int uo = uoidx[r * cap + idx];
-    if (uo < 0) continue;
-    float4* dst = reinterpret_cast<float4*>(gacc + static_cast<long long>(uo) * D);
-    for (int q = lane; q < vec; q += 32) atomicAdd(&dst[q], unpack4<kHalf>(src[(r * cap + idx) * vec + q]));
+  constexpr int UNR = 4;
+  const long long total = pre[c.n];
+  for (long long w0 = warp * UNR; w0 < total; w0 += nwarps * UNR) {
+    long long where[UNR];
+    int uo[UNR];
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) {
+      where[k] = -1;
+      uo[k] = -1;
+      if (w0 + k < total) {
+        int r;
+        long long idx;
+        locate(pre, c.n, w0 + k, &r, &idx);
+        where[k] = r * cap + idx;
+        uo[k] = uoidx[where[k]];
+      }
+    }
+    for (int q = lane; q < vec; q += 32) {
+      uint2 t[UNR];
+#pragma unroll
+      for (int k = 0; k < UNR; ++k) t[k] = uo[k] >= 0 ? src[where[k] * vec + q] : make_uint2(0u, 0u);
+#pragma unroll
+      for (int k = 0; k < UNR; ++k)
+        if (uo[k] >= 0) atomicAdd(reinterpret_cast<float4*>(gacc + static_cast<long long>(uo[k]) * D) + q, unpack4<kHalf>(t[k]));
+    }
   }
 }
 
@@ -497,25 +568,38 @@ emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __re
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int vec = st.dim >> 2;
   const int total = *n_uo;
-  for (long long u = warp; u < total; u += nwarps) {
-    const int row = u_row[u];
-    float4* g4 = reinterpret_cast<float4*>(gacc + u * st.dim);
-    float4* w4 = reinterpret_cast<float4*>(st.rows + static_cast<long long>(row < 0 ? 0 : row) * st.line);
+  constexpr int UNR = 4;  // rows per warp and pass
+  for (long long u0 = warp * UNR; u0 < total; u0 += nwarps * UNR) {
+    int row[UNR];
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) row[k] = u0 + k < total ? u_row[u0 + k] : -2;
     for (int q = lane; q < vec; q += 32) {
-      const float4 g = g4[q];
-      g4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < 0) continue;
-      float4 x = w4[q];
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-      if (kStates >= 1) a = w4[vec + q];
-      if (kStates >= 2) b = w4[2 * vec + q];
-      update_one<KIND>(x.x, g.x, a.x, b.x, h);
-      update_one<KIND>(x.y, g.y, a.y, b.y, h);
-      update_one<KIND>(x.z, g.z, a.z, b.z, h);
-      update_one<KIND>(x.w, g.w, a.w, b.w, h);
-      w4[q] = x;
-      if (kStates >= 1) w4[vec + q] = a;
-      if (kStates >= 2) w4[2 * vec + q] = b;
+      float4 g[UNR], x[UNR], a[UNR], b[UNR];
+#pragma unroll
+      for (int k = 0; k < UNR; ++k) {
+        g[k] = x[k] = a[k] = b[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row[k] == -2) continue;
+        g[k] = reinterpret_cast<const float4*>(gacc + (u0 + k) * st.dim)[q];
+        if (row[k] < 0) continue;
+        const float4* w4 = reinterpret_cast<const float4*>(st.rows + static_cast<long long>(row[k]) * st.line);
+        x[k] = w4[q];
+        if (kStates >= 1) a[k] = w4[vec + q];
+        if (kStates >= 2) b[k] = w4[2 * vec + q];
+      }
+#pragma unroll
+      for (int k = 0; k < UNR; ++k) {
+        if (row[k] == -2) continue;
+        reinterpret_cast<float4*>(gacc + (u0 + k) * st.dim)[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row[k] < 0) continue;
+        update_one<KIND>(x[k].x, g[k].x, a[k].x, b[k].x, h);
+        update_one<KIND>(x[k].y, g[k].y, a[k].y, b[k].y, h);
+        update_one<KIND>(x[k].z, g[k].z, a[k].z, b[k].z, h);
+        update_one<KIND>(x[k].w, g[k].w, a[k].w, b[k].w, h);
+        float4* w4 = reinterpret_cast<float4*>(st.rows + static_cast<long long>(row[k]) * st.line);
+        w4[q] = x[k];
+        if (kStates >= 1) w4[vec + q] = a[k];
+        if (kStates >= 2) w4[2 * vec + q] = b[k];
+      }
     }
   }
 }

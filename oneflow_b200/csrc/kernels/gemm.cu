@@ -11,11 +11,11 @@ namespace ofb {
 // Whether shapes that fill the machine use the two-SM kernel unless told otherwise.
 constexpr bool kDefault2Cta = true;
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int ST = 0, int MINB = 1>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shp, const GemmEpilogue& ep,
                        int* status, int max_ctas, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  using Cfg = GemmCfg<BN, ST>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, ST, MINB>;
   static bool configured = false;
   if (!configured) {
     OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -28,7 +28,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const int tiles = ((shp.M + 127) / 128) * ((shp.N + BN - 1) / BN) * (shp.splits > 1 ? shp.splits : 1);
-  int grid = tiles < sm_count ? tiles : sm_count;
+  int grid = tiles < sm_count * MINB ? tiles : sm_count * MINB;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, shp, ep, status);
   OFB_CUDA_OK(cudaGetLastError());
@@ -83,6 +83,10 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
     two = kDefault2Cta && tiles2 >= 74 && a->N >= 256 && a->M >= 256;
   }
   if (mode2 == 0) two = bn == 512;
+  // Few K blocks and many tiles: the epilogue is the bottleneck, so run two one-SM CTAs per SM (short ring) instead.
+  const bool short_k = a->K <= 1024 && bn == 0 && !a_mn && (long long)((a->M + 127) / 128) * ((a->N + 127) / 128) >= 2 * 148 &&
+                       std::getenv("OFB_GEMM_SHORTK_OFF") == nullptr;
+  if (short_k) two = false;
   if (two) {
     if (!a_mn) {
       if (get_tensor_map(&tmA, a->A, 2, 2, a->K, a->M, 0, (uint64_t)a->lda * 2, 0, 64, 128, 0, 3)) return -1;
@@ -101,6 +105,7 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
     if (a_mn && !b_mn) return launch_gemm_2cta<1, 0>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
     return launch_gemm_2cta<1, 1>(tmA, tmB, shp2, ep, st2, a->max_ctas, stream);
   }
+  if (short_k) bn = 128;
   if (bn != 128 && bn != 256) {
     // Small problems: prefer more, smaller tiles so that all SMs get work.
     long long tiles256 = (long long)((a->M + 127) / 128) * ((a->N + 255) / 256);
@@ -146,6 +151,10 @@ int gemm_dispatch(const OfbGemmArgs* a, const GemmEpilogue& ep, cudaStream_t str
     }
   }
   int* status = device_status_ptr();
+  if (short_k && shp.splits <= 1) {
+    if (!b_mn) return launch_gemm<128, 0, 0, 2, 2>(tmA, tmB, shp, ep, status, a->max_ctas, stream);
+    return launch_gemm<128, 0, 1, 2, 2>(tmA, tmB, shp, ep, status, a->max_ctas, stream);
+  }
 #define OFB_GEMM_CASE(BN_, AM_, BM_) \
   if (bn == BN_ && a_mn == AM_ && b_mn == BM_) return launch_gemm<BN_, AM_, BM_>(tmA, tmB, shp, ep, status, a->max_ctas, stream);
   OFB_GEMM_CASE(256, 0, 0)

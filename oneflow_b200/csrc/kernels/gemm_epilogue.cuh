@@ -208,8 +208,6 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmEpilogue& ep, cons
 // Epilogue of one accumulator tile for one warp: rows [row0, row0 + 32) x columns [n0, n0 + BN) of the problem,
 // accumulator at TMEM address `taddr` (lane quadrant and column base already applied). `atomic_out` selects
 // atomic accumulation into an fp32 C (split-K); the fused elementwise options are not combined with it.
-// The TMEM load of chunk c + 1 is in flight while chunk c is processed (two register buffers; tcgen05.wait::ld
-// is only issued right before a buffer is read, and nothing touches a buffer between its load and that wait).
 template <int BN>
 __device__ __forceinline__ void gemm_epilogue_warp(const GemmEpilogue& ep, const GemmShape& shp, uint32_t taddr, int row0, int n0,
                                                    int lane, uint32_t stage, bool atomic_out) {
@@ -217,22 +215,13 @@ __device__ __forceinline__ void gemm_epilogue_warp(const GemmEpilogue& ep, const
   int nchunks = (shp.N - n0 + 31) / 32;
   if (nchunks > BN / 32) nchunks = BN / 32;
   if (nchunks <= 0) return;
-  uint32_t ra[32], rb[32];
-  __syncwarp();  // tcgen05.ld is warp-collective
-  tmem_ld_32x32(taddr, ra);
 #pragma unroll 1
-  for (int c = 0; c < nchunks; c += 2) {
+  for (int c = 0; c < nchunks; ++c) {
+    uint32_t r[32];
+    __syncwarp();  // tcgen05.ld is warp-collective
+    tmem_ld_32x32(taddr + c * 32, r);
     tmem_wait_ld();
-    __syncwarp();
-    if (c + 1 < nchunks) tmem_ld_32x32(taddr + (c + 1) * 32, rb);
-    if (rows_valid > 0) gemm_epilogue_chunk(ep, ra, row0, n0 + c * 32, rows_valid, shp.N - (n0 + c * 32), lane, stage, atomic_out);
-    if (c + 1 < nchunks) {
-      tmem_wait_ld();
-      __syncwarp();
-      if (c + 2 < nchunks) tmem_ld_32x32(taddr + (c + 2) * 32, ra);
-      if (rows_valid > 0)
-        gemm_epilogue_chunk(ep, rb, row0, n0 + (c + 1) * 32, rows_valid, shp.N - (n0 + (c + 1) * 32), lane, stage, atomic_out);
-    }
+    if (rows_valid > 0) gemm_epilogue_chunk(ep, r, row0, n0 + c * 32, rows_valid, shp.N - (n0 + c * 32), lane, stage, atomic_out);
   }
 }
 

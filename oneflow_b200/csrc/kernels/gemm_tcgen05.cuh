@@ -51,11 +51,13 @@ struct GemmShape {
 #include "gemm_epilogue.cuh"
 namespace ofb {
 
-template <int BN>
+// ST = 0 picks the deep ring for compute-bound problems (one CTA per SM); a short ring (2) leaves room for two CTAs
+// per SM, which doubles the epilogue throughput of problems with few K blocks.
+template <int BN, int ST = 0>
 struct GemmCfg {
   static constexpr int BM = 128;
   static constexpr int BK = 64;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = ST > 0 ? ST : ((BN == 256) ? 4 : 6);
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
@@ -94,11 +96,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gsz;
 }
 
-template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, int A_MN, int B_MN, int ST = 0, int MINB = 1>
+__global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          GemmShape shp, GemmEpilogue ep, int* status) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, ST>;
   constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES;
   constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
   constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, A_MN, B_MN);
