@@ -95,33 +95,69 @@ bn_reduce_kernel(const bf16* __restrict__ a, const bf16* __restrict__ x, const b
   }
 }
 
-// sums[0..C) = sum x, sums[C..2C) = sum x^2  ->  mean, rstd (and the running statistics when given).
+// sums[0..C) = sum x, sums[C..2C) = sum x^2  ->  mean, rstd, the folded affine map y = scale * x + shift
+// (scale = gamma * rstd, shift = beta - mean * scale), and the running statistics when given.
 __global__ void bn_finalize_kernel(const float* __restrict__ sums, float inv_rows, float eps, float momentum, float unbias, int C,
-                                   float* mean, float* rstd, float* running_mean, float* running_var) {
+                                   const float* __restrict__ gamma, const float* __restrict__ beta, float* mean, float* rstd, float* scale,
+                                   float* shift, float* running_mean, float* running_var) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const float m = sums[c] * inv_rows;
   const float var = fmaxf(sums[C + c] * inv_rows - m * m, 0.f);
+  const float rs = rsqrtf(var + eps);
   mean[c] = m;
-  rstd[c] = rsqrtf(var + eps);
+  rstd[c] = rs;
+  const float sc = gamma[c] * rs;
+  scale[c] = sc;
+  shift[c] = beta[c] - m * sc;
   if (running_mean) {
     running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * m;
     running_var[c] = (1.f - momentum) * running_var[c] + momentum * var * unbias;
   }
 }
 
-// y = [relu]((x - mean) * rstd * gamma + beta [+ residual])
+// Backward coefficients per channel: dx = a * g + b * x + c with
+//   a = gamma rstd,  b = -a rstd s2 / rows,  c = -a s1 / rows - b mean      (s1 = sum g, s2 = sum g xhat)
+__global__ void bn_bwd_coeffs_kernel(const float* __restrict__ sums, const float* __restrict__ mean, const float* __restrict__ rstd,
+                                     const float* __restrict__ gamma, float inv_rows, int C, float* coef) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float a = gamma[c] * rstd[c];
+  const float b = -a * rstd[c] * sums[C + c] * inv_rows;
+  coef[c] = a;
+  coef[C + c] = b;
+  coef[2 * C + c] = -a * sums[c] * inv_rows - b * mean[c];
+}
+
+// Streaming kernels below: when the 8-channel vectors per row divide the block size, a thread keeps the same
+// channels for every row it visits, so the per-channel coefficients are loaded into registers once.
+__device__ __forceinline__ void load_coef8(const float* p, float (&v)[8]) {
+  const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+  v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+}
+
+// y = [relu](scale * x + shift [+ residual])
 __global__ void __launch_bounds__(256)
-bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, const float* __restrict__ mean,
-                const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ beta, long long vecs, int C,
-                int relu, bf16* __restrict__ y) {
+bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, const float* __restrict__ scale,
+                const float* __restrict__ shift, long long vecs, int C, int relu, bf16* __restrict__ y) {
   const int vpr = C >> 3;
+  const bool fixed = (blockDim.x % vpr) == 0;
+  float sc[8], sh[8];
+  if (fixed) {
+    load_coef8(scale + (threadIdx.x % vpr) * 8, sc);
+    load_coef8(shift + (threadIdx.x % vpr) * 8, sh);
+  }
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs; i += (long long)gridDim.x * blockDim.x) {
-    const int c0 = static_cast<int>(i % vpr) * 8;
+    if (!fixed) {
+      const int c0 = static_cast<int>(i % vpr) * 8;
+      load_coef8(scale + c0, sc);
+      load_coef8(shift + c0, sh);
+    }
     float v[8];
     ld8(x + i * 8, v);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = (v[j] - mean[c0 + j]) * rstd[c0 + j] * gamma[c0 + j] + beta[c0 + j];
+    for (int j = 0; j < 8; ++j) v[j] = fmaf(v[j], sc[j], sh[j]);
     if (residual) {
       float r[8];
       ld8(residual + i * 8, r);
@@ -136,14 +172,26 @@ bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual, c
   }
 }
 
-// dx = gamma * rstd * (g - s1 / rows - xhat * s2 / rows), g = dy (* [y > 0]); d_residual = g when wanted.
+// dx = a * g + b * x + c, g = dy (* [y > 0]); d_residual = g when wanted. coef = [a | b | c], each C long.
 __global__ void __launch_bounds__(256)
-bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ mean,
-                    const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ sums, float inv_rows,
+bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ coef,
                     long long vecs, int C, int relu, bf16* __restrict__ dx, bf16* __restrict__ d_residual) {
   const int vpr = C >> 3;
+  const bool fixed = (blockDim.x % vpr) == 0;
+  float ca[8], cb[8], cc[8];
+  if (fixed) {
+    const int c0 = (threadIdx.x % vpr) * 8;
+    load_coef8(coef + c0, ca);
+    load_coef8(coef + C + c0, cb);
+    load_coef8(coef + 2 * C + c0, cc);
+  }
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs; i += (long long)gridDim.x * blockDim.x) {
-    const int c0 = static_cast<int>(i % vpr) * 8;
+    if (!fixed) {
+      const int c0 = static_cast<int>(i % vpr) * 8;
+      load_coef8(coef + c0, ca);
+      load_coef8(coef + C + c0, cb);
+      load_coef8(coef + 2 * C + c0, cc);
+    }
     float g[8], xv[8];
     ld8(dy + i * 8, g);
     ld8(x + i * 8, xv);
@@ -156,10 +204,7 @@ bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, con
     if (d_residual) st8(d_residual + i * 8, g);
     float o[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float xhat = (xv[j] - mean[c0 + j]) * rstd[c0 + j];
-      o[j] = gamma[c0 + j] * rstd[c0 + j] * (g[j] - sums[c0 + j] * inv_rows - xhat * sums[C + c0 + j] * inv_rows);
-    }
+    for (int j = 0; j < 8; ++j) o[j] = fmaf(ca[j], g[j], fmaf(cb[j], xv[j], cc[j]));
     st8(dx + i * 8, o);
   }
 }
@@ -379,33 +424,36 @@ OFB_API int ofb_bn_reduce(int mode, const void* a, const void* x, const void* y,
   return 0;
 }
 
-OFB_API int ofb_bn_finalize(const float* sums, long long rows, float eps, float momentum, int C, float* mean, float* rstd,
-                            float* running_mean, float* running_var, void* stream) {
+OFB_API int ofb_bn_finalize(const float* sums, long long rows, float eps, float momentum, int C, const float* gamma, const float* beta,
+                            float* mean, float* rstd, float* scale, float* shift, float* running_mean, float* running_var, void* stream) {
   const float unbias = rows > 1 ? static_cast<float>(rows) / static_cast<float>(rows - 1) : 1.f;
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sums, 1.f / rows, eps, momentum, unbias, C, mean, rstd, running_mean,
-                                                                       running_var);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sums, 1.f / rows, eps, momentum, unbias, C, gamma, beta, mean, rstd,
+                                                                       scale, shift, running_mean, running_var);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-OFB_API int ofb_bn_apply(const void* x, const void* residual, const float* mean, const float* rstd, const float* gamma, const float* beta,
-                         long long rows, int C, int relu, void* y, void* stream) {
+// y = [relu](scale * x + shift [+ residual]) with per-channel fp32 scale / shift.
+OFB_API int ofb_bn_apply(const void* x, const void* residual, const float* scale, const float* shift, long long rows, int C, int relu,
+                         void* y, void* stream) {
   if (C % 8) return fail("bn: channels must be a multiple of 8");
   const long long vecs = rows * (C / 8);
   if (vecs == 0) return 0;
-  bn_apply_kernel<<<aux_grid(vecs), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, mean, rstd, gamma, beta, vecs, C,
-                                                                  relu, (bf16*)y);
+  bn_apply_kernel<<<aux_grid(vecs), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)residual, scale, shift, vecs, C, relu,
+                                                                  (bf16*)y);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
+// coef [3 C] is scratch written here. sums = [sum g | sum g xhat] from ofb_bn_reduce(mode 1).
 OFB_API int ofb_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean, const float* rstd, const float* gamma,
-                             const float* sums, long long rows, int C, int relu, void* dx, void* d_residual, void* stream) {
+                             const float* sums, float* coef, long long rows, int C, int relu, void* dx, void* d_residual, void* stream) {
   if (C % 8) return fail("bn: channels must be a multiple of 8");
   const long long vecs = rows * (C / 8);
   if (vecs == 0) return 0;
-  bn_bwd_apply_kernel<<<aux_grid(vecs), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)x, (const bf16*)y, mean, rstd, gamma,
-                                                                      sums, 1.f / rows, vecs, C, relu, (bf16*)dx, (bf16*)d_residual);
+  bn_bwd_coeffs_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sums, mean, rstd, gamma, 1.f / rows, C, coef);
+  bn_bwd_apply_kernel<<<aux_grid(vecs), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)x, (const bf16*)y, coef, vecs, C, relu,
+                                                                      (bf16*)dx, (bf16*)d_residual);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -39,16 +39,16 @@ def bn_train_fwd(x, gamma, beta, residual=None, relu=False, eps=1e-5, momentum=0
             running_var.mul_(1 - momentum).add_(var * (rows / max(rows - 1, 1)), alpha=momentum)
         return y.to(x.dtype).view(x.shape), mean, rstd
     sums = torch.zeros(2 * C, dtype=torch.float32, device=x.device)
-    mean = torch.empty(C, dtype=torch.float32, device=x.device)
-    rstd = torch.empty(C, dtype=torch.float32, device=x.device)
+    stats = torch.empty(4, C, dtype=torch.float32, device=x.device)
+    mean, rstd, scale, shift = stats[0], stats[1], stats[2], stats[3]
     y = torch.empty_like(x)
     lib = _lib()
     check(lib.ofb_bn_reduce(c_int(0), ptr(x), None, None, None, None, c_longlong(rows), c_int(C), c_int(0), ptr(sums), stream_ptr()),
           "bn_reduce")
-    check(lib.ofb_bn_finalize(ptr(sums), c_longlong(rows), c_float(eps), c_float(momentum), c_int(C), ptr(mean), ptr(rstd),
-                              ptr(running_mean), ptr(running_var), stream_ptr()), "bn_finalize")
-    check(lib.ofb_bn_apply(ptr(x), ptr(residual), ptr(mean), ptr(rstd), ptr(gamma), ptr(beta), c_longlong(rows), c_int(C),
-                           c_int(int(relu)), ptr(y), stream_ptr()), "bn_apply")
+    check(lib.ofb_bn_finalize(ptr(sums), c_longlong(rows), c_float(eps), c_float(momentum), c_int(C), ptr(gamma), ptr(beta), ptr(mean),
+                              ptr(rstd), ptr(scale), ptr(shift), ptr(running_mean), ptr(running_var), stream_ptr()), "bn_finalize")
+    check(lib.ofb_bn_apply(ptr(x), ptr(residual), ptr(scale), ptr(shift), c_longlong(rows), c_int(C), c_int(int(relu)), ptr(y),
+                           stream_ptr()), "bn_apply")
     K._count(3)
     return y, mean, rstd
 
@@ -63,8 +63,10 @@ def bn_eval_fwd(x, gamma, beta, running_mean, running_var, residual=None, relu=F
             y = y + residual.float()
         return (torch.relu(y) if relu else y).to(x.dtype)
     y = torch.empty_like(x)
-    check(_lib().ofb_bn_apply(ptr(x), ptr(residual), ptr(running_mean), ptr(rstd), ptr(gamma), ptr(beta), c_longlong(rows), c_int(C),
-                              c_int(int(relu)), ptr(y), stream_ptr()), "bn_apply")
+    scale = (gamma.float() * rstd).contiguous()
+    shift = (beta.float() - running_mean.float() * scale).contiguous()
+    check(_lib().ofb_bn_apply(ptr(x), ptr(residual), ptr(scale), ptr(shift), c_longlong(rows), c_int(C), c_int(int(relu)), ptr(y),
+                              stream_ptr()), "bn_apply")
     K._count()
     return y
 
@@ -82,13 +84,14 @@ def bn_train_bwd(dy, x, y, mean, rstd, gamma, relu=False, want_residual_grad=Fal
         dx = gamma * rstd * (g - s1 / rows - xhat * s2 / rows)
         return dx.to(x.dtype).view(x.shape), (g.to(x.dtype).view(x.shape) if want_residual_grad else None), s2, s1
     sums = torch.zeros(2 * C, dtype=torch.float32, device=x.device)
+    coef = torch.empty(3 * C, dtype=torch.float32, device=x.device)
     dx = torch.empty_like(x)
     dres = torch.empty_like(x) if want_residual_grad else None
     lib = _lib()
     dy = dy.contiguous()
     check(lib.ofb_bn_reduce(c_int(1), ptr(dy), ptr(x), ptr(y), ptr(mean), ptr(rstd), c_longlong(rows), c_int(C), c_int(int(relu)), ptr(sums),
                             stream_ptr()), "bn_reduce")
-    check(lib.ofb_bn_bwd_apply(ptr(dy), ptr(x), ptr(y), ptr(mean), ptr(rstd), ptr(gamma), ptr(sums), c_longlong(rows), c_int(C),
+    check(lib.ofb_bn_bwd_apply(ptr(dy), ptr(x), ptr(y), ptr(mean), ptr(rstd), ptr(gamma), ptr(sums), ptr(coef), c_longlong(rows), c_int(C),
                                c_int(int(relu)), ptr(dx), ptr(dres), stream_ptr()), "bn_bwd_apply")
     K._count(2)
     return dx, dres, sums[C:], sums[:C]
