@@ -117,8 +117,14 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int total_tiles = tiles_m * tiles_n;
   const int kblocks = (shp.K + BK - 1) / BK;
   const int tiles_m_per_rank = cp.rows_per_rank / BM;
-  // Row-tile rotation: MODE_AG starts with the local rows, MODE_RS ends with them.
-  const int rot = (MODE == MODE_AG ? cp.rank : (cp.rank + 1) % cp.n) * tiles_m_per_rank;
+  // Row-tile order. MODE_AG starts with the local rows (the peers' shards arrive meanwhile). MODE_RS interleaves the
+  // owners tile by tile (peer, ..., peer, self, peer, ...), so that the P2P stores are spread evenly over the whole
+  // kernel instead of saturating NVLink during its first part; every round ends with this rank's own rows.
+  auto map_tm = [&](int tm) {
+    if (MODE == MODE_AG) return (tm + cp.rank * tiles_m_per_rank) % tiles_m;
+    const int o = (cp.rank + 1 + tm % cp.n) % cp.n;
+    return o * tiles_m_per_rank + tm / cp.n;
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -130,7 +136,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tiles_m, tiles_n, tm, tn);
-        tm = (tm + rot) % tiles_m;
+        tm = map_tm(tm);
         const int m0 = tm * BM, n0 = tn * BN;
         const int owner = tm / tiles_m_per_rank;
         if (MODE == MODE_AG && owner != cp.rank && owner != ready_owner) {
@@ -201,21 +207,21 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    int cleared_owner = -1;
+    unsigned int cleared_owners = 0;  // owners whose staging slab of this parity is known to be free
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, tm, tn);
-      tm = (tm + rot) % tiles_m;
+      tm = map_tm(tm);
       const int m0 = tm * BM, n0 = tn * BN;
       const int owner = tm / tiles_m_per_rank;
-      if (MODE == MODE_RS && owner != cleared_owner) {
+      if (MODE == MODE_RS && !((cleared_owners >> owner) & 1u)) {
         // The owner must have finished reducing what we stored into this parity two calls ago.
         int ok_w = 1;
         if (lane == 0 && cp.epoch > 2)
           ok_w = wait_flag_ge(&my_sig->rs_consumed[owner], cp.epoch - 2, cp.status, 300 + owner) ? 1 : 0;
         ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
         if (!ok_w) { *abort_flag = 1; break; }
-        cleared_owner = owner;
+        cleared_owners |= 1u << owner;
       }
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();

@@ -11,7 +11,7 @@
 // Backward: dX = A X with the same X tile as the (MN-major) B operand and A = the symmetric gradient matrix of the
 //           three samples laid out block-diagonally (plus row/column 96 + s for the dense vector), which three
 //           builder warps assemble in shared memory from dout while the previous tile runs.
-// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer, then builder (backward only) and epilogue warps; the
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer, then builder (backward only: 4) and epilogue warps (backward: 8); the
 // tiles flow through a multi-stage shared-memory ring and two TMEM accumulators, every wait is bounded.
 //
 // Reference: oneflow/user/kernels/fused_dot_feature_interaction_kernel.cu (wmma, one CTA per sample).
@@ -175,7 +175,7 @@ interaction_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_
 
 // ------------------------------------------------------------------------------------------------ backward
 template <int STAGES>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 interaction_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmD,
                           const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ d_dense,
                           __nv_bfloat16* __restrict__ d_sparse, ItParams p, int* status) {
@@ -183,8 +183,8 @@ interaction_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* xt = smem;                              // [STAGES] X tiles
   uint8_t* at = smem + STAGES * kItTileBytes;      // [STAGES] A tiles
-  uint8_t* epi = at + STAGES * kItTileBytes;       // [4] epilogue staging, 4 KB each
-  __nv_bfloat16* gbuf = reinterpret_cast<__nv_bfloat16*>(epi + 4 * kEpiStageBytesPerWarp);  // [3][512]
+  uint8_t* epi = at + STAGES * kItTileBytes;       // [8] epilogue staging, 4 KB each
+  __nv_bfloat16* gbuf = reinterpret_cast<__nv_bfloat16*>(epi + 8 * kEpiStageBytesPerWarp);  // [3][512]
   uint64_t* x_full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(gbuf) + 3 * 1024);
   uint64_t* a_full = x_full + STAGES;
   uint64_t* empty = a_full + STAGES;
@@ -203,7 +203,7 @@ interaction_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -340,9 +340,11 @@ interaction_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 6..9)
+    // ---------------------------------------------------------------- epilogue (warps 6..13): two warps per TMEM lane
+    // quadrant, each draining two of the four 32-column chunks (one warp per scheduler alone cannot keep up)
     const int q = warp & 3;
-    const uint32_t stage_sm = smem_u32(epi + q * kEpiStageBytesPerWarp);
+    const int half = (warp - 6) >> 2;
+    const uint32_t stage_sm = smem_u32(epi + (warp - 6) * kEpiStageBytesPerWarp);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int g = blockIdx.x; g < p.groups; g += gridDim.x) {
@@ -350,7 +352,7 @@ interaction_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmS, const __grid_
       tc_fence_after();
       const long long b0 = static_cast<long long>(g) * kItSamples;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 128 + c * 32, r);
@@ -447,8 +449,8 @@ OFB_API int ofb_interaction_tc_bwd(const void* dense, const void* sparse, const 
   if (batch == 0) return 0;
   CUtensorMap tmS, tmD;
   if (it_maps(&tmS, &tmD, dense, sparse, batch, T)) return -1;
-  constexpr int STAGES = 3;
-  constexpr int SMEM = 2 * STAGES * kItTileBytes + 4 * kEpiStageBytesPerWarp + 3 * 1024 + 256 + 1024;
+  constexpr int STAGES = 2;
+  constexpr int SMEM = 2 * STAGES * kItTileBytes + 8 * kEpiStageBytesPerWarp + 3 * 1024 + 256 + 1024;
   auto kern = interaction_bwd_tc_kernel<STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -458,7 +460,7 @@ OFB_API int ofb_interaction_tc_bwd(const void* dense, const void* sparse, const 
   ItParams p{batch, T, out_dim, static_cast<int>((batch + kItSamples - 1) / kItSamples)};
   int grid = it_sm_count();
   if (grid > p.groups) grid = p.groups;
-  kern<<<grid, 320, SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
+  kern<<<grid, 448, SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
       tmS, tmD, reinterpret_cast<const __nv_bfloat16*>(dout), reinterpret_cast<__nv_bfloat16*>(d_dense),
       reinterpret_cast<__nv_bfloat16*>(d_sparse), p, device_status_ptr());
   OFB_CUDA_OK(cudaGetLastError());
