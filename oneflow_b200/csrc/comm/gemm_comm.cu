@@ -2,12 +2,12 @@
 // activations). One persistent tcgen05 kernel per call does the tensor-core tiles AND the transfer:
 //
 //   MODE_RS  "GEMM -> reduce-scatter" (row-parallel Linear forward, column-parallel dX):
-//       every rank computes its partial C[T, N] tile by tile; the epilogue stores each finished tile
-//       (bf16) straight into the staging buffer of the rank that owns those rows (plain P2P stores over
-//       NVLink) and bumps a per-tile flag there. Tiles for other ranks are computed first, the rank's own
-//       rows last, so the transfers run under the remaining MMA work. When a CTA has no tiles left it
-//       turns into a reducer: it waits (bounded) for the flags of its share of the local rows, sums the n
-//       partial tiles in fp32, adds bias and the residual shard and writes the [T/n, N] result.
+//       every rank computes its partial C[T, N] tile by tile, owners interleaved (peer, ..., peer, self, ...). The
+//       epilogue of a peer's tile stores it (bf16) straight into the staging buffer of the rank that owns those
+//       rows (plain P2P stores over NVLink) and publishes a per-(tile, quadrant) flag there. The epilogue of an own
+//       tile waits (bounded) for the peers' flags of that tile and finishes the reduction in registers:
+//       out = alpha * acc + the peers' partials + bias + residual shard. No separate reduction pass exists and the
+//       transfers are spread over the whole kernel.
 //   MODE_AG  "all-gather -> GEMM" (column-parallel Linear forward, row-parallel dX, ZeRO parameter gather
 //       in front of the first consuming GEMM):
 //       two extra copier warps per CTA pull the peers' row shards into this GPU's gathered buffer (each
@@ -227,9 +227,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const uint32_t stage_sm = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
-      if (MODE == MODE_RS) {
+      const int tile_local = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
+      if (MODE == MODE_RS && owner != cp.rank) {
         // The raw partial tile goes to the slab this rank owns in the staging buffer of the rows' owner (plain P2P
-        // stores over NVLink, full 64-byte row segments); bias and residual are added once, after the reduction.
+        // stores over NVLink, full 64-byte row segments); the owner adds it in the epilogue of its own tile.
         GemmEpilogue pe;
         pe.C = cp.stage[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.rows_per_rank * shp.N;
         pe.ldc = shp.N;
@@ -238,17 +239,61 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
         GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
         gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false);
+      } else if (MODE == MODE_RS) {
+        // Own rows: wait (bounded) until every peer's partial of this tile quadrant has landed in the local staging
+        // buffer, then finish the reduction here: out = alpha * acc + sum of the peers' partials + bias + residual.
+        int ok_w = 1;
+        if (lane == 0) {
+          for (int s = 0; s < cp.n && ok_w; ++s) {
+            if (s == cp.rank) continue;
+            const unsigned int* f = cp.flags[cp.rank] + (static_cast<long long>(parity) * cp.n + s) * cp.flag_stride + tile_local * 4 + quad;
+            ok_w = wait_flag_ge(f, cp.epoch, cp.status, 600 + s) ? 1 : 0;
+          }
+        }
+        ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+        if (!ok_w) { *abort_flag = 1; break; }
+        GemmEpilogue pe;
+        pe.C = cp.out; pe.ldc = cp.ldc;
+        pe.bias = cp.bias; pe.residual = cp.residual; pe.ldr = cp.ldr;
+        pe.aux_in = nullptr; pe.aux_out = nullptr; pe.ld_aux = 0;
+        pe.alpha = 1.f; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+        const int lrow0 = m0 - owner * cp.rows_per_rank + quad * 32;
+        const __nv_bfloat16* my_stage = cp.stage[cp.rank] + static_cast<long long>(parity) * cp.n * cp.rows_per_rank * shp.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= shp.N) break;
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_wait_ld();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+          for (int s = 0; s < cp.n; ++s) {
+            if (s == cp.rank) continue;
+            float h[32];
+            epi_load_bf16<true>(stage_sm, lane, my_stage + (static_cast<long long>(s) * cp.rows_per_rank + lrow0) * shp.N + col0, shp.N,
+                          cp.rows_per_rank - lrow0, shp.N - col0, h);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += h[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
+          gemm_epilogue_chunk(pe, r, lrow0, col0, cp.rows_per_rank - lrow0, shp.N - col0, lane, stage_sm, false);
+        }
       } else {
         gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
       }
       tc_fence_before();
-      if (MODE == MODE_RS) __threadfence_system();
+      if (MODE == MODE_RS && owner != cp.rank) __threadfence_system();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tempty[acc]);
-        if (MODE == MODE_RS) {
-          const int tile_local = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
-          atomicAdd_system(cp.flags[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.flag_stride + tile_local, 1u);
+        if (MODE == MODE_RS && owner != cp.rank) {
+          // per (tile, quadrant) flag holding the call number: never reset, older calls left smaller values
+          st_release_sys(cp.flags[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.flag_stride + tile_local * 4 + quad,
+                         cp.epoch);
         }
       }
       acc ^= 1;
@@ -320,79 +365,6 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
 
   if (MODE == MODE_RS && !*abort_flag) {
-    // ---------------------------------------------------------------- reduce the rows this rank owns
-    __shared__ int red_ok;
-    const int local_tiles = tiles_m_per_rank * tiles_n;
-    const __nv_bfloat16* my_stage = cp.stage[cp.rank] + static_cast<long long>(parity) * cp.n * cp.rows_per_rank * shp.N;
-    unsigned int* my_flags = cp.flags[cp.rank] + static_cast<long long>(parity) * cp.n * cp.flag_stride;
-    for (int lt = blockIdx.x; lt < local_tiles; lt += gridDim.x) {
-      if (threadIdx.x == 0) {
-        bool ok = true;
-        for (int s = 0; s < cp.n && ok; ++s) ok = wait_flag_ge(my_flags + s * cp.flag_stride + lt, 4u, cp.status, 600 + s);
-        if (ok)
-          for (int s = 0; s < cp.n; ++s) my_flags[s * cp.flag_stride + lt] = 0u;
-        red_ok = ok ? 1 : 0;
-      }
-      __syncthreads();
-      if (!red_ok) break;
-      const int ltm = lt / tiles_n, ltn = lt % tiles_n;
-      const int r0 = ltm * BM, c0 = ltn * BN;
-      constexpr int VPR = BN / 8;  // vectors per tile row
-      constexpr int UNR = 4;       // independent vectors per thread and pass: their loads are all in flight together
-      for (int e0 = threadIdx.x; e0 < BM * VPR; e0 += blockDim.x * UNR) {
-        float acc[UNR][8];
-        int rr[UNR], cc[UNR];
-        bool okv[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-          const int e = e0 + u * blockDim.x;
-          rr[u] = r0 + e / VPR;
-          cc[u] = c0 + (e % VPR) * 8;
-          okv[u] = e < BM * VPR && rr[u] < cp.rows_per_rank && cc[u] < shp.N;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
-        }
-        uint4 rq[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-          rq[u] = make_uint4(0u, 0u, 0u, 0u);
-          if (okv[u] && cp.residual) rq[u] = *reinterpret_cast<const uint4*>(cp.residual + static_cast<long long>(rr[u]) * cp.ldr + cc[u]);
-        }
-        for (int s = 0; s < cp.n; ++s) {
-          uint4 q[UNR];
-#pragma unroll
-          for (int u = 0; u < UNR; ++u) {
-            q[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (okv[u]) q[u] = *reinterpret_cast<const uint4*>(my_stage + (static_cast<long long>(s) * cp.rows_per_rank + rr[u]) * shp.N + cc[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < UNR; ++u) {
-            const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-          if (!okv[u]) continue;
-          if (cp.bias) {
-            const uint4 q = __ldg(reinterpret_cast<const uint4*>(cp.bias + cc[u]));
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
-          }
-          if (cp.residual) {
-            const uint32_t w[4] = {rq[u].x, rq[u].y, rq[u].z, rq[u].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y; }
-          }
-          *reinterpret_cast<uint4*>(cp.out + static_cast<long long>(rr[u]) * cp.ldc + cc[u]) =
-              make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]), pack_bf16x2(acc[u][4], acc[u][5]),
-                         pack_bf16x2(acc[u][6], acc[u][7]));
-        }
-      }
-      __syncthreads();
-    }
     // Tell the senders that this parity of the staging buffer may be reused.
     __threadfence_system();
     __syncthreads();
@@ -453,7 +425,7 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
   if (N % 8 || K % 8) return fail("gemm_rs: N and K must be multiples of 8");
   const int bn = 256;
   const int tiles_local = (T / n / 128) * ((N + bn - 1) / bn);
-  if (tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
+  if (4 * tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
   CUtensorMap tmA, tmB;
   if (get_tensor_map(&tmA, a, 2, 2, K, T, 0, (uint64_t)lda * 2, 0, 64, 128, 0, 3)) return -1;
   if (!b_mn_major) {

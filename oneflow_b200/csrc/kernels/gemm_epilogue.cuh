@@ -35,13 +35,18 @@ __device__ __forceinline__ uint4 epi_lds(uint32_t addr) {
 }
 
 // v[0..31] = bf16 tile src[row = lane][0..31] as fp32, loaded with coalesced 16-byte accesses (4 lanes per row).
+// L2_ONLY: bypass L1 (ld.global.cg) for memory that a peer GPU writes while this kernel runs.
+template <bool L2_ONLY = false>
 __device__ __forceinline__ void epi_load_bf16(uint32_t stage, int lane, const __nv_bfloat16* src, long long ld, int rows_valid,
                                               int cols_valid, float (&v)[32]) {
 #pragma unroll
   for (int it = 0; it < 4; ++it) {
     const int r = it * 8 + (lane >> 2), ch = lane & 3;
     uint4 q = make_uint4(0u, 0u, 0u, 0u);
-    if (r < rows_valid && ch * 8 < cols_valid) q = __ldg(reinterpret_cast<const uint4*>(src + r * ld + ch * 8));
+    if (r < rows_valid && ch * 8 < cols_valid) {
+      const uint4* p = reinterpret_cast<const uint4*>(src + r * ld + ch * 8);
+      q = L2_ONLY ? __ldcg(p) : __ldg(p);
+    }
     epi_sts(epi_addr64(stage, r, ch), q);
   }
   __syncwarp();
