@@ -21,6 +21,8 @@
 //
 // Reference counterparts: matmul + `_nccl_logical_reduce_scatter` / `_nccl_logical_all_gather` ops
 // (oneflow/user/kernels/nccl_logical_kernels.cpp:199-352) inserted by insert_nccl_logical_op_pass.cpp.
+#include <cstdlib>
+
 #include "../common/host_utils.h"
 #include "../kernels/gemm_tcgen05.cuh"
 #include "comm_common.cuh"
@@ -64,7 +66,7 @@ struct GemmCommCfg {
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 template <int BN, int B_MN, int MODE>
-__global__ void __launch_bounds__(MODE == MODE_AG ? 256 : 192, 1)
+__global__ void __launch_bounds__(MODE == MODE_AG ? 256 : 320, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlocal,
                  const __grid_constant__ CUtensorMap tmB, GemmShape shp, GemmEpilogue ep, GemmCommParams cp) {
   using Cfg = GemmCfg<BN>;
@@ -76,8 +78,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
+  // MODE_RS drains every accumulator with eight warps (two per TMEM lane quadrant, half of the columns each): its
+  // epilogue carries the P2P stores and the reduction of the own rows and would otherwise bound short-K problems.
+  constexpr int EPI_WARPS = MODE == MODE_RS ? 8 : 4;
   uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
-  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + EPI_WARPS * kEpiStageBytesPerWarp);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -96,7 +101,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -202,9 +207,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
-    // ---------------------------------------------------------------- epilogue (warps 2..5)
+  } else if (warp < 2 + EPI_WARPS) {
+    // ---------------------------------------------------------------- epilogue (warps 2..5, MODE_RS: 2..9)
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                       // which half of the tile's columns (MODE_RS)
+    constexpr int CPW = (BN / 32) / (EPI_WARPS / 4);         // 32-column chunks per warp
+    const int c_begin = half * CPW, c_end = c_begin + CPW;
     int acc = 0;
     uint32_t acc_phase = 0;
     unsigned int cleared_owners = 0;  // owners whose staging slab of this parity is known to be free
@@ -226,9 +234,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      const uint32_t stage_sm = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
+      const uint32_t stage_sm = smem_u32(epi_stage + (warp - 2) * kEpiStageBytesPerWarp);
       const int tile_local = (tm - owner * tiles_m_per_rank) * tiles_n + tn;
-      if (MODE == MODE_RS && owner != cp.rank) {
+      const bool remote_path = owner != cp.rank;
+      if (MODE == MODE_RS && remote_path) {
         // The raw partial tile goes to the slab this rank owns in the staging buffer of the rows' owner (plain P2P
         // stores over NVLink, full 64-byte row segments); the owner adds it in the epilogue of its own tile.
         GemmEpilogue pe;
@@ -238,7 +247,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         pe.ldr = 0; pe.ld_aux = 0;
         pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
         GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
-        gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false);
+        gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false, c_begin, c_end);
       } else if (MODE == MODE_RS) {
         // Own rows: wait (bounded) until every peer's partial of this tile quadrant has landed in the local staging
         // buffer, then finish the reduction here: out = alpha * acc + sum of the peers' partials + bias + residual.
@@ -246,53 +255,50 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
           for (int s = 0; s < cp.n && ok_w; ++s) {
             if (s == cp.rank) continue;
-            const unsigned int* f = cp.flags[cp.rank] + (static_cast<long long>(parity) * cp.n + s) * cp.flag_stride + tile_local * 4 + quad;
+            const unsigned int* f =
+                cp.flags[cp.rank] + (static_cast<long long>(parity) * cp.n + s) * cp.flag_stride + tile_local * 8 + half * 4 + quad;
             ok_w = wait_flag_ge(f, cp.epoch, cp.status, 600 + s) ? 1 : 0;
           }
         }
         ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
         if (!ok_w) { *abort_flag = 1; break; }
-        GemmEpilogue pe;
-        pe.C = cp.out; pe.ldc = cp.ldc;
-        pe.bias = cp.bias; pe.residual = cp.residual; pe.ldr = cp.ldr;
-        pe.aux_in = nullptr; pe.aux_out = nullptr; pe.ld_aux = 0;
-        pe.alpha = 1.f; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
         const int lrow0 = m0 - owner * cp.rows_per_rank + quad * 32;
         const __nv_bfloat16* my_stage = cp.stage[cp.rank] + static_cast<long long>(parity) * cp.n * cp.rows_per_rank * shp.N;
+        const int rows_valid = cp.rows_per_rank - lrow0;
+        GemmEpilogue pe;
+        pe.C = cp.out; pe.ldc = cp.ldc;
+        pe.bias = cp.bias; pe.residual = nullptr; pe.ldr = 0;
+        pe.aux_in = nullptr; pe.aux_out = nullptr; pe.ld_aux = 0;
+        pe.alpha = 1.f; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           const int col0 = n0 + c * 32;
-          if (col0 >= shp.N) break;
+          const int cols_valid = shp.N - col0;
+          if (cols_valid <= 0) break;
+          // the peers' partials and the residual shard, summed in fp32 with all their loads in flight together
+          float h[32];
+          epi_load_sum_bf16(stage_sm, lane, my_stage + static_cast<long long>(lrow0) * shp.N + col0,
+                            static_cast<long long>(cp.rows_per_rank) * shp.N, cp.n, cp.rank, shp.N,
+                            cp.residual ? cp.residual + static_cast<long long>(lrow0) * cp.ldr + col0 : nullptr, cp.ldr, rows_valid, cols_valid, h);
           uint32_t r[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_wait_ld();
-          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
-          for (int s = 0; s < cp.n; ++s) {
-            if (s == cp.rank) continue;
-            float h[32];
-            epi_load_bf16<true>(stage_sm, lane, my_stage + (static_cast<long long>(s) * cp.rows_per_rank + lrow0) * shp.N + col0, shp.N,
-                          cp.rows_per_rank - lrow0, shp.N - col0, h);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += h[j];
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
-          gemm_epilogue_chunk(pe, r, lrow0, col0, cp.rows_per_rank - lrow0, shp.N - col0, lane, stage_sm, false);
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), ep.alpha, h[j]));
+          gemm_epilogue_chunk(pe, r, lrow0, col0, rows_valid, cols_valid, lane, stage_sm, false);
         }
       } else {
         gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
       }
       tc_fence_before();
-      if (MODE == MODE_RS && owner != cp.rank) __threadfence_system();
+      if (MODE == MODE_RS && remote_path) __threadfence_system();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tempty[acc]);
-        if (MODE == MODE_RS && owner != cp.rank) {
+        if (MODE == MODE_RS && remote_path) {
           // per (tile, quadrant) flag holding the call number: never reset, older calls left smaller values
-          st_release_sys(cp.flags[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.flag_stride + tile_local * 4 + quad,
+          st_release_sys(cp.flags[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.flag_stride + tile_local * 8 + half * 4 + quad,
                          cp.epoch);
         }
       }
@@ -390,10 +396,11 @@ static int launch_gemm_comm(const CUtensorMap& tmA, const CUtensorMap& tmAl, con
   auto kern = gemm_comm_kernel<BN, B_MN, MODE>;
   static bool configured = false;
   if (!configured) {
-    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES + (MODE == MODE_RS ? 4 * kEpiStageBytesPerWarp : 0)));
     configured = true;
   }
-  kern<<<grid, MODE == MODE_AG ? 256 : 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmAl, tmB, shp, ep, cp);
+  kern<<<grid, MODE == MODE_AG ? 256 : 320, Cfg::SMEM_BYTES + (MODE == MODE_RS ? 4 * kEpiStageBytesPerWarp : 0), stream>>>(tmA, tmAl, tmB, shp, ep, cp);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -425,7 +432,7 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
   if (N % 8 || K % 8) return fail("gemm_rs: N and K must be multiples of 8");
   const int bn = 256;
   const int tiles_local = (T / n / 128) * ((N + bn - 1) / bn);
-  if (4 * tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
+  if (8 * tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
   CUtensorMap tmA, tmB;
   if (get_tensor_map(&tmA, a, 2, 2, K, T, 0, (uint64_t)lda * 2, 0, 64, 128, 0, 3)) return -1;
   if (!b_mn_major) {

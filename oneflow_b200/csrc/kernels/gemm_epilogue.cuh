@@ -64,6 +64,68 @@ __device__ __forceinline__ void epi_load_bf16(uint32_t stage, int lane, const __
   __syncwarp();
 }
 
+__device__ __forceinline__ uint32_t epi_bf16x2_add(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// v[0..31] = sum over several bf16 tiles of the same shape: sources s = 0..nsrc-1 except `skip` at
+// base + s * src_stride (row pitch ld, read through L2 only: peers write them), plus one more tile `extra`
+// (row pitch ld_extra) when it is not null. The tiles are added as packed bf16 pairs in the coalesced layout (what a
+// bf16 reduce-scatter does on the wire as well), all loads of a group of four sources are issued before the first is
+// consumed, and only the sum goes through the staging tile, whatever the number of sources.
+__device__ __forceinline__ void epi_load_sum_bf16(uint32_t stage, int lane, const __nv_bfloat16* base, long long src_stride, int nsrc, int skip,
+                                                  long long ld, const __nv_bfloat16* extra, long long ld_extra, int rows_valid, int cols_valid,
+                                                  float (&v)[32]) {
+  uint4 sum[4];
+#pragma unroll
+  for (int it = 0; it < 4; ++it) sum[it] = make_uint4(0u, 0u, 0u, 0u);
+  const int ch = lane & 3;
+  const bool col_ok = ch * 8 < cols_valid;
+  const int total = nsrc + (extra ? 1 : 0);
+  for (int s0 = 0; s0 < total; s0 += 4) {
+    uint4 q[4][4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int s = s0 + k;
+      const __nv_bfloat16* src = nullptr;
+      long long pitch = ld;
+      if (s < nsrc && s != skip) src = base + s * src_stride;
+      if (s == nsrc) { src = extra; pitch = ld_extra; }
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + (lane >> 2);
+        q[k][it] = make_uint4(0u, 0u, 0u, 0u);
+        if (src && col_ok && r < rows_valid) q[k][it] = __ldcg(reinterpret_cast<const uint4*>(src + r * pitch + ch * 8));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        sum[it].x = epi_bf16x2_add(sum[it].x, q[k][it].x);
+        sum[it].y = epi_bf16x2_add(sum[it].y, q[k][it].y);
+        sum[it].z = epi_bf16x2_add(sum[it].z, q[k][it].z);
+        sum[it].w = epi_bf16x2_add(sum[it].w, q[k][it].w);
+      }
+  }
+#pragma unroll
+  for (int it = 0; it < 4; ++it) epi_sts(epi_addr64(stage, it * 8 + (lane >> 2), ch), sum[it]);
+  __syncwarp();
+#pragma unroll
+  for (int c16 = 0; c16 < 4; ++c16) {
+    const uint4 q = epi_lds(epi_addr64(stage, lane, c16));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      v[c16 * 8 + 2 * j] = f.x;
+      v[c16 * 8 + 2 * j + 1] = f.y;
+    }
+  }
+  __syncwarp();
+}
+
 // dst[row][0..31] (bf16) = v of the thread that owns the row (+ old contents when `accumulate`).
 __device__ __forceinline__ void epi_store_bf16(uint32_t stage, int lane, const float (&v)[32], __nv_bfloat16* dst, long long ld,
                                                int rows_valid, int cols_valid, bool accumulate) {
@@ -215,13 +277,13 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmEpilogue& ep, cons
 // atomic accumulation into an fp32 C (split-K); the fused elementwise options are not combined with it.
 template <int BN>
 __device__ __forceinline__ void gemm_epilogue_warp(const GemmEpilogue& ep, const GemmShape& shp, uint32_t taddr, int row0, int n0,
-                                                   int lane, uint32_t stage, bool atomic_out) {
+                                                   int lane, uint32_t stage, bool atomic_out, int c_begin = 0, int c_end = BN / 32) {
   const int rows_valid = shp.M - row0;
   int nchunks = (shp.N - n0 + 31) / 32;
-  if (nchunks > BN / 32) nchunks = BN / 32;
-  if (nchunks <= 0) return;
+  if (nchunks > c_end) nchunks = c_end;
+  if (nchunks <= c_begin) return;
 #pragma unroll 1
-  for (int c = 0; c < nchunks; ++c) {
+  for (int c = c_begin; c < nchunks; ++c) {
     uint32_t r[32];
     __syncwarp();  // tcgen05.ld is warp-collective
     tmem_ld_32x32(taddr + c * 32, r);

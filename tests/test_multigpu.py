@@ -19,8 +19,9 @@ def test_collectives_2gpu():
     run_case("collectives", _n(2), "cuda")
 
 
-def test_fused_gemm_collectives_2gpu():
-    run_case("fused_gemm", _n(2), "cuda")
+@pytest.mark.parametrize("n", [2, 4])
+def test_fused_gemm_collectives(n):
+    run_case("fused_gemm", _n(n), "cuda")
 
 
 def test_tensor_parallel_matches_unsharded_2gpu():
