@@ -290,6 +290,40 @@ def case_resnet_parallel(rank, world, dev):
         assert _native.read_status() == (0, 0), _native.read_status()
 
 
+def case_sync_bn_partial_fc(rank, world, dev):
+    """SyncBatchNorm over 2 ranks == BatchNorm on the concatenated batch; partial-FC sampling keeps all positives."""
+    import oneflow_b200 as flow
+    torch.manual_seed(0)
+    full = torch.randn(4 * world, 6, 5, 5)
+    w0, b0 = torch.rand(6) + 0.5, torch.randn(6)
+    ref_bn = torch.nn.BatchNorm2d(6)
+    ref_bn.weight.data.copy_(w0); ref_bn.bias.data.copy_(b0)
+    xr = full.clone().requires_grad_()
+    yr = ref_bn(xr)
+    (yr * yr).sum().backward()
+    bn = flow.nn.SyncBatchNorm(6).to(dev)
+    bn.weight.data.copy_(w0); bn.bias.data.copy_(b0)
+    x = full[rank * 4:(rank + 1) * 4].clone().to(dev).requires_grad_()
+    y = bn(x)
+    (y * y).sum().backward()
+    close(y, yr[rank * 4:(rank + 1) * 4], 1e-4, "sync bn forward")
+    close(x.grad, xr.grad[rank * 4:(rank + 1) * 4], 1e-3, "sync bn dx")
+    gw = bn.weight.grad.clone(); dist.all_reduce(gw)
+    close(gw, ref_bn.weight.grad, 1e-3, "sync bn dgamma")
+    close(bn.running_var, ref_bn.running_var, 1e-4, "running var")
+    # partial FC
+    classes, dim, per_rank = 64 * world, 8, 16
+    weight = torch.randn(classes // world, dim).to(dev)
+    label = torch.randint(0, classes, (24,)).to(dev)
+    mapped, sampled, sw = flow.nn.distributed_partial_fc_sample(weight, label, per_rank)
+    assert sw.shape == (per_rank, dim) and sampled.numel() == per_rank
+    assert int(mapped.min()) >= 0 and int(mapped.max()) < per_rank * world
+    gathered = [torch.empty_like(sampled) for _ in range(world)]
+    dist.all_gather(gathered, sampled)
+    allc = torch.cat(gathered)
+    assert torch.equal(allc[mapped], label), "re-mapped labels must point at their classes"
+
+
 def main():
     case, devkind = sys.argv[1], sys.argv[2]
     rank, world, dev = setup(devkind)
@@ -300,6 +334,8 @@ def main():
             case_fused_gemm(rank, world, dev)
         elif case == "tp_matches_single":
             case_tp_matches_single(rank, world, dev)
+        elif case == "sync_bn_partial_fc":
+            case_sync_bn_partial_fc(rank, world, dev)
         elif case == "dlrm_parallel":
             case_dlrm_parallel(rank, world, dev)
         elif case == "resnet_parallel":

@@ -44,3 +44,20 @@ def test_dlrm_two_ranks_match_one_rank_cpu():
 
 def test_resnet_data_parallel_cpu():
     run_case("resnet_parallel", 2)
+
+
+def test_sync_batchnorm_and_partial_fc_cpu():
+    run_case("sync_bn_partial_fc", 2)
+
+
+def test_auto_parallel_chain():
+    from oneflow_b200.framework import auto_parallel as ap
+    # a transformer MLP block with many tokens: the classic answer is column-parallel then row-parallel
+    big = [ap.LinearSpec("w1", 4096, 16384, tokens=8192), ap.LinearSpec("w2", 16384, 4096, tokens=8192)]
+    choices = ap.solve_chain(big, world=4, mem_bytes_per_rank=1.2e9)
+    assert [c.kind for c in choices] == ["column", "row"], [c.kind for c in choices]
+    # small weights, huge batch: plain data parallelism is cheapest
+    small = [ap.LinearSpec("a", 256, 256, tokens=1 << 20), ap.LinearSpec("b", 256, 256, tokens=1 << 20)]
+    assert [c.kind for c in ap.solve_chain(small, world=8)] == ["data", "data"]
+    # one rank: nothing to decide, no communication
+    assert all(c.kind == "data" for c in ap.solve_chain(big, world=1))
