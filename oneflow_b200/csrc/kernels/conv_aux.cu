@@ -365,9 +365,12 @@ upsample2_zero_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, int N,
 
 // cols[(n, oh, ow)][(r * S + s) * Cin + c] = x[n, stride oh + r - pad, stride ow + s - pad, c] (zero outside and in
 // the padding columns up to ldc). For small Cin (the RGB stem), one thread per 8 output columns.
+// CIN_ / R_ / S_ > 0 fix the shape at compile time (constant divisors); 0 takes the runtime values.
+template <int CIN_, int R_, int S_>
 __global__ void __launch_bounds__(256)
-im2col_small_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, int N, int H, int W, int Cin, int R, int S, int stride, int pad,
-                    int OH, int OW, int ldc) {
+im2col_small_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, int N, int H, int W, int Cin_rt, int R_rt, int S_rt, int stride,
+                    int pad, int OH, int OW, int ldc) {
+  const int Cin = CIN_ > 0 ? CIN_ : Cin_rt, R = R_ > 0 ? R_ : R_rt, S = S_ > 0 ? S_ : S_rt;
   const int vpr = ldc >> 3;
   const long long total = static_cast<long long>(N) * OH * OW * vpr;
   const int kcols = R * S * Cin;
@@ -505,8 +508,11 @@ OFB_API int ofb_im2col_small(const void* x, void* cols, int N, int H, int W, int
                              void* stream) {
   if (ldc % 8 || ldc < R * S * Cin) return fail("im2col: leading dimension must be a multiple of 8 covering R S Cin");
   const int OH = (H + 2 * pad - R) / stride + 1, OW = (W + 2 * pad - S) / stride + 1;
-  im2col_small_kernel<<<aux_grid((long long)N * OH * OW * (ldc / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)cols, N, H, W, Cin,
-                                                                                                    R, S, stride, pad, OH, OW, ldc);
+  const int grid = aux_grid((long long)N * OH * OW * (ldc / 8));
+  if (Cin == 3 && R == 7 && S == 7)
+    im2col_small_kernel<3, 7, 7><<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)cols, N, H, W, Cin, R, S, stride, pad, OH, OW, ldc);
+  else
+    im2col_small_kernel<0, 0, 0><<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)cols, N, H, W, Cin, R, S, stride, pad, OH, OW, ldc);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

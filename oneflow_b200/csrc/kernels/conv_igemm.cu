@@ -48,11 +48,11 @@ __device__ __forceinline__ void conv_tile_origin(const ConvGeom& g, int t, int p
   n0 = tn * bn;
 }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(192, 1)
+template <int MODE, int BN, int ST = 0, int MINB = 1>
+__global__ void __launch_bounds__(192, MINB)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, ConvGeom g, GemmEpilogue ep,
                   int* status) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, ST>;
   constexpr int BM = 128, BK = 64, STAGES = Cfg::STAGES;
   constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
   constexpr int A_MN = MODE == kConvWgrad ? 1 : 0;
@@ -325,11 +325,11 @@ static void conv_pick_box(int W, int H, int pixels, int* lbw, int* lbh) {
   *lbh = h;
 }
 
-template <int MODE, int BN>
+template <int MODE, int BN, int ST = 0, int MINB = 1>
 static int conv_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const ConvGeom& g, const GemmEpilogue& ep, int units,
                        cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = conv_igemm_kernel<MODE, BN>;
+  using Cfg = GemmCfg<BN, ST>;
+  auto kern = conv_igemm_kernel<MODE, BN, ST, MINB>;
   static bool configured = false;
   if (!configured) {
     OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -341,7 +341,7 @@ static int conv_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Con
     OFB_CUDA_OK(cudaGetDevice(&dev));
     OFB_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const int grid = units < sm_count ? units : sm_count;
+  const int grid = units < sm_count * MINB ? units : sm_count * MINB;
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, g, ep, device_status_ptr());
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -372,6 +372,8 @@ OFB_API int ofb_conv_fprop(const void* x, const void* w, void* y, int N, int H, 
   std::memset(&ep, 0, sizeof(ep));
   ep.C = y; ep.ldc = Cout; ep.alpha = 1.f;
   const int units = g.tiles_w * g.tiles_h * g.tiles_n * ((Cout + bnt - 1) / bnt);
+  // few K blocks: the accumulator drain bounds the tile rate, two CTAs per SM (short ring) double it
+  if (bnt == 128 && R * S * (Cin / 64) <= 18 && units >= 4 * 148) return conv_launch<kConvFprop, 128, 2, 2>(tmA, tmB, g, ep, units, stream);
   return bnt == 256 ? conv_launch<kConvFprop, 256>(tmA, tmB, g, ep, units, stream) : conv_launch<kConvFprop, 128>(tmA, tmB, g, ep, units, stream);
 }
 
@@ -394,6 +396,7 @@ OFB_API int ofb_conv_dgrad(const void* dy, const void* w, void* dx, int N, int H
   ep.C = dx; ep.ldc = Cin; ep.alpha = 1.f;
   const int bnt = Cin >= 256 ? 256 : 128;
   const int units = g.tiles_w * g.tiles_h * g.tiles_n * ((Cin + bnt - 1) / bnt);
+  if (bnt == 128 && R * S * (Cout / 64) <= 18 && units >= 4 * 148) return conv_launch<kConvDgrad, 128, 2, 2>(tmA, tmB, g, ep, units, stream);
   return bnt == 256 ? conv_launch<kConvDgrad, 256>(tmA, tmB, g, ep, units, stream) : conv_launch<kConvDgrad, 128>(tmA, tmB, g, ep, units, stream);
 }
 

@@ -85,7 +85,8 @@ class _Conv:
             y = N.subsample2(y)
         return y
 
-    def bwd(self, dy, need_dx=True):
+    def bwd(self, dy, need_dx=True, residual=None):
+        """``residual`` (shape of the input gradient) is added to the returned gradient."""
         st = self.net.store
         w = st.p[self.name]
         if self.stride == 2 and self.k > 1:
@@ -93,9 +94,12 @@ class _Conv:
         C.conv_wgrad(self.x, dy, (self.k, self.k), out=st.g[self.name], accumulate=st.acc_flag(self.name))
         dx = None
         if need_dx:
-            dx = C.conv_dgrad(dy, w)
+            fuse = residual is not None and not (self.stride == 2 and self.k == 1)
+            dx = C.conv_dgrad(dy, w, residual if fuse else None)
             if self.stride == 2 and self.k == 1:
                 dx = N.upsample2_zero(dx, self.in_shape)
+            if residual is not None and not fuse:
+                dx = K.bias_mask_scale(dx, None, None, 1.0, addend=residual)
         self.x = None
         return dx
 
@@ -158,11 +162,10 @@ class _Bottleneck:
         d, _ = self.bn2.bwd(d)
         d = self.conv2.bwd(d)
         d, _ = self.bn1.bwd(d)
-        d = self.conv1.bwd(d)
         if self.down is not None:
             dd, _ = self.down[1].bwd(dres)
             dres = self.down[0].bwd(dd)
-        return K.bias_mask_scale(d, None, None, 1.0, addend=dres)
+        return self.conv1.bwd(d, residual=dres)     # identity-branch gradient added in the dgrad GEMM epilogue
 
 
 class ResNet:

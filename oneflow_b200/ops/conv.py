@@ -51,12 +51,15 @@ def conv_fprop(x, w):
     return y
 
 
-def conv_dgrad(dy, w):
-    """Gradient of conv_fprop wrt x."""
+def conv_dgrad(dy, w, residual=None):
+    """Gradient of conv_fprop wrt x (+ ``residual`` of the same shape, added in the GEMM epilogue for 1x1 filters)."""
     N, H, W, Cout = dy.shape
     _, R, S, Cin = w.shape
     if R == 1 and S == 1:
-        return G.gemm(dy.reshape(-1, Cout), w.reshape(Cout, Cin), b_layout="kn").view(N, H, W, Cin)
+        res2d = residual.reshape(-1, Cin) if residual is not None else None
+        return G.gemm(dy.reshape(-1, Cout), w.reshape(Cout, Cin), b_layout="kn", residual=res2d).view(N, H, W, Cin)
+    if residual is not None:
+        return K.bias_mask_scale(conv_dgrad(dy, w), None, None, 1.0, addend=residual)
     if not _igemm_ok(dy, w):
         if dy.is_cuda:
             raise ValueError("conv_dgrad: unsupported shape on CUDA")
