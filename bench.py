@@ -335,11 +335,11 @@ def main():
 
     tp, pp = args.tp, args.pp
     if tp == 0 or pp == 0:
-        # BASELINE config: TP=4 x PP=2 at 8 GPUs; smaller degrees below that.
+        # headline configuration: TP=4 x PP=2 at 8 GPUs; smaller degrees below that.
         tp, pp = {1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (4, 2)}.get(world, (world, 1))
     is_bert = args.workload == "bert-large"
     if is_bert:
-        # BASELINE config: 2-D placement DP=2 x TP=4 at 8 GPUs, micro-batch 32 per data-parallel rank
+        # headline configuration: 2-D placement DP=2 x TP=4 at 8 GPUs, micro-batch 32 per data-parallel rank
         tp, pp = (args.tp or min(world, 4)), 1
         args.micro_batch = 32
     dp = world // (tp * pp)

@@ -13,7 +13,7 @@ import oneflow.nn as nn
 
 
 def mlp_config1(tmp):
-    """BASELINE config 1: 2-layer MLP 784->512->10 fp32 ReLU, params broadcast on cpu[0,1], input split(0),
+    """Two-rank CPU training check: 2-layer MLP 784->512->10 fp32 ReLU, params broadcast on cpu[0,1], input split(0),
     nn.Graph + SGD lr 0.1 + cross-entropy, seed 0, 20 steps, then save/load round trip."""
     rank, world = flow.env.get_rank(), flow.env.get_world_size()
     torch.manual_seed(0)

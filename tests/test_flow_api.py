@@ -1,4 +1,4 @@
-"""The flow API on CPU ranks: global tensors, exhaustive boxing, SBP signatures, nn.Graph (BASELINE config 1,
+"""The flow API on CPU ranks: global tensors, exhaustive boxing, SBP signatures, nn.Graph (the two-rank MLP training check,
 gradient accumulation, ZeRO, pipeline stages), DDP, flow.comm — each case runs as real processes under the
 launcher (gloo), the way the reference runs its multi-rank tests."""
 import os
