@@ -11,7 +11,7 @@ from . import functional, init  # noqa: F401
 
 from . import graph, module_ext, parallel, utils  # noqa: F401
 from .graph import Graph  # noqa: F401
-from .modules import FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
+from .modules import Conv2d, FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
 from .extra_modules import (CombinedMarginLoss, FusedBatchNorm1d, FusedBatchNorm2d, FusedBatchNorm3d, MinMaxObserver,  # noqa: F401
                             MovingAverageMinMaxObserver, FakeQuantization, Quantization)
 

@@ -1,3 +1,4 @@
 from .fused_mlp import FusedMLP, fused_linear_act  # noqa: F401
 from .partial_fc import distributed_partial_fc_sample  # noqa: F401
 from .sync_batchnorm import SyncBatchNorm  # noqa: F401
+from .conv import Conv2d, conv2d  # noqa: F401

@@ -305,3 +305,26 @@ def test_conv_implicit_gemm(N, H, W, Cin, Cout, R):
     assert (dw2 - 2 * w32.grad).abs().max().item() <= 2e-2 * scale + 2e-3
     torch.cuda.synchronize()
     assert _native.read_status() == (0, 0)
+
+
+def test_flow_conv2d_channels_last_uses_igemm():
+    import oneflow_b200 as flow
+    torch.manual_seed(0)
+    conv = flow.nn.Conv2d(64, 128, 3, padding=1, bias=True).cuda().bfloat16().to(memory_format=torch.channels_last)
+    x = torch.randn(4, 64, 20, 20, device="cuda").bfloat16().to(memory_format=torch.channels_last).requires_grad_()
+    n0 = K.launch_count
+    y = conv(x)
+    assert K.launch_count == n0 + 1, "the eligible convolution must run on the implicit-GEMM kernel"
+    assert y.shape == (4, 128, 20, 20) and y.is_contiguous(memory_format=torch.channels_last)
+    ref = torch.nn.functional.conv2d(x.detach().float(), conv.weight.detach().float(), conv.bias.detach().float(), padding=1)
+    torch.testing.assert_close(y.float(), ref, atol=5e-2, rtol=3e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = conv.weight.detach().float().requires_grad_()
+    torch.nn.functional.conv2d(xr, wr, None, padding=1).backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=8e-2, rtol=3e-2)
+    assert (conv.weight.grad.float() - wr.grad).abs().max() <= 2e-2 * wr.grad.abs().max() + 1e-2
+    # a strided convolution takes the library path and still works
+    conv2 = flow.nn.Conv2d(64, 64, 3, stride=2, padding=1).cuda().bfloat16()
+    assert conv2(x.detach()).shape == (4, 64, 10, 10)
