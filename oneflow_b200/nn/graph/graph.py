@@ -284,9 +284,53 @@ class Graph:
                 new = GT.rebox(p.detach(), nd)
                 p._local, p._nd_sbp = new._local, new._nd_sbp
 
+    def _apply_auto_parallel(self, args):
+        """``config.enable_auto_parallel``: the Linear layers whose weights are still fully broadcast on a 1-D placement
+        get the SBP signatures that the chain solver of framework/auto_parallel.py finds cheapest (data, column or row
+        parallel); the dispatch rules insert the boxing between them."""
+        if not self.config.auto_parallel:
+            return
+        from ...framework import auto_parallel as AP
+        tokens = None
+        for a in args:
+            if isinstance(a, GT.GlobalTensor) and a.dim() >= 2:
+                tokens = int(a.numel() // a.shape[-1])
+                break
+        if tokens is None:
+            return
+        specs, mods = [], {}
+        for blk in self._blocks.values():
+            root = blk.origin if hasattr(blk, "origin") else blk
+            if not isinstance(root, torch.nn.Module):
+                continue
+            for name, m in root.named_modules():
+                w = getattr(m, "weight", None)
+                if isinstance(m, torch.nn.Linear) and isinstance(w, GT.GlobalTensor) and len(w.placement.hierarchy) == 1 and \
+                        w.placement.hierarchy[0] > 1 and all(s_.kind == "B" for s_ in w.sbp):
+                    key = f"{id(root)}.{name}"
+                    specs.append(AP.LinearSpec(key, m.in_features, m.out_features, tokens, w.element_size()))
+                    mods[key] = m
+        if not specs:
+            return
+        world = next(iter(mods.values())).weight.placement.hierarchy[0]
+        ratio = float(self.config.extra.get("auto_parallel_computation_cost_ratio", 1.0) or 1.0)
+        choices = AP.solve_chain(specs, world, flops_per_s=1.4e15 / max(ratio, 1e-6))
+        for c in choices:
+            m = mods[c.name]
+            if c.kind == "data":
+                continue
+            w = m.weight
+            new = GT.rebox(w.detach(), [S.split(0) if c.kind == "column" else S.split(1)])
+            w._local, w._nd_sbp = new._local, new._nd_sbp
+            if m.bias is not None and c.kind == "column":
+                nb = GT.rebox(m.bias.detach(), [S.split(0)])
+                m.bias._local, m.bias._nd_sbp = nb._local, nb._nd_sbp
+        self._auto_parallel_choices = [(c.name.split(".", 1)[1], c.kind) for c in choices]
+
     def _compile(self, args):
         if Graph._nesting > 0:
             raise RuntimeError("nn.Graph objects cannot be nested")
+        self._apply_auto_parallel(args)
         self._apply_zero()
         self._compiled = True
         if self._pending_state is not None:

@@ -296,11 +296,60 @@ def ddp_and_comm(tmp):
         print("DDP COMM OK")
 
 
+def auto_parallel_graph(tmp):
+    """nn.Graph with config.enable_auto_parallel: the solver shards the big Linear layers, losses match the
+    fully replicated run."""
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    P = flow.placement("cpu", list(range(world)))
+
+    def run(auto):
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Linear(256, 2048), nn.ReLU(), nn.Linear(2048, 256))
+        model.to_global(P, flow.sbp.broadcast)
+        opt = flow.optim.SGD(model.parameters(), lr=0.05)
+        g = torch.Generator().manual_seed(1)
+        x = flow.tensor(torch.randn(16, 256, generator=g), placement=P, sbp=flow.sbp.broadcast)
+        y = flow.tensor(torch.randn(16, 256, generator=g), placement=P, sbp=flow.sbp.broadcast)
+
+        class G(nn.Graph):
+            def __init__(self):
+                super().__init__()
+                self.model = model
+                self.add_optimizer(opt)
+                if auto:
+                    self.config.enable_auto_parallel(True)
+                    self.config.set_auto_parallel_computation_cost_ratio(1e-4)   # tiny test layers: make compute matter
+
+            def build(self, a, b):
+                loss = ((self.model(a) - b) ** 2).mean()
+                loss.backward()
+                return loss
+
+        graph = G()
+        out = []
+        for _ in range(4):
+            l = graph(x, y)
+            l = l.to_global(P, flow.sbp.broadcast).to_local() if hasattr(l, "to_global") else l
+            out.append(float(l))
+        return out, getattr(graph, "_auto_parallel_choices", None), model
+
+    base, _, _ = run(False)
+    auto, choices, model = run(True)
+    assert choices is not None and any(k != "data" for _, k in choices), choices
+    w0 = model[0].weight
+    assert any(s.kind == "S" for s in w0.sbp) or any(s.kind == "S" for s in model[2].weight.sbp)
+    for a, b in zip(base, auto):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(a)), (base, auto, choices)
+    assert auto[-1] < auto[0]
+    if rank == 0:
+        print("AUTO PARALLEL", choices, auto)
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
     {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
-     "ddp_comm": ddp_and_comm}[case](tmp)
+     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph}[case](tmp)
     flow.comm.barrier()
     if flow.env.get_rank() == 0:
         print(f"CASE {case} OK")

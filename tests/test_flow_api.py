@@ -24,7 +24,7 @@ def launch(case, nproc, timeout=900):
     assert p.returncode == 0 and f"CASE {case} OK" in p.stdout, p.stdout[-4000:]
 
 
-def test_baseline_config1_mlp_graph_sgd_two_cpu_ranks():
+def test_mlp_graph_sgd_two_cpu_ranks():
     launch("mlp_config1", 2)
 
 
@@ -43,6 +43,10 @@ def test_graph_features():
 
 def test_ddp_and_comm():
     launch("ddp_comm", 2)
+
+
+def test_graph_auto_parallel():
+    launch("auto_parallel", 2)
 
 
 def test_launcher_kills_group_on_failure(tmp_path):
