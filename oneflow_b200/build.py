@@ -94,8 +94,24 @@ def build_core(verbose=False):
     return lib
 
 
+def build_api(verbose=False):
+    """C++ inference API (csrc/api) on top of libofb_kernels.so."""
+    srcs = sorted(glob.glob(os.path.join(CSRC, "api", "*.cpp")))
+    if not srcs:
+        return None
+    headers = glob.glob(os.path.join(CSRC, "api", "*.h")) + [os.path.join(CSRC, "kernels", "ofb_kernels.h")]
+    lib = os.path.join(LIB, "libofb_api.so")
+    kern = os.path.join(LIB, "libofb_kernels.so")
+    if os.path.exists(lib) and not any(_newer(s, lib, headers + [kern]) for s in srcs):
+        return lib
+    _run([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", lib] + srcs +
+         ["-L", LIB, "-lofb_kernels", "-lcudart", "-Xlinker", "-rpath=$ORIGIN"], os.path.join(OBJ, "api.log"))
+    print(f"[build] built {os.path.relpath(lib, ROOT)}", flush=True)
+    return lib
+
+
 def build_all(verbose=False):
-    return [build_kernels(verbose), build_core(verbose)]
+    return [build_kernels(verbose), build_core(verbose), build_api(verbose)]
 
 
 if __name__ == "__main__":
