@@ -146,6 +146,9 @@ class DLRMTrainer:
         self._tids = None
         self.keep_trace = False     # tests: keep the last step's activations and activation gradients
         self.trace = None
+        # the embedding shuffles run on their own stream, next to the bottom MLP (forward) and its gradients + the
+        # dense optimizer (backward), like the reference's dedicated <name>_EMBEDDING / _ID_SHUFFLE streams
+        self.emb_stream = torch.cuda.Stream(device=self.device) if self.engine is not None else None
 
     # ------------------------------------------------------------------ pieces
     def _emb_forward(self, ids):
@@ -194,6 +197,8 @@ class DLRMTrainer:
         """Inference: click probabilities [B]."""
         x0 = K.cast_scale(dense, out_dtype=torch.bfloat16)
         bottom = self._mlp_forward("bottom", x0, len(self.bottom_dims) - 1, True)
+        if self.emb_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.emb_stream)   # a row update may still be running there
         emb, _ = self._emb_forward(ids)
         z = K.interaction_fwd(bottom[-1], emb, False, self.cfg.interaction_dim)
         top = self._mlp_forward("top", z, len(self.top_dims) - 1, False)
@@ -207,9 +212,20 @@ class DLRMTrainer:
         self.steps += 1
         self.store.start_accumulation()
         nb, nt = len(self.bottom_dims) - 1, len(self.top_dims) - 1
+        side = self.emb_stream
+        if side is not None:
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)                      # ids are ready; the previous step's row update is on `side` already
+            with torch.cuda.stream(side):
+                emb, plan = self._emb_forward(ids)
+            ids.record_stream(side)
         x0 = K.cast_scale(dense, out_dtype=torch.bfloat16)
         bottom = self._mlp_forward("bottom", x0, nb, True)
-        emb, plan = self._emb_forward(ids)
+        if side is not None:
+            main.wait_stream(side)
+            emb.record_stream(main)
+        else:
+            emb, plan = self._emb_forward(ids)
         z = K.interaction_fwd(bottom[-1], emb, False, cfg.interaction_dim)
         top = self._mlp_forward("top", z, nt, False)
         loss, dlogits = K.bce_logits(top[-1], labels, loss_scale=1.0 / B, grad_scale=1.0 / B)
@@ -217,7 +233,13 @@ class DLRMTrainer:
         d_dense, d_sparse = K.interaction_bwd(bottom[-1], emb, dz, False)
         if self.keep_trace:
             self.trace = {"emb": emb, "d_sparse": d_sparse, "logits": top[-1][:, 0], "d_dense": d_dense, "dz": dz, "bottom": bottom[-1]}
-        self._emb_backward(d_sparse, plan)
+        if side is not None:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self._emb_backward(d_sparse, plan)
+            d_sparse.record_stream(side)
+        else:
+            self._emb_backward(d_sparse, plan)
         # ReLU' of the bottom MLP's output, then its layers
         d_bottom = K.bias_act_bwd(bottom[-1], None, d_dense, 3)
         self._mlp_backward("bottom", bottom, d_bottom, nb, need_dx=False)
