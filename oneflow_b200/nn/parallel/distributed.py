@@ -74,15 +74,13 @@ class DistributedDataParallel(torch.nn.Module):
 
     def _device_coll(self, device):
         if self._coll is None:
-            try:
+            if self.world > 8:
+                self._coll = False          # the peer-memory collectives address one node (8 GPUs): larger groups use NCCL
+            else:
+                # a missing kernel library or a failed peer mapping raises: no silent switch to another path on a GPU
                 from ...comm.symmetric import DeviceCollectives, SymmetricArena
-                from ...ops import _native
-                if not _native.kernels_available():
-                    raise RuntimeError
                 arena = SymmetricArena(None, list(range(self.world)), device, 3 * (64 << 20) + (1 << 22))
                 self._coll = DeviceCollectives(arena, io_bytes=64 << 20)
-            except Exception:
-                self._coll = False
         return self._coll or None
 
     def finish_pending(self):

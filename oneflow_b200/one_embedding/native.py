@@ -51,12 +51,13 @@ def _pow2(n):
 
 
 def available(device) -> bool:
+    """True on CUDA devices. A missing or stale kernel library raises there instead of silently selecting the
+    tensor-op path."""
     if torch.device(device).type != "cuda":
         return False
-    try:
-        return hasattr(_native.kernels(), "ofb_emb_forward")
-    except Exception:
-        return False
+    if not hasattr(_native.kernels(), "ofb_emb_forward"):
+        raise _native.NativeLibraryError("libofb_kernels.so lacks the embedding kernels: rebuild with python -m oneflow_b200.build")
+    return True
 
 
 class NativeEmbeddingEngine:

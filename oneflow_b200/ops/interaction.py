@@ -27,10 +27,7 @@ def dot_feature_interaction_reference(features, output_concat=None, self_interac
 def dot_feature_interaction(features, output_concat=None, self_interaction=False, output_padding=0, pooling="none"):
     x0 = features[0]
     if x0.is_cuda and x0.dtype == torch.bfloat16 and pooling == "none":
-        try:
-            from .interaction_native import dot_feature_interaction_native
-        except ImportError:
-            dot_feature_interaction_native = None
-        if dot_feature_interaction_native is not None:
-            return dot_feature_interaction_native(features, output_concat, self_interaction, output_padding)
+        # CUDA bf16 inputs always take the native kernels: a missing kernel library raises instead of falling back
+        from .interaction_native import dot_feature_interaction_native
+        return dot_feature_interaction_native(features, output_concat, self_interaction, output_padding)
     return dot_feature_interaction_reference(features, output_concat, self_interaction, output_padding, pooling)
