@@ -348,7 +348,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                                         static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
       uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
       long long i = v0 + ct;
-      // 8 independent 16-byte loads in flight per thread before the first store
+      // 8 independent 16-byte loads in flight per thread before the first store (16 measured slower at TP4: the
+      // deeper read queue competes with the TMA loads of the MMA loop)
       for (; i + 7 * 64 < v1; i += 8 * 64) {
         uint4 t[8];
 #pragma unroll
