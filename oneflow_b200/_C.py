@@ -190,6 +190,9 @@ def local_all_reduce(x, inplace=False):
     return comm.all_reduce(t)
 
 
+from ._C_extra import *  # noqa: F401,F403,E402  (the long tail of fused functions)
+
+
 def __getattr__(name):
     if hasattr(torch, name):
         return getattr(torch, name)

@@ -1,0 +1,90 @@
+"""The long tail of flow._C fused functions against their straightforward statements (CPU)."""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from oneflow_b200 import _C
+
+
+def test_fused_glu_modes():
+    torch.manual_seed(0)
+    x, w, b = torch.randn(5, 16), torch.randn(24, 16), torch.randn(24)
+    y = _C.fused_glu(x, w, b, activation="silu")
+    h, g = (x @ w.t() + b).chunk(2, -1)
+    torch.testing.assert_close(y, h * F.silu(g))
+    v, c = torch.randn(12, 16), torch.randn(12)
+    y2 = _C.fused_glu(x, w[:12], b[:12], v, c, activation="gelu")
+    torch.testing.assert_close(y2, (x @ w[:12].t() + b[:12]) * F.gelu(x @ v.t() + c))
+
+
+def test_norm_family():
+    torch.manual_seed(1)
+    x, skip, bias, gamma, beta = torch.randn(4, 32), torch.randn(4, 32), torch.randn(32), torch.rand(32), torch.randn(32)
+    y = _C.skip_layer_norm(x, gamma=gamma, beta=beta, bias=bias, skip=skip, epsilon=1e-5, alpha=0.5)
+    torch.testing.assert_close(y, F.layer_norm(x + bias + 0.5 * skip, (32,), gamma, beta, 1e-5))
+    r = _C.rms_norm(x, gamma, (32,), 1e-6)
+    torch.testing.assert_close(r, x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6) * gamma)
+    torch.testing.assert_close(_C.rms_layer_norm(x, gamma, 1e-6), r)
+    torch.testing.assert_close(_C.skip_rms_norm(x, weight=gamma, skip=skip, alpha=1.0, epsilon=1e-6), _C.rms_norm(x + skip, gamma, (32,), 1e-6))
+
+
+def test_cross_interaction_weighted_sum_clip():
+    torch.manual_seed(2)
+    x, x0, w, b = torch.randn(6, 8), torch.randn(6, 8), torch.randn(1, 8), torch.randn(8)
+    torch.testing.assert_close(_C.fused_cross_feature_interaction(x, w, x0, b, "vector"), (x @ w.t()) * x0 + b + x)
+    W = torch.randn(8, 8)
+    torch.testing.assert_close(_C.fused_cross_feature_interaction(x, W, x0, b, "matrix"), (x @ W.t() + b) * x0 + x)
+    ts = [torch.randn(3, 4) for _ in range(3)]
+    torch.testing.assert_close(_C.fused_weighted_sum(ts, [0.1, 0.2, 0.3], 2.0), 2.0 * (0.1 * ts[0] + 0.2 * ts[1] + 0.3 * ts[2]))
+    grads = [torch.randn(10), torch.randn(5, 5)]
+    norm = torch.cat([g.flatten() for g in grads]).norm()
+    total = _C.fused_clip_grad(grads, 1.0, 2.0)
+    torch.testing.assert_close(total, norm)
+    assert abs(torch.cat([g.flatten() for g in grads]).norm().item() - 1.0) < 1e-3
+    torch.testing.assert_close(_C.fused_fast_gelu_mul(x, x0), F.gelu(x, approximate="tanh") * x0)
+
+
+def test_attention_helpers_and_rotary():
+    torch.manual_seed(3)
+    s = torch.randn(2, 3, 5, 5)
+    t = _C.fused_scale_tril(s, 0, -1e4, 0.5)
+    assert torch.all(t[..., 0, 1:] == -1e4) and torch.allclose(t[..., 2, :3], s[..., 2, :3] * 0.5)
+    hs = torch.randn(7, 2, 3 * 4 * 8)
+    qk, v = _C.fused_self_attention(hs, head_size=8, alpha=0.25)
+    assert qk.shape == (2, 4, 7, 7) and v.shape == (7, 2, 32)
+    q = hs.view(7, 2, 4, 3, 8)[..., 0, :]
+    k = hs.view(7, 2, 4, 3, 8)[..., 1, :]
+    torch.testing.assert_close(qk[1, 2], 0.25 * q[:, 1, 2] @ k[:, 1, 2].t())
+    # rotary embedding preserves norms and is the identity at position 0
+    x = torch.randn(2, 4, 6, 16)
+    y = _C.fused_apply_rotary_emb(x, x_layout="BHMK", mode="plane")
+    torch.testing.assert_close(y.norm(dim=-1), x.norm(dim=-1))
+    torch.testing.assert_close(y[:, :, 0], x[:, :, 0])
+    yi = _C.fused_apply_rotary_emb(x, x_layout="BHMK", mode="interval")
+    torch.testing.assert_close(yi.norm(dim=-1), x.norm(dim=-1))
+    pk, pv = torch.randn(2, 4, 3, 8), torch.randn(2, 4, 3, 8)
+    k2, v2 = _C.fused_attention_concat_past_key_value(past_key=pk, past_key_layout="BHMK", past_value=pv, past_value_layout="BHMK",
+                                                     key=torch.randn(2, 4, 1, 8), key_layout="BHMK", value=torch.randn(2, 4, 1, 8),
+                                                     value_layout="BHMK")
+    assert k2.shape == (2, 4, 4, 8) and v2.shape == (2, 4, 4, 8)
+
+
+def test_box_iou_family():
+    torch.manual_seed(4)
+    x1, y1, x2, y2 = torch.rand(8), torch.rand(8), torch.rand(8), torch.rand(8)
+    w1, h1, w2, h2 = torch.rand(8) + 0.1, torch.rand(8) + 0.1, torch.rand(8) + 0.1, torch.rand(8) + 0.1
+    b = _C.fused_get_boundding_boxes_coord(x1, y1, w1, h1, x2, y2, w2, h2)
+    b1_x1, b1_x2, b1_y1, b1_y2, b2_x1, b2_x2, b2_y1, b2_y2 = b
+    inter = _C.fused_get_intersection_area(b1_x1, b1_x2, b2_x1, b2_x2, b1_y1, b1_y2, b2_y1, b2_y2)
+    iou = _C.fused_get_iou(w1, h1, w2, h2, inter, 1e-7)
+    assert torch.all((iou >= 0) & (iou <= 1 + 1e-5))
+    same = _C.fused_get_iou(w1, h1, w1, h1, w1 * h1, 0.0)
+    torch.testing.assert_close(same, torch.ones(8))
+    c2 = _C.fused_get_convex_diagonal_squared(b1_x1, b1_x2, b2_x1, b2_x2, b1_y1, b1_y2, b2_y1, b2_y2, 1e-8)
+    rho2 = _C.fused_get_center_dist(b1_x1, b1_x2, b2_x1, b2_x2, b1_y1, b1_y2, b2_y1, b2_y2)
+    torch.testing.assert_close(rho2, (x2 - x1) ** 2 + (y2 - y1) ** 2)
+    v = _C.fused_get_ciou_diagonal_angle(w1, h1, w2, h2, 1e-8)
+    y, alpha = _C.fused_get_ciou_result(v, iou, rho2, c2, 1e-7)
+    torch.testing.assert_close(y, iou - (rho2 / c2 + v * (v / (v - iou + 1 + 1e-7))))
+    assert torch.all(c2 >= rho2 - 1e-6)
