@@ -155,7 +155,9 @@ class BertStage:
         if tp is None:
             qkv = G.gemm(x, self._p(p + "wqkv"), bias=self._p(p + "bqkv"))
         else:
-            qkv = tp.ag_gemm(x, self._p(p + "wqkv"), bias=self._p(p + "bqkv"))
+            # gathered inputs are kept for the weight gradients (a copy is cheaper than a second gather)
+            x_g, qkv = tp.ag_gemm(x, self._p(p + "wqkv"), bias=self._p(p + "bqkv"), return_gathered=True)
+            x_full = x_g.clone() if x_g.is_cuda else x_g
         q5 = qkv.view(B, S, 3, Hl, D)
         attn, lse = K.fmha_fwd(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], causal=False, kv_len=kv_len)
         a2 = attn.view(B * S, Hl * D)
@@ -168,16 +170,17 @@ class BertStage:
             a, h1 = G.gemm(x1, self._p(p + "w1"), bias=self._p(p + "b1"), act=G.ACT_GELU, want_aux=True)
             y2 = G.gemm(a, self._p(p + "w2"), bias=self._p(p + "b2"), residual=x1)
         else:
-            a, h1 = tp.ag_gemm(x1, self._p(p + "w1"), bias=self._p(p + "b1"), act=G.ACT_GELU, want_aux=True)
+            x1_g, a, h1 = tp.ag_gemm(x1, self._p(p + "w1"), bias=self._p(p + "b1"), act=G.ACT_GELU, want_aux=True, return_gathered=True)
+            x1_full = x1_g.clone() if x1_g.is_cuda else x1_g
             y2 = tp.gemm_rs(a, self._p(p + "w2"), bias=self._p(p + "b2"), residual=x1)
         out, m2, r2 = K.layer_norm_fwd(y2, self._p(p + "ln2.g"), self._p(p + "ln2.b"), cfg.eps)
-        sv[li] = (x, qkv, attn, lse, y1, m1, r1, h1, y2, m2, r2)
+        sv[li] = (x, qkv, attn, lse, y1, m1, r1, h1, y2, m2, r2) + ((x_full, x1_full) if tp is not None else (None, None))
         return out
 
     def _layer_bwd(self, li, dout, B, S, kv_len, sv):
         cfg, p, tp = self.cfg, f"l.{li}.", self.tp
         Hl, D = cfg.heads // self.tp_size, cfg.head_dim
-        x, qkv, attn, lse, y1, m1, r1, h1, y2, m2, r2 = sv.pop(li)
+        x, qkv, attn, lse, y1, m1, r1, h1, y2, m2, r2, x_full, x1_full = sv.pop(li)
         dy2, dg, db = K.layer_norm_bwd(dout, y2, self._p(p + "ln2.g"), m2, r2)
         self._lngrad(p + "ln2.g", p + "ln2.b", dg, db)
         a = K.bias_act_fwd(h1, None, G.ACT_GELU)
@@ -189,15 +192,17 @@ class BertStage:
             dy2_full, dh1 = tp.ag_gemm(dy2, self._p(p + "w2"), b_layout="kn", aux_in=h1, act=G.ACT_GELU, return_gathered=True)
             self._wgrad(p + "w2", dy2_full, a)
         del a, h1
-        x1, _, _ = K.layer_norm_fwd(y1, self._p(p + "ln1.g"), self._p(p + "ln1.b"), cfg.eps)
         self._bgrad(p + "b1", dh1)
         if tp is None:
+            x1, _, _ = K.layer_norm_fwd(y1, self._p(p + "ln1.g"), self._p(p + "ln1.b"), cfg.eps)
             self._wgrad(p + "w1", dh1, x1)
             dx1 = G.gemm(dh1, self._p(p + "w1"), b_layout="kn", residual=dy2)
+            del x1
         else:
-            self._wgrad(p + "w1", dh1, tp.all_gather_rows(x1))
+            self._wgrad(p + "w1", dh1, x1_full)
             dx1 = tp.gemm_rs(dh1, self._p(p + "w1"), b_layout="kn", residual=dy2)
-        del dh1, x1
+            del x1_full
+        del dh1
         dy1, dg, db = K.layer_norm_bwd(dx1, y1, self._p(p + "ln1.g"), m1, r1)
         self._lngrad(p + "ln1.g", p + "ln1.b", dg, db)
         a2 = attn.view(B * S, Hl * D)
@@ -218,7 +223,7 @@ class BertStage:
             self._wgrad(p + "wqkv", dqkv, x)
             dx = G.gemm(dqkv, self._p(p + "wqkv"), b_layout="kn", residual=dy1)
         else:
-            self._wgrad(p + "wqkv", dqkv, tp.all_gather_rows(x))
+            self._wgrad(p + "wqkv", dqkv, x_full)
             dx = tp.gemm_rs(dqkv, self._p(p + "wqkv"), b_layout="kn", residual=dy1)
         return dx
 

@@ -228,7 +228,10 @@ class GPTStage:
         if tp is None:
             qkv = G.gemm(ln1, self._p(p + "attn.wqkv"), bias=self._p(p + "attn.bqkv"))
         else:
-            qkv = tp.ag_gemm(ln1, self._p(p + "attn.wqkv"), bias=self._p(p + "attn.bqkv"))
+            # the gathered LayerNorm output is kept for the weight gradient: copying it out of the exchange buffer is
+            # several times cheaper than gathering it again in the backward pass
+            ln1_g, qkv = tp.ag_gemm(ln1, self._p(p + "attn.wqkv"), bias=self._p(p + "attn.bqkv"), return_gathered=True)
+            ln1_full = ln1_g.clone() if ln1_g.is_cuda else ln1_g
         del ln1
         q5 = qkv.view(B, S, 3, Hl, D)
         attn, lse = K.fmha_fwd(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], causal=cfg.causal)
@@ -242,16 +245,18 @@ class GPTStage:
             a, h1 = G.gemm(ln2, self._p(p + "mlp.w1"), bias=self._p(p + "mlp.b1"), act=self.act, want_aux=True)
             y = G.gemm(a, self._p(p + "mlp.w2"), bias=self._p(p + "mlp.b2"), residual=x1)
         else:
-            a, h1 = tp.ag_gemm(ln2, self._p(p + "mlp.w1"), bias=self._p(p + "mlp.b1"), act=self.act, want_aux=True)
+            ln2_g, a, h1 = tp.ag_gemm(ln2, self._p(p + "mlp.w1"), bias=self._p(p + "mlp.b1"), act=self.act, want_aux=True,
+                                      return_gathered=True)
+            ln2_full = ln2_g.clone() if ln2_g.is_cuda else ln2_g
             y = tp.gemm_rs(a, self._p(p + "mlp.w2"), bias=self._p(p + "mlp.b2"), residual=x1)
-        sv[li] = (x, mean1, rstd1, qkv, attn, lse, x1, mean2, rstd2, h1)
+        sv[li] = (x, mean1, rstd1, qkv, attn, lse, x1, mean2, rstd2, h1) + ((ln1_full, ln2_full) if tp is not None else (None, None))
         return y
 
     def _layer_bwd(self, li, dy, B, S, sv):
         cfg, p = self.cfg, f"h.{li}."
         tp = self.tp
         Hl, D = cfg.heads // self.tp_size, cfg.head_dim
-        x, mean1, rstd1, qkv, attn, lse, x1, mean2, rstd2, h1 = sv.pop(li)
+        x, mean1, rstd1, qkv, attn, lse, x1, mean2, rstd2, h1, ln1_full, ln2_full = sv.pop(li)
         # ---- MLP
         a = K.bias_act_fwd(h1, None, self.act)
         self._bgrad(p + "mlp.b2", dy)
@@ -264,15 +269,17 @@ class GPTStage:
             self._wgrad(p + "mlp.w2", dy_full, a)
             del dy_full
         del a, h1
-        ln2, _, _ = K.layer_norm_fwd(x1, self._p(p + "ln2.g"), self._p(p + "ln2.b"), cfg.eps)
         self._bgrad(p + "mlp.b1", dh1)
         if tp is None:
+            ln2, _, _ = K.layer_norm_fwd(x1, self._p(p + "ln2.g"), self._p(p + "ln2.b"), cfg.eps)
             self._wgrad(p + "mlp.w1", dh1, ln2)
             dln2 = G.gemm(dh1, self._p(p + "mlp.w1"), b_layout="kn")
+            del ln2
         else:
-            self._wgrad(p + "mlp.w1", dh1, tp.all_gather_rows(ln2))
+            self._wgrad(p + "mlp.w1", dh1, ln2_full)
             dln2 = tp.gemm_rs(dh1, self._p(p + "mlp.w1"), b_layout="kn")
-        del dh1, ln2
+            del ln2_full
+        del dh1
         dx1, dg, db = K.layer_norm_bwd(dln2, x1, self._p(p + "ln2.g"), mean2, rstd2, add_to_dx=dy)
         self._lngrad(p + "ln2.g", p + "ln2.b", dg, db)
         del dln2, dy
@@ -291,15 +298,17 @@ class GPTStage:
         K.fmha_bwd(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], attn, dattn.view(B, S, Hl, D), lse, causal=cfg.causal, dqkv=dqkv5)
         dqkv = dqkv5.view(B * S, 3 * Hl * D)
         del dattn, attn, qkv
-        ln1, _, _ = K.layer_norm_fwd(x, self._p(p + "ln1.g"), self._p(p + "ln1.b"), cfg.eps)
         self._bgrad(p + "attn.bqkv", dqkv)
         if tp is None:
+            ln1, _, _ = K.layer_norm_fwd(x, self._p(p + "ln1.g"), self._p(p + "ln1.b"), cfg.eps)
             self._wgrad(p + "attn.wqkv", dqkv, ln1)
             dln1 = G.gemm(dqkv, self._p(p + "attn.wqkv"), b_layout="kn")
+            del ln1
         else:
-            self._wgrad(p + "attn.wqkv", dqkv, tp.all_gather_rows(ln1))
+            self._wgrad(p + "attn.wqkv", dqkv, ln1_full)
             dln1 = tp.gemm_rs(dqkv, self._p(p + "attn.wqkv"), b_layout="kn")
-        del dqkv, ln1
+            del ln1_full
+        del dqkv
         dx, dg, db = K.layer_norm_bwd(dln1, x, self._p(p + "ln1.g"), mean1, rstd1, add_to_dx=dx1)
         self._lngrad(p + "ln1.g", p + "ln1.b", dg, db)
         return dx

@@ -144,6 +144,30 @@ def case_gpt_parallel(rank, world, dev, tp, pp, dp):
         assert _native.read_status() == (0, 0), _native.read_status()
 
 
+def case_bert_tp(rank, world, dev):
+    """BERT encoder stack under tensor parallelism (sequence-parallel activations, fused GEMM+collective kernels on
+    CUDA): finite, decreasing loss, identical on all ranks."""
+    from oneflow_b200.models import bert as B
+    from oneflow_b200.parallel.setup import build_gpt_trainer
+    tp = world
+    D = 64 if dev.type == "cuda" else 16
+    cfg = B.BertConfig(vocab_size=512, hidden=2 * D * tp, layers=2, heads=2 * tp, ffn=4 * D * tp, seq_len=128 if dev.type == "cuda" else 32,
+                       max_predictions=8)
+    micro_batch, n_micro = (4 if dev.type == "cuda" else 2), 2
+    tr = build_gpt_trainer(cfg, tp=tp, pp=1, dp=1, micro_batch=micro_batch, n_micro=n_micro, device=dev, lr=2e-3, weight_decay=0.01,
+                           seed=3, stage_cls=B.BertStage)
+    batch = B.make_batch(cfg, micro_batch * n_micro, generator=torch.Generator().manual_seed(9)).to(dev)
+    losses = [float(tr.train_step(batch).item()) for _ in range(5)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+    t = torch.tensor([losses[-1]], dtype=torch.float64, device=dev)
+    dist.all_reduce(t)
+    assert abs(losses[-1] - float(t) / world) < 1e-3 * max(1.0, abs(losses[-1])), (losses, float(t))
+    if dev.type == "cuda":
+        from oneflow_b200.ops import _native
+        torch.cuda.synchronize()
+        assert _native.read_status() == (0, 0), _native.read_status()
+
+
 def case_tp_matches_single(rank, world, dev):
     """Tensor-parallel forward/backward of one stage equals the unsharded stage when the shards are cut from
     the same full weights."""
@@ -334,6 +358,8 @@ def main():
             case_fused_gemm(rank, world, dev)
         elif case == "tp_matches_single":
             case_tp_matches_single(rank, world, dev)
+        elif case == "bert_tp":
+            case_bert_tp(rank, world, dev)
         elif case == "sync_bn_partial_fc":
             case_sync_bn_partial_fc(rank, world, dev)
         elif case == "dlrm_parallel":

@@ -49,3 +49,7 @@ def test_dlrm_two_gpus_match_one_gpu():
 
 def test_resnet_data_parallel_2gpu():
     run_case("resnet_parallel", _n(2), "cuda")
+
+
+def test_bert_tensor_parallel_2gpu():
+    run_case("bert_tp", _n(2), "cuda")

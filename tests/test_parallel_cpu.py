@@ -61,3 +61,7 @@ def test_auto_parallel_chain():
     assert [c.kind for c in ap.solve_chain(small, world=8)] == ["data", "data"]
     # one rank: nothing to decide, no communication
     assert all(c.kind == "data" for c in ap.solve_chain(big, world=1))
+
+
+def test_bert_tensor_parallel_cpu():
+    run_case("bert_tp", 2)
