@@ -238,10 +238,10 @@ emb_resolve_kernel(OfbEmbStore st, EmbCtx c, long long keys_off, long long cnt_o
       ukey = keys[where];
       long long s = static_cast<long long>(slot_hash(static_cast<long long>(ukey))) & tmask;
       for (long long probe = 0; probe <= tmask; ++probe) {
-        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&st.tkeys[s]);
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&st.slots[s].key);
         if (cur == kEmptyKey) {
           if (!insert) break;  // absent and not inserting: the row reads as zeros
-          cur = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
+          cur = atomicCAS(&st.slots[s].key, kEmptyKey, ukey);
           if (cur == kEmptyKey) {
             is_new = true;
             cur = ukey;
@@ -261,18 +261,18 @@ emb_resolve_kernel(OfbEmbStore st, EmbCtx c, long long keys_off, long long cnt_o
     if (is_new) {
       new_row = grouped_count(nmask, 0, st.counters);
       if (new_row < st.row_cap) {
-        st.trow[s_found] = new_row;
+        st.slots[s_found].row = new_row;
         st.row_key[new_row] = ukey;
       } else {
-        st.trow[s_found] = -1;
+        st.slots[s_found].row = -1;
         new_row = -1;
         record(c.status, kStatusHashTableFull, 2);
       }
     }
     // number the rows touched in this step (a key can arrive from several ranks: the first stamp wins)
-    const bool fresh = s_found >= 0 && atomicExch(&st.stamp[s_found], epoch) != epoch;
+    const bool fresh = s_found >= 0 && atomicExch(&st.slots[s_found].stamp, epoch) != epoch;
     const unsigned int umask = __ballot_sync(0xffffffffu, fresh);
-    if (fresh) st.uo_of[s_found] = grouped_count(umask, 0, n_uo);
+    if (fresh) st.slots[s_found].uo = grouped_count(umask, 0, n_uo);
     if (active) slot_tmp[where] = s_found;
     // initialise the new rows, one row per warp pass
     unsigned int todo = __ballot_sync(0xffffffffu, new_row >= 0);
@@ -360,12 +360,21 @@ emb_serve_kernel(OfbEmbStore st, EmbCtx c, long long cnt_off, long long emb_off,
       }
     }
 #pragma unroll
-    for (int u = 0; u < UNR; ++u) row[u] = sl[u] >= 0 ? st.trow[sl[u]] : -1;
+    int uov[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      row[u] = uov[u] = -1;
+      if (sl[u] >= 0) {  // row and touch number sit side by side in the slot: one 8-byte read
+        const int2 q = *reinterpret_cast<const int2*>(&st.slots[sl[u]].row);
+        row[u] = q.x;
+        uov[u] = q.y;
+      }
+    }
     if (lane < UNR) {
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
         if (lane == u && where[u] >= 0) {
-          const int uo = sl[u] >= 0 ? st.uo_of[sl[u]] : -1;
+          const int uo = uov[u];
           rowidx[where[u]] = row[u];
           uoidx[where[u]] = uo;
           if (uo >= 0) u_row[uo] = row[u];
@@ -614,8 +623,8 @@ emb_find_kernel(OfbEmbStore st, const long long* __restrict__ keys, long long n,
     long long s = static_cast<long long>(slot_hash(key)) & tmask;
     int row = -1;
     for (long long probe = 0; probe <= tmask; ++probe) {
-      unsigned long long prev = st.tkeys[s];
-      if (prev == kEmptyKey && insert) prev = atomicCAS(&st.tkeys[s], kEmptyKey, ukey);
+      unsigned long long prev = st.slots[s].key;
+      if (prev == kEmptyKey && insert) prev = atomicCAS(&st.slots[s].key, kEmptyKey, ukey);
       if (prev == kEmptyKey) {
         if (insert) {
           row = atomicAdd(&st.counters[0], 1);
@@ -625,13 +634,13 @@ emb_find_kernel(OfbEmbStore st, const long long* __restrict__ keys, long long n,
             row = -1;
             record(status, kStatusHashTableFull, 4);
           }
-          st.trow[s] = row;
+          st.slots[s].row = row;
         }
         break;
       }
       if (prev == ukey) {
         // a concurrent inserter of the same key may not have published the row yet: callers pass unique keys
-        row = st.trow[s];
+        row = st.slots[s].row;
         break;
       }
       s = (s + 1) & tmask;

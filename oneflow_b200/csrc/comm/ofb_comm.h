@@ -16,11 +16,17 @@ typedef struct OfbCommCtx {
 
 // One rank's shard of an embedding: open-addressing key index (power-of-two `tcap`, empty = all ones) over
 // densely allocated fp32 rows of `line` floats ([weights (dim) | optimizer state]).
+// One slot of the key index: everything a lookup needs sits in one 32-byte sector.
+typedef struct OfbEmbSlot {
+  unsigned long long key;       // all ones = empty
+  int row;                      // row of the key (-1: none)
+  int uo;                       // number of the key among the rows touched in the step `stamp`
+  unsigned int stamp;           // last step that touched the key
+  int pad[3];
+} OfbEmbSlot;
+
 typedef struct OfbEmbStore {
-  unsigned long long* tkeys;    // [tcap]
-  int* trow;                    // [tcap] row of the key
-  unsigned int* stamp;          // [tcap] last step that touched the key
-  int* uo_of;                   // [tcap] number of the key among the rows touched in that step
+  OfbEmbSlot* slots;            // [tcap]
   float* rows;                  // [row_cap][line]
   unsigned long long* row_key;  // [row_cap] key of each row (snapshots)
   int* counters;                // [0] rows in use

@@ -21,7 +21,8 @@
 namespace ofb {
 
 constexpr int kMaxTensors = 48;
-constexpr int kChunk = 65536;  // elements per chunk; one CTA handles one chunk
+constexpr int kMaxChunk = 65536;  // largest chunk (elements): one CTA handles one chunk at a time
+constexpr int kMinChunk = 4096;   // small problems get small chunks so that every SM has work
 
 struct TensorTable {
   void* grad[kMaxTensors];
@@ -32,6 +33,7 @@ struct TensorTable {
   long long size[kMaxTensors];
   int first_chunk[kMaxTensors + 1];  // prefix sum of chunk counts
   int n;
+  int chunk;                         // elements per chunk of this call
 };
 
 struct OptimHyper {
@@ -63,8 +65,8 @@ __global__ void __launch_bounds__(512) multi_tensor_update_kernel(const __grid_c
   const float scale = h.scale * (h.scale_ptr ? *h.scale_ptr : 1.f);
   for (int chunk = blockIdx.x; chunk < tab.first_chunk[tab.n]; chunk += gridDim.x) {
     const int ti = find_tensor(tab, chunk);
-    const long long base = static_cast<long long>(chunk - tab.first_chunk[ti]) * kChunk;
-    const long long end = min(tab.size[ti], base + kChunk);
+    const long long base = static_cast<long long>(chunk - tab.first_chunk[ti]) * tab.chunk;
+    const long long end = min(tab.size[ti], base + tab.chunk);
     float* w = tab.master[ti];
     float* mm = tab.m[ti];
     float* vv = tab.v[ti];
@@ -141,8 +143,8 @@ __global__ void __launch_bounds__(512) multi_tensor_sqsum_kernel(const __grid_co
   float s = 0.f, bad = 0.f;
   for (int chunk = blockIdx.x; chunk < tab.first_chunk[tab.n]; chunk += gridDim.x) {
     const int ti = find_tensor(tab, chunk);
-    const long long base = static_cast<long long>(chunk - tab.first_chunk[ti]) * kChunk;
-    const long long end = min(tab.size[ti], base + kChunk);
+    const long long base = static_cast<long long>(chunk - tab.first_chunk[ti]) * tab.chunk;
+    const long long end = min(tab.size[ti], base + tab.chunk);
     const void* gp = tab.grad[ti];
     for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
       float g = load_grad(gp, i, grad_is_bf16);
@@ -194,6 +196,11 @@ static int build_table(TensorTable& tab, int n, void* const* grads, float* const
                        float* const* ms, float* const* vs, const long long* sizes) {
   if (n > kMaxTensors) return fail("multi-tensor table holds at most 48 tensors per launch");
   tab.n = n;
+  long long total = 0;
+  for (int i = 0; i < n; ++i) total += sizes[i];
+  long long per = (total + 148 * 4 - 1) / (148 * 4);          // about four chunks per SM
+  per = (per + kMinChunk - 1) / kMinChunk * kMinChunk;
+  tab.chunk = static_cast<int>(per < kMinChunk ? kMinChunk : (per > kMaxChunk ? kMaxChunk : per));
   int chunks = 0;
   for (int i = 0; i < n; ++i) {
     tab.grad[i] = grads ? grads[i] : nullptr;
@@ -207,7 +214,7 @@ static int build_table(TensorTable& tab, int n, void* const* grads, float* const
                           reinterpret_cast<uintptr_t>(tab.v[i]);
     if (all & 15) return fail("multi-tensor kernels need 16-byte aligned tensors");
     tab.first_chunk[i] = chunks;
-    chunks += static_cast<int>((sizes[i] + kChunk - 1) / kChunk);
+    chunks += static_cast<int>((sizes[i] + tab.chunk - 1) / tab.chunk);
   }
   tab.first_chunk[n] = chunks;
   return chunks;

@@ -23,7 +23,7 @@ from ..ops import kernels as _k
 
 
 class EmbStoreStruct(Structure):
-    _fields_ = [("tkeys", c_void_p), ("trow", c_void_p), ("stamp", c_void_p), ("uo_of", c_void_p), ("rows", c_void_p),
+    _fields_ = [("slots", c_void_p), ("rows", c_void_p),
                 ("row_key", c_void_p), ("counters", c_void_p), ("init_kind", c_void_p), ("init_a", c_void_p), ("init_b", c_void_p),
                 ("tcap", c_longlong), ("row_cap", c_longlong), ("line", c_int), ("dim", c_int), ("num_tables", c_int),
                 ("state_init", c_float), ("seed", c_ulonglong)]
@@ -79,10 +79,10 @@ class NativeEmbeddingEngine:
         # ---- table shard
         self.row_cap = int(row_capacity)
         self.tcap = _pow2(2 * self.row_cap)
-        self.tkeys = torch.full((self.tcap,), -1, dtype=i64, device=dev)
-        self.trow = torch.full((self.tcap,), -1, dtype=i32, device=dev)
-        self.stamp = torch.zeros((self.tcap,), dtype=i32, device=dev)
-        self.uo_of = torch.zeros((self.tcap,), dtype=i32, device=dev)
+        # key index: 32-byte slots {key u64 = all ones (empty), row i32 = -1, uo i32, stamp u32, pad}
+        self.slots = torch.zeros((self.tcap, 4), dtype=i64, device=dev)
+        self.slots[:, 0] = -1
+        self.slots[:, 1] = 0xFFFFFFFF
         self.rows = torch.empty((self.row_cap, self.line), dtype=f32, device=dev)
         self.row_key = torch.empty((self.row_cap,), dtype=i64, device=dev)
         self.counters = torch.zeros((4,), dtype=i32, device=dev)
@@ -102,7 +102,7 @@ class NativeEmbeddingEngine:
         self.epoch = 0   # step number: never reset, the table's touch stamps compare against it
         self._alloc_exchange(max(int(max_ids), 1024))
         st = EmbStoreStruct()
-        for name in ("tkeys", "trow", "stamp", "uo_of", "rows", "row_key", "counters", "init_kind", "init_a", "init_b"):
+        for name in ("slots", "rows", "row_key", "counters", "init_kind", "init_a", "init_b"):
             setattr(st, name, getattr(self, name).data_ptr())
         st.tcap, st.row_cap, st.line, st.dim, st.num_tables = self.tcap, self.row_cap, self.line, D, self.num_tables
         st.state_init, st.seed = float(state_init), int(seed) & 0xFFFFFFFFFFFFFFFF
