@@ -47,6 +47,20 @@ __all__ = ["sbp", "placement", "GlobalTensor", "to_global", "to_local", "Tensor"
            "mock_torch", "device", "Size", "Generator", "manual_seed", "no_grad", "enable_grad", "set_grad_enabled",
            "inference_mode", "autocast", "_C", "boxing", "models", "ops", "parallel", "framework"]
 
+from .framework import toplevel_extra as _extra  # noqa: E402
+
+for _n in dir(_extra):
+    if not _n.startswith("_") and _n not in ("os", "types", "np", "torch", "F", "builtins_slice", "TensorBuffer") and _n not in globals():
+        globals()[_n] = getattr(_extra, _n)
+globals()["slice"] = _extra.slice
+globals()["view"] = _extra.view
+globals()["repeat"] = _extra.repeat
+globals()["expand"] = _extra.expand
+globals()["cast"] = _extra.cast
+globals()["pad"] = _extra.pad
+globals()["gelu"] = _extra.gelu
+del _n
+
 env.init()
 _atexit.register(env.shutdown)
 
