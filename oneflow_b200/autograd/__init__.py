@@ -3,3 +3,5 @@ saved-tensor hooks, grad modes). Reference: python/oneflow/autograd/*.py."""
 from torch.autograd import *  # noqa: F401,F403
 from torch.autograd import Function, backward, functional, grad, graph  # noqa: F401
 from torch import enable_grad, inference_mode, no_grad, set_grad_enabled  # noqa: F401
+from torch import is_grad_enabled  # noqa: F401,E402
+from torch.autograd.functional import hessian, hvp, jacobian, jvp, vhp, vjp  # noqa: F401,E402

@@ -1,2 +1,4 @@
-"""``flow.backends``: cuda / cudnn / mps switches (torch.backends)."""
-from torch.backends import cuda, cudnn, mps  # noqa: F401
+"""``flow.backends``: cuda / cudnn / mps switches."""
+from torch.backends import mps  # noqa: F401
+
+from . import cuda, cudnn  # noqa: F401

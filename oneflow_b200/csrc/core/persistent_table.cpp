@@ -170,6 +170,17 @@ OFC_API int64_t ofc_ptable_get(void* p, const int64_t* keys, void* values_out, u
   return found;
 }
 OFC_API int64_t ofc_ptable_size(void* p) { return static_cast<int64_t>(static_cast<PTable*>(p)->index.size()); }
+// Copies up to ``cap`` keys of the current index (unspecified order) into ``out``; returns how many were written.
+OFC_API int64_t ofc_ptable_keys(void* p, int64_t* out, int64_t cap) {
+  auto* t = static_cast<PTable*>(p);
+  std::lock_guard<std::mutex> g(t->mu);
+  int64_t n = 0;
+  for (auto& kv : t->index) {
+    if (n >= cap) break;
+    out[n++] = kv.first;
+  }
+  return n;
+}
 OFC_API int ofc_ptable_save_snapshot(void* p, const char* name) {
   auto* t = static_cast<PTable*>(p);
   std::lock_guard<std::mutex> g(t->mu);

@@ -59,6 +59,14 @@ def init_rdma():
     return None
 
 
+def destory_rdma():
+    """Counterpart of :func:`init_rdma` under the reference's (misspelt) name; nothing to tear down."""
+    return None
+
+
+destroy_rdma = destory_rdma
+
+
 def rdma_is_initialized():
     return False
 

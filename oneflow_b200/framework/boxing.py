@@ -312,3 +312,8 @@ def convert(local, logical_shape, dtype, in_placement, in_nd, out_placement, out
     if full.device != dev_out:
         full = full.to(dev_out)
     return from_all_broadcast(full, out_placement, out_nd, out_coords)
+
+
+# ``flow.boxing.enable_fusion`` / ``flow.boxing.nccl.*`` (reference: python/oneflow/boxing/__init__.py:16-17)
+from . import boxing_nccl as nccl  # noqa: E402,F401
+from .config_util import api_enable_fusion as enable_fusion  # noqa: E402,F401

@@ -289,8 +289,7 @@ def _stub_module(name, doc, **attrs):
 
 
 # Internal helper modules of the reference that user code occasionally imports by name.
-asyncs = _stub_module("asyncs", "Asynchronous helpers: thread pools for host-side work.",
-                      thread=types.SimpleNamespace(__doc__="see concurrent.futures.ThreadPoolExecutor"))
+from .. import asyncs, hub, multiprocessing  # noqa: E402,F401
 hook = _stub_module("hook", "Tensor hook helpers.", register_hook=lambda t, fn: t.register_hook(fn))
 docstr = _stub_module("docstr", "Docstrings are attached in place in this implementation.")
 env_util = _stub_module("env_util", "Environment helpers (see oneflow.env).")
@@ -300,26 +299,4 @@ register_class_method_util = _stub_module("register_class_method_util", "Tensor 
 stateful_op = _stub_module("stateful_op", "Stateful op holder of the reference's eager kernels (kernels here are stateless C entry points).")
 
 
-class _Remat:
-    """Rematerialisation (DTR) controls: activation memory is bounded by the explicit engines / utils.checkpoint here,
-    so the budget is recorded but nothing is evicted dynamically."""
-    budget = None
-
-    @staticmethod
-    def set_budget(budget):
-        _Remat.budget = budget
-
-    @staticmethod
-    def get_budget():
-        return _Remat.budget
-
-    @staticmethod
-    def set_small_pieces_optimization(mode=True):
-        _Remat.small_pieces = bool(mode)
-
-    @staticmethod
-    def is_enabled():
-        return _Remat.budget is not None
-
-
-remat = _Remat
+from .. import remat  # noqa: E402,F401

@@ -7,11 +7,23 @@ import torch.nn as _tnn
 from torch.nn import *  # noqa: F401,F403
 from torch.nn import Module  # noqa: F401
 
-from . import functional, init  # noqa: F401
+import importlib as _importlib
 
-from . import graph, module_ext, parallel, utils  # noqa: F401
+# ``from torch.nn import *`` above bound torch's functional / init / utils / parallel / modules under these names, and
+# ``from . import x`` would keep an attribute that already exists — import this package's sub-modules explicitly.
+for _n in ("functional", "init", "graph", "module_ext", "parallel", "utils", "modules"):
+    globals()[_n] = _importlib.import_module(__name__ + "." + _n)
+del _n
 from .graph import Graph  # noqa: F401
 from .modules import Conv2d, FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
+from .modules import (AllReduce, COCOReader, CoinFlip, CropMirrorNormalize, DistributedPariticalFCSample,  # noqa: F401
+                      GPTIndexedBinDataReader, OFRecordBytesDecoder, OFRecordImageDecoder, OFRecordImageDecoderRandomCrop,
+                      OFRecordImageGpuDecoderRandomCropResize, OFRecordRawDecoder, OFRecordReader, QatConv1d, QatConv2d,
+                      QatConv3d, QuickGELU, RawReader, RMSLayerNorm, SquareReLU)
+image = _importlib.import_module(__name__ + ".image")
+qat = _importlib.import_module(__name__ + ".qat")
+
+OfrecordReader, OfrecordRawDecoder = OFRecordReader, OFRecordRawDecoder
 from .extra_modules import (CombinedMarginLoss, FusedBatchNorm1d, FusedBatchNorm2d, FusedBatchNorm3d, MinMaxObserver,  # noqa: F401
                             MovingAverageMinMaxObserver, FakeQuantization, Quantization)
 

@@ -51,7 +51,12 @@ class GraphModule:
         return self.stage_id
 
 
-class ModuleProxy:
+class Proxy:
+    """Base of what a Graph holds in place of an ``nn.Module`` or tensor attribute: ``.to(GraphModule)`` gives the
+    graph-side settings, ``.to(nn.Module)`` the original (reference: python/oneflow/nn/graph/proxy.py:60-79)."""
+
+
+class ModuleProxy(Proxy):
     """What ``self.m = module`` becomes inside a Graph: calls go to the module, with stage placement and
     activation checkpointing applied; attribute access reaches sub-modules (as proxies) and parameters."""
 

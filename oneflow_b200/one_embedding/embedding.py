@@ -43,6 +43,12 @@ def make_normal_initializer(mean, std):
     return {"type": "normal", "mean": float(mean), "std": float(std)}
 
 
+def make_trunc_normal_initializer(mean=0.0, std=1.0, a=-2.0, b=2.0):
+    """Normal(mean, std) re-drawn until it falls inside [a, b]
+    (reference: python/oneflow/one_embedding.py:792-813)."""
+    return {"type": "trunc_normal", "mean": float(mean), "std": float(std), "a": float(a), "b": float(b)}
+
+
 def make_constant_initializer(value):
     return {"type": "constant", "value": float(value)}
 
@@ -151,6 +157,10 @@ class RowStore:
                 emb[sel] = torch.rand((sel.numel(), self.embedding_dim), generator=gen, device=self.device) * (init["high"] - init["low"]) + init["low"]
             elif init["type"] == "normal":
                 emb[sel] = torch.randn((sel.numel(), self.embedding_dim), generator=gen, device=self.device) * init["std"] + init["mean"]
+            elif init["type"] == "trunc_normal":
+                v = torch.empty((sel.numel(), self.embedding_dim), device=self.device)
+                torch.nn.init.trunc_normal_(v, init["mean"], init["std"], init["a"], init["b"], generator=gen)
+                emb[sel] = v
             else:
                 emb[sel] = init["value"]
         return rows
@@ -354,6 +364,8 @@ class Embedding(torch.nn.Module):
             return False
         if self.embedding_dim % 4 or os.environ.get("ONEFLOW_B200_EMBEDDING_ENGINE", "1") == "0":
             return False
+        if any(i["type"] not in ("uniform", "normal", "constant") for i in self.inits):
+            return False                      # the device engine draws uniform / normal / constant rows only
         from . import native
         if not native.available(ids.device):
             return False
@@ -523,3 +535,116 @@ class Optimizer:
     def load_state_dict(self, sd):
         self.hyper.update(sd["hyper"])
         self.embedding.step_count = sd["step"]
+
+
+# ------------------------------------------------------------------------------------------------ offline table access
+_NP = {torch.int64: "int64", torch.int32: "int32", torch.uint64: "uint64", torch.uint32: "uint32", torch.float32: "float32",
+       torch.float16: "float16", torch.float64: "float64", torch.bfloat16: None}
+
+
+def _np_dtype(dt):
+    import numpy as np
+    if isinstance(dt, torch.dtype):
+        name = _NP.get(dt)
+        if name is None:
+            raise TypeError(f"persistent tables hold numpy-representable values, not {dt}")
+        return np.dtype(name)
+    return np.dtype(dt)
+
+
+class PersistentTableWriter:
+    """Writes (key, row) pairs into one persistent table directory per path, keys assigned to paths round robin by
+    ``key % len(paths)`` — the parallel layout a sharded embedding loads — and seals them with a snapshot on
+    :meth:`close` (reference: oneflow/api/python/framework/one_embedding.cpp, ``PersistentTableWriterImpl``)."""
+
+    def __init__(self, paths, snapshot_name, key_type, value_type, storage_dim, target_chunk_size_mb=4096,
+                 physical_block_size=4096):
+        from ..runtime.core import PersistentTable
+        self.key_dtype, self.value_dtype = _np_dtype(key_type), _np_dtype(value_type)
+        self.storage_dim, self.snapshot_name = int(storage_dim), snapshot_name
+        self.tables = [PersistentTable(p, self.storage_dim * self.value_dtype.itemsize, physical_block_size) for p in paths]
+        self.closed = False
+
+    def write(self, keys, values):
+        import numpy as np
+        keys = np.ascontiguousarray(keys).astype(np.int64).reshape(-1)
+        values = np.ascontiguousarray(values, dtype=self.value_dtype).reshape(keys.size, self.storage_dim)
+        n = len(self.tables)
+        for i, t in enumerate(self.tables):
+            sel = (keys % n) == i if n > 1 else slice(None)
+            if n == 1 or sel.any():
+                t.put(keys[sel], values[sel])
+
+    def close(self):
+        if not self.closed:
+            for t in self.tables:
+                t.save_snapshot(self.snapshot_name)
+                t.close()
+            self.closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
+class PersistentTableReader:
+    """Iterates ``(keys, values)`` numpy batches of at most 65536 rows over the named snapshot of each table path
+    (reference: oneflow/api/python/framework/one_embedding.cpp:194-275)."""
+
+    kBatchSize = 65536
+
+    def __init__(self, paths, snapshot_name, key_type, value_type, storage_dim, target_chunk_size_mb=4096,
+                 physical_block_size=4096):
+        from ..runtime.core import PersistentTable
+        self.key_dtype, self.value_dtype = _np_dtype(key_type), _np_dtype(value_type)
+        self.storage_dim = int(storage_dim)
+        self.tables = []
+        for p in paths:
+            t = PersistentTable(p, self.storage_dim * self.value_dtype.itemsize, physical_block_size, read_only=True)
+            t.load_snapshot(snapshot_name)
+            self.tables.append(t)
+        self._cur, self._keys, self._off = 0, None, 0
+        self.closed = False
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        while self._cur < len(self.tables):
+            if self._keys is None:
+                self._keys, self._off = self.tables[self._cur].keys(), 0
+            if self._off < self._keys.size:
+                k = self._keys[self._off:self._off + self.kBatchSize]
+                self._off += k.size
+                v, _ = self.tables[self._cur].get(k, dtype=self.value_dtype)
+                return k.astype(self.key_dtype), v.reshape(k.size, self.storage_dim)
+            self._cur, self._keys = self._cur + 1, None
+        raise StopIteration
+
+    next = __next__
+
+    def close(self):
+        if not self.closed:
+            for t in self.tables:
+                t.close()
+            self.closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
+def make_persistent_table_reader(paths, snapshot_name, key_type, value_type, storage_dim, physical_block_size=4096):
+    """reference: python/oneflow/one_embedding.py:1240-1261"""
+    return PersistentTableReader(paths, snapshot_name, key_type, value_type, storage_dim, 4 * 1024, physical_block_size)
+
+
+def make_persistent_table_writer(paths, snapshot_name, key_type, value_type, storage_dim, physical_block_size=4096):
+    """reference: python/oneflow/one_embedding.py:1264-1285"""
+    return PersistentTableWriter(paths, snapshot_name, key_type, value_type, storage_dim, 4 * 1024, physical_block_size)

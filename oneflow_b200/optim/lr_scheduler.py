@@ -45,7 +45,10 @@ class PolynomialLR(_t.LRScheduler):
 
 
 class WarmupLR(_t.LRScheduler):
-    """Constant or linear warm-up for ``warmup_iters`` steps, then the wrapped scheduler (or the base lr)."""
+    """Constant or linear warm-up for ``warmup_iters`` steps, then the wrapped scheduler (or the base lr).
+    Without ``warmup_prefix`` the wrapped scheduler counts steps from 0 underneath the warm-up and a linear warm-up ends
+    on the value that scheduler has at step ``warmup_iters``; with it the wrapped scheduler starts after the warm-up and
+    the warm-up ends on the base lr (reference: python/oneflow/nn/optimizer/warmup_lr.py:96-200)."""
 
     def __init__(self, scheduler_or_optimizer, warmup_factor=1.0 / 3, warmup_iters=5, warmup_method="linear",
                  warmup_prefix=False, last_step=-1, verbose=False):
@@ -55,26 +58,51 @@ class WarmupLR(_t.LRScheduler):
         else:
             self.inner, optimizer = None, scheduler_or_optimizer
         if warmup_method not in ("linear", "constant"):
-            raise ValueError("warmup_method must be 'linear' or 'constant'")
+            raise ValueError(f"'warmup_method' must be 'linear' or 'constant', but got {warmup_method}")
+        if self.inner is None and warmup_iters == 0:
+            raise ValueError("When 'scheduler_or_optimizer' is an optimizer warmup_iters can't be equal to 0")
         self.factor, self.iters, self.method, self.prefix = warmup_factor, warmup_iters, warmup_method, warmup_prefix
+        self.end_factors = None
+        if self.inner is not None and not warmup_prefix and warmup_method == "linear" and warmup_iters > 0:
+            self.end_factors = self._inner_factors_at(warmup_iters)
+        self._started = False              # the base class takes one step while constructing; the wrapped one already did
         super().__init__(optimizer, last_epoch=last_step)
+        self._started = True
+
+    def _inner_factors_at(self, steps):
+        """lr / base lr of the wrapped scheduler ``steps`` steps from now, found by stepping it and rolling back."""
+        import copy
+        import warnings
+        opt = self.inner.optimizer
+        state, lrs = copy.deepcopy(self.inner.state_dict()), [g["lr"] for g in opt.param_groups]
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            for _ in range(steps):
+                self.inner.step()
+        out = [g["lr"] / b if b else 1.0 for g, b in zip(opt.param_groups, self.inner.base_lrs)]
+        self.inner.load_state_dict(state)
+        for g, lr in zip(opt.param_groups, lrs):
+            g["lr"] = lr
+        return out
 
     def get_lr(self):
         s = self.last_epoch
         if s < self.iters:
             if self.method == "constant":
-                f = self.factor
-            else:
-                f = self.factor + (1 - self.factor) * s / max(self.iters, 1)
-            return [b * f for b in self.base_lrs]
+                return [b * self.factor for b in self.base_lrs]
+            ends = self.end_factors or [1.0] * len(self.base_lrs)
+            return [b * (self.factor + (e - self.factor) * s / max(self.iters, 1)) for b, e in zip(self.base_lrs, ends)]
         if self.inner is None:
             return list(self.base_lrs)
         return list(self.inner.get_last_lr())
 
     def step(self, epoch=None):
-        if self.inner is not None and self.last_epoch + 1 >= (self.iters if self.prefix else 0):
+        if self.inner is not None and self._started and self.last_epoch + 1 > (self.iters if self.prefix else 0):
             self.inner.step()
         super().step()
+
+
+WarmUpLR = WarmupLR
 
 
 class CosineAnnealingWarmRestartsLR(CosineAnnealingWarmRestarts):

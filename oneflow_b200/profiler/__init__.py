@@ -45,3 +45,32 @@ class CudaTimer:
         torch.cuda.synchronize()
         self.ms = self.e0.elapsed_time(self.e1)
         return False
+
+
+from torch.profiler import ProfilerAction, tensorboard_trace_handler  # noqa: E402,F401
+
+
+def range_push(range_name):
+    """Open an NVTX range on the calling thread (reference: python/oneflow/profiler/__init__.py:40-45)."""
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(range_name)
+
+
+def range_pop():
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_pop()
+
+
+def profiler_start():
+    """Start the CUDA profiler's capture window (``cudaProfilerStart``), for tools run with a capture range."""
+    if torch.cuda.is_available():
+        torch.cuda.profiler.start()
+
+
+def profiler_stop():
+    if torch.cuda.is_available():
+        torch.cuda.profiler.stop()
+
+
+def kineto_available():
+    return torch.autograd.kineto_available()

@@ -25,7 +25,7 @@ def lib():
         for name in ("ofc_store_server_start", "ofc_store_client_connect", "ofc_allocator_create", "ofc_allocator_alloc",
                      "ofc_ptable_open", "ofc_executor_create", "ofc_records_open", "ofc_tokens_open"):
             getattr(L, name).restype = c_void_p
-        for name in ("ofc_store_add", "ofc_ptable_get", "ofc_ptable_size", "ofc_executor_completed", "ofc_records_next",
+        for name in ("ofc_store_add", "ofc_ptable_get", "ofc_ptable_size", "ofc_ptable_keys", "ofc_executor_completed", "ofc_records_next",
                      "ofc_tokens_count"):
             getattr(L, name).restype = c_int64
         L.ofc_copy_cost.restype = c_double
@@ -188,6 +188,12 @@ class PersistentTable:
     def __len__(self):
         return lib().ofc_ptable_size(c_void_p(self.h))
 
+    def keys(self) -> np.ndarray:
+        """All keys of the current index (unspecified order)."""
+        out = np.empty(len(self), dtype=np.int64)
+        n = lib().ofc_ptable_keys(c_void_p(self.h), out.ctypes.data_as(POINTER(c_int64)), c_int64(out.size))
+        return out[:n]
+
     def save_snapshot(self, name):
         _check(lib().ofc_ptable_save_snapshot(c_void_p(self.h), name.encode()), "ptable.save_snapshot")
 
@@ -254,6 +260,9 @@ class RecordReader:
 
     def __next__(self):
         n = lib().ofc_records_next(c_void_p(self.h), self.buf, c_int64(len(self.buf)))
+        while n == -3 and len(self.buf) < (1 << 31):     # record larger than the buffer: it stays queued, grow and retry
+            self.buf = ctypes.create_string_buffer(len(self.buf) * 4)
+            n = lib().ofc_records_next(c_void_p(self.h), self.buf, c_int64(len(self.buf)))
         if n == 0:
             raise StopIteration
         if n == -4:

@@ -345,11 +345,64 @@ def auto_parallel_graph(tmp):
         print("AUTO PARALLEL", choices, auto)
 
 
+def data_readers(tmp):
+    """Sharded readers: every rank reads its own part files / batch slice; dense outputs are global split(0) tensors;
+    the torch.distributed-shaped wrappers of flow.distributed forward to flow.comm."""
+    import numpy as np
+    from oneflow_b200.utils.ofrecord import write_ofrecord_file
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    d = os.path.join(tmp, "rec")
+    if rank == 0:
+        os.makedirs(d, exist_ok=True)
+        for part in range(2 * world):
+            write_ofrecord_file(os.path.join(d, f"part-{part:03d}"),
+                                [{"label": np.array([part * 100 + i], np.int32), "x": np.full(4, part * 100 + i, np.float32)} for i in range(6)])
+        np.arange(40 * 3, dtype=np.float32).reshape(40, 3).tofile(os.path.join(tmp, "raw.bin"))
+    flow.comm.barrier()
+    pl = flow.placement("cpu", list(range(world)))
+    r = flow.nn.OFRecordReader(d, batch_size=4 * world, data_part_num=2 * world, part_name_suffix_length=3, placement=pl, sbp=flow.sbp.split(0))
+    lab = flow.nn.OFRecordRawDecoder("label", shape=(1,), dtype=flow.int32)
+    xs = flow.nn.OFRecordRawDecoder("x", shape=(4,), dtype=flow.float32)
+    b = r()
+    la, x = lab(b), xs(b)
+    assert la.is_global and tuple(la.shape) == (4 * world, 1) and tuple(x.shape) == (4 * world, 4)
+    mine = la.to_local().reshape(-1).tolist()
+    assert len(mine) == 4 and all((v // 100) % world == rank for v in mine), mine      # parts dealt round robin
+    full = la.to_global(pl, flow.sbp.broadcast).to_local().reshape(-1).tolist()
+    assert len(set(full)) == 4 * world
+    assert torch.equal(x.to_local()[:, 0], la.to_local().reshape(-1).float())
+    rr = flow.nn.RawReader([os.path.join(tmp, "raw.bin")], shape=(3,), dtype=flow.float32, batch_size=2 * world, random_shuffle=False,
+                           placement=pl, sbp=flow.sbp.split(0))
+    y = rr()
+    assert tuple(y.shape) == (2 * world, 3) and y.to_local()[0, 0].item() == rank * 2 * 3
+    cf = flow.nn.CoinFlip(batch_size=2 * world, random_seed=1, placement=pl, sbp=flow.sbp.split(0))()
+    assert tuple(cf.shape) == (2 * world,)
+    # flow.distributed wrappers
+    D = flow.distributed
+    t = torch.full((3,), float(rank + 1))
+    D.all_reduce(t, D.ReduceOp.SUM)
+    assert t[0].item() == sum(range(1, world + 1))
+    outs = [torch.zeros(2) for _ in range(world)]
+    D.all_gather(outs, torch.full((2,), float(rank)))
+    assert [o[0].item() for o in outs] == list(range(world))
+    bt = torch.full((2,), float(rank))
+    D.broadcast(bt, 0)
+    assert bt[0].item() == 0.0
+    assert D.get_rank() == rank and D.get_world_size() == world and D.is_initialized() and D.is_available()
+    if rank == 0:
+        D.send(torch.arange(4.0), 1)
+    elif rank == 1:
+        got = torch.zeros(4)
+        D.recv(got, 0)
+        assert got[3].item() == 3.0
+    D.barrier()
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
     {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
-     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph}[case](tmp)
+     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers}[case](tmp)
     flow.comm.barrier()
     if flow.env.get_rank() == 0:
         print(f"CASE {case} OK")

@@ -1,0 +1,225 @@
+"""Import paths and the smaller pieces of the public API: dotted ``oneflow.*`` imports, config switches, remat,
+sysconfig, mock helpers, extra functionals and modules, schedulers, parameter grouping, persistent table IO (CPU)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import oneflow as flow
+
+
+@pytest.mark.parametrize("path", [
+    "oneflow.nn", "oneflow.nn.functional", "oneflow.nn.init", "oneflow.nn.utils", "oneflow.nn.utils.rnn", "oneflow.nn.utils.prune",
+    "oneflow.nn.utils.clip_grad", "oneflow.nn.utils.parameters_grouping", "oneflow.nn.utils.skip_init", "oneflow.nn.image",
+    "oneflow.nn.qat", "oneflow.nn.graph", "oneflow.nn.parallel", "oneflow.nn.modules.module", "oneflow.nn.modules.utils",
+    "oneflow.nn.modules.dataset", "oneflow.nn.optimizer.adam", "oneflow.nn.optimizer.sgd", "oneflow.nn.optimizer.warmup_lr",
+    "oneflow.nn.optimizer.cosine_decay_lr", "oneflow.nn.parameter", "oneflow.nn.common_types", "oneflow.optim",
+    "oneflow.optim.lr_scheduler", "oneflow.optim.swa_utils", "oneflow.framework.tensor", "oneflow.framework.config_util",
+    "oneflow.linalg", "oneflow.fft", "oneflow.special", "oneflow.sysconfig", "oneflow.remat", "oneflow.unittest",
+    "oneflow.unittest.env", "oneflow.asyncs", "oneflow.hub", "oneflow.multiprocessing", "oneflow.cuda.amp",
+    "oneflow.cuda.type_tensor", "oneflow.backends.cudnn", "oneflow.backends.cuda", "oneflow.utils.data",
+    "oneflow.utils.data.distributed", "oneflow.utils.hooks", "oneflow.utils.checkpoint", "oneflow.distributed",
+    "oneflow.one_embedding", "oneflow.profiler", "oneflow.mock_torch", "oneflow.autograd", "oneflow.comm", "oneflow.env",
+    "oneflow.sbp", "oneflow.amp", "oneflow._oneflow_internal",
+])
+def test_dotted_import_paths(path):
+    assert importlib.import_module(path) is not None
+
+
+def test_from_imports_give_the_flow_objects():
+    from oneflow.framework.tensor import Tensor
+    from oneflow.nn.modules.module import Module
+    from oneflow.nn.optimizer.adam import Adam
+    from oneflow.nn.parameter import Parameter
+    from oneflow.nn.utils import clip_grad_norm_
+    from oneflow.nn.utils.clip_grad import clip_grad_norm_ as again
+    assert Tensor is flow.Tensor and Module is flow.nn.Module and Adam is flow.optim.Adam and again is clip_grad_norm_
+    assert isinstance(flow.nn.Parameter(flow.ones(1)), Parameter)
+    assert flow.nn.functional.__name__.startswith("oneflow_b200") and flow.nn.init.__name__.startswith("oneflow_b200")
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("oneflow.no_such_module")
+
+
+def test_config_switches_and_boxing_namespace():
+    from oneflow.framework import config_util as cu
+    flow.boxing.nccl.set_fusion_threshold_mbytes(32)
+    flow.boxing.nccl.allow_fuse_all_reduce(False)
+    flow.boxing.enable_fusion(True)
+    flow.backends.cudnn.set_reserved_mem_mbytes(256)
+    r = cu.resource()
+    assert r["nccl_fusion_threshold_mb"] == 32 and r["nccl_fusion_all_reduce"] is False and r["reserved_device_mem_mbyte"] == 256
+    with pytest.raises(TypeError):
+        flow.boxing.nccl.set_fusion_threshold_mbytes("big")
+    old = flow.backends.cuda.matmul.allow_tf32
+    flow.backends.cuda.matmul.allow_tf32 = True
+    assert torch.backends.cuda.matmul.allow_tf32 is True
+    flow.backends.cuda.matmul.allow_tf32 = old
+    with pytest.raises(AssertionError):
+        flow.backends.cuda.matmul.nonsense
+
+
+def test_remat_sysconfig_unittest_env(monkeypatch):
+    assert flow.remat.parse_size("2GB") == 2 << 30 and flow.remat.parse_size("1.5 mb") == int(1.5 * 2 ** 20)
+    flow.remat.set_budget("512MB")
+    assert flow.remat.get_budget() == 512 << 20 and flow.remat.is_enabled()
+    assert flow.sysconfig.get_include().endswith("api") and flow.sysconfig.with_cuda() and flow.sysconfig.get_cuda_version() >= 12000
+    assert any(f.startswith("-l") for f in flow.sysconfig.get_link_flags())
+    monkeypatch.setenv("ONEFLOW_TEST_DEVICE_NUM", "2")
+    assert flow.unittest.env.device_num() == 2
+    skipped = flow.unittest.skip_unless_1n1d()(type("T", (flow.unittest.TestCase,), {}))
+    assert getattr(skipped, "__unittest_skip__", False)
+    kept = flow.unittest.skip_unless_1n2d()(type("T", (flow.unittest.TestCase,), {}))
+    assert not getattr(kept, "__unittest_skip__", False)
+
+
+def test_mock_helpers():
+    import math
+    from oneflow.mock_torch import DummyModule, DynamicMockModule, ModuleWrapper
+    d = DummyModule("x")
+    assert not d.a.b(1)["k"] and list(d) == []
+
+    class K(d.Base):
+        pass
+    w = ModuleWrapper(math, lazy=True)
+    assert w.pi == math.pi and not w.nothing
+    with pytest.raises(AttributeError):
+        ModuleWrapper(math).nothing
+    m = DynamicMockModule.from_package("json")
+    m.hijack("dumps", 5)
+    assert m.dumps == 5 and m.loads("1") == 1 and m.decoder is not None
+
+
+def test_functional_additions():
+    import torchvision
+    F = flow.nn.functional
+    x = torch.randn(5, 7)
+    assert torch.allclose(F.quick_gelu(x), x * torch.sigmoid(1.702 * x)) and torch.allclose(F.square_relu(x), x.clamp(min=0) ** 2)
+    lab = torch.randint(0, 7, (5,))
+    assert torch.allclose(F.sparse_softmax_cross_entropy(lab, x), torch.nn.functional.cross_entropy(x, lab, reduction="none"))
+    assert F.interpolate_like(torch.randn(1, 2, 4, 4), torch.randn(1, 2, 8, 6)).shape == (1, 2, 8, 6)
+    # the reference's documented example (python/oneflow/framework/docstr/ctc_decode.py)
+    lp = torch.tensor([[[-1.54, -1.20, -1.95, -1.65, -1.81], [-1.84, -1.74, -1.58, -1.55, -1.12]],
+                       [[-1.68, -1.48, -1.89, -1.30, -2.07], [-1.13, -1.45, -1.24, -1.61, -1.66]],
+                       [[-1.56, -1.40, -2.83, -1.67, -1.48], [-1.20, -2.01, -2.05, -1.95, -1.24]],
+                       [[-2.09, -1.76, -1.36, -1.67, -1.45], [-1.85, -1.48, -1.34, -2.16, -1.55]]])
+    dec, neg = F.ctc_greedy_decoder(lp, torch.tensor([4, 4]))
+    assert dec.tolist() == [[1, 3, 1, 2], [0, 2, 0, 0]] and torch.allclose(neg, torch.tensor([[5.26], [4.79]]))
+    dec2, neg2 = F.ctc_greedy_decoder(lp, torch.tensor([4, 2]), merge_repeated=False)
+    assert dec2.tolist() == [[1, 3, 1, 2], [0, 0, 0, 0]] and abs(neg2[1, 0].item() - 2.25) < 1e-6
+    # depend: identity forward, zero gradient to the dependency
+    a = torch.randn(3, requires_grad=True)
+    b = torch.randn(3, requires_grad=True)
+    y = F.depend(a * 2, [b * 3])
+    y.sum().backward()
+    assert torch.equal(a.grad, torch.full((3,), 2.0)) and torch.equal(b.grad, torch.zeros(3))
+    # deformable convolution against torchvision, with groups, offset groups, stride, padding and mask
+    torch.manual_seed(0)
+    inp, w = torch.randn(2, 8, 9, 11), torch.randn(6, 4, 3, 3)
+    off, msk, bias = torch.randn(2, 2 * 2 * 9, 5, 6) * 1.5, torch.rand(2, 2 * 9, 5, 6), torch.randn(6)
+    mine = F.deform_conv2d(inp, off, w, bias, stride=(2, 2), padding=(1, 1), mask=msk)
+    ref = torchvision.ops.deform_conv2d(inp, off, w, bias, stride=(2, 2), padding=(1, 1), mask=msk)
+    assert torch.allclose(mine, ref, atol=1e-4)
+    zero = F.deform_conv2d(inp, torch.zeros(2, 18, 9, 11), w[:, :, :, :], None, padding=(1, 1))
+    assert torch.allclose(zero, torch.nn.functional.conv2d(inp, w, padding=1, groups=2), atol=1e-4)
+
+
+def test_small_modules_and_qat_conv():
+    x = torch.randn(4, 16)
+    assert torch.allclose(flow.nn.QuickGELU()(x), x * torch.sigmoid(1.702 * x))
+    assert torch.allclose(flow.nn.SquareReLU()(x), torch.relu(x) ** 2)
+    n = flow.nn.RMSLayerNorm(16, eps=1e-6)
+    assert torch.allclose(n(x), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-6)
+    assert torch.equal(flow.nn.AllReduce("cpu:0")(x), x)                      # one rank: the sum is the input
+    w = torch.randn(32, 8)
+    mapped, sampled, sw = flow.nn.DistributedPariticalFCSample(10)(w, torch.tensor([3, 7, 3]))
+    assert sw.shape == (10, 8) and torch.equal(sampled[mapped], torch.tensor([3, 7, 3]))
+    torch.manual_seed(0)
+    q = flow.nn.QatConv2d(3, 5, 3, padding=1, quantization_bit=8)
+    ref = torch.nn.Conv2d(3, 5, 3, padding=1)
+    ref.load_state_dict({k: v for k, v in q.state_dict().items() if k in ("weight", "bias")})
+    img = torch.randn(2, 3, 8, 8)
+    out = q(img)
+    assert out.shape == (2, 5, 8, 8) and (out - ref(img)).abs().max() < 0.15 and not torch.equal(out, ref(img))
+    out.sum().backward()
+    assert q.weight.grad is not None and q.weight.grad.abs().sum() > 0       # straight-through gradient
+    assert flow.nn.QatConv1d(2, 2, 3)(torch.randn(1, 2, 9)).shape == (1, 2, 7)
+    assert flow.nn.qat.QatConv3d(1, 2, 3)(torch.randn(1, 1, 5, 5, 5)).shape == (1, 2, 3, 3, 3)
+
+
+def test_warmup_lr_matches_reference_schedule():
+    p = [torch.nn.Parameter(torch.zeros(1))]
+
+    def run(prefix):
+        o = flow.optim.SGD(p, lr=0.001)
+        cd = flow.optim.lr_scheduler.CosineDecayLR(o, decay_steps=5, alpha=0.1)
+        w = flow.optim.lr_scheduler.WarmUpLR(cd, warmup_factor=0.5, warmup_iters=2, warmup_method="linear", warmup_prefix=prefix)
+        out = []
+        for _ in range(7):
+            out.append(o.param_groups[0]["lr"])
+            o.step()
+            w.step()
+        return out
+
+    cos = lambda s: 0.001 * (0.9 * 0.5 * (1 + np.cos(np.pi * min(s, 5) / 5)) + 0.1)  # noqa: E731
+    a = run(False)   # the decay runs underneath; the warm-up ends on the decay's value at step 2
+    assert np.allclose(a, [0.0005, 0.0005 + (cos(2) - 0.0005) / 2, cos(2), cos(3), cos(4), cos(5), cos(6)], atol=1e-9)
+    b = run(True)    # the decay starts after the warm-up
+    assert np.allclose(b, [0.0005, 0.00075, cos(0), cos(1), cos(2), cos(3), cos(4)], atol=1e-9)
+    o = flow.optim.SGD(p, lr=0.001)
+    c = flow.optim.lr_scheduler.WarmUpLR(o, warmup_factor=0.5, warmup_iters=5, warmup_method="constant")
+    seen = []
+    for _ in range(7):
+        seen.append(o.param_groups[0]["lr"])
+        o.step()
+        c.step()
+    assert np.allclose(seen, [0.0005] * 5 + [0.001] * 2)
+    with pytest.raises(ValueError):
+        flow.optim.lr_scheduler.WarmUpLR(o, warmup_iters=0)
+
+
+def test_contiguous_params_group():
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.Linear(7, 3))
+    ref = [p.detach().clone() for p in m.parameters()]
+    g = flow.nn.utils.ContiguousParamsGroup([list(m[0].parameters()), list(m[1].parameters())], group_on_current_buffer=False)
+    assert len(g.grouped_parameters) == 2 and all(t.numel() % 128 == 0 for t in g.grouped_parameters)
+    assert all(torch.equal(a, b) for a, b in zip(ref, m.parameters()))
+    m(torch.randn(4, 5)).sum().backward()
+    assert m[0].weight.grad.data_ptr() == g.grouped_parameters_grad[0].data_ptr() and g.grouped_parameters_grad[0].abs().sum() > 0
+    torch.optim.SGD(g.grouped_parameters, lr=0.1).step()                     # one flat update moves the views
+    assert not torch.equal(m[0].weight, ref[0]) and not torch.equal(m[1].bias, ref[3])
+    g2 = flow.nn.utils.ContiguousParamsGroup([[m[0].weight, m[0].bias], [m[1].bias]])   # regroup on the existing buffers
+    assert [t.numel() for t in g2.grouped_parameters] == [256, 128]
+    assert flow.nn.init.calc_fan((8, 4, 3, 3), "fan_out", "channels_first") == 72.0
+    assert flow.nn.init.calc_fan((8, 3, 3, 4), "fan_in", "channels_last") == 36.0
+    assert flow.nn.init.get_data_format("NCHW") == "channels_first" and flow.nn.init.get_data_format("NHWC") == "channels_last"
+
+
+def test_persistent_table_reader_writer(tmp_path):
+    paths = [str(tmp_path / "t0"), str(tmp_path / "t1")]
+    k = np.arange(1000, dtype=np.int64) * 7
+    v = np.random.RandomState(0).rand(1000, 8).astype(np.float32)
+    with flow.one_embedding.make_persistent_table_writer(paths, "snap", flow.int64, flow.float32, 8) as w:
+        w.write(k[:600], v[:600])
+        w.write(k[600:], v[600:])
+    got = {}
+    with flow.one_embedding.make_persistent_table_reader(paths, "snap", flow.int64, flow.float32, 8) as r:
+        for kk, vv in r:
+            assert kk.dtype == np.int64 and vv.shape == (kk.size, 8)
+            got.update({int(a): b for a, b in zip(kk, vv)})
+    assert len(got) == 1000 and all(np.array_equal(got[int(a)], b) for a, b in zip(k, v))
+    init = flow.one_embedding.make_trunc_normal_initializer(mean=0, std=0.01, a=-0.02, b=0.02)
+    assert init["type"] == "trunc_normal" and init["b"] == 0.02
+
+
+def test_autograd_and_profiler_names():
+    j = flow.autograd.jacobian(lambda t: t ** 2, torch.tensor([1.0, 2.0]))
+    assert torch.allclose(j, torch.diag(torch.tensor([2.0, 4.0]))) and flow.autograd.is_grad_enabled()
+    flow.profiler.range_push("r")
+    flow.profiler.range_pop()
+    assert flow.profiler.kineto_available() in (True, False) and flow.profiler.ProfilerAction is not None
+    with flow.asyncs.thread(flow.asyncs.Thread()) as t:
+        y = flow.ones(2) + 1
+    t.join()
+    assert y.tolist() == [2.0, 2.0]
