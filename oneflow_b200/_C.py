@@ -191,9 +191,21 @@ def local_all_reduce(x, inplace=False):
 
 
 from ._C_extra import *  # noqa: F401,F403,E402  (the long tail of fused functions)
+from ._C_more import *  # noqa: F401,F403,E402
+from ._C_more import T, _fused_gru_cell, _fused_lstm_cell  # noqa: F401,E402
 
 
 def __getattr__(name):
+    """Ops not defined here: the function of that name of the top-level package, of ``flow.nn.functional``, of torch."""
+    import sys
+    if name.startswith("__"):
+        raise AttributeError(name)
+    top = sys.modules.get("oneflow_b200")
+    if top is not None and name in top.__dict__ and callable(top.__dict__[name]):
+        return top.__dict__[name]
+    fn = sys.modules.get("oneflow_b200.nn.functional")
+    if fn is not None and name in fn.__dict__:
+        return fn.__dict__[name]
     if hasattr(torch, name):
         return getattr(torch, name)
     if hasattr(torch.nn.functional, name):

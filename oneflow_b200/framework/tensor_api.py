@@ -112,4 +112,89 @@ def install_tensor_methods():
     T.placement = property(_placement)
     T.sbp = property(_sbp)
     T.global_id = lambda self: id(self)
+    _install_reference_methods(T)
     T._ofb_patched = True
+
+
+def _install_reference_methods(T):
+    """Tensor methods of the reference that torch.Tensor lacks (reference: python/oneflow/framework/tensor.py
+    RegisterMethods, python/oneflow/framework/docstr/tensor.py)."""
+    import warnings
+
+    import torch.nn.functional as F
+
+    def _top(name):
+        def method(self, *a, **k):
+            import oneflow_b200 as flow
+            return getattr(flow, name)(self, *a, **k)
+        method.__name__ = name
+        return method
+
+    T.cast = lambda self, dtype: self.to(dtype)
+    T.gelu = lambda self, approximate="none": F.gelu(self, approximate=approximate)
+    T.mish = lambda self: F.mish(self)
+    T.selu = lambda self: F.selu(self)
+    T.silu = lambda self: F.silu(self)
+    T.softplus = lambda self, beta=1, threshold=20: F.softplus(self, beta, threshold)
+    T.softsign = lambda self: F.softsign(self)
+    T.in_top_k = lambda self, predictions, k: _top("in_top_k")(self, predictions, k)
+    T.nms = lambda self, scores, iou_threshold: _top("nms")(self, scores, iou_threshold)
+    T.is_lazy = property(lambda self: False)
+    T.is_consistent = property(lambda self: isinstance(self, GT.GlobalTensor))
+    T.to_consistent = lambda self, *a, **k: self.to_global(*a, **k)
+
+    def local_to_global(self, placement=None, sbp=None, *, check_meta=True, copy=False):
+        if isinstance(self, GT.GlobalTensor):
+            raise RuntimeError("local_to_global: the tensor is already global")
+        if placement is None or sbp is None:
+            raise ValueError("local_to_global needs both placement and sbp")
+        return GT.to_global(self, placement, sbp, check_meta=check_meta, copy=copy)
+
+    def global_to_global(self, placement=None, sbp=None, *, grad_sbp=None, check_meta=False, copy=False):
+        if not isinstance(self, GT.GlobalTensor):
+            raise RuntimeError("global_to_global: the tensor is local")
+        if placement is None and sbp is None:
+            raise ValueError("global_to_global needs placement or sbp")
+        return GT.to_global(self, placement, sbp, grad_sbp=grad_sbp, check_meta=check_meta, copy=copy)
+    T.local_to_global, T.global_to_global = local_to_global, global_to_global
+
+    # offload / load: the storage moves between device and pinned host memory, the tensor object stays the same
+    def offload(self):
+        t = self._local if isinstance(self, GT.GlobalTensor) else self
+        if not t.is_cuda:
+            warnings.warn("offload: the tensor is already in host memory")
+            return
+        dev = t.device
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        host.copy_(t.data)
+        t.data = host
+        t._ofb_offloaded_from = dev
+
+    def load(self):
+        t = self._local if isinstance(self, GT.GlobalTensor) else self
+        dev = getattr(t, "_ofb_offloaded_from", None)
+        if dev is None:
+            warnings.warn("load: the tensor is not offloaded")
+            return
+        t.data = t.data.to(dev, non_blocking=True)
+        t._ofb_offloaded_from = None
+
+    def is_offloaded(self):
+        t = self._local if isinstance(self, GT.GlobalTensor) else self
+        return getattr(t, "_ofb_offloaded_from", None) is not None
+    T.offload, T.load, T.is_offloaded = offload, load, is_offloaded
+
+    def _init_method(fn):
+        def method(self, *a, **k):
+            with torch.no_grad():
+                fn(self, *a, **k)
+            return self
+        return method
+    I = torch.nn.init
+    T.kaiming_normal_ = _init_method(lambda self, a=0, mode="fan_in", nonlinearity="leaky_relu": I.kaiming_normal_(self, a, mode, nonlinearity))
+    T.kaiming_uniform_ = _init_method(lambda self, a=0, mode="fan_in", nonlinearity="leaky_relu": I.kaiming_uniform_(self, a, mode, nonlinearity))
+    T.xavier_normal_ = _init_method(lambda self, gain=1.0: I.xavier_normal_(self, gain))
+    T.xavier_uniform_ = _init_method(lambda self, gain=1.0: I.xavier_uniform_(self, gain))
+    T.orthogonal_ = _init_method(lambda self, gain=1.0: I.orthogonal_(self, gain))
+    T.trunc_normal_ = _init_method(lambda self, mean=0.0, std=1.0, a=-2.0, b=2.0: I.trunc_normal_(self, mean, std, a, b))
+    T._meta_repr = lambda self: f"tensor(..., size={tuple(self.shape)}, dtype={self.dtype}, device={self.device})"

@@ -197,6 +197,78 @@ class Graph:
     def training(self):
         return self.config.training
 
+    @property
+    def is_compiled(self):
+        """True once the first call has fixed placement decisions and input meta."""
+        return self._compiled
+
+    # ------------------------------------------------------------------ sharing / runtime state / dynamic shapes
+    def enable_shared(self, mode=True):
+        """Lets other graphs of the same class reuse this graph's compile-time decisions (auto-parallel choices)
+        through :meth:`share_from`; must be set before the first call
+        (reference: python/oneflow/nn/graph/graph.py:879-899)."""
+        if mode and self._compiled:
+            raise RuntimeError("enable_shared must be set before graph compile")
+        object.__setattr__(self, "_enable_shared_from_this", bool(mode))
+
+    def share_from(self, shared_graph):
+        if not isinstance(shared_graph, Graph):
+            raise TypeError("shared_graph must be an instance of nn.Graph")
+        if not getattr(shared_graph, "_enable_shared_from_this", False):
+            raise RuntimeError("shared_graph must have been enabled to be shared")
+        if not shared_graph._compiled:
+            raise RuntimeError("shared_graph must have been compiled")
+        object.__setattr__(self, "_shared_graph", shared_graph)
+
+    def enable_save_runtime_state_dict(self, mode=True):
+        if mode and self._compiled:
+            raise RuntimeError("enable_save_runtime_state_dict must be set before graph compile")
+        object.__setattr__(self, "_enable_save_runtime_state_dict", bool(mode))
+
+    @staticmethod
+    def with_dynamic_input_shape(*, size=10, enable_shared=True):
+        """Decorator for ``__init__``: the graph then accepts inputs of changing shapes, remembering the
+        ``size`` most recently used input signatures instead of insisting on the first one
+        (reference: python/oneflow/nn/graph/graph.py:2125-2143, python/oneflow/nn/graph/cache.py)."""
+        import functools
+
+        def deco(init):
+            @functools.wraps(init)
+            def wrapped(self, *args, **kwargs):
+                init(self, *args, **kwargs)
+                object.__setattr__(self, "_dynamic_metas", OrderedDict())
+                object.__setattr__(self, "_dynamic_cache_size", int(size))
+            return wrapped
+        return deco
+
+    def _ops_repr(self):
+        """One line per block and leaf module, in execution-independent (registration) order."""
+        lines = []
+        for name, proxy in self._blocks.items():
+            for sub, mod in proxy._module.named_modules():
+                if not list(mod.children()):
+                    lines.append(f"(OPERATOR: {self._name}.{name}{'.' + sub if sub else ''}: {mod})")
+        return lines
+
+    @property
+    def _graph_proto(self):
+        """A plain-dict description of the graph: name, config, blocks with stage settings, optimizers, input meta."""
+        cfg = {k: v for k, v in vars(self.config).items() if not k.startswith("_") and isinstance(v, (int, float, bool, str, type(None)))}
+        blocks = {n: {"type": type(p._module).__name__, "stage_id": p._gm.stage_id,
+                      "activation_checkpointing": p._gm.activation_checkpointing,
+                      "parameters": sum(q.numel() for q in p._module.parameters())} for n, p in self._blocks.items()}
+        return {"name": self._name, "training": self.config.training, "config": cfg, "blocks": blocks,
+                "optimizers": [type(o["optim"]).__name__ for o in self._opts],
+                "inputs": [str(m) for m in (self._input_meta or [])], "compiled": self._compiled}
+
+    @property
+    def _full_graph_proto(self):
+        return self._graph_proto
+
+    @property
+    def _compiled_graph_proto(self):
+        return self._graph_proto if self._compiled else None
+
     def debug(self, v_level=-1, *, ranks=None, max_py_stack_depth=2, only_user_py_stack=True, op_repr_with_py_stack=False):
         self._debug_level, self._debug_ranks = v_level, ranks
         from ...framework import boxing
@@ -335,6 +407,9 @@ class Graph:
     def _compile(self, args):
         if Graph._nesting > 0:
             raise RuntimeError("nn.Graph objects cannot be nested")
+        shared = getattr(self, "_shared_graph", None)
+        if shared is not None and getattr(shared, "_auto_parallel_choices", None) is not None and not self.config.auto_parallel:
+            self._auto_parallel_choices = list(shared._auto_parallel_choices)
         self._apply_auto_parallel(args)
         self._apply_zero()
         self._compiled = True
@@ -355,6 +430,12 @@ class Graph:
         if not self._compiled:
             self._compile(args)
             self._input_meta = [self._meta(a) for a in args]
+        elif getattr(self, "_dynamic_metas", None) is not None:
+            key = tuple(self._meta(a) for a in args)
+            self._dynamic_metas[key] = True
+            self._dynamic_metas.move_to_end(key)
+            while len(self._dynamic_metas) > self._dynamic_cache_size:
+                self._dynamic_metas.popitem(last=False)
         else:
             meta = [self._meta(a) for a in args]
             if self._input_meta is not None and meta != self._input_meta:

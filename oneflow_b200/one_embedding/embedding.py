@@ -327,6 +327,8 @@ class Embedding(torch.nn.Module):
         self.sparse_optimizer = ("sgd", {"lr": 0.0})
         self.step_count = 0
         self.gradient_fp16 = os.environ.get("ONEFLOW_ONE_EMBEDDING_GRADIENT_SHUFFLE_USE_FP16", "1") == "1"
+        from . import ops as _ops
+        _ops.register(self)                 # reachable by name from the stage ops of flow._C
 
     # -------------------------------------------------------------- store
     def _ensure_store(self, device):

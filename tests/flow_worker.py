@@ -398,11 +398,42 @@ def data_readers(tmp):
     D.barrier()
 
 
+def embedding_stages(tmp):
+    """The OneEmbedding stage ops across ranks: id shuffle -> lookup -> embedding shuffle equals the fused forward, and the
+    gradient shuffle delivers every rank's gradient rows, summed per key, to the key's owner."""
+    C = flow._C
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    opts = flow.one_embedding.make_table_options(flow.one_embedding.make_uniform_initializer(-0.1, 0.1))
+    store = flow.one_embedding.make_device_mem_store_options(persistent_path=os.path.join(tmp, "emb"), capacity=4096, size_factor=1)
+    emb = flow.one_embedding.MultiTableEmbedding("stages", embedding_dim=4, dtype=flow.float32, key_type=flow.int64,
+                                                 tables=[opts], store_options=store)
+    g = torch.Generator().manual_seed(5 + rank)
+    ids = torch.randint(0, 20, (12,), generator=g)
+    mat, inv_part, n_cur, cur_ids, cur_tids, cur_inv = C.one_embedding_id_shuffle(ids, None, 1, "stages")
+    assert mat.numel() == world * world and int(mat.reshape(world, world)[rank].sum()) == torch.unique(ids).numel()
+    lines = C.one_embedding_lookup(n_cur, cur_ids, cur_tids, flow.float32, flow.float32, 4, 4, "stages", "", "", 0)
+    out = C.one_embedding_embedding_shuffle(lines, mat, cur_inv, inv_part, "stages")
+    assert torch.allclose(out, emb(ids).reshape(-1, 4))
+    # a key held by two ranks resolves to the same row on both
+    gathered = [torch.zeros(12, 5) for _ in range(world)]
+    flow.comm.all_gather(gathered, torch.cat([ids.float().unsqueeze(1), out], 1))
+    table = {}
+    for t in gathered:
+        for row in t.tolist():
+            assert table.setdefault(row[0], row[1:]) == row[1:]
+    grad = torch.full((12, 4), float(rank + 1))
+    ug = C.one_embedding_embedding_gradient_shuffle(grad, mat, cur_inv, inv_part, "stages")
+    assert ug.shape == (int(n_cur), 4)
+    total = ug.sum().reshape(1)
+    flow.comm.all_reduce(total)
+    assert abs(total.item() - sum(12 * 4 * (r + 1) for r in range(world))) < 1e-3
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
     {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
-     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers}[case](tmp)
+     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers, "embedding_stages": embedding_stages}[case](tmp)
     flow.comm.barrier()
     if flow.env.get_rank() == 0:
         print(f"CASE {case} OK")

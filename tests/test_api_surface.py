@@ -223,3 +223,58 @@ def test_autograd_and_profiler_names():
         y = flow.ones(2) + 1
     t.join()
     assert y.tolist() == [2.0, 2.0]
+
+
+def test_tensor_methods_of_the_reference():
+    x = flow.randn(4, 6)
+    assert x.cast(flow.int32).dtype == torch.int32 and x.is_lazy is False and x.is_consistent is False
+    assert torch.allclose(x.silu(), torch.nn.functional.silu(x)) and torch.allclose(x.mish(), torch.nn.functional.mish(x))
+    assert torch.allclose(x.softplus(beta=2), torch.nn.functional.softplus(x, 2)) and torch.allclose(x.gelu(), torch.nn.functional.gelu(x))
+    w = flow.empty(8, 8).xavier_uniform_()
+    assert w.abs().max() <= (6 / 16) ** 0.5 + 1e-6
+    assert flow.empty(64).trunc_normal_(std=0.02, a=-0.04, b=0.04).abs().max() <= 0.04
+    assert not x.is_offloaded()
+    with pytest.warns(UserWarning):
+        x.offload()                                           # a host tensor has nowhere to go
+    with pytest.raises(RuntimeError):
+        x.global_to_global(sbp=flow.sbp.broadcast)
+    pl = flow.placement("cpu", [0])
+    g = x.local_to_global(pl, flow.sbp.broadcast)
+    assert g.is_global and g.is_consistent and g.global_to_global(sbp=flow.sbp.broadcast) is g
+
+
+def test_graph_sharing_dynamic_shapes_and_description():
+    class G(flow.nn.Graph):
+        @flow.nn.Graph.with_dynamic_input_shape(size=2)
+        def __init__(self):
+            super().__init__()
+            self.m = torch.nn.Linear(4, 2)
+
+        def build(self, x):
+            return self.m(x)
+
+    g = G()
+    g.enable_shared()
+    assert not g.is_compiled
+    assert [g(torch.randn(n, 4)).shape[0] for n in (3, 5, 7)] == [3, 5, 7] and len(g._dynamic_metas) == 2 and g.is_compiled
+    assert "Linear" in g._ops_repr()[0] and g._graph_proto["blocks"]["m"]["parameters"] == 10 and g._compiled_graph_proto["compiled"]
+    with pytest.raises(RuntimeError):
+        g.enable_shared()                                     # only before the first call
+
+    class H(flow.nn.Graph):
+        def __init__(self):
+            super().__init__()
+            self.m = torch.nn.Linear(4, 2)
+
+        def build(self, x):
+            return self.m(x)
+
+    h = H()
+    h.share_from(g)
+    h(torch.randn(3, 4))
+    with pytest.raises(RuntimeError):
+        h(torch.randn(4, 4))                                  # a plain graph keeps its first input signature
+    with pytest.raises(RuntimeError):
+        H().share_from(H())                                   # the source was never enabled for sharing
+    o = flow.optim.SGD([torch.nn.Parameter(torch.ones(2))], lr=0.1)
+    assert o.support_sparse() is False and hasattr(flow.optim.Optimizer, "clip_grad")

@@ -53,6 +53,10 @@ def test_sharded_data_readers_and_distributed_wrappers():
     launch("data_readers", 2)
 
 
+def test_one_embedding_stage_ops_two_ranks():
+    launch("embedding_stages", 2)
+
+
 def test_launcher_kills_group_on_failure(tmp_path):
     script = tmp_path / "boom.py"
     script.write_text("import os, sys, time\nif os.environ['RANK']=='1': sys.exit(3)\ntime.sleep(60)\n")
