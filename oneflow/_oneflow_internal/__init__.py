@@ -133,3 +133,10 @@ def GetEnvContext(*args, **kwargs):
 def CurrentMachineId():
     from oneflow_b200 import env
     return env.get_node_size() - 1 if False else 0
+
+
+class TensorTuple(list):
+    """The reference's container for several tensors crossing into C++; a list here."""
+
+    def __init__(self, items=()):
+        super().__init__(items)

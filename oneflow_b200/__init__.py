@@ -55,6 +55,7 @@ from .framework import toplevel_extra as _extra  # noqa: E402
 for _n in dir(_extra):
     if not _n.startswith("_") and _n not in ("os", "types", "np", "torch", "F", "builtins_slice", "TensorBuffer") and _n not in globals():
         globals()[_n] = getattr(_extra, _n)
+globals()["Generator"] = _extra.Generator
 globals()["slice"] = _extra.slice
 globals()["view"] = _extra.view
 globals()["repeat"] = _extra.repeat
@@ -63,6 +64,10 @@ globals()["cast"] = _extra.cast
 globals()["pad"] = _extra.pad
 globals()["gelu"] = _extra.gelu
 del _n
+
+from .framework import compat_ops as _compat  # noqa: E402
+
+_compat.install()
 
 env.init()
 _atexit.register(env.shutdown)

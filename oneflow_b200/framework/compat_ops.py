@@ -1,0 +1,147 @@
+"""Functions whose reference signature differs from the torch function of the same name (extra positional
+arguments, scalar operands where torch wants tensors, looser index dtypes, ``generator`` / ``addend`` / ``dtype``
+keywords).  Installed over the top-level namespace, ``flow.nn.functional`` and ``flow._C``
+(signatures: oneflow/core/functional/functional_api.yaml; python/oneflow/nn/modules/*.py)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+
+def addmm(input, mat1, mat2, alpha=1, beta=1):
+    """``beta * input + alpha * (mat1 @ mat2)`` with ``alpha`` / ``beta`` also accepted positionally
+    (reference: python/oneflow/nn/modules/math_ops.py:195-250)."""
+    return torch.addmm(input, mat1, mat2, beta=beta, alpha=alpha)
+
+
+def matmul(input, other, transpose_a=False, transpose_b=False, alpha=1.0):
+    """MatMul with optional transposes of the two innermost axes and a scale."""
+    a = input.transpose(-1, -2) if transpose_a else input
+    b = other.transpose(-1, -2) if transpose_b else other
+    out = torch.matmul(a, b)
+    return out if alpha == 1.0 else out * alpha
+
+
+def bernoulli(input, p=None, *, dtype=None, generator=None, inplace=False, out=None):
+    """Bernoulli draws with probabilities ``input`` (or one probability ``p``), in ``dtype`` (default: float32 for
+    integer inputs' sake as well), optionally written back into ``input``."""
+    if p is None:
+        res = torch.bernoulli(input.float() if not input.is_floating_point() else input, generator=generator)
+    else:
+        res = torch.empty_like(input, dtype=torch.float32).bernoulli_(float(p), generator=generator)
+    if inplace:
+        return input.copy_(res.to(input.dtype))
+    return res.to(dtype if dtype is not None else (input.dtype if input.is_floating_point() else torch.float32))
+
+
+def one_hot(input, num_classes=-1, on_value=1, off_value=0):
+    """One-hot of any integer index dtype, with selectable on / off values; the result is int64 unless a value is a
+    float."""
+    oh = F.one_hot(input.long(), num_classes)
+    if on_value == 1 and off_value == 0:
+        return oh
+    dt = torch.float32 if isinstance(on_value, float) or isinstance(off_value, float) else torch.int64
+    return torch.where(oh.bool(), torch.tensor(on_value, dtype=dt, device=input.device),
+                       torch.tensor(off_value, dtype=dt, device=input.device))
+
+
+def dropout(input, p=0.5, training=True, inplace=False, generator=None, *, addend=None):
+    """Dropout with an optional generator for the mask and an ``addend`` added to the result (the fused residual)."""
+    if training and p > 0:
+        if generator is None:
+            out = F.dropout(input, p, True, inplace)
+        else:
+            keep = (torch.rand(input.shape, generator=generator, device=generator.device) >= p).to(input.device)
+            out = input.mul_(keep / (1 - p)) if inplace else input * (keep / (1 - p))
+    else:
+        out = input
+    return out if addend is None else out + addend
+
+
+class Dropout(torch.nn.Dropout):
+    """``nn.Dropout(p, inplace, generator)`` whose ``forward(x, addend=None)`` adds ``addend`` after dropping
+    (reference: python/oneflow/nn/modules/dropout.py:43-57)."""
+
+    def __init__(self, p=0.5, inplace=False, generator=None):
+        super().__init__(p, inplace)
+        self.generator = generator
+
+    def forward(self, x, addend=None):
+        return dropout(x, self.p, self.training, self.inplace, self.generator, addend=addend)
+
+
+def _scalar_ok(fn):
+    def f(input, other):
+        if not isinstance(other, torch.Tensor):
+            other = torch.as_tensor(other, device=input.device)
+        if not isinstance(input, torch.Tensor):
+            input = torch.as_tensor(input, device=other.device)
+        return fn(input, other)
+    f.__name__ = fn.__name__
+    f.__doc__ = f"torch.{fn.__name__} that also takes a Python scalar on either side."
+    return f
+
+
+logical_and, logical_or, logical_xor = _scalar_ok(torch.logical_and), _scalar_ok(torch.logical_or), _scalar_ok(torch.logical_xor)
+
+
+def where(condition, x=None, y=None):
+    """``where`` whose condition may be any dtype (non-zero is true) and whose branches may be Python scalars."""
+    if condition.dtype != torch.bool:
+        condition = condition != 0
+    if x is None and y is None:
+        return torch.where(condition)
+    return torch.where(condition, x, y)
+
+
+def masked_select(input, mask):
+    return torch.masked_select(input, mask if mask.dtype == torch.bool else mask != 0)
+
+
+def masked_fill(input, mask, value):
+    return torch.masked_fill(input, mask if mask.dtype == torch.bool else mask != 0, value)
+
+
+def nonzero(input, as_tuple=False):
+    return torch.nonzero(input, as_tuple=as_tuple)
+
+
+def empty_strided(size, stride, dtype=None, device=None, requires_grad=False, pin_memory=False, **kw):
+    t = torch.empty_strided(tuple(size), tuple(stride), dtype=dtype, device=device, pin_memory=pin_memory)
+    return t.requires_grad_(True) if requires_grad and (t.is_floating_point() or t.is_complex()) else t
+
+
+def install():
+    """Put the functions above where the reference has them."""
+    import oneflow_b200 as flow
+    from .. import _C
+    from ..nn import functional as NF
+    top = dict(addmm=addmm, matmul=matmul, bernoulli=bernoulli, logical_and=logical_and, logical_or=logical_or,
+               logical_xor=logical_xor, where=where, masked_select=masked_select, masked_fill=masked_fill, nonzero=nonzero,
+               empty_strided=empty_strided)
+    for k, v in top.items():
+        setattr(flow, k, v)
+        setattr(_C, k, v)
+    for k, v in dict(one_hot=one_hot, dropout=dropout).items():
+        setattr(NF, k, v)
+        setattr(_C, k, v)
+    flow.nn.Dropout = Dropout
+
+    T = torch.Tensor
+    T.contiguous_ = lambda self: _C.contiguous_(self)
+    T.addmm = lambda self, mat1, mat2, alpha=1, beta=1: addmm(self, mat1, mat2, alpha, beta)
+    T.logical_and = lambda self, other: logical_and(self, other)
+    T.logical_or = lambda self, other: logical_or(self, other)
+    T.logical_xor = lambda self, other: logical_xor(self, other)
+    _copy = T.copy_
+
+    def copy_(self, other, non_blocking=False):
+        """``copy_`` that also takes a numpy array (the reference's ``Tensor.copy_`` does)."""
+        if isinstance(other, np.ndarray):
+            other = torch.from_numpy(other)
+        if self.is_leaf and self.requires_grad and torch.is_grad_enabled():
+            with torch.no_grad():                   # overwriting a parameter's value is not a differentiable step
+                return _copy(self, other, non_blocking)
+        return _copy(self, other, non_blocking)
+    T.copy_ = copy_

@@ -19,7 +19,17 @@ class _TensorMeta(type):
         return isinstance(obj, torch.Tensor)
 
     def __call__(cls, *args, **kwargs):
-        return torch.Tensor(*args, **kwargs)
+        """``flow.Tensor(2, 3)`` allocates; ``flow.Tensor(data)`` copies ``data`` (array, list, tensor) into a new
+        float32 tensor — never aliasing the caller's numpy memory — on ``device`` when given."""
+        if len(args) == 1 and not isinstance(args[0], (int, torch.Size)):
+            data = args[0]
+            dev = kwargs.get("device")
+            if isinstance(data, torch.Tensor):
+                return data.detach().clone().to(device=dev if dev is not None else data.device)
+            return torch.tensor(np.asarray(data), dtype=kwargs.get("dtype", torch.float32), device=dev)
+        dev = kwargs.pop("device", None)
+        t = torch.Tensor(*args, **kwargs)
+        return t.to(dev) if dev is not None else t
 
     def __getattr__(cls, name):
         """``flow.Tensor.add`` and the like: the unbound tensor methods."""

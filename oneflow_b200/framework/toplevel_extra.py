@@ -113,7 +113,7 @@ def gather_nd(x, index):
 
 
 def in_top_k(targets, predictions, k):
-    top = predictions.topk(k, dim=-1).indices
+    top = predictions.topk(min(int(k), predictions.shape[-1]), dim=-1).indices
     return (top == targets.long().unsqueeze(-1)).any(-1)
 
 
@@ -326,3 +326,20 @@ stateful_op = _stub_module("stateful_op", "Stateful op holder of the reference's
 
 
 from .. import remat  # noqa: E402,F401
+
+
+def Generator(device="auto"):
+    """``flow.Generator(device)``; ``"auto"`` picks CUDA when there is a device, the host otherwise
+    (reference: python/oneflow/framework/generator.py)."""
+    if str(device) == "auto":
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    return torch.Generator(device=device)
+
+
+def default_generator(device="auto"):
+    if str(device) == "auto":
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        return torch.cuda.default_generators[dev.index if dev.index is not None else torch.cuda.current_device()]
+    return torch.default_generator

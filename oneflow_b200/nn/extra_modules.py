@@ -16,7 +16,7 @@ class CombinedMarginLoss(nn.Module):
         self.m1, self.m2, self.m3 = m1, m2, m3
 
     def forward(self, x, label):
-        onehot = torch.nn.functional.one_hot(label, x.shape[-1]).bool()
+        onehot = torch.nn.functional.one_hot(label.long(), x.shape[-1]).bool()
         theta = torch.acos(x.clamp(-1 + 1e-7, 1 - 1e-7))
         target = torch.cos(self.m1 * theta + self.m2) - self.m3
         return torch.where(onehot, target, x)

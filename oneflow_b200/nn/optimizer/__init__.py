@@ -10,7 +10,7 @@ from ...optim import lr_scheduler as _lrs
 _FILES = {
     "adadelta": (_optim, ["Adadelta"]), "adagrad": (_optim, ["Adagrad"]), "adam": (_optim, ["Adam"]),
     "adamw": (_optim, ["AdamW"]), "lamb": (_optim, ["LAMB"]), "lbfgs": (_optim, ["LBFGS"]),
-    "rmsprop": (_optim, ["RMSprop"]), "sgd": (_optim, ["SGD"]), "swa_utils": (_optim.swa_utils, ["AveragedModel", "SWALR", "update_bn"]),
+    "rmsprop": (_optim, ["RMSprop"]), "sgd": (_optim, ["SGD"]), "ftrl": (_optim, ["Ftrl"]), "swa_utils": (_optim.swa_utils, ["AveragedModel", "SWALR", "update_bn"]),
     "lr_scheduler": (_lrs, ["LRScheduler"]), "chained_scheduler": (_lrs, ["ChainedScheduler"]),
     "constant_lr": (_lrs, ["ConstantLR"]), "cosine_annealing_lr": (_lrs, ["CosineAnnealingLR"]),
     "cosine_annealing_warm_restarts": (_lrs, ["CosineAnnealingWarmRestarts"]), "cosine_decay_lr": (_lrs, ["CosineDecayLR"]),

@@ -41,7 +41,7 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=Fals
         else:
             norms.append(torch.linalg.vector_norm(g.detach(), norm_type).float().cpu())
     if math.isinf(norm_type):
-        total = torch.stack(norms).max()
+        total = torch.stack(norms).max() if norm_type > 0 else torch.stack(norms).min()
     else:
         total = torch.linalg.vector_norm(torch.stack(norms), norm_type)
     if error_if_nonfinite and not torch.isfinite(total):

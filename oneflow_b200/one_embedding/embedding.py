@@ -476,17 +476,7 @@ class MultiTableMultiColumnEmbedding(Embedding):
     """Tables whose rows are made of several columns with their own initializers (summed dims == embedding_dim)."""
 
 
-class Ftrl(torch.optim.Optimizer):
-    """FTRL-proximal for embedding rows (reference: python/oneflow/one_embedding.py Ftrl)."""
-
-    def __init__(self, params, lr=1e-3, weight_decay=0.0, lr_power=-0.5, initial_accumulator_value=0.1, lambda1=0.0,
-                 lambda2=0.0, beta=0.0):
-        super().__init__(params, dict(lr=lr, weight_decay=weight_decay, lr_power=lr_power,
-                                      initial_accumulator_value=initial_accumulator_value, lambda1=lambda1,
-                                      lambda2=lambda2, beta=beta))
-
-    def step(self, closure=None):
-        return closure() if closure is not None else None
+from ..optim.optimizer import Ftrl  # noqa: E402  (the dense FTRL optimizer; sparse rows take the FTRL row update)
 
 
 class SmartDecayAdam(torch.optim.Adam):

@@ -2,8 +2,8 @@
 import torch.optim as _torch_optim
 from torch.optim import swa_utils  # noqa: F401
 
-from . import lr_scheduler  # noqa: F401
-from .optimizer import LAMB, LBFGS, SGD, Adadelta, Adagrad, Adam, AdamW, RMSprop  # noqa: F401
+from . import lr_scheduler, optimizer  # noqa: F401
+from .optimizer import LAMB, LBFGS, SGD, Adadelta, Adagrad, Adam, AdamW, Ftrl, ParamGroup, RMSprop  # noqa: F401
 
 from .optimizer import _ClipMixin  # noqa: E402
 

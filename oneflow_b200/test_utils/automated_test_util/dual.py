@@ -186,6 +186,12 @@ class DualObject:
     def __bool__(self):
         return bool(self.pytorch)
 
+    def __array__(self, dtype=None, copy=None):
+        """numpy sees the PyTorch side (``np.allclose(flow_result.numpy(), dual.numpy())`` in hand-written checks)."""
+        p = self.pytorch
+        a = p.detach().cpu().numpy() if isinstance(p, torch_original.Tensor) else np.asarray(p)
+        return a.astype(dtype) if dtype is not None else a
+
     def __index__(self):
         return operator.index(self.pytorch)
 
