@@ -19,7 +19,8 @@ def matmul(input, other, transpose_a=False, transpose_b=False, alpha=1.0):
     """MatMul with optional transposes of the two innermost axes and a scale."""
     a = input.transpose(-1, -2) if transpose_a else input
     b = other.transpose(-1, -2) if transpose_b else other
-    out = torch.matmul(a, b)
+    from .global_tensor import matmul_any
+    out = matmul_any(a, b)
     return out if alpha == 1.0 else out * alpha
 
 
@@ -112,6 +113,82 @@ def empty_strided(size, stride, dtype=None, device=None, requires_grad=False, pi
     return t.requires_grad_(True) if requires_grad and (t.is_floating_point() or t.is_complex()) else t
 
 
+class PixelShuffle(torch.nn.Module):
+    """Pixel shuffle with separate height and width factors: ``[N, C*h*w, H, W] -> [N, C, H*h, W*w]``
+    (reference: python/oneflow/nn/modules/pixelshuffle.py)."""
+
+    def __init__(self, upscale_factor=None, h_upscale_factor=None, w_upscale_factor=None):
+        super().__init__()
+        if upscale_factor is not None:
+            if h_upscale_factor is not None or w_upscale_factor is not None:
+                raise ValueError("give either upscale_factor or h_upscale_factor and w_upscale_factor")
+            h_upscale_factor = w_upscale_factor = upscale_factor
+        if h_upscale_factor is None or w_upscale_factor is None:
+            raise ValueError("h_upscale_factor and w_upscale_factor are both required")
+        if h_upscale_factor <= 0 or w_upscale_factor <= 0:
+            raise ValueError("The scale factor of height and width must larger than zero")
+        self.h_upscale_factor, self.w_upscale_factor = int(h_upscale_factor), int(w_upscale_factor)
+
+    def forward(self, input):
+        n, c, h, w = input.shape
+        hf, wf = self.h_upscale_factor, self.w_upscale_factor
+        if c % (hf * wf):
+            raise ValueError("The channels of input tensor must be divisible by (h_upscale_factor * w_upscale_factor)")
+        out = input.reshape(n, c // (hf * wf), hf, wf, h, w).permute(0, 1, 4, 2, 5, 3)
+        return out.reshape(n, c // (hf * wf), h * hf, w * wf)
+
+    def extra_repr(self):
+        return f"w_upscale_factor={self.w_upscale_factor}, h_upscale_factor={self.h_upscale_factor}"
+
+
+def _C_slice(x, start, stop, step):
+    """``_C.slice(x, start, stop, step)``: one entry per leading axis."""
+    return x[tuple(slice(a, b, c) for a, b, c in zip(start, stop, step))]
+
+
+def _C_slice_update(x, update, start, stop, step, inplace=False):
+    """``_C.slice_update(ref, value, start, stop, step)``: writes ``value`` into the slice; differentiable in both."""
+    out = x if inplace else x.clone()
+    out[tuple(slice(a, b, c) for a, b, c in zip(start, stop, step))] = update
+    return out
+
+
+_TYPE_NAMES = {torch.float32: "FloatTensor", torch.float64: "DoubleTensor", torch.float16: "HalfTensor",
+               torch.bfloat16: "BFloat16Tensor", torch.uint8: "ByteTensor", torch.int8: "CharTensor", torch.int16: "ShortTensor",
+               torch.int32: "IntTensor", torch.int64: "LongTensor", torch.bool: "BoolTensor",
+               torch.complex64: "ComplexFloatTensor", torch.complex128: "ComplexDoubleTensor"}
+
+
+def _tensor_type(self, dtype=None, non_blocking=False, **kw):
+    """``Tensor.type()`` names the type as ``oneflow.FloatTensor`` / ``oneflow.cuda.FloatTensor``; with an argument
+    (a dtype, a type name or a typed-tensor class) it converts."""
+    if dtype is None:
+        return ("oneflow.cuda." if self.is_cuda else "oneflow.") + _TYPE_NAMES[self.dtype]
+    if isinstance(dtype, torch.dtype):
+        return self.to(dtype)
+    name = dtype if isinstance(dtype, str) else getattr(dtype, "__name__", str(dtype))
+    cuda = ".cuda." in "." + name or getattr(dtype, "is_cuda", False)
+    short = name.split(".")[-1]
+    for dt, n in _TYPE_NAMES.items():
+        if n == short:
+            out = self.to(dt)
+            if cuda and not out.is_cuda:
+                out = out.cuda()
+            elif not cuda and out.is_cuda and isinstance(dtype, str) and name.startswith(("oneflow.", "torch.")) and ".cuda." not in name:
+                out = out.cpu()
+            return out
+    raise ValueError(f"invalid type: '{name}'")
+
+
+def sort(input, dim=-1, descending=False, stable=True):
+    """Sort with ties kept in index order (the reference's sort is stable; results match numpy's on small inputs)."""
+    return torch.sort(input, dim=dim, descending=descending, stable=stable)
+
+
+def argsort(input, dim=-1, descending=False, stable=True):
+    return torch.argsort(input, dim=dim, descending=descending, stable=stable)
+
+
 def install():
     """Put the functions above where the reference has them."""
     import oneflow_b200 as flow
@@ -119,7 +196,7 @@ def install():
     from ..nn import functional as NF
     top = dict(addmm=addmm, matmul=matmul, bernoulli=bernoulli, logical_and=logical_and, logical_or=logical_or,
                logical_xor=logical_xor, where=where, masked_select=masked_select, masked_fill=masked_fill, nonzero=nonzero,
-               empty_strided=empty_strided)
+               empty_strided=empty_strided, sort=sort, argsort=argsort)
     for k, v in top.items():
         setattr(flow, k, v)
         setattr(_C, k, v)
@@ -127,9 +204,15 @@ def install():
         setattr(NF, k, v)
         setattr(_C, k, v)
     flow.nn.Dropout = Dropout
+    flow.nn.PixelShuffle = PixelShuffle
+    _C.slice = _C_slice
+    _C.slice_update = _C_slice_update
+    torch.Tensor.type = _tensor_type
 
     T = torch.Tensor
     T.contiguous_ = lambda self: _C.contiguous_(self)
+    T.sort = lambda self, dim=-1, descending=False, stable=True: sort(self, dim, descending, stable)
+    T.argsort = lambda self, dim=-1, descending=False, stable=True: argsort(self, dim, descending, stable)
     T.addmm = lambda self, mat1, mat2, alpha=1, beta=1: addmm(self, mat1, mat2, alpha, beta)
     T.logical_and = lambda self, other: logical_and(self, other)
     T.logical_or = lambda self, other: logical_or(self, other)

@@ -90,6 +90,25 @@ class GlobalTensor(torch.Tensor):
     def tolist(self):
         return self.numpy().tolist()
 
+    def new(self, *args, **kwargs):
+        """``x.new()`` / ``x.new(*sizes)`` / ``x.new(data)``: a new tensor of this tensor's dtype, placement and sbp."""
+        from . import tensor_api
+        if len(args) == 1 and not isinstance(args[0], (int, torch.Size)):
+            return tensor_api.tensor(args[0], dtype=self.dtype, placement=self._placement, sbp=self._nd_sbp)
+        size = tuple(args[0]) if len(args) == 1 and isinstance(args[0], torch.Size) else tuple(args)
+        size = size if size else (0,)
+        return tensor_api.empty(size, dtype=self.dtype, placement=self._placement, sbp=self._safe_sbp(size))
+
+    def _safe_sbp(self, size):
+        """This tensor's sbp where it fits a tensor of ``size``; axes that cannot be split there are broadcast."""
+        return tuple(s if s.kind != "S" or (s.axis < len(size) and size[s.axis] >= self._placement.hierarchy[i]) else B
+                     for i, s in enumerate(self._nd_sbp))
+
+    def type_as(self, other):
+        if isinstance(other, GlobalTensor):
+            return self.to(other.dtype)
+        return self.to_local().to(other.dtype)
+
     def __repr__(self):
         return (f"GlobalTensor(shape={tuple(self.shape)}, dtype={self.dtype}, placement={self._placement}, "
                 f"sbp={tuple(str(s) for s in self._nd_sbp)}, local_shape={tuple(self._local.shape)})")
@@ -100,9 +119,32 @@ class GlobalTensor(torch.Tensor):
 
     __torch_function__ = torch._C._disabled_torch_function_impl
 
+    # matmul with a 1-D operand: torch finishes that case with an in-place ``squeeze_``, which cannot change the logical
+    # shape a wrapper tensor was built with, so the method spellings (and ``flow.matmul``) use out-of-place squeezes
+    def matmul(self, other):
+        return matmul_any(self, other)
+
+    def __matmul__(self, other):
+        return matmul_any(self, other)
+
+    def __rmatmul__(self, other):
+        return matmul_any(other, self)
+
     @classmethod
     def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
         return dispatch(func, args, kwargs or {})
+
+
+def matmul_any(a, b):
+    """``a @ b`` for any ranks, global or local operands."""
+    if a.dim() == 1 or b.dim() == 1:
+        out = torch.matmul(a.unsqueeze(0) if a.dim() == 1 else a, b.unsqueeze(-1) if b.dim() == 1 else b)
+        if b.dim() == 1:
+            out = out.squeeze(-1)
+        if a.dim() == 1:
+            out = out.squeeze(-1 if b.dim() == 1 else -2)
+        return out
+    return torch.matmul(a, b)
 
 
 def is_global(x):
@@ -482,6 +524,8 @@ def view_rule(func, args, kwargs):
         target = None
         acc = 1
         for j, o in enumerate(out_shape):
+            if acc == pre and o == 1 and in_shape[d] != 1:
+                continue                       # a size-1 axis inserted in front of the split dimension
             if acc == pre and o != 0:
                 n = pl.hierarchy[axis]
                 # d is the leading factor of output dim j (trailing dims merged in) or is itself cut in two

@@ -245,8 +245,8 @@ def roc_auc_score(label, pred):
     pos = y > 0.5
     n_pos, n_neg = int(pos.sum()), int((~pos).sum())
     if n_pos == 0 or n_neg == 0:
-        return torch.tensor(float("nan"))
-    return (ranks[pos].sum() - n_pos * (n_pos + 1) / 2) / (n_pos * n_neg)
+        return torch.tensor([float("nan")])
+    return ((ranks[pos].sum() - n_pos * (n_pos + 1) / 2) / (n_pos * n_neg)).reshape(1)
 
 
 # ------------------------------------------------------------------------------------------------ tensor buffers (ragged lists)
@@ -275,6 +275,13 @@ def tensor_buffer_to_list_of_tensors(buf, out_shapes=None, out_dtypes=None, dyna
             t = t.to(out_dtypes[i] if i < len(out_dtypes) else out_dtypes[-1])
         out.append(t)
     return out
+
+
+def tensor_buffer_to_tensor(buf, dtype, instance_shape):
+    """Stack equally shaped buffer entries into one ``[*batch, *instance_shape]`` tensor."""
+    out = torch.stack([t.reshape(tuple(instance_shape)).to(dtype) for t in buf.tensors])
+    lead = getattr(buf, "batch_shape", None)
+    return out.reshape(tuple(lead) + tuple(instance_shape)) if lead else out
 
 
 def gen_tensor_buffer(shape, shape_list, value_list, data_type=torch.float32, dynamic_out=False):
@@ -336,10 +343,4 @@ def Generator(device="auto"):
     return torch.Generator(device=device)
 
 
-def default_generator(device="auto"):
-    if str(device) == "auto":
-        device = "cuda" if torch.cuda.is_available() else "cpu"
-    dev = torch.device(device)
-    if dev.type == "cuda":
-        return torch.cuda.default_generators[dev.index if dev.index is not None else torch.cuda.current_device()]
-    return torch.default_generator
+default_generator = torch.default_generator     # the process-wide generator object (seed / manual_seed / get_state)

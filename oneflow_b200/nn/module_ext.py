@@ -38,25 +38,14 @@ def module_to_local(self):
 
 
 def make_contiguous_params_group(self):
-    """Moves all (local) parameters into one flat buffer per dtype; returns {dtype: flat tensor}."""
-    by_dtype = {}
-    for p in self.parameters():
-        if isinstance(p, GT.GlobalTensor):
-            continue
-        by_dtype.setdefault((p.dtype, p.device), []).append(p)
-    flats = {}
-    for (dt, dev), ps in by_dtype.items():
-        sizes = [(p.numel() + 63) // 64 * 64 for p in ps]
-        flat = torch.zeros(sum(sizes), dtype=dt, device=dev)
-        off = 0
-        for p, n in zip(ps, sizes):
-            view = flat[off:off + p.numel()].view(p.shape)
-            view.copy_(p.data)
-            p.data = view
-            off += n
-        flats[dt] = flat
-    self._contiguous_params = flats
-    return flats
+    """Moves all local parameters (and their gradients) into flat buffers, one per dtype and device, and keeps the
+    grouping as ``self.cpg`` (a ``nn.utils.ContiguousParamsGroup``): optimizers and gradient collectives can then work
+    on ``self.cpg.grouped_parameters`` / ``grouped_grads`` (reference: python/oneflow/nn/modules/module.py,
+    ``make_contiguous_params_group``)."""
+    from .utils import ContiguousParamsGroup
+    params = [p for p in self.parameters() if not isinstance(p, GT.GlobalTensor)]
+    self.cpg = ContiguousParamsGroup([params], group_on_current_buffer=False)
+    return self.cpg
 
 
 def install():
@@ -66,4 +55,14 @@ def install():
     M.to_global = module_to_global
     M.to_local = module_to_local
     M.make_contiguous_params_group = make_contiguous_params_group
+    _load = M.load_state_dict
+
+    def load_state_dict(self, state_dict, strict=True, assign=False):
+        """``load_state_dict`` that also takes numpy arrays as values (the reference converts them)."""
+        import numpy as np
+        if any(isinstance(v, np.ndarray) for v in state_dict.values()):
+            state_dict = type(state_dict)((k, torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
+                                          for k, v in state_dict.items())
+        return _load(self, state_dict, strict=strict, assign=assign)
+    M.load_state_dict = load_state_dict
     M._ofb_patched = True

@@ -95,7 +95,38 @@ class ContiguousParamsGroup:
         else:
             self._group_on_new_buffer()
 
+    def _group_globals(self):
+        """Global parameters: one flat buffer of this rank's shards per (group, dtype, placement, sbp); each parameter's
+        local shard and local gradient become views into it, and the buffer is presented as a global tensor of the
+        same placement and sbp (its logical extent is the local extent times the number of shards when split)."""
+        from ...framework import global_tensor as GT
+        todo = {}
+        for idx, params in enumerate(self.params_group_list):
+            for p in params:
+                if isinstance(p, GT.GlobalTensor):
+                    todo.setdefault((p.dtype, p.placement, tuple(p.sbp), idx), []).append(p)
+        for (dt, pl, nd, idx), ps in todo.items():
+            total = sum(numel_in_bucket(p._local) for p in ps)
+            flat = torch.zeros(total, dtype=dt, device=ps[0]._local.device)
+            gflat = torch.zeros(total, dtype=dt, device=ps[0]._local.device)
+            at = 0
+            for p in ps:
+                n = p._local.numel()
+                flat[at:at + n] = p._local.detach().reshape(-1)
+                p._local.data = flat[at:at + n].view(p._local.shape)
+                p._ofb_grad_view = gflat[at:at + n].view(p._local.shape)
+                at += numel_in_bucket(p._local)
+            shards = 1
+            for axis, s in enumerate(nd):
+                if s.kind == "S":
+                    shards *= pl.hierarchy[axis]
+            flat_nd = tuple(GT.S.split(0) if s.kind == "S" else s for s in nd)
+            self.grouped_tensors.append(GT.wrap(flat, (total * shards,), pl, flat_nd))
+            self.grouped_grads.append(GT.wrap(gflat, (total * shards,), pl, flat_nd))
+        self.params_group_list = [[p for p in params if not isinstance(p, GT.GlobalTensor)] for params in self.params_group_list]
+
     def _group_on_new_buffer(self):
+        self._group_globals()
         sizes = {}
         for idx, params in enumerate(self.params_group_list):
             for p in params:
@@ -123,11 +154,10 @@ class ContiguousParamsGroup:
 
     def _group_on_current_buffer(self):
         for params in self.params_group_list:
-            by_buf = {}
+            by_buf, alone = {}, []
             for p in params:
                 if not hasattr(p, "_ref_tensor"):
-                    self.grouped_tensors.append(p)        # never grouped before: stays on its own
-                    self.grouped_grads.append(p.grad)
+                    alone.append(p)                       # never grouped before: stays on its own, after the buffers
                     continue
                 by_buf.setdefault(id(p._ref_tensor), []).append(p)
             for members in by_buf.values():
@@ -144,6 +174,17 @@ class ContiguousParamsGroup:
                     lo, hi = q._ref_index, q._ref_index + numel_in_bucket(q)
                 self.grouped_tensors.append(buf[lo:hi])
                 self.grouped_grads.append(buf.grad[lo:hi])
+            for p in alone:
+                self.grouped_tensors.append(p)
+                self.grouped_grads.append(p.grad)
+
+    @property
+    def grouped_grads(self):
+        return self._grouped_grads
+
+    @grouped_grads.setter
+    def grouped_grads(self, v):
+        self._grouped_grads = v
 
     @property
     def grouped_parameters(self):

@@ -29,6 +29,10 @@ class sbp:
     def __getstate__(self):
         return (self.kind, self.axis)
 
+    def __call__(self):
+        """``flow.sbp.broadcast()`` / ``flow.sbp.split(0)()``: the symbol itself (both spellings are in use)."""
+        return self
+
     def is_split(self):
         return self.kind == "S"
 
