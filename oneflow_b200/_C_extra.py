@@ -168,46 +168,77 @@ def fused_codegeex_qkv_reshape(query, key, value, num_attention_heads):
 
 def fused_attention_concat_past_key_value(*, past_key=None, past_key_layout="BHMK", past_value=None, past_value_layout="BHMK", key,
                                           key_layout="BHMK", value, value_layout="BHMK", key_head_size=None):
-    """Appends this step's key / value to the cache along the sequence axis (M) of the given layout."""
-    def seq_axis(layout):
-        return layout.replace("(", "").replace(")", "").index("M")
-    if past_key is None:
-        return key, value
-    return torch.cat([past_key, key], seq_axis(past_key_layout)), torch.cat([past_value, value], seq_axis(past_value_layout))
+    """Appends this step's key / value to the cache along the sequence axis.  The new tensors may come in any layout
+    (also packed ``H2K`` / ``H3K``: key is tensor 0 / 1, value tensor 1 / 2 of the packing); the results are laid out
+    like the caches (``past_*_layout``)."""
+    from .ops import attn_layout as L
+    hs = key_head_size
+    if hs is None:
+        ref = key if key_layout in ("BHMK", "BMHK", "MBHK") else (past_key if past_key is not None and past_key.dim() == 4 else None)
+        if ref is None:
+            raise ValueError("key_head_size is required when no 4-D tensor gives the head size")
+        hs = ref.shape[-1]
+    k_index = {"H2K": 0, "H3K": 1}.get(key_layout[3:-1] if "(" in key_layout else "", 0)
+    v_index = {"H2K": 1, "H3K": 2}.get(value_layout[3:-1] if "(" in value_layout else "", 0)
+    k = L.unpack(key, key_layout, head_size=hs, index=k_index)
+    v = L.unpack(value, value_layout, head_size=hs, index=v_index)
+    if past_key is not None:
+        k = torch.cat([L.unpack(past_key, past_key_layout, head_size=hs), k], 2)
+        v = torch.cat([L.unpack(past_value, past_value_layout, head_size=hs), v], 2)
+    return L.pack(k, past_key_layout).contiguous(), L.pack(v, past_value_layout).contiguous()
 
 
 def fused_apply_rotary_emb(x, *, cos=None, sin=None, position_ids=None, x_layout="BHMK", output_layout=None, mode="plane",
                            tensor_index=None, k_size=None, base=1e4, rotary_size=None):
-    """Rotary position embedding on the last dimension. mode "plane": the two halves of the rotary part form the
-    pairs; "interval": neighbouring elements do. cos / sin default to the standard base-10000 table at the
-    positions 0..M-1 (or position_ids)."""
-    layout = x_layout.replace("(", "").replace(")", "")
-    if layout not in ("BHMK", "BMHK", "MBHK"):
-        raise ValueError("fused_apply_rotary_emb: unsupported layout " + x_layout)
-    m_axis = layout.index("M")
-    K_ = x.shape[-1]
-    rot = rotary_size or K_
-    M = x.shape[m_axis]
+    """Rotary position embedding over the first ``rotary_size`` elements of every head.
+
+    ``cos`` / ``sin``: tables ``[positions, rotary_size // n]``, column ``c`` used for element ``c`` of a block; computed
+    from ``base`` when absent, the two elements of pair ``j`` then get the frequency ``base ** (-2j / (rotary_size // n))``.  ``position_ids``: ``[B, n, M]`` for
+    ``n``-dimensional positions (the rotary part splits into ``n`` blocks, one per coordinate); positions ``0..M-1``
+    when absent.  Element ``i`` of a block is paired in ``"plane"`` mode with the element half a block away
+    (``(-x2, x1)``), in ``"interval"`` mode with its neighbour (``(-x[2j+1], x[2j])``).  ``x`` may be packed
+    (``BM(H3K)``: ``tensor_index`` picks query / key / value); the result comes in ``output_layout``
+    (reference: oneflow/user/kernels/fused_attention_kernels.cu, FusedApplyRotaryEmb)."""
+    from .ops import attn_layout as L
+    packed = x_layout.endswith(("(H2K)", "(H3K)"))
+    if packed and (output_layout is None or output_layout == x_layout):
+        # the packed tensors are all rotated and come back packed the same way
+        n = 2 if x_layout.endswith("(H2K)") else 3
+        parts = [fused_apply_rotary_emb(x, cos=cos, sin=sin, position_ids=position_ids, x_layout=x_layout, output_layout="BMHK",
+                                        mode=mode, tensor_index=t, k_size=k_size, base=base, rotary_size=rotary_size)
+                 for t in range(n)]
+        y = torch.stack(parts, 3)                                                 # [B, M, H, n, K]
+        y = y.reshape(y.shape[0], y.shape[1], -1)
+        return (y if x_layout.startswith("BM") else y.transpose(0, 1)).contiguous()
+    q = L.unpack(x, x_layout, head_size=k_size, index=tensor_index or 0)
+    B, H, M, K = q.shape
+    rs = int(rotary_size) if rotary_size else K
+    nd = position_ids.shape[1] if position_ids is not None else 1
+    act = rs // nd
+    dev = x.device
+    i = torch.arange(rs, device=dev)
+    col, blk = i % act, i // act
+    pos = position_ids.to(dev).long() if position_ids is not None else torch.arange(M, device=dev).expand(B, 1, M)
+    p = pos[:, blk, :].permute(0, 2, 1)                                             # [B, M, rs]: position per element
     if cos is None or sin is None:
-        pos = position_ids.float() if position_ids is not None else torch.arange(M, device=x.device, dtype=torch.float32)
-        inv = base ** (-torch.arange(0, rot, 2, device=x.device, dtype=torch.float32) / rot)
-        ang = pos.reshape(-1, 1) * inv
-        ang = torch.cat([ang, ang], -1) if mode == "plane" else ang.repeat_interleave(2, -1)
-        cos, sin = ang.cos(), ang.sin()
-    shape = [1] * x.dim()
-    shape[m_axis], shape[-1] = cos.shape[0], rot
-    c, s = cos[..., :rot].reshape(shape).to(x.dtype), sin[..., :rot].reshape(shape).to(x.dtype)
-    xr, rest = x[..., :rot], x[..., rot:]
-    if mode == "plane":
-        h = rot // 2
-        rotated = torch.cat([-xr[..., h:], xr[..., :h]], -1)
+        # pair index of an element: its offset inside the half block ("plane") or half its offset ("interval")
+        pair = col % max(act // 2, 1) if mode == "plane" else col // 2
+        freq = float(base) ** (-2.0 * pair.float() / act)
+        ang = p.float() * freq
+        c, s = ang.cos(), ang.sin()
     else:
-        rotated = torch.stack([-xr[..., 1::2], xr[..., 0::2]], -1).flatten(-2)
-    y = torch.cat([xr * c + rotated * s, rest], -1)
-    if output_layout and output_layout.replace("(", "").replace(")", "") != layout:
-        out = output_layout.replace("(", "").replace(")", "")
-        y = y.permute([layout.index(ch) for ch in out])
-    return y
+        c, s = cos.to(dev)[p, col], sin.to(dev)[p, col]
+    c, s = c[:, None].to(q.dtype), s[:, None].to(q.dtype)                           # [B, 1, M, rs]
+    xr = q[..., :rs]
+    if mode == "plane":
+        xb = xr.reshape(B, H, M, nd, act)
+        rot = torch.cat([-xb[..., act // 2:], xb[..., :act // 2]], -1).reshape(B, H, M, rs)
+    elif mode == "interval":
+        rot = torch.stack([-xr[..., 1::2], xr[..., 0::2]], -1).flatten(-2)
+    else:
+        raise ValueError(f"fused_apply_rotary_emb: unknown mode {mode!r}")
+    y = torch.cat([xr * c + rot * s, q[..., rs:]], -1)
+    return L.pack(y, output_layout or x_layout).contiguous()
 
 
 # ------------------------------------------------------------------------------------------------ box IoU family (YOLO CIoU loss)

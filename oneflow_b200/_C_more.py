@@ -857,10 +857,10 @@ def multi_tensor_adam_update(model, model_diff, m, v, learning_rate_val, l2, bet
 
 
 def multi_tensor_yolov5_weight_update(model, model_update, d):
-    """MultiTensorYoloV5WeightUpdate: the EMA step ``update = d * update + (1 - d) * model``."""
+    """MultiTensorYoloV5WeightUpdate: the EMA step ``model = d * model + (1 - d) * model_update``, in place."""
     with torch.no_grad():
-        torch._foreach_mul_(list(model_update), d)
-        torch._foreach_add_(list(model_update), list(model), alpha=1 - d)
+        torch._foreach_mul_(list(model), d)
+        torch._foreach_add_(list(model), list(model_update), alpha=1 - d)
 
 
 # ------------------------------------------------------------------------------------------------ gradient accumulation helpers

@@ -189,6 +189,26 @@ def argsort(input, dim=-1, descending=False, stable=True):
     return torch.argsort(input, dim=dim, descending=descending, stable=stable)
 
 
+def _C_group_norm(x, gamma=None, beta=None, affine=False, num_groups=1, epsilon=1e-5, data_format="channels_first",
+                  activation="none"):
+    """``_C.group_norm``: group normalisation over channels-first or channels-last data with an optional fused
+    activation (``"none"`` or ``"silu"``)."""
+    if data_format == "channels_last":
+        x = x.movedim(-1, 1)
+    y = F.group_norm(x, num_groups, gamma if affine else None, beta if affine else None, epsilon)
+    if activation == "silu":
+        y = F.silu(y)
+    elif activation not in (None, "none"):
+        raise ValueError(f"group_norm: unsupported activation {activation!r}")
+    return y.movedim(1, -1) if data_format == "channels_last" else y
+
+
+def _C_roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio, aligned):
+    """``_C.roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio, aligned)``."""
+    from .toplevel_extra import roi_align
+    return roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio, aligned)
+
+
 def install():
     """Put the functions above where the reference has them."""
     import oneflow_b200 as flow
@@ -206,6 +226,8 @@ def install():
     flow.nn.Dropout = Dropout
     flow.nn.PixelShuffle = PixelShuffle
     _C.slice = _C_slice
+    _C.group_norm = _C_group_norm
+    _C.roi_align = _C_roi_align
     _C.slice_update = _C_slice_update
     torch.Tensor.type = _tensor_type
 

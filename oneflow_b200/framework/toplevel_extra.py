@@ -197,7 +197,17 @@ def nms(boxes, scores, iou_threshold):
     return torch.stack(keep) if keep else torch.empty(0, dtype=torch.long, device=boxes.device)
 
 
-def roi_align(input, boxes, output_size, spatial_scale=1.0, sampling_ratio=-1, aligned=False):
+def roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio=-1, aligned=False):
+    """RoIAlign with the reference's argument order: ``x`` [N, C, H, W], ``rois`` [K, 5] = (batch index, x1, y1, x2, y2),
+    output ``[K, C, pooled_h, pooled_w]`` (reference: functional_api.yaml ``roi_align``)."""
+    try:
+        from torchvision.ops import roi_align as _tv
+    except ImportError:
+        return _roi_align_impl(x, rois, (int(pooled_h), int(pooled_w)), float(spatial_scale), int(sampling_ratio), bool(aligned))
+    return _tv(x, rois.to(x.dtype), (int(pooled_h), int(pooled_w)), float(spatial_scale), int(sampling_ratio), bool(aligned))
+
+
+def _roi_align_impl(input, boxes, output_size, spatial_scale=1.0, sampling_ratio=-1, aligned=False):
     """input [N, C, H, W]; boxes [K, 5] = (batch index, x1, y1, x2, y2). Bilinear RoIAlign (average of the samples)."""
     oh, ow = (output_size, output_size) if isinstance(output_size, int) else output_size
     N, C, H, W = input.shape
@@ -213,10 +223,13 @@ def roi_align(input, boxes, output_size, spatial_scale=1.0, sampling_ratio=-1, a
         sr_w = sampling_ratio if sampling_ratio > 0 else max(int(np.ceil(rw / ow)), 1)
         ys = y1 + (torch.arange(oh * sr_h, device=input.device, dtype=torch.float32) + 0.5) * rh / (oh * sr_h)
         xs = x1 + (torch.arange(ow * sr_w, device=input.device, dtype=torch.float32) + 0.5) * rw / (ow * sr_w)
-        gy = (ys / max(H - 1, 1)) * 2 - 1
-        gx = (xs / max(W - 1, 1)) * 2 - 1
+        # samples up to one pixel outside the map read the edge value, farther out they count as zero
+        vy, vx = ((ys >= -1) & (ys <= H)).float(), ((xs >= -1) & (xs <= W)).float()
+        gy = (ys.clamp(0, H - 1) / max(H - 1, 1)) * 2 - 1
+        gx = (xs.clamp(0, W - 1) / max(W - 1, 1)) * 2 - 1
         grid = torch.stack(torch.meshgrid(gy, gx, indexing="ij")[::-1], -1).unsqueeze(0)
         samp = F.grid_sample(input[b:b + 1].float(), grid, mode="bilinear", padding_mode="zeros", align_corners=True)
+        samp = samp * (vy[:, None] * vx[None, :])
         out[k] = samp.view(C, oh, sr_h, ow, sr_w).mean((2, 4)).to(input.dtype)
     return out
 

@@ -174,7 +174,7 @@ def test_rnn_cells_and_multi_tensor_updates():
     C.multi_tensor_adam_update(w, g, m, v, 0.01, 0.0, 0.9, 0.999, 1 - 0.9, 1 - 0.999, True, 1.0, 0.0, 1e-8)
     assert torch.allclose(w[0], p.detach(), atol=1e-6)
     ema, model = [torch.zeros(3)], [torch.ones(3)]
-    C.multi_tensor_yolov5_weight_update(model, ema, 0.9)
+    C.multi_tensor_yolov5_weight_update(ema, model, 0.9)
     assert torch.allclose(ema[0], torch.full((3,), 0.1))
     data, sizes = C.pack_padded_sequence(torch.arange(6.0).reshape(2, 3, 1), torch.tensor([3, 1]), True)
     assert sizes.tolist() == [2, 1, 1] and data.reshape(-1).tolist() == [0.0, 3.0, 1.0, 2.0]
