@@ -5,6 +5,8 @@ import torch
 import torch.nn.functional as F
 
 from oneflow_b200 import _C
+import oneflow as flow
+import pytest
 
 
 def test_fused_glu_modes():
@@ -88,3 +90,63 @@ def test_box_iou_family():
     y, alpha = _C.fused_get_ciou_result(v, iou, rho2, c2, 1e-7)
     torch.testing.assert_close(y, iou - (rho2 / c2 + v * (v / (v - iou + 1 + 1e-7))))
     assert torch.all(c2 >= rho2 - 1e-6)
+
+
+def test_attention_layouts_roundtrip_and_packing():
+    from oneflow_b200.ops import attn_layout as L
+    B, H, M, K = 2, 3, 5, 4
+    q, k, v = (torch.randn(B, H, M, K) for _ in range(3))
+    for layout in ("BHMK", "BMHK", "MBHK", "BM(HK)", "MB(HK)"):
+        assert torch.equal(L.unpack(L.pack(q, layout), layout, head_size=K), q), layout
+    packed = torch.stack([q, k, v], 3).permute(0, 2, 1, 3, 4).reshape(B, M, H * 3 * K)          # BM(H3K)
+    for i, t in enumerate((q, k, v)):
+        assert torch.equal(L.unpack(packed, "BM(H3K)", head_size=K, index=i), t)
+        assert torch.equal(L.unpack(packed.transpose(0, 1), "MB(H3K)", num_heads=H, index=i), t)
+    with pytest.raises(ValueError):
+        L.unpack(packed, "BM(H3K)")
+
+
+def test_concat_past_key_value_layouts():
+    B, H, M, K = 2, 3, 4, 8
+    pk, pv, nk, nv = (torch.randn(B, H, n, K) for n in (M, M, 1, 1))
+    ck, cv = flow._C.fused_attention_concat_past_key_value(
+        past_key=pk, past_key_layout="BHMK", past_value=pv.permute(2, 0, 1, 3), past_value_layout="MBHK",
+        key=nk.permute(0, 2, 1, 3).reshape(B, 1, H * K), key_layout="BM(HK)", value=nv.permute(0, 2, 1, 3), value_layout="BMHK",
+        key_head_size=K)
+    assert torch.equal(ck, torch.cat([pk, nk], 2)) and torch.equal(cv, torch.cat([pv, nv], 2).permute(2, 0, 1, 3))
+    k0, v0 = flow._C.fused_attention_concat_past_key_value(past_key_layout="BHMK", past_value_layout="BHMK", key=nk, key_layout="BHMK",
+                                                          value=nv, value_layout="BHMK")
+    assert torch.equal(k0, nk) and torch.equal(v0, nv)
+
+
+def test_rotary_embedding_modes_and_positions():
+    B, H, M, K, rs = 2, 2, 6, 8, 4
+    x = torch.randn(B, H, M, K)
+    pos = torch.randint(0, 12, (B, 1, M))
+    y = flow._C.fused_apply_rotary_emb(x, position_ids=pos, x_layout="BHMK", mode="interval", base=100.0, rotary_size=rs)
+    freq = 100.0 ** (-2.0 * torch.arange(rs // 2).float() / rs)
+    ang = pos[:, 0, :, None].float() * freq                                           # [B, M, rs/2]
+    c, s = ang.cos()[:, None], ang.sin()[:, None]
+    e, o = x[..., 0:rs:2], x[..., 1:rs:2]
+    assert torch.allclose(y[..., 0:rs:2], e * c - o * s, atol=1e-5) and torch.allclose(y[..., 1:rs:2], o * c + e * s, atol=1e-5)
+    assert torch.equal(y[..., rs:], x[..., rs:])                                      # the non-rotary tail passes through
+    y2 = flow._C.fused_apply_rotary_emb(x, position_ids=pos, x_layout="BHMK", mode="plane", base=100.0, rotary_size=rs)
+    a, b = x[..., :rs // 2], x[..., rs // 2:rs]
+    assert torch.allclose(y2[..., :rs // 2], a * c - b * s, atol=1e-5) and torch.allclose(y2[..., rs // 2:rs], b * c + a * s, atol=1e-5)
+    # rotations preserve the norm of every pair, whatever the layout the result is asked in
+    y3 = flow._C.fused_apply_rotary_emb(x.permute(0, 2, 1, 3).reshape(B, M, H * K), x_layout="BM(HK)", output_layout="MBHK", k_size=K,
+                                        mode="interval")
+    assert y3.shape == (M, B, H, K) and torch.allclose(y3.norm(dim=-1), x.permute(2, 0, 1, 3).norm(dim=-1), atol=1e-5)
+
+
+def test_roi_align_matches_torchvision_including_boxes_past_the_border():
+    import torchvision
+    from oneflow_b200.framework.toplevel_extra import _roi_align_impl
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 16, 16)
+    rois = torch.tensor([[0, 1., 2., 9., 11.], [1, 0.5, 0.5, 14.2, 8.8], [0, -3., -2., 40., 37.]])
+    for aligned in (False, True):
+        for sr in (2, -1):
+            ref = torchvision.ops.roi_align(x, rois, (5, 5), 0.5, sr, aligned)
+            assert torch.allclose(_roi_align_impl(x, rois, (5, 5), 0.5, sr, aligned), ref, atol=1e-5)
+            assert torch.allclose(flow.roi_align(x, rois, 0.5, 5, 5, sr, aligned), ref, atol=1e-5)
