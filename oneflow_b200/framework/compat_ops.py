@@ -209,6 +209,31 @@ def _C_roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio, ali
     return roi_align(x, rois, spatial_scale, pooled_h, pooled_w, sampling_ratio, aligned)
 
 
+def _long_target(t):
+    return t.long() if isinstance(t, torch.Tensor) and t.dtype in (torch.int32, torch.int16, torch.int8, torch.uint8) else t
+
+
+def cross_entropy(input, target, weight=None, size_average=None, ignore_index=-100, reduce=None, reduction="mean",
+                  label_smoothing=0.0):
+    """``cross_entropy`` whose class-index targets may be any integer dtype (the reference takes int32 labels)."""
+    return F.cross_entropy(input, _long_target(target), weight, ignore_index=ignore_index, reduction=reduction,
+                           label_smoothing=label_smoothing)
+
+
+def nll_loss(input, target, weight=None, size_average=None, ignore_index=-100, reduce=None, reduction="mean"):
+    return F.nll_loss(input, _long_target(target), weight, ignore_index=ignore_index, reduction=reduction)
+
+
+class CrossEntropyLoss(torch.nn.CrossEntropyLoss):
+    def forward(self, input, target):
+        return super().forward(input, _long_target(target))
+
+
+class NLLLoss(torch.nn.NLLLoss):
+    def forward(self, input, target):
+        return super().forward(input, _long_target(target))
+
+
 def install():
     """Put the functions above where the reference has them."""
     import oneflow_b200 as flow
@@ -220,7 +245,8 @@ def install():
     for k, v in top.items():
         setattr(flow, k, v)
         setattr(_C, k, v)
-    for k, v in dict(one_hot=one_hot, dropout=dropout).items():
+    flow.nn.CrossEntropyLoss, flow.nn.NLLLoss = CrossEntropyLoss, NLLLoss
+    for k, v in dict(one_hot=one_hot, dropout=dropout, cross_entropy=cross_entropy, nll_loss=nll_loss).items():
         setattr(NF, k, v)
         setattr(_C, k, v)
     flow.nn.Dropout = Dropout

@@ -285,4 +285,5 @@ def _install_reference_methods(T):
             t = torch.zeros(t.shape, dtype=t.dtype)          # the symbolic all-zero gradient of autograd, made real
         return _numpy(t, *args, **kwargs)
     T.numpy = numpy
+    T.is_view = lambda self: self._is_view()
     T._meta_repr = lambda self: f"tensor(..., size={tuple(self.shape)}, dtype={self.dtype}, device={self.device})"

@@ -512,7 +512,14 @@ class Graph:
                 opt = o["optim"]
                 if hasattr(opt, "clip_grad"):
                     opt.clip_grad()
-                opt.step()
+                scaled = [(g, g["lr"]) for g in opt.param_groups if g.get("lr_scale", 1.0) != 1.0]
+                for g, lr in scaled:                      # per-group ``lr_scale`` takes effect in graph mode
+                    g["lr"] = lr * g["lr_scale"]
+                try:
+                    opt.step()
+                finally:
+                    for g, lr in scaled:
+                        g["lr"] = lr
         for o in self._opts:
             o["optim"].zero_grad(set_to_none=True)
             if o["lr_sch"] is not None and not found_inf:

@@ -45,6 +45,12 @@ class _ClipMixin:
                                 and p.grad.data_ptr() % 16 == 0 for p in ps)
 
 
+def _lr(g):
+    """Learning rate of a group.  (The group option ``lr_scale`` is a graph-mode feature: ``nn.Graph`` multiplies the
+    rate by it around its optimizer step; eager steps ignore it, as the reference does.)"""
+    return g["lr"]
+
+
 class _Base(_ClipMixin, torch.optim.Optimizer):
     """Shared step loop: ``_update(p, grad, state, group)`` per parameter with a gradient; ``state["step"]`` counts from 1."""
 
@@ -101,9 +107,9 @@ class SGD(_Base):
                 buf = state["momentum_buf"] = torch.zeros_like(p)
             buf.mul_(g["momentum"]).add_(grad, alpha=1 - g["dampening"])
             grad = grad + g["momentum"] * buf if g["nesterov"] else buf
-            p.add_(grad, alpha=g["lr"] if g["maximize"] else -g["lr"])
+            p.add_(grad, alpha=_lr(g) if g["maximize"] else -_lr(g))
         else:
-            p.add_(grad, alpha=-g["lr"])
+            p.add_(grad, alpha=-_lr(g))
 
     def _fused_step(self):
         from ..ops import kernels as K
@@ -121,7 +127,7 @@ class SGD(_Base):
                     ms.append(st["momentum_buf"])
             for p in ps:
                 self.state[p]["step"] = int(self.state[p].get("step", 0)) + 1
-            K.multi_tensor_sgd([p.grad for p in ps], [p.data for p in ps], None, ms, lr=g["lr"], momentum=g["momentum"],
+            K.multi_tensor_sgd([p.grad for p in ps], [p.data for p in ps], None, ms, lr=_lr(g), momentum=g["momentum"],
                                dampening=g["dampening"], nesterov=g["nesterov"],
                                maximize=g["maximize"] and g["momentum"] > 0, l2=g["weight_decay"])
         return True
@@ -167,8 +173,8 @@ class _AdamFamily(_Base):
         else:
             denom = v.sqrt() / math.sqrt(bc2) + g["eps"]
         if self.decoupled and g["weight_decay"]:
-            p.mul_(1 - g["lr"] * g["weight_decay"])
-        p.addcdiv_(m, denom, value=-g["lr"] / bc1)
+            p.mul_(1 - _lr(g) * g["weight_decay"])
+        p.addcdiv_(m, denom, value=-_lr(g) / bc1)
 
     def _fused_step(self):
         if any(g["amsgrad"] for g in self.param_groups):
@@ -188,7 +194,7 @@ class _AdamFamily(_Base):
                 ms.append(st["exp_avg"])
                 vs.append(st["exp_avg_sq"])
             b1, b2 = g["betas"]
-            K.multi_tensor_adamw([p.grad for p in ps], [p.data for p in ps], None, ms, vs, lr=g["lr"], beta1=b1, beta2=b2,
+            K.multi_tensor_adamw([p.grad for p in ps], [p.data for p in ps], None, ms, vs, lr=_lr(g), beta1=b1, beta2=b2,
                                  eps=g["eps"], weight_decay=g["weight_decay"] if self.decoupled else 0.0,
                                  l2=0.0 if self.decoupled else g["weight_decay"], step=int(self.state[ps[0]]["step"]),
                                  bias_correction=g["do_bias_correction"])
@@ -218,7 +224,7 @@ class Adagrad(_Base):
             grad = grad + g["weight_decay"] * p
         s = state["sum"]
         s.addcmul_(grad, grad)
-        lr = g["lr"] / (1 + (state["step"] - 1) * g["lr_decay"])
+        lr = _lr(g) / (1 + (state["step"] - 1) * g["lr_decay"])
         p.addcdiv_(grad, s.sqrt() + g["eps"], value=-lr)
 
 
@@ -239,7 +245,7 @@ class Adadelta(_Base):
         sq.mul_(rho).addcmul_(grad, grad, value=1 - rho)
         delta = (acc + eps).sqrt_().div_((sq + eps).sqrt_()).mul_(grad)
         acc.mul_(rho).addcmul_(delta, delta, value=1 - rho)
-        p.add_(delta, alpha=-g["lr"])
+        p.add_(delta, alpha=-_lr(g))
 
 
 class RMSprop(_Base):
@@ -278,7 +284,7 @@ class RMSprop(_Base):
         else:
             denom = (r + g["eps"]).sqrt_()
         v = state["momentum_buffer"]
-        v.mul_(g["momentum"]).addcdiv_(grad, denom, value=g["lr"])
+        v.mul_(g["momentum"]).addcdiv_(grad, denom, value=_lr(g))
         p.sub_(v)
 
 
@@ -313,7 +319,7 @@ class LAMB(_Base):
         trust = wn / dn if wn > 0 and dn > 0 else 1.0
         if g["adam_w_mode"] and g["weight_decay"]:
             direction = direction + g["weight_decay"] * p
-        p.add_(direction, alpha=-g["lr"] * trust)
+        p.add_(direction, alpha=-_lr(g) * trust)
 
 
 class Ftrl(_Base):
@@ -336,7 +342,7 @@ class Ftrl(_Base):
     def _update(self, p, grad, state, g):
         if g["weight_decay"]:
             grad = grad + g["weight_decay"] * p
-        n, z, lp, lr = state["accumulate"], state["z"], g["lr_power"], g["lr"]
+        n, z, lp, lr = state["accumulate"], state["z"], g["lr_power"], _lr(g)
         new_n = n + grad * grad
         z.add_(grad - (new_n.pow(lp) - n.pow(lp)) / lr * p)
         n.copy_(new_n)
