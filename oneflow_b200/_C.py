@@ -72,10 +72,18 @@ class _TrilSoftmax(torch.autograd.Function):
         return dx, None, None, None, None
 
 
-def fused_scale_tril_softmax_mask_scale(x, mask, *, diagonal=0, tril_scale_value=1.0, mask_scale_value=1.0,
-                                        tril_fill_value=float("-inf")):
-    """(dropout_mask * softmax(tril(x * tril_scale)) * mask_scale, softmax_y) over [.., s_q, s_k] scores."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
+def fused_scale_tril_softmax_mask_scale(x, mask=None, *, p=None, diagonal=0, tril_scale_value=1.0, mask_scale_value=None,
+                                        tril_fill_value=float("-inf"), generator=None):
+    """``(dropout_mask * softmax(tril(x * tril_scale)) * mask_scale, softmax_y)`` over ``[.., s_q, s_k]`` scores.
+    Either a ready ``mask`` with its ``mask_scale_value`` is given, or a dropout probability ``p`` from which the mask
+    is drawn and the scale ``1 / (1 - p)`` follows (the reference's signature)."""
+    if mask is None and p is not None and p > 0:
+        gen_dev = generator.device if generator is not None else x.device
+        mask = (torch.rand(x.shape, device=gen_dev, generator=generator) >= p).to(x.device)
+        mask_scale_value = 1.0 / (1.0 - p)
+    if mask_scale_value is None:
+        mask_scale_value = 1.0
+    if mask is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
         return _TrilSoftmax.apply(x, mask, diagonal, tril_scale_value, mask_scale_value)
     s_q, s_k = x.shape[-2:]
     keep = torch.ones(s_q, s_k, dtype=torch.bool, device=x.device).tril(diagonal)
@@ -92,8 +100,15 @@ def fused_scale_mask_softmax(x, mask, fill_value=-10000.0, scale=1.0):
     return torch.softmax((x * scale).masked_fill(~mask.bool(), fill_value), -1)
 
 
-def fused_scale_mask_softmax_dropout(x, mask, dropout_mask, fill_value=-10000.0, scale=1.0, p=0.5):
+def fused_scale_mask_softmax_dropout(x, mask, dropout_mask=None, *, fill_value=0.0, scale=1.0, p=0.5, training=True, generator=None):
+    """``(dropout(softmax(masked_fill(x * scale, mask == 0, fill_value))), softmax_y)``.  The dropout mask is drawn here
+    (``p``, ``training``, ``generator``) unless a ready ``dropout_mask`` is passed."""
     sm = fused_scale_mask_softmax(x, mask, fill_value, scale)
+    if dropout_mask is None:
+        if not training or p == 0:
+            return sm, sm
+        gen_dev = generator.device if generator is not None else x.device
+        dropout_mask = (torch.rand(sm.shape, device=gen_dev, generator=generator) >= p).to(x.device)
     return sm * dropout_mask.to(x.dtype) * (1.0 / (1.0 - p)), sm
 
 
@@ -180,8 +195,15 @@ def fused_dot_feature_interaction(features, output_concat=None, self_interaction
     return dot_feature_interaction(features, output_concat, self_interaction, output_padding, pooling)
 
 
-def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
-    return torch.nn.functional.layer_norm(x, normalized_shape, weight, bias, eps)
+def layer_norm(x, normalized_shape=None, weight=None, bias=None, eps=1e-5, *, begin_norm_axis=None, begin_params_axis=None,
+               epsilon=None):
+    """Layer norm, either torch-style (``normalized_shape``) or with the reference's ``begin_norm_axis`` /
+    ``begin_params_axis`` / ``epsilon`` (normalise over the axes from ``begin_norm_axis`` on, no affine)."""
+    if begin_norm_axis is not None or isinstance(normalized_shape, int):
+        axis = begin_norm_axis if begin_norm_axis is not None else normalized_shape
+        e = epsilon if epsilon is not None else (weight if isinstance(weight, float) else eps)
+        return torch.nn.functional.layer_norm(x, tuple(x.shape[axis:]), None, None, e)
+    return torch.nn.functional.layer_norm(x, normalized_shape, weight, bias, epsilon if epsilon is not None else eps)
 
 
 def local_all_reduce(x, inplace=False):

@@ -26,7 +26,7 @@ from . import remat, sysconfig, unittest  # noqa: E402
 
 _tensor_api.install_tensor_methods()
 
-device = _torch.device
+device = _tensor_api.device
 Size = _torch.Size
 Generator = _torch.Generator
 manual_seed = _torch.manual_seed

@@ -6,9 +6,12 @@ import torch
 def _typed(name, dtype):
     class _T:
         def __new__(cls, *args, **kwargs):
-            if len(args) == 1 and not isinstance(args[0], int):
-                return torch.as_tensor(args[0], dtype=dtype, device="cuda")
-            return torch.empty(*args, dtype=dtype, device="cuda", **kwargs)
+            dev = kwargs.pop("device", "cuda")
+            if len(args) == 1 and not isinstance(args[0], (int, torch.Size)):
+                return torch.as_tensor(args[0], dtype=dtype, device=dev)
+            if not args:
+                args = (0,)
+            return torch.empty(*args, dtype=dtype, device=dev, **kwargs)
 
     class _Meta(type):
         def __instancecheck__(cls, obj):

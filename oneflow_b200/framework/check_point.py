@@ -148,7 +148,7 @@ def _standin(t, ctx=None):
     reference's tensor state; pickled by the default protocol-2 reduce as NEWOBJ + BUILD."""
     oneflow, _ = _alias()
     is_param = isinstance(t, torch.nn.Parameter) or getattr(t, "_is_param", False)
-    cls = oneflow.nn.Parameter if is_param else oneflow.Tensor
+    cls = oneflow.nn._ParameterStandin if is_param else oneflow.Tensor
     obj = object.__new__(cls)
     object.__setattr__(obj, "_pickle_state", tensor_state(t, ctx))
     return obj
@@ -200,6 +200,11 @@ class _Pickler(pickle._Pickler):
         # numpy >= 2 names its internals ``numpy._core``; the reference pins numpy < 2, which only knows
         # ``numpy.core`` (an alias numpy 2 still resolves), so write the portable spelling.
         module = getattr(obj, "__module__", None)
+        if module == "oneflow.nn" and getattr(obj, "__name__", "") == "Parameter":
+            # the stand-in class of parameters: named by its class path, which resolves to the parameter class on load
+            self.write(pickle.GLOBAL + b"oneflow.nn\nParameter\n")
+            self.memoize(obj)
+            return
         if isinstance(module, str) and module.startswith("numpy._core"):
             qual = name or getattr(obj, "__qualname__", obj.__name__)
             self.write(pickle.GLOBAL + module.replace("numpy._core", "numpy.core").encode() + b"\n" + qual.encode() + b"\n")
@@ -327,7 +332,13 @@ class _Unpickler(pickle.Unpickler):
 # ------------------------------------------------------------------------------------------------ public API
 def save(obj, path, global_dst_rank=None, save_as_external_data=False):
     """Saves ``obj`` (tensors, state dicts, arbitrary picklable containers). With ``global_dst_rank`` global
-    tensors are gathered to that rank, which alone writes the file(s)."""
+    tensors are gathered to that rank, which alone writes the file(s).  ``path`` may also be a writable binary
+    file object (``io.BytesIO``, an open file): the single-file form is written into it."""
+    stream = path if hasattr(path, "write") else None
+    if stream is not None:
+        if save_as_external_data:
+            raise ValueError("save_as_external_data needs a directory path, not a file object")
+        path = Path(".")
     path = Path(path)
     from ..nn.graph.graph import Graph
     if isinstance(obj, Graph):
@@ -340,6 +351,9 @@ def save(obj, path, global_dst_rank=None, save_as_external_data=False):
         path.mkdir(parents=True, exist_ok=True)
     _Pickler(buf, ctx).dump({"protocol_version": PROTOCOL_VERSION, "__oneflow__": None, "data": obj})
     if not writer:
+        return
+    if stream is not None:
+        stream.write(buf.getvalue())
         return
     if save_as_external_data:
         (path / PICKLE_FILENAME).write_bytes(buf.getvalue())
@@ -368,10 +382,22 @@ def _load_legacy_dir(path: Path, ctx):
 def load(path, global_src_rank=None, map_location=None):
     """Loads what ``save`` wrote (single file or directory), a legacy variable directory, or a ``torch.save``
     file. With ``global_src_rank`` only that rank reads; tensors come back as global broadcast tensors on
-    ``cpu[src]``. ``map_location``: device / device string, or a placement (tensors become global)."""
-    path = Path(path)
+    ``cpu[src]``. ``map_location``: device / device string, or a placement (tensors become global).  ``path`` may
+    also be a readable binary file object or the bytes themselves."""
+    blob = path.read() if hasattr(path, "read") else (bytes(path) if isinstance(path, (bytes, bytearray)) else None)
     if isinstance(map_location, str):
         map_location = torch.device(map_location)
+    if blob is not None:
+        ctx = _Ctx(Path("."), global_src_rank, False, map_location)
+        try:
+            top = _Unpickler(io.BytesIO(blob)).load()
+        except Exception:
+            return torch.load(io.BytesIO(blob), map_location=map_location if isinstance(map_location, torch.device) else None,
+                              weights_only=False)
+        if isinstance(top, dict) and "protocol_version" in top and "data" in top:
+            top = top["data"]
+        return _resolve(top, ctx, {})
+    path = Path(path)
     rank = _rank()
     reader = global_src_rank is None or global_src_rank == rank
     ctx = _Ctx(path, global_src_rank, False, map_location)

@@ -14,6 +14,23 @@ from . import global_tensor as GT
 from .placement import placement as Placement
 
 
+class _DeviceMeta(type):
+    def __instancecheck__(cls, obj):
+        return isinstance(obj, torch.device)
+
+    def __call__(cls, *args, **kwargs):
+        """``flow.device("cuda")`` names the current CUDA device (``cuda:0`` unless changed), so it compares equal to the
+        ``.device`` of tensors placed there; everything else is ``torch.device``."""
+        d = torch.device(*args, **kwargs)
+        if d.type == "cuda" and d.index is None:
+            return torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+        return d
+
+
+class device(metaclass=_DeviceMeta):
+    """``flow.device``: constructor and ``isinstance`` target for device objects (which are ``torch.device``)."""
+
+
 class _TensorMeta(type):
     def __instancecheck__(cls, obj):
         return isinstance(obj, torch.Tensor)
@@ -26,7 +43,7 @@ class _TensorMeta(type):
             dev = kwargs.get("device")
             if isinstance(data, torch.Tensor):
                 return data.detach().clone().to(device=dev if dev is not None else data.device)
-            return torch.tensor(np.asarray(data), dtype=kwargs.get("dtype", torch.float32), device=dev)
+            return torch.tensor(np.asarray(data), dtype=kwargs.get("dtype", torch.get_default_dtype()), device=dev)
         dev = kwargs.pop("device", None)
         t = torch.Tensor(*args, **kwargs)
         return t.to(dev) if dev is not None else t

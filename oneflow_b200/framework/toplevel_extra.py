@@ -357,3 +357,9 @@ def Generator(device="auto"):
 
 
 default_generator = torch.default_generator     # the process-wide generator object (seed / manual_seed / get_state)
+
+
+def distributed_partial_fc_sample(weight, label, num_sample):
+    """Deprecated function form of ``nn.DistributedPariticalFCSample``."""
+    from ..nn.modules.partial_fc import distributed_partial_fc_sample as _f
+    return _f(weight, label, num_sample)

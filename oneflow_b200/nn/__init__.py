@@ -29,24 +29,19 @@ from .extra_modules import (CombinedMarginLoss, FusedBatchNorm1d, FusedBatchNorm
 
 
 
-class _ParameterMeta(type):
-    def __instancecheck__(cls, obj):
-        return isinstance(obj, _tnn.Parameter) or getattr(obj, "_is_param", False)
-
-    def __call__(cls, data=None, requires_grad=True):
-        return _tnn.Parameter(data, requires_grad)
+Parameter = _tnn.Parameter        # global tensors become parameters through torch's ``_is_param`` protocol
 
 
-class Parameter(metaclass=_ParameterMeta):
-    """``flow.nn.Parameter(data, requires_grad=True)`` builds a torch Parameter (global tensors stay global
-    and are marked as parameters); the class object is also the ``oneflow.nn.Parameter`` path of checkpoints."""
+class _ParameterStandin:
+    """What a parameter is written as inside a checkpoint: an object of the class path ``oneflow.nn.Parameter`` that
+    carries the reference's tensor state (``framework.check_point`` writes the class path itself)."""
     _pickle_state = None
 
     def __getstate__(self):
         return self._pickle_state
 
 
-Parameter.__module__ = "oneflow.nn"
+_ParameterStandin.__module__, _ParameterStandin.__name__, _ParameterStandin.__qualname__ = "oneflow.nn", "Parameter", "Parameter"
 module_ext.install()
 GraphModule = graph.GraphModule
 
