@@ -117,6 +117,13 @@ eager = _ns("eager", Sync=_sync, ClusterSync=_sync)
 eager.multi_client = _ns("eager.multi_client", Sync=_sync)
 
 
+# Exception types of the C extension: the builtin ones, so that ``except RuntimeError`` and
+# ``except oneflow._oneflow_internal.exception.RuntimeError`` catch the same errors.
+exception = _ns("exception", Exception=Exception, RuntimeError=RuntimeError, ValueError=ValueError, TypeError=TypeError,
+                IndexError=IndexError, NotImplementedError=NotImplementedError, CheckFailedError=RuntimeError,
+                InvalidValueError=ValueError, UnimplementedError=NotImplementedError)
+
+
 def max_alignment_size():
     return 512
 

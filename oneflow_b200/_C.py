@@ -9,6 +9,8 @@ import math
 
 import torch
 
+from .framework.generator import resolve as _resolve_gen
+
 from .framework.global_tensor import to_global, to_local  # noqa: F401
 from .ops import gemm as G
 from .ops import kernels as K
@@ -78,6 +80,7 @@ def fused_scale_tril_softmax_mask_scale(x, mask=None, *, p=None, diagonal=0, tri
     Either a ready ``mask`` with its ``mask_scale_value`` is given, or a dropout probability ``p`` from which the mask
     is drawn and the scale ``1 / (1 - p)`` follows (the reference's signature)."""
     if mask is None and p is not None and p > 0:
+        generator = _resolve_gen(generator, x.device)
         gen_dev = generator.device if generator is not None else x.device
         mask = (torch.rand(x.shape, device=gen_dev, generator=generator) >= p).to(x.device)
         mask_scale_value = 1.0 / (1.0 - p)
@@ -107,6 +110,7 @@ def fused_scale_mask_softmax_dropout(x, mask, dropout_mask=None, *, fill_value=0
     if dropout_mask is None:
         if not training or p == 0:
             return sm, sm
+        generator = _resolve_gen(generator, x.device)
         gen_dev = generator.device if generator is not None else x.device
         dropout_mask = (torch.rand(sm.shape, device=gen_dev, generator=generator) >= p).to(x.device)
     return sm * dropout_mask.to(x.dtype) * (1.0 / (1.0 - p)), sm

@@ -7,6 +7,8 @@ from __future__ import annotations
 import math
 
 import torch
+
+from .framework.generator import resolve as _resolve_gen
 import torch.nn.functional as F
 
 
@@ -377,6 +379,7 @@ def global_arange(*args, dtype=None, placement, sbp):
 
 def bernoulli_(input, p=None, *, dtype=None, generator=None):
     """BernoulliInplace (probabilities taken from ``input``) / BernoulliProbInplace (one probability ``p``)."""
+    generator = _resolve_gen(generator, input.device)
     if p is None:
         return input.copy_(torch.bernoulli(input, generator=generator))
     return input.bernoulli_(p, generator=generator)
@@ -384,7 +387,7 @@ def bernoulli_(input, p=None, *, dtype=None, generator=None):
 
 def exponential_(x, lambd=1.0, generator=None):
     """Exponential"""
-    return x.exponential_(lambd, generator=generator)
+    return x.exponential_(lambd, generator=_resolve_gen(generator, x.device))
 
 
 def uniform_(x, from_=0.0, to=1.0, **kw):

@@ -24,9 +24,15 @@ def matmul(input, other, transpose_a=False, transpose_b=False, alpha=1.0):
     return out if alpha == 1.0 else out * alpha
 
 
+def _gen(generator, device):
+    from .generator import resolve
+    return resolve(generator, device)
+
+
 def bernoulli(input, p=None, *, dtype=None, generator=None, inplace=False, out=None):
     """Bernoulli draws with probabilities ``input`` (or one probability ``p``), in ``dtype`` (default: float32 for
     integer inputs' sake as well), optionally written back into ``input``."""
+    generator = _gen(generator, input.device)
     if p is None:
         res = torch.bernoulli(input.float() if not input.is_floating_point() else input, generator=generator)
     else:
@@ -50,6 +56,7 @@ def one_hot(input, num_classes=-1, on_value=1, off_value=0):
 def dropout(input, p=0.5, training=True, inplace=False, generator=None, *, addend=None):
     """Dropout with an optional generator for the mask and an ``addend`` added to the result (the fused residual)."""
     if training and p > 0:
+        generator = _gen(generator, input.device)
         if generator is None:
             out = F.dropout(input, p, True, inplace)
         else:

@@ -106,15 +106,24 @@ def tensor(data, dtype=None, device=None, placement=None, sbp=None, requires_gra
     return t.requires_grad_(requires_grad) if requires_grad else t
 
 
+def _resolve_gen(generator, device):
+    from .generator import resolve
+    return resolve(generator, device)
+
+
 def _factory(torch_fn):
     def fn(*args, placement=None, sbp=None, device=None, requires_grad=False, **kwargs):
         if placement is None:
             if device is not None:
                 kwargs["device"] = device
+            if kwargs.get("generator") is not None:
+                kwargs["generator"] = _resolve_gen(kwargs["generator"], device or "cpu")
             t = torch_fn(*args, **kwargs)
             return t.requires_grad_(requires_grad) if requires_grad else t
         # global: every rank draws the logical tensor (first rank's values win along broadcast axes)
         kwargs["device"] = placement.device() if placement.contains(GT._rank()) else "cpu"
+        if kwargs.get("generator") is not None:
+            kwargs["generator"] = _resolve_gen(kwargs["generator"], kwargs["device"])
         t = torch_fn(*args, **kwargs)
         return _globalize(t, placement, sbp, requires_grad)
     fn.__name__ = torch_fn.__name__
@@ -135,6 +144,8 @@ def _like_factory(torch_fn):
         if placement is None:
             if device is not None:
                 kwargs["device"] = device
+            if kwargs.get("generator") is not None:
+                kwargs["generator"] = _resolve_gen(kwargs["generator"], device or input.device)
             t = torch_fn(input, *args, **kwargs)       # a global input gives a global result through the dispatch
             return t.requires_grad_(requires_grad) if requires_grad else t
         dev = placement.device() if placement.contains(GT._rank()) else "cpu"

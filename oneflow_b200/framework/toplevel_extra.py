@@ -348,15 +348,7 @@ stateful_op = _stub_module("stateful_op", "Stateful op holder of the reference's
 from .. import remat  # noqa: E402,F401
 
 
-def Generator(device="auto"):
-    """``flow.Generator(device)``; ``"auto"`` picks CUDA when there is a device, the host otherwise
-    (reference: python/oneflow/framework/generator.py)."""
-    if str(device) == "auto":
-        device = "cuda" if torch.cuda.is_available() else "cpu"
-    return torch.Generator(device=device)
-
-
-default_generator = torch.default_generator     # the process-wide generator object (seed / manual_seed / get_state)
+from .generator import Generator, default_generator, get_rng_state, set_rng_state  # noqa: E402,F401
 
 
 def distributed_partial_fc_sample(weight, label, num_sample):
