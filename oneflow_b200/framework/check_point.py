@@ -312,10 +312,42 @@ def _resolve(obj, ctx, memo):
         r = obj.torch_dtype
     elif hasattr(obj, "to_sbp"):
         r = obj.to_sbp()
+    elif isinstance(obj, torch.nn.Module) or (hasattr(obj, "__dict__") and not isinstance(obj, (type, torch.Tensor))
+                                              and type(obj).__module__.split(".")[0] not in ("builtins", "torch", "numpy")):
+        # an object pickled whole (a module, an optimizer, a user class): its attributes are resolved in place
+        memo[oid] = obj
+        try:
+            attrs = vars(obj)
+        except TypeError:
+            return obj
+        for k, v in list(attrs.items()):
+            nv = _resolve(v, ctx, memo)
+            if nv is not v:
+                attrs[k] = nv
+        if isinstance(obj, torch.nn.Module):
+            _complete_modules(obj)
+        return obj
     else:
         r = obj
     memo[oid] = r
     return r
+
+
+def _complete_modules(root):
+    """A module pickled whole by another version of the library may lack bookkeeping attributes that
+    ``Module.__call__`` reads (hook tables and the like): every submodule gets the defaults of a fresh module for
+    what it does not carry."""
+    defaults = torch.nn.Module().__dict__
+    stack, seen = [root], set()
+    while stack:
+        m = stack.pop()
+        if id(m) in seen:
+            continue
+        seen.add(id(m))
+        for k, v in defaults.items():
+            if k not in m.__dict__:
+                m.__dict__[k] = type(v)() if isinstance(v, (dict, set, list)) else v
+        stack.extend(c for c in m.__dict__.get("_modules", {}).values() if isinstance(c, torch.nn.Module))
 
 
 class _Unpickler(pickle.Unpickler):

@@ -174,15 +174,17 @@ def _tensor_type(self, dtype=None, non_blocking=False, **kw):
     if isinstance(dtype, torch.dtype):
         return self.to(dtype)
     name = dtype if isinstance(dtype, str) else getattr(dtype, "__name__", str(dtype))
-    cuda = ".cuda." in "." + name or getattr(dtype, "is_cuda", False)
+    cuda = ".cuda." in "." + name or getattr(dtype, "is_cuda", False) is True
     short = name.split(".")[-1]
+    if short == "Tensor":
+        short = "FloatTensor"               # ``flow.Tensor`` is the float32 host tensor type
     for dt, n in _TYPE_NAMES.items():
         if n == short:
             out = self.to(dt)
             if cuda and not out.is_cuda:
                 out = out.cuda()
-            elif not cuda and out.is_cuda and isinstance(dtype, str) and name.startswith(("oneflow.", "torch.")) and ".cuda." not in name:
-                out = out.cpu()
+            elif not cuda and out.is_cuda and (not isinstance(dtype, str) or name.startswith(("oneflow.", "torch."))):
+                out = out.cpu()             # a host tensor type (class or qualified name) names the host as well
             return out
     raise ValueError(f"invalid type: '{name}'")
 

@@ -104,10 +104,17 @@ class GlobalTensor(torch.Tensor):
         return tuple(s if s.kind != "S" or (s.axis < len(size) and size[s.axis] >= self._placement.hierarchy[i]) else B
                      for i, s in enumerate(self._nd_sbp))
 
+    def contiguous(self, memory_format=torch.contiguous_format):
+        """The logical tensor always reads as contiguous; what matters to kernels is the local shard, so a shard
+        that is a strided view (after ``transpose`` / ``permute``) is copied into dense memory here."""
+        if self._local.is_contiguous(memory_format=memory_format):
+            return self
+        return self.clone(memory_format=memory_format)
+
     def type_as(self, other):
         if isinstance(other, GlobalTensor):
             return self.to(other.dtype)
-        return self.to_local().to(other.dtype)
+        return self.to_local().to(device=other.device, dtype=other.dtype)
 
     def __repr__(self):
         return (f"GlobalTensor(shape={tuple(self.shape)}, dtype={self.dtype}, placement={self._placement}, "

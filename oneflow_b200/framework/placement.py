@@ -52,7 +52,9 @@ class placement:
             type = device_type
         if isinstance(type, torch.device):
             type = type.type
-        if type not in ("cpu", "cuda"):
+        if getattr(type, "type", None) == "mock":
+            type = "mock"
+        if type not in ("cpu", "cuda", "mock"):      # "mock": the pseudo device kind for tests, host memory behind it
             raise ValueError(f"unknown device type {type!r}")
         if ranks is None:
             ranks = list(range(dist.get_world_size() if dist.is_initialized() else 1))
@@ -164,6 +166,6 @@ class placement:
         return mine
 
     def device(self):
-        if self.type == "cpu":
+        if self.type in ("cpu", "mock"):
             return torch.device("cpu")
         return torch.device("cuda", torch.cuda.current_device())

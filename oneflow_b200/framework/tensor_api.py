@@ -14,13 +14,33 @@ from . import global_tensor as GT
 from .placement import placement as Placement
 
 
+class _MockDevice:
+    """The reference's pseudo device for tests (``DeviceType::kMockDevice``, oneflow/core/common/device_type.proto):
+    it names a device kind without memory of its own; host memory stands behind it."""
+    type = "mock"
+
+    def __init__(self, index=0):
+        self.index = index
+
+    def __eq__(self, other):
+        return isinstance(other, _MockDevice) and other.index == self.index
+
+    def __hash__(self):
+        return hash(("mock", self.index))
+
+    def __repr__(self):
+        return f"device(type='mock', index={self.index})"
+
+
 class _DeviceMeta(type):
     def __instancecheck__(cls, obj):
-        return isinstance(obj, torch.device)
+        return isinstance(obj, (torch.device, _MockDevice))
 
     def __call__(cls, *args, **kwargs):
         """``flow.device("cuda")`` names the current CUDA device (``cuda:0`` unless changed), so it compares equal to the
         ``.device`` of tensors placed there; everything else is ``torch.device``."""
+        if args and isinstance(args[0], str) and args[0].partition(":")[0] == "mock":
+            return _MockDevice(int(args[0].partition(":")[2] or (args[1] if len(args) > 1 else 0)))
         d = torch.device(*args, **kwargs)
         if d.type == "cuda" and d.index is None:
             return torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
@@ -203,6 +223,14 @@ def _install_reference_methods(T):
         return method
 
     T.cast = lambda self, dtype: self.to(dtype)
+    _type_as = T.type_as
+
+    def type_as(self, other):
+        """``type_as`` that follows a global target onto its placement and sbp."""
+        if isinstance(other, GT.GlobalTensor) and not isinstance(self, GT.GlobalTensor):
+            return _globalize(self.to(other.dtype), other.placement, other.sbp, False)
+        return _type_as(self, other)
+    T.type_as = type_as
     T.gelu = lambda self, approximate="none": F.gelu(self, approximate=approximate)
     T.mish = lambda self: F.mish(self)
     T.selu = lambda self: F.selu(self)

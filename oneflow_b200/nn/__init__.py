@@ -15,7 +15,8 @@ for _n in ("functional", "init", "graph", "module_ext", "parallel", "utils", "mo
     globals()[_n] = _importlib.import_module(__name__ + "." + _n)
 del _n
 from .graph import Graph  # noqa: F401
-from .modules import Conv2d, FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
+from .modules import FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
+from .modules.nhwc import AvgPool2d, BatchNorm2d, Conv2d, MaxPool2d  # noqa: F401  (layout by ONEFLOW_ENABLE_NHWC)
 from .modules import (AllReduce, COCOReader, CoinFlip, CropMirrorNormalize, DistributedPariticalFCSample,  # noqa: F401
                       GPTIndexedBinDataReader, OFRecordBytesDecoder, OFRecordImageDecoder, OFRecordImageDecoderRandomCrop,
                       OFRecordImageGpuDecoderRandomCropResize, OFRecordRawDecoder, OFRecordReader, QatConv1d, QatConv2d,

@@ -120,3 +120,13 @@ def deform_conv2d(input, offset, weight, bias=None, stride=(1, 1), padding=(0, 0
     if bias is not None:
         out = out + bias.float().reshape(1, -1, 1, 1)
     return out.to(input.dtype)
+
+
+def batch_norm(input, running_mean, running_var, weight=None, bias=None, training=False, momentum=0.1, eps=1e-5):
+    """``batch_norm``; 4-D inputs are read as [N, H, W, C] while ``ONEFLOW_ENABLE_NHWC=1``
+    (reference: python/oneflow/nn/functional/batch_norm.py:38-45)."""
+    import os
+    if input.dim() == 4 and os.getenv("ONEFLOW_ENABLE_NHWC") == "1":
+        return _F.batch_norm(input.permute(0, 3, 1, 2), running_mean, running_var, weight, bias, training, momentum,
+                             eps).permute(0, 2, 3, 1)
+    return _F.batch_norm(input, running_mean, running_var, weight, bias, training, momentum, eps)

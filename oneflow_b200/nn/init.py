@@ -46,3 +46,23 @@ def calc_fan(shape, mode, data_format):
     if mode == "fan_out":
         return fan_out
     raise NotImplementedError("only 'fan_in', 'fan_out' and 'fan_sum' modes are supported")
+
+
+def _nhwc_aware(fn):
+    """The fan-based initialisers read a 4-D weight as [Cout, kH, kW, Cin] while ``ONEFLOW_ENABLE_NHWC=1`` (or with
+    ``data_format="NHWC"``): they then run on the [Cout, Cin, kH, kW] view of the same memory
+    (reference: python/oneflow/nn/init.py:141-142, 204-205, 246-247)."""
+    import functools
+    import os
+
+    @functools.wraps(fn)
+    def init(tensor, *args, data_format="NCHW", **kwargs):
+        if tensor.dim() == 4 and (os.getenv("ONEFLOW_ENABLE_NHWC") == "1" or get_data_format(data_format) == "channels_last"):
+            fn(tensor.permute(0, 3, 1, 2), *args, **kwargs)
+            return tensor
+        return fn(tensor, *args, **kwargs)
+    return init
+
+
+xavier_uniform_, xavier_normal_ = _nhwc_aware(_I.xavier_uniform_), _nhwc_aware(_I.xavier_normal_)
+kaiming_uniform_, kaiming_normal_ = _nhwc_aware(_I.kaiming_uniform_), _nhwc_aware(_I.kaiming_normal_)

@@ -65,4 +65,57 @@ def install():
                                           for k, v in state_dict.items())
         return _load(self, state_dict, strict=strict, assign=assign)
     M.load_state_dict = load_state_dict
+
+    _state = M.state_dict
+
+    def state_dict(self, *args, destination=None, prefix="", keep_vars=True):
+        """``state_dict`` whose values are the parameters and buffers themselves (the reference never detaches
+        them: python/oneflow/nn/modules/module.py, ``_save_to_state_dict``); ``keep_vars=False`` detaches."""
+        return _state(self, *args, destination=destination, prefix=prefix, keep_vars=keep_vars)
+    M.state_dict = state_dict
+
+    def _tuple_hook(hook):
+        # backward hooks see ``TensorTuple`` arguments; a returned gradient is cast to the dtype it replaces
+        from oneflow._oneflow_internal import TensorTuple
+
+        def wrapped(module, grad_input, grad_output):
+            res = hook(module, TensorTuple(grad_input), TensorTuple(grad_output))
+            if res is None:
+                return None
+            res = tuple(res) if isinstance(res, (tuple, list)) else (res,)
+            return tuple(r.to(dtype=g.dtype, device=g.device) if isinstance(r, torch.Tensor) and g is not None else r
+                         for r, g in zip(res, grad_input))
+        wrapped.__wrapped__ = hook
+        return wrapped
+
+    _full, _legacy = M.register_full_backward_hook, M.register_backward_hook
+
+    def register_full_backward_hook(self, hook, prepend=False):
+        return _full(self, _tuple_hook(hook), prepend=prepend)
+
+    def register_backward_hook(self, hook):
+        return _legacy(self, _tuple_hook(hook))
+    register_full_backward_hook.__doc__, register_backward_hook.__doc__ = _full.__doc__, _legacy.__doc__
+    M.register_full_backward_hook = register_full_backward_hook
+    M.register_backward_hook = register_backward_hook
+
+    def _global_batch_first(cls):
+        # The library's RNN kernels turn a batch-first result around with an in-place ``transpose_``; a global
+        # tensor's logical shape is fixed at construction, so for global inputs the two transposes are done here,
+        # out of place, and the kernel runs sequence-first.
+        fwd = cls.forward
+
+        def forward(self, input, hx=None):
+            if isinstance(input, GT.GlobalTensor) and self.batch_first and input.dim() == 3:
+                self.batch_first = False
+                try:
+                    out, h = fwd(self, input.transpose(0, 1).contiguous(), hx)
+                finally:
+                    self.batch_first = True
+                return out.transpose(0, 1), h
+            return fwd(self, input, hx)
+        forward.__doc__ = fwd.__doc__
+        cls.forward = forward
+    for _cls in (torch.nn.RNN, torch.nn.LSTM, torch.nn.GRU):
+        _global_batch_first(_cls)
     M._ofb_patched = True

@@ -13,6 +13,7 @@ import torch.distributed as dist
 
 
 class DistributedDataParallel(torch.nn.Module):
+    _is_ddp_module = True      # the mark the reference sets on a module it has wrapped
     def __init__(self, module, *, broadcast_buffers=True, broadcast_parameters=True, bucket_size=10, use_bucket=True):
         super().__init__()
         self.module = module

@@ -278,3 +278,120 @@ def test_graph_sharing_dynamic_shapes_and_description():
         H().share_from(H())                                   # the source was never enabled for sharing
     o = flow.optim.SGD([torch.nn.Parameter(torch.ones(2))], lr=0.1)
     assert o.support_sparse() is False and hasattr(flow.optim.Optimizer, "clip_grad")
+
+
+def test_generator_per_device_streams():
+    """``flow.Generator``: one seed for every device, ``"auto"`` follows the consuming op, and the process-wide
+    generator is the one behind ``flow.get_rng_state`` (reference: python/oneflow/test/modules/test_generator.py)."""
+    import oneflow
+    auto, cpu = flow.Generator(device="auto"), flow.Generator(device="cpu")
+    assert auto.initial_seed() == cpu.initial_seed()
+    with pytest.raises(RuntimeError):
+        flow.Generator(device="invalid")
+    flow.Generator(device="cpu:1000")
+    g = flow.Generator()
+    assert g.manual_seed(7) is g and g.initial_seed() == 7
+    a = flow.rand(8, generator=g)
+    g.manual_seed(7)
+    assert torch.equal(a, flow.rand(8, generator=g))
+    assert flow.randperm(6, generator=g).sort().values.tolist() == list(range(6))
+    out = flow._C.dropout(flow.ones(1000), p=0.5, training=True, generator=flow.Generator(), addend=None)
+    assert 300 < int((out == 0).sum()) < 700
+    d = flow.default_generator
+    assert d.seed() == d.initial_seed()
+    assert torch.equal(d.get_state(), flow.get_rng_state())
+    flow.randn(10, generator=d)
+    assert torch.equal(d.get_state(), flow.get_rng_state())
+    assert issubclass(oneflow._oneflow_internal.exception.RuntimeError, Exception)
+
+
+def test_nhwc_layers_by_environment(monkeypatch):
+    """``ONEFLOW_ENABLE_NHWC=1``: conv / pooling / batch norm take [N, H, W, C], the conv weight is
+    [Cout, kH, kW, Cin]; results equal the NCHW layers on permuted data."""
+    monkeypatch.setenv("ONEFLOW_ENABLE_NHWC", "1")
+    x = torch.randn(2, 12, 12, 3)
+    nchw = x.permute(0, 3, 1, 2)
+    kw = dict(kernel_size=3, stride=(1, 2), padding=(0, 1), ceil_mode=True)
+    assert torch.equal(flow.nn.MaxPool2d(**kw)(x), torch.nn.MaxPool2d(**kw)(nchw).permute(0, 2, 3, 1))
+    assert torch.allclose(flow.nn.AvgPool2d(2)(x), torch.nn.AvgPool2d(2)(nchw).permute(0, 2, 3, 1))
+    c = flow.nn.Conv2d(3, 8, 3, padding=1)
+    assert tuple(c.weight.shape) == (8, 3, 3, 3) and c.channel_pos == "channels_last"
+    ref = torch.nn.Conv2d(3, 8, 3, padding=1)
+    ref.load_state_dict({"weight": c.weight.detach().permute(0, 3, 1, 2), "bias": c.bias.detach()})
+    y = c(x)
+    assert torch.allclose(y, ref(nchw).permute(0, 2, 3, 1), atol=1e-5)
+    y.sum().backward()
+    assert c.weight.grad.shape == c.weight.shape
+    rb = torch.nn.BatchNorm2d(3)(nchw).permute(0, 2, 3, 1)
+    assert torch.allclose(flow.nn.BatchNorm2d(3)(x), rb, atol=1e-5)
+    assert torch.allclose(flow.nn.functional.batch_norm(x, None, None, training=True), rb, atol=1e-5)
+    w = flow.nn.init.kaiming_normal_(torch.empty(64, 3, 3, 16), mode="fan_out")
+    assert abs(float(w.std()) - (2 / (64 * 9)) ** 0.5) < 0.01
+    monkeypatch.setenv("ONEFLOW_ENABLE_NHWC", "0")
+    c2 = flow.nn.Conv2d(3, 8, 3, padding=1)
+    assert c2.channel_pos == "channels_first" and c2(nchw).shape == (2, 8, 12, 12)
+    c2.to_memory_format(flow.channels_last)
+    assert c2.channel_pos == "channels_last" and c2(x).shape == (2, 12, 12, 8)
+
+
+def test_whole_module_save_load_and_module_semantics(tmp_path):
+    """A module saved whole comes back runnable; ``state_dict`` hands out the parameters themselves; backward hooks
+    see ``TensorTuple`` arguments and may return gradients of another dtype."""
+    from oneflow._oneflow_internal import TensorTuple
+    m = torch.nn.Sequential(flow.nn.Conv2d(3, 4, 3), torch.nn.ReLU())
+    flow.save(m, str(tmp_path / "m"))
+    m2 = flow.load(str(tmp_path / "m"))
+    x = torch.randn(1, 3, 5, 5)
+    assert torch.equal(m(x), m2(x))
+    with open(tmp_path / "m", "rb") as f:
+        assert torch.equal(flow.load(f)(x), m(x))
+    assert m.state_dict()["0.weight"] is m[0].weight
+    assert not m.state_dict(keep_vars=False)["0.weight"].requires_grad
+    seen = []
+
+    def hook(mod, gin, gout):
+        seen.append((isinstance(gin, TensorTuple), isinstance(gout, TensorTuple)))
+        return (torch.tensor([1, 1]),)
+    r = flow.nn.ReLU()
+    r.register_full_backward_hook(hook)
+    x0 = torch.tensor([1.0, -1.0], requires_grad=True)
+    r(x0 + 1).sum().backward()
+    assert seen == [(True, True)] and x0.grad.tolist() == [1.0, 1.0]
+
+    class F(flow.autograd.Function):
+        @staticmethod
+        def forward(ctx, a):
+            ctx.save_for_backward(a.clone())
+            F.ctx = ctx
+            return a * 2
+
+        @staticmethod
+        def backward(ctx, g):
+            return g * 2
+    out = F.apply(torch.randn(3, requires_grad=True))
+    assert F.ctx._is_data_valid()
+    out.sum().backward()
+    assert not F.ctx._is_data_valid()
+    assert flow.device("mock").type == "mock" and flow.placement("mock", [0]).type == "mock"
+
+
+def test_global_rnn_batch_first_and_type_as():
+    P = flow.placement("cpu", [0])
+    mt = torch.nn.LSTM(2, 3, batch_first=True)
+    mf = flow.nn.LSTM(2, 3, batch_first=True)
+    mf.load_state_dict({k: v.detach().numpy() for k, v in mt.state_dict().items()})
+    mf = mf.to_global(P, flow.sbp.broadcast)
+    x = torch.rand(5, 7, 2)
+    xg = x.clone().requires_grad_().to_global(P, flow.sbp.broadcast)
+    out, _ = mf(xg)
+    ref, _ = mt(x)
+    assert out.shape == ref.shape and torch.allclose(out.to_local(), ref, atol=1e-5)
+    out.sum().backward()
+    t = xg.detach().transpose(0, 1)
+    assert not t.to_local().is_contiguous() and t.contiguous().to_local().is_contiguous()
+    tgt = flow.ones(2, 2, dtype=flow.int32).to_global(P, flow.sbp.broadcast)
+    g = torch.rand(2, 2).type_as(tgt)
+    assert g.is_global and g.dtype == flow.int32 and g.placement == tgt.placement
+    loc = tgt.type_as(torch.rand(1))
+    assert not loc.is_global and loc.dtype == torch.float32
+    assert torch.ones(2, dtype=torch.int8).type(flow.Tensor).dtype == torch.float32
