@@ -22,7 +22,7 @@ from .framework.tensor_api import (Tensor, arange, empty, eye, from_numpy, full,
 from .framework.check_point import load, save  # noqa: E402
 from . import _C, amp, autograd, comm, env, nn, optim, utils  # noqa: E402
 from . import distributed, one_embedding, profiler, cuda, backends, mock_torch, framework, models, ops, parallel  # noqa: E402
-from . import remat, sysconfig, unittest  # noqa: E402
+from . import remat, sysconfig, unittest, version  # noqa: E402
 
 _tensor_api.install_tensor_methods()
 

@@ -243,6 +243,24 @@ class NLLLoss(torch.nn.NLLLoss):
         return super().forward(input, _long_target(target))
 
 
+_LOW = (torch.bfloat16, torch.float16)
+
+
+def softsign(input):
+    """``x / (1 + |x|)``; 16-bit inputs are evaluated in float32 and rounded once (the reference's kernels do the
+    arithmetic in float: oneflow/core/ep/common/primitive/unary_functor.h)."""
+    if input.dtype in _LOW:
+        return F.softsign(input.float()).to(input.dtype)
+    return F.softsign(input)
+
+
+def rsqrt(input):
+    """``1 / sqrt(x)``, rounded once for 16-bit host tensors as well."""
+    if input.dtype in _LOW and not input.is_cuda:
+        return torch.rsqrt(input.float()).to(input.dtype)
+    return torch.rsqrt(input)
+
+
 def install():
     """Put the functions above where the reference has them."""
     import oneflow_b200 as flow
@@ -255,6 +273,8 @@ def install():
         setattr(flow, k, v)
         setattr(_C, k, v)
     flow.nn.CrossEntropyLoss, flow.nn.NLLLoss = CrossEntropyLoss, NLLLoss
+    flow.softsign = _C.softsign = NF.softsign = softsign
+    flow.rsqrt = _C.rsqrt = rsqrt
     for k, v in dict(one_hot=one_hot, dropout=dropout, cross_entropy=cross_entropy, nll_loss=nll_loss).items():
         setattr(NF, k, v)
         setattr(_C, k, v)

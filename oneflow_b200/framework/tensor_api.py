@@ -223,6 +223,49 @@ def _install_reference_methods(T):
         return method
 
     T.cast = lambda self, dtype: self.to(dtype)
+
+    class _CallableTensor(torch.Tensor):
+        """What ``x.real`` / ``x.imag`` give: the tensor itself, which may also be called (``x.real()``) since
+        the reference spells these as methods. Results of operations on it are plain tensors."""
+        __torch_function__ = torch._C._disabled_torch_function_impl
+
+        def __call__(self):
+            return self.as_subclass(torch.Tensor)
+
+    for _name in ("real", "imag"):
+        _desc = getattr(T, _name)
+
+        def _get(self, _desc=_desc):
+            out = _desc.__get__(self)
+            return out.as_subclass(_CallableTensor) if type(out) is torch.Tensor else out
+        setattr(T, _name, property(_get, _desc.__set__, doc=_desc.__doc__))
+
+    class _SliceError(RuntimeError, IndexError, ValueError, TypeError):
+        """A bad slice (zero or negative step, float bounds) is a ``RuntimeError`` or ``IndexError`` in the reference
+        and a ``ValueError`` / ``TypeError`` in Python: every one of them catches it."""
+
+    _getitem = T.__getitem__
+
+    def __getitem__(self, index):
+        try:
+            return _getitem(self, index)
+        except (ValueError, TypeError) as e:
+            raise _SliceError(str(e)) from None
+        except IndexError as e:
+            if "out of bounds" in str(e):
+                raise IndexError(f"{e} (index out of range)") from None
+            raise
+    T.__getitem__ = __getitem__
+
+    _backward = T.backward
+
+    def backward(self, gradient=None, retain_graph=None, create_graph=False, inputs=None):
+        """``backward`` that also starts from a complex scalar (the seed gradient is one, as for real scalars)."""
+        if gradient is None and self.is_complex() and self.numel() == 1:
+            gradient = torch.ones_like(self)
+        return _backward(self, gradient, retain_graph, create_graph, inputs)
+    backward.__doc__ = _backward.__doc__
+    T.backward = backward
     _type_as = T.type_as
 
     def type_as(self, other):
@@ -236,7 +279,7 @@ def _install_reference_methods(T):
     T.selu = lambda self: F.selu(self)
     T.silu = lambda self: F.silu(self)
     T.softplus = lambda self, beta=1, threshold=20: F.softplus(self, beta, threshold)
-    T.softsign = lambda self: F.softsign(self)
+    T.softsign = _top("softsign")
     T.in_top_k = lambda self, predictions, k: _top("in_top_k")(self, predictions, k)
     T.nms = lambda self, scores, iou_threshold: _top("nms")(self, scores, iou_threshold)
     T.is_lazy = property(lambda self: False)
@@ -339,6 +382,8 @@ def _install_reference_methods(T):
             t = t.resolve_conj()
         if t._is_zerotensor():
             t = torch.zeros(t.shape, dtype=t.dtype)          # the symbolic all-zero gradient of autograd, made real
+        if t.dtype == torch.bfloat16:
+            t = t.float()                                    # numpy has no bfloat16: float32, as in the reference
         return _numpy(t, *args, **kwargs)
     T.numpy = numpy
     T.is_view = lambda self: self._is_view()

@@ -395,3 +395,47 @@ def test_global_rnn_batch_first_and_type_as():
     loc = tgt.type_as(torch.rand(1))
     assert not loc.is_global and loc.dtype == torch.float32
     assert torch.ones(2, dtype=torch.int8).type(flow.Tensor).dtype == torch.float32
+
+
+def test_mock_torch_import_redirection():
+    """Under ``mock_torch.enable()`` an ``import torch`` in user code gives views of this framework's modules named
+    ``oneflow...``; ``disable()`` gives the library back, also to module-valued names of the calling scope."""
+    import subprocess
+    import sys
+    code = r'''
+import oneflow as flow, oneflow.mock_torch as mock
+with mock.enable():
+    import torch, torch.nn, torch.version
+with mock.disable():
+    import torch, torch.nn, torch.version
+real = torch
+assert torch.__package__ == "torch"
+mock.enable()
+assert torch.__package__ == "oneflow" and torch.nn.__package__ == "oneflow.nn", (torch.__package__, torch.nn.__package__)
+assert torch.version.__version__ == flow.__version__
+from torch import nn
+assert nn.__package__ == "oneflow.nn" and nn.Linear(2, 2)(torch.ones(1, 2)).shape == (1, 2)
+try:
+    from torch import noexist
+    raise SystemExit("no error")
+except ImportError as e:
+    assert "cannot import name 'noexist' from 'oneflow'" in str(e), e
+try:
+    import torch.noexist
+    raise SystemExit("no error")
+except ModuleNotFoundError as e:
+    assert "oneflow.noexist is not implemented" in str(e), e
+mock.disable()
+assert torch is real and torch.nn.__package__ == "torch.nn"
+with mock.enable(lazy=True):
+    from torch import not_exist
+    assert not_exist.__name__ == "oneflow.not_exist" and not_exist.x.__name__ == "oneflow.not_exist.x"
+    assert not torch.not_exist and list(torch.not_exist) == [] and not isinstance(int, torch._six.string_class)
+    with mock.disable():
+        assert torch.__package__ == "torch"
+    assert torch.__package__ == "oneflow"
+assert torch.__package__ == "torch" and torch.ones(2).sum().item() == 2.0
+print("MOCK OK")
+'''
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert "MOCK OK" in out.stdout, out.stdout + out.stderr
