@@ -147,3 +147,4 @@ class TensorTuple(list):
 
     def __init__(self, items=()):
         super().__init__(items)
+

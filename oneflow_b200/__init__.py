@@ -22,7 +22,7 @@ from .framework.tensor_api import (Tensor, arange, empty, eye, from_numpy, full,
 from .framework.check_point import load, save  # noqa: E402
 from . import _C, amp, autograd, comm, env, nn, optim, utils  # noqa: E402
 from . import distributed, one_embedding, profiler, cuda, backends, mock_torch, framework, models, ops, parallel  # noqa: E402
-from . import remat, sysconfig, unittest, version  # noqa: E402
+from . import fx, remat, sysconfig, unittest, version  # noqa: E402
 
 _tensor_api.install_tensor_methods()
 
@@ -42,7 +42,7 @@ boxing = framework.boxing
 _SUBMODULES = ["nn", "nn.functional", "nn.graph", "nn.parallel", "nn.utils", "nn.init", "optim", "optim.lr_scheduler", "comm",
                "env", "sbp", "amp", "autograd", "utils", "utils.data", "distributed", "distributed.launch", "one_embedding",
                "profiler", "cuda", "backends", "mock_torch", "framework", "models", "ops", "parallel", "_C", "remat", "sysconfig",
-               "unittest", "asyncs", "hub", "multiprocessing"]
+               "unittest", "asyncs", "hub", "multiprocessing", "fx", "version"]
 
 __all__ = ["sbp", "placement", "GlobalTensor", "to_global", "to_local", "Tensor", "tensor", "zeros", "ones", "empty", "full",
            "randn", "rand", "randint", "randperm", "arange", "eye", "linspace", "from_numpy", "save", "load", "nn", "optim",

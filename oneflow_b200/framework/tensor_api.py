@@ -114,9 +114,11 @@ def tensor(data, dtype=None, device=None, placement=None, sbp=None, requires_gra
         if dtype is not None:
             t = t.to(dtype)
     else:
-        if isinstance(data, np.ndarray) and data.dtype == np.float64 and dtype is None:
-            dtype = torch.float32 if False else None
-        t = torch.tensor(data, dtype=dtype)
+        if isinstance(data, (list, tuple)) and data and all(isinstance(d, torch.Tensor) for d in data):
+            t = torch.stack([d.detach() for d in data])       # a sequence of tensors stacks along a new first axis
+            t = t.to(dtype) if dtype is not None else t
+        else:
+            t = torch.tensor(data, dtype=dtype)
     if placement is not None:
         return _globalize(t, placement, sbp, requires_grad)
     if device is not None:
@@ -266,6 +268,30 @@ def _install_reference_methods(T):
         return _backward(self, gradient, retain_graph, create_graph, inputs)
     backward.__doc__ = _backward.__doc__
     T.backward = backward
+    def _register_post_grad_accumulation_hook(self, hook):
+        """``hook(grad)`` runs after a gradient was accumulated into ``.grad``; a returned tensor replaces it, None
+        keeps what the hook changed in place (reference: Tensor._register_post_grad_accumulation_hook)."""
+        def run(param):
+            res = hook(param.grad)
+            if res is not None:
+                param.grad = res
+        return self.register_post_accumulate_grad_hook(run)
+    T._register_post_grad_accumulation_hook = _register_post_grad_accumulation_hook
+
+    def _no_buffer(self):
+        raise RuntimeError("_tensor_buffer_shapes_and_dtypes is only available for tensors of dtype tensor_buffer")
+    T._tensor_buffer_shapes_and_dtypes = property(_no_buffer)
+
+    def global_id(self):
+        if not isinstance(self, GT.GlobalTensor):
+            raise RuntimeError("global_id is only available for global tensors")
+        return id(self)
+    T.global_id = global_id
+
+    def _where(self, x=None, y=None):
+        from .compat_ops import where
+        return where(self, x, y)
+    T.where = _where
     _type_as = T.type_as
 
     def type_as(self, other):

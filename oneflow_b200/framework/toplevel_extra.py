@@ -263,11 +263,26 @@ def roc_auc_score(label, pred):
 
 
 # ------------------------------------------------------------------------------------------------ tensor buffers (ragged lists)
+class _TensorBufferDType:
+    """``flow.tensor_buffer``: the element type of a ragged batch (the reference's ``DataType::kTensorBuffer``)."""
+
+    def __repr__(self):
+        return "oneflow.tensor_buffer"
+
+
+tensor_buffer = _TensorBufferDType()
+
+
 class TensorBuffer:
     """A batch of variable-shaped tensors (what data-loading ops of the reference pass around)."""
+    dtype = tensor_buffer
 
     def __init__(self, tensors):
         self.tensors = list(tensors)
+
+    @property
+    def _tensor_buffer_shapes_and_dtypes(self):
+        return [(tuple(t.shape), t.dtype) for t in self.tensors]
 
     def __len__(self):
         return len(self.tensors)

@@ -21,6 +21,7 @@ the SBP rules, kernels launch on CUDA streams), and nn.Graph supplies what the p
 from __future__ import annotations
 
 import contextlib
+import os
 from collections import OrderedDict
 from typing import List
 
@@ -183,6 +184,11 @@ class Graph:
     def add_optimizer(self, optim, *, lr_sch=None, is_sparse=False):
         if lr_sch is not None and getattr(lr_sch, "optimizer", optim) is not optim:
             raise ValueError("lr_sch must wrap the optimizer it is added with")
+        if lr_sch is not None:
+            # The graph advances a schedule of its own, as the reference compiles the schedule into the job: the
+            # caller's scheduler object is left where it is and can go on driving eager steps.
+            import copy
+            lr_sch = copy.deepcopy(lr_sch, {id(optim): optim})
         self._opts.append({"optim": optim, "lr_sch": lr_sch, "is_sparse": is_sparse})
         self.config.training = True
 
@@ -196,6 +202,10 @@ class Graph:
     @property
     def training(self):
         return self.config.training
+
+    @property
+    def _is_compiled(self):
+        return self._compiled
 
     @property
     def is_compiled(self):
@@ -404,7 +414,45 @@ class Graph:
                 m.bias._local, m.bias._nd_sbp = nb._local, nb._nd_sbp
         self._auto_parallel_choices = [(c.name.split(".", 1)[1], c.kind) for c in choices]
 
-    def _compile(self, args):
+    def _filter_states(self):
+        """Names of the graph's state tensors (parameters and buffers of its blocks, each tensor once), in block
+        order (reference: python/oneflow/nn/graph/graph.py:716-741)."""
+        seen, names = set(), []
+        for bname, proxy in self._blocks.items():
+            mod = proxy._module
+            for kind in (mod.named_parameters(), mod.named_buffers()):
+                for n, t in kind:
+                    if id(t) not in seen:
+                        seen.add(id(t))
+                        names.append(f"{bname}.{n}")
+        self._eager_state_op_names = list(names)
+        return names
+
+    def _generate_config_proto(self):
+        """Fills ``self.config.proto``: the job configuration with one entry per optimizer (its parameter groups,
+        update rule and learning-rate schedule), as the reference hands to its compiler."""
+        state = getattr(self, "_eager_state_op_names", None) or self._filter_states()
+        by_id = {}
+        for bname, proxy in self._blocks.items():
+            for n, t in proxy._module.named_parameters():
+                by_id.setdefault(id(t), f"{bname}.{n}")
+        opts = []
+        for o in self._opts:
+            opt, sch = o["optim"], o["lr_sch"]
+            groups = []
+            for g in opt.param_groups:
+                conf = {k: v for k, v in g.items() if k != "params" and isinstance(v, (int, float, bool, str, tuple, type(None)))}
+                conf["variable_op_names"] = [by_id.get(id(p), "<unnamed>") for p in g["params"] if p.requires_grad]
+                groups.append(conf)
+            opts.append({"type": type(opt).__name__, "param_groups": groups, "is_sparse": o["is_sparse"],
+                         "lr_scheduler": None if sch is None else type(sch).__name__})
+        self.config._proto = dict(self.config._as_dict(), job_name=self._name, state_op_names=state, optimizer_conf=opts)
+        return self.config._proto
+
+    def _compile(self, *args):
+        if len(args) == 1 and isinstance(args[0], tuple):
+            args = args[0]
+        self._generate_config_proto()
         if Graph._nesting > 0:
             raise RuntimeError("nn.Graph objects cannot be nested")
         shared = getattr(self, "_shared_graph", None)
@@ -438,10 +486,37 @@ class Graph:
                 self._dynamic_metas.popitem(last=False)
         else:
             meta = [self._meta(a) for a in args]
-            if self._input_meta is not None and meta != self._input_meta:
+            # ONEFLOW_RUN_GRAPH_BY_VM=1: the graph is replayed op by op, so any input signature is accepted
+            by_vm = os.getenv("ONEFLOW_RUN_GRAPH_BY_VM") == "1"
+            if self._input_meta is not None and meta != self._input_meta and not by_vm:
                 raise RuntimeError(f"nn.Graph {self._name}: inputs must keep the same shape/dtype/placement/sbp on every call "
                                    f"(first call {self._input_meta}, now {meta})")
-        return self._run(args, kwargs)
+        try:
+            return self._run(self._shield_inputs(args), kwargs)
+        finally:
+            probe = self.__dict__.pop("_probe", None)
+            if probe is not None:
+                self._written_inputs = {i for i, t, v in probe if t._version != v}
+
+    def _shield_inputs(self, args):
+        """In-place operations inside ``build`` must not reach the caller's tensors (a graph works on its own
+        copies of the inputs). The first call runs on clones of all local tensor inputs and notes which of them
+        ``build`` wrote to; later calls clone only those."""
+        local = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor) and not isinstance(a, GT.GlobalTensor)]
+        known = getattr(self, "_written_inputs", None)
+        if known is None:
+            out = list(args)
+            for i in local:
+                out[i] = args[i].clone()
+            self._probe = [(i, out[i], out[i]._version) for i in local]
+            return tuple(out)
+        if not known:
+            return args
+        out = list(args)
+        for i in known:
+            if i < len(out) and isinstance(out[i], torch.Tensor) and not isinstance(out[i], GT.GlobalTensor):
+                out[i] = out[i].clone()
+        return tuple(out)
 
     @contextlib.contextmanager
     def _backward_scaling(self, factor_fn):
@@ -520,11 +595,26 @@ class Graph:
                 finally:
                     for g, lr in scaled:
                         g["lr"] = lr
+        if os.getenv("ONEFLOW_DEBUG_MODE"):
+            self._log_step_lr()
         for o in self._opts:
             o["optim"].zero_grad(set_to_none=True)
             if o["lr_sch"] is not None and not found_inf:
                 o["lr_sch"].step()
         self._train_step += 1
+
+    def _log_step_lr(self):
+        """Debug mode keeps ``log/local/<pid>-train_step2lr.csv``: one ``train_step, lr`` line per step (the first
+        optimizer's first group), as the reference's runtime writes."""
+        path = os.path.join("log", "local", f"{os.getpid()}-train_step2lr.csv")
+        if self._opts:
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            fresh = not getattr(self, "_lr_log_started", False)
+            with open(path, "w" if fresh else "a") as f:
+                if fresh:
+                    f.write("train_step, lr\n")
+                    self._lr_log_started = True
+                f.write(f"{self._train_step}, {self._opts[0]['optim'].param_groups[0]['lr']}\n")
 
     def __repr__(self):
         lines = [f"(GRAPH:{self._name}:{type(self).__name__}): ("]

@@ -106,5 +106,14 @@ class GraphConfig:
         """Capture the whole step in a CUDA graph after the first call (static shapes, CUDA tensors)."""
         self.cuda_graph = bool(mode)
 
+    def _as_dict(self):
+        return {k: (str(v) if isinstance(v, torch.dtype) else v) for k, v in vars(self).items() if not k.startswith("_")}
+
+    @property
+    def proto(self):
+        """The job configuration as a plain dict (the reference holds a JobConfigProto); nn.Graph adds the optimizer
+        entries when it compiles."""
+        return getattr(self, "_proto", None) or self._as_dict()
+
     def __repr__(self):
         return f"GraphConfig({ {k: v for k, v in self.__dict__.items() if k != 'extra'} })"
