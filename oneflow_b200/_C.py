@@ -75,22 +75,26 @@ class _TrilSoftmax(torch.autograd.Function):
 
 
 def fused_scale_tril_softmax_mask_scale(x, mask=None, *, p=None, diagonal=0, tril_scale_value=1.0, mask_scale_value=None,
-                                        tril_fill_value=float("-inf"), generator=None):
+                                        tril_fill_value=0.0, generator=None):
     """``(dropout_mask * softmax(tril(x * tril_scale)) * mask_scale, softmax_y)`` over ``[.., s_q, s_k]`` scores.
     Either a ready ``mask`` with its ``mask_scale_value`` is given, or a dropout probability ``p`` from which the mask
-    is drawn and the scale ``1 / (1 - p)`` follows (the reference's signature)."""
-    if mask is None and p is not None and p > 0:
+    is drawn and the scale ``1 / (1 - p)`` follows (the reference's signature). Scores above the diagonal are set to
+    ``tril_fill_value`` before the softmax (0 by default, as in the reference; language models pass -10000 or -inf)."""
+    if mask is None and p is not None and p >= 1:
+        mask, mask_scale_value = torch.zeros(x.shape, dtype=torch.bool, device=x.device), 0.0
+    elif mask is None and p is not None and p > 0:
         generator = _resolve_gen(generator, x.device)
         gen_dev = generator.device if generator is not None else x.device
         mask = (torch.rand(x.shape, device=gen_dev, generator=generator) >= p).to(x.device)
         mask_scale_value = 1.0 / (1.0 - p)
     if mask_scale_value is None:
         mask_scale_value = 1.0
-    if mask is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
+    if mask is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048 \
+            and tril_fill_value <= -1e4:           # the kernel drops the masked scores outright
         return _TrilSoftmax.apply(x, mask, diagonal, tril_scale_value, mask_scale_value)
     s_q, s_k = x.shape[-2:]
     keep = torch.ones(s_q, s_k, dtype=torch.bool, device=x.device).tril(diagonal)
-    sm = torch.softmax((x * tril_scale_value).masked_fill(~keep, float("-inf")), -1)
+    sm = torch.softmax((x * tril_scale_value).masked_fill(~keep, tril_fill_value), -1)
     y = sm * (mask.to(x.dtype) if mask is not None else 1.0) * mask_scale_value
     return y, sm
 
@@ -110,6 +114,8 @@ def fused_scale_mask_softmax_dropout(x, mask, dropout_mask=None, *, fill_value=0
     if dropout_mask is None:
         if not training or p == 0:
             return sm, sm
+        if p >= 1:
+            return sm * 0.0, sm                    # everything is dropped; no 1 / (1 - p) to form
         generator = _resolve_gen(generator, x.device)
         gen_dev = generator.device if generator is not None else x.device
         dropout_mask = (torch.rand(sm.shape, device=gen_dev, generator=generator) >= p).to(x.device)

@@ -56,6 +56,8 @@ for _n in dir(_extra):
     if not _n.startswith("_") and _n not in ("os", "types", "np", "torch", "F", "builtins_slice", "TensorBuffer") and _n not in globals():
         globals()[_n] = getattr(_extra, _n)
 globals()["Generator"] = _extra.Generator
+from .cuda.type_tensor import host_types as _host_types  # noqa: E402
+globals().update(_host_types())
 globals()["slice"] = _extra.slice
 globals()["view"] = _extra.view
 globals()["repeat"] = _extra.repeat

@@ -3,10 +3,10 @@
 import torch
 
 
-def _typed(name, dtype):
+def _typed(name, dtype, device="cuda"):
     class _T:
         def __new__(cls, *args, **kwargs):
-            dev = kwargs.pop("device", "cuda")
+            dev = kwargs.pop("device", device)
             if len(args) == 1 and not isinstance(args[0], (int, torch.Size)):
                 return torch.as_tensor(args[0], dtype=dtype, device=dev)
             if not args:
@@ -15,10 +15,16 @@ def _typed(name, dtype):
 
     class _Meta(type):
         def __instancecheck__(cls, obj):
-            return isinstance(obj, torch.Tensor) and obj.is_cuda and obj.dtype == dtype
+            return isinstance(obj, torch.Tensor) and obj.is_cuda == (device == "cuda") and obj.dtype == dtype
 
-    T = _Meta(name, (_T,), {"dtype": dtype, "is_cuda": True})
+    T = _Meta(name, (_T,), {"dtype": dtype, "is_cuda": device == "cuda"})
     return T
+
+
+def host_types():
+    """The host-side typed constructors (``flow.FloatTensor`` ...): like the CUDA ones they convert whatever data or
+    tensor they are given to their dtype."""
+    return {n: _typed(n, globals()[n].dtype, "cpu") for n in __all__}
 
 
 HalfTensor = _typed("HalfTensor", torch.float16)

@@ -80,10 +80,11 @@ class Generator:
         return self.for_device("cpu").initial_seed() if self._default else self._seed
 
     def get_state(self):
-        return self.for_device().get_state()
+        """The state of this generator's own device; an ``"auto"`` generator answers with its host stream."""
+        return self.for_device(self._device or "cpu").get_state()
 
     def set_state(self, state):
-        self.for_device().set_state(state.cpu() if isinstance(state, torch.Tensor) else state)
+        self.for_device(self._device or "cpu").set_state(state.cpu() if isinstance(state, torch.Tensor) else state)
         return self
 
     def __repr__(self):
