@@ -411,11 +411,24 @@ def _load_legacy_dir(path: Path, ctx):
     return out
 
 
-def load(path, global_src_rank=None, map_location=None):
+def _torch_load(src, map_location, support_pytorch_format, shown):
+    """Last resort of ``load``: the file is not in this format; read it as a ``torch.save`` file when allowed."""
+    cause = None
+    if support_pytorch_format:
+        try:
+            return torch.load(src, map_location=map_location if isinstance(map_location, torch.device) else None,
+                              weights_only=False)
+        except Exception as e:
+            cause = e
+    raise ValueError(f"Cannot load file {shown}" + (f" ({type(cause).__name__}: {cause})" if cause else "")) from cause
+
+
+def load(path, global_src_rank=None, map_location=None, *, support_pytorch_format=True):
     """Loads what ``save`` wrote (single file or directory), a legacy variable directory, or a ``torch.save``
     file. With ``global_src_rank`` only that rank reads; tensors come back as global broadcast tensors on
     ``cpu[src]``. ``map_location``: device / device string, or a placement (tensors become global).  ``path`` may
-    also be a readable binary file object or the bytes themselves."""
+    also be a readable binary file object or the bytes themselves. A file in neither this nor (unless
+    ``support_pytorch_format=False``) PyTorch's format raises ``ValueError("Cannot load file ...")``."""
     blob = path.read() if hasattr(path, "read") else (bytes(path) if isinstance(path, (bytes, bytearray)) else None)
     if isinstance(map_location, str):
         map_location = torch.device(map_location)
@@ -424,8 +437,7 @@ def load(path, global_src_rank=None, map_location=None):
         try:
             top = _Unpickler(io.BytesIO(blob)).load()
         except Exception:
-            return torch.load(io.BytesIO(blob), map_location=map_location if isinstance(map_location, torch.device) else None,
-                              weights_only=False)
+            return _torch_load(io.BytesIO(blob), map_location, support_pytorch_format, "<stream>")
         if isinstance(top, dict) and "protocol_version" in top and "data" in top:
             top = top["data"]
         return _resolve(top, ctx, {})
@@ -452,8 +464,7 @@ def load(path, global_src_rank=None, map_location=None):
     except Exception:
         if path.is_dir():
             raise
-        return torch.load(str(path), map_location=map_location if isinstance(map_location, torch.device) else None,
-                          weights_only=False)
+        return _torch_load(str(path), map_location, support_pytorch_format, path)
     if not (isinstance(top, dict) and "protocol_version" in top and "data" in top):
         return _resolve(top, ctx, {})
     if top["protocol_version"] != PROTOCOL_VERSION:
