@@ -366,6 +366,20 @@ from .. import remat  # noqa: E402,F401
 from .generator import Generator, default_generator, get_rng_state, set_rng_state  # noqa: E402,F401
 
 
+def set_default_tensor_type(t):
+    """Default floating-point dtype from a typed tensor class or its name (``flow.DoubleTensor``,
+    ``"oneflow.FloatTensor"``; reference: python/oneflow/framework/dtype.py)."""
+    from .compat_ops import _TYPE_NAMES
+    name = t if isinstance(t, str) else getattr(t, "__name__", str(t))
+    short = name.split(".")[-1]
+    for dt, n in _TYPE_NAMES.items():
+        if n == short:
+            if not dt.is_floating_point:
+                raise TypeError("only floating-point types are supported as the default type")
+            return torch.set_default_dtype(dt)
+    raise TypeError(f"invalid type object: {name}")
+
+
 def distributed_partial_fc_sample(weight, label, num_sample):
     """Deprecated function form of ``nn.DistributedPariticalFCSample``."""
     from ..nn.modules.partial_fc import distributed_partial_fc_sample as _f
