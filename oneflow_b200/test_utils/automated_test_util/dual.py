@@ -137,7 +137,7 @@ class DualObject:
         if key.startswith("__") and key.endswith("__"):
             raise AttributeError(key)
         p, o = self.pytorch, self.oneflow
-        if key in _GLOBAL_ONLY and isinstance(p, torch_original.Tensor):
+        if key in _GLOBAL_ONLY and isinstance(p, (torch_original.Tensor, torch_original.nn.Module)):
             p_attr = lambda *a, **k: p                                   # noqa: E731  PyTorch has no global tensors
         else:
             try:
