@@ -439,3 +439,41 @@ print("MOCK OK")
 '''
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert "MOCK OK" in out.stdout, out.stdout + out.stderr
+
+
+def test_graph_private_schedule_inputs_and_proto(tmp_path, monkeypatch):
+    """nn.Graph advances its own copy of the LR schedule (the caller's scheduler stays put), logs ``step, lr`` in
+    debug mode, keeps in-place writes of ``build`` off the caller's inputs and fills ``config.proto``."""
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("ONEFLOW_DEBUG_MODE", "1")
+    m = torch.nn.Linear(4, 2)
+    opt = flow.optim.SGD(m.parameters(), lr=0.1)
+    sch = flow.optim.lr_scheduler.StepLR(opt, step_size=2, gamma=0.5)
+
+    class G(flow.nn.Graph):
+        def __init__(self):
+            super().__init__()
+            self.m = m
+            self.add_optimizer(opt, lr_sch=sch)
+
+        def build(self, x):
+            x += 1.0
+            loss = self.m(x).sum()
+            loss.backward()
+            return x
+
+    g = G()
+    x = torch.zeros(3, 4)
+    for _ in range(5):
+        out = g(x)
+    assert torch.equal(x, torch.zeros(3, 4)) and torch.equal(out, torch.ones(3, 4))
+    assert sch.last_step == 0 and sch.get_last_lr() == [0.1]
+    import glob
+    import os
+    rows = open(glob.glob(f"log/*/{os.getpid()}-train_step2lr.csv")[0]).read().strip().splitlines()[1:]
+    assert [float(r.split(",")[1]) for r in rows] == [0.1, 0.1, 0.05, 0.05, 0.025]
+    proto = g.config.proto
+    assert proto["optimizer_conf"][0]["type"] == "SGD" and proto["optimizer_conf"][0]["lr_scheduler"] == "StepLR"
+    assert g._filter_states() == ["m.weight", "m.bias"] and g._is_compiled
+    fx = flow.fx.symbolic_trace(torch.nn.Sequential(flow.nn.Conv2d(3, 4, 3), torch.nn.ReLU()))
+    assert [n.op for n in fx.graph.nodes] == ["placeholder", "call_module", "call_module", "output"]
