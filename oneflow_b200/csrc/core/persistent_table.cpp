@@ -1,9 +1,16 @@
 // On-disk key -> fixed-size row store for embedding tables that do not fit in memory (the SSD tier behind the
 // device / host caches of OneEmbedding). Rows are appended to a values file in blocks aligned to the
 // device's physical block size and read / written with positioned I/O (O_DIRECT when the filesystem allows
-// it, buffered otherwise); the key -> row-index map lives in memory and is persisted with every snapshot.
-// A snapshot is a hard copy of the index plus the row count at that time; rows are append-or-overwrite, so
-// loading a snapshot restores the index and truncates the logical row count.
+// it, buffered otherwise); the key -> row-index map lives in memory.
+//
+// Snapshots are point-in-time: a snapshot is a copy of the index, and every row that exists when a snapshot is
+// taken (or when the table is opened) is frozen from then on. Updating a key whose row is frozen appends a new
+// row and re-points the index, so the rows a snapshot refers to keep their values; only rows written since the
+// last snapshot are overwritten in place. Appends always go to the physical end of the values file, which never
+// moves backwards, so loading an older snapshot and writing on cannot clobber rows of a younger one.
+//
+// Crash safety of the index: besides the full copy written by close() and by every snapshot, each put() appends
+// its (key, row) pairs to `index.log` and flushes it; open() loads `index` and replays the log.
 //
 // Reference: oneflow/core/embedding/persistent_table.cpp (O_DIRECT + Linux AIO, :197-236, :395),
 // persistent_table_key_value_store.cu.
@@ -31,7 +38,9 @@ struct PTable {
   int fd = -1;
   bool direct = false, read_only = false;
   std::unordered_map<int64_t, int64_t> index;  // key -> row number
-  int64_t rows = 0;
+  int64_t rows = 0;         // next row to append (physical end of the values file, in rows); never decreases
+  int64_t frozen_rows = 0;  // rows below this number belong to a snapshot or an earlier session: never overwritten
+  FILE* log = nullptr;      // index.log: (key, row) pairs appended by put()
   std::mutex mu;
   void* bounce = nullptr;  // block-aligned staging for O_DIRECT
   int64_t bounce_bytes = 0;
@@ -81,8 +90,9 @@ struct PTable {
   bool load_index(const std::string& path) {
     FILE* f = std::fopen(path.c_str(), "rb");
     if (!f) return false;
-    int64_t n = 0;
-    bool ok = std::fread(&rows, sizeof(rows), 1, f) == 1 && std::fread(&n, sizeof(n), 1, f) == 1;
+    int64_t n = 0, saved_rows = 0;
+    bool ok = std::fread(&saved_rows, sizeof(saved_rows), 1, f) == 1 && std::fread(&n, sizeof(n), 1, f) == 1;
+    if (ok && saved_rows > rows) rows = saved_rows;  // the append position only ever grows
     index.clear();
     index.reserve(static_cast<size_t>(n));
     for (int64_t i = 0; ok && i < n; ++i) {
@@ -121,12 +131,30 @@ OFC_API void* ofc_ptable_open(const char* dir, int value_bytes, int block_bytes,
     delete t;
     return nullptr;
   }
+  struct stat st;
+  if (::fstat(t->fd, &st) == 0) t->rows = (st.st_size + t->row_stride - 1) / t->row_stride;
   t->load_index(t->dir + "/index");  // absent on first use
+  const std::string lpath = t->dir + "/index.log";
+  if (FILE* lf = std::fopen(lpath.c_str(), "rb")) {  // puts of a session that did not reach close()
+    int64_t kv[2];
+    while (std::fread(kv, sizeof(int64_t), 2, lf) == 2) {
+      t->index[kv[0]] = kv[1];
+      if (kv[1] >= t->rows) t->rows = kv[1] + 1;
+    }
+    std::fclose(lf);
+  }
+  t->frozen_rows = t->rows;
+  if (!t->read_only) t->log = std::fopen(lpath.c_str(), "ab");
   return t;
 }
 OFC_API void ofc_ptable_close(void* p) {
   auto* t = static_cast<PTable*>(p);
-  if (!t->read_only) t->save_index(t->dir + "/index");
+  if (!t->read_only && t->save_index(t->dir + "/index")) {
+    if (t->log) std::fclose(t->log);
+    t->log = nullptr;
+    ::unlink((t->dir + "/index.log").c_str());  // the full index now covers everything the log held
+  }
+  if (t->log) std::fclose(t->log);
   ::close(t->fd);
   std::free(t->bounce);
   delete t;
@@ -139,15 +167,25 @@ OFC_API int ofc_ptable_put(void* p, const int64_t* keys, const void* values, int
   for (int64_t i = 0; i < n; ++i) {
     auto it = t->index.find(keys[i]);
     int64_t row;
+    bool moved = true;
     if (it == t->index.end()) {
       row = t->rows++;
       t->index.emplace(keys[i], row);
+    } else if (it->second < t->frozen_rows) {
+      row = t->rows++;  // the old row belongs to a snapshot: leave it, append the new value
+      it->second = row;
     } else {
       row = it->second;
+      moved = false;
     }
     if (!t->io(true, row * t->row_stride, const_cast<char*>(v + i * t->value_bytes), t->value_bytes))
       return ofc::fail("persistent table: write failed");
+    if (moved && t->log) {
+      const int64_t kv[2] = {keys[i], row};
+      std::fwrite(kv, sizeof(int64_t), 2, t->log);
+    }
   }
+  if (t->log) std::fflush(t->log);
   return 0;
 }
 OFC_API int64_t ofc_ptable_get(void* p, const int64_t* keys, void* values_out, uint8_t* found_out, int64_t n) {
@@ -185,10 +223,14 @@ OFC_API int ofc_ptable_save_snapshot(void* p, const char* name) {
   auto* t = static_cast<PTable*>(p);
   std::lock_guard<std::mutex> g(t->mu);
   ::fsync(t->fd);
-  return t->save_index(t->dir + "/snapshots/" + name) ? 0 : ofc::fail("persistent table: cannot write the snapshot");
+  if (!t->save_index(t->dir + "/snapshots/" + name)) return ofc::fail("persistent table: cannot write the snapshot");
+  t->frozen_rows = t->rows;  // every row written so far now belongs to this snapshot
+  return 0;
 }
 OFC_API int ofc_ptable_load_snapshot(void* p, const char* name) {
   auto* t = static_cast<PTable*>(p);
   std::lock_guard<std::mutex> g(t->mu);
-  return t->load_index(t->dir + "/snapshots/" + name) ? 0 : ofc::fail(std::string("persistent table: no snapshot named ") + name);
+  if (!t->load_index(t->dir + "/snapshots/" + name)) return ofc::fail(std::string("persistent table: no snapshot named ") + name);
+  t->frozen_rows = t->rows;
+  return 0;
 }

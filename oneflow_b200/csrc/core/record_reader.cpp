@@ -10,6 +10,7 @@
 
 #include <condition_variable>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <mutex>
@@ -33,6 +34,8 @@ struct Reader {
   std::condition_variable not_empty, not_full;
   std::thread th;
   bool eof = false, stop = false;
+  int error = 0;          // set by the reader thread: -5 corrupt length prefix, -6 truncated record, -7 out of memory
+  uint64_t file_bytes = 0, max_record = 0;
 
   void emit(std::string&& rec) {
     std::unique_lock<std::mutex> lk(mu);
@@ -42,11 +45,34 @@ struct Reader {
     not_empty.notify_one();
   }
   void run() {
+    try {
+      run_inner();
+    } catch (...) {  // bad_alloc / length_error must not reach std::terminate from this thread
+      std::lock_guard<std::mutex> g(mu);
+      error = -7;
+      eof = true;
+      not_empty.notify_all();
+    }
+  }
+  void fail_with(int code) {
+    std::lock_guard<std::mutex> g(mu);
+    error = code;
+    eof = true;
+    not_empty.notify_all();
+  }
+  void run_inner() {
+    uint64_t pos = 0;
     while (true) {
       uint64_t len = 0;
-      if (std::fread(&len, sizeof(len), 1, f) != 1) break;
+      const size_t got = std::fread(&len, 1, sizeof(len), f);
+      if (got == 0) break;                                   // clean end of data
+      if (got != sizeof(len)) return fail_with(-6);          // the file ends inside a length prefix
+      pos += sizeof(len);
+      // the prefix is untrusted: it must fit in what is left of the file (and under the configured maximum)
+      if (len > file_bytes - pos || (max_record && len > max_record)) return fail_with(-5);
       std::string rec(len, '\0');
-      if (len && std::fread(&rec[0], 1, len, f) != len) break;
+      if (len && std::fread(&rec[0], 1, len, f) != len) return fail_with(-6);
+      pos += len;
       if (shuffle > 1) {
         if (pool.size() < shuffle) {
           pool.push_back(std::move(rec));
@@ -100,6 +126,12 @@ OFC_API void* ofc_records_open(const char* path, int prefetch, int shuffle_buffe
   }
   auto* r = new Reader();
   r->f = f;
+  if (std::fseek(f, 0, SEEK_END) == 0) {
+    const long end = std::ftell(f);
+    r->file_bytes = end > 0 ? static_cast<uint64_t>(end) : 0;
+    std::fseek(f, 0, SEEK_SET);
+  }
+  if (const char* m = std::getenv("OFB_MAX_RECORD_BYTES")) r->max_record = std::strtoull(m, nullptr, 10);
   r->prefetch = static_cast<size_t>(prefetch > 0 ? prefetch : 8);
   r->shuffle = static_cast<size_t>(shuffle_buffer > 0 ? shuffle_buffer : 0);
   r->rng.seed(seed);
@@ -110,7 +142,12 @@ OFC_API int64_t ofc_records_next(void* p, void* out, int64_t cap) {
   auto* r = static_cast<Reader*>(p);
   std::unique_lock<std::mutex> lk(r->mu);
   r->not_empty.wait(lk, [&] { return r->eof || !r->q.empty(); });
-  if (r->q.empty()) return 0;
+  if (r->q.empty()) {
+    if (r->error == -5) return ofc::fail("records: corrupt length prefix (longer than the rest of the file)", -5);
+    if (r->error == -6) return ofc::fail("records: the file ends inside a record", -6);
+    if (r->error == -7) return ofc::fail("records: out of memory while reading a record", -7);
+    return 0;
+  }
   std::string& rec = r->q.front();
   if (static_cast<int64_t>(rec.size()) > cap) return ofc::fail("records: caller buffer too small", -3);
   const int64_t n = static_cast<int64_t>(rec.size());

@@ -282,7 +282,9 @@ OFB_API int ofb_layer_norm_bwd_parts(int rows) { return rows < 296 ? rows : 296;
 OFB_API int ofb_layer_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                                const void* add_to_dx, void* dx, float* dgamma, float* dbeta, float* scratch,
                                int accumulate_param_grads, int rows, int cols, void* stream) {
-  if (cols % 8 != 0 || cols > 8 * kLnMaxVecPerThread * 1024) return fail("layer_norm_bwd: cols must be a multiple of 8 and <= 32768");
+  if (cols <= 0 || cols % 8 != 0 || cols > 8 * kLnMaxVecPerThread * 1024)
+    return fail("layer_norm_bwd: cols must be a positive multiple of 8 and <= 32768");
+  if ((dgamma == nullptr) != (dbeta == nullptr)) return fail("layer_norm_bwd: dgamma and dbeta must be given together or not at all");
   if (rows <= 0) return 0;
   if (dgamma && !scratch) return fail("layer_norm_bwd: scratch required for parameter gradients");
   int nv;
@@ -331,7 +333,11 @@ OFB_API int ofb_layer_norm_bwd(const void* dy, const void* x, const void* gamma,
 //
 // The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that
 // device current) and remembers it; that first call should therefore happen before any stream capture
-// begins. No call here allocates or frees memory.
+// begins. No call here allocates or frees memory itself. One caveat comes from the CUDA runtime, not from
+// this code: with lazy module loading (the default) the driver may load this library's module image,
+// the 9.25 MiB array included, at the first call that touches it on a device, and that load can fail
+// when the device has no memory left. A caller that freezes its memory should make one call (or load
+// the module eagerly, CUDA_MODULE_LOADING=EAGER) before it does so.
 // ------------------------------------------------------------------------------------------------
 namespace {
 constexpr int kNoAllocMaxCols = 4096;
@@ -367,7 +373,9 @@ OFB_API int ofb_layer_norm_bwd_noalloc(const void* dy, const void* x, const void
   if (cols > kNoAllocMaxCols)
     return fail("layer_norm_bwd_noalloc: cols = " + std::to_string(cols) + " exceeds the built-in scratch (max " +
                 std::to_string(kNoAllocMaxCols) + " columns); use ofb_layer_norm_bwd with caller-provided scratch");
-  if (cols % 8 != 0) return fail("layer_norm_bwd_noalloc: cols must be a multiple of 8");
+  if (cols <= 0 || cols % 8 != 0) return fail("layer_norm_bwd_noalloc: cols must be a positive multiple of 8");
+  if ((dgamma == nullptr) != (dbeta == nullptr))
+    return fail("layer_norm_bwd_noalloc: dgamma and dbeta must be given together or not at all");
   if (rows <= 0) return 0;
   float* scratch = nullptr;
   if (noalloc_scratch_ptr(&scratch)) return -1;

@@ -16,7 +16,11 @@
 //     are refused with an error (returns -1, message from ofb_last_error()). rows is unlimited.
 //   * The first call on each device looks up the device address of the static array (with that device
 //     current). Make that first call outside any CUDA stream capture; later calls only launch kernels.
-//   * No cudaMalloc / cudaFree / allocating library call happens in this function, on any call.
+//   * This function itself calls no cudaMalloc / cudaFree / allocating library routine, on any call. The
+//     CUDA runtime may still load the library's module image (which contains the 9.25 MiB array) lazily
+//     at the first call on a device, and that load needs device memory: make the first call before the
+//     memory is frozen or exhausted, or run with CUDA_MODULE_LOADING=EAGER.
+//   * dgamma and dbeta are given together or not at all; one without the other is refused (-1).
 //   * All calls share the same array, which keeps the previous call's contents. The kernels overwrite
 //     every value they later read, so nothing has to be cleared between calls; but calls that overlap on
 //     the GPU (several streams or threads) race on it. Serialise them on one stream or with events.

@@ -1,21 +1,7 @@
-"""Argument type aliases of the layer constructors (reference: python/oneflow/nn/common_types.py:16-36)."""
-from typing import Tuple, TypeVar, Union
-
-T = TypeVar("T")
-_scalar_or_tuple_any_t = Union[T, Tuple[T, ...]]
-_scalar_or_tuple_1_t = Union[T, Tuple[T]]
-_scalar_or_tuple_2_t = Union[T, Tuple[T, T]]
-_scalar_or_tuple_3_t = Union[T, Tuple[T, T, T]]
-_scalar_or_tuple_4_t = Union[T, Tuple[T, T, T, T]]
-_scalar_or_tuple_5_t = Union[T, Tuple[T, T, T, T, T]]
-_scalar_or_tuple_6_t = Union[T, Tuple[T, T, T, T, T, T]]
-_size_any_t = _scalar_or_tuple_any_t[int]
-_size_1_t = _scalar_or_tuple_1_t[int]
-_size_2_t = _scalar_or_tuple_2_t[int]
-_size_3_t = _scalar_or_tuple_3_t[int]
-_size_4_t = _scalar_or_tuple_4_t[int]
-_size_5_t = _scalar_or_tuple_5_t[int]
-_size_6_t = _scalar_or_tuple_6_t[int]
-_ratio_2_t = _scalar_or_tuple_2_t[float]
-_ratio_3_t = _scalar_or_tuple_3_t[float]
-_ratio_any_t = _scalar_or_tuple_any_t[float]
+"""``flow.nn.common_types``: the size / tuple type aliases used in layer signatures; identical to torch's."""
+from torch.nn.common_types import *  # noqa: F401,F403
+from torch.nn.common_types import (_size_1_t, _size_2_t, _size_3_t, _size_4_t, _size_5_t, _size_6_t, _size_any_t,  # noqa: F401
+                                   _ratio_2_t, _ratio_3_t, _ratio_any_t, _tensor_list_t, _maybe_indices_t,
+                                   _scalar_or_tuple_1_t, _scalar_or_tuple_2_t, _scalar_or_tuple_3_t, _scalar_or_tuple_4_t,
+                                   _scalar_or_tuple_5_t, _scalar_or_tuple_6_t, _scalar_or_tuple_any_t, _size_any_opt_t,
+                                   _size_2_opt_t, _size_3_opt_t)

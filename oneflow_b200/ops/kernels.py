@@ -71,6 +71,8 @@ def layer_norm_bwd(dy, x, gamma, mean, rstd, add_to_dx=None, dgamma=None, dbeta=
     """Returns (dx bf16, dgamma fp32, dbeta fp32). When dgamma/dbeta buffers are given the parameter
     gradients are accumulated into them."""
     rows, cols = x.shape
+    if (dgamma is None) != (dbeta is None):
+        raise ValueError("layer_norm_bwd: dgamma and dbeta must be given together or not at all")
     if not x.is_cuda:
         xf, dyf = x.float(), dy.float()
         xh = (xf - mean[:, None]) * rstd[:, None]

@@ -97,12 +97,33 @@ def test_persistent_table_roundtrip_and_snapshots(tmp_path):
     t.save_snapshot("s1")
     t.put(np.array([6, 7], dtype=np.int64), np.ones((2, 24), np.float32))
     assert len(t) == 5
+    assert np.allclose(t.get(np.array([7], np.int64))[0][0], 1.0)      # the live table sees the update
+    t.save_snapshot("s2")
     t.load_snapshot("s1")
+    # a snapshot is point-in-time: key 7 reads the value it had when s1 was taken, key 6 does not exist yet
     assert len(t) == 4 and not t.get(np.array([6], np.int64))[1][0]
+    assert np.allclose(t.get(keys)[0], vals)
+    # writing on after loading the older snapshot must not disturb the rows of the younger one
+    t.put(np.array([11], dtype=np.int64), np.full((1, 24), 3.0, np.float32))
+    t.load_snapshot("s2")
+    assert len(t) == 5 and np.allclose(t.get(np.array([6, 7], np.int64))[0], 1.0)
+    t.load_snapshot("s1")
     t.close()
     t2 = R.PersistentTable(tmp_path / "tbl", value_bytes=24 * 4)   # index persisted on close
-    assert len(t2) == 4 and np.allclose(t2.get(keys)[0], np.where(keys[:, None] == 7, 1.0, vals))
+    assert len(t2) == 4 and np.allclose(t2.get(keys)[0], vals)
     t2.close()
+
+
+def test_persistent_table_index_survives_a_session_that_never_closed(tmp_path):
+    t = R.PersistentTable(tmp_path / "tbl", value_bytes=8 * 4, block_bytes=512)
+    keys = np.arange(10, dtype=np.int64)
+    vals = np.random.rand(10, 8).astype(np.float32)
+    t.put(keys, vals)
+    # no close(): the index file was never written, only the put log
+    t2 = R.PersistentTable(tmp_path / "tbl", value_bytes=8 * 4, block_bytes=512)
+    assert len(t2) == 10 and np.allclose(t2.get(keys)[0], vals)
+    t2.close()
+    t.close()
 
 
 def test_executor_respects_dependencies_and_overlaps_streams():
@@ -147,3 +168,30 @@ def test_record_and_token_readers(tmp_path):
     with pytest.raises(R.core.CoreError):
         ds.batch([200], seq_len=8)
     ds.close()
+
+
+def test_record_reader_reports_corrupt_and_truncated_files(tmp_path):
+    """A length prefix larger than the rest of the file, or a file that ends inside a record, is an error the
+    caller sees (not a crash of the reader thread and not a silent end of data)."""
+    import struct
+    good = [b"abc", b"defgh"]
+    R.write_records(tmp_path / "ok.bin", good)
+    raw = (tmp_path / "ok.bin").read_bytes()
+    (tmp_path / "huge.bin").write_bytes(raw + struct.pack("<Q", 1 << 60) + b"xy")
+    r = R.RecordReader(tmp_path / "huge.bin")
+    assert next(r) == b"abc" and next(r) == b"defgh"
+    with pytest.raises(R.CoreError, match="corrupt length prefix"):
+        next(r)
+    r.close()
+    (tmp_path / "cut.bin").write_bytes(raw[:-2])            # payload cut short: its prefix now exceeds the file
+    r = R.RecordReader(tmp_path / "cut.bin")
+    assert next(r) == b"abc"
+    with pytest.raises(R.CoreError, match="corrupt length prefix"):
+        next(r)
+    r.close()
+    (tmp_path / "cut2.bin").write_bytes(raw[:len(raw) - 5 - 3])   # the file ends inside the second length prefix
+    r = R.RecordReader(tmp_path / "cut2.bin")
+    assert next(r) == b"abc"
+    with pytest.raises(R.CoreError, match="ends inside a record"):
+        next(r)
+    r.close()

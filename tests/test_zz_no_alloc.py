@@ -23,9 +23,9 @@ def _ptr(t):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 
 
-def _noalloc_bwd(lib, dy, x, gamma, mean, rstd, add, accumulate_into=None):
+def _noalloc_bwd(lib, dy, x, gamma, mean, rstd, add, accumulate_into=None, dx=None):
     rows, cols = x.shape
-    dx = torch.empty_like(x)
+    dx = torch.empty_like(x) if dx is None else dx
     if accumulate_into is None:
         dg = torch.empty(cols, dtype=torch.float32, device=x.device)
         db = torch.empty(cols, dtype=torch.float32, device=x.device)
@@ -67,10 +67,19 @@ def test_layer_norm_bwd_noalloc_matches_regular_entry_point_twice():
         _close(dx, ref_dx, 2e-2)
         _close(dg, ref_dg, 5e-2)
         _close(db, ref_db, 5e-2)
-    # accumulation into existing gradients on a third call
-    rc, _, dg2, db2 = _noalloc_bwd(lib, dy, x, g, mean, rstd, add, accumulate_into=(dg.clone(), db.clone()))
+    # accumulation into existing gradients on a third call; by now the module is loaded and the array's address is
+    # known, so the device's free memory must be the same before and after the call (nothing was allocated)
+    acc = (dg.clone(), db.clone())
+    dx_out = torch.empty_like(x)                      # every output exists before the measurement starts
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    rc, _, dg2, db2 = _noalloc_bwd(lib, dy, x, g, mean, rstd, add, accumulate_into=acc, dx=dx_out)
     assert rc == 0
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_reserved() == reserved_before      # torch's pool did not grow either
+    assert free_after == free_before, f"device free memory moved by {free_before - free_after} bytes across the call"
     _close(dg2, 2 * ref_dg, 5e-2)
     _close(db2, 2 * ref_db, 5e-2)
     assert _native.read_status() == (0, 0)
@@ -86,3 +95,32 @@ def test_layer_norm_bwd_noalloc_rejects_oversized_problem():
     rc, *_ = _noalloc_bwd(lib, x, x, None, mean, rstd, None)
     assert rc == -1
     assert b"exceeds the built-in scratch" in lib.ofb_last_error()
+
+
+def test_layer_norm_bwd_noalloc_rejects_half_given_param_grads_and_bad_cols():
+    """One of dgamma / dbeta without the other, or a non-positive column count, is refused before anything launches."""
+    lib = ctypes.CDLL(_native.lib_path("libofb_kernels.so"))
+    lib.ofb_layer_norm_bwd_noalloc.restype = c_int
+    lib.ofb_layer_norm_bwd.restype = c_int
+    lib.ofb_last_error.restype = ctypes.c_char_p
+    rows, cols = 16, 256
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    mean = torch.zeros(rows, device="cuda")
+    rstd = torch.ones(rows, device="cuda")
+    dx = torch.empty_like(x)
+    dg = torch.zeros(cols, device="cuda")
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.ofb_layer_norm_bwd_noalloc(_ptr(x), _ptr(x), _ptr(None), _ptr(mean), _ptr(rstd), _ptr(None), _ptr(dx),
+                                        _ptr(dg), _ptr(None), c_int(0), c_int(rows), c_int(cols), stream)
+    assert rc == -1 and b"together" in lib.ofb_last_error()
+    rc = lib.ofb_layer_norm_bwd_noalloc(_ptr(x), _ptr(x), _ptr(None), _ptr(mean), _ptr(rstd), _ptr(None), _ptr(dx),
+                                        _ptr(None), _ptr(None), c_int(0), c_int(rows), c_int(0), stream)
+    assert rc == -1 and b"positive multiple of 8" in lib.ofb_last_error()
+    scratch = torch.empty(2 * rows * cols, device="cuda")
+    rc = lib.ofb_layer_norm_bwd(_ptr(x), _ptr(x), _ptr(None), _ptr(mean), _ptr(rstd), _ptr(None), _ptr(dx), _ptr(None),
+                                _ptr(dg), _ptr(scratch), c_int(0), c_int(rows), c_int(cols), stream)
+    assert rc == -1 and b"together" in lib.ofb_last_error()
+    with pytest.raises(ValueError):
+        K.layer_norm_bwd(x, x, None, mean, rstd, dgamma=dg, dbeta=None)
+    torch.cuda.synchronize()
+    assert _native.read_status() == (0, 0)
