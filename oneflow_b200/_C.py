@@ -195,9 +195,18 @@ def fused_mlp(x, weights, biases, skip_final_activation=False):
 
 
 def fused_matmul_bias(x, weight, bias, _add_to_output=None, alpha=1.0, beta=1.0):
-    from .nn.modules.fused_mlp import fused_linear_act
-    y = fused_linear_act(x, weight, bias, 0)
-    return y if _add_to_output is None else y * alpha + _add_to_output * beta
+    """``alpha * (x @ weight^T + bias) + beta * _add_to_output``: one GEMM with the bias and the addend in its epilogue
+    (for alpha = beta = 1), global tensors included (framework/fused_ops.linear)."""
+    from .framework import fused_ops
+    if alpha == 1.0 and beta == 1.0:
+        return fused_ops.linear(x, weight, bias, residual=_add_to_output)
+    y = fused_ops.linear(x, weight, bias)
+    return y * alpha if _add_to_output is None else y * alpha + _add_to_output * beta
+
+
+def fused_attention_qkv_packed(qkv, *, seq_len, head_size, causal=True, scale=None):
+    from .framework import fused_ops
+    return fused_ops.fused_attention_qkv_packed(qkv, seq_len=seq_len, head_size=head_size, causal=causal, scale=scale)
 
 
 def fused_dot_feature_interaction(features, output_concat=None, self_interaction=False, output_padding=0, pooling="none"):

@@ -169,10 +169,14 @@ _B = _Bsbp()
 
 
 def _collides(nd_sbp, axis):
+    """True when changing mesh axis `axis` cannot be done as a 1-D step on the local shard: an INNER axis (higher
+    index) splits the same tensor dimension, so the shard this axis sees is not contiguous in that dimension. Splits of
+    the same dimension by OUTER axes are harmless: nested splits apply outermost first, so the inner step works inside
+    the outer shard."""
     s = nd_sbp[axis]
     if s.kind != "S":
         return False
-    return any(a != axis and o.kind == "S" and o.axis == s.axis for a, o in enumerate(nd_sbp))
+    return any(a > axis and o.kind == "S" and o.axis == s.axis for a, o in enumerate(nd_sbp))
 
 
 def plan(in_nd, out_nd):
@@ -283,6 +287,10 @@ def convert(local, logical_shape, dtype, in_placement, in_nd, out_placement, out
         return out
     in_coords = in_placement.coords(me)
     out_coords = out_placement.coords(me)
+    if in_placement.hierarchy == out_placement.hierarchy and tuple(in_nd) == tuple(out_nd):
+        # same mesh shape, same layout, other ranks (a pipeline stage boundary): every rank hands its shard to the
+        # rank at the same mesh coordinates, nothing is gathered
+        return _one_to_one(local, logical_shape, dtype, in_placement, out_placement, in_nd, in_coords, out_coords)
     full = None
     if in_coords is not None:
         full = to_all_broadcast(local, logical_shape, in_placement, in_nd, in_coords)
@@ -312,6 +320,73 @@ def convert(local, logical_shape, dtype, in_placement, in_nd, out_placement, out
     if full.device != dev_out:
         full = full.to(dev_out)
     return from_all_broadcast(full, out_placement, out_nd, out_coords)
+
+
+_P2P_GROUPS = {}
+_P2P_PENDING = []      # (work, tensor) of asynchronous sends still in flight: keeps the buffers alive
+
+
+def _p2p_group(src, dst):
+    """One communicator per ordered rank pair: traffic in the two directions of a pipeline boundary never queues
+    behind each other (a send only completes once the peer posted its receive), and it runs on that communicator's
+    own stream beside the compute stream. gloo shares the default group."""
+    if dist.get_backend() != "nccl":
+        return None
+    key = (src, dst)
+    g = _P2P_GROUPS.get(key)
+    if g is None:
+        g = dist.new_group(ranks=sorted([src, dst]), use_local_synchronization=True)
+        _P2P_GROUPS[key] = g
+    return g
+
+
+def _reap_sends(limit=64):
+    if len(_P2P_PENDING) > limit:
+        keep = []
+        for w, t in _P2P_PENDING:
+            if not w.is_completed():
+                keep.append((w, t))
+        _P2P_PENDING[:] = keep[-4 * limit:]
+
+
+def _one_to_one(local, logical_shape, dtype, in_pl, out_pl, nd, in_coords, out_coords):
+    me = _rank()
+    out = None
+    if in_coords is not None:
+        dst = out_pl.rank_at(in_coords)
+        if dst == me:
+            out = local
+        else:
+            t = local.contiguous()
+            if out_pl.type == "cuda" and not t.is_cuda and dist.get_backend() == "nccl":
+                t = t.to(torch.device("cuda", torch.cuda.current_device()))
+            if t.is_cuda and dist.get_backend() == "gloo":
+                t = t.cpu()
+            if debug_routes:
+                log.warning("boxing naive-1-to-1: rank %d -> %d, %s", me, dst, tuple(t.shape))
+            w = dist.isend(t, dst, group=_p2p_group(me, dst))
+            _P2P_PENDING.append((w, t))
+            _reap_sends()
+    if out_coords is None:
+        return torch.empty((0,), dtype=dtype, device=local.device if local is not None else "cpu")
+    if out is None:
+        src = in_pl.rank_at(out_coords)
+        shape = local_shape(logical_shape, out_pl.hierarchy, nd, out_coords)
+        dev = out_pl.device()
+        recv_dev = torch.device("cpu") if dist.get_backend() == "gloo" else dev
+        buf = torch.empty(tuple(shape), dtype=dtype, device=recv_dev)
+        dist.irecv(buf, src, group=_p2p_group(src, me)).wait()
+        out = buf.to(dev) if buf.device != dev else buf
+    elif out.device != out_pl.device():
+        out = out.to(out_pl.device())
+    return out
+
+
+def flush_sends():
+    """Waits for the asynchronous stage-boundary sends issued so far (end of a step)."""
+    for w, _t in _P2P_PENDING:
+        w.wait()
+    _P2P_PENDING.clear()
 
 
 # ``flow.boxing.enable_fusion`` / ``flow.boxing.nccl.*`` (reference: python/oneflow/boxing/__init__.py:16-17)

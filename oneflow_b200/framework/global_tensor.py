@@ -44,9 +44,31 @@ def _contig_strides(shape):
 
 
 class GlobalTensor(torch.Tensor):
-    _local: torch.Tensor
     _placement: Placement
     _nd_sbp: tuple
+
+    # The local shard. A row-parallel product may hand out a tensor whose shard is still a thunk (a partial sum that
+    # nobody has asked for yet, see framework/fused_ops.DeferredPartial): reading ``_local`` then runs the plain GEMM,
+    # while a boxing step that wants the reduced rows asks the thunk for the fused GEMM->reduce-scatter instead.
+    @property
+    def _local(self):
+        d = self.__dict__
+        loc = d.get("_loc")
+        if loc is None:
+            th = d.get("_thunk")
+            if th is not None:
+                loc = th.materialize()
+                view = d.get("_thunk_view")
+                if view is not None:
+                    loc = loc.view(view)
+                d["_loc"], d["_thunk"] = loc, None
+        return loc
+
+    @_local.setter
+    def _local(self, value):
+        d = self.__dict__
+        d["_loc"] = value
+        d["_thunk"] = None
 
     @staticmethod
     def __new__(cls, local, logical_shape, placement, nd_sbp, requires_grad=False):
@@ -171,10 +193,23 @@ def wrap(local, logical_shape, pl, nd, requires_grad=False):
     return GlobalTensor(local, logical_shape, pl, nd, requires_grad=requires_grad)
 
 
+def wrap_deferred(thunk, local_view, logical_shape, dtype, device, pl, nd):
+    """A global tensor whose local shard is computed on first use by ``thunk`` (``materialize`` / ``reduce_scatter``)."""
+    g = GlobalTensor(torch.empty((0,), dtype=dtype, device=device), logical_shape, pl, nd)
+    d = g.__dict__
+    d["_loc"], d["_thunk"], d["_thunk_view"] = None, thunk, tuple(local_view)
+    return g
+
+
 def rebox(x: GlobalTensor, nd) -> GlobalTensor:
     nd = tuple(nd)
     if nd == x._nd_sbp:
         return x
+    if x.__dict__.get("_thunk") is not None:
+        from .fused_ops import take_deferred_reduce_scatter
+        local = take_deferred_reduce_scatter(x, nd)
+        if local is not None:
+            return wrap(local, x.shape, x._placement, nd)
     local = boxing.convert_same_placement(x._local, tuple(x.shape), x._placement, x._nd_sbp, nd)
     return wrap(local, x.shape, x._placement, nd)
 
@@ -869,6 +904,10 @@ class _GlobalToGlobal(torch.autograd.Function):
     @staticmethod
     def forward(ctx, g, pl, nd, grad_nd):
         ctx.in_pl, ctx.in_nd, ctx.grad_nd = g._placement, g._nd_sbp, grad_nd
+        ctx.out_nd = tuple(nd)
+        if pl == g._placement:
+            out = rebox(g, nd)                 # same ranks: a deferred partial sum can take its fused reduce-scatter
+            return wrap(out._local, g.shape, pl, nd) if out is g else out
         local = boxing.convert(g._local, tuple(g.shape), g.dtype, g._placement, g._nd_sbp, pl, nd)
         return wrap(local, g.shape, pl, nd)
 
@@ -876,6 +915,13 @@ class _GlobalToGlobal(torch.autograd.Function):
     def backward(ctx, grad):
         # the gradient returns to the input's placement, with grad_sbp if given else its own sbp
         # (reference: oneflow/core/autograd/gradient_funcs/global_to_global.cpp:52-75)
+        if grad._placement != ctx.in_pl and ctx.grad_nd is None and grad._placement.hierarchy == ctx.in_pl.hierarchy:
+            # a placement change between equal meshes (pipeline stage boundary): first bring the gradient to the layout
+            # the forward tensor had, inside its own placement. Both sides of the transfer then agree on the layout
+            # without exchanging it (the rank that skipped this stage only holds a placeholder), and each rank sends
+            # its shard to its counterpart.
+            want = tuple(B if s_.kind == "P" else s_ for s_ in ctx.out_nd)
+            grad = rebox(grad, want)
         nd = ctx.grad_nd if ctx.grad_nd is not None else grad._nd_sbp
         if len(nd) != ctx.in_pl.ndim:
             nd = (B,) * ctx.in_pl.ndim
@@ -911,6 +957,8 @@ def to_global(x, placement=None, sbp=None, *, grad_sbp=None, check_meta=True, co
             return x
         if x.requires_grad and torch.is_grad_enabled():
             return _GlobalToGlobal.apply(x, pl, nd, gnd)
+        if pl == x._placement:
+            return rebox(x, nd)
         local = boxing.convert(x._local, tuple(x.shape), x.dtype, x._placement, x._nd_sbp, pl, nd)
         return wrap(local, x.shape, pl, nd)
     if placement is None or sbp is None:

@@ -32,16 +32,19 @@ _GROUP_CACHE = {}
 
 
 def group_for_ranks(ranks):
-    """Process group over exactly these global ranks. Every rank of the world must call this with the same
-    arguments in the same order (new_group is collective)."""
+    """Process group over exactly these global ranks. Only the member ranks create it (group-local synchronisation), each
+    when it first needs it: ranks outside a placement (other pipeline stages) never have to take part. The members
+    reach the creation in the same order because they run the same program on the same global tensors."""
     ranks = tuple(ranks)
     if not dist.is_initialized():
         return None
     if ranks == tuple(range(dist.get_world_size())):
         return dist.group.WORLD
+    if dist.get_rank() not in ranks:
+        return None
     g = _GROUP_CACHE.get(ranks)
     if g is None:
-        g = dist.new_group(list(ranks))
+        g = dist.new_group(list(ranks), use_local_synchronization=True)
         _GROUP_CACHE[ranks] = g
     return g
 
@@ -146,24 +149,13 @@ class placement:
         return group_for_ranks(self.ranks_flat)
 
     def axis_group(self, axis):
-        """Sub-group of the calling rank along one mesh axis. Collective over the world: all the sub-groups of
-        that axis are created (in a fixed order) the first time any of them is requested."""
+        """Sub-group of the calling rank along one mesh axis (None on ranks outside the placement)."""
         if not dist.is_initialized():
             return None
         me = dist.get_rank()
-        mine = None
-        others = [range(d) for i, d in enumerate(self.hierarchy) if i != axis]
-        for combo in itertools.product(*others):
-            c = list(combo)
-            c.insert(axis, 0)
-            ranks = []
-            for i in range(self.hierarchy[axis]):
-                c[axis] = i
-                ranks.append(self.rank_at(c))
-            g = group_for_ranks(ranks)
-            if me in ranks:
-                mine = g
-        return mine
+        if me not in self.ranks_flat:
+            return None
+        return group_for_ranks(self.axis_ranks(axis, me))
 
     def device(self):
         if self.type in ("cpu", "mock"):

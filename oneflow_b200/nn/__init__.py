@@ -17,6 +17,7 @@ del _n
 from .graph import Graph  # noqa: F401
 from .modules import FusedMLP, SyncBatchNorm, distributed_partial_fc_sample  # noqa: F401
 from .modules.nhwc import AvgPool2d, BatchNorm2d, Conv2d, MaxPool2d  # noqa: F401  (layout by ONEFLOW_ENABLE_NHWC)
+from .modules.native_layers import Embedding, LayerNorm, Linear  # noqa: F401  (forward on the native kernels)
 from .modules import (AllReduce, COCOReader, CoinFlip, CropMirrorNormalize, DistributedPariticalFCSample,  # noqa: F401
                       GPTIndexedBinDataReader, OFRecordBytesDecoder, OFRecordImageDecoder, OFRecordImageDecoderRandomCrop,
                       OFRecordImageGpuDecoderRandomCropResize, OFRecordRawDecoder, OFRecordReader, QatConv1d, QatConv2d,

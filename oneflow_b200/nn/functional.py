@@ -10,6 +10,25 @@ def __getattr__(name):
     return getattr(_F, name)
 
 
+def linear(input, weight, bias=None):
+    """``input @ weight^T + bias``: the tcgen05 GEMM for bf16 CUDA tensors, SBP-aware (fused tensor-parallel products)
+    for global tensors, torch's op otherwise."""
+    from ..framework import fused_ops
+    return fused_ops.linear(input, weight, bias)
+
+
+def layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5):
+    from ..framework import fused_ops
+    return fused_ops.layer_norm(input, normalized_shape, weight, bias, eps)
+
+
+def embedding(input, weight, padding_idx=None, max_norm=None, norm_type=2.0, scale_grad_by_freq=False, sparse=False):
+    if padding_idx is not None or max_norm is not None or scale_grad_by_freq or sparse:
+        return _F.embedding(input, weight, padding_idx, max_norm, norm_type, scale_grad_by_freq, sparse)
+    from ..framework import fused_ops
+    return fused_ops.embedding(input, weight)
+
+
 def conv2d(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
     """torch's conv2d, or the implicit-GEMM tcgen05 kernels for bf16 channels-last stride-1 "same" convolutions."""
     from .modules.conv import conv2d as _conv2d
@@ -32,7 +51,11 @@ def square_relu(x):
 
 def sparse_softmax_cross_entropy(labels, logits):
     """Per-element cross entropy of integer ``labels`` against ``logits`` over the last axis, no reduction
-    (reference: python/oneflow/nn/modules/sparse_softmax_cross_entropy.py:19-70)."""
+    (reference: python/oneflow/nn/modules/sparse_softmax_cross_entropy.py:19-70). 2-D bf16 CUDA logits and global
+    logits (the class axis may be split: vocabulary parallel) run the fused kernels and return fp32."""
+    from ..framework import fused_ops, global_tensor as _GT
+    if logits.dim() == 2 and (isinstance(logits, _GT.GlobalTensor) or (logits.is_cuda and logits.dtype == _torch.bfloat16)):
+        return fused_ops.sparse_softmax_cross_entropy(logits, labels)
     nc = logits.shape[-1]
     loss = _F.cross_entropy(logits.reshape(-1, nc).float(), labels.reshape(-1).long(), reduction="none")
     return loss.reshape(labels.shape).to(logits.dtype)

@@ -98,11 +98,57 @@ class ModuleProxy(Proxy):
     def __setattr__(self, name, value):
         setattr(self._module, name, value)
 
+    # containers (ModuleList / Sequential / ModuleDict): ``self.m.layers[i].to(GraphModule).set_stage(...)``
+    def _child(self, key):
+        mod = object.__getattribute__(self, "_module")
+        name = str(key)
+        if isinstance(key, int) and key < 0:
+            name = str(len(mod) + key)
+        child = mod._modules.get(name)
+        if child is None:
+            raise KeyError(key)
+        ch = self._children.get(name)
+        if ch is None:
+            ch = ModuleProxy(child, f"{self._name}.{name}", self._graph)
+            self._children[name] = ch
+        return ch
+
+    def __getitem__(self, key):
+        if isinstance(key, slice):
+            return [self._child(i) for i in range(*key.indices(len(self._module)))]
+        return self._child(key)
+
+    def __len__(self):
+        return len(self._module)
+
+    def __iter__(self):
+        mod = self._module
+        if isinstance(mod, torch.nn.ModuleDict):
+            return iter(mod.keys())
+        return (self._child(i) for i in range(len(mod)))
+
+    def _walk(self):
+        yield self
+        for ch in self._children.values():
+            yield from ch._walk()
+
     def __call__(self, *args, **kwargs):
         gm = self._gm
         if gm.stage_placement is not None:
             args = tuple(_to_stage(a, gm.stage_placement) for a in args)
             kwargs = {k: _to_stage(v, gm.stage_placement) for k, v in kwargs.items()}
+            if not gm.stage_placement.contains(GT._rank()):
+                # a stage of another rank: the recorded plan knows what it returns, nothing of it runs here
+                meta = self.__dict__.get("_skip_meta")
+                if meta is not None and not kwargs:
+                    return _skipped_stage(meta, args)
+                out = self._call_module(gm, args, kwargs)
+                if not kwargs:
+                    self.__dict__["_skip_meta"] = _record_outputs(out)
+                return out
+        return self._call_module(gm, args, kwargs)
+
+    def _call_module(self, gm, args, kwargs):
         mod = self._module
         fn = mod
         if self._children:
@@ -114,22 +160,33 @@ class ModuleProxy(Proxy):
 
 
 class _ChildPatched:
-    """Calls the module while its direct children are temporarily replaced by their proxies, so that stage /
-    checkpoint settings of nested blocks take effect."""
+    """Calls the module while its children that have proxies are temporarily replaced by shims calling those proxies,
+    so that stage / checkpoint settings of nested blocks take effect. Pure containers (ModuleList, ModuleDict) stay in
+    place and their entries are replaced instead."""
 
     def __init__(self, proxy):
         self.proxy = proxy
 
+    @staticmethod
+    def _patch(proxy, saved):
+        mod = proxy._module
+        for name, ch in proxy._children.items():
+            child = mod._modules.get(name)
+            if child is None:
+                continue
+            if isinstance(child, (torch.nn.ModuleList, torch.nn.ModuleDict)):
+                _ChildPatched._patch(ch, saved)
+            else:
+                saved.append((mod, name, child))
+                mod._modules[name] = _CallShim(ch)
+
     def __call__(self, *args, **kwargs):
-        mod = self.proxy._module
-        saved = {}
-        for name, ch in self.proxy._children.items():
-            saved[name] = mod._modules[name]
-            mod._modules[name] = _CallShim(ch)
+        saved = []
+        self._patch(self.proxy, saved)
         try:
-            return mod(*args, **kwargs)
+            return self.proxy._module(*args, **kwargs)
         finally:
-            for name, m in saved.items():
+            for mod, name, m in saved:
                 mod._modules[name] = m
 
 
@@ -149,6 +206,54 @@ def _to_stage(x, placement):
     return x
 
 
+def _record_outputs(out):
+    """(tree spec, per-leaf description) of what a stage's module returned on a rank outside its placement."""
+    from torch.utils import _pytree as pytree
+    flat, spec = pytree.tree_flatten(out)
+    leaves = []
+    for t in flat:
+        if isinstance(t, GT.GlobalTensor):
+            leaves.append(("g", tuple(t.shape), t.dtype, t.placement, t.sbp, bool(t.requires_grad)))
+        elif isinstance(t, torch.Tensor):
+            return None                      # a local tensor result cannot be reproduced without running the module
+        else:
+            leaves.append(("o", t))
+    return spec, leaves
+
+
+class _SkippedStage(torch.autograd.Function):
+    """Stands for a pipeline stage that runs on other ranks: placeholders of the recorded outputs go forward, placeholder
+    gradients of the inputs go backward (the stage-boundary ``to_global`` around it moves the real data)."""
+
+    @staticmethod
+    def forward(ctx, leaves, anchor, *tensors):
+        ctx.in_meta = [(tuple(t.shape), t.dtype, t.placement, t.sbp) if isinstance(t, GT.GlobalTensor) else None for t in tensors]
+        gl = [l for l in leaves if l[0] == "g"]
+        outs = tuple(GT._placeholder(torch.empty(l[1], dtype=l[2], device="meta"), l[3], l[4]) for l in gl)
+        ctx.mark_non_differentiable(*[o for o, l in zip(outs, gl) if not (l[5] and o.dtype.is_floating_point)])
+        return outs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        res = [None, None]
+        for m in ctx.in_meta:
+            res.append(None if m is None or not m[1].is_floating_point else
+                       GT._placeholder(torch.empty(m[0], dtype=m[1], device="meta"), m[2], m[3]))
+        return tuple(res)
+
+
+def _skipped_stage(meta, args):
+    from torch.utils import _pytree as pytree
+    spec, leaves = meta
+    tensors = [a for a in args if isinstance(a, torch.Tensor)]
+    # the real stage's outputs depend on its parameters, so they take part in autograd even when no input does: the
+    # anchor gives the stand-in the same property (the stage-boundary transfer after it must get its backward node)
+    anchor = torch.zeros((), requires_grad=torch.is_grad_enabled())
+    outs = list(_SkippedStage.apply(leaves, anchor, *tensors))
+    flat = [outs.pop(0) if l[0] == "g" else l[1] for l in leaves]
+    return pytree.tree_unflatten(flat, spec)
+
+
 class Graph:
     _nesting = 0
 
@@ -164,6 +269,8 @@ class Graph:
         self._debug_ranks = None
         self._name = f"{type(self).__name__}_{id(self) & 0xffff}"
         self._pending_state = None
+        self._flat = []
+        self._plan = None
 
     # ------------------------------------------------------------------ construction API
     def __setattr__(self, name, value):
@@ -301,6 +408,8 @@ class Graph:
         for i, o in enumerate(self._opts):
             opt = o["optim"]
             sd[f"System-Optimizer-{i}"] = opt.state_dict()
+            if o.get("flat") is not None:
+                sd[f"System-FlatOptimizer-{i}"] = o["flat"].state_dict()
             if o["lr_sch"] is not None:
                 sd[f"System-LRScheduler-{i}"] = o["lr_sch"].state_dict()
         if self._grad_scaler is not None and hasattr(self._grad_scaler, "state_dict"):
@@ -318,6 +427,9 @@ class Graph:
             k = f"System-Optimizer-{i}"
             if k in state_dict:
                 o["optim"].load_state_dict(state_dict[k])
+            k = f"System-FlatOptimizer-{i}"
+            if k in state_dict and o.get("flat") is not None:
+                o["flat"].load_state_dict(state_dict[k])
             k = f"System-LRScheduler-{i}"
             if k in state_dict and o["lr_sch"] is not None:
                 o["lr_sch"].load_state_dict(state_dict[k])
@@ -332,11 +444,12 @@ class Graph:
         the ordinary state dict plus the recorded input meta."""
         sd = self.state_dict(destination)
         sd["System-InputMeta"] = self._input_meta
+        sd["System-Plan"] = self._plan
         return sd
 
     def load_runtime_state_dict(self, state_dict, *, warmup_with_run=True):
         self._input_meta = state_dict.get("System-InputMeta")
-        self.load_state_dict({k: v for k, v in state_dict.items() if k != "System-InputMeta"}, strict=False)
+        self.load_state_dict({k: v for k, v in state_dict.items() if k not in ("System-InputMeta", "System-Plan")}, strict=False)
 
     # ------------------------------------------------------------------ compile
     def _all_params(self):
@@ -355,7 +468,10 @@ class Graph:
         consumers all-gather on use."""
         if self.config.zero_stage <= 0:
             return
+        flat_ids = {id(sl.param) for f in getattr(self, "_flat", []) for sl in f.slots}
         for p in self._all_params():
+            if id(p) in flat_ids:
+                continue          # sharded inside the flat optimizer state
             if not isinstance(p, GT.GlobalTensor):
                 continue
             if p.numel() < self.config.zero_shard_min_size:
@@ -370,6 +486,34 @@ class Graph:
             if tuple(nd) != p.sbp:
                 new = GT.rebox(p.detach(), nd)
                 p._local, p._nd_sbp = new._local, new._nd_sbp
+
+    def _build_flat_optimizers(self):
+        """Optimizer generation at compile time: Adam / AdamW / SGD whose parameters are bf16 CUDA tensors (or any
+        parameters with ``config.enable_multi_tensor_update``) run as flat fused buffers (nn/graph/flat_optim.py); their
+        ZeRO sharding happens inside that state, over the data-parallel axis found at the first step."""
+        from ...optim import optimizer as O
+        from .flat_optim import FlatOptimizer
+        self._flat = []
+        for o in self._opts:
+            opt = o["optim"]
+            o["flat"] = None
+            if not isinstance(opt, (O._AdamFamily, O.SGD)) or o["is_sparse"]:
+                continue
+            if any(g.get("amsgrad") for g in opt.param_groups):
+                continue
+            ps = [p for g in opt.param_groups for p in g["params"] if p.requires_grad]
+            locs = [p._local if isinstance(p, GT.GlobalTensor) else p for p in ps]
+            locs = [t for t in locs if t is not None and t.numel()]
+            if not locs:
+                continue
+            auto = all(t.is_cuda and t.dtype == torch.bfloat16 for t in locs)
+            if not (auto or self.config.multi_tensor_update):
+                continue
+            if len({(t.device, t.dtype) for t in locs}) != 1 or not locs[0].dtype.is_floating_point:
+                continue
+            f = FlatOptimizer(opt, zero_stage=self.config.zero_stage)
+            o["flat"] = f
+            self._flat.append(f)
 
     def _apply_auto_parallel(self, args):
         """``config.enable_auto_parallel``: the Linear layers whose weights are still fully broadcast on a 1-D placement
@@ -459,6 +603,7 @@ class Graph:
         if shared is not None and getattr(shared, "_auto_parallel_choices", None) is not None and not self.config.auto_parallel:
             self._auto_parallel_choices = list(shared._auto_parallel_choices)
         self._apply_auto_parallel(args)
+        self._build_flat_optimizers()
         self._apply_zero()
         self._compiled = True
         if self._pending_state is not None:
@@ -520,8 +665,11 @@ class Graph:
 
     @contextlib.contextmanager
     def _backward_scaling(self, factor_fn):
-        """Inside build(), ``loss.backward()`` applies the gradient-accumulation average and the loss scale."""
+        """Inside build(), ``loss.backward()`` applies the gradient-accumulation average and the loss scale. While a
+        pipeline schedule runs, the call is recorded instead and executed when the schedule reaches that micro-batch's
+        backward slot."""
         orig = torch.Tensor.backward
+        graph = self
 
         def backward(t, gradient=None, *a, **k):
             f = factor_fn()
@@ -532,20 +680,70 @@ class Graph:
                     gradient = torch.ones_like(t) * f
                 else:
                     gradient = gradient * f
+            pending = graph.__dict__.get("_pending_backward")
+            if pending is not None:
+                pending.append((t, gradient, a, k))
+                return None
             return orig(t, gradient, *a, **k)
         torch.Tensor.backward = backward
+        self.__dict__["_orig_backward"] = orig
         try:
             yield
         finally:
             torch.Tensor.backward = orig
 
+    # ------------------------------------------------------------------ plan
+    def _stage_layout(self):
+        """(number of pipeline stages, this rank's stage index or None, stage placements): stages are the distinct
+        ``set_stage`` placements in stage-id order. A rank that belongs to several stages (or to none) gets no
+        pipeline schedule: its micro-batches run one after the other."""
+        stages = {}
+        for proxy in self._blocks.values():
+            for p in proxy._walk():
+                gm = p._gm
+                if gm.stage_placement is not None:
+                    stages.setdefault(gm.stage_id if gm.stage_id is not None else len(stages), gm.stage_placement)
+        if len(stages) < 2:
+            return 1, 0, []
+        order = [stages[k] for k in sorted(stages)]
+        me = GT._rank()
+        mine = [i for i, pl in enumerate(order) if pl.contains(me)]
+        return len(order), (mine[0] if len(mine) == 1 else None), order
+
+    def _record_plan(self, trace):
+        """The per-rank execution plan built from the first call: pipeline stages with their blocks, the fused
+        products and boxing steps each micro-batch issues here (in order), the flat optimizer buffers. It is what
+        ``runtime_state_dict`` carries and what ``debug`` / ``repr`` print; the stage table also drives the schedule."""
+        n_stages, my_stage, order = self._stage_layout()
+        blocks = []
+        for name, proxy in self._blocks.items():
+            for p in proxy._walk():
+                gm = p._gm
+                if gm.stage_id is not None or gm.activation_checkpointing:
+                    blocks.append({"block": p._name, "stage_id": gm.stage_id,
+                                   "placement": None if gm.stage_placement is None else list(gm.stage_placement.ranks_flat),
+                                   "activation_checkpointing": gm.activation_checkpointing,
+                                   "runs_here": gm.stage_placement is None or gm.stage_placement.contains(GT._rank())})
+        ops = [{"op": n, **d} for n, d in (trace or [])]
+        flat = [{"optimizer": type(f.optim).__name__, "elements": f.total, "dtype": str(getattr(f, "dtype", None)),
+                 "zero_stage": f.zero_stage} for f in self._flat]
+        self._plan = {"rank": GT._rank(), "stages": n_stages, "stage_of_rank": my_stage,
+                      "schedule": "1F1B" if (n_stages > 1 and my_stage is not None) else "sequential",
+                      "micro_batches": self.config.grad_acc_steps if self.config.training else 1,
+                      "blocks": blocks, "fused_ops_per_micro_batch": ops, "flat_optimizers": flat}
+        return self._plan
+
+    # ------------------------------------------------------------------ run
     def _run(self, args, kwargs):
         cfg = self.config
         n = cfg.grad_acc_steps if cfg.training else 1
         micro_args = _unpack(args, n)
         scaler = self._grad_scaler
         loss_scale = float(scaler.get_scale()) if scaler is not None and hasattr(scaler, "get_scale") else 1.0
-        outs = []
+        outs = [None] * n
+        first_call = self.__dict__.get("_plan") is None
+        from ...framework import fused_ops
+        trace = [] if first_call else None
         Graph._nesting += 1
         try:
             ctx = contextlib.nullcontext()
@@ -553,38 +751,96 @@ class Graph:
                 dev = "cuda" if any(isinstance(a, torch.Tensor) and a.device.type == "cuda" for a in args) else "cpu"
                 ctx = torch.autocast(dev, dtype=cfg.amp_dtype if dev == "cuda" or cfg.amp_dtype == torch.bfloat16 else torch.bfloat16)
             grad_ctx = contextlib.nullcontext() if cfg.training else torch.no_grad()
+            n_stages, my_stage, _ = self._stage_layout()
+            pipelined = cfg.training and n_stages > 1 and my_stage is not None and n > 1
             with ctx, grad_ctx, self._backward_scaling(lambda: loss_scale / n):
-                for m in range(n):
-                    outs.append(self.build(*micro_args[m], **kwargs))
+                if not pipelined:
+                    for m in range(n):
+                        fused_ops.op_trace = trace if m == 0 else None
+                        outs[m] = self.build(*micro_args[m], **kwargs)
+                else:
+                    self._run_1f1b(micro_args, kwargs, outs, n_stages, my_stage, trace)
         finally:
             Graph._nesting -= 1
+            fused_ops.op_trace = None
+            self.__dict__["_pending_backward"] = None
         if cfg.training:
             self._optimizer_step(loss_scale)
+        if first_call:
+            self._record_plan(trace)
         return _pack(outs)
+
+    def _run_1f1b(self, micro_args, kwargs, outs, n_stages, my_stage, trace):
+        """One-forward-one-backward order over the micro-batches for this rank's stage (reference: the stage buffers
+        of pipeline_buffer_pass.cpp:44-110 let stage s run ``n_stages - s - 1`` forwards ahead of its backwards).
+        ``build`` runs once per micro-batch; its ``backward()`` call is held back until the schedule's backward slot.
+        Activations and their gradients cross stages inside the stage-boundary ``to_global`` (asynchronous sends on
+        the p2p communicator's own stream, the compute stream only waits for what it receives)."""
+        from ...framework import fused_ops
+        n = len(micro_args)
+        orig = self.__dict__["_orig_backward"]
+        warm = min(n_stages - my_stage - 1, n)
+        queue = []
+
+        def fwd(m):
+            self.__dict__["_pending_backward"] = pend = []
+            fused_ops.op_trace = trace if m == 0 else None
+            outs[m] = self.build(*micro_args[m], **kwargs)
+            fused_ops.op_trace = None
+            self.__dict__["_pending_backward"] = None
+            queue.append(pend)
+
+        def bwd():
+            for t, gradient, a, k in queue.pop(0):
+                orig(t, gradient, *a, **k)
+        for m in range(warm):
+            fwd(m)
+        for m in range(warm, n):
+            fwd(m)
+            bwd()
+        while queue:
+            bwd()
 
     def _optimizer_step(self, loss_scale):
         scaler = self._grad_scaler
         found_inf = False
-        params = self._all_params()
+        dynamic = scaler is not None and getattr(scaler, "dynamic", False)
+        flat_ids = set()
+        for f in self._flat:
+            flat_ids.update(id(s.param) for s in f.slots)
+        params = [p for p in self._all_params() if id(p) not in flat_ids]
         if loss_scale != 1.0:
             inv = 1.0 / loss_scale
             for p in params:
                 if p.grad is not None:
                     p.grad.mul_(inv)
-        if scaler is not None and getattr(scaler, "dynamic", False):
-            bad = torch.zeros((), dtype=torch.float32)
-            for p in params:
-                if p.grad is not None:
-                    g = p.grad._local if isinstance(p.grad, GT.GlobalTensor) else p.grad
-                    if g.numel():
-                        bad = bad + (~torch.isfinite(g)).any().float().cpu()
+        if dynamic:
+            # one not-finite count over every local gradient, one read
+            grads = [(p.grad._local if isinstance(p.grad, GT.GlobalTensor) else p.grad) for p in params if p.grad is not None]
+            grads = [g.reshape(-1) for g in grads if g is not None and g.numel()]
+            grads += [f.grad for f in self._flat if f.total]
+            bad = torch.zeros((), dtype=torch.float32, device=grads[0].device if grads else "cpu")
+            if grads:
+                dev_groups = {}
+                for g in grads:
+                    dev_groups.setdefault((g.device, g.dtype), []).append(g)
+                for (_dev, _dt), gs in dev_groups.items():
+                    if gs[0].is_cuda and gs[0].dtype in (torch.float32, torch.bfloat16):
+                        from ...ops import kernels as K
+                        bad = bad + K.multi_tensor_sqsum(gs)[1].to(bad.device)
+                    else:
+                        bad = bad + sum((~torch.isfinite(g)).sum() for g in gs).to(bad.device, torch.float32)
             if dist.is_initialized():
                 dist.all_reduce(bad)
             found_inf = bool(bad.item() > 0)
             scaler.update(found_inf)
         if not found_inf:
+            for f in self._flat:
+                f.step(loss_scale)
             for o in self._opts:
                 opt = o["optim"]
+                if o.get("flat") is not None:
+                    continue
                 if hasattr(opt, "clip_grad"):
                     opt.clip_grad()
                 scaled = [(g, g["lr"]) for g in opt.param_groups if g.get("lr_scale", 1.0) != 1.0]
@@ -597,8 +853,11 @@ class Graph:
                         g["lr"] = lr
         if os.getenv("ONEFLOW_DEBUG_MODE"):
             self._log_step_lr()
+        for f in self._flat:
+            f.zero_grad()
         for o in self._opts:
-            o["optim"].zero_grad(set_to_none=True)
+            if o.get("flat") is None:
+                o["optim"].zero_grad(set_to_none=True)
             if o["lr_sch"] is not None and not found_inf:
                 o["lr_sch"].step()
         self._train_step += 1
@@ -637,7 +896,17 @@ def _unpack(args, n):
         if isinstance(a, torch.Tensor) and a.dim() > 0:
             if a.shape[0] % n:
                 raise ValueError(f"batch dimension {a.shape[0]} is not divisible by the {n} gradient accumulation steps")
-            if isinstance(a, GT.GlobalTensor):
+            if isinstance(a, GT.GlobalTensor) and all(sb.kind == "B" or (sb.kind == "S" and sb.axis == 0) for sb in a.sbp) and \
+                    (not a.placement.contains(GT._rank()) or a._local.shape[0] % n == 0):
+                # every rank cuts its own shard: no traffic (with a split batch axis a micro-batch is then a strided
+                # selection of the global batch, which training does not care about)
+                m = a.shape[0] // n
+                shape = (m,) + tuple(a.shape[1:])
+                if a.placement.contains(GT._rank()):
+                    pieces = [GT.wrap(c, shape, a.placement, a.sbp) for c in a._local.chunk(n, 0)]
+                else:
+                    pieces = [GT.wrap(a._local, shape, a.placement, a.sbp) for _ in range(n)]
+            elif isinstance(a, GT.GlobalTensor):
                 m = a.shape[0] // n
                 pieces = [a[i * m:(i + 1) * m] for i in range(n)]
                 # keep the original layout for every micro-batch
