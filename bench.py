@@ -7,11 +7,17 @@ gradient accumulation over micro-batches of 4.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
 
+The default arm trains the GPT of oneflow_b200/models/gpt_flow.py: flow.nn modules on global tensors with SBP
+annotations, driven by an nn.Graph whose pipeline stages are declared with set_stage (TP4 x PP2 at 8 GPUs), gradient
+accumulation and flow.optim.AdamW. `--impl engine` runs the same network on the hand-scheduled stage engine
+(oneflow_b200/parallel) for comparison; `--impl torch_proxy` runs it in stock PyTorch (cuBLAS, flash_attn, NCCL with
+Megatron-style tensor / pipeline parallelism, fused torch.optim.AdamW) as the stand-in baseline, since
+`--impl reference` can only report why the reference framework cannot be built here.
+
 Rank 0 prints ONE JSON line. `value` is timed on the device (CUDA events, max over ranks) with the
-batch already resident; `e2e` repeats the measurement through the public trainer API including the
+batch already resident; `e2e` repeats the measurement through the public API including the
 per-step host->device copy of the token batch from pinned memory and the device->host read of the loss.
-`--impl reference` reports why the reference framework cannot run here.
-Other workloads of the same engine: --workload bert | gpt-small (smaller configs for quick checks).
+Other workloads: --workload bert-large | gpt-small | resnet50 | dlrm.
 """
 from __future__ import annotations
 
@@ -33,7 +39,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "engine", "torch_proxy", "reference"])
     ap.add_argument("--workload", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "bert-large", "dlrm", "dlrm-tiny", "resnet50", "resnet-tiny"])
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--global-batch", type=int, default=64)
@@ -321,7 +327,6 @@ def main():
     from oneflow_b200.models import gpt as gpt_mod
     from oneflow_b200.ops import _native
     from oneflow_b200.ops import kernels as K
-    from oneflow_b200.parallel.setup import build_gpt_trainer
 
     if args.workload == "gpt-6.7b":
         cfg = gpt_mod.GPT_6_7B
@@ -346,11 +351,37 @@ def main():
     if is_bert:
         args.global_batch = args.micro_batch * dp
     n_micro = args.global_batch // (args.micro_batch * dp)
-    stage_kw = {}
-    if is_bert:
-        stage_kw["stage_cls"] = bert_mod.BertStage
-    trainer = build_gpt_trainer(cfg, tp=tp, pp=pp, dp=dp, micro_batch=args.micro_batch, n_micro=n_micro,
-                                device=device, lr=1e-4, zero_stage=1, **stage_kw)
+    impl = args.impl
+    if is_bert and impl == "ours":
+        impl = "engine"            # BERT runs on the stage engine
+    has_loss = True
+    if impl == "engine":
+        from oneflow_b200.parallel.setup import build_gpt_trainer
+        stage_kw = {}
+        if is_bert:
+            stage_kw["stage_cls"] = bert_mod.BertStage
+        trainer = build_gpt_trainer(cfg, tp=tp, pp=pp, dp=dp, micro_batch=args.micro_batch, n_micro=n_micro,
+                                    device=device, lr=1e-4, zero_stage=1, **stage_kw)
+        has_loss = trainer.has_loss
+        train_step = trainer.train_step
+        api = "parallel.setup.build_gpt_trainer (stage engine)"
+    elif impl == "torch_proxy":
+        from oneflow_b200.models import torch_proxy
+        proxy = torch_proxy.GPTProxy(cfg, tp=tp, pp=pp, dp=dp, micro_batch=args.micro_batch, n_micro=n_micro, device=device, lr=1e-4)
+        has_loss = proxy.has_loss
+        train_step = proxy.train_step
+        api = "stock PyTorch: cuBLAS + flash_attn + NCCL TP/PP + fused torch.optim.AdamW"
+    else:
+        from oneflow_b200.models import gpt_flow
+        graph, model, layout = gpt_flow.build_gpt_graph(cfg, tp=tp, pp=pp, dp=dp, grad_acc=n_micro, device_type="cuda",
+                                                       lr=1e-4, weight_decay=0.1, clip_grad=1.0, zero_stage=1)
+        has_loss = layout.stages[-1].contains(rank)
+
+        def train_step(tokens):
+            x, y = gpt_flow.make_inputs(layout, tokens)
+            loss = graph(x, y)                              # one value per micro-batch, on the last stage
+            return loss.to_local().float().mean() if has_loss else torch.zeros((), device=device)
+        api = "flow.nn modules + global tensors + nn.Graph(set_stage, gradient accumulation) + flow.optim.AdamW"
     local_batch = args.micro_batch * n_micro
     seq = cfg.seq_len
     gen = torch.Generator().manual_seed(1234 + (rank // (tp * pp)))
@@ -366,7 +397,7 @@ def main():
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        loss = trainer.train_step(dev_tokens)
+        loss = train_step(dev_tokens)
     barrier()
     if _native.read_status() != (0, 0):
         raise SystemExit("a kernel reported a bounded-wait failure during warm-up")
@@ -380,13 +411,19 @@ def main():
     barrier()
     e0.record()
     for _ in range(args.steps):
-        loss = trainer.train_step(dev_tokens)
+        loss = train_step(dev_tokens)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
     launches = K.launch_count - launches0
     clocks = sampler.stop() if rank == 0 else None
-    final_loss = float(loss.item()) if trainer.has_loss else float("nan")
+    # the loss lives on the last pipeline stage: the largest rank holds it and tells the others over the host path
+    lt = torch.tensor([float(loss.item()) if has_loss else float("-inf")], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    final_loss = float(lt.item())
+    if not (final_loss == final_loss and abs(final_loss) < 1e4):
+        raise SystemExit(f"the training loss is not finite: {final_loss}")
 
     # ---------------- end-to-end region through the public trainer API
     barrier()
@@ -397,7 +434,7 @@ def main():
     d2h_bytes = 0
     for _ in range(args.steps):
         batch = host_tokens.to(device, non_blocking=True)      # H2D from pinned memory, every step
-        loss = trainer.train_step(batch)
+        loss = train_step(batch)
         host_loss = loss.to("cpu")                               # D2H read of the step's result
         d2h_bytes = host_loss.numel() * host_loss.element_size()
     t1.record()
@@ -425,12 +462,14 @@ def main():
                        "ffn": cfg.ffn, "vocab": cfg.vocab_size, "global_batch": args.global_batch, "seq_len": seq,
                        "micro_batch": args.micro_batch, "grad_accum_steps": n_micro,
                        "parallelism": f"tp{tp}xpp{pp}xdp{dp}", "optimizer": "AdamW fp32 master, ZeRO-1 over dp",
+                       "api": api,
                        "l2": "working set (13 GB of bf16 weights + activations per step) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": host_tokens.numel() * host_tokens.element_size(),
                     "d2h_bytes_per_step": d2h_bytes},
-            "gpu_launches": launches,
+            "impl": args.impl,
+            "gpu_launches": launches if impl != "torch_proxy" else 0,
             "model_tflops_per_gpu": flops * args.steps / (ms / 1e3) / 1e12 / world,
             "final_loss": final_loss,
             "kernel_status": list(status),

@@ -55,6 +55,11 @@ struct GemmCommParams {
   long long k_cols;                   // K (row length of the gathered matrix)
   unsigned int pull_target;           // cumulative arrival count expected on the per-peer pull counters
   int pull_slot;                      // first local counter slot of the per-peer pull counters
+  // Element offset of the parity-1 half of the staging / gathered buffers. It is a property of the buffer (half of
+  // its capacity), not of the current problem: consecutive calls with different shapes then never place one call's
+  // parity-1 data over the parity-0 data of the previous call that a slow peer may still be reading.
+  long long parity_stride;
+  int tune;                           // OFB_GEMM_COMM_TUNE bit mask, experiments only (0 in normal use)
 };
 
 template <int BN>
@@ -241,18 +246,19 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // The raw partial tile goes to the slab this rank owns in the staging buffer of the rows' owner (plain P2P
         // stores over NVLink, full 64-byte row segments); the owner adds it in the epilogue of its own tile.
         GemmEpilogue pe;
-        pe.C = cp.stage[owner] + (static_cast<long long>(parity) * cp.n + cp.rank) * cp.rows_per_rank * shp.N;
+        pe.C = cp.stage[owner] + parity * cp.parity_stride + static_cast<long long>(cp.rank) * cp.rows_per_rank * shp.N;
         pe.ldc = shp.N;
         pe.bias = nullptr; pe.residual = nullptr; pe.aux_in = nullptr; pe.aux_out = nullptr;
         pe.ldr = 0; pe.ld_aux = 0;
         pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
         GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
-        gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false, c_begin, c_end);
+        if (!(cp.tune & 1))
+          gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false, c_begin, c_end);
       } else if (MODE == MODE_RS) {
         // Own rows: wait (bounded) until every peer's partial of this tile quadrant has landed in the local staging
         // buffer, then finish the reduction here: out = alpha * acc + sum of the peers' partials + bias + residual.
         int ok_w = 1;
-        if (lane == 0) {
+        if (lane == 0 && !(cp.tune & 4)) {
           for (int s = 0; s < cp.n && ok_w; ++s) {
             if (s == cp.rank) continue;
             const unsigned int* f =
@@ -263,7 +269,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
         if (!ok_w) { *abort_flag = 1; break; }
         const int lrow0 = m0 - owner * cp.rows_per_rank + quad * 32;
-        const __nv_bfloat16* my_stage = cp.stage[cp.rank] + static_cast<long long>(parity) * cp.n * cp.rows_per_rank * shp.N;
+        const __nv_bfloat16* my_stage = cp.stage[cp.rank] + parity * cp.parity_stride;
         const int rows_valid = cp.rows_per_rank - lrow0;
         GemmEpilogue pe;
         pe.C = cp.out; pe.ldc = cp.ldc;
@@ -278,7 +284,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // the peers' partials and the residual shard, summed in fp32 with all their loads in flight together
           float h[32];
           epi_load_sum_bf16(stage_sm, lane, my_stage + static_cast<long long>(lrow0) * shp.N + col0,
-                            static_cast<long long>(cp.rows_per_rank) * shp.N, cp.n, cp.rank, shp.N,
+                            static_cast<long long>(cp.rows_per_rank) * shp.N, (cp.tune & 8) ? 0 : cp.n, cp.rank, shp.N,
                             cp.residual ? cp.residual + static_cast<long long>(lrow0) * cp.ldr + col0 : nullptr, cp.ldr, rows_valid, cols_valid, h);
           uint32_t r[32];
           __syncwarp();
@@ -292,7 +298,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
       }
       tc_fence_before();
-      if (MODE == MODE_RS && remote_path) __threadfence_system();
+      if (MODE == MODE_RS && remote_path && !(cp.tune & 2)) __threadfence_system();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tempty[acc]);
@@ -312,8 +318,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
     const long long v0 = per_cta * blockIdx.x;
     const long long v1 = min(shard_vecs, v0 + per_cta);
-    const long long buf_elems = static_cast<long long>(shp.M) * cp.k_cols;
-    __nv_bfloat16* my_gathered = cp.gathered[cp.rank] + parity * buf_elems;
+    __nv_bfloat16* my_gathered = cp.gathered[cp.rank] + parity * cp.parity_stride;
     bool ok = true;
     // 1. publish the local shard: peers must have finished pulling what this parity held two calls ago
     if (ct == 0 && cp.epoch > 2) {
@@ -344,7 +349,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (ct == 0) ok_shared = okw;
       asm volatile("bar.sync 1, 64;" ::: "memory");
       if (!ok_shared) { *abort_flag = 1; break; }
-      const uint4* src = reinterpret_cast<const uint4*>(cp.gathered[o] + parity * buf_elems +
+      const uint4* src = reinterpret_cast<const uint4*>(cp.gathered[o] + parity * cp.parity_stride +
                                                         static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
       uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
       long long i = v0 + ct;
@@ -425,8 +430,8 @@ OFB_API int ofb_gemm_comm_grid(int* out) {
 //   stage_off / flag_off: byte offsets of the staging and flag regions inside every rank's arena.
 OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, const void* b, long long ldb, int b_mn_major,
                         void* out, long long ldc, const void* bias, const void* residual, long long ldr, int T, int N, int K,
-                        float alpha, long long stage_off, long long flag_off, int flag_stride, unsigned int epoch,
-                        int done_slot, void* stream) {
+                        float alpha, long long stage_off, long long stage_bytes, long long flag_off, int flag_stride,
+                        unsigned int epoch, int done_slot, void* stream) {
   const int n = ctx->n;
   if (n < 1 || n > kMaxPeers) return fail("gemm_rs: group size must be 1..8");
   if (T % (n * 128)) return fail("gemm_rs: rows must be a multiple of 128 * group size");
@@ -434,6 +439,7 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
   const int bn = 256;
   const int tiles_local = (T / n / 128) * ((N + bn - 1) / bn);
   if (8 * tiles_local > flag_stride) return fail("gemm_rs: flag region too small for this problem");
+  if (2ll * T * N * 2 > stage_bytes) return fail("gemm_rs: staging region too small for this problem");
   CUtensorMap tmA, tmB;
   if (get_tensor_map(&tmA, a, 2, 2, K, T, 0, (uint64_t)lda * 2, 0, 64, 128, 0, 3)) return -1;
   if (!b_mn_major) {
@@ -460,6 +466,8 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
   cp.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   cp.residual = reinterpret_cast<const __nv_bfloat16*>(residual); cp.ldr = ldr;
   cp.done_slot = done_slot; cp.done_target = epoch * static_cast<unsigned int>(grid);
+  cp.parity_stride = stage_bytes / 4;  // half of the region, in bf16 elements
+  if (const char* e = std::getenv("OFB_GEMM_COMM_TUNE")) cp.tune = std::atoi(e);
   auto s = reinterpret_cast<cudaStream_t>(stream);
   return b_mn_major ? launch_gemm_comm<256, 1, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s)
                     : launch_gemm_comm<256, 0, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s);
@@ -469,7 +477,8 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
 // this rank's gathered buffer (parity = epoch & 1) for later kernels (weight gradients).
 OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* b, long long ldb, int b_mn_major, void* out,
                         long long ldc, const void* bias, const void* aux_in, void* aux_out, long long ld_aux, int act, int T,
-                        int N, int K, float alpha, long long gathered_off, unsigned int epoch, int pull_slot, void* stream) {
+                        int N, int K, float alpha, long long gathered_off, long long gathered_bytes, unsigned int epoch,
+                        int pull_slot, void* stream) {
   const int n = ctx->n;
   if (n < 1 || n > kMaxPeers) return fail("ag_gemm: group size must be 1..8");
   if (T % (n * 128)) return fail("ag_gemm: rows must be a multiple of 128 * group size");
@@ -477,9 +486,10 @@ OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* 
   const int bn = 256;
   int grid = 0;
   if (ofb_gemm_comm_grid(&grid)) return -1;
-  const long long buf_elems = static_cast<long long>(T) * K;
+  if (2ll * T * K * 2 > gathered_bytes) return fail("ag_gemm: gathered region too small for this problem");
+  const long long parity_stride = gathered_bytes / 4;  // half of the region, in bf16 elements
   auto* my_g = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ctx->arena[ctx->rank]) + gathered_off) +
-               (epoch & 1) * buf_elems;
+               (epoch & 1) * parity_stride;
   CUtensorMap tmA, tmAl, tmB;
   if (get_tensor_map(&tmA, my_g, 2, 2, K, T, 0, (uint64_t)K * 2, 0, 64, 128, 0, 3)) return -1;
   if (get_tensor_map(&tmAl, x_local, 2, 2, K, T / n, 0, (uint64_t)K * 2, 0, 64, 128, 0, 3)) return -1;
@@ -507,6 +517,7 @@ OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* 
   cp.k_cols = K;
   cp.pull_slot = pull_slot;
   cp.pull_target = epoch * static_cast<unsigned int>(grid);
+  cp.parity_stride = parity_stride;
   auto s = reinterpret_cast<cudaStream_t>(stream);
   return b_mn_major ? launch_gemm_comm<256, 1, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s)
                     : launch_gemm_comm<256, 0, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s);

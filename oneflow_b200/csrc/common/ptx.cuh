@@ -84,14 +84,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory; once any role of the CTA has
 // given up, everybody else leaves its wait at the next poll.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long timeout_ns = OFB_MBAR_TIMEOUT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > OFB_MBAR_TIMEOUT_NS) {
+      if (global_timer_ns() - t0 > timeout_ns) {
         *abort_flag = 1;
         return false;
       }

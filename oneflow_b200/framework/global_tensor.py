@@ -806,6 +806,206 @@ def conv_bwd_rule(func, args, kwargs):
                    [tuple(nd), param_nd, param_nd])
 
 
+# ------------------------------------------------------------------------------------------------ dimension-preserving ops
+def _keep_splits(func, args, kwargs, x_pos, blocked, like_pos=(), out_dim_map=None, n_out=1, partial_ok=False):
+    """Signature family "a split passes through unless it is on a dimension the op works along": the tensors at
+    ``x_pos`` (same rank, aligned dims) keep every split whose dimension is not in ``blocked`` and are broadcast on the
+    other mesh axes; ``like_pos`` tensors are broadcast. ``out_dim_map(d)`` gives the output dimension of input dimension
+    d (None: identity). The reference declares these per op (e.g. concat: oneflow/user/ops/concat_op.cpp, slice:
+    slice_op.cpp, pooling: max_pool_op.cpp, dropout: dropout_op.cpp, normalization: normalization_op.cpp)."""
+    flat = list(args)
+    xs = [flat[i] for i in x_pos]
+    tensors = []
+    for x in xs:
+        tensors += list(x) if isinstance(x, (list, tuple)) else [x]
+    gs = [t for t in tensors if isinstance(t, GlobalTensor)]
+    pl = _common_placement(gs + [flat[i] for i in like_pos if i < len(flat) and isinstance(flat[i], GlobalTensor)])
+    ref = gs[0]
+    nd_in, nd_out = [], []
+    for axis in range(pl.ndim):
+        kinds = [g._nd_sbp[axis] for g in gs]
+        s0 = kinds[0]
+        same = all(k == s0 for k in kinds)
+        if same and s0.kind == "S" and (s0.axis % max(ref.dim(), 1)) not in blocked:
+            nd_in.append(s0)
+            d = s0.axis if out_dim_map is None else out_dim_map(s0.axis)
+            nd_out.append(S.split(d))
+        elif same and s0.kind == "P" and partial_ok:
+            nd_in.append(P)
+            nd_out.append(P)
+        else:
+            nd_in.append(B)
+            nd_out.append(B)
+    mapping = {id(g): rebox(g, nd_in) for g in gs}
+    allb = (B,) * pl.ndim
+    for i in like_pos:
+        if i < len(flat) and isinstance(flat[i], GlobalTensor):
+            mapping[id(flat[i])] = rebox(flat[i], allb)
+    a2, k2 = _replace(args, kwargs, mapping)
+    return _finish(func, a2, k2, pl, [tuple(nd_out)] * n_out if n_out > 1 else [tuple(nd_out)])
+
+
+@rule(aten.select.int)
+def select_rule(func, args, kwargs):
+    x, dim = args[0], args[1] % args[0].dim()
+    return _keep_splits(func, args, kwargs, (0,), {dim}, out_dim_map=lambda d: d - 1 if d > dim else d, partial_ok=True)
+
+
+@rule(aten.slice.Tensor)
+def slice_rule(func, args, kwargs):
+    x = args[0]
+    dim = (args[1] if len(args) > 1 else 0) % max(x.dim(), 1)
+    start = args[2] if len(args) > 2 and args[2] is not None else 0
+    end = args[3] if len(args) > 3 and args[3] is not None else x.shape[dim]
+    step = args[4] if len(args) > 4 else 1
+    whole = start == 0 and end >= x.shape[dim] and step == 1
+    return _keep_splits(func, args, kwargs, (0,), set() if whole else {dim}, partial_ok=True)
+
+
+@rule(aten.narrow.default)
+def narrow_rule(func, args, kwargs):
+    x, dim = args[0], args[1] % args[0].dim()
+    return _keep_splits(func, args, kwargs, (0,), {dim}, partial_ok=True)
+
+
+@rule(aten.cat.default)
+def cat_rule(func, args, kwargs):
+    ts = args[0]
+    dim = (args[1] if len(args) > 1 else kwargs.get("dim", 0)) % max(ts[0].dim(), 1)
+    if not all(isinstance(t, GlobalTensor) and t.dim() == ts[0].dim() for t in ts):
+        return fallback_all_broadcast(func, args, kwargs)
+    return _keep_splits(func, args, kwargs, (0,), {dim}, partial_ok=True)
+
+
+@rule(aten.stack.default)
+def stack_rule(func, args, kwargs):
+    ts = args[0]
+    if not all(isinstance(t, GlobalTensor) for t in ts):
+        return fallback_all_broadcast(func, args, kwargs)
+    dim = (args[1] if len(args) > 1 else kwargs.get("dim", 0)) % (ts[0].dim() + 1)
+    return _keep_splits(func, args, kwargs, (0,), set(), out_dim_map=lambda d: d + 1 if d >= dim else d, partial_ok=True)
+
+
+@rule(aten.split.Tensor, aten.split_with_sizes.default, aten.unsafe_split.Tensor, aten.unsafe_split_with_sizes.default)
+def split_rule(func, args, kwargs):
+    x = args[0]
+    dim = (args[2] if len(args) > 2 else kwargs.get("dim", 0)) % max(x.dim(), 1)
+    return _keep_splits(func, args, kwargs, (0,), {dim}, partial_ok=True)
+
+
+@rule(aten.unbind.int)
+def unbind_rule(func, args, kwargs):
+    x = args[0]
+    dim = (args[1] if len(args) > 1 else 0) % max(x.dim(), 1)
+    return _keep_splits(func, args, kwargs, (0,), {dim}, out_dim_map=lambda d: d - 1 if d > dim else d, partial_ok=True)
+
+
+@rule(aten.index_select.default)
+def index_select_rule(func, args, kwargs):
+    dim = args[1] % max(args[0].dim(), 1)
+    return _keep_splits(func, args, kwargs, (0,), {dim}, like_pos=(2,), partial_ok=True)
+
+
+@rule(aten.gather.default)
+def gather_rule(func, args, kwargs):
+    # input and index have the same rank and are walked together on every dimension but `dim`
+    dim = args[1] % max(args[0].dim(), 1)
+    return _keep_splits(func, args, kwargs, (0, 2), {dim})
+
+
+@rule(aten.native_dropout.default)
+def dropout_rule(func, args, kwargs):
+    # every shard draws its own mask: any split passes through, a partial sum has to be completed first
+    return _keep_splits(func, args, kwargs, (0,), set(), n_out=2)
+
+
+@rule(aten.native_dropout_backward.default)
+def dropout_bwd_rule(func, args, kwargs):
+    return _keep_splits(func, args, kwargs, (0, 1), set())
+
+
+@rule(aten.max_pool2d_with_indices.default, aten.max_pool3d_with_indices.default)
+def max_pool_rule(func, args, kwargs):
+    x = args[0]
+    spatial = set(range(x.dim() - (2 if "2d" in func._schema.name else 3), x.dim()))
+    return _keep_splits(func, args, kwargs, (0,), spatial, n_out=2)
+
+
+@rule(aten.max_pool2d_with_indices_backward.default, aten.max_pool3d_with_indices_backward.default)
+def max_pool_bwd_rule(func, args, kwargs):
+    x = args[1]
+    spatial = set(range(x.dim() - (2 if "2d" in func._schema.name else 3), x.dim()))
+    idx_pos = len(args) - 1
+    return _keep_splits(func, args, kwargs, (0, 1, idx_pos), spatial)
+
+
+@rule(aten.avg_pool2d.default, aten.avg_pool3d.default, aten._adaptive_avg_pool2d.default, aten._adaptive_avg_pool3d.default,
+      aten.upsample_nearest2d.default, aten.upsample_bilinear2d.default)
+def spatial_rule(func, args, kwargs):
+    x = args[0]
+    nsp = 3 if "3d" in func._schema.name else 2
+    return _keep_splits(func, args, kwargs, (0,), set(range(x.dim() - nsp, x.dim())))
+
+
+@rule(aten.avg_pool2d_backward.default, aten._adaptive_avg_pool2d_backward.default)
+def spatial_bwd_rule(func, args, kwargs):
+    x = args[1]
+    return _keep_splits(func, args, kwargs, (0, 1), set(range(x.dim() - 2, x.dim())))
+
+
+@rule(aten._native_batch_norm_legit.default, aten._native_batch_norm_legit_no_training.default, aten.native_batch_norm.default,
+      aten._native_batch_norm_legit_functional.default)
+def batch_norm_rule(func, args, kwargs):
+    """Inference keeps batch and spatial splits (the statistics are given). Training needs the statistics of the whole
+    batch: the input is gathered unless only the channel dimension is split (per-channel statistics are then local)."""
+    x = args[0]
+    name = func._schema.name
+    training = False if name.endswith("no_training") else bool(args[5])
+    pl = x._placement
+    allb = (B,) * pl.ndim
+    params = [a for a in args[1:5] if isinstance(a, GlobalTensor)]
+    nd = []
+    for s_ in x._nd_sbp:
+        if s_.kind == "S" and s_.axis != 1 and not training:
+            nd.append(s_)
+        else:
+            nd.append(B)
+    mapping = {id(x): rebox(x, nd)}
+    for p_ in params:
+        mapping[id(p_)] = rebox(p_, allb)
+    a2, k2 = _replace(args, kwargs, mapping)
+    meta = _infer_meta(func, args, kwargs)
+    n_t = len([m for m in pytree.tree_flatten(meta)[0] if isinstance(m, torch.Tensor)])
+    return _finish(func, a2, k2, pl, [tuple(nd)] + [allb] * (n_t - 1), meta_out=meta)
+
+
+@rule(aten._scaled_dot_product_flash_attention.default, aten._scaled_dot_product_efficient_attention.default,
+      aten._scaled_dot_product_flash_attention_for_cpu.default, aten._scaled_dot_product_cudnn_attention.default)
+def sdpa_rule(func, args, kwargs):
+    """[B, H, S, D] attention: batch and head splits are independent problems (the reference declares exactly these two,
+    oneflow/user/ops/scaled_dot_product_flash_attention_op.cpp:71-100); a sequence or feature split is gathered."""
+    q = args[0]
+    pl = q._placement
+    gs = [a for a in args[:3] if isinstance(a, GlobalTensor)]
+    nd = []
+    for axis in range(pl.ndim):
+        s0 = q._nd_sbp[axis]
+        ok = s0.kind == "S" and s0.axis in (0, 1) and all(g._nd_sbp[axis] == s0 for g in gs)
+        nd.append(s0 if ok else B)
+    mapping = {id(g): rebox(g, nd) for g in gs}
+    for a in list(args[3:]) + list(kwargs.values()):
+        if isinstance(a, GlobalTensor):
+            mapping[id(a)] = rebox(a, (B,) * pl.ndim)
+    a2, k2 = _replace(args, kwargs, mapping)
+    meta = _infer_meta(func, args, kwargs)
+    flat = [m for m in pytree.tree_flatten(meta)[0] if isinstance(m, torch.Tensor)]
+    out_nds = []
+    for m in flat:
+        # outputs that carry batch and head dimensions keep the split; scalars (rng state, offsets) are broadcast
+        out_nds.append(tuple(s_ if (s_.kind == "S" and m.dim() > s_.axis and m.shape[s_.axis] == q.shape[s_.axis]) else B for s_ in nd))
+    return _finish(func, a2, k2, pl, out_nds, meta_out=meta)
+
+
 @rule(aten.copy_.default)
 def copy_rule(func, args, kwargs):
     dst, src = args[0], args[1]

@@ -60,7 +60,7 @@ class TPContext:
             full = self.all_gather_rows(x_shard)
             res = G.gemm(full, w, b_layout=b_layout, bias=bias, act=act, aux_in=aux_in, want_aux=want_aux)
             return self._pack(res, full, want_aux, return_gathered)
-        if Kd > self.hidden_cap or T > self.max_tokens:
+        if 2 * T * Kd * 2 > self.gathered_bytes:
             raise ValueError("ag_gemm: problem larger than the gathered buffer")
         out = torch.empty((T, N), dtype=torch.bfloat16, device=x_shard.device)
         aux = torch.empty((T, N), dtype=torch.bfloat16, device=x_shard.device) if want_aux else None
@@ -70,11 +70,13 @@ class TPContext:
             ctypes.byref(self.arena.ctx), _native.ptr(x_shard), _native.ptr(w), c_longlong(w.stride(0)),
             c_int(0 if b_layout == "nk" else 1), _native.ptr(out), c_longlong(N), _native.ptr(bias), _native.ptr(aux_in),
             _native.ptr(aux), c_longlong(ld_aux), c_int(G._act_code(act)), c_int(T), c_int(N), c_int(Kd), c_float(1.0),
-            c_longlong(self.gathered_off), c_uint(self.ag_epoch), c_int(8), _native.stream_ptr()), "ag_gemm")
+            c_longlong(self.gathered_off), c_longlong(self.gathered_bytes), c_uint(self.ag_epoch), c_int(8),
+            _native.stream_ptr()), "ag_gemm")
         K._count()
         gathered = None
         if return_gathered:
-            gathered = self.arena.view(self.gathered_off + (self.ag_epoch & 1) * T * Kd * 2, (T, Kd), torch.bfloat16)
+            # parity halves sit at fixed offsets of the region, whatever the shape of the call
+            gathered = self.arena.view(self.gathered_off + (self.ag_epoch & 1) * (self.gathered_bytes // 2), (T, Kd), torch.bfloat16)
         res = (out, aux) if want_aux else out
         return self._pack(res, gathered, want_aux, return_gathered)
 
@@ -106,7 +108,8 @@ class TPContext:
             ctypes.byref(self.arena.ctx), _native.ptr(a), c_longlong(a.stride(0)), _native.ptr(w), c_longlong(w.stride(0)),
             c_int(0 if b_layout == "nk" else 1), _native.ptr(out), c_longlong(N), _native.ptr(bias), _native.ptr(residual),
             c_longlong(residual.stride(0) if residual is not None else 0), c_int(T), c_int(N), c_int(Kd), c_float(1.0),
-            c_longlong(self.stage_off), c_longlong(self.flag_off), c_int(self.flag_stride), c_uint(self.rs_epoch),
+            c_longlong(self.stage_off), c_longlong(self.stage_bytes), c_longlong(self.flag_off), c_int(self.flag_stride),
+            c_uint(self.rs_epoch),
             c_int(2), _native.stream_ptr()), "gemm_rs")
         K._count()
         return out

@@ -158,6 +158,42 @@ def global_ops(tmp):
     I = flow.tensor(idx, placement=P, sbp=B)
     e = torch.nn.functional.embedding(I, E)
     assert e.sbp == (Pm,) and np.allclose(e.numpy(), table[idx].numpy(), atol=1e-6)
+    # dimension-preserving ops keep a split that is not on the dimension they work along (no gather happens)
+    t4 = torch.randn(2 * world, 4, 6, 6, generator=g)
+    X = flow.tensor(t4, placement=P, sbp=S(0))
+    F = torch.nn.functional
+
+    def same(got, want, sbp):
+        assert got.sbp == (sbp,), (got.sbp, sbp)
+        assert np.allclose(got.numpy(), want.numpy(), atol=1e-5)
+    same(X[:, 1], t4[:, 1], S(0))                                   # select on another dimension
+    same(X[:, 1:3], t4[:, 1:3], S(0))                               # slice on another dimension
+    same(X.select(0, 1), t4.select(0, 1), B)                        # select on the split dimension: gathered
+    same(torch.cat([X, X * 2], 1), torch.cat([t4, t4 * 2], 1), S(0))
+    same(torch.stack([X, X + 1], 0), torch.stack([t4, t4 + 1], 0), S(1))
+    for got, want in zip(X.split(2, dim=1), t4.split(2, dim=1)):
+        same(got, want, S(0))
+    for got, want in zip(X.unbind(1), t4.unbind(1)):
+        same(got, want, S(0))
+    ii = torch.tensor([2, 0])
+    same(X.index_select(1, flow.tensor(ii, placement=P, sbp=B)), t4.index_select(1, ii), S(0))
+    same(F.max_pool2d(X, 2), F.max_pool2d(t4, 2), S(0))
+    same(F.avg_pool2d(X, 2), F.avg_pool2d(t4, 2), S(0))
+    same(F.adaptive_avg_pool2d(X, 1), F.adaptive_avg_pool2d(t4, 1), S(0))
+    same(F.dropout(X, 0.0, True), t4, S(0))
+    rm, rv = torch.zeros(4), torch.ones(4)
+    Bn = lambda t: flow.tensor(t, placement=P, sbp=B)  # noqa: E731
+    same(F.batch_norm(X, Bn(rm), Bn(rv), training=False), F.batch_norm(t4, rm, rv, training=False), S(0))
+    got = F.batch_norm(X, Bn(rm.clone()), Bn(rv.clone()), training=True)  # training: statistics of the whole batch
+    assert np.allclose(got.numpy(), F.batch_norm(t4, rm.clone(), rv.clone(), training=True).numpy(), atol=1e-5)
+    q = torch.randn(2 * world, 2, 5, 8, generator=g)
+    Q = flow.tensor(q, placement=P, sbp=S(0))
+    same(F.scaled_dot_product_attention(Q, Q, Q, is_causal=True), F.scaled_dot_product_attention(q, q, q, is_causal=True), S(0))
+    Xr = flow.tensor(t4, placement=P, sbp=S(0)).requires_grad_(True)
+    tr = t4.clone().requires_grad_(True)
+    (F.max_pool2d(torch.cat([Xr[:, :2], Xr[:, 2:] * 3], 1), 2).sum()).backward()
+    (F.max_pool2d(torch.cat([tr[:, :2], tr[:, 2:] * 3], 1), 2).sum()).backward()
+    assert np.allclose(Xr.grad.numpy(), tr.grad.numpy(), atol=1e-5)
     if rank == 0:
         print("GLOBAL OPS OK")
 
