@@ -32,7 +32,7 @@
 
 namespace {
 
-enum Op : uint32_t { kSet = 1, kGet = 2, kAdd = 3, kStamp = 4, kAges = 5 };
+enum Op : uint32_t { kSet = 1, kGet = 2, kAdd = 3, kStamp = 4, kAges = 5, kDel = 6, kCas = 7, kCount = 8, kHas = 9 };
 
 int64_t now_ms() {
   return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
@@ -89,7 +89,41 @@ struct Server {
         if (it == kv.end()) r.status = -1; else out = it->second;
         break;
       }
-      case kAdd: r.status = (counters[key] += h.arg); break;
+      case kAdd: {
+        // counters are visible as decimal-string values too, so that a reader of the key (the process-group
+        // rendezvous reads what another rank added) sees the count
+        auto it = counters.find(key);
+        if (it == counters.end()) {
+          auto kvit = kv.find(key);
+          int64_t base = 0;
+          if (kvit != kv.end()) base = std::strtoll(kvit->second.c_str(), nullptr, 10);
+          it = counters.emplace(key, base).first;
+        }
+        r.status = (it->second += h.arg);
+        kv[key] = std::to_string(it->second);
+        break;
+      }
+      case kDel: r.status = static_cast<int64_t>(kv.erase(key)); counters.erase(key); break;
+      case kCas: {
+        // value = u32 length of `expected` + expected + desired. An absent key matches an empty `expected`.
+        uint32_t el = 0;
+        if (val.size() >= 4) std::memcpy(&el, val.data(), 4);
+        if (val.size() < 4 + static_cast<size_t>(el)) { r.status = -100; break; }
+        const std::string expected = val.substr(4, el), desired = val.substr(4 + el);
+        auto it = kv.find(key);
+        if ((it == kv.end() && expected.empty()) || (it != kv.end() && it->second == expected)) {
+          kv[key] = desired;
+          counters.erase(key);
+          out = desired;
+        } else if (it != kv.end()) {
+          out = it->second;
+        } else {
+          out = expected;
+        }
+        break;
+      }
+      case kCount: r.status = static_cast<int64_t>(kv.size()); break;
+      case kHas: r.status = kv.count(key) ? 1 : 0; break;
       case kStamp: stamps[h.arg] = now_ms(); break;
       case kAges: {
         // value = world x i64 ages in ms (time since last stamp, or since server start if never stamped)
@@ -259,6 +293,29 @@ OFC_API int ofc_store_get(void* client, const char* key, void* out, int cap, int
     if (now_ms() > deadline) return ofc::fail(std::string("control store: timed out waiting for key ") + key, -2);
     std::this_thread::sleep_for(std::chrono::milliseconds(5));
   }
+}
+OFC_API int ofc_store_delete(void* client, const char* key) {
+  return static_cast<int>(static_cast<Client*>(client)->request(kDel, key, nullptr, 0, 0, nullptr));
+}
+OFC_API int64_t ofc_store_num_keys(void* client) { return static_cast<Client*>(client)->request(kCount, "", nullptr, 0, 0, nullptr); }
+OFC_API int ofc_store_has(void* client, const char* key) {
+  return static_cast<int>(static_cast<Client*>(client)->request(kHas, key, nullptr, 0, 0, nullptr));
+}
+// Sets key to `desired` if its current value equals `expected` (an absent key equals an empty `expected`); the value
+// the key holds afterwards is copied to out. Returns its length or a negative error.
+OFC_API int ofc_store_compare_set(void* client, const char* key, const void* expected, int elen, const void* desired, int dlen,
+                                  void* out, int cap) {
+  std::string payload(4 + static_cast<size_t>(elen) + static_cast<size_t>(dlen), '\0');
+  const uint32_t el = static_cast<uint32_t>(elen);
+  std::memcpy(&payload[0], &el, 4);
+  if (elen) std::memcpy(&payload[4], expected, static_cast<size_t>(elen));
+  if (dlen) std::memcpy(&payload[4 + static_cast<size_t>(elen)], desired, static_cast<size_t>(dlen));
+  std::string v;
+  int64_t st = static_cast<Client*>(client)->request(kCas, key, payload.data(), static_cast<uint32_t>(payload.size()), 0, &v);
+  if (st < 0) return static_cast<int>(st);
+  if (static_cast<int>(v.size()) > cap) return ofc::fail("control store: value larger than the caller's buffer", -3);
+  std::memcpy(out, v.data(), v.size());
+  return static_cast<int>(v.size());
 }
 OFC_API int64_t ofc_store_add(void* client, const char* key, int64_t delta) {
   return static_cast<Client*>(client)->request(kAdd, key, nullptr, 0, delta, nullptr);

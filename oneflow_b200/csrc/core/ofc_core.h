@@ -32,6 +32,11 @@ void ofc_store_client_close(void* client);
 int ofc_store_set(void* client, const char* key, const void* value, int len);
 int ofc_store_get(void* client, const char* key, void* out, int cap, int timeout_ms);   // returns value length, -2 on timeout
 int64_t ofc_store_add(void* client, const char* key, int64_t delta);
+int ofc_store_delete(void* client, const char* key);                    // 1 if the key existed
+int64_t ofc_store_num_keys(void* client);
+int ofc_store_has(void* client, const char* key);                       // 1 / 0
+int ofc_store_compare_set(void* client, const char* key, const void* expected, int elen, const void* desired, int dlen,
+                          void* out, int cap);                           // length of the value the key holds afterwards
 int ofc_store_barrier(void* client, const char* name, int world_size, int timeout_ms);  // -2 on timeout
 int ofc_store_heartbeat_start(void* client, int interval_ms);
 // Returns the number of ranks whose last heartbeat is older than max_age_ms; lost_out (cap entries) gets their ids.

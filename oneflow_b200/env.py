@@ -1,7 +1,10 @@
 """``flow.env``: rank / world queries and process-group bootstrap from MASTER_ADDR / MASTER_PORT /
 WORLD_SIZE / RANK / LOCAL_RANK (reference: python/oneflow/env.py:19-93,
-python/oneflow/framework/env_util.py:167-192). The control plane is torch.distributed's TCPStore; the
-data plane is gloo for CPU tensors and NCCL plus the in-tree peer-memory kernels for CUDA tensors."""
+python/oneflow/framework/env_util.py:167-192). The control plane is the in-tree control store
+(framework/control_plane.py over csrc/core/control_store.cpp): rank 0 hosts it on MASTER_PORT, the process groups
+rendezvous through it, every rank heartbeats into it and the rank-consistency check of global-tensor operations
+runs over it (``ONEFLOW_CONTROL_STORE=torch`` falls back to torch.distributed's TCPStore). The data plane is gloo for
+CPU tensors and NCCL plus the in-tree peer-memory kernels for CUDA tensors."""
 from __future__ import annotations
 
 import datetime
@@ -29,7 +32,15 @@ def init(backend=None, timeout_seconds=None):
     kwargs = {}
     if torch.cuda.is_available():
         torch.cuda.set_device(get_local_rank())
-    dist.init_process_group(backend, timeout=timeout, **kwargs)
+    rank = int(os.environ.get("RANK", "0"))
+    from .ops import _native
+    if os.environ.get("ONEFLOW_CONTROL_STORE", "native") != "torch" and _native.core_available():
+        from .framework import control_plane
+        store = control_plane.start(rank, world, os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]),
+                                    timeout_s=min(timeout.total_seconds(), 1800.0))
+        dist.init_process_group(backend, timeout=timeout, store=store, rank=rank, world_size=world, **kwargs)
+    else:
+        dist.init_process_group(backend, timeout=timeout, **kwargs)
     _initialized_here = True
 
 
@@ -76,8 +87,16 @@ def all_device_placement(device_type):
     return placement.all(device_type)
 
 
+def lost_ranks(max_age_seconds=5.0):
+    """Ranks whose heartbeat into the control store is overdue (host-side failure detection)."""
+    from .framework import control_plane
+    return control_plane.lost_ranks(max_age_seconds)
+
+
 def shutdown():
     global _initialized_here
     if dist.is_initialized() and _initialized_here:
         dist.destroy_process_group()
         _initialized_here = False
+    from .framework import control_plane
+    control_plane.shutdown()

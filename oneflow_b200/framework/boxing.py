@@ -214,6 +214,11 @@ def _apply_step(local, step, logical_shape, placement, cur_nd, coords):
     shp = _axis_shape(logical_shape, placement.hierarchy, cur_nd, coords, axis)
     if debug_routes:
         log.warning("boxing %s on mesh axis %d: %s -> %s", name, axis, a, b)
+    if n > 1 and name.startswith("ccl-"):
+        # with ONEFLOW_TIMEOUT_SECONDS set, the ranks first agree (over the control store) that they all run this step
+        from . import control_plane
+        if control_plane.consistency_timeout() is not None:
+            control_plane.check_consistency(ranks, f"{name} {tuple(logical_shape)} {a}->{b} axis {axis}")
     if name == "ccl-p-to-b":
         return p_to_b(local, group, ranks, idx)
     if name == "ccl-p-to-s":

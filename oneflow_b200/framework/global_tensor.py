@@ -1166,6 +1166,12 @@ def to_global(x, placement=None, sbp=None, *, grad_sbp=None, check_meta=True, co
     pl = placement
     nd = _norm_sbp(sbp, pl)
     me_in = _in_placement(pl)
+    if me_in and pl.size > 1 and dist.is_initialized():
+        # local -> global is collective over the placement (shape agreement, broadcast of B data): with
+        # ONEFLOW_TIMEOUT_SECONDS set, a rank that never arrives here is reported instead of waited for
+        from . import control_plane
+        if control_plane.consistency_timeout() is not None:
+            control_plane.check_consistency(list(pl.ranks_flat), f"local_to_global {tuple(x.shape)} {x.dtype} {tuple(str(s_) for s_ in nd)}")
     local = x
     if me_in:
         dev = pl.device()

@@ -25,7 +25,7 @@ def lib():
         for name in ("ofc_store_server_start", "ofc_store_client_connect", "ofc_allocator_create", "ofc_allocator_alloc",
                      "ofc_ptable_open", "ofc_executor_create", "ofc_records_open", "ofc_tokens_open"):
             getattr(L, name).restype = c_void_p
-        for name in ("ofc_store_add", "ofc_ptable_get", "ofc_ptable_size", "ofc_ptable_keys", "ofc_executor_completed", "ofc_records_next",
+        for name in ("ofc_store_add", "ofc_store_num_keys", "ofc_ptable_get", "ofc_ptable_size", "ofc_ptable_keys", "ofc_executor_completed", "ofc_records_next",
                      "ofc_tokens_count"):
             getattr(L, name).restype = c_int64
         L.ofc_copy_cost.restype = c_double
@@ -104,6 +104,21 @@ class ControlClient:
 
     def add(self, key, delta=1):
         return _check(lib().ofc_store_add(c_void_p(self.h), key.encode(), c_int64(delta)), "store.add")
+
+    def delete(self, key) -> bool:
+        return _check(lib().ofc_store_delete(c_void_p(self.h), key.encode()), "store.delete") > 0
+
+    def has(self, key) -> bool:
+        return _check(lib().ofc_store_has(c_void_p(self.h), key.encode()), "store.has") > 0
+
+    def num_keys(self) -> int:
+        return _check(lib().ofc_store_num_keys(c_void_p(self.h)), "store.num_keys")
+
+    def compare_set(self, key, expected: bytes, desired: bytes, cap=1 << 20) -> bytes:
+        buf = ctypes.create_string_buffer(cap)
+        n = _check(lib().ofc_store_compare_set(c_void_p(self.h), key.encode(), expected, len(expected), desired, len(desired),
+                                               buf, cap), "store.compare_set")
+        return buf.raw[:n]
 
     def barrier(self, name, world_size, timeout_s=30.0):
         _check(lib().ofc_store_barrier(c_void_p(self.h), name.encode(), world_size, int(timeout_s * 1000)), "store.barrier")

@@ -465,11 +465,58 @@ def embedding_stages(tmp):
     assert abs(total.item() - sum(12 * 4 * (r + 1) for r in range(world))) < 1e-3
 
 
+def rank_divergence(tmp):
+    """A rank that skips a global-tensor operation makes its peers raise within ONEFLOW_TIMEOUT_SECONDS instead of
+    hanging in the collective; ranks that run DIFFERENT operations are told so; heartbeats name a rank that is gone.
+    (The reference's check: python/oneflow/test/exceptions/test_global_branch_error_local_to_global_with_split_sbp.py.)"""
+    import time
+    from oneflow_b200.framework import control_plane as CP
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+    assert CP.client() is not None, "the process group must have been created over the in-tree control store"
+    P = flow.placement("cpu", list(range(world)))
+    os.environ["ONEFLOW_TIMEOUT_SECONDS"] = "2"
+    # 1. everybody agrees: the check is transparent
+    x = flow.tensor(torch.arange(8.0).reshape(4, 2), placement=P, sbp=flow.sbp.split(0))
+    assert np.allclose(x.to_global(P, flow.sbp.broadcast).numpy(), np.arange(8.0).reshape(4, 2))
+    # 2. rank 1 takes another branch and never calls to_global
+    t0 = time.time()
+    if rank == 0:
+        try:
+            flow.rand(2).to_global(placement=P, sbp=flow.sbp.split(0))
+            raise SystemExit("the missing rank was not noticed")
+        except RuntimeError as e:
+            assert "Maybe executing different code in different ranks" in str(e), str(e)
+            assert "did not reach" in str(e)
+        assert 1.5 < time.time() - t0 < 20
+    else:
+        time.sleep(3)
+    os.environ["ONEFLOW_TIMEOUT_SECONDS"] = "30"
+    CP.barrier("after-skip", world, 30)
+    CP.resync()
+    # 3. the ranks run different boxing steps on the same group
+    os.environ["ONEFLOW_TIMEOUT_SECONDS"] = "5"
+    y = flow.tensor(torch.ones(4, 4), placement=P, sbp=flow.sbp.split(0))
+    try:
+        y.to_global(P, flow.sbp.broadcast if rank == 0 else flow.sbp.split(1))
+        raise SystemExit("the differing operation was not noticed")
+    except RuntimeError as e:
+        assert "differs between ranks" in str(e) and "Maybe executing different code" in str(e), str(e)
+    os.environ.pop("ONEFLOW_TIMEOUT_SECONDS")
+    CP.barrier("after-mismatch", world, 30)
+    CP.resync()
+    # 4. heartbeats: every rank is alive now
+    assert flow.env.lost_ranks(5.0) == []
+    if rank == 0:
+        print("RANK DIVERGENCE OK")
+    CP.barrier("end", world, 30)
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
     {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
-     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers, "embedding_stages": embedding_stages}[case](tmp)
-    flow.comm.barrier()
+     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers, "embedding_stages": embedding_stages, "rank_divergence": rank_divergence}[case](tmp)
+    if case != "rank_divergence":
+        flow.comm.barrier()
     if flow.env.get_rank() == 0:
         print(f"CASE {case} OK")

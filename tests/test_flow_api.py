@@ -53,6 +53,10 @@ def test_sharded_data_readers_and_distributed_wrappers():
     launch("data_readers", 2)
 
 
+def test_rank_divergence_is_reported_not_waited_for():
+    launch("rank_divergence", 2, timeout=180)
+
+
 def test_one_embedding_stage_ops_two_ranks():
     launch("embedding_stages", 2)
 
