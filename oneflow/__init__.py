@@ -44,7 +44,7 @@ def _resolve(rel):
 
 class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
     def find_spec(self, fullname, path=None, target=None):
-        if not fullname.startswith("oneflow."):
+        if not fullname.startswith("oneflow.") or fullname == "oneflow.__main__":
             return None
         if _resolve(fullname[len("oneflow."):]) is None:
             return None

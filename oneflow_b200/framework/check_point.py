@@ -399,6 +399,8 @@ def _is_legacy_dir(path: Path):
 
 
 def _load_legacy_dir(path: Path, ctx):
+    if (path / META_FILENAME).is_file() and (path / DATA_FILENAME).is_file():
+        return load_tensor_dir(path)          # the directory of one variable: the tensor itself
     if not (path / SNAPSHOT_DONE).exists() and not any((p / META_FILENAME).exists() for p in path.iterdir() if p.is_dir()):
         raise ValueError(f"{path} is not a valid checkpoint directory")
     out = {}

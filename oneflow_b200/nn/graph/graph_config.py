@@ -2,7 +2,19 @@
 Each setter records the option; nn.Graph reads them when it prepares its step function."""
 from __future__ import annotations
 
+import warnings
+
 import torch
+
+_warned = set()
+
+
+def _no_effect(name, why):
+    """Some switches of the reference steer compiler passes that have no counterpart in this runtime. They are accepted
+    (scripts keep running) and say so once per process instead of silently doing nothing."""
+    if name not in _warned:
+        _warned.add(name)
+        warnings.warn(f"nn.Graph config.{name} is accepted but changes nothing here: {why}", stacklevel=3)
 
 
 class GraphConfig:
@@ -63,17 +75,23 @@ class GraphConfig:
 
     def enable_cudnn_conv_heuristic_search_algo(self, mode: bool = True):
         self.cudnn_conv_heuristic_search = bool(mode)
+        _no_effect("enable_cudnn_conv_heuristic_search_algo", "convolutions run the in-tree implicit-GEMM kernels or PyTorch's, not a cuDNN algorithm search")
 
     def enable_straighten_algorithm(self, mode: str = "MemoryFirst"):
         if mode not in ("Disable", "SpeedFirst", "MemoryFirst", "OverlapCpuGpu", "DelayShortGpu"):
             raise ValueError(f"unknown straighten mode {mode}")
         self.straighten_algorithm = mode
+        _no_effect("enable_straighten_algorithm", "kernels launch in program order on CUDA streams, there is no task graph to reorder")
 
     def enable_compress_memory(self, mode: bool = True):
         self.compress_memory = bool(mode)
+        if mode:
+            _no_effect("enable_compress_memory", "memory comes from the caching allocator, there is no static memory plan to compress")
 
     def enable_choose_best_memory_allocation(self, mode: bool = True):
         self.extra["best_memory_allocation"] = bool(mode)
+        if mode:
+            _no_effect("enable_choose_best_memory_allocation", "there is no static memory plan")
 
     def enable_auto_parallel(self, mode: bool = True):
         self.auto_parallel = bool(mode)
@@ -95,11 +113,13 @@ class GraphConfig:
 
     def enable_auto_memory(self, mode="AdaptiveMemory"):
         self.auto_memory = mode
+        _no_effect("enable_auto_memory", "use GraphModule.activation_checkpointing per block to trade compute for memory")
 
     def enable_multi_tensor_update(self, mode: bool = True):
         self.multi_tensor_update = bool(mode)
 
     def enable_fused_model_update_cast(self, mode: bool = True):
+        # always in effect for bf16 parameters: the flat optimizer writes the low-precision copy in the update kernel
         self.fused_model_update_cast = bool(mode)
 
     def enable_cuda_graph(self, mode: bool = True):

@@ -196,3 +196,27 @@ def test_one_embedding_single_rank_sgd_and_adam(tmp_path):
     with pytest.raises(ValueError):
         oe.Optimizer(oe.MultiTableEmbedding("u", 8, torch.float32, torch.int64, tables,
                                             oe.make_device_mem_store_options(str(tmp_path), 10, size_factor=1)), flow.optim.Adam)
+
+
+def test_load_variable_directory_written_by_the_reference():
+    """The reference ships a saved model of its C++ API tests: a legacy variable directory (one folder per variable with
+    the raw bytes in ``out`` and a text-proto ``meta``). ``flow.load`` must read it as it is (read-only, in place)."""
+    import struct
+    import oneflow as flow
+    root = "/root/reference/oneflow/api/cpp/tests/graph_test_model/affine_with_parameter"
+    if not os.path.isdir(os.path.join(root, "model.a")):
+        pytest.skip("the reference tree is not mounted")
+    sd = flow.load(root)
+    assert set(sd) >= {"model.a", "model.b"}
+    a = sd["model.a"]
+    assert tuple(a.shape) == (3, 4) and a.dtype == flow.float32
+    raw = open(os.path.join(root, "model.a", "out"), "rb").read()
+    assert np.allclose(a.numpy().reshape(-1), np.array(struct.unpack("<12f", raw), dtype=np.float32))
+    one = flow.load(os.path.join(root, "model.a"))          # a single tensor directory loads as the tensor
+    assert np.array_equal(np.asarray(one.numpy()), a.numpy())
+
+
+def test_doctor_entry_point():
+    p = subprocess.run([sys.executable, "-m", "oneflow", "--doctor"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       cwd=ROOT, timeout=300)
+    assert p.returncode == 0 and "version:" in p.stdout and "native kernel library" in p.stdout, p.stdout
