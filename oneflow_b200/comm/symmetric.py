@@ -215,3 +215,60 @@ class DeviceCollectives:
         piece = full[:, :, r * Al:(r + 1) * Al]                       # [n, outer, Al, mid, B/n, inner]
         out.copy_(piece.permute(1, 2, 3, 0, 4, 5).reshape(out.shape))
         return out
+
+
+class MultimemAllReduce:
+    """All-reduce through the NVSwitch's in-fabric reduction (csrc/comm/multimem.cu): every rank reduces one slice with
+    ``multimem.ld_reduce`` and re-broadcasts it with ``multimem.st`` over a multicast mapping of one symmetric buffer.
+
+    The buffer and its multicast binding come from torch's symmetric memory (it owns the cuMulticast plumbing and the
+    handle exchange); the barrier flags live in a small arena of this package. ``available`` is False when the group
+    has no multicast support (no NVSwitch / NVLS): callers then use the peer-to-peer collectives."""
+
+    def __init__(self, group, ranks, device, nbytes=64 << 20):
+        self.available = False
+        self.device = torch.device(device)
+        self.n = len(ranks)
+        self.nbytes = int(nbytes)
+        self.epoch = 0
+        if self.n < 2 or self.device.type != "cuda":
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            pg = group if group is not None else dist.group.WORLD
+            try:
+                symm_mem.enable_symm_mem_for_group(pg.group_name)
+            except Exception:
+                pass
+            self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.hdl = symm_mem.rendezvous(self.buf, group=pg.group_name)
+            self.mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        except Exception as e:  # no symmetric-memory backend for this group
+            self.reason = f"{type(e).__name__}: {e}"
+            return
+        if not self.mc:
+            self.reason = "the group has no multicast (NVLS) support"
+            return
+        self.arena = SymmetricArena(group, ranks, device, 1 << 16)     # only its signal block is used
+        self.available = True
+
+    def all_reduce(self, x, scale=1.0):
+        """sum over ranks of x, times scale, in x's dtype (fp32 or bf16); returns a new tensor shaped like x."""
+        if x.dtype not in _DT:
+            raise TypeError("multimem all-reduce takes fp32 or bf16")
+        esz = x.element_size()
+        q = self.n * (16 // esz)
+        n = x.numel()
+        padded = (n + q - 1) // q * q
+        if padded * esz > self.nbytes:
+            raise ValueError("tensor larger than the multicast buffer")
+        view = self.buf[:padded * esz].view(x.dtype)
+        view[:n].copy_(x.reshape(-1))
+        if padded != n:
+            view[n:].zero_()
+        self.epoch += 1
+        _native.check(_native.kernels().ofb_comm_multimem_all_reduce(
+            ctypes.byref(self.arena.ctx), c_void_p(self.mc), c_longlong(padded), c_int(_DT[x.dtype]), c_float(scale),
+            c_uint(self.epoch), c_int(4), c_int(0), _native.stream_ptr()), "multimem_all_reduce")
+        _k._count()
+        return view[:n].clone().view(x.shape)

@@ -497,6 +497,16 @@ emb_grad_push_kernel(EmbCtx c, const int* __restrict__ cnt, long long grad_off, 
   signal_when_grid_done(c, done_cnt, epoch, 1);
 }
 
+// Records the step of the update in every row the step touched (smart-decay Adam), after the update kernel has read
+// the previous value.
+__global__ void emb_stamp_step_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __restrict__ n_uo, int step) {
+  const int total = *n_uo;
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+    const int row = u_row[u];
+    if (row >= 0) *reinterpret_cast<int*>(st.rows + static_cast<long long>(row) * st.line + 3 * st.dim) = step;
+  }
+}
+
 // --------------------------------------------------------------------------------------------- owner: update
 template <bool kHalf>
 __global__ void __launch_bounds__(256)
@@ -552,6 +562,11 @@ __device__ __forceinline__ void update_one(float& x, float g, float& s1, float& 
     s1 = h.beta1 * s1 + (1.f - h.beta1) * g;
     s2 = h.beta2 * s2 + (1.f - h.beta2) * g * g;
     x -= (h.lr / h.bias_corr1) * s1 / (sqrtf(s2) / sqrtf(h.bias_corr2) + h.eps) + h.lr * h.weight_decay * x;
+  } else if (KIND == 5) {  // smart-decay adam: the caller put beta^skipped into bias_corr1/2 and the catch-up factor into lr_eff
+    const float catchup = s1 * h.lr_eff;
+    s1 = h.bias_corr1 * s1 + (1.f - h.beta1) * g;
+    s2 = h.bias_corr2 * s2 + (1.f - h.beta2) * g * g;
+    x -= h.lr * (s1 + catchup) / (sqrtf(s2) + h.eps);
   } else if (KIND == 3) {  // adagrad
     s1 += g * g;
     x -= h.lr_eff * g / (sqrtf(s1) + h.eps) + h.lr * h.weight_decay * x;
@@ -572,6 +587,9 @@ __global__ void __launch_bounds__(256)
 emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __restrict__ n_uo, float* __restrict__ gacc,
                   OfbEmbUpdate h) {
   constexpr int kStates = KIND == 0 ? 0 : (KIND == 1 || KIND == 3) ? 1 : 2;
+  // KIND 5 (smart-decay Adam, reference: one_embedding_update_kernels.cu:140-186): a row also remembers the step of its
+  // last update (first word after the two moments). Moments decay by beta^(steps since then), and the steps in
+  // between, in which the row would have kept moving along its first moment, are caught up in one go.
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -600,6 +618,15 @@ emb_update_kernel(OfbEmbStore st, const int* __restrict__ u_row, const int* __re
         if (row[k] == -2) continue;
         reinterpret_cast<float4*>(gacc + (u0 + k) * st.dim)[q] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row[k] < 0) continue;
+        OfbEmbUpdate hk = h;
+        if (KIND == 5) {
+          const int prev = *reinterpret_cast<const int*>(st.rows + static_cast<long long>(row[k]) * st.line + 3 * st.dim);
+          const float skip = static_cast<float>(h.step - prev);
+          hk.bias_corr1 = powf(h.beta1, skip);
+          hk.bias_corr2 = powf(h.beta2, skip);
+          hk.lr_eff = skip > 1.f ? h.beta1 * (1.f - powf(h.beta1, skip - 1.f)) / (1.f - h.beta1) : 0.f;
+        }
+        const OfbEmbUpdate& h = hk;
         update_one<KIND>(x[k].x, g[k].x, a[k].x, b[k].x, h);
         update_one<KIND>(x[k].y, g[k].y, a[k].y, b[k].y, h);
         update_one<KIND>(x[k].z, g[k].z, a[k].z, b[k].z, h);
@@ -705,7 +732,7 @@ OFB_API int ofb_emb_backward(const OfbCommCtx* cctx, const OfbEmbStore* st, cons
   if (emb_check(cctx, st, sh, n)) return -1;
   if (!upd) return fail("embedding: no update rule");
   const int need = upd->kind == 0 ? 1 : (upd->kind == 1 || upd->kind == 3) ? 2 : 3;
-  if (st->line < need * st->dim) return fail("embedding: rows too short for this optimizer's state");
+  if (st->line < need * st->dim + (upd->kind == 5 ? 4 : 0)) return fail("embedding: rows too short for this optimizer's state");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   EmbCtx c = to_emb_ctx(cctx);
   const long long worst = sh->cap * c.n;
@@ -727,7 +754,12 @@ OFB_API int ofb_emb_backward(const OfbCommCtx* cctx, const OfbEmbStore* st, cons
     case 1: emb_update_kernel<1><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
     case 2: emb_update_kernel<2><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
     case 3: emb_update_kernel<3><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+    case 5: emb_update_kernel<5><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
     default: emb_update_kernel<4><<<ug, 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, sh->gacc, *upd); break;
+  }
+  OFB_CUDA_OK(cudaGetLastError());
+  if (upd->kind == 5) {
+    emb_stamp_step_kernel<<<emb_grid(worst, 256), 256, 0, stream>>>(*st, sh->u_row, sh->n_uo, upd->step);
   }
   OFB_CUDA_OK(cudaGetLastError());
   return 0;

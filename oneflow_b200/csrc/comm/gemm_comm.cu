@@ -24,7 +24,7 @@
 #include <cstdlib>
 
 #include "../common/host_utils.h"
-#include "../kernels/gemm_tcgen05.cuh"
+#include "../kernels/gemm_2cta.cuh"
 #include "comm_common.cuh"
 #include "ofb_comm.h"
 
@@ -395,6 +395,376 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Two-SM versions (cta_group::2, 256 x 256 tiles over a CTA pair, 6-stage ring: the main loop of gemm_2cta.cuh).
+// The one-SM kernels above spend most of their time in their own main loop (about 1.1 PFLOP/s against 1.5 for the
+// pair kernel), so the exchange is moved onto the faster loop:
+//
+//   MODE_RS  Tiles are walked owner by owner, (rank+1), (rank+2), ..., this rank's own rows LAST. Partial tiles of the
+//            other owners go straight to their staging slabs with plain P2P stores and NO fence per tile (a system
+//            fence after every tile stalls the epilogue for a NVLink round trip each time; measured: 46 us of a
+//            182 us call at two ranks). Each epilogue warp fences ONCE, after its last remote tile, and then
+//            publishes the flags of all the tiles it sent. The own tiles come last, when the peers' partials are
+//            already there or about to be, and are reduced in the epilogue as before.
+//   MODE_AG  Same scheme as the one-SM kernel (copier warps pull the peers' shards while the pair starts on the local
+//            rows), on the pair main loop.
+// rows_per_rank must be a multiple of 256 (a pair's tile never straddles two owners).
+template <int B_MN, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? 256 : 192, 1)
+gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlocal,
+                  const __grid_constant__ CUtensorMap tmB, GemmShape shp, GemmEpilogue ep, GemmCommParams cp) {
+  using Cfg = Gemm2Cfg;
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BNH = Cfg::BNH, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
+  constexpr uint32_t IDESC = make_idesc_bf16(2 * BM, BN, 0, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Gemm2Cfg::EPI_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* ok_shared = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  SignalBlock* my_sig = cp.sig[cp.rank];
+  const int parity = cp.epoch & 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = shp.M / (2 * BM);
+  const int tiles_n = (shp.N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int kblocks = (shp.K + BK - 1) / BK;
+  const int tmpr = cp.rows_per_rank / (2 * BM);   // row tiles per owner
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  // Raster: bands of `band` row tiles that never straddle two owners, walked down the band first (the CTAs running at
+  // the same time share A and B tiles in L2); the owners are taken in the order given above.
+  int band = tmpr;
+  while (band > 16) band = (band % 2 == 0) ? band / 2 : 1;
+  if (band < 1) band = 1;
+  const int first_owner = MODE == MODE_AG ? cp.rank : (cp.rank + 1) % cp.n;
+  auto coords = [&](int t, int& tm, int& tn) {
+    const int per_band = band * tiles_n;
+    const int g = t / per_band, r = t - g * per_band;
+    const int seq_tm = g * band + r % band;                       // position in the owner-ordered sequence
+    tn = r / band;
+    tm = (seq_tm + first_owner * tmpr) % tiles_m;                 // physical row tile
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int ready_owner = cp.rank;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        int tm, tn;
+        coords(t, tm, tn);
+        const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM;
+        const int n0 = tn * BN + static_cast<int>(cta) * BNH;
+        const int owner = tm / tmpr;
+        if (MODE == MODE_AG && owner != cp.rank && owner != ready_owner) {
+          if (!wait_local_ge(&my_sig->local_cnt[cp.pull_slot + owner], cp.pull_target, cp.status, 200 + owner)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();
+          ready_owner = owner;
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (leader) mbar_arrive_expect_tx(&full[stage], 2 * (A_BYTES + B_BYTES));
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * B_BYTES;
+          if (MODE == MODE_AG && owner == cp.rank) {
+            tma_load_2d_pair(a_dst, &tmAlocal, bar, kb * BK, m0 - cp.rank * cp.rows_per_rank);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, bar, kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(b_dst + c * (BK * 128), &tmB, bar, n0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, bar, kb * BK, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (leader && elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_bf16_ss_pair(d_tmem, da, db, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
+    const int quad = warp & 3;
+    const uint32_t stage_sm = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    unsigned int cleared_owners = 0;
+    bool published = MODE != MODE_RS;   // the flags of this warp's remote tiles are out
+    bool bail = false;
+    auto flag_of = [&](int dst_rank, int src_rank, int tile_local) {
+      return cp.flags[dst_rank] + (static_cast<long long>(parity) * cp.n + src_rank) * cp.flag_stride + tile_local * 8 +
+             static_cast<int>(cta) * 4 + quad;
+    };
+    auto publish = [&]() {
+      // one fence for everything this warp stored to peers, then the flag of every tile it sent
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        for (int t = pair; t < total_tiles; t += n_pairs) {
+          int tm, tn;
+          coords(t, tm, tn);
+          const int owner = tm / tmpr;
+          if (owner == cp.rank) break;
+          st_release_sys(flag_of(owner, cp.rank, (tm - owner * tmpr) * tiles_n + tn), cp.epoch);
+        }
+      }
+      __syncwarp();
+      published = true;
+    };
+    for (int t = pair; t < total_tiles; t += n_pairs) {
+      int tm, tn;
+      coords(t, tm, tn);
+      const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM, n0 = tn * BN;
+      const int owner = tm / tmpr;
+      const bool remote_path = MODE == MODE_RS && owner != cp.rank;
+      if (MODE == MODE_RS && !remote_path && !published) publish();
+      if (remote_path && !((cleared_owners >> owner) & 1u)) {
+        int ok_w = 1;
+        if (lane == 0 && cp.epoch > 2)
+          ok_w = wait_flag_ge(&my_sig->rs_consumed[owner], cp.epoch - 2, cp.status, 300 + owner) ? 1 : 0;
+        ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+        if (!ok_w) { *abort_flag = 1; bail = true; break; }
+        cleared_owners |= 1u << owner;
+      }
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { bail = true; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      const int tile_local = (tm - owner * tmpr) * tiles_n + tn;
+      if (remote_path) {
+        GemmEpilogue pe;
+        pe.C = cp.stage[owner] + parity * cp.parity_stride + static_cast<long long>(cp.rank) * cp.rows_per_rank * shp.N;
+        pe.ldc = shp.N;
+        pe.bias = nullptr; pe.residual = nullptr; pe.aux_in = nullptr; pe.aux_out = nullptr;
+        pe.ldr = 0; pe.ld_aux = 0;
+        pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+        GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
+        if (!(cp.tune & 1))
+          gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false);
+      } else if (MODE == MODE_RS) {
+        int ok_w = 1;
+        if (lane == 0 && !(cp.tune & 4)) {
+          for (int s = 0; s < cp.n && ok_w; ++s) {
+            if (s == cp.rank) continue;
+            ok_w = wait_flag_ge(flag_of(cp.rank, s, tile_local), cp.epoch, cp.status, 600 + s) ? 1 : 0;
+          }
+        }
+        ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+        if (!ok_w) { *abort_flag = 1; bail = true; break; }
+        const int lrow0 = m0 - owner * cp.rows_per_rank + quad * 32;
+        const __nv_bfloat16* my_stage = cp.stage[cp.rank] + parity * cp.parity_stride;
+        const int rows_valid = cp.rows_per_rank - lrow0;
+        GemmEpilogue pe;
+        pe.C = cp.out; pe.ldc = cp.ldc;
+        pe.bias = cp.bias; pe.residual = nullptr; pe.ldr = 0;
+        pe.aux_in = nullptr; pe.aux_out = nullptr; pe.ld_aux = 0;
+        pe.alpha = 1.f; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          const int cols_valid = shp.N - col0;
+          if (cols_valid <= 0) break;
+          float h[32];
+          epi_load_sum_bf16(stage_sm, lane, my_stage + static_cast<long long>(lrow0) * shp.N + col0,
+                            static_cast<long long>(cp.rows_per_rank) * shp.N, (cp.tune & 8) ? 0 : cp.n, cp.rank, shp.N,
+                            cp.residual ? cp.residual + static_cast<long long>(lrow0) * cp.ldr + col0 : nullptr, cp.ldr, rows_valid, cols_valid, h);
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), ep.alpha, h[j]));
+          gemm_epilogue_chunk(pe, r, lrow0, col0, rows_valid, cols_valid, lane, stage_sm, false);
+        }
+      } else {
+        gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (MODE == MODE_RS && !published && !bail) publish();   // a pair that had no own tile at the end of its sequence
+  } else if (MODE == MODE_AG) {
+    // ---------------------------------------------------------------- copiers (warps 6, 7 of both CTAs)
+    const int ct = threadIdx.x - 192;  // 0..63
+    const long long shard_vecs = static_cast<long long>(cp.rows_per_rank) * cp.k_cols / 8;
+    const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
+    const long long v0 = per_cta * blockIdx.x;
+    const long long v1 = min(shard_vecs, v0 + per_cta);
+    __nv_bfloat16* my_gathered = cp.gathered[cp.rank] + parity * cp.parity_stride;
+    bool ok = true;
+    if (ct == 0 && cp.epoch > 2) {
+      for (int p = 0; p < cp.n && ok; ++p)
+        if (p != cp.rank) ok = wait_flag_ge(&my_sig->ag_pulled[p], cp.epoch - 2, cp.status, 400 + p);
+    }
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(cp.x_local);
+      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(cp.rank) * cp.rows_per_rank * cp.k_cols);
+      for (long long i = v0 + ct; i < v1; i += 64) dst[i] = src[i];
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (ct == 0) {
+      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + cp.rank], 1u) + 1u;
+      if (arrived == cp.pull_target) {
+        for (int p = 0; p < cp.n; ++p)
+          if (p != cp.rank) st_release_sys(&cp.sig[p]->ag_ready[cp.rank], cp.epoch);
+      }
+    }
+    for (int k = 1; k < cp.n; ++k) {
+      const int o = (cp.rank + k) % cp.n;
+      if (ct == 0) *ok_shared = (ok && wait_flag_ge(&my_sig->ag_ready[o], cp.epoch, cp.status, 500 + o)) ? 1 : 0;
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (!*ok_shared) { *abort_flag = 1; break; }
+      const uint4* src = reinterpret_cast<const uint4*>(cp.gathered[o] + parity * cp.parity_stride +
+                                                        static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
+      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
+      long long i = (cp.tune & 32) ? v1 : v0 + ct;
+      for (; i + 7 * 64 < v1; i += 8 * 64) {
+        uint4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = src[i + u * 64];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * 64] = t[u];
+      }
+      for (; i < v1; i += 64) dst[i] = src[i];
+      __threadfence();
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (ct == 0) {
+        const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + o], 1u) + 1u;
+        if (arrived == cp.pull_target) st_release_sys(&cp.sig[o]->ag_pulled[cp.rank], cp.epoch);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+
+  if (MODE == MODE_RS && !*abort_flag) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.done_slot], 1u) + 1u;
+      if (arrived == cp.done_target)
+        for (int p = 0; p < cp.n; ++p) st_release_sys(&cp.sig[p]->rs_consumed[cp.rank], cp.epoch);
+    }
+  }
+  cluster_sync_all();
+  tc_fence_after();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0 && cp.status) {
+      if (atomicCAS(cp.status, 0, (int)kStatusMbarTimeout) == 0) cp.status[1] = 2100 + static_cast<int>(cta);
+    }
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
+template <int B_MN, int MODE>
+static int launch_gemm_comm2(const CUtensorMap& tmA, const CUtensorMap& tmAl, const CUtensorMap& tmB, const GemmShape& shp,
+                             const GemmEpilogue& ep, const GemmCommParams& cp, int grid, cudaStream_t stream) {
+  auto kern = gemm_comm2_kernel<B_MN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  kern<<<grid & ~1, MODE == MODE_AG ? 256 : 192, Gemm2Cfg::SMEM_BYTES, stream>>>(tmA, tmAl, tmB, shp, ep, cp);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// The pair kernels are used when a pair's 256-row tile cannot straddle two owners (OFB_GEMM_COMM_2CTA=0 turns them off).
+static bool use_pair_kernel(int T, int n) {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = std::getenv("OFB_GEMM_COMM_2CTA");
+    mode = e ? std::atoi(e) : 1;
+  }
+  return mode != 0 && T % (n * 256) == 0;
+}
+
 template <int BN, int B_MN, int MODE>
 static int launch_gemm_comm(const CUtensorMap& tmA, const CUtensorMap& tmAl, const CUtensorMap& tmB, const GemmShape& shp,
                             const GemmEpilogue& ep, const GemmCommParams& cp, int grid, cudaStream_t stream) {
@@ -469,6 +839,13 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
   cp.parity_stride = stage_bytes / 4;  // half of the region, in bf16 elements
   if (const char* e = std::getenv("OFB_GEMM_COMM_TUNE")) cp.tune = std::atoi(e);
   auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (use_pair_kernel(T, n)) {
+    // each CTA of a pair stages 128 of the tile's 256 B columns
+    if (!b_mn_major && get_tensor_map(&tmB, b, 2, 2, K, N, 0, (uint64_t)ldb * 2, 0, 64, 128, 0, 3)) return -1;
+    cp.done_target = epoch * static_cast<unsigned int>(grid & ~1);
+    return b_mn_major ? launch_gemm_comm2<1, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s)
+                      : launch_gemm_comm2<0, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s);
+  }
   return b_mn_major ? launch_gemm_comm<256, 1, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s)
                     : launch_gemm_comm<256, 0, MODE_RS>(tmA, tmA, tmB, shp, ep, cp, grid, s);
 }
@@ -518,7 +895,14 @@ OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* 
   cp.pull_slot = pull_slot;
   cp.pull_target = epoch * static_cast<unsigned int>(grid);
   cp.parity_stride = parity_stride;
+  if (const char* e = std::getenv("OFB_GEMM_COMM_TUNE")) cp.tune = std::atoi(e);
   auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (use_pair_kernel(T, n)) {
+    if (!b_mn_major && get_tensor_map(&tmB, b, 2, 2, K, N, 0, (uint64_t)ldb * 2, 0, 64, 128, 0, 3)) return -1;
+    cp.pull_target = epoch * static_cast<unsigned int>(grid & ~1);
+    return b_mn_major ? launch_gemm_comm2<1, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s)
+                      : launch_gemm_comm2<0, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s);
+  }
   return b_mn_major ? launch_gemm_comm<256, 1, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s)
                     : launch_gemm_comm<256, 0, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s);
 }

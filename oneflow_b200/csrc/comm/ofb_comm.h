@@ -66,8 +66,9 @@ typedef struct OfbEmbShuffle {
 } OfbEmbShuffle;
 
 typedef struct OfbEmbUpdate {
-  int kind;             // 0 sgd, 1 momentum, 2 adam, 3 adagrad, 4 ftrl
+  int kind;             // 0 sgd, 1 momentum, 2 adam, 3 adagrad, 4 ftrl, 5 smart-decay adam (rows: [w | m | v | last step ...])
   float lr, lr_eff, scale, weight_decay, l2, momentum, beta1, beta2, eps, bias_corr1, bias_corr2, lr_power, lambda1, lambda2, beta;
+  int step;             // 1-based number of this update (smart-decay adam)
 } OfbEmbUpdate;
 
 int ofb_emb_forward(const OfbCommCtx* ctx, const OfbEmbStore* st, const OfbEmbShuffle* sh, const long long* ids, const int* tids,

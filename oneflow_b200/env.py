@@ -36,8 +36,17 @@ def init(backend=None, timeout_seconds=None):
     from .ops import _native
     if os.environ.get("ONEFLOW_CONTROL_STORE", "native") != "torch" and _native.core_available():
         from .framework import control_plane
-        store = control_plane.start(rank, world, os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]),
-                                    timeout_s=min(timeout.total_seconds(), 1800.0))
+        port = int(os.environ["MASTER_PORT"])
+        if "TORCHELASTIC_RUN_ID" in os.environ or os.environ.get("TORCHELASTIC_USE_AGENT_STORE") == "True":
+            # started by torch.distributed.run: its agent already serves a store on MASTER_PORT; the control store takes
+            # a free port, which rank 0 announces through the agent's store
+            boot = dist.TCPStore(os.environ["MASTER_ADDR"], port, world, False, timeout)
+            if rank == 0:
+                from .runtime.core import ControlServer
+                control_plane._server = ControlServer(world, 0)
+                boot.set("ofb_control_port", str(control_plane._server.port))
+            port = int(boot.get("ofb_control_port").decode())
+        store = control_plane.start(rank, world, os.environ["MASTER_ADDR"], port, timeout_s=min(timeout.total_seconds(), 1800.0))
         dist.init_process_group(backend, timeout=timeout, store=store, rank=rank, world_size=world, **kwargs)
     else:
         dist.init_process_group(backend, timeout=timeout, **kwargs)

@@ -95,7 +95,7 @@ def start(rank, world, host, port, timeout_s=300.0, heartbeat_s=1.0):
         return ControlStore(_client, timeout_s)
     if host in ("localhost", ""):
         host = "127.0.0.1"
-    if rank == 0:
+    if rank == 0 and _server is None:
         _server = ControlServer(world, port)
     _client = ControlClient(host, port, rank, timeout_s=timeout_s)
     if heartbeat_s:

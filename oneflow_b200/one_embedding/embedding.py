@@ -221,7 +221,19 @@ def _row_update(kind, rows, grad, D, hyper, step):
         m = rows[:, D:2 * D]
         m.mul_(hyper["momentum"]).add_(g)
         w -= lr * (m + wd * w)
-    elif kind in ("adam", "smart_decay_adam"):
+    elif kind == "smart_decay_adam":
+        # rows remember the step of their last update (first value after the moments): the moments decay by
+        # beta^(steps since then) and the missed steps along the first moment are caught up at once
+        # (oneflow/user/kernels/one_embedding_update_kernels.cu:140-186; no bias correction, no weight decay)
+        m, v, last = rows[:, D:2 * D], rows[:, 2 * D:3 * D], rows[:, 3 * D]
+        b1, b2, eps = hyper["beta1"], hyper["beta2"], hyper["eps"]
+        skip = (float(step) - last).clamp_(min=1.0)[:, None]
+        catchup = torch.where(skip > 1, m * b1 * (1 - b1 ** (skip - 1)) / (1 - b1), torch.zeros_like(m))
+        m.copy_(b1 ** skip * m + (1 - b1) * g)
+        v.copy_(b2 ** skip * v + (1 - b2) * g * g)
+        w -= lr * (m + catchup) / (v.sqrt() + eps)
+        last.fill_(float(step))
+    elif kind == "adam":
         m, v = rows[:, D:2 * D], rows[:, 2 * D:3 * D]
         b1, b2, eps = hyper["beta1"], hyper["beta2"], hyper["eps"]
         m.mul_(b1).add_(g, alpha=1 - b1)
@@ -247,7 +259,7 @@ def _row_update(kind, rows, grad, D, hyper, step):
         raise ValueError(f"unknown sparse optimizer {kind}")
 
 
-_STATE_FACTOR = {"sgd": 1, "momentum": 2, "adam": 3, "smart_decay_adam": 3, "adagrad": 2, "ftrl": 3}
+_STATE_FACTOR = {"sgd": 1, "momentum": 2, "adam": 3, "smart_decay_adam": 4, "adagrad": 2, "ftrl": 3}
 
 
 # ------------------------------------------------------------------------------------------------ exchange helpers
@@ -480,7 +492,10 @@ from ..optim.optimizer import Ftrl  # noqa: E402  (the dense FTRL optimizer; spa
 
 
 class SmartDecayAdam(torch.optim.Adam):
-    """Adam whose moment decay accounts for the steps a row was not touched (sparse-aware)."""
+    """Names the sparse-aware Adam for ``one_embedding.Optimizer``: every embedding row remembers the step of its last
+    update, its moments decay by ``beta ** (steps since then)`` and the skipped steps are caught up in one move (the
+    row update of ``_row_update`` / csrc/comm/emb_shuffle.cu, kind 5; it needs ``size_factor >= 4``). As a dense
+    optimizer on ordinary parameters, where every element is touched every step, it is Adam."""
 
 
 class Optimizer:

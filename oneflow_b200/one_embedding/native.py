@@ -39,10 +39,10 @@ class EmbShuffleStruct(Structure):
 class EmbUpdateStruct(Structure):
     _fields_ = [("kind", c_int)] + [(k, c_float) for k in (
         "lr", "lr_eff", "scale", "weight_decay", "l2", "momentum", "beta1", "beta2", "eps", "bias_corr1", "bias_corr2",
-        "lr_power", "lambda1", "lambda2", "beta")]
+        "lr_power", "lambda1", "lambda2", "beta")] + [("step", c_int)]
 
 
-_KIND = {"sgd": 0, "momentum": 1, "adam": 2, "smart_decay_adam": 2, "adagrad": 3, "ftrl": 4}
+_KIND = {"sgd": 0, "momentum": 1, "adam": 2, "smart_decay_adam": 5, "adagrad": 3, "ftrl": 4}
 _INIT = {"uniform": 0, "normal": 1, "constant": 2}
 
 
@@ -190,6 +190,7 @@ class NativeEmbeddingEngine:
         u.lr_eff = lr / (1.0 + (step - 1) * float(hyper.get("lr_decay", 0.0)))
         u.lr_power, u.lambda1 = float(hyper.get("lr_power", -0.5)), float(hyper.get("lambda1", 0.0))
         u.lambda2, u.beta = float(hyper.get("lambda2", 0.0)), float(hyper.get("beta", 0.0))
+        u.step = int(step)
         _native.check(_native.kernels().ofb_emb_backward(
             ctypes.byref(self.arena.ctx), ctypes.byref(self.st), ctypes.byref(self.sh), _native.ptr(grad), c_longlong(n),
             c_int(int(self.half)), c_uint(self.epoch), ctypes.byref(u), _native.stream_ptr()), "emb_backward")

@@ -70,6 +70,21 @@ def case_collectives(rank, world, dev):
     ref = odd.clone()
     dist.all_reduce(ref)
     close(coll.all_reduce(odd), ref, 1e-4, "all_reduce odd size")
+    if dev.type == "cuda":
+        # in-switch reduction (multimem.ld_reduce / multimem.st) where the fabric offers it
+        from oneflow_b200.comm.symmetric import MultimemAllReduce
+        mm = MultimemAllReduce(None, list(range(world)), dev, nbytes=32 << 20)
+        if mm.available:
+            for _ in range(3):
+                out = mm.all_reduce(x, scale=0.5)
+                close(out, sum(full) * 0.5, 1e-4, "multimem all_reduce fp32")
+            out = mm.all_reduce(xb)
+            close(out, sum(f.bfloat16().float() for f in full), 2e-2, "multimem all_reduce bf16")
+            close(mm.all_reduce(odd), ref, 1e-4, "multimem all_reduce odd size")
+            if rank == 0:
+                print("MULTIMEM all-reduce checked")
+        elif rank == 0:
+            print("MULTIMEM not available:", getattr(mm, "reason", "?"))
 
 
 def case_fused_gemm(rank, world, dev):

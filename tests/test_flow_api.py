@@ -198,6 +198,43 @@ def test_one_embedding_single_rank_sgd_and_adam(tmp_path):
                                             oe.make_device_mem_store_options(str(tmp_path), 10, size_factor=1)), flow.optim.Adam)
 
 
+def test_smart_decay_adam_catches_up_rows_that_skipped_steps(tmp_path):
+    """A row that was not touched for some steps decays its moments by beta^skipped and catches the skipped moves up, as
+    the reference's sparse kernel does; a row touched every step follows the plain recurrences."""
+    import oneflow as flow
+    oe = flow.one_embedding
+    tables = [oe.make_table_options(oe.make_constant_initializer(1.0))]
+    emb = oe.MultiTableEmbedding("sd", embedding_dim=4, dtype=torch.float32, key_type=torch.int64, tables=tables,
+                                 store_options=oe.make_device_mem_store_options(str(tmp_path), capacity=100, size_factor=4))
+    lr, b1, b2, eps = 0.1, 0.9, 0.999, 1e-8
+    opt = oe.Optimizer(emb, oe.SmartDecayAdam, lr=lr, betas=(b1, b2), eps=eps)
+    # id 1 is looked up every step, id 2 only at steps 1 and 4
+    sched = [[1, 2], [1], [1], [1, 2]]
+    w = {1: np.ones(4), 2: np.ones(4)}
+    m = {1: np.zeros(4), 2: np.zeros(4)}
+    v = {1: np.zeros(4), 2: np.zeros(4)}
+    last = {1: 0, 2: 0}
+    for step, ids in enumerate(sched, 1):
+        x = torch.tensor([ids])
+        y = emb(x)
+        (y * torch.arange(1.0, 5.0)).sum().backward()       # gradient of every looked-up row: [1, 2, 3, 4]
+        opt.step()
+        opt.zero_grad()
+        g = np.arange(1.0, 5.0)
+        for i in ids:
+            skip = step - last[i]
+            catch = m[i] * b1 * (1 - b1 ** (skip - 1)) / (1 - b1) if skip > 1 else 0.0
+            m[i] = b1 ** skip * m[i] + (1 - b1) * g
+            v[i] = b2 ** skip * v[i] + (1 - b2) * g * g
+            w[i] = w[i] - lr * (m[i] + catch) / (np.sqrt(v[i]) + eps)
+            last[i] = step
+    got = emb(torch.tensor([[1, 2]])).detach().numpy()[0]
+    assert np.allclose(got[0], w[1], atol=1e-5) and np.allclose(got[1], w[2], atol=1e-5), (got, w)
+    with pytest.raises(ValueError):    # the step slot needs a fourth block in the stored line
+        oe.Optimizer(oe.MultiTableEmbedding("sd3", 4, torch.float32, torch.int64, tables,
+                                            oe.make_device_mem_store_options(str(tmp_path), 10, size_factor=3)), oe.SmartDecayAdam)
+
+
 def test_load_variable_directory_written_by_the_reference():
     """The reference ships a saved model of its C++ API tests: a legacy variable directory (one folder per variable with
     the raw bytes in ``out`` and a text-proto ``meta``). ``flow.load`` must read it as it is (read-only, in place)."""
