@@ -60,6 +60,8 @@ struct GemmCommParams {
   // parity-1 data over the parity-0 data of the previous call that a slow peer may still be reading.
   long long parity_stride;
   int tune;                           // OFB_GEMM_COMM_TUNE bit mask, experiments only (0 in normal use)
+  unsigned int* ag_flags[kMaxPeers];  // pair kernel, MODE_AG: per rank [n owners][256] "CTA b of owner o has pushed its slice" epochs
+  int ag_done_slot;                   // local counter slot that detects the last CTA of an all-gather call
 };
 
 template <int BN>
@@ -396,6 +398,39 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
+// Drains a 32-row x 256-column strip of an accumulator (this warp's TMEM lane quadrant) as bf16 to `dst` with full-row
+// stores: the strip is staged in shared memory (512 bytes per row, 16-byte pieces XOR-swizzled by the row so that both the
+// row-per-thread writes and the row-per-instruction reads are conflict free), then every store instruction of the warp
+// writes ONE whole row of 512 contiguous bytes and the 32 rows go out back to back. Over NVLink this is what reaches the
+// link rate from few warps: stores of 64-byte row segments with a TMEM read between them measured about half of it.
+__device__ __forceinline__ void rs_store_strip_wide(uint32_t smem_strip, uint32_t taddr, float alpha, __nv_bfloat16* dst, long long ld,
+                                                    int rows_valid, int cols_valid, int lane) {
+#pragma unroll 1
+  for (int c = 0; c < 8; ++c) {
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 q;
+      q.x = pack_bf16x2(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
+      q.y = pack_bf16x2(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
+      q.z = pack_bf16x2(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
+      q.w = pack_bf16x2(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
+      epi_sts(smem_strip + lane * 512 + ((((c * 4 + j) ^ lane) & 31) << 4), q);
+    }
+  }
+  __syncwarp();
+  const bool col_ok = lane * 8 < cols_valid;
+#pragma unroll 8
+  for (int rr = 0; rr < 32; ++rr) {
+    const uint4 q = epi_lds(smem_strip + rr * 512 + (((lane ^ rr) & 31) << 4));
+    if (col_ok && rr < rows_valid) *reinterpret_cast<uint4*>(dst + rr * ld + lane * 8) = q;
+  }
+  __syncwarp();
+}
+
 // Two-SM versions (cta_group::2, 256 x 256 tiles over a CTA pair, 6-stage ring: the main loop of gemm_2cta.cuh).
 // The one-SM kernels above spend most of their time in their own main loop (about 1.1 PFLOP/s against 1.5 for the
 // pair kernel), so the exchange is moved onto the faster loop:
@@ -414,7 +449,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? 25
 gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlocal,
                   const __grid_constant__ CUtensorMap tmB, GemmShape shp, GemmEpilogue ep, GemmCommParams cp) {
   using Cfg = Gemm2Cfg;
-  constexpr int BM = Cfg::BM, BN = Cfg::BN, BNH = Cfg::BNH, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BNH = Cfg::BNH, BK = Cfg::BK;
+  // MODE_RS gives one ring stage up for a 16 KB staging strip per epilogue warp (full-row stores to the peers)
+  constexpr int STAGES = MODE == MODE_RS ? 5 : Cfg::STAGES;
+  constexpr int EPI_PER_WARP = MODE == MODE_RS ? 32 * 512 : kEpiStageBytesPerWarp;
   constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
   constexpr uint32_t IDESC = make_idesc_bf16(2 * BM, BN, 0, B_MN);
 
@@ -423,7 +461,7 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
   uint8_t* epi_stage = smem + STAGES * (A_BYTES + B_BYTES);
-  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + Gemm2Cfg::EPI_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + 4 * EPI_PER_WARP);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -563,7 +601,7 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
     const int quad = warp & 3;
-    const uint32_t stage_sm = smem_u32(epi_stage + quad * kEpiStageBytesPerWarp);
+    const uint32_t stage_sm = smem_u32(epi_stage + quad * EPI_PER_WARP);
     int acc = 0;
     uint32_t acc_phase = 0;
     unsigned int cleared_owners = 0;
@@ -616,8 +654,13 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         pe.ldr = 0; pe.ld_aux = 0;
         pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
         GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
-        if (!(cp.tune & 1))
-          gemm_epilogue_warp<BN>(pe, slab, taddr, m0 - owner * cp.rows_per_rank + quad * 32, n0, lane, stage_sm, false);
+        const int lrow = m0 - owner * cp.rows_per_rank + quad * 32;
+        if (cp.tune & 16) {
+          gemm_epilogue_warp<BN>(pe, slab, taddr, lrow, n0, lane, stage_sm, false);      // 64-byte segments (comparison)
+        } else if (!(cp.tune & 1)) {
+          rs_store_strip_wide(stage_sm, taddr, ep.alpha, reinterpret_cast<__nv_bfloat16*>(pe.C) + static_cast<long long>(lrow) * shp.N + n0,
+                              shp.N, cp.rows_per_rank - lrow, shp.N - n0, lane);
+        }
       } else if (MODE == MODE_RS) {
         int ok_w = 1;
         if (lane == 0 && !(cp.tune & 4)) {
@@ -664,55 +707,56 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     if (MODE == MODE_RS && !published && !bail) publish();   // a pair that had no own tile at the end of its sequence
   } else if (MODE == MODE_AG) {
-    // ---------------------------------------------------------------- copiers (warps 6, 7 of both CTAs)
+    // ---------------------------------------------------------------- copiers (warps 6, 7 of both CTAs): PUSH
+    // Every CTA owns one slice of this rank's shard and stores it into the gathered buffer of every peer (plain P2P
+    // stores, 512 contiguous bytes per warp instruction, several in flight: stores reach the link rate from these few
+    // threads, loads of the same width measured about half of it), nearest consumer first. After a system fence it
+    // raises its flag on that peer; the peer's CTA with the same index sees it and counts the slice as arrived.
     const int ct = threadIdx.x - 192;  // 0..63
     const long long shard_vecs = static_cast<long long>(cp.rows_per_rank) * cp.k_cols / 8;
     const long long per_cta = (shard_vecs + gridDim.x - 1) / gridDim.x;
     const long long v0 = per_cta * blockIdx.x;
     const long long v1 = min(shard_vecs, v0 + per_cta);
-    __nv_bfloat16* my_gathered = cp.gathered[cp.rank] + parity * cp.parity_stride;
-    bool ok = true;
-    if (ct == 0 && cp.epoch > 2) {
-      for (int p = 0; p < cp.n && ok; ++p)
-        if (p != cp.rank) ok = wait_flag_ge(&my_sig->ag_pulled[p], cp.epoch - 2, cp.status, 400 + p);
-    }
-    asm volatile("bar.sync 1, 64;" ::: "memory");
-    {
-      const uint4* src = reinterpret_cast<const uint4*>(cp.x_local);
-      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(cp.rank) * cp.rows_per_rank * cp.k_cols);
-      for (long long i = v0 + ct; i < v1; i += 64) dst[i] = src[i];
-    }
-    __threadfence_system();
-    asm volatile("bar.sync 1, 64;" ::: "memory");
+    const long long my_rows_off = static_cast<long long>(cp.rank) * cp.rows_per_rank * cp.k_cols;
+    const uint4* src = reinterpret_cast<const uint4*>(cp.x_local);
+    // the peers must be done with what this parity of their buffers held two calls ago
     if (ct == 0) {
-      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + cp.rank], 1u) + 1u;
-      if (arrived == cp.pull_target) {
-        for (int p = 0; p < cp.n; ++p)
-          if (p != cp.rank) st_release_sys(&cp.sig[p]->ag_ready[cp.rank], cp.epoch);
-      }
+      int okc = 1;
+      if (cp.epoch > 2)
+        for (int p = 0; p < cp.n && okc; ++p)
+          if (p != cp.rank) okc = wait_flag_ge(&my_sig->ag_pulled[p], cp.epoch - 2, cp.status, 400 + p) ? 1 : 0;
+      *ok_shared = okc;
     }
-    for (int k = 1; k < cp.n; ++k) {
-      const int o = (cp.rank + k) % cp.n;
-      if (ct == 0) *ok_shared = (ok && wait_flag_ge(&my_sig->ag_ready[o], cp.epoch, cp.status, 500 + o)) ? 1 : 0;
-      asm volatile("bar.sync 1, 64;" ::: "memory");
-      if (!*ok_shared) { *abort_flag = 1; break; }
-      const uint4* src = reinterpret_cast<const uint4*>(cp.gathered[o] + parity * cp.parity_stride +
-                                                        static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
-      uint4* dst = reinterpret_cast<uint4*>(my_gathered + static_cast<long long>(o) * cp.rows_per_rank * cp.k_cols);
-      long long i = (cp.tune & 32) ? v1 : v0 + ct;
-      for (; i + 7 * 64 < v1; i += 8 * 64) {
-        uint4 t[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) t[u] = src[i + u * 64];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) dst[i + u * 64] = t[u];
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    bool okc = *ok_shared != 0;
+    if (!okc) *abort_flag = 1;
+    for (int k = 0; k < cp.n && okc; ++k) {
+      const int p = (cp.rank - k + cp.n) % cp.n;   // k = 0: the local copy (kept for the weight gradient)
+      uint4* dst = reinterpret_cast<uint4*>(cp.gathered[p] + parity * cp.parity_stride + my_rows_off);
+      long long i = (cp.tune & 32) && k ? v1 : v0 + ct;
+      for (; i + 3 * 64 < v1; i += 4 * 64) {
+        const uint4 t0 = src[i], t1 = src[i + 64], t2 = src[i + 128], t3 = src[i + 192];
+        dst[i] = t0; dst[i + 64] = t1; dst[i + 128] = t2; dst[i + 192] = t3;
       }
       for (; i < v1; i += 64) dst[i] = src[i];
-      __threadfence();
-      asm volatile("bar.sync 1, 64;" ::: "memory");
-      if (ct == 0) {
-        const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.pull_slot + o], 1u) + 1u;
-        if (arrived == cp.pull_target) st_release_sys(&cp.sig[o]->ag_pulled[cp.rank], cp.epoch);
+      if (k) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+        if (ct == 0) st_release_sys(cp.ag_flags[p] + cp.rank * 256 + blockIdx.x, cp.epoch);
+      }
+    }
+    // arrivals: this CTA vouches for the slice of the CTA with its index on every other owner (the counter of the own
+    // shard advances too, so that calls of this kernel and of the one-SM kernel may alternate on one context)
+    if (ct == 0 && okc) {
+      atomicAdd(&my_sig->local_cnt[cp.pull_slot + cp.rank], 1u);
+      for (int k = 1; k < cp.n; ++k) {
+        const int o = (cp.rank + k) % cp.n;
+        if (!wait_flag_ge(cp.ag_flags[cp.rank] + o * 256 + blockIdx.x, cp.epoch, cp.status, 500 + o)) {
+          *abort_flag = 1;
+          break;
+        }
+        __threadfence();
+        atomicAdd(&my_sig->local_cnt[cp.pull_slot + o], 1u);
       }
     }
   }
@@ -727,6 +771,15 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.done_slot], 1u) + 1u;
       if (arrived == cp.done_target)
         for (int p = 0; p < cp.n; ++p) st_release_sys(&cp.sig[p]->rs_consumed[cp.rank], cp.epoch);
+    }
+  }
+  if (MODE == MODE_AG && !*abort_flag) {
+    // every tile of this rank has been computed from its gathered buffer: the peers may write this parity again
+    if (threadIdx.x == 0) {
+      const unsigned int arrived = atomicAdd(&my_sig->local_cnt[cp.ag_done_slot], 1u) + 1u;
+      if (arrived % gridDim.x == 0)     // the last CTA of this call (only this kernel counts on this slot)
+        for (int p = 0; p < cp.n; ++p)
+          if (p != cp.rank) st_release_sys(&cp.sig[p]->ag_pulled[cp.rank], cp.epoch);
     }
   }
   cluster_sync_all();
@@ -745,12 +798,13 @@ template <int B_MN, int MODE>
 static int launch_gemm_comm2(const CUtensorMap& tmA, const CUtensorMap& tmAl, const CUtensorMap& tmB, const GemmShape& shp,
                              const GemmEpilogue& ep, const GemmCommParams& cp, int grid, cudaStream_t stream) {
   auto kern = gemm_comm2_kernel<B_MN, MODE>;
+  constexpr int smem_bytes = MODE == MODE_RS ? 5 * (Gemm2Cfg::A_BYTES + Gemm2Cfg::B_BYTES) + 4 * 32 * 512 + 256 + 1024 : Gemm2Cfg::SMEM_BYTES;
   static bool configured = false;
   if (!configured) {
-    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::SMEM_BYTES));
+    OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     configured = true;
   }
-  kern<<<grid & ~1, MODE == MODE_AG ? 256 : 192, Gemm2Cfg::SMEM_BYTES, stream>>>(tmA, tmAl, tmB, shp, ep, cp);
+  kern<<<grid & ~1, MODE == MODE_AG ? 256 : 192, smem_bytes, stream>>>(tmA, tmAl, tmB, shp, ep, cp);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -854,8 +908,8 @@ OFB_API int ofb_gemm_rs(const OfbCommCtx* ctx, const void* a, long long lda, con
 // this rank's gathered buffer (parity = epoch & 1) for later kernels (weight gradients).
 OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* b, long long ldb, int b_mn_major, void* out,
                         long long ldc, const void* bias, const void* aux_in, void* aux_out, long long ld_aux, int act, int T,
-                        int N, int K, float alpha, long long gathered_off, long long gathered_bytes, unsigned int epoch,
-                        int pull_slot, void* stream) {
+                        int N, int K, float alpha, long long gathered_off, long long gathered_bytes, long long ag_flag_off,
+                        unsigned int epoch, int pull_slot, void* stream) {
   const int n = ctx->n;
   if (n < 1 || n > kMaxPeers) return fail("ag_gemm: group size must be 1..8");
   if (T % (n * 128)) return fail("ag_gemm: rows must be a multiple of 128 * group size");
@@ -889,7 +943,9 @@ OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* 
   for (int i = 0; i < n; ++i) {
     cp.sig[i] = reinterpret_cast<SignalBlock*>(ctx->signals[i]);
     cp.gathered[i] = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ctx->arena[i]) + gathered_off);
+    cp.ag_flags[i] = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(ctx->arena[i]) + ag_flag_off);
   }
+  cp.ag_done_slot = 3;
   cp.x_local = reinterpret_cast<const __nv_bfloat16*>(x_local);
   cp.k_cols = K;
   cp.pull_slot = pull_slot;
@@ -897,7 +953,7 @@ OFB_API int ofb_ag_gemm(const OfbCommCtx* ctx, const void* x_local, const void* 
   cp.parity_stride = parity_stride;
   if (const char* e = std::getenv("OFB_GEMM_COMM_TUNE")) cp.tune = std::atoi(e);
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (use_pair_kernel(T, n)) {
+  if (use_pair_kernel(T, n) && ag_flag_off > 0 && grid <= 256) {
     if (!b_mn_major && get_tensor_map(&tmB, b, 2, 2, K, N, 0, (uint64_t)ldb * 2, 0, 64, 128, 0, 3)) return -1;
     cp.pull_target = epoch * static_cast<unsigned int>(grid & ~1);
     return b_mn_major ? launch_gemm_comm2<1, MODE_AG>(tmA, tmAl, tmB, shp, ep, cp, grid, s)

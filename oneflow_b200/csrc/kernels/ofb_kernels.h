@@ -28,6 +28,21 @@ typedef struct OfbGemmArgs {
   float alpha;
 } OfbGemmArgs;
 
+// Set-associative LRU cache of fp32 rows (lru_cache.cu): 32 ways per set, storage provided by the caller.
+typedef struct OfbLruCache {
+  void* keys;     // int64  [n_sets * 32]
+  void* ticks;    // uint32 [n_sets * 32], zero-initialised (0 = empty way)
+  void* lines;    // fp32   [n_sets * 32 * line]
+  void* locks;    // uint32 [n_sets], zero-initialised
+  long long n_sets;
+  int line;       // floats per row, multiple of 4
+} OfbLruCache;
+int ofb_lru_get(const OfbLruCache* c, const long long* keys, long long n, float* out, unsigned int tick, int* n_miss, int* miss_index,
+                long long* miss_keys, unsigned char* hit_mask, void* stream);
+int ofb_lru_put(const OfbLruCache* c, const long long* keys, const float* rows, long long n, unsigned int tick, int* n_evicted,
+                long long* evicted_keys, float* evicted_rows, void* stream);
+int ofb_lru_dump(const OfbLruCache* c, int* n_out, long long* keys_out, float* rows_out, long long cap, void* stream);
+
 int ofb_gemm_bf16(const OfbGemmArgs* args, void* stream);
 const char* ofb_last_error(void);
 int ofb_read_status(int clear, int* out_code, int* out_detail);

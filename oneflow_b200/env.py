@@ -34,22 +34,28 @@ def init(backend=None, timeout_seconds=None):
         torch.cuda.set_device(get_local_rank())
     rank = int(os.environ.get("RANK", "0"))
     from .ops import _native
-    if os.environ.get("ONEFLOW_CONTROL_STORE", "native") != "torch" and _native.core_available():
+    native = os.environ.get("ONEFLOW_CONTROL_STORE", "native") != "torch" and _native.core_available()
+    elastic = "TORCHELASTIC_RUN_ID" in os.environ
+    if native and not torch.cuda.is_available() and not elastic:
+        # CPU job started by this package's launcher: the control store IS the rendezvous of every process group
         from .framework import control_plane
-        port = int(os.environ["MASTER_PORT"])
-        if "TORCHELASTIC_RUN_ID" in os.environ or os.environ.get("TORCHELASTIC_USE_AGENT_STORE") == "True":
-            # started by torch.distributed.run: its agent already serves a store on MASTER_PORT; the control store takes
-            # a free port, which rank 0 announces through the agent's store
-            boot = dist.TCPStore(os.environ["MASTER_ADDR"], port, world, False, timeout)
+        store = control_plane.start(rank, world, os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]),
+                                    timeout_s=min(timeout.total_seconds(), 1800.0))
+        dist.init_process_group(backend, timeout=timeout, store=store, rank=rank, world_size=world, **kwargs)
+    else:
+        # NCCL's communicator bootstrap calls store methods that a store implemented outside torch cannot provide,
+        # and torch.distributed.run already serves a store on MASTER_PORT: the process groups use torch's store, the
+        # control store (heartbeats, consistency check, barriers) takes a free port that rank 0 announces
+        dist.init_process_group(backend, timeout=timeout, **kwargs)
+        if native:
+            from .framework import control_plane
+            port = [0]
             if rank == 0:
                 from .runtime.core import ControlServer
                 control_plane._server = ControlServer(world, 0)
-                boot.set("ofb_control_port", str(control_plane._server.port))
-            port = int(boot.get("ofb_control_port").decode())
-        store = control_plane.start(rank, world, os.environ["MASTER_ADDR"], port, timeout_s=min(timeout.total_seconds(), 1800.0))
-        dist.init_process_group(backend, timeout=timeout, store=store, rank=rank, world_size=world, **kwargs)
-    else:
-        dist.init_process_group(backend, timeout=timeout, **kwargs)
+                port[0] = control_plane._server.port
+            dist.broadcast_object_list(port, src=0)
+            control_plane.start(rank, world, os.environ["MASTER_ADDR"], int(port[0]), timeout_s=min(timeout.total_seconds(), 1800.0))
     _initialized_here = True
 
 

@@ -754,7 +754,10 @@ class Graph:
             n_stages, my_stage, _ = self._stage_layout()
             pipelined = cfg.training and n_stages > 1 and my_stage is not None and n > 1
             with ctx, grad_ctx, self._backward_scaling(lambda: loss_scale / n):
-                if not pipelined:
+                if not pipelined and self._captured_ready(args, kwargs, first_call):
+                    for m in range(n):
+                        outs[m] = self._replay_captured(micro_args[m])
+                elif not pipelined:
                     for m in range(n):
                         fused_ops.op_trace = trace if m == 0 else None
                         outs[m] = self.build(*micro_args[m], **kwargs)
@@ -769,6 +772,67 @@ class Graph:
         if first_call:
             self._record_plan(trace)
         return _pack(outs)
+
+    # ------------------------------------------------------------------ captured micro-batch (config.enable_cuda_graph)
+    def _captured_ready(self, args, kwargs, first_call):
+        """``config.enable_cuda_graph``: after the first (eager, plan-recording) call the forward + backward of ONE
+        micro-batch is captured into a CUDA graph and every later micro-batch is a replay of it on fresh inputs (the
+        reference captures its kernels per stream: oneflow/core/ep/cuda/cuda_stream.h:70-120,
+        oneflow/core/kernel/cuda_graph_support.h:29-34). Conditions: one process (kernels that talk to peers take their
+        call number by value), CUDA inputs, every trainable parameter in a flat optimizer buffer (gradients then
+        accumulate in place in static memory). Anything else raises, so the switch never silently does nothing."""
+        if not self.config.cuda_graph or first_call:
+            return False
+        if self.__dict__.get("_cg") is not None:
+            return True
+        if self.__dict__.get("_cg_failed"):
+            return False
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            raise NotImplementedError("config.enable_cuda_graph: capture is limited to single-process graphs (the fused "
+                                      "collectives take their call number by value)")
+        if kwargs or not any(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+            raise NotImplementedError("config.enable_cuda_graph needs positional CUDA tensor inputs")
+        flat_ids = {id(sl.param) for f in self._flat for sl in f.slots}
+        if self.config.training and any(id(p) not in flat_ids for p in self._all_params() if p.requires_grad):
+            raise NotImplementedError("config.enable_cuda_graph needs all trainable parameters in a fused (flat) optimizer")
+        return self._capture(args)
+
+    def _capture(self, args):
+        n = self.config.grad_acc_steps if self.config.training else 1
+        sample = _unpack(args, n)[0]
+
+        def static_copy(a):
+            if isinstance(a, GT.GlobalTensor):
+                return GT.wrap(a._local.clone(), a.shape, a.placement, a.sbp)
+            return a.clone() if isinstance(a, torch.Tensor) else a
+        static_args = tuple(static_copy(a) for a in sample)
+        torch.cuda.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self.build(*static_args)
+        except Exception as e:           # an op on the path cannot be captured: say so once and stay eager
+            import warnings
+            torch.cuda.synchronize()
+            self.__dict__["_cg_failed"] = True
+            warnings.warn(f"nn.Graph {self._name}: CUDA-graph capture failed ({type(e).__name__}: {e}); running eagerly")
+            return False
+        # the capture only recorded the kernels: it did not run them, so nothing was accumulated yet
+        self.__dict__["_cg"] = (g, static_args, out)
+        if self._plan is not None:
+            self._plan["captured_micro_batch"] = True
+        return True
+
+    def _replay_captured(self, margs):
+        g, static_args, out = self._cg
+        for s, a in zip(static_args, margs):
+            if isinstance(s, GT.GlobalTensor):
+                s._local.copy_(a._local)
+            elif isinstance(s, torch.Tensor):
+                s.copy_(a)
+        g.replay()
+        from torch.utils import _pytree as pytree
+        return pytree.tree_map(lambda t: t.detach().clone() if isinstance(t, torch.Tensor) else t, out)
 
     def _run_1f1b(self, micro_args, kwargs, outs, n_stages, my_stage, trace):
         """One-forward-one-backward order over the micro-batches for this rank's stage (reference: the stage buffers

@@ -225,14 +225,15 @@ def _row_update(kind, rows, grad, D, hyper, step):
         # rows remember the step of their last update (first value after the moments): the moments decay by
         # beta^(steps since then) and the missed steps along the first moment are caught up at once
         # (oneflow/user/kernels/one_embedding_update_kernels.cu:140-186; no bias correction, no weight decay)
-        m, v, last = rows[:, D:2 * D], rows[:, 2 * D:3 * D], rows[:, 3 * D]
+        m, v = rows[:, D:2 * D], rows[:, 2 * D:3 * D]
+        last = rows[:, 3 * D].view(torch.int32)             # the step counter is kept as an integer in the float slot
         b1, b2, eps = hyper["beta1"], hyper["beta2"], hyper["eps"]
-        skip = (float(step) - last).clamp_(min=1.0)[:, None]
+        skip = (int(step) - last).clamp_(min=1).to(rows.dtype)[:, None]
         catchup = torch.where(skip > 1, m * b1 * (1 - b1 ** (skip - 1)) / (1 - b1), torch.zeros_like(m))
         m.copy_(b1 ** skip * m + (1 - b1) * g)
         v.copy_(b2 ** skip * v + (1 - b2) * g * g)
         w -= lr * (m + catchup) / (v.sqrt() + eps)
-        last.fill_(float(step))
+        last.fill_(int(step))
     elif kind == "adam":
         m, v = rows[:, D:2 * D], rows[:, 2 * D:3 * D]
         b1, b2, eps = hyper["beta1"], hyper["beta2"], hyper["eps"]

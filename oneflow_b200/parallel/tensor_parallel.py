@@ -41,11 +41,13 @@ class TPContext:
             self.flag_bytes = 2 * 8 * self.flag_stride * 4
             self.gathered_bytes = 2 * max_tokens * hidden * 2
             io = max(max_tokens * hidden * 2, 1 << 22)
-            total = self.stage_bytes + self.flag_bytes + self.gathered_bytes + 3 * io + (1 << 22)
+            self.ag_flag_bytes = 8 * 256 * 4          # per owner, one arrival flag per CTA of the pushing rank
+            total = self.stage_bytes + self.flag_bytes + self.gathered_bytes + self.ag_flag_bytes + 3 * io + (1 << 22)
             self.arena = SymmetricArena(group, ranks, device, total)
             self.stage_off = self.arena.region(self.stage_bytes)
             self.flag_off = self.arena.region(self.flag_bytes)
             self.gathered_off = self.arena.region(self.gathered_bytes)
+            self.ag_flag_off = self.arena.region(self.ag_flag_bytes)
             self.coll = DeviceCollectives(self.arena, io_bytes=io)
             self.hidden_cap = hidden
 
@@ -70,7 +72,7 @@ class TPContext:
             ctypes.byref(self.arena.ctx), _native.ptr(x_shard), _native.ptr(w), c_longlong(w.stride(0)),
             c_int(0 if b_layout == "nk" else 1), _native.ptr(out), c_longlong(N), _native.ptr(bias), _native.ptr(aux_in),
             _native.ptr(aux), c_longlong(ld_aux), c_int(G._act_code(act)), c_int(T), c_int(N), c_int(Kd), c_float(1.0),
-            c_longlong(self.gathered_off), c_longlong(self.gathered_bytes), c_uint(self.ag_epoch), c_int(8),
+            c_longlong(self.gathered_off), c_longlong(self.gathered_bytes), c_longlong(self.ag_flag_off), c_uint(self.ag_epoch), c_int(8),
             _native.stream_ptr()), "ag_gemm")
         K._count()
         gathered = None

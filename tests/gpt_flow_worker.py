@@ -85,6 +85,9 @@ def main():
     graph, model, lay = GF.build_gpt_graph(cfg, tp=tp, pp=pp, dp=dp, grad_acc=n_micro, device_type=device, lr=lr,
                                            weight_decay=wd, clip_grad=clip, zero_stage=1, seed=3, dtype=dtype)
     graph.config.enable_multi_tensor_update(True)
+    captured = os.environ.get("OFB_TEST_CUDA_GRAPH") == "1"
+    if captured:
+        graph.config.enable_cuda_graph(True)      # micro-batches after the first call replay a captured CUDA graph
     params = {}
     for name, p in model.named_parameters():
         pl = p.placement
@@ -126,6 +129,8 @@ def main():
             assert "all_gather_gemm" in ops and "gemm_reduce_scatter" in ops, ops
         if pp > 1:
             assert plan["schedule"] == "1F1B" and plan["stages"] == pp
+        if captured:
+            assert plan.get("captured_micro_batch") is True, "the micro-batch was not captured"
         print(f"GPT FLOW tp{tp} pp{pp} dp{dp} {device} OK", [round(v, 4) for v in losses[:4]])
     flow.comm.barrier()
 

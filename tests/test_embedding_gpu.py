@@ -46,16 +46,17 @@ def test_lookup_initialisation_and_dedup():
     assert _native.read_status() == (0, 0)
 
 
-@pytest.mark.parametrize("kind,factor", [("sgd", 1), ("momentum", 2), ("adam", 3), ("adagrad", 2), ("ftrl", 3)])
+@pytest.mark.parametrize("kind,factor", [("sgd", 1), ("momentum", 2), ("adam", 3), ("adagrad", 2), ("ftrl", 3), ("smart_decay_adam", 4)])
 def test_row_optimizers_match_reference_update(kind, factor):
     from oneflow_b200.one_embedding.embedding import _row_update
     hyper = {"sgd": {"lr": 0.3}, "momentum": {"lr": 0.3, "momentum": 0.9},
              "adam": {"lr": 0.01, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "weight_decay": 0.01},
+             "smart_decay_adam": {"lr": 0.01, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8},
              "adagrad": {"lr": 0.1, "lr_decay": 0.01, "eps": 1e-10},
              "ftrl": {"lr": 0.1, "lr_power": -0.5, "lambda1": 0.001, "lambda2": 0.01, "beta": 0.1}}[kind]
     eng = _engine(factor, state_init=0.1 if kind in ("adagrad", "ftrl") else 0.0)
     torch.manual_seed(1)
-    for step in (1, 2):
+    for step in ((1, 2, 5) if kind == "smart_decay_adam" else (1, 2)):     # the jump to step 5 leaves rows untouched for a while
         ids = torch.randint(0, 500, (2048, 3), device="cuda")
         out = eng.forward(ids)
         keys, rows = _rows_of(eng, ids)

@@ -13,12 +13,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _PORT = [29900]
 
 
-def run(tp, pp, dp, device, timeout=900):
+def run(tp, pp, dp, device, timeout=900, extra_env=None):
     _PORT[0] += 1
     n = tp * pp * dp
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(_PORT[0]), os.path.join(ROOT, "tests", "gpt_flow_worker.py"), str(tp), str(pp), str(dp), device]
-    env = dict(os.environ, OMP_NUM_THREADS="2", MASTER_ADDR="127.0.0.1", OFB_TEST_DUMP_AFTER=str(timeout - 60))
+    env = dict(os.environ, OMP_NUM_THREADS="2", MASTER_ADDR="127.0.0.1", OFB_TEST_DUMP_AFTER=str(timeout - 60), **(extra_env or {}))
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env, cwd=ROOT)
     keep = os.environ.get("OFB_KEEP_TEST_LOGS")
     if keep:
@@ -36,6 +36,13 @@ def test_gpt_flow_graph_matches_pytorch_cpu(tp, pp, dp):
 @pytest.mark.gpu
 def test_gpt_flow_graph_matches_pytorch_one_gpu():
     run(1, 1, 1, "cuda")
+
+
+@pytest.mark.gpu
+def test_gpt_flow_graph_with_captured_micro_batch_one_gpu():
+    """``config.enable_cuda_graph``: the forward + backward of a micro-batch is captured once and replayed; the loss curve
+    must be the one of the eager run (and of the PyTorch statement)."""
+    run(1, 1, 1, "cuda", extra_env={"OFB_TEST_CUDA_GRAPH": "1"})
 
 
 @pytest.mark.gpu
