@@ -346,8 +346,30 @@ class Embedding(torch.nn.Module):
     # -------------------------------------------------------------- store
     def _ensure_store(self, device):
         if self.store is None:
-            self.store = RowStore(self.storage_dim, device, self.capacity_per_rank, self.inits, self.embedding_dim,
-                                  seed=self.seed + self.rank)
+            full = RowStore(self.storage_dim, device, self.capacity_per_rank, self.inits, self.embedding_dim,
+                            seed=self.seed + self.rank)
+            caches = self.store_options["kv_store"]["caches"]
+            if caches and caches[0].get("policy") == "lru":
+                # device LRU cache in front of the full table in host memory or on disk (one_embedding/cached_store.py)
+                from . import cached_store as CS
+                budget = float(caches[0].get("cache_memory_budget_mb", 64))
+                cache_rows = max(32, int(budget * (1 << 20) / (self.storage_dim * 4)))
+                host_full = any(c.get("policy") == "full" and c.get("value_memory_kind") == "host" for c in caches[1:])
+                pt = self.store_options["kv_store"]["persistent_table"]
+                if host_full or not pt.get("path"):
+                    backing = CS.HostTable(self.storage_dim, self.capacity_per_rank)
+                else:
+                    import os as _os
+                    path = _os.path.join(pt["path"], f"{self.name}-{self.rank}")
+                    _os.makedirs(path, exist_ok=True)
+                    backing = CS.SsdTable(self.storage_dim, path, int(pt.get("physical_block_size", 512)))
+
+                def init_rows(keys, table_ids, size, _full=full):
+                    _full.size = size
+                    return _full._init_rows(keys, table_ids)
+                self.store = CS.CachedRowStore(self.storage_dim, device, cache_rows, backing, init_rows)
+            else:
+                self.store = full
         return self.store
 
     def set_sparse_optimizer(self, kind, hyper):
@@ -377,6 +399,9 @@ class Embedding(torch.nn.Module):
             return True
         if self.store is not None or self.dtype not in (torch.float16, torch.bfloat16) or self.world > 8:
             return False
+        caches = self.store_options["kv_store"]["caches"]
+        if caches and caches[0].get("policy") == "lru":
+            return False                      # cached host / SSD stores: the device holds an LRU cache, not the table
         if self.embedding_dim % 4 or os.environ.get("ONEFLOW_B200_EMBEDDING_ENGINE", "1") == "0":
             return False
         if any(i["type"] not in ("uniform", "normal", "constant") for i in self.inits):

@@ -198,6 +198,44 @@ def test_one_embedding_single_rank_sgd_and_adam(tmp_path):
                                             oe.make_device_mem_store_options(str(tmp_path), 10, size_factor=1)), flow.optim.Adam)
 
 
+@pytest.mark.parametrize("kind", ["host", "ssd"])
+def test_cached_embedding_store_matches_full_store(tmp_path, kind):
+    """An LRU cache far smaller than the working set in front of a host-memory / SSD table: training must follow the
+    run with the whole table resident, rows must survive being evicted and fetched again, and a snapshot must hold
+    every row."""
+    import oneflow as flow
+    oe = flow.one_embedding
+    tables = [oe.make_table_options(oe.make_uniform_initializer(-0.1, 0.1)) for _ in range(2)]
+
+    def build(opts, name):
+        emb = oe.MultiTableEmbedding(name, embedding_dim=8, dtype=torch.float32, key_type=torch.int64, tables=tables, store_options=opts)
+        return emb, oe.Optimizer(emb, flow.optim.Adam, lr=0.05)
+    full, fopt = build(oe.make_device_mem_store_options(str(tmp_path / "full"), capacity=4096, size_factor=3), "full_" + kind)
+    budget_mb = 64 * 24 * 4 / (1 << 20)                      # room for 64 rows of 24 floats: the steps touch ~400 distinct rows
+    if kind == "host":
+        opts = oe.make_cached_host_mem_store_options(budget_mb, str(tmp_path / "h"), capacity=4096, size_factor=3)
+    else:
+        opts = oe.make_cached_ssd_store_options(budget_mb, str(tmp_path / "s"), capacity=4096, size_factor=3)
+    cached, copt = build(opts, "cached_" + kind)
+    g = torch.Generator().manual_seed(3)
+    for step in range(12):
+        ids = torch.randint(0, 200, (64, 2), generator=g)
+        outs = []
+        for emb, opt in ((full, fopt), (cached, copt)):
+            y = emb(ids)
+            ((y - 0.5) ** 2).sum().backward()
+            opt.step()
+            opt.zero_grad()
+            outs.append(y.detach())
+        assert torch.allclose(outs[0], outs[1], atol=1e-6), step
+    st = cached.store
+    assert st.stats["evicted"] > 0 and st.stats["misses"] > st.stats["created"] > 0, st.stats   # rows went out and came back
+    probe = torch.arange(0, 200).reshape(100, 2)
+    assert torch.allclose(full(probe), cached(probe), atol=1e-6)
+    snap = st.snapshot()
+    assert snap["keys"].numel() == st.size == full.store.size
+
+
 def test_smart_decay_adam_catches_up_rows_that_skipped_steps(tmp_path):
     """A row that was not touched for some steps decays its moments by beta^skipped and catches the skipped moves up, as
     the reference's sparse kernel does; a row touched every step follows the plain recurrences."""
