@@ -435,16 +435,13 @@ __device__ __forceinline__ void rs_store_strip_wide(uint32_t smem_strip, uint32_
 // The one-SM kernels above spend most of their time in their own main loop (about 1.1 PFLOP/s against 1.5 for the
 // pair kernel), so the exchange is moved onto the faster loop:
 //
-//   MODE_RS  Three phases inside the one kernel. (1) Tiles are walked owner by owner, (rank+1), (rank+2), ..., this rank's
-//            own rows LAST, and EVERY partial tile is stored as bf16 into the staging slab of the rows' owner (own tiles
-//            into this rank's own slab): plain P2P stores of whole 512-byte rows from a shared-memory strip, NO fence
-//            per tile (a system fence after every tile stalls the epilogue for a NVLink round trip each time; measured:
-//            46 us of a 182 us call at two ranks). The NVLink stores start with the first tile and the own tiles'
-//            MMAs run while the link drains. (2) Each epilogue warp fences ONCE and publishes the flags of all the strips
-//            it stored. (3) A streaming reduction over this rank's rows: a warp takes a (strip, column half) unit, waits
-//            (bounded) for that strip's flag from all n sources and writes out = sum of the n partials + bias + residual
-//            with 16-byte accesses, 2 rows per instruction. (Reducing inside the own tiles' epilogue, as the one-SM
-//            kernel does, makes that epilogue latency-bound: 25 us per tile against 6.6 us of MMA at K = 1024.)
+//   MODE_RS  Tiles are walked owner by owner, (rank+1), (rank+2), ..., this rank's own rows LAST. Partial tiles of the
+//            other owners go straight to their staging slabs with plain P2P stores of whole 512-byte rows (from a 16 KB
+//            shared-memory strip per epilogue warp) and NO fence per tile (a system
+//            fence after every tile stalls the epilogue for a NVLink round trip each time; measured: 46 us of a
+//            182 us call at two ranks). Each epilogue warp fences ONCE, after its last remote tile, and then
+//            publishes the flags of all the tiles it sent. The own tiles come last, when the peers' partials are
+//            already there or about to be, and are reduced in the epilogue as before.
 //   MODE_AG  Copier warps PUSH this rank's shard into the peers' gathered buffers while the pair starts on the local
 //            rows; per-CTA arrival flags let the TMA producer start on an owner's rows as soon as they are complete.
 // rows_per_rank must be a multiple of 256 (a pair's tile never straddles two owners).
@@ -624,6 +621,7 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           int tm, tn;
           coords(t, tm, tn);
           const int owner = tm / tmpr;
+          if (owner == cp.rank) break;
           st_release_sys(flag_of(owner, cp.rank, (tm - owner * tmpr) * tiles_n + tn), cp.epoch);
         }
       }
@@ -636,6 +634,7 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM, n0 = tn * BN;
       const int owner = tm / tmpr;
       const bool remote_path = MODE == MODE_RS && owner != cp.rank;
+      if (MODE == MODE_RS && !remote_path && !published) publish();
       if (remote_path && !((cleared_owners >> owner) & 1u)) {
         int ok_w = 1;
         if (lane == 0 && cp.epoch > 2)
@@ -647,13 +646,57 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { bail = true; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      if (MODE == MODE_RS) {
-        // the partial strip goes to the slab this rank owns in the staging buffer of the rows' owner (its own included)
-        __nv_bfloat16* slab = cp.stage[owner] + parity * cp.parity_stride + static_cast<long long>(cp.rank) * cp.rows_per_rank * shp.N;
+      const int tile_local = (tm - owner * tmpr) * tiles_n + tn;
+      if (remote_path) {
+        GemmEpilogue pe;
+        pe.C = cp.stage[owner] + parity * cp.parity_stride + static_cast<long long>(cp.rank) * cp.rows_per_rank * shp.N;
+        pe.ldc = shp.N;
+        pe.bias = nullptr; pe.residual = nullptr; pe.aux_in = nullptr; pe.aux_out = nullptr;
+        pe.ldr = 0; pe.ld_aux = 0;
+        pe.alpha = ep.alpha; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+        GemmShape slab{cp.rows_per_rank, shp.N, shp.K, 1};
         const int lrow = m0 - owner * cp.rows_per_rank + quad * 32;
-        if (!(cp.tune & 1) || !remote_path)
-          rs_store_strip_wide(stage_sm, taddr, ep.alpha, slab + static_cast<long long>(lrow) * shp.N + n0, shp.N, cp.rows_per_rank - lrow,
-                              shp.N - n0, lane);
+        if (cp.tune & 16) {
+          gemm_epilogue_warp<BN>(pe, slab, taddr, lrow, n0, lane, stage_sm, false);      // 64-byte segments (comparison)
+        } else if (!(cp.tune & 1)) {
+          rs_store_strip_wide(stage_sm, taddr, ep.alpha, reinterpret_cast<__nv_bfloat16*>(pe.C) + static_cast<long long>(lrow) * shp.N + n0,
+                              shp.N, cp.rows_per_rank - lrow, shp.N - n0, lane);
+        }
+      } else if (MODE == MODE_RS) {
+        int ok_w = 1;
+        if (lane == 0 && !(cp.tune & 4)) {
+          for (int s = 0; s < cp.n && ok_w; ++s) {
+            if (s == cp.rank) continue;
+            ok_w = wait_flag_ge(flag_of(cp.rank, s, tile_local), cp.epoch, cp.status, 600 + s) ? 1 : 0;
+          }
+        }
+        ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+        if (!ok_w) { *abort_flag = 1; bail = true; break; }
+        const int lrow0 = m0 - owner * cp.rows_per_rank + quad * 32;
+        const __nv_bfloat16* my_stage = cp.stage[cp.rank] + parity * cp.parity_stride;
+        const int rows_valid = cp.rows_per_rank - lrow0;
+        GemmEpilogue pe;
+        pe.C = cp.out; pe.ldc = cp.ldc;
+        pe.bias = cp.bias; pe.residual = nullptr; pe.ldr = 0;
+        pe.aux_in = nullptr; pe.aux_out = nullptr; pe.ld_aux = 0;
+        pe.alpha = 1.f; pe.act = kActNone; pe.out_fp32 = 0; pe.accumulate = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          const int cols_valid = shp.N - col0;
+          if (cols_valid <= 0) break;
+          float h[32];
+          epi_load_sum_bf16(stage_sm, lane, my_stage + static_cast<long long>(lrow0) * shp.N + col0,
+                            static_cast<long long>(cp.rows_per_rank) * shp.N, (cp.tune & 8) ? 0 : cp.n, cp.rank, shp.N,
+                            cp.residual ? cp.residual + static_cast<long long>(lrow0) * cp.ldr + col0 : nullptr, cp.ldr, rows_valid, cols_valid, h);
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), ep.alpha, h[j]));
+          gemm_epilogue_chunk(pe, r, lrow0, col0, rows_valid, cols_valid, lane, stage_sm, false);
+        }
       } else {
         gemm_epilogue_warp<BN>(ep, shp, taddr, m0 + quad * 32, n0, lane, stage_sm, false);
       }
@@ -663,83 +706,7 @@ gemm_comm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (MODE == MODE_RS && !bail) {
-      publish();
-      // ---- phase 3: streaming reduction of this rank's rows. Unit = (strip of 32 rows x 256 columns, column half).
-      const int tiles_local = tmpr * tiles_n;
-      const long long units = static_cast<long long>(tiles_local) * 8 * 2;
-      const long long gwarp = static_cast<long long>(blockIdx.x) * 4 + quad;
-      const long long nwarps = static_cast<long long>(gridDim.x) * 4;
-      const __nv_bfloat16* my_stage = cp.stage[cp.rank] + parity * cp.parity_stride;
-      const long long src_stride = static_cast<long long>(cp.rows_per_rank) * shp.N;
-      for (long long u = gwarp; u < units && !bail; u += nwarps) {
-        const int half = static_cast<int>(u & 1);
-        const int strip = static_cast<int>((u >> 1) & 7);       // cta * 4 + quad of the producing warps
-        const int tl = static_cast<int>(u >> 4);
-        int ok_w = 1;
-        if (lane < cp.n && !(cp.tune & 4))
-          ok_w = wait_flag_ge(cp.flags[cp.rank] + (static_cast<long long>(parity) * cp.n + lane) * cp.flag_stride + tl * 8 + strip, cp.epoch,
-                              cp.status, 600 + lane) ? 1 : 0;
-        ok_w = __all_sync(0xffffffffu, ok_w);
-        if (!ok_w) { *abort_flag = 1; bail = true; break; }
-        const int row0 = (tl / tiles_n) * 2 * BM + (strip >> 2) * BM + (strip & 3) * 32;
-        const int col0 = (tl % tiles_n) * BN + half * 128 + (lane & 15) * 8;
-        if (col0 >= shp.N) continue;
-        float bias8[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) bias8[j] = 0.f;
-        if (cp.bias) {
-          const uint4 bb = __ldg(reinterpret_cast<const uint4*>(cp.bias + col0));
-          const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = unpack_bf16x2(bw[j]);
-            bias8[2 * j] = f.x;
-            bias8[2 * j + 1] = f.y;
-          }
-        }
-#pragma unroll 2
-        for (int it = 0; it < 16; ++it) {
-          const int row = row0 + it * 2 + (lane >> 4);
-          if (row >= cp.rows_per_rank) break;
-          float acc8[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc8[j] = bias8[j];
-          const long long off = static_cast<long long>(row) * shp.N + col0;
-          uint4 q[kMaxPeers];
-#pragma unroll
-          for (int sr = 0; sr < kMaxPeers; ++sr)
-            if (sr < cp.n) q[sr] = __ldcg(reinterpret_cast<const uint4*>(my_stage + sr * src_stride + off));
-          uint4 rq = make_uint4(0u, 0u, 0u, 0u);
-          if (cp.residual) rq = __ldg(reinterpret_cast<const uint4*>(cp.residual + static_cast<long long>(row) * cp.ldr + col0));
-#pragma unroll
-          for (int sr = 0; sr < kMaxPeers; ++sr) {
-            if (sr < cp.n) {
-              const uint32_t w[4] = {q[sr].x, q[sr].y, q[sr].z, q[sr].w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = unpack_bf16x2(w[j]);
-                acc8[2 * j] += f.x;
-                acc8[2 * j + 1] += f.y;
-              }
-            }
-          }
-          {
-            const uint32_t w[4] = {rq.x, rq.y, rq.z, rq.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16x2(w[j]);
-              acc8[2 * j] += f.x;
-              acc8[2 * j + 1] += f.y;
-            }
-          }
-          uint4 o;
-          o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
-          o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
-          *reinterpret_cast<uint4*>(cp.out + static_cast<long long>(row) * cp.ldc + col0) = o;
-        }
-      }
-    }
+    if (MODE == MODE_RS && !published && !bail) publish();   // a pair that had no own tile at the end of its sequence
   } else if (MODE == MODE_AG) {
     // ---------------------------------------------------------------- copiers (warps 6, 7 of both CTAs): PUSH
     // Every CTA owns one slice of this rank's shard and stores it into the gathered buffer of every peer (plain P2P

@@ -119,7 +119,7 @@ layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 // dx = rstd * (g*dy - mean_c(g*dy) - xhat * mean_c(g*dy*xhat)); each CTA also accumulates
 // sum_rows(dy*xhat) and sum_rows(dy) for its rows and writes them to partial[blockIdx.x].
 template <int NV>
-__global__ void __launch_bounds__(NV == 4 ? 1024 : 256)
+__global__ void __launch_bounds__(NV == 4 ? 1024 : 256, NV == 4 ? 1 : 2)
 layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
                       const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ add_to_dx,
@@ -146,18 +146,43 @@ layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
       for (int j = 0; j < 8; ++j) g[i][j] = 1.f;
     }
   }
+  // The loads of the NEXT row (x, dy, the addend, its statistics) are issued before this row's block-wide reduction:
+  // one row per CTA in flight leaves the memory system idle during the reduction (measured 0.27-0.38 of the HBM rate),
+  // two keep it busy.
+  uint4 nx[NV], nd[NV], na[NV];
+  float nmu = 0.f, nrs = 0.f;
+  auto prefetch = [&](int r) {
+    const long long o = static_cast<long long>(r) * cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      if (vi < nvec) {
+        nx[i] = reinterpret_cast<const uint4*>(x + o)[vi];
+        nd[i] = reinterpret_cast<const uint4*>(dy + o)[vi];
+        if (add_to_dx) na[i] = reinterpret_cast<const uint4*>(add_to_dx + o)[vi];
+      }
+    }
+    nmu = mean[r];
+    nrs = rstd[r];
+  };
+  constexpr bool kPrefetch = NV < 4;   // the 1024-thread form has 64 registers per thread: no room for a second row
+  if (blockIdx.x < rows) prefetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long off = static_cast<long long>(row) * cols;
-    const uint4* xr = reinterpret_cast<const uint4*>(x + off);
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + off);
-    const float mu = mean[row], rs = rstd[row];
+    const float mu = nmu, rs = nrs;
+    uint4 cx[NV], cd[NV], ca[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) { cx[i] = nx[i]; cd[i] = nd[i]; ca[i] = na[i]; }
+    if (kPrefetch) {
+      if (row + static_cast<int>(gridDim.x) < rows) prefetch(row + gridDim.x);
+    }
     float xh[NV][8], gd[NV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
       if (vi < nvec) {
-        uint4 px = xr[vi], pd = dyr[vi];
+        const uint4 px = cx[i], pd = cd[i];
         const uint32_t wx[4] = {px.x, px.y, px.z, px.w};
         const uint32_t wd[4] = {pd.x, pd.y, pd.z, pd.w};
 #pragma unroll
@@ -177,6 +202,9 @@ layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
     block_sum2(s1, s2, red);
     const float m1 = s1 / cols, m2 = s2 / cols;
     uint4* dxr = reinterpret_cast<uint4*>(dx + off);
+    if (!kPrefetch) {
+      if (row + static_cast<int>(gridDim.x) < rows) prefetch(row + gridDim.x);   // after the reduction: registers are free again
+    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
@@ -185,7 +213,7 @@ layer_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
 #pragma unroll
         for (int j = 0; j < 8; ++j) r[j] = rs * (gd[i][j] - m1 - xh[i][j] * m2);
         if (add_to_dx) {
-          uint4 pa = reinterpret_cast<const uint4*>(add_to_dx + off)[vi];
+          const uint4 pa = ca[i];
           const uint32_t wa[4] = {pa.x, pa.y, pa.z, pa.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(wa[j]); r[2 * j] += f.x; r[2 * j + 1] += f.y; }

@@ -52,13 +52,16 @@ def _device_coll(group, ranks, device):
     return c
 
 
-def _use_device_coll(t, n):
+def _use_device_coll(t, n, staged_fp32=True):
+    """The in-kernel collectives take fp32 / bf16 tensors that fit their exchange region: the input region holds 64 MB;
+    the two-shot all-reduce also stages an fp32 copy (``staged_fp32``), reduce-scatter / all-gather / all-to-all do not."""
     if not t.is_cuda or n < 2 or n > 8:
         return False
     if t.dtype not in (torch.float32, torch.bfloat16):
         return False
     from ..ops import _native
-    return _native.kernels_available() and t.numel() * 4 <= (64 << 20)
+    need = t.numel() * (4 if staged_fp32 else t.element_size())
+    return _native.kernels_available() and need <= (64 << 20)
 
 
 # ------------------------------------------------------------------------------------------------ 1-D steps
@@ -81,7 +84,8 @@ def s_to_b(local, dim, group, ranks, idx, logical_extent):
     n = len(ranks)
     if n == 1:
         return local
-    if dim == 0 and logical_extent % n == 0 and _use_device_coll(local, n) and local.numel() % 8 == 0:
+    if dim == 0 and logical_extent % n == 0 and local.numel() % 8 == 0 and local.is_cuda and \
+            local.numel() * n * local.element_size() <= (64 << 20) and _use_device_coll(local, n, staged_fp32=False):
         return _device_coll(group, ranks, local.device).all_gather(local.contiguous())
     return _all_gather_uneven(local, dim, group, n, logical_extent)
 
@@ -105,7 +109,7 @@ def p_to_s(local, dim, group, ranks, idx):
     n = len(ranks)
     if n == 1:
         return local
-    if dim == 0 and local.shape[0] % n == 0 and _use_device_coll(local, n) and (local.numel() // n) % 8 == 0:
+    if dim == 0 and local.shape[0] % n == 0 and _use_device_coll(local, n, staged_fp32=False) and (local.numel() // n) % 8 == 0:
         return _device_coll(group, ranks, local.device).reduce_scatter(local.contiguous())
     full = p_to_b(local, group, ranks, idx)
     return b_to_s(full, dim, n, idx)
