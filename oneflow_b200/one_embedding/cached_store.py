@@ -71,7 +71,9 @@ class DeviceLruCache:
                 ctypes.byref(self.c), _native.ptr(keys), c_longlong(n), _native.ptr(out), c_uint(self._next_tick()), _native.ptr(self._cnt),
                 _native.ptr(miss_index), _native.ptr(miss_keys), _native.ptr(hit), _native.stream_ptr()), "lru_get")
         m = int(self._cnt.item())
-        return out, hit.bool(), miss_index[:m].long()
+        # the kernel lists misses in the order its warps found them; callers get them in batch order (row creation
+        # draws from a stream, so the order must not depend on scheduling)
+        return out, hit.bool(), miss_index[:m].long().sort().values
 
     def put(self, keys, rows):
         """Inserts / overwrites; returns the (keys, rows) pushed out of the cache."""

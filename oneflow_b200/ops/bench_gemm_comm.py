@@ -1,0 +1,91 @@
+"""Micro-benchmark of the fused GEMM+collective kernels and of raw NVLink accesses, one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m oneflow_b200.ops.bench_gemm_comm [--tokens 8192] [--hidden 4096] [--ffn 16384] [--no-p2p]
+
+For the four tensor-parallel products of a GPT layer (attention output and MLP down projection as GEMM -> reduce-scatter,
+QKV and MLP up projection as all-gather -> GEMM) it prints the CUDA-event time of the fused kernel and of the plain GEMM of
+the same shape (max over ranks, microseconds), and, per access pattern, the bandwidth of SM loads / stores to the next
+rank's symmetric arena (GB/s). ``OFB_GEMM_COMM_2CTA=0`` selects the one-SM kernels."""
+import argparse
+import ctypes
+import json
+import os
+from ctypes import c_int, c_longlong
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=16384)
+    ap.add_argument("--no-p2p", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    from oneflow_b200.comm.symmetric import SymmetricArena
+    from oneflow_b200.ops import _native
+    from oneflow_b200.ops import gemm as G
+    from oneflow_b200.parallel.tensor_parallel import TPContext
+    T, H, F, n = args.tokens, args.hidden, args.ffn, world
+    tp = TPContext(None, list(range(world)), dev, max_tokens=T, max_cols=H, hidden=H)
+    bf = torch.bfloat16
+
+    def timeit(fn, iters=20, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+    res = {}
+    x_sh = torch.randn(T // n, H, device=dev, dtype=bf)
+    x_full = torch.randn(T, H, device=dev, dtype=bf)
+    for name, (N, K) in {"attn_out": (H, H // n), "mlp_down": (H, F // n)}.items():
+        a = torch.randn(T, K, device=dev, dtype=bf)
+        w = torch.randn(N, K, device=dev, dtype=bf) * 0.02
+        res[f"gemm_rs_{name}"] = timeit(lambda: tp.gemm_rs(a, w))
+        res[f"plain_{name}"] = timeit(lambda: G.gemm(a, w))
+    for name, N in {"qkv": 3 * H // n, "mlp_up": F // n}.items():
+        w = torch.randn(N, H, device=dev, dtype=bf) * 0.02
+        res[f"ag_gemm_{name}"] = timeit(lambda: tp.ag_gemm(x_sh, w))
+        res[f"plain_{name}"] = timeit(lambda: G.gemm(x_full, w))
+    bw = {}
+    if not args.no_p2p and world > 1:
+        ar = SymmetricArena(None, list(range(world)), dev, 2 * (256 << 20) + (1 << 22))
+        o_a, o_b = ar.region(256 << 20), ar.region(256 << 20)
+        lib = _native.kernels()
+        nbytes = 128 << 20
+        for mode, nm in ((0, "pull_wide"), (1, "push_wide"), (2, "push_seg64"), (3, "push_seg256")):
+            for ctas in (37, 148, 296):
+                def f():
+                    _native.check(lib.ofb_comm_p2p_bandwidth(ctypes.byref(ar.ctx), c_int((rank + 1) % world), c_int(mode), c_longlong(o_a),
+                                                             c_longlong(o_b), c_longlong(nbytes), c_longlong(8192), c_int(ctas),
+                                                             _native.stream_ptr()), "p2p_bandwidth")
+                us = timeit(f, iters=10, warm=3)
+                bw[f"{nm}_{ctas}ctas"] = round(nbytes / us / 1e3, 1)
+    status = _native.read_status()
+    if rank == 0:
+        print("GEMM_COMM_US", json.dumps({"ranks": world, "tokens": T, "hidden": H, "ffn": F, **{k: round(v, 1) for k, v in res.items()},
+                                          "kernel_status": list(status)}))
+        if bw:
+            print("P2P_GBS", json.dumps({"ranks": world, **bw}))
+    dist.barrier()
+
+
+if __name__ == "__main__":
+    main()
