@@ -124,17 +124,19 @@ def fused_scale_mask_softmax_dropout(x, mask, dropout_mask=None, *, fill_value=0
 
 class _Fmha(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
-        out, lse = K.fmha_fwd(q, k, v, causal=causal, scale=scale)
+    def forward(ctx, q, k, v, causal, scale, dropout_p=0.0, seed=0, offset=0):
+        out, lse = K.fmha_fwd(q, k, v, causal=causal, scale=scale, dropout_p=dropout_p, seed=seed, offset=offset)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.causal, ctx.scale = causal, scale
+        ctx.causal, ctx.scale, ctx.drop = causal, scale, (dropout_p, seed, offset)
         return out
 
     @staticmethod
     def backward(ctx, d_o):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o.contiguous(), lse, causal=ctx.causal, scale=ctx.scale)
-        return dq, dk, dv, None, None
+        p, seed, offset = ctx.drop
+        dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o.contiguous(), lse, causal=ctx.causal, scale=ctx.scale, dropout_p=p, seed=seed,
+                                offset=offset)
+        return dq, dk, dv, None, None, None, None, None
 
 
 def _bshd_ok(t):
@@ -142,17 +144,40 @@ def _bshd_ok(t):
     return t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == S * t.stride(1) and t.data_ptr() % 16 == 0
 
 
-def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None):
-    """query/key/value: [B, H, S, D] (torch convention). The fused tcgen05 kernel is used for bf16 CUDA inputs
-    with head dim 64/128, no explicit mask and no dropout."""
+_DROPOUT_CALLS = [0]
+
+
+def _dropout_stream(generator, device):
+    """(seed, offset) of the next attention dropout: the seed of the generator in charge, and a call counter so that two
+    calls never share a mask."""
+    generator = _resolve_gen(generator, device)
+    seed = generator.initial_seed() if generator is not None else torch.initial_seed()
+    _DROPOUT_CALLS[0] += 1
+    return seed, _DROPOUT_CALLS[0]
+
+
+def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, generator=None):
+    """query: [B, H, Sq, D], key / value: [B, Hk, Sk, D] (torch convention; Hk divides H for grouped-query attention).
+    With ``is_causal`` and Sq != Sk the diagonal is aligned to the bottom-right corner, as in the flash-attention
+    library the reference calls (oneflow/user/kernels/scaled_dot_product_attention_kernel.cu:54-138). The fused tcgen05
+    kernel serves bf16 CUDA inputs with head dim 64/128 and no explicit mask, dropout (Philox, regenerated in backward)
+    included."""
     D = query.shape[-1]
-    if (query.is_cuda and query.dtype == torch.bfloat16 and D in (64, 128) and attn_mask is None and dropout_p == 0.0
-            and query.shape == key.shape == value.shape):
+    H, Hk = query.shape[1], key.shape[1]
+    Sq, Sk = query.shape[-2], key.shape[-2]
+    if (query.is_cuda and query.dtype == torch.bfloat16 and D in (64, 128) and attn_mask is None and 0.0 <= dropout_p < 1.0
+            and key.shape == value.shape and key.dtype == value.dtype == torch.bfloat16 and H % Hk == 0 and query.shape[0] == key.shape[0]):
         q, k, v = (t.transpose(1, 2) for t in (query, key, value))  # [B, S, H, D] views
-        if not all(_bshd_ok(t) for t in (q, k, v)):
+        if not all(_bshd_ok(t) for t in (q, k, v)) or k.stride(1) != v.stride(1):
             q, k, v = (t.contiguous() for t in (q, k, v))
         sc = scale if scale is not None else 1.0 / math.sqrt(D)
-        return _Fmha.apply(q, k, v, bool(is_causal), sc).transpose(1, 2)
+        seed, offset = _dropout_stream(generator, query.device) if dropout_p > 0.0 else (0, 0)
+        return _Fmha.apply(q, k, v, bool(is_causal), sc, float(dropout_p), seed, offset).transpose(1, 2)
+    if Hk != H and H % Hk == 0:
+        key, value = (t.repeat_interleave(H // Hk, dim=1) for t in (key, value))
+    if is_causal and Sq != Sk and attn_mask is None:
+        attn_mask = torch.ones(Sq, Sk, dtype=torch.bool, device=query.device).tril(Sk - Sq)
+        is_causal = False
     return torch.nn.functional.scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale=scale)
 
 
@@ -170,7 +195,7 @@ def fused_multi_head_attention_inference(query, key, value, num_heads, causal=Fa
     D = HD // num_heads
     q4, k4, v4 = (t.reshape(B, t.shape[1], num_heads, D) for t in (q, k, v))
     if (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and attn_bias is None and causal_diagonal_offset == 0
-            and k.shape[1] == S and all(_bshd_ok(t) for t in (q4, k4, v4))):
+            and (k.shape[1] == S or not causal) and k4.stride(1) == v4.stride(1) and all(_bshd_ok(t) for t in (q4, k4, v4))):
         with torch.no_grad():
             out, _ = K.fmha_fwd(q4, k4, v4, causal=causal)
         return out.reshape(B, S, HD)

@@ -95,17 +95,19 @@ def build_core(verbose=False):
 
 
 def build_api(verbose=False):
-    """C++ inference API (csrc/api) on top of libofb_kernels.so."""
+    """C++ inference API (csrc/api): graph compiler and executor on top of libofb_kernels.so and libofb_core.so."""
     srcs = sorted(glob.glob(os.path.join(CSRC, "api", "*.cpp")))
     if not srcs:
         return None
-    headers = glob.glob(os.path.join(CSRC, "api", "*.h")) + [os.path.join(CSRC, "kernels", "ofb_kernels.h")]
+    headers = glob.glob(os.path.join(CSRC, "api", "*.h")) + [os.path.join(CSRC, "kernels", "ofb_kernels.h"),
+                                                              os.path.join(CSRC, "core", "ofc_core.h")]
     lib = os.path.join(LIB, "libofb_api.so")
     kern = os.path.join(LIB, "libofb_kernels.so")
-    if os.path.exists(lib) and not any(_newer(s, lib, headers + [kern]) for s in srcs):
+    core = os.path.join(LIB, "libofb_core.so")
+    if os.path.exists(lib) and not any(_newer(s, lib, headers + [kern, core]) for s in srcs):
         return lib
     _run([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", lib] + srcs +
-         ["-L", LIB, "-lofb_kernels", "-lcudart", "-Xlinker", "-rpath=$ORIGIN"], os.path.join(OBJ, "api.log"))
+         ["-L", LIB, "-lofb_kernels", "-lofb_core", "-lcudart", "-Xlinker", "-rpath=$ORIGIN"], os.path.join(OBJ, "api.log"))
     print(f"[build] built {os.path.relpath(lib, ROOT)}", flush=True)
     return lib
 

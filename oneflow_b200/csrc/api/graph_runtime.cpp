@@ -1,0 +1,1008 @@
+// Operator-graph compiler and executor behind oneflow_api::Graph (see oneflow_api.h for the overview).
+//
+//   graph.txt --parse--> IR (tensors + operators) --compile--> Plan --run--> outputs
+//
+// IR text (version 2), one record per line:
+//   tensor <id> <bf16|i64|f32> <input|param|act> <ndim> <d0> ... [file=<raw file>] [alias=<id>] [offset=<elements>]
+//   op <type> in=<id,id,...> out=<id,...> [key=value ...]          (-1 marks an absent optional input)
+//   input <id> / output <id>                                      (in call order)
+// Tensor ids are dense and operators are listed in a valid execution order. A dimension of -1 is the row count that is
+// bound at the first Forward (only the layer-list form, version 1, uses it).
+//
+// Reference counterparts: the job -> OpGraph -> task graph -> plan pipeline (oneflow/core/job/job_build_and_infer_ctx.cpp,
+// oneflow/core/graph/op_graph.cpp, task_graph.cpp, oneflow/core/job/plan_util.cpp), the memory-sharing pass
+// (oneflow/core/job/intra_job_mem_sharing_util.cpp) and the runtime that launches the plan
+// (oneflow/core/framework/nn_graph.cpp, oneflow/core/lazy/actor/).
+#include "graph_runtime.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <stdexcept>
+
+#include "../core/ofc_core.h"
+#include "../kernels/ofb_kernels.h"
+
+extern "C" {
+int ofb_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int rows, int cols,
+                       float eps, void* stream);
+int ofb_softmax_fwd(const void* x, const void* dropout_mask, const void* attn_mask, long long attn_mask_rows, void* y, void* softmax_y,
+                    long long rows, int cols, int tril, int tril_rows, int diagonal, float scale, float mask_fill, float out_scale,
+                    void* stream);
+int ofb_fmha_fwd_ex(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride, void* out, float* lse,
+                    const int* kv_len, int B, int Sq, int Sk, int H, int Hk, int D, int causal, float scale, float p_dropout,
+                    unsigned long long seed, unsigned int offset, void* stream);
+int ofb_graph_unary(const void* x, void* y, long long n, int fn, float alpha, void* stream);
+int ofb_graph_binary(const void* a, const void* b, void* y, long long n, long long cols, int b_mode, int op, void* stream);
+int ofb_graph_strided_copy(const void* x, void* y, int ndim, const long long* shape, const long long* in_strides, long long in_offset,
+                           const long long* out_strides, long long out_offset, int elem_bytes, void* stream);
+int ofb_graph_gather_rows(const long long* ids, const void* table, void* out, long long n_ids, int cols, long long table_rows,
+                          void* stream);
+}
+
+namespace oneflow_api {
+
+using namespace detail;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------ IR
+struct TensorDef {
+  DType dtype = DType::kBFloat16;
+  std::vector<int64_t> shape;
+  int kind = 2;   // 0 input, 1 param, 2 activation
+  std::string file;
+  int alias_of = -1;
+  int64_t alias_off = 0;   // elements into the aliased tensor
+};
+struct OpDef {
+  std::string type;
+  std::vector<int> in, out;
+  std::map<std::string, std::string> attr;
+};
+struct IR {
+  std::vector<TensorDef> tensors;
+  std::vector<OpDef> ops;
+  std::vector<int> inputs, outputs;
+  bool dynamic_rows = false;
+};
+
+std::vector<std::string> split(const std::string& s, char sep) {
+  std::vector<std::string> out;
+  std::string cur;
+  for (char c : s) {
+    if (c == sep) { out.push_back(cur); cur.clear(); }
+    else cur.push_back(c);
+  }
+  out.push_back(cur);
+  return out;
+}
+std::vector<int64_t> int_list(const std::string& s) {
+  std::vector<int64_t> out;
+  if (s.empty()) return out;
+  for (auto& t : split(s, ',')) out.push_back(std::stoll(t));
+  return out;
+}
+int64_t attr_int(const OpDef& op, const char* k, int64_t dflt) {
+  auto it = op.attr.find(k);
+  return it == op.attr.end() ? dflt : std::stoll(it->second);
+}
+double attr_float(const OpDef& op, const char* k, double dflt) {
+  auto it = op.attr.find(k);
+  return it == op.attr.end() ? dflt : std::stod(it->second);
+}
+std::string attr_str(const OpDef& op, const char* k, const std::string& dflt) {
+  auto it = op.attr.find(k);
+  return it == op.attr.end() ? dflt : it->second;
+}
+int act_code(const std::string& a) { return a == "gelu" ? 1 : a == "gelu_tanh" ? 2 : a == "relu" ? 3 : 0; }
+
+IR parse_v2(std::istream& f) {
+  IR ir;
+  std::string line;
+  int lineno = 1;
+  while (std::getline(f, line)) {
+    ++lineno;
+    if (line.empty() || line[0] == '#') continue;
+    std::istringstream ss(line);
+    std::string rec;
+    ss >> rec;
+    auto bad = [&](const std::string& why) { return std::runtime_error("graph.txt line " + std::to_string(lineno) + ": " + why); };
+    if (rec == "tensor") {
+      int id, ndim;
+      std::string dt, kind;
+      ss >> id >> dt >> kind >> ndim;
+      if (!ss || id != static_cast<int>(ir.tensors.size())) throw bad("tensor ids must be dense and ascending");
+      if (ndim < 0 || ndim > 8) throw bad("tensor rank out of range");
+      TensorDef t;
+      t.dtype = dt == "bf16" ? DType::kBFloat16 : dt == "i64" ? DType::kInt64 : dt == "f32" ? DType::kFloat : throw bad("unknown dtype " + dt);
+      t.kind = kind == "input" ? 0 : kind == "param" ? 1 : kind == "act" ? 2 : throw bad("unknown tensor kind " + kind);
+      for (int i = 0; i < ndim; ++i) {
+        int64_t d;
+        ss >> d;
+        if (!ss || d < -1) throw bad("bad dimension");
+        if (d == -1) ir.dynamic_rows = true;
+        t.shape.push_back(d);
+      }
+      std::string kv;
+      while (ss >> kv) {
+        auto eq = kv.find('=');
+        if (eq == std::string::npos) throw bad("expected key=value, got " + kv);
+        const std::string k = kv.substr(0, eq), v = kv.substr(eq + 1);
+        if (k == "file") t.file = v;
+        else if (k == "alias") t.alias_of = std::stoi(v);
+        else if (k == "offset") t.alias_off = std::stoll(v);
+        else throw bad("unknown tensor attribute " + k);
+      }
+      if (t.alias_of >= id) throw bad("an alias must point to an earlier tensor");
+      if (t.kind == 1 && t.file.empty() && t.alias_of < 0) throw bad("a parameter needs file=");
+      ir.tensors.push_back(std::move(t));
+    } else if (rec == "op") {
+      OpDef op;
+      ss >> op.type;
+      std::string kv;
+      while (ss >> kv) {
+        auto eq = kv.find('=');
+        if (eq == std::string::npos) throw bad("expected key=value, got " + kv);
+        const std::string k = kv.substr(0, eq), v = kv.substr(eq + 1);
+        if (k == "in") for (auto x : int_list(v)) op.in.push_back(static_cast<int>(x));
+        else if (k == "out") for (auto x : int_list(v)) op.out.push_back(static_cast<int>(x));
+        else op.attr[k] = v;
+      }
+      for (int t : op.in) if (t < -1 || t >= static_cast<int>(ir.tensors.size())) throw bad("operator input out of range");
+      for (int t : op.out) if (t < 0 || t >= static_cast<int>(ir.tensors.size())) throw bad("operator output out of range");
+      if (op.out.empty()) throw bad("operator without output");
+      ir.ops.push_back(std::move(op));
+    } else if (rec == "input" || rec == "output") {
+      int id;
+      ss >> id;
+      if (!ss || id < 0 || id >= static_cast<int>(ir.tensors.size())) throw bad("bad tensor id");
+      (rec == "input" ? ir.inputs : ir.outputs).push_back(id);
+    } else {
+      throw bad("unknown record " + rec);
+    }
+  }
+  if (ir.inputs.empty() || ir.outputs.empty()) throw std::runtime_error("graph.txt: the graph needs at least one input and one output");
+  return ir;
+}
+
+// The layer-list form: "linear in out wfile bfile act" / "layer_norm n gfile bfile eps" / "activation n act" lines, one
+// [rows, features] tensor flowing through them; translated to the operator IR with a row count bound later.
+IR parse_v1(std::istream& f) {
+  IR ir;
+  ir.dynamic_rows = true;
+  std::string line;
+  int64_t width = -1;
+  int cur = -1;
+  auto add_tensor = [&](DType dt, std::vector<int64_t> shape, int kind, const std::string& file) {
+    TensorDef t;
+    t.dtype = dt; t.shape = std::move(shape); t.kind = kind; t.file = file;
+    ir.tensors.push_back(t);
+    return static_cast<int>(ir.tensors.size()) - 1;
+  };
+  auto ensure_input = [&](int64_t feat) {
+    if (cur < 0) {
+      cur = add_tensor(DType::kBFloat16, {-1, feat}, 0, "");
+      ir.inputs.push_back(cur);
+    } else if (width != feat) {
+      throw std::runtime_error("layer width does not match the previous layer");
+    }
+  };
+  while (std::getline(f, line)) {
+    if (line.empty() || line[0] == '#') continue;
+    std::istringstream ss(line);
+    std::string kind;
+    ss >> kind;
+    OpDef op;
+    if (kind == "linear") {
+      int64_t in, out;
+      std::string wf, bf, act;
+      ss >> in >> out >> wf >> bf >> act;
+      ensure_input(in);
+      const int w = add_tensor(DType::kBFloat16, {out, in}, 1, wf);
+      const int b = bf == "-" ? -1 : add_tensor(DType::kBFloat16, {out}, 1, bf);
+      const int y = add_tensor(DType::kBFloat16, {-1, out}, 2, "");
+      op.type = "linear"; op.in = {cur, w, b, -1}; op.out = {y}; op.attr["act"] = act;
+      cur = y; width = out;
+    } else if (kind == "layer_norm") {
+      int64_t n;
+      std::string gf, bf, eps;
+      ss >> n >> gf >> bf >> eps;
+      ensure_input(n);
+      const int g = add_tensor(DType::kBFloat16, {n}, 1, gf);
+      const int b = add_tensor(DType::kBFloat16, {n}, 1, bf);
+      const int y = add_tensor(DType::kBFloat16, {-1, n}, 2, "");
+      op.type = "layer_norm"; op.in = {cur, g, b}; op.out = {y}; op.attr["eps"] = eps;
+      cur = y; width = n;
+    } else if (kind == "activation") {
+      int64_t n;
+      std::string act;
+      ss >> n >> act;
+      ensure_input(n);
+      const int y = add_tensor(DType::kBFloat16, {-1, n}, 2, "");
+      op.type = "unary"; op.in = {cur}; op.out = {y}; op.attr["fn"] = std::to_string(act_code(act));
+      cur = y; width = n;
+    } else {
+      throw std::runtime_error("unknown layer type: " + kind);
+    }
+    ir.ops.push_back(std::move(op));
+  }
+  if (ir.ops.empty()) throw std::runtime_error("empty graph");
+  ir.outputs.push_back(cur);
+  return ir;
+}
+
+// ------------------------------------------------------------------------------------------------ plan
+struct Range {
+  int64_t key, bytes;
+};
+bool overlaps(const Range& a, const Range& b) { return a.key < b.key + b.bytes && b.key < a.key + a.bytes; }
+
+struct PlannedOp {
+  const OpDef* def = nullptr;
+  std::vector<int> deps;        // indices of earlier operators this one must follow
+  int stream = 0;
+  int64_t workspace_bytes = 0;
+  void* workspace = nullptr;
+  std::vector<Range> reads, writes;
+};
+
+struct Plan {
+  int64_t rows = 0;
+  std::vector<std::vector<int64_t>> shape;     // resolved shapes per tensor
+  std::vector<int> root;                       // storage root per tensor
+  std::vector<int64_t> byte_off;               // byte offset of the tensor inside its root's storage
+  std::vector<void*> base;                     // per root: planned address (activations); null for inputs (bound per call)
+  std::vector<PlannedOp> ops;
+  PlanStats stats;
+};
+
+int64_t numel(const std::vector<int64_t>& s) {
+  int64_t n = 1;
+  for (auto d : s) n *= d;
+  return n;
+}
+
+}  // namespace
+
+struct Graph::Impl {
+  IR ir;
+  std::string dir;
+  int device = 0;
+  int n_streams = 2;
+  std::vector<std::shared_ptr<void>> params;   // per tensor id (params only)
+  std::vector<void*> allocators;              // one pool per stream of the plan
+  void* executor = nullptr;
+  std::vector<cudaStream_t> streams;
+  std::vector<cudaEvent_t> events;             // one per planned operator
+  std::unique_ptr<Plan> plan;
+  std::mutex run_mu;
+  // per call
+  std::vector<void*> bound;                    // per root: address of inputs for the running call
+  std::mutex err_mu;
+  std::string error;
+
+  ~Impl() {
+    if (executor) ofc_executor_destroy(executor);
+    for (auto e : events) cudaEventDestroy(e);
+    for (auto s : streams) cudaStreamDestroy(s);
+    for (void* al : allocators) ofc_allocator_destroy(al);
+  }
+
+  void fail(const std::string& msg) {
+    std::lock_guard<std::mutex> g(err_mu);
+    if (error.empty()) error = msg;
+  }
+  bool failed() {
+    std::lock_guard<std::mutex> g(err_mu);
+    return !error.empty();
+  }
+
+  void compile(int64_t rows);
+  void* addr(int tensor) const {
+    const int r = plan->root[static_cast<size_t>(tensor)];
+    char* b = static_cast<char*>(plan->base[static_cast<size_t>(r)] ? plan->base[static_cast<size_t>(r)] : bound[static_cast<size_t>(r)]);
+    return b + plan->byte_off[static_cast<size_t>(tensor)];
+  }
+  void run_op(int index);
+  void run_op_device(const PlannedOp& p, cudaStream_t s);
+  void run_op_host(const PlannedOp& p);
+};
+
+namespace {
+
+int64_t workspace_for(const OpDef& op, const Plan& plan) {
+  if (op.type == "layer_norm") {
+    const auto& s = plan.shape[static_cast<size_t>(op.in[0])];
+    return numel(s) / s.back() * 8;
+  }
+  if (op.type == "attention") {
+    const auto& q = plan.shape[static_cast<size_t>(op.in[0])];
+    return q[0] * q[1] * q[2] * 4;
+  }
+  return 0;
+}
+
+void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
+  auto need = [&](bool c, const std::string& why) {
+    if (!c) throw std::runtime_error("operator " + op.type + ": " + why);
+  };
+  auto shp = [&](int t) -> const std::vector<int64_t>& { return plan.shape[static_cast<size_t>(t)]; };
+  auto dt = [&](int t) { return ir.tensors[static_cast<size_t>(t)].dtype; };
+  const std::string& t = op.type;
+  if (t == "linear") {
+    need(op.in.size() >= 2 && op.in[0] >= 0 && op.in[1] >= 0, "needs x and weight");
+    const auto& x = shp(op.in[0]);
+    const auto& w = shp(op.in[1]);
+    need(w.size() == 2 && !x.empty() && x.back() == w[1], "weight must be [N, K] with K the last axis of x");
+    need(numel(shp(op.out[0])) == numel(x) / w[1] * w[0], "output size mismatch");
+    if (op.in.size() > 2 && op.in[2] >= 0) need(numel(shp(op.in[2])) == w[0], "bias must have N elements");
+    if (op.in.size() > 3 && op.in[3] >= 0) need(numel(shp(op.in[3])) == numel(shp(op.out[0])), "residual must match the output");
+  } else if (t == "matmul") {
+    need(op.in.size() == 2, "needs two inputs");
+    const auto& a = shp(op.in[0]);
+    const auto& b = shp(op.in[1]);
+    need(a.size() >= 2 && b.size() >= 2, "operands need at least two axes");
+    const bool tb = attr_int(op, "tb", 0) != 0;
+    const int64_t K = a.back(), N = tb ? b[b.size() - 2] : b.back(), Kb = tb ? b.back() : b[b.size() - 2];
+    need(K == Kb, "inner dimensions differ");
+    const int64_t batch_a = numel(a) / (a[a.size() - 2] * K), batch_b = numel(b) / (N * K);
+    need(batch_b == 1 || batch_b == batch_a, "batch dimensions differ");
+    need(numel(shp(op.out[0])) == batch_a * a[a.size() - 2] * N, "output size mismatch");
+  } else if (t == "layer_norm") {
+    need(op.in.size() == 3, "needs x, gamma, beta");
+    need(numel(shp(op.in[1])) == shp(op.in[0]).back() && numel(shp(op.in[2])) == shp(op.in[0]).back(), "gamma / beta length");
+  } else if (t == "embedding") {
+    need(op.in.size() == 2 && dt(op.in[0]) == DType::kInt64 && shp(op.in[1]).size() == 2, "needs int64 ids and a [rows, cols] table");
+    need(numel(shp(op.out[0])) == numel(shp(op.in[0])) * shp(op.in[1])[1], "output size mismatch");
+  } else if (t == "binary") {
+    need(op.in.size() == 2, "needs two inputs");
+    const int64_t n = numel(shp(op.in[0])), nb = numel(shp(op.in[1]));
+    const int64_t mode = attr_int(op, "bmode", 0), cols = attr_int(op, "cols", 1);
+    need(n == numel(shp(op.out[0])), "the first operand must have the output's shape");
+    need((mode == 0 && nb == n) || (mode == 1 && nb == cols && n % cols == 0) || (mode == 2 && cols > 0 && nb * cols == n), "broadcast description does not match the shapes");
+  } else if (t == "unary" || t == "softmax") {
+    need(op.in.size() == 1 && numel(shp(op.in[0])) == numel(shp(op.out[0])), "shape mismatch");
+  } else if (t == "attention") {
+    need(op.in.size() == 3, "needs q, k, v");
+    const auto& q = shp(op.in[0]);
+    const auto& k = shp(op.in[1]);
+    need(q.size() == 4 && k.size() == 4 && shp(op.in[2]) == k && q[0] == k[0] && q[3] == k[3] && q[2] % k[2] == 0, "q [B,Sq,H,D], k / v [B,Sk,Hk,D]");
+    need(numel(shp(op.out[0])) == numel(q), "output size mismatch");
+  } else if (t == "copy") {
+    need(op.in.size() == 1, "needs one input");
+    const auto s = int_list(attr_str(op, "shape", "")), is = int_list(attr_str(op, "in_strides", "")), os = int_list(attr_str(op, "out_strides", ""));
+    need(!s.empty() && s.size() <= 5 && is.size() == s.size() && os.size() == s.size(), "shape / in_strides / out_strides of 1..5 axes");
+    // bounds of both views
+    int64_t in_max = attr_int(op, "in_offset", 0), out_max = attr_int(op, "out_offset", 0);
+    for (size_t i = 0; i < s.size(); ++i) {
+      need(s[i] > 0 && is[i] >= 0 && os[i] >= 0, "non-positive extent or negative stride");
+      in_max += (s[i] - 1) * is[i];
+      out_max += (s[i] - 1) * os[i];
+    }
+    need(in_max < numel(shp(op.in[0])) && out_max < numel(shp(op.out[0])), "view reaches outside its tensor");
+    need(dt(op.in[0]) == dt(op.out[0]), "dtype mismatch");
+  } else {
+    throw std::runtime_error("unknown operator type: " + t);
+  }
+}
+
+}  // namespace
+
+void Graph::Impl::compile(int64_t rows) {
+  auto p = std::make_unique<Plan>();
+  p->rows = rows;
+  const size_t nt = ir.tensors.size();
+  p->shape.resize(nt);
+  p->root.resize(nt);
+  p->byte_off.assign(nt, 0);
+  p->base.assign(nt, nullptr);
+  for (size_t i = 0; i < nt; ++i) {
+    p->shape[i] = ir.tensors[i].shape;
+    for (auto& d : p->shape[i])
+      if (d == -1) {
+        if (rows <= 0) throw std::runtime_error("the graph has an unbound row count");
+        d = rows;
+      }
+    const TensorDef& t = ir.tensors[i];
+    if (t.alias_of >= 0) {
+      const size_t a = static_cast<size_t>(t.alias_of);
+      p->root[i] = p->root[a];
+      p->byte_off[i] = p->byte_off[a] + t.alias_off * SizeOf(ir.tensors[a].dtype);
+      const int r = p->root[i];
+      if (p->byte_off[i] + numel(p->shape[i]) * SizeOf(t.dtype) > numel(p->shape[static_cast<size_t>(r)]) * SizeOf(ir.tensors[static_cast<size_t>(r)].dtype))
+        throw std::runtime_error("tensor " + std::to_string(i) + ": alias reaches outside its source");
+    } else {
+      p->root[i] = static_cast<int>(i);
+    }
+  }
+  auto root_bytes = [&](int r) { return numel(p->shape[static_cast<size_t>(r)]) * SizeOf(ir.tensors[static_cast<size_t>(r)].dtype); };
+  auto root_kind = [&](int r) { return ir.tensors[static_cast<size_t>(r)].kind; };
+
+  const int n_ops = static_cast<int>(ir.ops.size());
+  p->ops.resize(static_cast<size_t>(n_ops));
+  // 1. liveness of activation storages in operator order
+  std::vector<int> first(nt, -1), last(nt, -1);
+  for (int i = 0; i < n_ops; ++i) {
+    const OpDef& op = ir.ops[static_cast<size_t>(i)];
+    check_op(op, ir, *p);
+    p->ops[static_cast<size_t>(i)].def = &op;
+    for (int t : op.in) {
+      if (t < 0) continue;
+      const int r = p->root[static_cast<size_t>(t)];
+      if (root_kind(r) == 2) {
+        if (first[static_cast<size_t>(r)] < 0) throw std::runtime_error("operator " + op.type + " reads tensor " + std::to_string(t) + " before it is written");
+        last[static_cast<size_t>(r)] = i;
+      }
+    }
+    for (int t : op.out) {
+      const int r = p->root[static_cast<size_t>(t)];
+      if (root_kind(r) != 2) throw std::runtime_error("operator " + op.type + " writes a tensor that is not an activation");
+      if (first[static_cast<size_t>(r)] < 0) first[static_cast<size_t>(r)] = i;
+      last[static_cast<size_t>(r)] = i;
+    }
+  }
+  for (int t : ir.outputs) {
+    const int r = p->root[static_cast<size_t>(t)];
+    if (root_kind(r) == 2) {
+      if (first[static_cast<size_t>(r)] < 0) throw std::runtime_error("an output is never written");
+      last[static_cast<size_t>(r)] = n_ops;   // read back after the last operator
+    }
+  }
+  // Conflicts (read-after-write, write-after-read, write-after-write) between the ranges two operators touch; an edge that
+  // a dependency already recorded implies directly is left out.
+  auto add_deps = [&](std::vector<std::vector<int>>& deps_out) {
+    deps_out.assign(static_cast<size_t>(n_ops), {});
+    for (int i = 0; i < n_ops; ++i) {
+      const PlannedOp& a = p->ops[static_cast<size_t>(i)];
+      std::vector<int>& mine = deps_out[static_cast<size_t>(i)];
+      for (int j = i - 1; j >= 0; --j) {
+        const PlannedOp& b = p->ops[static_cast<size_t>(j)];
+        bool conflict = false;
+        for (const Range& w : b.writes) {
+          for (const Range& r : a.reads) conflict = conflict || overlaps(w, r);
+          for (const Range& r : a.writes) conflict = conflict || overlaps(w, r);
+        }
+        for (const Range& r : b.reads)
+          for (const Range& w : a.writes) conflict = conflict || overlaps(r, w);
+        if (!conflict) continue;
+        bool implied = false;
+        for (int d : mine) {
+          const auto& dd = deps_out[static_cast<size_t>(d)];
+          if (std::find(dd.begin(), dd.end(), j) != dd.end()) { implied = true; break; }
+        }
+        if (!implied) mine.push_back(j);   // descending order
+      }
+    }
+  };
+  auto virtual_range = [&](int t) {   // a storage as a range of its own, wherever it will live
+    const int r = p->root[static_cast<size_t>(t)];
+    return Range{(int64_t{1} << 62) + static_cast<int64_t>(r) * (int64_t{1} << 40), std::max<int64_t>(root_bytes(r), 1)};
+  };
+  // 2. data dependencies (on storages, before any memory is shared) and from them the streams: an operator continues the
+  //    chain of its most recent producer that nobody continued yet, else it opens / takes another stream
+  for (int i = 0; i < n_ops; ++i) {
+    PlannedOp& po = p->ops[static_cast<size_t>(i)];
+    for (int t : po.def->in)
+      if (t >= 0 && root_kind(p->root[static_cast<size_t>(t)]) != 1) po.reads.push_back(virtual_range(t));   // parameters never change
+    for (int t : po.def->out) po.writes.push_back(virtual_range(t));
+  }
+  {
+    std::vector<std::vector<int>> data_deps;
+    add_deps(data_deps);
+    std::vector<char> continued(static_cast<size_t>(n_ops), 0);
+    int next_stream = 0, used = 0;
+    for (int i = 0; i < n_ops; ++i) {
+      PlannedOp& a = p->ops[static_cast<size_t>(i)];
+      int chosen = -1;
+      for (int d : data_deps[static_cast<size_t>(i)])
+        if (!continued[static_cast<size_t>(d)]) { chosen = d; break; }
+      if (chosen >= 0) {
+        a.stream = p->ops[static_cast<size_t>(chosen)].stream;
+        continued[static_cast<size_t>(chosen)] = 1;
+      } else {
+        a.stream = next_stream;
+        next_stream = (next_stream + 1) % n_streams;
+      }
+      used = std::max(used, a.stream + 1);
+    }
+    p->stats.n_streams_used = used;
+  }
+  // 3. addresses from the caching allocator, one pool per stream so that sharing memory never ties two streams together:
+  //    allocate at the first write (in the pool of the writer's stream), free after the last access
+  for (void* al : allocators) ofc_allocator_destroy(al);
+  allocators.clear();
+  if (device >= 0) check_cuda(cudaSetDevice(device), "cudaSetDevice");
+  for (int sidx = 0; sidx < p->stats.n_streams_used; ++sidx) {
+    void* al = ofc_allocator_create(device < 0 ? 0 : 1, int64_t{32} << 20);
+    if (!al) throw std::runtime_error(std::string("allocator: ") + ofc_last_error());
+    allocators.push_back(al);
+  }
+  auto in_use_now = [&] {
+    int64_t total = 0;
+    for (void* al : allocators) {
+      int64_t reserved = 0, in_use = 0, chunks = 0, free_blocks = 0;
+      ofc_allocator_stats(al, &reserved, &in_use, &chunks, &free_blocks);
+      total += in_use;
+    }
+    return total;
+  };
+  std::vector<std::vector<int>> born(static_cast<size_t>(n_ops)), dies(static_cast<size_t>(n_ops) + 1);
+  std::vector<int> pool(nt, 0);
+  for (size_t r = 0; r < nt; ++r)
+    if (first[r] >= 0) {
+      born[static_cast<size_t>(first[r])].push_back(static_cast<int>(r));
+      dies[static_cast<size_t>(last[r])].push_back(static_cast<int>(r));
+    }
+  for (int i = 0; i < n_ops; ++i) {
+    PlannedOp& po = p->ops[static_cast<size_t>(i)];
+    void* al = allocators[static_cast<size_t>(po.stream)];
+    for (int r : born[static_cast<size_t>(i)]) {
+      void* ptr = ofc_allocator_alloc(al, std::max<int64_t>(root_bytes(r), 16));
+      if (!ptr) throw std::runtime_error(std::string("allocator: ") + ofc_last_error());
+      p->base[static_cast<size_t>(r)] = ptr;
+      pool[static_cast<size_t>(r)] = po.stream;
+      p->stats.activation_bytes += root_bytes(r);
+    }
+    po.workspace_bytes = workspace_for(*po.def, *p);
+    if (po.workspace_bytes > 0) {
+      po.workspace = ofc_allocator_alloc(al, po.workspace_bytes);
+      if (!po.workspace) throw std::runtime_error(std::string("allocator: ") + ofc_last_error());
+    }
+    p->stats.arena_bytes = std::max(p->stats.arena_bytes, in_use_now());
+    // the real ranges, taken while everything this operator touches is still allocated
+    auto range_of = [&](int t) {
+      const int r = p->root[static_cast<size_t>(t)];
+      if (p->base[static_cast<size_t>(r)]) return Range{reinterpret_cast<int64_t>(p->base[static_cast<size_t>(r)]), std::max<int64_t>(root_bytes(r), 1)};
+      return virtual_range(t);
+    };
+    po.reads.clear();
+    po.writes.clear();
+    for (int t : po.def->in)
+      if (t >= 0 && root_kind(p->root[static_cast<size_t>(t)]) != 1) po.reads.push_back(range_of(t));
+    for (int t : po.def->out) po.writes.push_back(range_of(t));
+    if (po.workspace) po.writes.push_back(Range{reinterpret_cast<int64_t>(po.workspace), po.workspace_bytes});
+    if (po.workspace) ofc_allocator_free(al, po.workspace);
+    for (int r : dies[static_cast<size_t>(i)]) ofc_allocator_free(allocators[static_cast<size_t>(pool[static_cast<size_t>(r)])], p->base[static_cast<size_t>(r)]);
+  }
+  // outputs (dies[n_ops]) stay allocated: they are read after the run
+  // 4. the dependencies the scheduler enforces: conflicts on addresses, which cover the data dependencies and add the
+  //    ones that memory sharing introduces (a buffer may only be rewritten after the last reader of its previous tenant)
+  {
+    std::vector<std::vector<int>> deps;
+    add_deps(deps);
+    for (int i = 0; i < n_ops; ++i) {
+      p->ops[static_cast<size_t>(i)].deps = deps[static_cast<size_t>(i)];
+      p->stats.n_dependencies += static_cast<int64_t>(deps[static_cast<size_t>(i)].size());
+    }
+  }
+  p->stats.n_ops = n_ops;
+  p->stats.n_tensors = static_cast<int64_t>(nt);
+  // 5. runtime objects
+  if (device >= 0) {
+    while (static_cast<int>(streams.size()) < n_streams) {
+      cudaStream_t s;
+      check_cuda(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate");
+      streams.push_back(s);
+    }
+    while (static_cast<int>(events.size()) < n_ops) {
+      cudaEvent_t e;
+      check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+      events.push_back(e);
+    }
+  }
+  if (!executor) {
+    executor = ofc_executor_create(n_streams);
+    if (!executor) throw std::runtime_error(std::string("executor: ") + ofc_last_error());
+  }
+  plan = std::move(p);
+}
+
+// ------------------------------------------------------------------------------------------------ operators on the GPU
+void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
+  const OpDef& op = *p.def;
+  auto shp = [&](int t) -> const std::vector<int64_t>& { return plan->shape[static_cast<size_t>(t)]; };
+  auto ok = [&](int rc) {
+    if (rc != 0) throw std::runtime_error(op.type + ": " + ofb_last_error());
+  };
+  const std::string& t = op.type;
+  if (t == "linear") {
+    const auto& w = shp(op.in[1]);
+    const int64_t K = w[1], N = w[0], M = numel(shp(op.in[0])) / K;
+    OfbGemmArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.A = addr(op.in[0]); a.lda = K;
+    a.B = addr(op.in[1]); a.ldb = K;
+    a.C = addr(op.out[0]); a.ldc = N;
+    a.bias = op.in.size() > 2 && op.in[2] >= 0 ? addr(op.in[2]) : nullptr;
+    if (op.in.size() > 3 && op.in[3] >= 0) { a.residual = addr(op.in[3]); a.ldr = N; }
+    a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
+    a.act = act_code(attr_str(op, "act", "none"));
+    a.alpha = 1.f;
+    ok(ofb_gemm_bf16(&a, s));
+  } else if (t == "matmul") {
+    const auto& as = shp(op.in[0]);
+    const auto& bs = shp(op.in[1]);
+    const bool tb = attr_int(op, "tb", 0) != 0;
+    const int64_t M = as[as.size() - 2], K = as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
+    const int64_t batch = numel(as) / (M * K), batch_b = numel(bs) / (N * K);
+    for (int64_t b = 0; b < batch; ++b) {
+      OfbGemmArgs a;
+      std::memset(&a, 0, sizeof(a));
+      a.A = static_cast<char*>(addr(op.in[0])) + b * M * K * 2; a.lda = K;
+      a.B = static_cast<char*>(addr(op.in[1])) + (batch_b == 1 ? 0 : b) * N * K * 2;
+      a.ldb = tb ? K : N;
+      a.b_mn_major = tb ? 0 : 1;
+      a.C = static_cast<char*>(addr(op.out[0])) + b * M * N * 2; a.ldc = N;
+      a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
+      a.alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
+      ok(ofb_gemm_bf16(&a, s));
+    }
+  } else if (t == "layer_norm") {
+    const auto& x = shp(op.in[0]);
+    const int64_t cols = x.back(), rows = numel(x) / cols;
+    float* mean = static_cast<float*>(p.workspace);
+    ok(ofb_layer_norm_fwd(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), addr(op.out[0]), mean, mean + rows, static_cast<int>(rows),
+                          static_cast<int>(cols), static_cast<float>(attr_float(op, "eps", 1e-5)), s));
+  } else if (t == "embedding") {
+    const auto& tb = shp(op.in[1]);
+    ok(ofb_graph_gather_rows(static_cast<const long long*>(addr(op.in[0])), addr(op.in[1]), addr(op.out[0]), numel(shp(op.in[0])),
+                             static_cast<int>(tb[1]), tb[0], s));
+  } else if (t == "binary") {
+    ok(ofb_graph_binary(addr(op.in[0]), addr(op.in[1]), addr(op.out[0]), numel(shp(op.in[0])), attr_int(op, "cols", 1),
+                        static_cast<int>(attr_int(op, "bmode", 0)), static_cast<int>(attr_int(op, "fn", 0)), s));
+  } else if (t == "unary") {
+    ok(ofb_graph_unary(addr(op.in[0]), addr(op.out[0]), numel(shp(op.in[0])), static_cast<int>(attr_int(op, "fn", 0)),
+                       static_cast<float>(attr_float(op, "alpha", 1.0)), s));
+  } else if (t == "softmax") {
+    const auto& x = shp(op.in[0]);
+    const int64_t cols = x.back(), rows = numel(x) / cols;
+    ok(ofb_softmax_fwd(addr(op.in[0]), nullptr, nullptr, 0, addr(op.out[0]), nullptr, rows, static_cast<int>(cols), 0, 0, 0,
+                       static_cast<float>(attr_float(op, "scale", 1.0)), 0.f, 1.f, s));
+  } else if (t == "attention") {
+    const auto& q = shp(op.in[0]);
+    const auto& k = shp(op.in[1]);
+    const int64_t qs = attr_int(op, "q_stride", q[2] * q[3]), ks = attr_int(op, "kv_stride", k[2] * k[3]);
+    ok(ofb_fmha_fwd_ex(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), qs, ks, addr(op.out[0]), static_cast<float*>(p.workspace), nullptr,
+                       static_cast<int>(q[0]), static_cast<int>(q[1]), static_cast<int>(k[1]), static_cast<int>(q[2]), static_cast<int>(k[2]),
+                       static_cast<int>(q[3]), static_cast<int>(attr_int(op, "causal", 0)),
+                       static_cast<float>(attr_float(op, "scale", 1.0 / std::sqrt(static_cast<double>(q[3])))), 0.f, 0ull, 0u, s));
+  } else if (t == "copy") {
+    const auto sh = int_list(attr_str(op, "shape", "")), is = int_list(attr_str(op, "in_strides", "")), os = int_list(attr_str(op, "out_strides", ""));
+    std::vector<long long> a(sh.begin(), sh.end()), b(is.begin(), is.end()), c(os.begin(), os.end());
+    ok(ofb_graph_strided_copy(addr(op.in[0]), addr(op.out[0]), static_cast<int>(a.size()), a.data(), b.data(), attr_int(op, "in_offset", 0),
+                              c.data(), attr_int(op, "out_offset", 0), static_cast<int>(SizeOf(ir.tensors[static_cast<size_t>(op.in[0])].dtype)), s));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ operators on the host
+namespace {
+
+inline float ldb(const void* p, int64_t i) { return from_bf16(static_cast<const uint16_t*>(p)[i]); }
+inline void stb(void* p, int64_t i, float v) { static_cast<uint16_t*>(p)[i] = to_bf16(v); }
+
+float host_unary(float x, int fn, float alpha) {
+  switch (fn) {
+    case 0: return x * alpha;
+    case 1: return 0.5f * x * (1.f + std::erf(x * 0.7071067811865476f));
+    case 2: return 0.5f * x * (1.f + std::tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case 3: return x > 0.f ? x : 0.f;
+    case 4: return std::tanh(x);
+    case 5: return 1.f / (1.f + std::exp(-x));
+    case 6: return x / (1.f + std::exp(-x));
+    case 7: return x + alpha;
+    case 8: return std::exp(x);
+    case 9: return 1.f / std::sqrt(x);
+    case 10: return x * x;
+    default: return x;
+  }
+}
+float host_binary(float a, float b, int op) {
+  switch (op) {
+    case 0: return a + b;
+    case 1: return a - b;
+    case 2: return a * b;
+    case 3: return a / b;
+    case 4: return a > b ? a : b;
+    default: return a < b ? a : b;
+  }
+}
+
+}  // namespace
+
+void Graph::Impl::run_op_host(const PlannedOp& p) {
+  const OpDef& op = *p.def;
+  auto shp = [&](int t) -> const std::vector<int64_t>& { return plan->shape[static_cast<size_t>(t)]; };
+  const std::string& t = op.type;
+  if (t == "linear") {
+    const auto& w = shp(op.in[1]);
+    const int64_t K = w[1], N = w[0], M = numel(shp(op.in[0])) / K;
+    const void *x = addr(op.in[0]), *wt = addr(op.in[1]);
+    const void* bias = op.in.size() > 2 && op.in[2] >= 0 ? addr(op.in[2]) : nullptr;
+    const void* res = op.in.size() > 3 && op.in[3] >= 0 ? addr(op.in[3]) : nullptr;
+    const int act = act_code(attr_str(op, "act", "none"));
+    void* y = addr(op.out[0]);
+    std::vector<float> xr(static_cast<size_t>(K));
+    for (int64_t m = 0; m < M; ++m) {
+      for (int64_t k = 0; k < K; ++k) xr[static_cast<size_t>(k)] = ldb(x, m * K + k);
+      for (int64_t n = 0; n < N; ++n) {
+        float acc = 0.f;
+        for (int64_t k = 0; k < K; ++k) acc += xr[static_cast<size_t>(k)] * ldb(wt, n * K + k);
+        if (bias) acc += ldb(bias, n);
+        if (act) acc = host_unary(acc, act, 1.f);
+        if (res) acc += ldb(res, m * N + n);
+        stb(y, m * N + n, acc);
+      }
+    }
+  } else if (t == "matmul") {
+    const auto& as = shp(op.in[0]);
+    const auto& bs = shp(op.in[1]);
+    const bool tb = attr_int(op, "tb", 0) != 0;
+    const int64_t M = as[as.size() - 2], K = as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
+    const int64_t batch = numel(as) / (M * K), batch_b = numel(bs) / (N * K);
+    const float alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
+    const void *a = addr(op.in[0]), *b = addr(op.in[1]);
+    void* y = addr(op.out[0]);
+    for (int64_t bi = 0; bi < batch; ++bi) {
+      const int64_t ao = bi * M * K, bo = (batch_b == 1 ? 0 : bi) * N * K, yo = bi * M * N;
+      for (int64_t m = 0; m < M; ++m)
+        for (int64_t n = 0; n < N; ++n) {
+          float acc = 0.f;
+          for (int64_t k = 0; k < K; ++k) acc += ldb(a, ao + m * K + k) * (tb ? ldb(b, bo + n * K + k) : ldb(b, bo + k * N + n));
+          stb(y, yo + m * N + n, acc * alpha);
+        }
+    }
+  } else if (t == "layer_norm") {
+    const auto& x = shp(op.in[0]);
+    const int64_t cols = x.back(), rows = numel(x) / cols;
+    const float eps = static_cast<float>(attr_float(op, "eps", 1e-5));
+    const void *xp = addr(op.in[0]), *g = addr(op.in[1]), *b = addr(op.in[2]);
+    void* y = addr(op.out[0]);
+    for (int64_t r = 0; r < rows; ++r) {
+      double mean = 0, var = 0;
+      for (int64_t c = 0; c < cols; ++c) mean += ldb(xp, r * cols + c);
+      mean /= static_cast<double>(cols);
+      for (int64_t c = 0; c < cols; ++c) {
+        const double d = ldb(xp, r * cols + c) - mean;
+        var += d * d;
+      }
+      const float rstd = 1.f / std::sqrt(static_cast<float>(var / static_cast<double>(cols)) + eps);
+      for (int64_t c = 0; c < cols; ++c)
+        stb(y, r * cols + c, (ldb(xp, r * cols + c) - static_cast<float>(mean)) * rstd * ldb(g, c) + ldb(b, c));
+    }
+  } else if (t == "embedding") {
+    const auto& tb = shp(op.in[1]);
+    const int64_t n = numel(shp(op.in[0])), cols = tb[1];
+    const int64_t* ids = static_cast<const int64_t*>(addr(op.in[0]));
+    const uint16_t* table = static_cast<const uint16_t*>(addr(op.in[1]));
+    uint16_t* y = static_cast<uint16_t*>(addr(op.out[0]));
+    for (int64_t i = 0; i < n; ++i) {
+      if (ids[i] >= 0 && ids[i] < tb[0]) std::memcpy(y + i * cols, table + ids[i] * cols, static_cast<size_t>(cols) * 2);
+      else std::memset(y + i * cols, 0, static_cast<size_t>(cols) * 2);
+    }
+  } else if (t == "binary") {
+    const int64_t n = numel(shp(op.in[0])), cols = attr_int(op, "cols", 1);
+    const int mode = static_cast<int>(attr_int(op, "bmode", 0)), fn = static_cast<int>(attr_int(op, "fn", 0));
+    const void *a = addr(op.in[0]), *b = addr(op.in[1]);
+    void* y = addr(op.out[0]);
+    for (int64_t i = 0; i < n; ++i) stb(y, i, host_binary(ldb(a, i), ldb(b, mode == 0 ? i : (mode == 1 ? i % cols : i / cols)), fn));
+  } else if (t == "unary") {
+    const int64_t n = numel(shp(op.in[0]));
+    const int fn = static_cast<int>(attr_int(op, "fn", 0));
+    const float alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
+    const void* x = addr(op.in[0]);
+    void* y = addr(op.out[0]);
+    for (int64_t i = 0; i < n; ++i) stb(y, i, host_unary(ldb(x, i), fn, alpha));
+  } else if (t == "softmax") {
+    const auto& x = shp(op.in[0]);
+    const int64_t cols = x.back(), rows = numel(x) / cols;
+    const float scale = static_cast<float>(attr_float(op, "scale", 1.0));
+    const void* xp = addr(op.in[0]);
+    void* y = addr(op.out[0]);
+    std::vector<float> e(static_cast<size_t>(cols));
+    for (int64_t r = 0; r < rows; ++r) {
+      float mx = -INFINITY, sum = 0.f;
+      for (int64_t c = 0; c < cols; ++c) mx = std::max(mx, ldb(xp, r * cols + c) * scale);
+      for (int64_t c = 0; c < cols; ++c) sum += (e[static_cast<size_t>(c)] = std::exp(ldb(xp, r * cols + c) * scale - mx));
+      for (int64_t c = 0; c < cols; ++c) stb(y, r * cols + c, e[static_cast<size_t>(c)] / sum);
+    }
+  } else if (t == "attention") {
+    const auto& q = shp(op.in[0]);
+    const auto& k = shp(op.in[1]);
+    const int64_t B = q[0], Sq = q[1], H = q[2], D = q[3], Sk = k[1], Hk = k[2];
+    const int64_t qs = attr_int(op, "q_stride", H * D), ks = attr_int(op, "kv_stride", Hk * D);
+    const bool causal = attr_int(op, "causal", 0) != 0;
+    const float scale = static_cast<float>(attr_float(op, "scale", 1.0 / std::sqrt(static_cast<double>(D))));
+    const void *qp = addr(op.in[0]), *kp = addr(op.in[1]), *vp = addr(op.in[2]);
+    void* y = addr(op.out[0]);
+    std::vector<float> sc(static_cast<size_t>(Sk)), acc(static_cast<size_t>(D));
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t h = 0; h < H; ++h) {
+        const int64_t hk = h / (H / Hk);
+        for (int64_t i = 0; i < Sq; ++i) {
+          const int64_t vis = causal ? std::min<int64_t>(Sk, i + (Sk - Sq) + 1) : Sk;
+          float mx = -INFINITY;
+          for (int64_t j = 0; j < vis; ++j) {
+            float s = 0.f;
+            for (int64_t d = 0; d < D; ++d) s += ldb(qp, (b * Sq + i) * qs + h * D + d) * ldb(kp, (b * Sk + j) * ks + hk * D + d);
+            sc[static_cast<size_t>(j)] = s * scale;
+            mx = std::max(mx, s * scale);
+          }
+          float sum = 0.f;
+          std::fill(acc.begin(), acc.end(), 0.f);
+          for (int64_t j = 0; j < vis; ++j) {
+            const float e = std::exp(sc[static_cast<size_t>(j)] - mx);
+            sum += e;
+            for (int64_t d = 0; d < D; ++d) acc[static_cast<size_t>(d)] += e * ldb(vp, (b * Sk + j) * ks + hk * D + d);
+          }
+          for (int64_t d = 0; d < D; ++d) stb(y, ((b * Sq + i) * H + h) * D + d, vis > 0 ? acc[static_cast<size_t>(d)] / sum : 0.f);
+        }
+      }
+  } else if (t == "copy") {
+    const auto sh = int_list(attr_str(op, "shape", "")), is = int_list(attr_str(op, "in_strides", "")), os = int_list(attr_str(op, "out_strides", ""));
+    const int64_t esz = SizeOf(ir.tensors[static_cast<size_t>(op.in[0])].dtype);
+    const char* x = static_cast<const char*>(addr(op.in[0]));
+    char* y = static_cast<char*>(addr(op.out[0]));
+    const int64_t n = numel(sh), io = attr_int(op, "in_offset", 0), oo = attr_int(op, "out_offset", 0);
+    for (int64_t i = 0; i < n; ++i) {
+      int64_t r = i, in = io, out = oo;
+      for (int d = static_cast<int>(sh.size()) - 1; d >= 0; --d) {
+        const int64_t c = r % sh[static_cast<size_t>(d)];
+        r /= sh[static_cast<size_t>(d)];
+        in += c * is[static_cast<size_t>(d)];
+        out += c * os[static_cast<size_t>(d)];
+      }
+      std::memcpy(y + out * esz, x + in * esz, static_cast<size_t>(esz));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ execution
+namespace {
+struct TaskArg {
+  Graph::Impl* impl;
+  int index;
+};
+void task_trampoline(void* arg) {
+  auto* a = static_cast<TaskArg*>(arg);
+  a->impl->run_op(a->index);
+}
+}  // namespace
+
+void Graph::Impl::run_op(int index) {
+  if (failed()) return;   // an earlier operator failed: let the rest drain
+  const PlannedOp& p = plan->ops[static_cast<size_t>(index)];
+  try {
+    if (device < 0) {
+      run_op_host(p);
+      return;
+    }
+    check_cuda(cudaSetDevice(device), "cudaSetDevice");
+    cudaStream_t s = streams[static_cast<size_t>(p.stream)];
+    // the scheduler ran every dependency's host side already, so its event has been recorded
+    for (int d : p.deps)
+      if (plan->ops[static_cast<size_t>(d)].stream != p.stream) check_cuda(cudaStreamWaitEvent(s, events[static_cast<size_t>(d)], 0), "cudaStreamWaitEvent");
+    run_op_device(p, s);
+    check_cuda(cudaEventRecord(events[static_cast<size_t>(index)], s), "cudaEventRecord");
+  } catch (const std::exception& e) {
+    fail(e.what());
+  }
+}
+
+Graph Graph::Load(const std::string& dir, int device, int n_streams) {
+  std::ifstream f(dir + "/graph.txt");
+  if (!f) throw std::runtime_error("cannot open " + dir + "/graph.txt");
+  std::string line;
+  std::getline(f, line);
+  auto impl = std::make_shared<Impl>();
+  impl->dir = dir;
+  impl->device = device;
+  impl->n_streams = std::max(1, std::min(n_streams, 16));
+  if (line.rfind("oneflow_b200 graph v2", 0) == 0) impl->ir = parse_v2(f);
+  else if (line.rfind("oneflow_b200 inference graph v1", 0) == 0) impl->ir = parse_v1(f);
+  else throw std::runtime_error("not an exported graph: " + dir);
+  // parameters
+  impl->params.resize(impl->ir.tensors.size());
+  for (size_t i = 0; i < impl->ir.tensors.size(); ++i) {
+    const TensorDef& t = impl->ir.tensors[i];
+    if (t.kind != 1 || t.alias_of >= 0) continue;
+    const size_t bytes = static_cast<size_t>(numel(t.shape) * SizeOf(t.dtype));
+    std::ifstream pf(dir + "/" + t.file, std::ios::binary);
+    if (!pf) throw std::runtime_error("cannot open " + dir + "/" + t.file);
+    std::vector<char> host(bytes);
+    pf.read(host.data(), static_cast<std::streamsize>(bytes));
+    if (static_cast<size_t>(pf.gcount()) != bytes) throw std::runtime_error("short read: " + t.file);
+    impl->params[i] = storage_alloc(bytes, device);
+    copy_in(impl->params[i].get(), host.data(), bytes, device);
+  }
+  if (!impl->ir.dynamic_rows) impl->compile(0);
+  Graph g;
+  g.impl_ = impl;
+  return g;
+}
+
+int Graph::num_inputs() const { return static_cast<int>(impl_->ir.inputs.size()); }
+int Graph::num_outputs() const { return static_cast<int>(impl_->ir.outputs.size()); }
+Shape Graph::input_shape(int i) const {
+  const int t = impl_->ir.inputs.at(static_cast<size_t>(i));
+  return Shape(impl_->plan ? impl_->plan->shape[static_cast<size_t>(t)] : impl_->ir.tensors[static_cast<size_t>(t)].shape);
+}
+Shape Graph::output_shape(int i) const {
+  const int t = impl_->ir.outputs.at(static_cast<size_t>(i));
+  return Shape(impl_->plan ? impl_->plan->shape[static_cast<size_t>(t)] : impl_->ir.tensors[static_cast<size_t>(t)].shape);
+}
+int64_t Graph::in_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs[0])].shape.back(); }
+int64_t Graph::out_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.outputs[0])].shape.back(); }
+PlanStats Graph::stats() const { return impl_->plan ? impl_->plan->stats : PlanStats(); }
+
+DType Graph::input_dtype(int i) const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs.at(static_cast<size_t>(i)))].dtype; }
+int Graph::device() const { return impl_->device; }
+void Graph::BindRows(int64_t rows) {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  if (!impl_->ir.dynamic_rows) throw std::runtime_error("the graph was exported with fixed shapes; the input does not match them");
+  if (!impl_->plan || impl_->plan->rows != rows) impl_->compile(rows);
+}
+
+Tensor Graph::Forward(const Tensor& input) const { return Forward(std::vector<Tensor>{input}).at(0); }
+
+std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
+  Impl& im = *impl_;
+  std::lock_guard<std::mutex> run_guard(im.run_mu);
+  if (inputs.size() != im.ir.inputs.size()) throw std::runtime_error("Forward: wrong number of inputs");
+  if (im.ir.dynamic_rows) {
+    const int64_t feat = in_features();
+    const int64_t rows = inputs[0].shape().elem_cnt() / (feat > 0 ? feat : 1);
+    if (!im.plan || im.plan->rows != rows) im.compile(rows);
+  }
+  const Plan& plan = *im.plan;
+  im.bound.assign(im.ir.tensors.size(), nullptr);
+  for (size_t i = 0; i < im.ir.tensors.size(); ++i)
+    if (im.params[i]) im.bound[i] = im.params[i].get();
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    const int t = im.ir.inputs[i];
+    const TensorDef& def = im.ir.tensors[static_cast<size_t>(t)];
+    if (inputs[i].dtype() != def.dtype) throw std::runtime_error("Forward: input " + std::to_string(i) + " has the wrong dtype");
+    if (inputs[i].shape().elem_cnt() != numel(plan.shape[static_cast<size_t>(t)]))
+      throw std::runtime_error("Forward: input " + std::to_string(i) + " has the wrong number of elements");
+    if (inputs[i].device() != im.device) throw std::runtime_error("Forward: input " + std::to_string(i) + " lives on another device");
+    im.bound[static_cast<size_t>(plan.root[static_cast<size_t>(t)])] = inputs[i].data();
+  }
+  {
+    std::lock_guard<std::mutex> g(im.err_mu);
+    im.error.clear();
+  }
+  const int n_ops = static_cast<int>(plan.ops.size());
+  std::vector<TaskArg> args(static_cast<size_t>(n_ops));
+  for (int i = 0; i < n_ops; ++i) {
+    args[static_cast<size_t>(i)] = TaskArg{&im, i};
+    const PlannedOp& p = plan.ops[static_cast<size_t>(i)];
+    std::vector<int64_t> reads(p.deps.begin(), p.deps.end());
+    const int64_t own = i;
+    if (ofc_executor_submit(im.executor, p.stream, task_trampoline, &args[static_cast<size_t>(i)], reads.data(), static_cast<int>(reads.size()), &own, 1) != 0)
+      throw std::runtime_error(std::string("executor: ") + ofc_last_error());
+  }
+  if (ofc_executor_wait_all(im.executor, 600000) != 0) throw std::runtime_error(std::string("executor: ") + ofc_last_error());
+  if (im.device >= 0) {
+    check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+    for (auto s : im.streams) check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  }
+  if (im.failed()) throw std::runtime_error(im.error);
+  std::vector<Tensor> outs;
+  for (int t : im.ir.outputs) {
+    const TensorDef& def = im.ir.tensors[static_cast<size_t>(t)];
+    Tensor o = Tensor::empty(Shape(plan.shape[static_cast<size_t>(t)]), im.device, def.dtype);
+    const size_t bytes = static_cast<size_t>(numel(plan.shape[static_cast<size_t>(t)]) * SizeOf(def.dtype));
+    if (im.device < 0) std::memcpy(o.data(), im.addr(t), bytes);
+    else check_cuda(cudaMemcpy(o.data(), im.addr(t), bytes, cudaMemcpyDeviceToDevice), "cudaMemcpy");
+    outs.push_back(std::move(o));
+  }
+  return outs;
+}
+
+}  // namespace oneflow_api

@@ -1,15 +1,30 @@
-// C++ inference API: load an exported network and run it on the GPU without Python.
+// C++ inference API: load an exported network and run it without Python.
 //
 //   #include "oneflow_api.h"
-//   auto graph = oneflow_api::Graph::Load("model_dir");            // reads graph.txt + raw bf16 weight files
+//   auto graph = oneflow_api::Graph::Load("model_dir");            // reads graph.txt + raw weight files, compiles a plan
 //   oneflow_api::Tensor x = oneflow_api::Tensor::from_buffer(host_floats, {batch, features});
-//   oneflow_api::Tensor y = graph.Forward(x);                      // tcgen05 GEMMs with fused bias/activation, LayerNorm
+//   oneflow_api::Tensor y = graph.Forward(x);                      // or Forward(std::vector<Tensor>) -> std::vector<Tensor>
 //   std::vector<float> out = y.to_host();
 //
-// The directory is written by oneflow_b200.utils.export.export_inference_graph (feed-forward stacks of Linear,
-// ReLU / GELU and LayerNorm). A C ABI (ofb_api_*) wraps the same objects for other languages.
+// The directory is written by oneflow_b200.utils.export: `export_graph(module, example_inputs, dir)` records the operator
+// graph of any module built from the supported operators (linear with fused bias / activation / residual, batched matmul,
+// LayerNorm, embedding, element-wise unary and binary ops with row broadcasting, softmax, fused attention, reshapes as
+// aliases, permute / slice / concatenation as strided copies) with static shapes; `export_inference_graph` is the older
+// layer-list form, still read. Loading compiles the operator graph into a plan (graph_runtime.cpp):
+//   * reshapes become aliases of their source's storage;
+//   * every activation gets an address from the caching allocator of libofb_core (bin_allocator) by walking the
+//     operators in order, allocating at the first write and freeing after the last read, so that buffers with disjoint
+//     lifetimes share memory;
+//   * dependencies are derived from the address ranges each operator reads and writes (true, anti and output
+//     dependencies, including the ones memory sharing introduces);
+//   * operators are spread over the streams of the instruction scheduler of libofb_core (task_executor): a chain stays
+//     on its producer's stream, independent branches go to other streams; on the GPU each stream is a CUDA stream and
+//     cross-stream dependencies are CUDA events.
+// `device` >= 0 runs the sm_100a kernels of libofb_kernels on that GPU; device = -1 runs a plain host implementation of
+// the same operators (fp32 arithmetic, bf16 storage), which is what the tests without a GPU use.
 //
-// Reference counterpart: oneflow/api/cpp/ (oneflow_api::Tensor, Shape, Graph::Load(dir) running a saved nn.Graph).
+// Reference counterpart: oneflow/api/cpp/ (oneflow_api::Tensor, Shape, Graph::Load(dir) running a saved nn.Graph through
+// the job -> plan compiler and the actor runtime).
 #pragma once
 #include <cstdint>
 #include <memory>
@@ -31,19 +46,25 @@ class Shape {
     return n;
   }
   const std::vector<int64_t>& dims() const { return dims_; }
+  bool operator==(const Shape& o) const { return dims_ == o.dims_; }
 
  private:
   std::vector<int64_t> dims_;
 };
 
-// A bf16 tensor in device memory (shared ownership).
+enum class DType { kBFloat16 = 0, kInt64 = 1, kFloat = 2 };
+inline int64_t SizeOf(DType t) { return t == DType::kBFloat16 ? 2 : (t == DType::kInt64 ? 8 : 4); }
+
+// A tensor in device memory (device >= 0) or host memory (device = -1), shared ownership.
 class Tensor {
  public:
   Tensor() = default;
-  static Tensor from_buffer(const float* host, const Shape& shape, int device = 0);
-  static Tensor empty(const Shape& shape, int device = 0);
+  static Tensor from_buffer(const float* host, const Shape& shape, int device = 0);      // stored as bf16
+  static Tensor from_int64(const int64_t* host, const Shape& shape, int device = 0);     // stored as int64 (token ids)
+  static Tensor empty(const Shape& shape, int device = 0, DType dtype = DType::kBFloat16);
   std::vector<float> to_host() const;
   const Shape& shape() const { return shape_; }
+  DType dtype() const { return dtype_; }
   void* data() const { return data_.get(); }
   int device() const { return device_; }
 
@@ -51,14 +72,33 @@ class Tensor {
   Shape shape_;
   std::shared_ptr<void> data_;
   int device_ = 0;
+  DType dtype_ = DType::kBFloat16;
+};
+
+struct PlanStats {
+  int64_t n_ops = 0, n_tensors = 0;
+  int64_t activation_bytes = 0;   // sum of all activation sizes
+  int64_t arena_bytes = 0;        // peak bytes in use at once after sharing (activations + operator workspaces)
+  int64_t n_dependencies = 0;
+  int n_streams_used = 0;
 };
 
 class Graph {
  public:
-  static Graph Load(const std::string& dir, int device = 0);
+  static Graph Load(const std::string& dir, int device = 0, int n_streams = 2);
   Tensor Forward(const Tensor& input) const;
-  int64_t in_features() const;
-  int64_t out_features() const;
+  std::vector<Tensor> Forward(const std::vector<Tensor>& inputs) const;
+  int64_t in_features() const;    // last axis of the first input
+  int64_t out_features() const;   // last axis of the first output
+  int num_inputs() const;
+  int num_outputs() const;
+  Shape input_shape(int i) const;
+  Shape output_shape(int i) const;
+  DType input_dtype(int i) const;
+  int device() const;
+  // Graphs exported without a batch size (the layer-list form) are compiled for a row count on first use, or here.
+  void BindRows(int64_t rows);
+  PlanStats stats() const;
   struct Impl;
 
  private:
@@ -69,10 +109,22 @@ class Graph {
 
 extern "C" {
 void* ofb_api_graph_load(const char* dir, int device);
+void* ofb_api_graph_load_ex(const char* dir, int device, int n_streams);
 long long ofb_api_graph_in_features(void* graph);
 long long ofb_api_graph_out_features(void* graph);
-// x: host fp32 [rows, in_features]; y: host fp32 [rows, out_features]. Returns 0 on success.
+// x: host fp32 [rows, in_features]; y: host fp32 [rows, out_features]. Returns 0 on success. For graphs with one bf16 input
+// whose leading axes multiply to `rows` as exported.
 int ofb_api_graph_forward(void* graph, const float* x, long long rows, float* y);
+// General form: n_in host buffers (fp32 for bf16 inputs, int64 for id inputs) in the graph's input order with the exported
+// shapes; n_out host fp32 buffers sized by ofb_api_graph_output_numel.
+int ofb_api_graph_run(void* graph, const void* const* inputs, int n_in, float* const* outputs, int n_out);
+int ofb_api_graph_num_inputs(void* graph);
+int ofb_api_graph_num_outputs(void* graph);
+long long ofb_api_graph_input_numel(void* graph, int i);
+int ofb_api_graph_input_is_int64(void* graph, int i);
+long long ofb_api_graph_output_numel(void* graph, int i);
+// stats_out[6]: ops, tensors, activation bytes, arena bytes, dependencies, streams used
+int ofb_api_graph_stats(void* graph, long long* stats_out);
 void ofb_api_graph_free(void* graph);
 const char* ofb_api_last_error(void);
 }

@@ -112,7 +112,7 @@ __device__ __forceinline__ void store_vec(TOut* dst, const float (&v)[VEC]) {
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(512) collective_kernel(CommCtx c, int mode, long long in_off, long long stage_off,
                                                          TOut* __restrict__ out, long long count, float scale,
-                                                         unsigned int epoch) {
+                                                         unsigned int epoch, long long gather_src_stride) {
   constexpr int VEC = 16 / sizeof(TIn);
   using PIn = Pack<TIn, VEC>;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -186,7 +186,9 @@ __global__ void __launch_bounds__(512) collective_kernel(CommCtx c, int mode, lo
   } else {
     for (int k = 0; k < c.n; ++k) {
       const int p = (c.rank + k) % c.n;
-      const TIn* src = reinterpret_cast<const TIn*>(c.arena[p] + in_off);
+      // gather_src_stride != 0: every rank keeps the WHOLE buffer in its arena and contributes the slice at its own
+      // offset (in-place all-gather of a flat parameter buffer); 0: every rank's shard sits at in_off
+      const TIn* src = reinterpret_cast<const TIn*>(c.arena[p] + in_off + p * gather_src_stride);
       for (long long i0 = tid * VEC; i0 < slice; i0 += nth * VEC * UNR) {
         PIn v[UNR];
 #pragma unroll
@@ -287,8 +289,8 @@ static int comm_grid(long long work, int threads, int max_ctas) {
 // mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 barrier only. dtype codes: 0 fp32, 1 bf16.
 // Every launch of a collective on one context must use the same grid size (the barrier counts CTAs):
 // the launcher therefore always uses `ctas` CTAs (default 64).
-OFB_API int ofb_comm_collective(const OfbCommCtx* ctx, int mode, long long in_off, long long stage_off, int in_dtype,
-                                void* out, int out_dtype, long long count, float scale, unsigned int epoch, int ctas,
+static int comm_collective_impl(const OfbCommCtx* ctx, int mode, long long in_off, long long stage_off, int in_dtype, void* out,
+                                int out_dtype, long long count, float scale, unsigned int epoch, int ctas, long long gather_src_stride,
                                 void* stream) {
   if (ctx->n < 1 || ctx->n > kMaxPeers) return fail("comm: group size must be 1..8");
   const int vec = in_dtype == 0 ? 4 : 8;
@@ -296,7 +298,8 @@ OFB_API int ofb_comm_collective(const OfbCommCtx* ctx, int mode, long long in_of
   CommCtx c = to_ctx(ctx);
   auto s = (cudaStream_t)stream;
   const int grid = ctas > 0 ? (ctas > 132 ? 132 : ctas) : 64;
-#define OFB_COLL(TI, TO) collective_kernel<TI, TO><<<grid, 512, 0, s>>>(c, mode, in_off, stage_off, (TO*)out, count, scale, epoch)
+#define OFB_COLL(TI, TO) \
+  collective_kernel<TI, TO><<<grid, 512, 0, s>>>(c, mode, in_off, stage_off, (TO*)out, count, scale, epoch, gather_src_stride)
   if (in_dtype == 0 && out_dtype == 0) OFB_COLL(float, float);
   else if (in_dtype == 0 && out_dtype == 1) OFB_COLL(float, __nv_bfloat16);
   else if (in_dtype == 1 && out_dtype == 0) OFB_COLL(__nv_bfloat16, float);
@@ -305,6 +308,22 @@ OFB_API int ofb_comm_collective(const OfbCommCtx* ctx, int mode, long long in_of
 #undef OFB_COLL
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+OFB_API int ofb_comm_collective(const OfbCommCtx* ctx, int mode, long long in_off, long long stage_off, int in_dtype,
+                                void* out, int out_dtype, long long count, float scale, unsigned int epoch, int ctas,
+                                void* stream) {
+  return comm_collective_impl(ctx, mode, in_off, stage_off, in_dtype, out, out_dtype, count, scale, epoch, ctas, 0, stream);
+}
+
+// In-place all-gather of a flat buffer that every rank holds whole in its arena at in_off: rank p's slice (count / n
+// elements at byte offset p * slice bytes) is copied into `out` (normally this rank's own copy of the buffer) at the
+// same position. No staging copy on either side.
+OFB_API int ofb_comm_all_gather_inplace(const OfbCommCtx* ctx, long long in_off, int dtype, void* out, long long count,
+                                        unsigned int epoch, int ctas, void* stream) {
+  const long long esz = dtype == 0 ? 4 : 2;
+  if (ctx->n < 1 || count % ctx->n) return fail("comm: element count must be a multiple of the group size");
+  return comm_collective_impl(ctx, 2, in_off, in_off, dtype, out, dtype, count, 1.f, epoch, ctas, (count / ctx->n) * esz, stream);
 }
 
 OFB_API int ofb_comm_all_to_all(const OfbCommCtx* ctx, long long in_off, int dtype, void* out, long long outer, long long I,

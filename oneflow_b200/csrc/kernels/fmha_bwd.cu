@@ -1,7 +1,9 @@
-// Fused multi-head attention backward for sm_100a (bf16, head dim 64 or 128).
+// Fused multi-head attention backward for sm_100a (bf16, head dim 64 or 128; query length != key length,
+// grouped-query attention and Philox dropout as in the forward kernel).
 //
-// One CTA owns a 128-key tile (K_j, V_j stay resident in shared memory) of one (batch, head)
-// and walks over the query tiles i that see it. Per (i, j) pair five tcgen05 products run,
+// One CTA owns a 128-key tile (K_j, V_j stay resident in shared memory) of one (batch, key/value head)
+// and walks over the query tiles i that see it, for every query head of the group in turn (so dK and dV of a
+// shared key/value head accumulate in TMEM and need no second reduction). Per (i, j) pair five tcgen05 products run,
 // all fed from the same shared-memory tiles without any transposition pass:
 //     S   = Q_i K_j^T            (K-major  x K-major)       -> TMEM
 //     dP  = dO_i V_j^T           (K-major  x K-major)       -> TMEM
@@ -16,23 +18,27 @@
 // Reference counterpart: oneflow/user/kernels/scaled_dot_product_attention_grad_kernel.cu
 // (flash-attention library call).
 #include "../common/host_utils.h"
+#include "../common/philox.cuh"
 #include "../common/ptx.cuh"
 #include "ofb_kernels.h"
 
 namespace ofb {
 
 int fmha_tensor_map(CUtensorMap* out, const void* ptr, int B, int S, int H, int D, long long row_stride);
+int fmha_dropout_cfg(DropoutCfg* d, float p_dropout, unsigned long long seed, unsigned int offset);
 
 struct FmhaBwdParams {
-  const float* lse;     // [B, H, S]
-  const float* delta;   // [B, H, S] rowsum(dO * O)
-  float* dq_acc;        // [B, S, H, D] fp32, zero-initialised, receives red.add
-  __nv_bfloat16* dk;    // element (b,s,h,d) at ((b*S+s)*dkv_row_stride + h*D + d)
+  const float* lse;     // [B, H, Sq]
+  const float* delta;   // [B, H, Sq] rowsum(dO * O)
+  float* dq_acc;        // [B, Sq, H, D] fp32, zero-initialised, receives red.add
+  __nv_bfloat16* dk;    // element (b,s,hk,d) at ((b*Sk+s)*dkv_row_stride + hk*D + d)
   __nv_bfloat16* dv;
   long long dkv_row_stride;
   const int* kv_len;
-  int B, H, S, D;
+  int B, H, Hk, Sq, Sk, D;
   int causal;
+  int causal_off;       // Sk - Sq
+  DropoutCfg drop;
   float scale;          // softmax scale
   float scale_log2e;
   int* status;
@@ -67,7 +73,7 @@ __device__ __forceinline__ bool compute_sync(uint64_t* bar, uint32_t& parity, vo
   return ok;
 }
 
-template <int D>
+template <int D, bool DROP>
 __global__ void __launch_bounds__(192, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -105,14 +111,17 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int jt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hk;          // query heads per key/value head
   const int k0 = jt * 128;
-  const int n_qt = (p.S + 127) / 128;
-  int kv_limit = p.S;
+  const int n_qt = (p.Sq + 127) / 128;
+  int kv_limit = p.Sk;
   if (p.kv_len) kv_limit = min(kv_limit, p.kv_len[b]);
-  const int i_start = p.causal ? jt : 0;
+  // first query tile with a row that sees this key tile: row + causal_off >= k0
+  const int i_start = p.causal ? max(0, k0 - p.causal_off) / 128 : 0;
   const bool tile_visible = k0 < kv_limit;
-  const int n_iter = tile_visible ? n_qt - i_start : 0;
+  const int n_i = tile_visible ? max(0, n_qt - i_start) : 0;   // query tiles per head
+  const int n_iter = n_i * group;                               // iteration t: head hk*group + t / n_i, tile i_start + t % n_i
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -156,13 +165,14 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive_expect_tx(kv_full, 2 * Cfg::T_BYTES);
 #pragma unroll
       for (int c = 0; c < DCH; ++c) {
-        tma_load_4d(sK + c * CH_BYTES, &tmK, kv_full, c * 64, h, k0, b);
-        tma_load_4d(sV + c * CH_BYTES, &tmV, kv_full, c * 64, h, k0, b);
+        tma_load_4d(sK + c * CH_BYTES, &tmK, kv_full, c * 64, hk, k0, b);
+        tma_load_4d(sV + c * CH_BYTES, &tmV, kv_full, c * 64, hk, k0, b);
       }
       for (int t = 0; t < n_iter; ++t) {
         const int st = t & 1;
         const uint32_t ph = ((t >> 1) & 1) ^ 1;
-        const int qrow = (i_start + t) * 128;
+        const int h = hk * group + t / n_i;
+        const int qrow = (i_start + t % n_i) * 128;
         if (!mbar_wait(&q_empty[st], ph, abort_flag)) break;
         mbar_arrive_expect_tx(&q_full[st], Cfg::T_BYTES);
 #pragma unroll
@@ -244,17 +254,19 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t stg_parity = 0;
     for (int t = 0; t < n_iter; ++t) {
       const uint32_t ph1 = t & 1;
-      const int q0 = (i_start + t) * 128;
+      const int h = hk * group + t / n_i;
+      const int q0 = (i_start + t % n_i) * 128;
       const int row_g = q0 + r;
-      const bool row_ok = row_g < p.S;
-      const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.S + row_g;
+      const bool row_ok = row_g < p.Sq;
+      const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.Sq + row_g;
       const float lse = row_ok ? p.lse[stat_idx] : -INFINITY;
       const float delta = row_ok ? p.delta[stat_idx] : 0.f;
       const float lse2 = lse * kLog2e;
       const bool dead_row = !row_ok || lse == -INFINITY;
-      const bool need_mask = (p.causal && k0 + 127 > q0) || (k0 + 128 > kv_limit);
-      const int col_max = p.causal ? min(row_g, kv_limit - 1) : kv_limit - 1;
+      const bool need_mask = (p.causal && k0 + 127 > q0 + p.causal_off) || (k0 + 128 > kv_limit);
+      const int col_max = p.causal ? min(row_g + p.causal_off, kv_limit - 1) : kv_limit - 1;
       uint32_t pk[64];  // P, later dS, as packed bf16 pairs for this row
+      uint32_t keep_bits[DROP ? 4 : 1];  // dropout: bit c of word w = column 32 * w + c of this tile is kept
       if (!mbar_wait(s_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       // the previous pair's dQ reduction must have finished reading the staging area (= this P buffer)
@@ -279,13 +291,32 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
           }
       }
-      // Publish P. The buffer is free: the MMAs that read dS of the previous iteration were
-      // covered by the dq_full wait below in that iteration.
+      if constexpr (DROP) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          uint32_t bits = 0;
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            bits |= dropout_keep4(p.drop, static_cast<uint32_t>(b * p.H + h), static_cast<uint32_t>(row_g),
+                                  static_cast<uint32_t>((k0 + w * 32 + q4 * 4) >> 2)) << (q4 * 4);
+          keep_bits[w] = bits;
+        }
+      }
+      // Publish P (with dropout: only the kept probabilities, which is what multiplied V in the forward; the factor
+      // 1 / keep is applied to dV at the end). The buffer is free: the MMAs that read dS of the previous iteration
+      // were covered by the dq_full wait below in that iteration.
 #pragma unroll
       for (int g = 0; g < 16; ++g) {
         uint8_t* chunk = pds_row + (g >> 3) * CH_BYTES;
-        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) =
-            make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+        uint32_t w4[4] = {pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]};
+        if constexpr (DROP) {
+          // pair q of this 16-byte group holds columns 8 * g + 2 * q and + 1
+          const uint32_t bits = keep_bits[g >> 2] >> ((g & 3) * 8);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            w4[q] &= ((bits >> (2 * q)) & 1u ? 0x0000FFFFu : 0u) | ((bits >> (2 * q + 1)) & 1u ? 0xFFFF0000u : 0u);
+        }
+        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -306,8 +337,13 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; i += 2) {
             const int c = hh * 2 + cc;
             float2 pp = unpack_bf16x2(pk[c * 16 + (i >> 1)]);
-            float d0 = pp.x * (__uint_as_float(v[cc][i]) - delta) * p.scale;
-            float d1 = pp.y * (__uint_as_float(v[cc][i + 1]) - delta) * p.scale;
+            float g0 = __uint_as_float(v[cc][i]), g1 = __uint_as_float(v[cc][i + 1]);
+            if constexpr (DROP) {   // the gradient reaches P only through the kept entries, scaled by 1 / keep
+              g0 = (keep_bits[c] >> i) & 1u ? g0 * p.drop.inv_keep : 0.f;
+              g1 = (keep_bits[c] >> (i + 1)) & 1u ? g1 * p.drop.inv_keep : 0.f;
+            }
+            float d0 = pp.x * (g0 - delta) * p.scale;
+            float d1 = pp.y * (g1 - delta) * p.scale;
             pk[c * 16 + (i >> 1)] = pack_bf16x2(d0, d1);
           }
       }
@@ -365,37 +401,38 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) {
       tc_fence_after();
       const int krow = k0 + r;
-      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
-      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.Sk + krow) * p.dkv_row_stride + hk * D;
+      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.Sk + krow) * p.dkv_row_stride + hk * D;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tdK : tdV;
         __nv_bfloat16* dst = which == 0 ? dk_row : dv_row;
+        const float osc = (DROP && which == 1) ? p.drop.inv_keep : 1.f;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(src + lane_addr + c * 32, v);
           tmem_wait_ld();
-          if (krow < p.S) {
+          if (krow < p.Sk) {
 #pragma unroll
             for (int g = 0; g < 4; ++g)
               *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(
-                  pack_bf16x2(__uint_as_float(v[g * 8]), __uint_as_float(v[g * 8 + 1])),
-                  pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
-                  pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
-                  pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+                  pack_bf16x2(__uint_as_float(v[g * 8]) * osc, __uint_as_float(v[g * 8 + 1]) * osc),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * osc, __uint_as_float(v[g * 8 + 3]) * osc),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * osc, __uint_as_float(v[g * 8 + 5]) * osc),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * osc, __uint_as_float(v[g * 8 + 7]) * osc));
           }
         }
       }
     }
   } else {
-    // Key tile invisible to every query (beyond kv_len): zero gradients.
+    // Key tile invisible to every query (beyond kv_len, or right of the causal diagonal for all rows): zero gradients.
     const int r = (warp & 3) * 32 + lane;
     const int krow = k0 + r;
-    if (krow < p.S) {
-      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
-      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.S + krow) * p.dkv_row_stride + h * D;
+    if (krow < p.Sk) {
+      __nv_bfloat16* dk_row = p.dk + (static_cast<long long>(b) * p.Sk + krow) * p.dkv_row_stride + hk * D;
+      __nv_bfloat16* dv_row = p.dv + (static_cast<long long>(b) * p.Sk + krow) * p.dkv_row_stride + hk * D;
       for (int i = 0; i < D; i += 8) {
         *reinterpret_cast<uint4*>(dk_row + i) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(dv_row + i) = make_uint4(0, 0, 0, 0);
@@ -453,17 +490,17 @@ __global__ void fmha_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16
   }
 }
 
-template <int D>
+template <int D, bool DROP>
 static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                            const CUtensorMap& tdq, const FmhaBwdParams& p, cudaStream_t stream) {
   using Cfg = FmhaBwdCfg<D>;
-  auto kern = fmha_bwd_kernel<D>;
+  auto kern = fmha_bwd_kernel<D, DROP>;
   static bool configured = false;
   if (!configured) {
     OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured = true;
   }
-  dim3 grid((p.S + 127) / 128, p.H, p.B);
+  dim3 grid((p.Sk + 127) / 128, p.Hk, p.B);
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -473,65 +510,85 @@ static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 
 using namespace ofb;
 
-// Floats of scratch the backward needs: B*S*H*D for the fp32 dQ accumulator + B*H*S for delta.
+// Floats of scratch the backward needs: B*Sq*H*D for the fp32 dQ accumulator + B*H*Sq for delta.
 OFB_API long long ofb_fmha_bwd_scratch_floats(int B, int S, int H, int D) {
   return static_cast<long long>(B) * S * H * D + static_cast<long long>(B) * H * S;
 }
 
-// q,k,v: [B,S,H,D] views (token strides q_row_stride / kv_row_stride); o, d_o: contiguous [B,S,H,D];
-// dq,dk,dv: [B,S,H,D] views with token stride dqkv_row_stride (e.g. slices of one packed buffer).
-OFB_API int ofb_fmha_bwd(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
-                         const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-                         long long dqkv_row_stride, float* scratch, const int* kv_len, int B, int S, int H, int D,
-                         int causal, float scale, void* stream) {
+// q: [B,Sq,H,D] view (token stride q_row_stride); k, v: [B,Sk,Hk,D] views (kv_row_stride); o, d_o: contiguous
+// [B,Sq,H,D]; dq: [B,Sq,H,D] view with token stride dq_row_stride; dk, dv: [B,Sk,Hk,D] views with token stride
+// dkv_row_stride. scratch: ofb_fmha_bwd_scratch_floats(B, Sq, H, D) floats. Dropout arguments as in the forward call
+// whose output is differentiated.
+OFB_API int ofb_fmha_bwd_ex(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
+                            const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                            long long dq_row_stride, long long dkv_row_stride, float* scratch, const int* kv_len, int B,
+                            int Sq, int Sk, int H, int Hk, int D, int causal, float scale, float p_dropout,
+                            unsigned long long seed, unsigned int offset, void* stream) {
   if (D != 64 && D != 128) return fail("fmha_bwd: head dim must be 64 or 128");
-  if (dqkv_row_stride % 8) return fail("fmha_bwd: gradient row stride must be a multiple of 8");
+  if (Hk <= 0 || H % Hk) return fail("fmha_bwd: the number of query heads must be a multiple of the key/value heads");
+  if (dq_row_stride % 8 || dkv_row_stride % 8) return fail("fmha_bwd: gradient row strides must be multiples of 8");
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return fail("fmha_bwd: empty problem");
   auto s = reinterpret_cast<cudaStream_t>(stream);
   CUtensorMap tq, tk, tv, tdo;
-  if (fmha_tensor_map(&tq, q, B, S, H, D, q_row_stride)) return -1;
-  if (fmha_tensor_map(&tk, k, B, S, H, D, kv_row_stride)) return -1;
-  if (fmha_tensor_map(&tv, v, B, S, H, D, kv_row_stride)) return -1;
-  if (fmha_tensor_map(&tdo, d_o, B, S, H, D, static_cast<long long>(H) * D)) return -1;
-  const long long n_acc = static_cast<long long>(B) * S * H * D;
+  if (fmha_tensor_map(&tq, q, B, Sq, H, D, q_row_stride)) return -1;
+  if (fmha_tensor_map(&tk, k, B, Sk, Hk, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tv, v, B, Sk, Hk, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tdo, d_o, B, Sq, H, D, static_cast<long long>(H) * D)) return -1;
+  const long long n_acc = static_cast<long long>(B) * Sq * H * D;
   float* dq_acc = scratch;
   float* delta = scratch + n_acc;
   OFB_CUDA_OK(cudaMemsetAsync(dq_acc, 0, n_acc * sizeof(float), s));
   {
-    const long long rows = static_cast<long long>(B) * S * H;
+    const long long rows = static_cast<long long>(B) * Sq * H;
     const int threads = 256;
     const long long blocks = (rows * 32 + threads - 1) / threads;
     fmha_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, H, D);
+        reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, Sq, H, D);
     OFB_CUDA_OK(cudaGetLastError());
   }
   FmhaBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk); p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
-  p.dkv_row_stride = dqkv_row_stride; p.kv_len = kv_len;
-  p.B = B; p.H = H; p.S = S; p.D = D; p.causal = causal; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
+  p.dkv_row_stride = dkv_row_stride; p.kv_len = kv_len;
+  p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal; p.causal_off = Sk - Sq;
+  p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
   p.status = device_status_ptr();
+  if (fmha_dropout_cfg(&p.drop, p_dropout, seed, offset)) return -1;
   CUtensorMap tdq;
   {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail("cuTensorMapEncodeTiled is not available");
-    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
-    cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)H * D * 4, (cuuint64_t)S * H * D * 4};
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)Sq, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)H * D * 4, (cuuint64_t)Sq * H * D * 4};
     cuuint32_t box[4] = {32, 1, 128, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("fmha_bwd: cuTensorMapEncodeTiled(dq) failed with code " + std::to_string((int)r));
   }
-  int rc = D == 64 ? launch_fmha_bwd<64>(tq, tk, tv, tdo, tdq, p, s) : launch_fmha_bwd<128>(tq, tk, tv, tdo, tdq, p, s);
+  int rc;
+  if (p_dropout > 0.f)
+    rc = D == 64 ? launch_fmha_bwd<64, true>(tq, tk, tv, tdo, tdq, p, s) : launch_fmha_bwd<128, true>(tq, tk, tv, tdo, tdq, p, s);
+  else
+    rc = D == 64 ? launch_fmha_bwd<64, false>(tq, tk, tv, tdo, tdq, p, s) : launch_fmha_bwd<128, false>(tq, tk, tv, tdo, tdq, p, s);
   if (rc) return rc;
   {
-    const long long rows = static_cast<long long>(B) * S;
+    const long long rows = static_cast<long long>(B) * Sq;
     const long long total = rows * (H * D / 8);
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     fmha_dq_cast_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), rows,
-                                                                     H * D, dqkv_row_stride);
+                                                                     H * D, dq_row_stride);
     OFB_CUDA_OK(cudaGetLastError());
   }
   return 0;
+}
+
+// Self-attention form: one length, one head count, dq / dk / dv slices of one packed buffer.
+OFB_API int ofb_fmha_bwd(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
+                         const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                         long long dqkv_row_stride, float* scratch, const int* kv_len, int B, int S, int H, int D,
+                         int causal, float scale, void* stream) {
+  return ofb_fmha_bwd_ex(q, k, v, q_row_stride, kv_row_stride, o, d_o, lse, dq, dk, dv, dqkv_row_stride, dqkv_row_stride, scratch,
+                         kv_len, B, S, S, H, H, D, causal, scale, 0.f, 0ull, 0u, stream);
 }

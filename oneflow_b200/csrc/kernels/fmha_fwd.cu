@@ -1,5 +1,7 @@
 // Fused multi-head attention forward for sm_100a (bf16, head dim 64 or 128, causal or
-// full, optional per-batch key length for padding).
+// full, optional per-batch key length for padding, query length != key length with the causal
+// diagonal aligned to the bottom-right corner, grouped-query attention: H query heads share
+// Hk key/value heads, dropout on the probabilities from a Philox counter indexed by position).
 //
 // One CTA owns a 128-row query tile of one (batch, head). Roles:
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles through a 2-stage ring
@@ -16,17 +18,20 @@
 // attention library call), fused_attention_kernels.cu :710 (CUTLASS fMHA, no sm_100 path) and the
 // unfused fused_tril_scale_softmax_mask_scale chain.
 #include "../common/host_utils.h"
+#include "../common/philox.cuh"
 #include "../common/ptx.cuh"
 #include "ofb_kernels.h"
 
 namespace ofb {
 
 struct FmhaFwdParams {
-  __nv_bfloat16* out;   // [B, S, H, D] contiguous
-  float* lse;           // [B, H, S] natural-log sum-exp of the scaled scores
+  __nv_bfloat16* out;   // [B, Sq, H, D] contiguous
+  float* lse;           // [B, H, Sq] natural-log sum-exp of the scaled scores
   const int* kv_len;    // [B] number of valid keys per batch or null
-  int B, H, S, D;
+  int B, H, Hk, Sq, Sk, D;   // H query heads, Hk key/value heads (H % Hk == 0)
   int causal;
+  int causal_off;       // Sk - Sq: query row r sees key columns <= r + causal_off
+  DropoutCfg drop;
   float scale_log2e;    // softmax scale * log2(e)
   int* status;
 };
@@ -47,7 +52,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <int D>
+template <int D, bool DROP>
 __global__ void __launch_bounds__(192, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FmhaFwdParams p) {
@@ -76,15 +81,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Heavier (later) causal tiles first.
-  const int n_qt = (p.S + BM - 1) / BM;
+  const int n_qt = (p.Sq + BM - 1) / BM;
   const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hk);
   const int q0 = qt * BM;
-  int kv_limit = p.S;
+  int kv_limit = p.Sk;
   if (p.kv_len) kv_limit = min(kv_limit, p.kv_len[b]);
   int kv_end = kv_limit;
-  if (p.causal) kv_end = min(kv_end, q0 + BM);
-  const int n_kv = (kv_end + BN - 1) / BN;
+  if (p.causal) kv_end = min(kv_end, q0 + BM + p.causal_off);
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -123,10 +129,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
         mbar_arrive_expect_tx(&k_full[s], Cfg::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) tma_load_4d(sK + s * Cfg::KV_BYTES + c * CH_BYTES, &tmK, &k_full[s], c * 64, h, j * BN, b);
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sK + s * Cfg::KV_BYTES + c * CH_BYTES, &tmK, &k_full[s], c * 64, hk, j * BN, b);
         mbar_arrive_expect_tx(&v_full[s], Cfg::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) tma_load_4d(sV + s * Cfg::KV_BYTES + c * CH_BYTES, &tmV, &v_full[s], c * 64, h, j * BN, b);
+        for (int c = 0; c < DCH; ++c) tma_load_4d(sV + s * Cfg::KV_BYTES + c * CH_BYTES, &tmV, &v_full[s], c * 64, hk, j * BN, b);
       }
     }
     __syncwarp();
@@ -187,8 +193,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&s_full[s], ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int col_base = j * BN;
-      const bool need_mask = (p.causal && col_base + BN - 1 > q0) || (col_base + BN > kv_limit);
-      const int col_max = p.causal ? min(row_g, kv_limit - 1) : kv_limit - 1;  // last visible column
+      const bool need_mask = (p.causal && col_base + BN - 1 > q0 + p.causal_off) || (col_base + BN > kv_limit);
+      const int col_max = p.causal ? min(row_g + p.causal_off, kv_limit - 1) : kv_limit - 1;  // last visible column
       uint32_t sv[4][32];
       __syncwarp();
 #pragma unroll
@@ -238,11 +244,20 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(__uint_as_float(sv[c][i]) - m_use);       // masked entries are -inf -> 0
-          const float p1 = fast_exp2(__uint_as_float(sv[c][i + 1]) - m_use);
-          rs[(i >> 1) & 7] += p0 + p1;
-          packed[i >> 1] = pack_bf16x2(p0, p1);
+        for (int i = 0; i < 32; i += 4) {
+          float pv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(__uint_as_float(sv[c][i + e]) - m_use);  // masked entries are -inf -> 0
+          rs[(i >> 2) & 7] += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+          if constexpr (DROP) {
+            // the row sum keeps every probability; only what multiplies V is dropped (1 / keep is applied at the end)
+            const uint32_t keep = dropout_keep4(p.drop, static_cast<uint32_t>(b * p.H + h), static_cast<uint32_t>(row_g),
+                                                static_cast<uint32_t>((col_base + c * 32 + i) >> 2));
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pv[e] = (keep >> e) & 1u ? pv[e] : 0.f;
+          }
+          packed[i >> 1] = pack_bf16x2(pv[0], pv[1]);
+          packed[(i >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
         }
         uint8_t* chunk = p_row + (c >> 1) * CH_BYTES;
 #pragma unroll
@@ -262,15 +277,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(&pv_done[so], ((n_kv - 1) >> 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
+        const float inv = l_run > 0.f ? (DROP ? p.drop.inv_keep : 1.f) / l_run : 0.f;
+        __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.Sq + row_g) * p.H + h) * D;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(tO + lane_addr + c * 32, v);
           tmem_wait_ld();
-          if (row_g < p.S) {
+          if (row_g < p.Sq) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float f[8];
@@ -282,19 +297,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
           }
         }
-        if (row_g < p.S && p.lse)
-          p.lse[(static_cast<long long>(b) * p.H + h) * p.S + row_g] =
+        if (row_g < p.Sq && p.lse)
+          p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + row_g] =
               l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       }
     }
   } else {
-    // No visible keys at all (kv_len == 0): the output rows are zero.
+    // No visible keys at all (kv_len == 0, or a causal tile above the shifted diagonal): the output rows are zero.
     const int r = (warp & 3) * 32 + lane;
     const int row_g = q0 + r;
-    if (row_g < p.S) {
-      __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.S + row_g) * p.H + h) * D;
+    if (row_g < p.Sq) {
+      __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.Sq + row_g) * p.H + h) * D;
       for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
-      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.S + row_g] = -INFINITY;
+      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + row_g] = -INFINITY;
     }
   }
 
@@ -309,17 +324,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-template <int D>
+template <int D, bool DROP>
 static int launch_fmha_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FmhaFwdParams& p,
                            cudaStream_t stream) {
   using Cfg = FmhaFwdCfg<D>;
-  auto kern = fmha_fwd_kernel<D>;
+  auto kern = fmha_fwd_kernel<D, DROP>;
   static bool configured = false;
   if (!configured) {
     OFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured = true;
   }
-  dim3 grid((p.S + 127) / 128, p.H, p.B);
+  dim3 grid((p.Sq + 127) / 128, p.H, p.B);
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -341,24 +356,81 @@ int fmha_tensor_map(CUtensorMap* out, const void* ptr, int B, int S, int H, int 
   return 0;
 }
 
+// Fills a DropoutCfg from a drop probability, a 64-bit seed and a per-call offset.
+int fmha_dropout_cfg(DropoutCfg* d, float p_dropout, unsigned long long seed, unsigned int offset) {
+  if (!(p_dropout >= 0.f) || p_dropout >= 1.f) return fail("fmha: dropout probability must be in [0, 1)");
+  const double keep = 1.0 - static_cast<double>(p_dropout);
+  const double t = keep * 4294967296.0;
+  d->seed_lo = static_cast<uint32_t>(seed);
+  d->seed_hi = static_cast<uint32_t>(seed >> 32);
+  d->offset = offset;
+  d->threshold = t >= 4294967295.0 ? 0xFFFFFFFFu : static_cast<uint32_t>(t);
+  d->inv_keep = static_cast<float>(1.0 / keep);
+  return 0;
+}
+
+__global__ void fmha_dropout_mask_kernel(DropoutCfg d, unsigned char* __restrict__ mask, int BH, int Sq, int Sk) {
+  const long long groups = (Sk + 3) / 4;
+  const long long total = static_cast<long long>(BH) * Sq * groups;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const uint32_t cg = static_cast<uint32_t>(i % groups);
+    const uint32_t row = static_cast<uint32_t>((i / groups) % Sq);
+    const uint32_t bh = static_cast<uint32_t>(i / (groups * Sq));
+    const uint32_t keep = dropout_keep4(d, bh, row, cg);
+    for (int e = 0; e < 4; ++e) {
+      const long long col = 4ll * cg + e;
+      if (col < Sk) mask[(static_cast<long long>(bh) * Sq + row) * Sk + col] = (keep >> e) & 1u;
+    }
+  }
+}
+
 }  // namespace ofb
 
 using namespace ofb;
 
-// q, k, v: bf16 views [B, S, H, D] whose element (b, s, h, d) sits at ((b*S + s) * row_stride + h*D + d).
+// q: bf16 view [B, Sq, H, D], element (b, s, h, d) at ((b*Sq + s) * q_row_stride + h*D + d); k, v: [B, Sk, Hk, D] views
+// with token stride kv_row_stride. out: contiguous [B, Sq, H, D]; lse: [B, H, Sq]. With causal set, query row r sees
+// key columns <= r + (Sk - Sq). p_dropout > 0 drops probabilities by the Philox stream (seed, offset).
+OFB_API int ofb_fmha_fwd_ex(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
+                            void* out, float* lse, const int* kv_len, int B, int Sq, int Sk, int H, int Hk, int D, int causal,
+                            float scale, float p_dropout, unsigned long long seed, unsigned int offset, void* stream) {
+  if (D != 64 && D != 128) return fail("fmha: head dim must be 64 or 128");
+  if (Hk <= 0 || H % Hk) return fail("fmha: the number of query heads must be a multiple of the key/value heads");
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return fail("fmha: empty problem");
+  CUtensorMap tq, tk, tv;
+  if (fmha_tensor_map(&tq, q, B, Sq, H, D, q_row_stride)) return -1;
+  if (fmha_tensor_map(&tk, k, B, Sk, Hk, D, kv_row_stride)) return -1;
+  if (fmha_tensor_map(&tv, v, B, Sk, Hk, D, kv_row_stride)) return -1;
+  FmhaFwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse; p.kv_len = kv_len; p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal;
+  p.causal_off = Sk - Sq;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = device_status_ptr();
+  if (fmha_dropout_cfg(&p.drop, p_dropout, seed, offset)) return -1;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (p_dropout > 0.f) return D == 64 ? launch_fmha_fwd<64, true>(tq, tk, tv, p, s) : launch_fmha_fwd<128, true>(tq, tk, tv, p, s);
+  return D == 64 ? launch_fmha_fwd<64, false>(tq, tk, tv, p, s) : launch_fmha_fwd<128, false>(tq, tk, tv, p, s);
+}
+
 OFB_API int ofb_fmha_fwd(const void* q, const void* k, const void* v, long long q_row_stride, long long kv_row_stride,
                          void* out, float* lse, const int* kv_len, int B, int S, int H, int D, int causal, float scale,
                          void* stream) {
-  if (D != 64 && D != 128) return fail("fmha: head dim must be 64 or 128");
-  CUtensorMap tq, tk, tv;
-  if (fmha_tensor_map(&tq, q, B, S, H, D, q_row_stride)) return -1;
-  if (fmha_tensor_map(&tk, k, B, S, H, D, kv_row_stride)) return -1;
-  if (fmha_tensor_map(&tv, v, B, S, H, D, kv_row_stride)) return -1;
-  FmhaFwdParams p;
-  p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.lse = lse; p.kv_len = kv_len; p.B = B; p.H = H; p.S = S; p.D = D; p.causal = causal;
-  p.scale_log2e = scale * 1.4426950408889634f;
-  p.status = device_status_ptr();
-  auto s = reinterpret_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_fmha_fwd<64>(tq, tk, tv, p, s) : launch_fmha_fwd<128>(tq, tk, tv, p, s);
+  return ofb_fmha_fwd_ex(q, k, v, q_row_stride, kv_row_stride, out, lse, kv_len, B, S, S, H, H, D, causal, scale, 0.f, 0ull, 0u,
+                         stream);
+}
+
+// mask[b*H + h, row, col] = 1 where the attention dropout of (seed, offset) keeps the probability: the mask the fused
+// kernels regenerate on the fly, written out for tests and for the unfused fallback.
+OFB_API int ofb_fmha_dropout_mask(unsigned char* mask, int BH, int Sq, int Sk, float p_dropout, unsigned long long seed,
+                                  unsigned int offset, void* stream) {
+  DropoutCfg d;
+  if (fmha_dropout_cfg(&d, p_dropout, seed, offset)) return -1;
+  const long long total = static_cast<long long>(BH) * Sq * ((Sk + 3) / 4);
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  fmha_dropout_mask_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, mask, BH, Sq, Sk);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
 }

@@ -37,10 +37,15 @@ DIVERGED = ("Maybe executing different code in different ranks, please check if 
 class ControlStore(dist.Store):
     """``torch.distributed.Store`` over a ``runtime.ControlClient``."""
 
+    # torch keeps only the C++ half of a store it is handed; were the Python half collected, every call back into these
+    # methods would fail as "not implemented". Every instance therefore stays referenced for the life of the process.
+    _alive = []
+
     def __init__(self, client, timeout_s=300.0):
         super().__init__()
         self.c = client
         self._timeout_s = float(timeout_s)
+        ControlStore._alive.append(self)
 
     def set(self, key, value):
         if isinstance(value, str):
@@ -81,6 +86,28 @@ class ControlStore(dist.Store):
 
     def set_timeout(self, timeout):
         self._timeout_s = timeout.total_seconds() if isinstance(timeout, datetime.timedelta) else float(timeout)
+
+    # the extended interface newer process-group constructors ask for
+    def clone(self):
+        return ControlStore(self.c, self._timeout_s)
+
+    def has_extended_api(self):
+        return True
+
+    def append(self, key, value):
+        if isinstance(value, str):
+            value = value.encode()
+        while True:       # read-modify-write through compare-and-set: concurrent appends never lose a piece
+            old = self.c.get(key, timeout_s=self._timeout_s) if self.c.has(key) else b""
+            if self.c.compare_set(key, old, old + bytes(value)) == old + bytes(value):
+                return
+
+    def multi_get(self, keys):
+        return [self.get(k) for k in keys]
+
+    def multi_set(self, keys, values):
+        for k, v in zip(keys, values):
+            self.set(k, v)
 
     @property
     def timeout(self):

@@ -29,6 +29,16 @@ def embedding(input, weight, padding_idx=None, max_norm=None, norm_type=2.0, sca
     return fused_ops.embedding(input, weight)
 
 
+def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, generator=None):
+    """Fused attention (tcgen05 kernels for bf16 CUDA inputs: grouped-query heads, Sq != Sk, Philox dropout), torch's op
+    otherwise. Global tensors go through torch's op and its SBP rule."""
+    from ..framework import global_tensor as _GT
+    if any(isinstance(t, _GT.GlobalTensor) for t in (query, key, value)):
+        return _F.scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale=scale)
+    from .. import _C
+    return _C.scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale, generator)
+
+
 def conv2d(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
     """torch's conv2d, or the implicit-GEMM tcgen05 kernels for bf16 channels-last stride-1 "same" convolutions."""
     from .modules.conv import conv2d as _conv2d

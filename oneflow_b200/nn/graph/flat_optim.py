@@ -101,6 +101,7 @@ class FlatOptimizer:
             p._grad_nd_sbp = None
         self.step_count = 0
         self._state_ready = False
+        self._arena = None
         self._dp = None          # (placement, axis, group, ranks, collective helper) once the first step has seen the layouts
         self._lo, self._hi = 0, off
         self._sq = None
@@ -141,9 +142,37 @@ class FlatOptimizer:
         from ...parallel.zero import GradAllReduce
         return GradAllReduce(group, ranks, self.device)
 
+    def _move_into_arena(self):
+        """ZeRO on CUDA: the gradient and parameter buffers move into a peer-mapped arena (parallel.zero.ArenaZero), the
+        parameters' tensors and their ``_main_grad`` views are re-pointed, and from then on the gradient reduce-scatter
+        and the parameter all-gather work in place on them."""
+        from ...parallel.zero import ArenaZero
+        pl, a = self._dp
+        me = GT._rank()
+        az = ArenaZero(pl.axis_group(a), pl.axis_ranks(a, me), self.device, self.total, self.dtype)
+        az.flat[:self.total].copy_(self.flat)
+        az.grad[:self.total].copy_(self.grad)
+        self.flat, self.grad = az.flat, az.grad
+        for s in self.slots:
+            p = s.param
+            shape = _loc(p).shape
+            view = self.flat[s.off:s.off + s.n].view(shape)
+            if isinstance(p, GT.GlobalTensor):
+                p._local = view
+            else:
+                p.data = view
+            p._main_grad = self.grad[s.off:s.off + s.n].view(shape)
+        return az
+
     def _init_state(self):
         self._discover()
-        self._helper = self._dp_helper() if self._dp is not None else None
+        self._arena = None
+        if self._dp is not None and self.zero_stage >= 1 and self.device.type == "cuda" and \
+                self.dtype in (torch.float32, torch.bfloat16) and self._dp[0].hierarchy[self._dp[1]] <= 8:
+            self._arena = self._move_into_arena()
+            self._helper = self._arena
+        else:
+            self._helper = self._dp_helper() if self._dp is not None else None
         if self._helper is not None and self.zero_stage >= 1:
             self._lo, self._hi = self._helper.range(self.total)
         n = self._hi - self._lo
@@ -212,7 +241,10 @@ class FlatOptimizer:
                 o += v.numel()
         # 2. the data-parallel axis: flat mean over the axis (all-reduce, or reduce-scatter into this rank's slice)
         if self._helper is not None:
-            grad_shard = self._helper.reduce_scatter_grads(self.grad, self._lo, self._hi)
+            if self._arena is not None:
+                grad_shard = self._arena.reduce_scatter_grads()[:self._hi - self._lo]
+            else:
+                grad_shard = self._helper.reduce_scatter_grads(self.grad, self._lo, self._hi)
             dp_n = self._helper.size
             if self.zero_stage < 1:
                 grad_shard = self.grad[self._lo:self._hi]
@@ -245,7 +277,9 @@ class FlatOptimizer:
             a, b = lo - self._lo, hi - self._lo
             self._update(grad_shard[a:b], a, b, lo, hi, g, inv, factor, found)
         # 5. ZeRO: the updated low-precision parameters of the other slices
-        if self._helper is not None and self.zero_stage >= 1:
+        if self._arena is not None:
+            self._arena.all_gather_params()
+        elif self._helper is not None and self.zero_stage >= 1:
             self._helper.all_gather_params(self.flat, self._lo, self._hi)
 
     def _segments(self):

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 
 import torch
 
@@ -359,41 +359,65 @@ def _bshd_stride(t, name):
     return t.stride(1)
 
 
-def fmha_reference(q, k, v, causal, scale, kv_len=None):
-    """fp32 PyTorch attention on [B,S,H,D] tensors -> (out [B,S,H,D], lse [B,H,S])."""
-    B, S, H, D = q.shape
+def fmha_dropout_mask(B, H, Sq, Sk, p, seed, offset, device):
+    """bool [B, H, Sq, Sk]: the keep mask the fused attention kernels regenerate from (seed, offset) (Philox4x32-10 indexed by
+    batch*heads + head, query row and group of four key columns). CUDA only: the CPU fallback draws its own mask."""
+    mask = torch.empty((B * H, Sq, Sk), dtype=torch.uint8, device=device)
+    check(_lib().ofb_fmha_dropout_mask(ptr(mask), c_int(B * H), c_int(Sq), c_int(Sk), c_float(p), c_ulonglong(int(seed) & (2 ** 64 - 1)),
+                                       c_uint(int(offset) & 0xFFFFFFFF), stream_ptr()), "fmha_dropout_mask")
+    _count()
+    return mask.view(B, H, Sq, Sk).bool()
+
+
+def fmha_reference(q, k, v, causal, scale, kv_len=None, dropout_p=0.0, keep_mask=None):
+    """fp32 PyTorch attention: q [B,Sq,H,D], k / v [B,Sk,Hk,D] (H a multiple of Hk) -> (out [B,Sq,H,D], lse [B,H,Sq]).
+    Causal: query row r sees key columns <= r + (Sk - Sq). ``keep_mask`` (bool [B,H,Sq,Sk]) with ``dropout_p`` drops
+    probabilities after the softmax; without a mask one is drawn from torch's generator."""
+    B, Sq, H, D = q.shape
+    Sk, Hk = k.shape[1], k.shape[2]
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    if Hk != H:
+        kf, vf = (t.repeat_interleave(H // Hk, dim=1) for t in (kf, vf))
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:
-        m = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        m = torch.ones(Sq, Sk, dtype=torch.bool, device=q.device).tril(Sk - Sq)
         s = s.masked_fill(~m, float("-inf"))
     if kv_len is not None:
-        cols = torch.arange(S, device=q.device)[None, None, None, :]
+        cols = torch.arange(Sk, device=q.device)[None, None, None, :]
         s = s.masked_fill(cols >= kv_len.to(q.device)[:, None, None, None], float("-inf"))
     lse = torch.logsumexp(s, -1)
-    p = torch.exp(s - lse[..., None])
-    p = torch.nan_to_num(p, nan=0.0)
+    dead = torch.isinf(lse)[..., None]          # rows that see no key at all: zero output, zero gradient
+    p = torch.softmax(s.masked_fill(dead, 0.0), -1) * (~dead)
+    if dropout_p > 0.0:
+        if keep_mask is None:
+            keep_mask = torch.rand(p.shape, device=p.device) >= dropout_p
+        p = p * keep_mask.to(p.dtype) / (1.0 - dropout_p)
     o = torch.matmul(p, vf).permute(0, 2, 1, 3).contiguous()
     return o.to(q.dtype), lse
 
 
-def fmha_fwd(q, k, v, causal=False, scale=None, kv_len=None):
-    """Fused attention forward. q, k, v: bf16 [B,S,H,D] views (may alias one packed QKV buffer).
-    Returns (out [B,S,H,D] contiguous, lse fp32 [B,H,S])."""
-    B, S, H, D = q.shape
+def fmha_fwd(q, k, v, causal=False, scale=None, kv_len=None, dropout_p=0.0, seed=0, offset=0):
+    """Fused attention forward. q: bf16 [B,Sq,H,D] view, k / v: [B,Sk,Hk,D] views (all may alias one packed QKV buffer;
+    Hk divides H: grouped-query attention). ``dropout_p`` > 0 drops probabilities by the Philox stream (seed, offset);
+    the same pair must be given to ``fmha_bwd``. Returns (out [B,Sq,H,D] contiguous, lse fp32 [B,H,Sq])."""
+    B, Sq, H, D = q.shape
+    Sk, Hk = k.shape[1], k.shape[2]
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
-        return fmha_reference(q, k, v, causal, scale, kv_len)
+        return fmha_reference(q, k, v, causal, scale, kv_len, dropout_p)
+    if k.shape != v.shape or k.shape[0] != B or k.shape[3] != D or H % Hk:
+        raise ValueError(f"fmha: incompatible shapes q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
     qs, ks, vs = _bshd_stride(q, "q"), _bshd_stride(k, "k"), _bshd_stride(v, "v")
     if ks != vs:
         raise ValueError("fmha: k and v must share their token stride")
-    out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    out = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
     if kv_len is not None:
         kv_len = kv_len.to(device=q.device, dtype=torch.int32).contiguous()
-    check(_lib().ofb_fmha_fwd(ptr(q), ptr(k), ptr(v), c_longlong(qs), c_longlong(ks), ptr(out), ptr(lse), ptr(kv_len),
-                              c_int(B), c_int(S), c_int(H), c_int(D), c_int(int(causal)), c_float(scale), stream_ptr()),
-          "fmha_fwd")
+    check(_lib().ofb_fmha_fwd_ex(ptr(q), ptr(k), ptr(v), c_longlong(qs), c_longlong(ks), ptr(out), ptr(lse), ptr(kv_len),
+                                 c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hk), c_int(D), c_int(int(causal)), c_float(scale),
+                                 c_float(dropout_p), c_ulonglong(int(seed) & (2 ** 64 - 1)), c_uint(int(offset) & 0xFFFFFFFF),
+                                 stream_ptr()), "fmha_fwd")
     _count()
     return out, lse
 
@@ -521,43 +545,57 @@ def clip_factor(sq_and_bad, max_norm):
     return factor, found, norm
 
 
-def fmha_bwd_reference(q, k, v, o, d_o, lse, causal, scale, kv_len=None):
-    """fp32 PyTorch attention backward on [B,S,H,D] tensors -> (dq, dk, dv)."""
-    B, S, H, D = q.shape
+def fmha_bwd_reference(q, k, v, o, d_o, lse, causal, scale, kv_len=None, dropout_p=0.0, keep_mask=None):
+    """fp32 PyTorch attention backward (shapes as ``fmha_reference``) -> (dq, dk, dv)."""
     qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     with torch.enable_grad():
-        out, _ = fmha_reference(qf, kf, vf, causal, scale, kv_len)
+        out, _ = fmha_reference(qf, kf, vf, causal, scale, kv_len, dropout_p, keep_mask)
         out.backward(d_o.float())
     return qf.grad.to(q.dtype), kf.grad.to(q.dtype), vf.grad.to(q.dtype)
 
 
-def fmha_bwd(q, k, v, o, d_o, lse, causal=False, scale=None, kv_len=None, dqkv=None):
-    """Fused attention backward. Returns (dq, dk, dv) as [B,S,H,D] views of one packed [B,S,3,H,D] buffer
-    (``dqkv`` if given), so that the QKV projection's backward consumes a single matrix."""
-    B, S, H, D = q.shape
+def fmha_bwd(q, k, v, o, d_o, lse, causal=False, scale=None, kv_len=None, dqkv=None, dropout_p=0.0, seed=0, offset=0):
+    """Fused attention backward. Self-attention with one head count (q, k, v of one shape): returns (dq, dk, dv) as
+    [B,S,H,D] views of one packed [B,S,3,H,D] buffer (``dqkv`` if given), so that the QKV projection's backward consumes a
+    single matrix. Otherwise (other key length, fewer key/value heads): three separate contiguous tensors."""
+    B, Sq, H, D = q.shape
+    Sk, Hk = k.shape[1], k.shape[2]
+    packed = (Sk == Sq and Hk == H)
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
+        if dropout_p > 0.0:
+            raise ValueError("fmha_bwd on CPU cannot regenerate the forward's dropout mask; differentiate fmha_reference instead")
         dq, dk, dv = fmha_bwd_reference(q, k, v, o, d_o, lse, causal, scale, kv_len)
+        if not packed:
+            return dq, dk, dv
         if dqkv is None:
-            dqkv = torch.empty((B, S, 3, H, D), dtype=q.dtype)
+            dqkv = torch.empty((B, Sq, 3, H, D), dtype=q.dtype)
         dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2] = dq, dk, dv
         return dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
     qs, ks, vs = _bshd_stride(q, "q"), _bshd_stride(k, "k"), _bshd_stride(v, "v")
     if ks != vs:
         raise ValueError("fmha: k and v must share their token stride")
     _need_bf16(o, d_o)
-    if dqkv is None:
-        dqkv = torch.empty((B, S, 3, H, D), dtype=torch.bfloat16, device=q.device)
-    dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    if packed:
+        if dqkv is None:
+            dqkv = torch.empty((B, Sq, 3, H, D), dtype=torch.bfloat16, device=q.device)
+        dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+        dq_stride = dkv_stride = 3 * H * D
+    else:
+        dq = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+        dkv = torch.empty((B, Sk, 2, Hk, D), dtype=torch.bfloat16, device=q.device)
+        dk, dv = dkv[:, :, 0], dkv[:, :, 1]
+        dq_stride, dkv_stride = H * D, 2 * Hk * D
     _lib().ofb_fmha_bwd_scratch_floats.restype = c_longlong
-    n = _lib().ofb_fmha_bwd_scratch_floats(c_int(B), c_int(S), c_int(H), c_int(D))
+    n = _lib().ofb_fmha_bwd_scratch_floats(c_int(B), c_int(Sq), c_int(H), c_int(D))
     scratch = torch.empty(n, dtype=torch.float32, device=q.device)
     if kv_len is not None:
         kv_len = kv_len.to(device=q.device, dtype=torch.int32).contiguous()
-    check(_lib().ofb_fmha_bwd(ptr(q), ptr(k), ptr(v), c_longlong(qs), c_longlong(ks), ptr(o), ptr(d_o), ptr(lse),
-                              ptr(dq), ptr(dk), ptr(dv), c_longlong(3 * H * D), ptr(scratch), ptr(kv_len), c_int(B),
-                              c_int(S), c_int(H), c_int(D), c_int(int(causal)), c_float(scale), stream_ptr()),
-          "fmha_bwd")
+    check(_lib().ofb_fmha_bwd_ex(ptr(q), ptr(k), ptr(v), c_longlong(qs), c_longlong(ks), ptr(o), ptr(d_o), ptr(lse),
+                                 ptr(dq), ptr(dk), ptr(dv), c_longlong(dq_stride), c_longlong(dkv_stride), ptr(scratch), ptr(kv_len),
+                                 c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hk), c_int(D), c_int(int(causal)), c_float(scale),
+                                 c_float(dropout_p), c_ulonglong(int(seed) & (2 ** 64 - 1)), c_uint(int(offset) & 0xFFFFFFFF),
+                                 stream_ptr()), "fmha_bwd")
     _count(4)
     return dq, dk, dv
 

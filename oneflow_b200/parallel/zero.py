@@ -147,3 +147,63 @@ class GradAllReduce(_DPBase):
 
     def all_gather_params(self, flat, lo, hi):
         return
+
+
+class ArenaZero:
+    """ZeRO stage 1 on flat buffers that LIVE in the symmetric arena: the fp32 gradient buffer and the parameter buffer of
+    a rank are peer-mapped, so the reduce-scatter reads the peers' gradients where backward accumulated them and the
+    parameter all-gather writes the peers' updated slices where the modules read them. No pack, no staging copy, one
+    kernel each (what the reference arranges with SBP rewrites plus NCCL calls:
+    oneflow/core/job_rewriter/optimizer_placement_optimization_pass.cpp:381-467).
+
+    ``grad`` (fp32) and ``flat`` (parameter dtype) hold ``padded = n * per`` elements; rank r owns [r * per, (r + 1) * per)."""
+
+    def __init__(self, group, ranks, device, total, param_dtype):
+        from ..comm.symmetric import SymmetricArena
+        self.group, self.ranks = group, list(ranks)
+        self.size = len(self.ranks)
+        self.rank = self.ranks.index(dist.get_rank())
+        self.device = torch.device(device)
+        self.total = int(total)
+        self.per = _align_up((self.total + self.size - 1) // self.size, 64)
+        self.padded = self.per * self.size
+        esz = torch.empty((), dtype=param_dtype).element_size()
+        self.param_dtype = param_dtype
+        self.arena = SymmetricArena(group, ranks, device, self.padded * (4 + esz) + (1 << 16))
+        self.grad_off = self.arena.region(self.padded * 4)
+        self.flat_off = self.arena.region(self.padded * esz)
+        self.grad = self.arena.view(self.grad_off, (self.padded,), torch.float32)
+        self.flat = self.arena.view(self.flat_off, (self.padded,), param_dtype)
+        self.epoch = 0
+
+    def range(self, n=None):
+        lo = min(self.total, self.rank * self.per)
+        return lo, min(self.total, lo + self.per)
+
+    def reduce_scatter_grads(self, scale=None):
+        """fp32 [per]: this rank's slice of the sum of all ranks' gradient buffers, times ``scale`` (default 1 / n)."""
+        import ctypes
+        from ctypes import c_float, c_int, c_longlong, c_uint
+        from ..ops import _native
+        from ..ops import kernels as _k
+        scale = (1.0 / self.size) if scale is None else scale
+        out = torch.empty(self.per, dtype=torch.float32, device=self.device)
+        self.epoch += 1
+        _native.check(_native.kernels().ofb_comm_collective(
+            ctypes.byref(self.arena.ctx), c_int(1), c_longlong(self.grad_off), c_longlong(self.grad_off), c_int(0), _native.ptr(out),
+            c_int(0), c_longlong(self.padded), c_float(scale), c_uint(self.epoch), c_int(128), _native.stream_ptr()), "zero reduce-scatter")
+        _k._count()
+        return out
+
+    def all_gather_params(self):
+        """Every rank's freshly updated slice of the parameter buffer lands in this rank's copy, in place."""
+        import ctypes
+        from ctypes import c_int, c_longlong, c_uint
+        from ..ops import _native
+        from ..ops import kernels as _k
+        self.epoch += 1
+        dt = 0 if self.param_dtype == torch.float32 else 1
+        _native.check(_native.kernels().ofb_comm_all_gather_inplace(
+            ctypes.byref(self.arena.ctx), c_longlong(self.flat_off), c_int(dt), _native.ptr(self.flat), c_longlong(self.padded),
+            c_uint(self.epoch), c_int(128), _native.stream_ptr()), "zero all-gather")
+        _k._count()

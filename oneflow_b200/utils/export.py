@@ -1,6 +1,9 @@
-"""Export of feed-forward networks for the C++ inference API (csrc/api/oneflow_api.h).
+"""Export of networks for the C++ inference API (csrc/api/oneflow_api.h).
 
-``export_inference_graph(module, directory)`` walks an ``nn.Sequential`` (nested ones are flattened) of Linear, ReLU,
+``export_graph(module, example_inputs, directory)`` records the operator graph of ``module`` on the example inputs (static
+shapes) and writes ``graph.txt`` (tensors, operators, inputs, outputs) plus one raw file per parameter; the C++ side compiles
+it into a plan (memory sharing, dependencies, streams) and runs it on the sm_100a kernels or on its host implementation.
+``export_inference_graph(module, directory)`` is the older layer-list form: it walks an ``nn.Sequential`` (nested ones are flattened) of Linear, ReLU,
 GELU and LayerNorm layers and writes ``graph.txt`` plus one raw bf16 file per parameter; an activation that follows a
 Linear is folded into that layer's GEMM epilogue. ``InferenceGraph`` loads such a directory through the C ABI of
 ``libofb_api.so`` (what a C++ program does with ``oneflow_api::Graph::Load``).
@@ -77,31 +80,509 @@ def export_inference_graph(module, directory):
     return directory
 
 
-class InferenceGraph:
-    """ctypes face of the C ABI of the C++ inference API."""
+# ------------------------------------------------------------------------------------------------ operator-graph export
+import math
+import operator
 
-    def __init__(self, directory, device=0):
-        lib_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libofb_api.so")
-        self.lib = ctypes.CDLL(lib_path)
-        self.lib.ofb_api_graph_load.restype = ctypes.c_void_p
-        self.lib.ofb_api_last_error.restype = ctypes.c_char_p
-        self.lib.ofb_api_graph_in_features.restype = ctypes.c_longlong
-        self.lib.ofb_api_graph_out_features.restype = ctypes.c_longlong
-        self.h = self.lib.ofb_api_graph_load(directory.encode(), ctypes.c_int(device))
+import torch.fx
+import torch.nn.functional as F
+
+
+_UNARY = {"scale": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3, "tanh": 4, "sigmoid": 5, "silu": 6, "add_scalar": 7, "exp": 8, "rsqrt": 9,
+          "square": 10}
+_BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "maximum": 4, "minimum": 5}
+_INPLACE = {"iadd": "add", "imul": "mul", "isub": "sub", "itruediv": "div", "add_": "add", "mul_": "mul", "sub_": "sub", "div_": "div",
+            "relu_": "relu", "tanh_": "tanh", "sigmoid_": "sigmoid"}
+
+
+class _GraphEmitter(torch.fx.Interpreter):
+    """Runs the traced module on the example inputs and writes one IR operator per computing node.
+
+    Invariant: every tensor the interpreter holds is laid out in its torch storage exactly as in the IR tensor that stands for
+    that storage (a flat "root" tensor per storage). View operations therefore need no IR at all: a consumer reads the view's
+    shape, strides and offset off the torch tensor. Where torch would hand back a result in another layout (an element-wise
+    op on a permuted input keeps the permutation; attention returns [B, H, S, D]) the node's value is replaced by an equal
+    tensor in the layout the IR operator writes."""
+
+    def __init__(self, gm, directory):
+        super().__init__(gm)
+        self.dir = directory
+        self.tensors = []          # IR tensor records (without the leading "tensor <id>")
+        self.ops = []              # dicts: type, in, out, attr
+        self.inputs, self.outputs = [], []
+        self.roots = {}            # torch storage pointer -> IR id of the flat tensor standing for that storage
+        self.keep = []             # tensors kept alive so that storage pointers stay unique
+        self.alias_cache = {}
+        self.copy_cache = {}
+
+    # ---- IR helpers
+    @staticmethod
+    def _dtype(t):
+        if t.dtype.is_floating_point:
+            return "bf16"
+        if t.dtype in (torch.int64, torch.int32):
+            return "i64"
+        raise ValueError(f"cannot export tensors of dtype {t.dtype}")
+
+    def _new_tensor(self, dtype, kind, shape, extra=""):
+        self.tensors.append(f"{dtype} {kind} {len(shape)} " + " ".join(str(int(d)) for d in shape) + (" " + extra if extra else ""))
+        return len(self.tensors) - 1
+
+    def _kind(self, tid):
+        return self.tensors[tid].split()[1]
+
+    def _register(self, real, kind, extra=""):
+        """``real`` owns a fresh storage that it fills contiguously: a new flat IR tensor stands for it."""
+        assert real.is_contiguous() and real.storage_offset() == 0
+        rid = self._new_tensor(self._dtype(real), kind, [max(real.numel(), 1)], extra)
+        self.keep.append(real)
+        self.roots[real.untyped_storage().data_ptr()] = rid
+        return rid
+
+    def _root(self, real):
+        rid = self.roots.get(real.untyped_storage().data_ptr())
+        if rid is None:
+            rid = self._constant(real)
+        return rid
+
+    def _constant(self, real):
+        """A tensor that does not depend on the inputs (a parameter, a buffer, a table built in forward): saved as a file."""
+        n_storage = real.untyped_storage().nbytes() // real.element_size()
+        whole = torch.as_strided(real.detach(), (n_storage,), (1,), 0)       # the storage in its own order
+        name = f"t{len(self.tensors)}.bin"
+        if self._dtype(real) == "bf16":
+            _write_bf16(os.path.join(self.dir, name), whole)
+        else:
+            whole.to(torch.int64).cpu().numpy().tofile(os.path.join(self.dir, name))
+        rid = self._new_tensor(self._dtype(real), "param", [n_storage], f"file={name}")
+        self.keep.append(real)
+        self.roots[real.untyped_storage().data_ptr()] = rid
+        return rid
+
+    def _alias(self, root, offset, shape):
+        shape = tuple(int(d) for d in shape)
+        key = (root, int(offset), shape)
+        if key not in self.alias_cache:
+            self.alias_cache[key] = self._new_tensor(self.tensors[root].split()[0], self._kind(root), shape, f"alias={root} offset={int(offset)}")
+        return self.alias_cache[key]
+
+    def _operand(self, real):
+        """IR id of a contiguous tensor holding ``real``: an alias of its storage, or a strided copy when it is not contiguous."""
+        root = self._root(real)
+        if real.is_contiguous():
+            return self._alias(root, real.storage_offset(), real.shape)
+        key = (root, real.storage_offset(), tuple(real.shape), tuple(real.stride()))
+        if key not in self.copy_cache:
+            if real.dim() > 5:
+                raise ValueError("strided copies support at most 5 axes")
+            n = real.numel()
+            rid = self._new_tensor(self._dtype(real), "act", [n])
+            out_strides = torch.empty(real.shape, device="meta").stride()
+            self.ops.append({"type": "copy", "in": [root], "out": [rid],
+                             "attr": {"shape": ",".join(map(str, real.shape)), "in_strides": ",".join(map(str, real.stride())),
+                                      "in_offset": int(real.storage_offset()), "out_strides": ",".join(map(str, out_strides)),
+                                      "out_offset": 0}})
+            self.copy_cache[key] = (rid, len(self.ops))
+        rid, _ = self.copy_cache[key]
+        return self._alias(rid, 0, real.shape)
+
+    def _result(self, real):
+        """Fresh activation for an operator's result: (IR id to write, the tensor to hand on), laid out contiguously."""
+        real = real.contiguous() if not (real.is_contiguous() and real.storage_offset() == 0) else real
+        if real.untyped_storage().data_ptr() in self.roots:
+            real = real.clone()
+        rid = self._register(real, "act")
+        return self._alias(rid, 0, real.shape), real
+
+    def _emit(self, type_, ins, out, **attr):
+        self.copy_cache.clear()       # a cached copy is only valid until something may have rewritten its source
+        self.ops.append({"type": type_, "in": list(ins), "out": [out], "attr": attr})
+
+    # ---- operators: each returns the tensor that stands for the node from here on
+    def _unary(self, x, y, fn, alpha=1.0, inplace=False):
+        ix = self._operand(x)
+        if inplace:
+            if not x.is_contiguous():
+                raise ValueError("an in-place operator on a strided view cannot be exported")
+            self._emit("unary", [ix], ix, fn=_UNARY[fn], alpha=repr(float(alpha)))
+            return y
+        out, y = self._result(y)
+        self._emit("unary", [ix], out, fn=_UNARY[fn], alpha=repr(float(alpha)))
+        return y
+
+    def _binary(self, a, b, y, fn, inplace=False):
+        if not torch.is_tensor(b) or not torch.is_tensor(a):
+            t, c = (a, b) if torch.is_tensor(a) else (b, a)
+            c = float(c)
+            if fn == "add":
+                return self._unary(t, y, "add_scalar", c, inplace)
+            if fn == "mul":
+                return self._unary(t, y, "scale", c, inplace)
+            if fn == "sub" and torch.is_tensor(a):
+                return self._unary(t, y, "add_scalar", -c, inplace)
+            if fn == "div" and torch.is_tensor(a):
+                return self._unary(t, y, "scale", 1.0 / c, inplace)
+            raise ValueError(f"cannot export scalar {fn} with the tensor on the right")
+        if tuple(a.shape) != tuple(y.shape):
+            if not inplace and fn in ("add", "mul", "maximum", "minimum") and tuple(b.shape) == tuple(y.shape):
+                a, b = b, a
+            else:
+                raise ValueError(f"cannot export {fn}: the first operand {tuple(a.shape)} is broadcast to {tuple(y.shape)}")
+        cols = 1
+        bs = list(b.shape)
+        while bs and bs[0] == 1:
+            bs.pop(0)                                   # leading broadcast axes
+        tail = list(bs)
+        while tail and tail[-1] == 1:
+            tail.pop()                                  # trailing broadcast axes
+        if tuple(b.shape) == tuple(y.shape):
+            mode = 0
+        elif bs and tuple(y.shape[y.dim() - len(bs):]) == tuple(bs):
+            mode, cols = 1, b.numel()                   # b repeats over the leading axes: y as [rows, cols] with cols = |b|
+        elif b.dim() == y.dim() and tail and tuple(b.shape[:len(tail)]) == tuple(y.shape[:len(tail)]) and b.numel() == math.prod(tail):
+            mode, cols = 2, y.numel() // b.numel()      # one value of b per leading index
+        else:
+            raise ValueError(f"cannot export {fn} of shapes {tuple(a.shape)} and {tuple(b.shape)}")
+        ia, ib = self._operand(a), self._operand(b)
+        if inplace:
+            if not a.is_contiguous():
+                raise ValueError("an in-place operator on a strided view cannot be exported")
+            self._emit("binary", [ia, ib], ia, fn=_BINARY[fn], bmode=mode, cols=cols)
+            return y
+        out, y = self._result(y)
+        self._emit("binary", [ia, ib], out, fn=_BINARY[fn], bmode=mode, cols=cols)
+        return y
+
+    def _linear(self, x, w, b, y):
+        ins = [self._operand(x), self._operand(w), self._operand(b) if b is not None else -1, -1]
+        out, y = self._result(y)
+        self._emit("linear", ins, out, act="none")
+        return y
+
+    def _layer_norm(self, x, shape, w, b, eps, y):
+        if len(shape) != 1:
+            raise ValueError("only LayerNorm over the last dimension can be exported")
+        n = int(shape[0])
+        w = w if w is not None else torch.ones(n)
+        b = b if b is not None else torch.zeros(n)
+        ins = [self._operand(x), self._operand(w), self._operand(b)]
+        out, y = self._result(y)
+        self._emit("layer_norm", ins, out, eps=repr(float(eps)))
+        return y
+
+    def _embedding(self, ids, table, y):
+        ins = [self._operand(ids), self._operand(table)]
+        out, y = self._result(y)
+        self._emit("embedding", ins, out)
+        return y
+
+    def _matmul(self, a, b, y):
+        if a.dim() < 2 or b.dim() < 2:
+            raise ValueError("matmul of vectors cannot be exported")
+        if b.dim() > 2 and tuple(b.shape[:-2]) != tuple(a.shape[:-2]):
+            raise ValueError("matmul with broadcast batch axes cannot be exported")
+        ia = self._operand(a)
+        # a right operand whose transpose is contiguous ([.., N, K] in memory) is read in place as a K-major matrix
+        if not b.is_contiguous() and b.transpose(-1, -2).is_contiguous():
+            ib, tb = self._operand(b.transpose(-1, -2)), 1
+        else:
+            ib, tb = self._operand(b), 0
+        out, y = self._result(y)
+        self._emit("matmul", [ia, ib], out, tb=tb, alpha="1.0")
+        return y
+
+    def _softmax(self, x, dim, y):
+        if dim % x.dim() != x.dim() - 1:
+            raise ValueError("softmax over an inner axis cannot be exported")
+        ix = self._operand(x)
+        out, y = self._result(y)
+        self._emit("softmax", [ix], out, scale="1.0")
+        return y
+
+    def _token_major(self, t):
+        """[B, heads, S, D] -> (IR id of a [B, S, heads, D] tensor, token stride): read in place when the heads of one token are
+        adjacent (a slice of a packed projection), else through a copy."""
+        tt = t.transpose(1, 2)
+        B, S, H, D = tt.shape
+        st = tt.stride()
+        if st[3] == 1 and st[2] == D and st[1] >= H * D and (B == 1 or st[0] == S * st[1]) and tt.storage_offset() % 8 == 0 and st[1] % 8 == 0:
+            return self._alias(self._root(tt), tt.storage_offset(), (B, S, H, D)), int(st[1])
+        return self._operand(tt), int(H * D)
+
+    def _sdpa(self, q, k, v, y, causal, scale):
+        B, H, Sq, D = q.shape
+        Sk = k.shape[2]
+        if causal and Sq != Sk:
+            raise ValueError("torch aligns the causal mask top-left when Sq != Sk; the fused kernel aligns it bottom-right")
+        iq, qs = self._token_major(q)
+        ik, ks = self._token_major(k)
+        iv, vs = self._token_major(v)
+        if ks != vs:
+            ik, ks = self._operand(k.transpose(1, 2)), int(k.shape[1] * D)
+            iv, vs = self._operand(v.transpose(1, 2)), ks
+        # the operator writes [B, Sq, H, D]; the node's value becomes the [B, H, Sq, D] view of exactly that memory
+        y_ir = y.transpose(1, 2).contiguous()
+        rid = self._register(y_ir, "act")
+        sc = scale if scale is not None else 1.0 / math.sqrt(D)
+        self._emit("attention", [iq, ik, iv], self._alias(rid, 0, y_ir.shape), causal=int(bool(causal)), scale=repr(float(sc)), q_stride=qs,
+                   kv_stride=ks)
+        return y_ir.transpose(1, 2)
+
+    def _cat(self, tensors, dim, y):
+        y = y.contiguous()
+        if y.untyped_storage().data_ptr() in self.roots:
+            y = y.clone()
+        rid = self._register(y, "act")
+        out_strides = list(y.stride())
+        off = 0
+        for t in tensors:
+            if t.dim() > 5:
+                raise ValueError("concatenation supports at most 5 axes")
+            root = self._root(t)
+            self.copy_cache.clear()
+            self.ops.append({"type": "copy", "in": [root], "out": [rid],
+                             "attr": {"shape": ",".join(map(str, t.shape)), "in_strides": ",".join(map(str, t.stride())),
+                                      "in_offset": int(t.storage_offset()), "out_strides": ",".join(map(str, out_strides)),
+                                      "out_offset": int(off * out_strides[dim])}})
+            off += t.shape[dim]
+        return y
+
+    # ---- interpreter hooks
+    def placeholder(self, target, args, kwargs):
+        real = super().placeholder(target, args, kwargs)
+        if torch.is_tensor(real):
+            real = real.contiguous().clone()
+            self._register(real, "input")
+            self.inputs.append(self._operand(real))
+        return real
+
+    def output(self, target, args, kwargs):
+        res = super().output(target, args, kwargs)
+        outs = res if isinstance(res, (tuple, list)) else (res,)
+        for o in outs:
+            if not torch.is_tensor(o):
+                raise ValueError("graph outputs must be tensors")
+            self.outputs.append(self._operand(o))
+        return res
+
+    def _handle(self, name, a, kw, y, module=None):
+        """After a call node ran on concrete values: emit IR for it and return the value that stands for the node."""
+        flat = []
+        for x in list(a) + list(kw.values()):
+            flat += [t for t in (x if isinstance(x, (tuple, list)) else (x,)) if torch.is_tensor(t)]
+        inplace = name in _INPLACE or bool(getattr(module, "inplace", False))
+        if not torch.is_tensor(y):
+            if isinstance(y, (tuple, list)):
+                for r in y:
+                    if torch.is_tensor(r) and not any(r.untyped_storage().data_ptr() == t.untyped_storage().data_ptr() for t in flat):
+                        raise ValueError(f"cannot export {name}: it returns several new tensors")
+            return y
+        if not inplace and any(y.untyped_storage().data_ptr() == t.untyped_storage().data_ptr() for t in flat):
+            return y                    # a view of a traced tensor (or the tensor itself: dropout in eval mode, .to of the same dtype)
+        if module is not None:
+            m = module
+            if isinstance(m, torch.nn.Linear):
+                return self._linear(a[0], m.weight, m.bias, y)
+            if isinstance(m, torch.nn.LayerNorm):
+                return self._layer_norm(a[0], m.normalized_shape, m.weight, m.bias, m.eps, y)
+            if isinstance(m, torch.nn.Embedding):
+                return self._embedding(a[0], m.weight, y)
+            if isinstance(m, torch.nn.GELU):
+                return self._unary(a[0], y, "gelu_tanh" if m.approximate == "tanh" else "gelu")
+            for cls, fn in ((torch.nn.ReLU, "relu"), (torch.nn.Tanh, "tanh"), (torch.nn.Sigmoid, "sigmoid"), (torch.nn.SiLU, "silu")):
+                if isinstance(m, cls):
+                    return self._unary(a[0], y, fn, inplace=inplace)
+            if isinstance(m, torch.nn.Softmax):
+                return self._softmax(a[0], m.dim, y)
+            raise ValueError(f"cannot export module of type {type(m).__name__}")
+        n = name
+        if n in _INPLACE:
+            fn = _INPLACE[n]
+            return self._unary(a[0], y, fn, inplace=True) if fn in _UNARY else self._binary(a[0], a[1], y, fn, inplace=True)
+        if n == "linear":
+            return self._linear(a[0], a[1], a[2] if len(a) > 2 else kw.get("bias"), y)
+        if n == "layer_norm":
+            return self._layer_norm(a[0], a[1], a[2] if len(a) > 2 else kw.get("weight"), a[3] if len(a) > 3 else kw.get("bias"),
+                                    a[4] if len(a) > 4 else kw.get("eps", 1e-5), y)
+        if n == "embedding":
+            return self._embedding(a[0], a[1], y)
+        if n == "gelu":
+            return self._unary(a[0], y, "gelu_tanh" if kw.get("approximate", "none") == "tanh" else "gelu")
+        if n in ("relu", "tanh", "sigmoid", "silu", "exp", "rsqrt", "square"):
+            return self._unary(a[0], y, n)
+        if n == "neg":
+            return self._unary(a[0], y, "scale", -1.0)
+        if n in ("add", "sub", "mul", "truediv", "div", "maximum", "minimum"):
+            return self._binary(a[0], a[1], y, "div" if n == "truediv" else n)
+        if n in ("matmul", "bmm", "mm"):
+            return self._matmul(a[0], a[1], y)
+        if n == "softmax":
+            return self._softmax(a[0], a[1] if len(a) > 1 else kw.get("dim", -1), y)
+        if n == "scaled_dot_product_attention":
+            if (a[3] if len(a) > 3 else kw.get("attn_mask")) is not None:
+                raise ValueError("attention with an explicit mask cannot be exported")
+            if (a[4] if len(a) > 4 else kw.get("dropout_p", 0.0)):
+                raise ValueError("attention dropout has no place in an inference graph")
+            return self._sdpa(a[0], a[1], a[2], y, a[5] if len(a) > 5 else kw.get("is_causal", False), kw.get("scale"))
+        if n in ("cat", "concat"):
+            return self._cat(list(a[0]), int(a[1] if len(a) > 1 else kw.get("dim", 0)) % y.dim(), y)
+        if n in ("reshape", "contiguous", "clone", "flatten", "to", "float", "type_as", "dropout", "expand_as"):
+            # torch copied because the source view is not contiguous: a strided copy, then the new shape as an alias
+            src = a[0]
+            rid = self._operand(src)
+            root = int(self.tensors[rid].split("alias=")[1].split()[0]) if "alias=" in self.tensors[rid] else rid
+            flat_copy = src.contiguous()
+            self.keep.append(flat_copy)
+            self.roots[flat_copy.untyped_storage().data_ptr()] = root
+            return flat_copy.reshape(y.shape)
+        if all(t.untyped_storage().data_ptr() not in self.roots or self._kind(self.roots[t.untyped_storage().data_ptr()]) == "param" for t in flat):
+            y = y.contiguous()
+            self._constant(y)           # built from constants only (position ids, tables of fixed shape, ...)
+            return y
+        raise ValueError(f"cannot export operator {n}")
+
+    def call_module(self, target, args, kwargs):
+        m = self.fetch_attr(target)
+        return self._handle(type(m).__name__, args, kwargs, super().call_module(target, args, kwargs), module=m)
+
+    def call_function(self, target, args, kwargs):
+        return self._handle(getattr(target, "__name__", str(target)), args, kwargs, super().call_function(target, args, kwargs))
+
+    def call_method(self, target, args, kwargs):
+        return self._handle(target, args, kwargs, super().call_method(target, args, kwargs))
+
+
+def _fold(ops, outputs, tensor_lines):
+    """Peephole fusion: an activation, then a residual addition, that are the only consumer of a linear's result move into its
+    GEMM epilogue (bias -> activation -> + residual is the order the kernel applies). The fused operator takes the consumer's
+    place in the order, where all of its inputs exist."""
+    def root_of(t):
+        rec = tensor_lines[t]
+        return root_of(int(rec.split("alias=")[1].split()[0])) if "alias=" in rec else t
+
+    out_roots = {root_of(t) for t in outputs}
+    changed = True
+    while changed:
+        changed = False
+        readers = {}
+        for i, op in enumerate(ops):
+            for t in op["in"]:
+                if t >= 0:
+                    readers.setdefault(root_of(t), []).append(i)
+        for i, op in enumerate(ops):
+            if op["type"] != "linear" or op["in"][3] != -1:
+                continue
+            r = root_of(op["out"][0])
+            if r in out_roots or len(readers.get(r, [])) != 1:
+                continue
+            j = readers[r][0]
+            nxt = ops[j]
+            mine = {root_of(t) for t in op["in"] if t >= 0}
+            if any(root_of(o) in mine for k in range(i + 1, j) for o in ops[k]["out"]):
+                continue            # something rewrites one of the linear's inputs in between
+            if root_of(nxt["out"][0]) == r:
+                continue            # an in-place consumer: leave it alone
+            if nxt["type"] == "unary" and int(nxt["attr"]["fn"]) in (1, 2, 3) and op["attr"]["act"] == "none":
+                op["attr"]["act"] = {1: "gelu", 2: "gelu_tanh", 3: "relu"}[int(nxt["attr"]["fn"])]
+            elif nxt["type"] == "binary" and int(nxt["attr"]["fn"]) == 0 and int(nxt["attr"]["bmode"]) == 0:
+                other = [t for t in nxt["in"] if root_of(t) != r]
+                if len(other) != 1:
+                    continue
+                op["in"][3] = other[0]
+            else:
+                continue
+            op["out"] = nxt["out"]
+            ops[j] = op
+            del ops[i]
+            changed = True
+            break
+    return ops
+
+
+def export_graph(module, example_inputs, directory, fuse=True):
+    """Records ``module(*example_inputs)`` as an operator graph with the example's shapes and writes it for the C++ runtime.
+    Parameters are stored as bf16 (integer tables as int64). Returns the directory."""
+    os.makedirs(directory, exist_ok=True)
+    if torch.is_tensor(example_inputs):
+        example_inputs = (example_inputs,)
+    was_training = module.training
+    module.eval()
+    try:
+        gm = module if isinstance(module, torch.fx.GraphModule) else torch.fx.symbolic_trace(module)
+        em = _GraphEmitter(gm, directory)
+        with torch.no_grad():
+            em.run(*[t.detach().cpu() for t in example_inputs])
+    finally:
+        module.train(was_training)
+    ops = _fold(em.ops, em.outputs, em.tensors) if fuse else em.ops
+    lines = ["oneflow_b200 graph v2"]
+    lines += [f"tensor {i} {t}" for i, t in enumerate(em.tensors)]
+    for op in ops:
+        attrs = " ".join(f"{k}={v}" for k, v in op["attr"].items())
+        lines.append(f"op {op['type']} in={','.join(map(str, op['in']))} out={','.join(map(str, op['out']))} {attrs}".rstrip())
+    lines += [f"input {t}" for t in em.inputs] + [f"output {t}" for t in em.outputs]
+    with open(os.path.join(directory, "graph.txt"), "w") as f:
+        f.write("\n".join(lines) + "\n")
+    return directory
+
+
+class InferenceGraph:
+    """ctypes face of the C ABI of the C++ inference API. ``device`` -1 runs the host implementation of the operators."""
+
+    def __init__(self, directory, device=0, n_streams=2):
+        lib_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib")
+        for dep in ("libofb_core.so", "libofb_kernels.so"):
+            ctypes.CDLL(os.path.join(lib_dir, dep), mode=ctypes.RTLD_GLOBAL)
+        self.lib = lib = ctypes.CDLL(os.path.join(lib_dir, "libofb_api.so"))
+        lib.ofb_api_graph_load_ex.restype = ctypes.c_void_p
+        lib.ofb_api_last_error.restype = ctypes.c_char_p
+        for fn in ("ofb_api_graph_in_features", "ofb_api_graph_out_features", "ofb_api_graph_input_numel", "ofb_api_graph_output_numel"):
+            getattr(lib, fn).restype = ctypes.c_longlong
+        self.h = lib.ofb_api_graph_load_ex(directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams))
         if not self.h:
-            raise RuntimeError(self.lib.ofb_api_last_error().decode())
-        self.in_features = self.lib.ofb_api_graph_in_features(ctypes.c_void_p(self.h))
-        self.out_features = self.lib.ofb_api_graph_out_features(ctypes.c_void_p(self.h))
+            raise RuntimeError(lib.ofb_api_last_error().decode())
+        h = ctypes.c_void_p(self.h)
+        self.in_features = lib.ofb_api_graph_in_features(h)
+        self.out_features = lib.ofb_api_graph_out_features(h)
+        self.num_inputs = lib.ofb_api_graph_num_inputs(h)
+        self.num_outputs = lib.ofb_api_graph_num_outputs(h)
 
     def forward(self, x):
+        """One bf16 input [rows, in_features] -> [rows, out_features] (fp32 numpy arrays on the host)."""
         x = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
-        rows = x.shape[0]
+        rows = x.size // self.in_features
         y = np.empty((rows, self.out_features), dtype=np.float32)
         rc = self.lib.ofb_api_graph_forward(ctypes.c_void_p(self.h), x.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(rows),
                                             y.ctypes.data_as(ctypes.c_void_p))
         if rc != 0:
             raise RuntimeError(self.lib.ofb_api_last_error().decode())
         return y
+
+    def run(self, *inputs):
+        """Any number of inputs (float arrays for bf16 inputs, integer arrays for id inputs) -> list of flat fp32 outputs."""
+        h = ctypes.c_void_p(self.h)
+        if len(inputs) != self.num_inputs:
+            raise ValueError(f"the graph takes {self.num_inputs} inputs")
+        bufs = []
+        for i, x in enumerate(inputs):
+            dt = np.int64 if self.lib.ofb_api_graph_input_is_int64(h, ctypes.c_int(i)) else np.float32
+            a = np.ascontiguousarray(np.asarray(x, dtype=dt))
+            if a.size != self.lib.ofb_api_graph_input_numel(h, ctypes.c_int(i)):
+                raise ValueError(f"input {i} has {a.size} elements, the graph was exported for "
+                                 f"{self.lib.ofb_api_graph_input_numel(h, ctypes.c_int(i))}")
+            bufs.append(a)
+        outs = [np.empty(self.lib.ofb_api_graph_output_numel(h, ctypes.c_int(i)), dtype=np.float32) for i in range(self.num_outputs)]
+        in_ptrs = (ctypes.c_void_p * len(bufs))(*[b.ctypes.data for b in bufs])
+        out_ptrs = (ctypes.c_void_p * len(outs))(*[o.ctypes.data for o in outs])
+        rc = self.lib.ofb_api_graph_run(h, in_ptrs, ctypes.c_int(len(bufs)), out_ptrs, ctypes.c_int(len(outs)))
+        if rc != 0:
+            raise RuntimeError(self.lib.ofb_api_last_error().decode())
+        return outs
+
+    def stats(self):
+        s = (ctypes.c_longlong * 6)()
+        self.lib.ofb_api_graph_stats(ctypes.c_void_p(self.h), s)
+        return dict(zip(("ops", "tensors", "activation_bytes", "arena_bytes", "dependencies", "streams_used"), list(s)))
 
     def close(self):
         if self.h:

@@ -295,3 +295,22 @@ def test_doctor_entry_point():
     p = subprocess.run([sys.executable, "-m", "oneflow", "--doctor"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                        cwd=ROOT, timeout=300)
     assert p.returncode == 0 and "version:" in p.stdout and "native kernel library" in p.stdout, p.stdout
+
+
+def test_sdpa_grouped_heads_unequal_lengths_on_cpu():
+    """The CPU path of flow.nn.functional.scaled_dot_product_attention: grouped key/value heads are repeated, and with Sq != Sk
+    the causal diagonal sits at the bottom-right corner (query row r sees key columns <= r + Sk - Sq)."""
+    import oneflow_b200 as flow
+    from oneflow_b200.ops import kernels as K
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 4, 5, 8), torch.randn(2, 2, 7, 8), torch.randn(2, 2, 7, 8)
+    y = flow.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    o, lse = K.fmha_reference(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True, 1 / 8 ** 0.5)
+    assert torch.allclose(y, o.transpose(1, 2), atol=1e-5)
+    # more queries than keys: the first Sq - Sk rows see nothing and come back as zeros with zero gradient
+    q2 = torch.randn(1, 2, 6, 8, requires_grad=True)
+    k2, v2 = torch.randn(1, 2, 3, 8, requires_grad=True), torch.randn(1, 2, 3, 8)
+    o2, lse2 = K.fmha_reference(q2.transpose(1, 2), k2.transpose(1, 2), v2.transpose(1, 2), True, 0.3)
+    assert torch.equal(o2[0, :3], torch.zeros_like(o2[0, :3])) and torch.isinf(lse2[0, :, :3]).all()
+    o2.sum().backward()
+    assert torch.isfinite(q2.grad).all() and torch.isfinite(k2.grad).all() and q2.grad[0, :, :3].abs().sum() == 0

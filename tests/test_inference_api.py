@@ -1,10 +1,20 @@
-"""C++ inference API: export a network, load it through the C ABI of libofb_api.so, compare with PyTorch."""
+"""C++ inference API: export a network, load it through the C ABI of libofb_api.so (graph compiler + executor), compare with
+PyTorch. The host implementation of the operators (device -1) runs everywhere; the GPU tests run the sm_100a kernels."""
 import os
 
+import numpy as np
 import pytest
 import torch
+import torch.nn as nn
+import torch.nn.functional as F
 
 from oneflow_b200.utils import export as E
+
+
+def _bf16_weights(m):
+    for p in m.parameters():
+        p.data = p.data.bfloat16().float()
+    return m
 
 
 def _model():
@@ -12,6 +22,54 @@ def _model():
     return torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.GELU(), torch.nn.LayerNorm(256),
                                torch.nn.Sequential(torch.nn.Linear(256, 128), torch.nn.ReLU()), torch.nn.Dropout(0.1),
                                torch.nn.Linear(128, 16, bias=False))
+
+
+class Block(nn.Module):
+    """Embedding + one pre-LN transformer layer + output projection, written the usual PyTorch way."""
+
+    def __init__(self, d=64, heads=4, vocab=96, seq=16):
+        super().__init__()
+        self.emb, self.pos = nn.Embedding(vocab, d), nn.Embedding(seq, d)
+        self.ln1, self.qkv, self.proj = nn.LayerNorm(d), nn.Linear(d, 3 * d), nn.Linear(d, d)
+        self.ln2, self.fc1, self.fc2 = nn.LayerNorm(d), nn.Linear(d, 4 * d), nn.Linear(4 * d, d)
+        self.head = nn.Linear(d, vocab, bias=False)
+        self.heads = heads
+
+    def forward(self, ids):
+        B, S = ids.shape
+        x = self.emb(ids) + self.pos(torch.arange(S))
+        q, k, v = self.qkv(self.ln1(x)).view(B, S, 3, self.heads, -1).unbind(2)
+        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(B, S, -1))
+        x = x + self.fc2(F.gelu(self.fc1(self.ln2(x))))
+        return self.head(x)
+
+
+class TwoBranches(nn.Module):
+    """Two independent towers (they can run on different streams), joined by a concatenation; an unfused attention built from
+    matmul and softmax; an in-place activation."""
+
+    def __init__(self):
+        super().__init__()
+        self.a1, self.a2 = nn.Linear(32, 64), nn.Linear(64, 32)
+        self.b1, self.b2 = nn.Linear(32, 128), nn.Linear(128, 32)
+        self.act = nn.ReLU(inplace=True)
+        self.out = nn.Linear(64, 8)
+
+    def forward(self, x, y):
+        a = self.a2(torch.tanh(self.a1(x)))                      # [B, T, 32]
+        b = self.b2(self.act(self.b1(y))) * 0.5                  # [B, T, 32]
+        scores = torch.matmul(a, b.transpose(-1, -2)) / 4.0      # [B, T, T]
+        mixed = torch.matmul(torch.softmax(scores, -1), b)       # [B, T, 32]
+        z = torch.cat([a + mixed, b], dim=-1)                    # [B, T, 64]
+        return self.out(z), scores
+
+
+def _run_host(module, inputs, tmp_path, **kw):
+    d = E.export_graph(module, inputs, str(tmp_path))
+    g = E.InferenceGraph(d, device=-1, **kw)
+    outs = g.run(*[t.numpy() for t in inputs])
+    return g, outs
 
 
 def test_export_writes_graph_description(tmp_path):
@@ -25,6 +83,81 @@ def test_export_writes_graph_description(tmp_path):
     assert os.path.getsize(os.path.join(d, "p0.weight.bin")) == 64 * 256 * 2
 
 
+def test_layer_list_graph_on_the_host_runtime(tmp_path):
+    """The layer-list form has no batch size: the plan is compiled for the rows of the first call and again when they change."""
+    model = _bf16_weights(_model().eval())
+    d = E.export_inference_graph(model, str(tmp_path))
+    g = E.InferenceGraph(d, device=-1)
+    for rows in (5, 12, 5):
+        x = torch.randn(rows, 64).bfloat16().float()
+        y = g.forward(x.numpy())
+        torch.testing.assert_close(torch.from_numpy(y), model(x).detach(), atol=3e-2, rtol=3e-2)
+    g.close()
+
+
+def test_transformer_block_graph_on_the_host_runtime(tmp_path):
+    torch.manual_seed(1)
+    m = _bf16_weights(Block().eval())
+    ids = torch.randint(0, 96, (2, 16))
+    g, outs = _run_host(m, (ids,), tmp_path)
+    ref = m(ids).detach().numpy().reshape(-1)
+    assert np.abs(outs[0] - ref).max() < 0.05 * np.abs(ref).max()
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    # the attention reads q, k, v in place from the packed projection; GELU and both residual additions ride in GEMM epilogues
+    assert "op attention" in text and "q_stride=192 kv_stride=192" in text and "op copy" not in text
+    assert "act=gelu" in text and text.count("op binary") == 1 and text.count("op unary") == 0
+    st = g.stats()
+    assert st["ops"] == 11 and st["streams_used"] == 2          # the two embedding lookups are independent
+    assert st["arena_bytes"] < st["activation_bytes"]           # buffers with disjoint lifetimes share memory
+    # other ids, same plan
+    ids2 = torch.randint(0, 96, (2, 16))
+    out2 = g.run(ids2.numpy())[0]
+    assert np.abs(out2 - m(ids2).detach().numpy().reshape(-1)).max() < 0.05 * np.abs(ref).max()
+    g.close()
+
+
+@pytest.mark.parametrize("n_streams", [1, 3])
+def test_branches_concat_and_unfused_attention_on_the_host_runtime(tmp_path, n_streams):
+    torch.manual_seed(2)
+    m = _bf16_weights(TwoBranches().eval())
+    x, y = torch.randn(3, 8, 32).bfloat16().float(), torch.randn(3, 8, 32).bfloat16().float()
+    g, outs = _run_host(m, (x, y), tmp_path, n_streams=n_streams)
+    ref_out, ref_scores = m(x.clone(), y.clone())
+    assert np.abs(outs[0] - ref_out.detach().numpy().reshape(-1)).max() < 3e-2
+    assert np.abs(outs[1] - ref_scores.detach().numpy().reshape(-1)).max() < 3e-2
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert "tb=1" in text                                       # b^T is read in place as a K-major operand, no transpose copy
+    assert g.stats()["streams_used"] == min(n_streams, 2)
+    # many calls through one plan: the scheduler's dependency state carries over correctly
+    for _ in range(3):
+        again = g.run(x.numpy(), y.numpy())
+        assert np.array_equal(again[0], outs[0]) and np.array_equal(again[1], outs[1])
+    g.close()
+
+
+def test_graph_errors_are_reported(tmp_path):
+    class Bad(nn.Module):
+        def forward(self, x):
+            return torch.cumsum(x, -1)
+    with pytest.raises(ValueError, match="cannot export operator cumsum"):
+        E.export_graph(Bad(), (torch.randn(2, 8),), str(tmp_path / "bad"))
+    d = tmp_path / "broken"
+    d.mkdir()
+    (d / "graph.txt").write_text("oneflow_b200 graph v2\ntensor 0 bf16 input 2 4 8\ntensor 1 bf16 act 2 4 8\n"
+                                 "op linear in=0,1,-1,-1 out=1 act=none\ninput 0\noutput 1\n")
+    with pytest.raises(RuntimeError, match="linear"):
+        E.InferenceGraph(str(d), device=-1)
+    (d / "graph.txt").write_text("oneflow_b200 graph v2\ntensor 0 bf16 input 2 4 8\ntensor 1 bf16 act 2 4 8\n"
+                                 "op unary in=1 out=1 fn=3\ninput 0\noutput 1\n")
+    with pytest.raises(RuntimeError, match="before it is written"):
+        E.InferenceGraph(str(d), device=-1)
+    m = _bf16_weights(Block().eval())
+    g, _ = _run_host(m, (torch.randint(0, 96, (2, 16)),), tmp_path / "ok")
+    with pytest.raises(ValueError, match="elements"):
+        g.run(np.zeros((3, 16), dtype=np.int64))
+    g.close()
+
+
 @pytest.mark.gpu
 def test_cpp_inference_matches_pytorch(tmp_path):
     model = _model().eval()
@@ -33,9 +166,41 @@ def test_cpp_inference_matches_pytorch(tmp_path):
     assert (g.in_features, g.out_features) == (64, 16)
     x = torch.randn(37, 64)
     y = g.forward(x.numpy())
-    ref_model = _model().eval()
-    for p in ref_model.parameters():
-        p.data = p.data.bfloat16().float()
+    ref_model = _bf16_weights(_model().eval())
     ref = ref_model(x.bfloat16().float()).detach()
     torch.testing.assert_close(torch.from_numpy(y), ref, atol=5e-2, rtol=5e-2)
+    g.close()
+
+
+@pytest.mark.gpu
+def test_transformer_block_graph_on_the_gpu_runtime(tmp_path):
+    """The same exported graph on the sm_100a kernels (tcgen05 GEMMs with fused epilogues, fused attention reading the packed
+    projection, LayerNorm, gather) over two CUDA streams, against PyTorch fp32 and against the host runtime."""
+    torch.manual_seed(1)
+    m = _bf16_weights(Block(d=128, heads=2, vocab=256, seq=128).eval())
+    ids = torch.randint(0, 256, (2, 128))
+    d = E.export_graph(m, (ids,), str(tmp_path))
+    g = E.InferenceGraph(d, device=0)
+    out = g.run(ids.numpy())[0]
+    ref = m(ids).detach().numpy().reshape(-1)
+    assert np.abs(out - ref).max() < 0.05 * np.abs(ref).max()
+    host = E.InferenceGraph(d, device=-1).run(ids.numpy())[0]
+    assert np.abs(out - host).max() < 0.05 * np.abs(ref).max()
+    for _ in range(3):
+        assert np.array_equal(g.run(ids.numpy())[0], out)
+    g.close()
+
+
+@pytest.mark.gpu
+def test_branches_graph_on_the_gpu_runtime(tmp_path):
+    torch.manual_seed(2)
+    m = _bf16_weights(TwoBranches().eval())
+    x, y = torch.randn(4, 64, 32).bfloat16().float(), torch.randn(4, 64, 32).bfloat16().float()
+    d = E.export_graph(m, (x, y), str(tmp_path))
+    g = E.InferenceGraph(d, device=0, n_streams=2)
+    outs = g.run(x.numpy(), y.numpy())
+    ref_out, ref_scores = m(x.clone(), y.clone())
+    assert np.abs(outs[0] - ref_out.detach().numpy().reshape(-1)).max() < 5e-2
+    assert np.abs(outs[1] - ref_scores.detach().numpy().reshape(-1)).max() < 5e-2
+    assert g.stats()["streams_used"] == 2
     g.close()

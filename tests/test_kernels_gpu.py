@@ -341,6 +341,81 @@ def test_fmha_bwd_padding_ragged():
     close(dv, rv, 3e-2, 2e-2)
 
 
+@pytest.mark.parametrize("D,causal,Sq,Sk,H,Hk", [(64, True, 200, 456, 4, 2), (128, True, 384, 256, 4, 1), (64, False, 130, 300, 6, 3),
+                                                 (128, True, 256, 256, 8, 2), (64, True, 300, 100, 2, 2)])
+def test_fmha_grouped_heads_and_unequal_lengths(D, causal, Sq, Sk, H, Hk):
+    """Grouped-query heads (H query heads on Hk key/value heads) and Sq != Sk with the causal diagonal at the bottom-right
+    corner (Sq > Sk leaves the first rows without any visible key: zero output, zero gradient), forward and backward."""
+    torch.manual_seed(21)
+    B = 2
+    q = torch.randn(B, Sq, H, D, device=DEV, dtype=BF)
+    kv = torch.randn(B, Sk, 2, Hk, D, device=DEV, dtype=BF)
+    k, v = kv[:, :, 0], kv[:, :, 1]
+    sc = 1 / math.sqrt(D)
+    out, lse = K.fmha_fwd(q, k, v, causal=causal)
+    ro, rl = K.fmha_reference(q.cpu(), k.cpu(), v.cpu(), causal, sc)
+    close(out, ro)
+    live = torch.isfinite(rl)
+    assert torch.equal(torch.isfinite(lse.cpu()), live)
+    close(lse.cpu()[live], rl[live], 1e-2, 1e-2)
+    d_o = torch.randn_like(out)
+    dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o, lse, causal=causal)
+    assert dk.shape == (B, Sk, Hk, D) and dq.shape == (B, Sq, H, D)
+    rq, rk, rv = K.fmha_bwd_reference(q.cpu(), k.cpu(), v.cpu(), out.cpu(), d_o.cpu(), lse.cpu(), causal, sc)
+    close(dq, rq, 3e-2, 2e-2)
+    close(dk, rk, 3e-2, 2e-2 * math.sqrt(H // Hk))
+    close(dv, rv, 3e-2, 2e-2 * math.sqrt(H // Hk))
+
+
+@pytest.mark.parametrize("D,causal,p", [(64, True, 0.1), (128, False, 0.3)])
+def test_fmha_dropout_follows_its_philox_mask(D, causal, p):
+    """The kernels drop probabilities by a Philox stream indexed by position; forward and backward agree with the fp32
+    statement that applies the same mask (written out by the mask kernel), the mask keeps about 1 - p of the entries,
+    and another offset gives another mask."""
+    torch.manual_seed(22)
+    B, S, H = 2, 320, 3
+    qkv = torch.randn(B, S, 3, H, D, device=DEV, dtype=BF)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    sc = 1 / math.sqrt(D)
+    seed, off = 0x1234567890ABCDEF, 7
+    mask = K.fmha_dropout_mask(B, H, S, S, p, seed, off, DEV)
+    frac = mask.float().mean().item()
+    assert abs(frac - (1 - p)) < 5e-3, frac
+    assert not torch.equal(mask, K.fmha_dropout_mask(B, H, S, S, p, seed, off + 1, DEV))
+    assert torch.equal(mask, K.fmha_dropout_mask(B, H, S, S, p, seed, off, DEV))
+    out, lse = K.fmha_fwd(q, k, v, causal=causal, dropout_p=p, seed=seed, offset=off)
+    ro, rl = K.fmha_reference(q.cpu(), k.cpu(), v.cpu(), causal, sc, None, p, mask.cpu())
+    close(out, ro)
+    close(lse, rl, 1e-2, 1e-2)
+    d_o = torch.randn_like(out)
+    dq, dk, dv = K.fmha_bwd(q, k, v, out, d_o, lse, causal=causal, dropout_p=p, seed=seed, offset=off)
+    rq, rk, rv = K.fmha_bwd_reference(q.cpu(), k.cpu(), v.cpu(), out.cpu(), d_o.cpu(), lse.cpu(), causal, sc, None, p, mask.cpu())
+    close(dq, rq, 3e-2, 2e-2)
+    close(dk, rk, 3e-2, 2e-2)
+    close(dv, rv, 3e-2, 2e-2)
+
+
+def test_sdpa_entry_point_runs_the_fused_kernels():
+    """flow.nn.functional.scaled_dot_product_attention with grouped heads, Sq != Sk and dropout: fused kernels (the launch
+    counter moves), gradients flow, eval-mode result equals torch's op on the same inputs."""
+    import oneflow_b200 as flow
+    torch.manual_seed(23)
+    B, H, Hk, Sq, Sk, D = 2, 4, 2, 128, 256, 64
+    q = torch.randn(B, H, Sq, D, device=DEV, dtype=BF, requires_grad=True)
+    k = torch.randn(B, Hk, Sk, D, device=DEV, dtype=BF, requires_grad=True)
+    v = torch.randn(B, Hk, Sk, D, device=DEV, dtype=BF, requires_grad=True)
+    n0 = K.launch_count
+    y = flow.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    assert K.launch_count > n0
+    kk, vv = (t.repeat_interleave(H // Hk, dim=1) for t in (k, v))
+    m = torch.ones(Sq, Sk, dtype=torch.bool, device=DEV).tril(Sk - Sq)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), kk.float(), vv.float(), attn_mask=m)
+    close(y, ref)
+    y2 = flow.nn.functional.scaled_dot_product_attention(q, k, v, dropout_p=0.2)
+    y2.float().sum().backward()
+    assert q.grad is not None and k.grad.shape == k.shape and torch.isfinite(v.grad.float()).all()
+
+
 @pytest.mark.parametrize("self_inter,T,D", [(False, 26, 128), (True, 26, 128), (False, 7, 64), (False, 31, 32)])
 def test_dot_feature_interaction(self_inter, T, D):
     from oneflow_b200.ops.interaction import dot_feature_interaction, dot_feature_interaction_reference
