@@ -47,9 +47,39 @@ def _load(name: str):
     return ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
 
 
+class _ProfiledLibrary:
+    """Stands in for the kernel library while a ``flow.profiler.profile`` is active: every exported function is bracketed
+    with CUDA events on the current stream and a host timer, and reported to the recorder together with the tensors that
+    ``ptr()`` converted for the call (their shapes and bytes)."""
+
+    def __init__(self, lib, recorder):
+        self._lib, self._rec = lib, recorder
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if not name.startswith("ofb_") or name in ("ofb_last_error", "ofb_read_status") or name.endswith(("_floats", "_parts", "_max_cols")):
+            return fn
+        rec = self._rec
+
+        def call(*args):
+            return rec.native_call(name, fn, args)
+        call.__name__ = name
+        return call
+
+
+_recorder = None     # set by flow.profiler.profile while it is active
+
+
+def set_recorder(rec):
+    global _recorder
+    _recorder = rec
+
+
 def kernels():
     """The CUDA kernel library (raises NativeLibraryError when it was not built)."""
     global _kernels
+    if _recorder is not None and _kernels is not None:
+        return _ProfiledLibrary(_kernels, _recorder)
     if _kernels is None:
         with _lock:
             if _kernels is None:
@@ -101,4 +131,6 @@ def stream_ptr():
 
 
 def ptr(t):
+    if _recorder is not None and t is not None:
+        _recorder.saw_tensor(t)
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)

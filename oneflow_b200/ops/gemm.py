@@ -124,6 +124,11 @@ def gemm(a, b, *, a_layout="mk", b_layout="nk", bias=None, act=0, residual=None,
         if t is not None and (t.dtype != torch.bfloat16 or t.data_ptr() % 16 != 0):
             raise TypeError(f"gemm: {nm} must be 16-byte aligned bfloat16")
     lib = _native.kernels()
+    if _native._recorder is not None:
+        for t in (a, b, out, bias, residual, aux_in, aux):
+            if t is not None:
+                _native._recorder.saw_tensor(t)
+        _native._recorder.note(flops=2.0 * M * N * K, attrs=f"act={act} a={a_layout} b={b_layout}")
     _native.check(lib.ofb_gemm_bf16(args, _native.stream_ptr()), "ofb_gemm_bf16")
     from . import kernels as _k
     _k._count()

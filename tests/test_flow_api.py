@@ -314,3 +314,101 @@ def test_sdpa_grouped_heads_unequal_lengths_on_cpu():
     assert torch.equal(o2[0, :3], torch.zeros_like(o2[0, :3])) and torch.isinf(lse2[0, :, :3]).all()
     o2.sum().backward()
     assert torch.isfinite(q2.grad).all() and torch.isfinite(k2.grad).all() and q2.grad[0, :, :3].abs().sum() == 0
+
+
+def test_profiler_key_averages_table_on_cpu():
+    """flow.profiler.profile records ATen operators and record_function ranges; key_averages groups them (optionally by input
+    shape) and prints the reference's columns."""
+    import oneflow_b200 as flow
+    x = torch.randn(32, 16)
+    w = torch.randn(16, 16)
+    with flow.profiler.profile(activities=[flow.profiler.ProfilerActivity.CPU], record_shapes=True) as prof:
+        with flow.profiler.record_function("block"):
+            for _ in range(3):
+                y = torch.mm(x, w)
+            z = torch.relu(y)
+        torch.mm(z.t(), z)
+    evs = prof.events()
+    assert [e.name for e in evs][0] == "block" and evs[0].kind == "custom" and len(evs[0].children) >= 4
+    avg = prof.key_averages()
+    by_name = {e.name: e for e in avg}
+    assert by_name["aten::mm"].count == 4 and by_name["aten::relu"].count == 1 and by_name["block"].count == 1
+    assert by_name["aten::mm"].cpu_time_total > 0 and by_name["aten::mm"].cuda_time is None
+    shaped = prof.key_averages(group_by_input_shape=True)
+    mm = sorted((e.input_shapes, e.count) for e in shaped if e.name == "aten::mm")
+    assert mm == [("[(16,32), (32,16)]", 1), ("[(32,16), (16,16)]", 3)]
+    table = shaped.table()
+    head = table.splitlines()[0]
+    for col in ("Name", "CPU time total", "CPU time", "GPU time total", "GPU time", "Number of calls", "Input shapes"):
+        assert col in head
+    assert "Bandwidth" not in head
+    with pytest.raises(AssertionError, match="only work with cuda"):
+        flow.profiler.profile(activities=[flow.profiler.ProfilerActivity.CPU], record_bandwidth_for_cuda=True)
+    with pytest.raises(RuntimeError, match="didn't finish"):
+        flow.profiler.profile().key_averages()
+
+
+def test_remat_evicts_under_a_budget_and_recomputes_for_backward():
+    """flow.remat.scope: activations beyond the budget are evicted in forward (their storage is released), recomputed from
+    their producers when backward needs them, and the gradients equal the ones of a run without a budget."""
+    import oneflow_b200 as flow
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([torch.nn.Linear(128, 128) for _ in range(8)])
+
+        def forward(self, x):
+            for l in self.layers:
+                x = torch.tanh(l(x)) + x
+            return x
+
+    torch.manual_seed(0)
+    m, x = Net(), torch.randn(256, 128)
+    ref = m(x).pow(2).mean()
+    ref.backward()
+    g_ref = [p.grad.clone() for p in m.parameters()]
+    for p in m.parameters():
+        p.grad = None
+    act = 256 * 128 * 4
+    old = flow.remat.is_small_pieces_optimization_enabled()
+    flow.remat.set_small_pieces_optimization(False)
+    try:
+        with flow.remat.scope(budget=12 * act) as r:          # forward alone would hold 8 layers x 3 tensors
+            y = m(x)
+            assert r.stats["forced_eviction_num"] > 0 and flow.remat.allocated_memory("cpu") <= 12 * act
+            loss = y.pow(2).mean()
+            loss.backward()
+            assert r.stats["recomputation_num"] > 0
+        st = flow.remat.stats()
+        g_remat = [q.grad.clone() for q in m.parameters()]
+        for q in m.parameters():
+            q.grad = None
+        with flow.remat.scope() as free:                      # no budget: nothing is evicted, everything is held
+            m(x).pow(2).mean().backward()
+        assert free.stats["forced_eviction_num"] == 0
+        # a recomputation chain holds its inputs while it runs, so the peak may pass the budget, but stays below holding all
+        assert st["peak_bytes"] < free.stats["peak_bytes"]
+        assert torch.equal(loss.detach(), ref.detach())
+        for a, b in zip(g_ref, g_remat):
+            assert torch.equal(a, b)
+        assert torch.isfinite(y).all()                        # the result tensor is in memory after the scope
+        # explicit eviction and the in-memory query
+        with flow.remat.scope() as r:
+            a = torch.randn(64, 64)
+            b = a @ a
+            c = torch.relu(b)
+            assert flow.remat.is_in_memory(b)
+            flow.remat.evict(b)
+            assert not flow.remat.is_in_memory(b) and b.untyped_storage().nbytes() == 0
+            d = b + 1                                         # touching it brings it back
+            assert flow.remat.is_in_memory(b) and torch.equal(d, a @ a + 1)
+            with pytest.raises(RuntimeError, match="cannot be evicted"):
+                flow.remat.evict(a)                           # an input has no producer
+            flow.remat.disable_eviction(c)
+            with pytest.raises(RuntimeError, match="cannot be evicted"):
+                flow.remat.evict(c)
+            assert flow.remat.stats()["eager_eviction_num"] == 1 and flow.remat.stats()["recomputation_num"] == 1
+    finally:
+        flow.remat.set_small_pieces_optimization(old)
+    assert flow.remat.parse_size("1.5GB") == int(1.5 * 2 ** 30)

@@ -354,7 +354,10 @@ def test_fmha_grouped_heads_and_unequal_lengths(D, causal, Sq, Sk, H, Hk):
     sc = 1 / math.sqrt(D)
     out, lse = K.fmha_fwd(q, k, v, causal=causal)
     ro, rl = K.fmha_reference(q.cpu(), k.cpu(), v.cpu(), causal, sc)
-    close(out, ro)
+    # probabilities are rounded to bf16 (2^-9 relative) before they multiply V ~ N(0, 1): rows that see a handful of keys sum a
+    # few terms of magnitude ~0.3 that partly cancel, so the absolute bound is set from that, not from the output's RMS (which
+    # the all-zero rows above the shifted diagonal pull down)
+    close(out, ro, 1e-2, 5e-3)
     live = torch.isfinite(rl)
     assert torch.equal(torch.isfinite(lse.cpu()), live)
     close(lse.cpu()[live], rl[live], 1e-2, 1e-2)
@@ -486,3 +489,66 @@ def test_flow_conv2d_channels_last_uses_igemm():
     # a strided convolution takes the library path and still works
     conv2 = flow.nn.Conv2d(64, 64, 3, stride=2, padding=1).cuda().bfloat16()
     assert conv2(x.detach()).shape == (4, 64, 10, 10)
+
+
+def test_profiler_reports_native_kernels_with_bandwidth():
+    """Inside flow.profiler.profile the native kernel calls appear by name with device time, input shapes and a bandwidth
+    (bytes of the operands / device time); ATen ops appear beside them."""
+    import oneflow_b200 as flow
+    x = torch.randn(4096, 4096, device=DEV, dtype=BF)
+    w = torch.randn(4096, 4096, device=DEV, dtype=BF)
+    g, b = torch.ones(4096, device=DEV, dtype=BF), torch.zeros(4096, device=DEV, dtype=BF)
+    G.gemm(x, w)
+    with flow.profiler.profile(record_shapes=True, record_attrs=True, record_bandwidth_for_cuda=True) as prof:
+        with flow.profiler.record_function("step"):
+            for _ in range(3):
+                y = G.gemm(x, w)
+            K.layer_norm_fwd(y, g, b)
+            torch.relu(y)
+    avg = prof.key_averages(group_by_input_shape=True, group_by_attributes=True)
+    by = {e.name: e for e in avg}
+    assert by["gemm_bf16"].count == 3 and by["layer_norm_fwd"].count == 1 and by["aten::relu"].count == 1 and by["step"].count == 1
+    ge = by["gemm_bf16"]
+    assert ge.cuda_time > 20 and ge.flops == 3 * 2.0 * 4096 ** 3         # a 4096^3 GEMM takes > 20 us on any B200
+    assert ge.input_shapes == "[(4096,4096), (4096,4096), (4096,4096)]" and "act=0" in ge.attributes
+    ln = by["layer_norm_fwd"]
+    assert ln.bandwidth is not None and 50 < ln.bandwidth < 20000       # GB/s: two 32 MB passes in some tens of microseconds
+    assert by["step"].cuda_time_total >= ge.cuda_time_total
+    t = avg.table()
+    assert "Bandwidth" in t.splitlines()[0] and "GB/s" in t and "gemm_bf16" in t
+    # the library is handed out unwrapped again
+    assert type(_native.kernels()).__name__ == "CDLL"
+
+
+def test_remat_on_cuda_matches_unbounded_run():
+    """flow.remat.scope on CUDA tensors: eviction really lowers torch's allocated bytes, backward (on autograd's device thread)
+    recomputes what it needs, gradients equal the unbounded run."""
+    import oneflow_b200 as flow
+    torch.manual_seed(3)
+    layers = torch.nn.ModuleList([torch.nn.Linear(1024, 1024) for _ in range(8)]).to(DEV)
+    x = torch.randn(2048, 1024, device=DEV)
+
+    def run():
+        h = x
+        for l in layers:
+            h = torch.tanh(l(h)) + h
+        return h.pow(2).mean()
+    ref = run()
+    ref.backward()
+    g_ref = [p.grad.clone() for p in layers.parameters()]
+    for p in layers.parameters():
+        p.grad = None
+    act = 2048 * 1024 * 4
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    with flow.remat.scope(budget=10 * act) as r:
+        loss = run()
+        assert r.stats["forced_eviction_num"] > 0
+        assert torch.cuda.memory_allocated() - base <= 11 * act      # 24 activations were produced, at most the budget is held
+        loss.backward()
+        assert r.stats["recomputation_num"] > 0
+    torch.cuda.synchronize()
+    assert torch.allclose(loss, ref)
+    for a, p in zip(g_ref, layers.parameters()):
+        assert torch.allclose(a, p.grad, atol=1e-6, rtol=1e-5)
