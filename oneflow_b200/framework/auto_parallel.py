@@ -124,3 +124,336 @@ def apply_to_module(module, choices: Sequence[Choice], placement):
             b_sbp = _sbp.split(0) if c.kind == "column" else _sbp.broadcast
             m.bias.data = m.bias.data.to_global(placement, b_sbp)
     return module
+
+
+# ------------------------------------------------------------------------------------------------ general SBP graphs
+class SbpGraph:
+    """A graph of operators, each with candidate SBP signatures, joined by tensors whose boxing has a price.
+
+    ``add_node(name, costs)``: ``costs[i]`` = seconds of compute + the operator's own communication under candidate ``i``.
+    ``add_edge(u, v, matrix)``: ``matrix[i][j]`` = seconds to box u's output under u's candidate ``i`` into what v's
+    candidate ``j`` consumes. ``solve()`` returns the assignment with the least total cost, exactly, by the elimination
+    scheme of the reference (oneflow/core/auto_parallel/sbp_graph.cpp: node elimination for nodes with one or two
+    neighbours, edge elimination for parallel edges, node merging when neither applies):
+      * parallel edges between the same two nodes add up;
+      * a node with one neighbour folds into that neighbour's cost vector (minimum over its own candidates);
+      * a node with two neighbours becomes an edge between them (minimum over its candidates of edge + node + edge);
+      * if every remaining node has three or more neighbours, the node with the fewest candidates is merged into a
+        neighbour (the pair becomes one node whose candidates are the pairs);
+    every step records its argmin table, and the choices are read back in reverse order."""
+
+    def __init__(self):
+        self.costs = {}          # node -> list of float
+        self.edges = {}          # frozenset({u, v}) -> (u, v, matrix[i_u][j_v])
+        self.order = []
+
+    def add_node(self, name, costs):
+        if name in self.costs:
+            raise ValueError(f"duplicate node {name}")
+        self.costs[name] = [float(c) for c in costs]
+        self.order.append(name)
+
+    def add_edge(self, u, v, matrix):
+        if u == v:
+            raise ValueError("self edges are not allowed")
+        m = [[float(x) for x in row] for row in matrix]
+        if len(m) != len(self.costs[u]) or any(len(r) != len(self.costs[v]) for r in m):
+            raise ValueError(f"edge {u}->{v}: matrix shape does not match the candidate counts")
+        key = frozenset((u, v))
+        if key in self.edges:
+            a, b, old = self.edges[key]
+            if a != u:
+                m = [[m[j][i] for j in range(len(m))] for i in range(len(m[0]))]
+            self.edges[key] = (a, b, [[x + y for x, y in zip(r0, r1)] for r0, r1 in zip(old, m)])
+        else:
+            self.edges[key] = (u, v, m)
+
+    def _matrix(self, edges, u, v):
+        """Cost matrix indexed [candidate of u][candidate of v]."""
+        a, b, m = edges[frozenset((u, v))]
+        return m if a == u else [[m[j][i] for j in range(len(m))] for i in range(len(m[0]))]
+
+    def solve(self):
+        costs = {k: list(v) for k, v in self.costs.items()}
+        edges = dict(self.edges)
+        members = {k: [k] for k in costs}            # merged nodes: which original nodes a node stands for
+        decode = {k: [(i,) for i in range(len(v))] for k, v in costs.items()}   # candidate -> tuple of original choices
+        trail = []
+
+        def neighbours(n):
+            return [next(iter(k - {n})) for k in edges if n in k]
+
+        while len(costs) > 1:
+            n = next((x for x in costs if len(neighbours(x)) == 0), None)
+            if n is not None:                         # an isolated component: settle it on its own
+                best = min(range(len(costs[n])), key=costs[n].__getitem__)
+                trail.append(("fixed", n, best, costs[n][best]))
+                del costs[n]
+                continue
+            n = next((x for x in costs if len(neighbours(x)) == 1), None)
+            if n is not None:
+                u = neighbours(n)[0]
+                m = self._matrix(edges, u, n)
+                arg = []
+                for i in range(len(costs[u])):
+                    j = min(range(len(costs[n])), key=lambda j: m[i][j] + costs[n][j])
+                    costs[u][i] += m[i][j] + costs[n][j]
+                    arg.append(j)
+                trail.append(("leaf", n, u, arg))
+                del edges[frozenset((u, n))], costs[n]
+                continue
+            n = next((x for x in costs if len(neighbours(x)) == 2), None)
+            if n is not None:
+                u, w = neighbours(n)
+                mu, mw = self._matrix(edges, u, n), self._matrix(edges, n, w)
+                new = [[0.0] * len(costs[w]) for _ in costs[u]]
+                arg = [[0] * len(costs[w]) for _ in costs[u]]
+                for i in range(len(costs[u])):
+                    for k in range(len(costs[w])):
+                        j = min(range(len(costs[n])), key=lambda j: mu[i][j] + costs[n][j] + mw[j][k])
+                        new[i][k] = mu[i][j] + costs[n][j] + mw[j][k]
+                        arg[i][k] = j
+                trail.append(("series", n, u, w, arg))
+                del edges[frozenset((u, n))], edges[frozenset((n, w))], costs[n]
+                key = frozenset((u, w))
+                if key in edges:
+                    old = self._matrix(edges, u, w)
+                    new = [[x + y for x, y in zip(r0, r1)] for r0, r1 in zip(old, new)]
+                edges[key] = (u, w, new)
+                continue
+            # every node has >= 3 neighbours: merge the one with the fewest candidates into one of its neighbours
+            n = min(costs, key=lambda x: (len(costs[x]), len(neighbours(x))))
+            u = min(neighbours(n), key=lambda x: len(costs[x]))
+            m = self._matrix(edges, u, n)
+            name = ("merged", u, n)
+            pairs = [(i, j) for i in range(len(costs[u])) for j in range(len(costs[n]))]
+            costs[name] = [costs[u][i] + costs[n][j] + m[i][j] for i, j in pairs]
+            del edges[frozenset((u, n))]
+            for old_node, pos in ((u, 0), (n, 1)):
+                for x in neighbours(old_node):
+                    mx = self._matrix(edges, old_node, x)
+                    del edges[frozenset((old_node, x))]
+                    add = [[mx[p[pos]][k] for k in range(len(costs[x]))] for p in pairs]
+                    key = frozenset((name, x))
+                    if key in edges:
+                        prev = self._matrix(edges, name, x)
+                        add = [[a + b for a, b in zip(r0, r1)] for r0, r1 in zip(prev, add)]
+                    edges[key] = (name, x, add)
+            trail.append(("merge", name, u, n, pairs))
+            del costs[u], costs[n]
+        choice = {}
+        total = 0.0
+        if costs:
+            last = next(iter(costs))
+            choice[last] = min(range(len(costs[last])), key=costs[last].__getitem__)
+            total = costs[last][choice[last]]
+        for step in reversed(trail):
+            if step[0] == "fixed":
+                choice[step[1]] = step[2]
+                total += step[3]
+            elif step[0] == "leaf":
+                _, n, u, arg = step
+                choice[n] = arg[choice[u]]
+            elif step[0] == "series":
+                _, n, u, w, arg = step
+                choice[n] = arg[choice[u]][choice[w]]
+            else:
+                _, name, u, n, pairs = step
+                choice[u], choice[n] = pairs[choice.pop(name)]
+        return {k: choice[k] for k in self.order}, total
+
+    def cost_of(self, choice):
+        total = sum(self.costs[n][choice[n]] for n in self.costs)
+        for u, v, m in self.edges.values():
+            total += m[choice[u]][choice[v]]
+        return total
+
+
+@dataclass
+class Signature:
+    kind: str                    # "data", "column", "row", "split0", "broadcast", "split_last", "partial", "vocab"
+    ins: tuple                   # SBP each tensor input must arrive in
+    out: object                  # SBP of the output
+    params: dict                 # parameter name -> SBP
+    cost: float = 0.0            # seconds: compute + the signature's own communication (gradient all-reduce)
+
+
+def plan_module(module, example_inputs, world, *, flops_per_s=1.4e15, link_bytes_per_s=7.7e11, train=True, bytes_per_elem=2,
+                input_sbp=None, output_sbp=None):
+    """Auto-parallel for an arbitrary ``torch.nn.Module``: traces it (torch.fx) on the example inputs, gives every operator
+    its candidate SBP signatures, prices every tensor between two operators with the boxing cost model, and solves the
+    resulting SBP graph exactly. Returns ``(plan, total_seconds)`` where ``plan`` maps each node name of the trace to its
+    ``Signature``; ``plan.param_sbp`` maps parameter names (``"fc1.weight"``) to their SBP. 1-D placement of ``world`` ranks.
+
+    Reference: oneflow/core/auto_parallel/sbp_constructor.cpp (one SbpNode per op with its signature list, one SbpEdge per
+    consumed tensor with the copy cost between every pair of signatures), sbp_collector.cpp."""
+    import operator
+
+    import torch
+    import torch.fx
+    from torch.fx.passes.shape_prop import ShapeProp
+
+    if torch.is_tensor(example_inputs):
+        example_inputs = (example_inputs,)
+    leaf_types = (torch.nn.Linear, torch.nn.Embedding, torch.nn.LayerNorm, torch.nn.Softmax, torch.nn.ReLU, torch.nn.GELU, torch.nn.Tanh,
+                  torch.nn.Sigmoid, torch.nn.SiLU, torch.nn.Dropout, torch.nn.Identity)
+
+    class _Tracer(torch.fx.Tracer):
+        def is_leaf_module(self, m, qualname):
+            # this framework's own layers derive from torch's: they are leaves too, whatever module they are defined in
+            return isinstance(m, leaf_types) or super().is_leaf_module(m, qualname)
+
+    gm = torch.fx.GraphModule(module, _Tracer().trace(module))
+    ShapeProp(gm).propagate(*example_inputs)
+    S0, B, P = _sbp.split(0), _sbp.broadcast, _sbp.partial_sum
+    mult = 3.0 if train else 1.0
+    mods = dict(gm.named_modules())
+
+    def meta(n):
+        tm = n.meta.get("tensor_meta")
+        return tm if hasattr(tm, "shape") else None
+
+    def nbytes(n):
+        tm = meta(n)
+        if tm is None:
+            return 0
+        k = 1
+        for d in tm.shape:
+            k *= int(d)
+        return k * bytes_per_elem
+
+    def last(n):
+        return _sbp.split(len(meta(n).shape) - 1)
+
+    def grad_sync(param_bytes):
+        return _copy_cost(P, B, param_bytes, world) / link_bytes_per_s if train else 0.0
+
+    def tensor_args(n):
+        return [a for a in n.all_input_nodes if meta(a) is not None]
+
+    pointwise_fn = {torch.relu, torch.tanh, torch.sigmoid, torch.nn.functional.relu, torch.nn.functional.gelu, torch.nn.functional.silu,
+                    torch.nn.functional.dropout, operator.neg}
+    pointwise_mod = (torch.nn.ReLU, torch.nn.GELU, torch.nn.Tanh, torch.nn.Sigmoid, torch.nn.SiLU, torch.nn.Dropout, torch.nn.Identity)
+    rowwise_mod = (torch.nn.LayerNorm, torch.nn.Softmax)
+    binary_fn = {operator.add: True, torch.add: True, operator.sub: True, torch.sub: True, operator.mul: False, torch.mul: False,
+                 operator.truediv: False}
+
+    sigs = {}
+    for n in gm.graph.nodes:
+        if n.op == "output" or (n.op != "placeholder" and meta(n) is None):
+            continue
+        ins = tensor_args(n)
+        rank = len(meta(n).shape) if meta(n) is not None else 0
+        cands = []
+        if n.op == "placeholder":
+            fixed = input_sbp if input_sbp is not None else None
+            for s in ([fixed] if fixed is not None else [S0, B]):
+                cands.append(Signature("input", (), s, {}, 0.0))
+        elif n.op == "get_attr":
+            cands.append(Signature("broadcast", (), B, {}, 0.0))
+        elif n.op == "call_module" and isinstance(mods[n.target], torch.nn.Linear):
+            m = mods[n.target]
+            tokens = nbytes(n) // bytes_per_elem // m.out_features
+            fl = 2.0 * tokens * m.in_features * m.out_features * mult / world / flops_per_s
+            wb = m.in_features * m.out_features * bytes_per_elem
+            pw, pb = f"{n.target}.weight", f"{n.target}.bias"
+            has_b = m.bias is not None
+            cands.append(Signature("data", (S0,), S0, {pw: B, **({pb: B} if has_b else {})}, fl + grad_sync(wb)))
+            cands.append(Signature("column", (B,), last(n), {pw: S0, **({pb: S0} if has_b else {})}, fl))
+            cands.append(Signature("row", (_sbp.split(len(meta(ins[0]).shape) - 1),), P, {pw: _sbp.split(1), **({pb: B} if has_b else {})}, fl))
+        elif n.op == "call_module" and isinstance(mods[n.target], torch.nn.Embedding):
+            m = mods[n.target]
+            tb = m.num_embeddings * m.embedding_dim * bytes_per_elem
+            pw = f"{n.target}.weight"
+            cands.append(Signature("data", (S0,), S0, {pw: B}, grad_sync(tb)))
+            cands.append(Signature("vocab", (B,), P, {pw: S0}, 0.0))
+            cands.append(Signature("column", (B,), last(n), {pw: _sbp.split(1)}, 0.0))
+        elif (n.op == "call_module" and isinstance(mods[n.target], rowwise_mod)) or \
+                (n.op == "call_function" and n.target in (torch.softmax, torch.nn.functional.softmax, torch.nn.functional.layer_norm)):
+            params = {}
+            if n.op == "call_module":
+                params = {f"{n.target}.{k}": B for k, _ in mods[n.target].named_parameters(recurse=False)}
+                pbytes = sum(p.numel() for p in mods[n.target].parameters(recurse=False)) * bytes_per_elem
+            else:
+                pbytes = 0
+            cands.append(Signature("split0", (S0,) * len(ins), S0, params, grad_sync(pbytes)))
+            cands.append(Signature("broadcast", (B,) * len(ins), B, params, 0.0))
+        elif (n.op == "call_module" and isinstance(mods[n.target], pointwise_mod)) or (n.op == "call_function" and n.target in pointwise_fn) or \
+                (n.op == "call_method" and n.target in ("relu", "tanh", "sigmoid", "contiguous", "clone", "float", "to")):
+            cands.append(Signature("split0", (S0,) * len(ins), S0, {}, 0.0))
+            cands.append(Signature("broadcast", (B,) * len(ins), B, {}, 0.0))
+            if rank >= 2:
+                cands.append(Signature("split_last", (last(n),) * len(ins), last(n), {}, 0.0))
+        elif n.op == "call_function" and n.target in binary_fn and len(ins) == 2 and tuple(meta(ins[0]).shape) == tuple(meta(ins[1]).shape):
+            cands.append(Signature("split0", (S0, S0), S0, {}, 0.0))
+            cands.append(Signature("broadcast", (B, B), B, {}, 0.0))
+            if rank >= 2:
+                cands.append(Signature("split_last", (last(n), last(n)), last(n), {}, 0.0))
+            if binary_fn[n.target]:
+                cands.append(Signature("partial", (P, P), P, {}, 0.0))
+        else:
+            # anything else (reshapes, attention cores, reductions ...) keeps the batch split or runs replicated
+            cands.append(Signature("split0", (S0,) * len(ins), S0, {}, 0.0))
+            cands.append(Signature("broadcast", (B,) * len(ins), B, {}, 0.0))
+        sigs[n] = cands
+
+    g = SbpGraph()
+    for n, cands in sigs.items():
+        g.add_node(n.name, [c.cost for c in cands])
+    out_node = next(n for n in gm.graph.nodes if n.op == "output")
+    results = [a for a in out_node.all_input_nodes if a in sigs]
+    for n, cands in sigs.items():
+        for k, a in enumerate(tensor_args(n)):
+            if a not in sigs:
+                continue
+            nb = nbytes(a)
+            mat = []
+            for ca in sigs[a]:
+                row = []
+                for cn in cands:
+                    want = cn.ins[k] if k < len(cn.ins) else B
+                    c = _copy_cost(ca.out, want, nb, world) / link_bytes_per_s
+                    if train and ca.out != want:       # the gradient travels the transposed route
+                        back_from = P if want.kind == "B" else want
+                        back_to = B if ca.out.kind == "P" else ca.out
+                        c += _copy_cost(back_from, back_to, nb, world) / link_bytes_per_s
+                    row.append(c)
+                mat.append(row)
+            g.add_edge(a.name, n.name, mat)
+    # the results leave as output_sbp (default: whatever is not a partial sum)
+    for r in results:
+        extra = []
+        for c in sigs[r]:
+            want = output_sbp if output_sbp is not None else (S0 if c.out.kind == "P" else c.out)
+            extra.append(_copy_cost(c.out, want, nbytes(r), world) / link_bytes_per_s)
+        g.costs[r.name] = [a + b for a, b in zip(g.costs[r.name], extra)]
+    choice, total = g.solve()
+
+    class Plan(dict):
+        pass
+    plan = Plan()
+    plan.param_sbp = {}
+    plan.graph = g
+    for n, cands in sigs.items():
+        s = cands[choice[n.name]]
+        plan[n.name] = s
+        plan.param_sbp.update(s.params)
+    return plan, total
+
+
+def apply_plan(module, plan, placement):
+    """Distributes the parameters of ``module`` as ``plan.param_sbp`` says. Parameters that are global tensors already (on a 1-D
+    placement) are re-boxed in place; local parameters become global tensors on ``placement``."""
+    from . import global_tensor as GT
+    params = dict(module.named_parameters())
+    for name, s in plan.param_sbp.items():
+        p = params.get(name)
+        if p is None:
+            continue
+        if isinstance(p, GT.GlobalTensor):
+            if list(p.sbp) != [s]:
+                new = GT.rebox(p.detach(), [s])
+                p._local, p._nd_sbp = new._local, new._nd_sbp
+        else:
+            p.data = GT.rebox(GT.to_global(p.data, placement, [_sbp.broadcast]), [s])
+    return module

@@ -380,6 +380,33 @@ def auto_parallel_graph(tmp):
     if rank == 0:
         print("AUTO PARALLEL", choices, auto)
 
+    # general form: any module, traced; the plan of a residual MLP at a small token count is column -> row parallel, and
+    # the module distributed by it computes what the replicated module computes
+    from oneflow_b200.framework import auto_parallel as AP
+
+    class Res(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln, self.fc1, self.fc2 = nn.LayerNorm(64), nn.Linear(64, 256), nn.Linear(256, 64)
+
+        def forward(self, x):
+            return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.ln(x))))
+
+    torch.manual_seed(3)
+    ref_m = Res()
+    xs = torch.randn(8, 64)
+    want = ref_m(xs)
+    plan, _ = AP.plan_module(ref_m, xs, world, input_sbp=flow.sbp.broadcast)
+    assert plan["fc1"].kind == "column" and plan["fc2"].kind == "row", {k: v.kind for k, v in plan.items()}
+    m2 = Res()
+    m2.load_state_dict(ref_m.state_dict())
+    m2.to_global(P, flow.sbp.broadcast)
+    AP.apply_plan(m2, plan, P)
+    assert m2.fc1.weight.sbp[0] == flow.sbp.split(0) and m2.fc2.weight.sbp[0] == flow.sbp.split(1)
+    assert tuple(m2.fc1.weight.to_local().shape) == (256 // world, 64)
+    got = m2(flow.tensor(xs, placement=P, sbp=flow.sbp.broadcast)).to_global(P, flow.sbp.broadcast).to_local()
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+
 
 def data_readers(tmp):
     """Sharded readers: every rank reads its own part files / batch slice; dense outputs are global split(0) tensors;
