@@ -112,9 +112,31 @@ def build_api(verbose=False):
     return lib
 
 
+def build_sanitizers(verbose=False):
+    """The host runtime's multi-threaded self-test (csrc/core/selftest) linked with the runtime's sources under ThreadSanitizer
+    and under AddressSanitizer + UBSan: lib/ofb_core_selftest_tsan, lib/ofb_core_selftest_asan."""
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "core", "*.cpp"))) + [os.path.join(CSRC, "core", "selftest", "core_selftest.cpp")]
+    headers = glob.glob(os.path.join(CSRC, "core", "*.h"))
+    cxx = shutil.which("g++") or "g++"
+    outs = []
+    for tag, flags in (("tsan", ["-fsanitize=thread"]), ("asan", ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"])):
+        exe = os.path.join(LIB, f"ofb_core_selftest_{tag}")
+        if not os.path.exists(exe) or any(_newer(s, exe, headers) for s in srcs):
+            _run([cxx, "-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", "-pthread"] + flags + ["-o", exe] + srcs + ["-lrt", "-ldl"],
+                 os.path.join(OBJ, f"selftest_{tag}.log"))
+            print(f"[build] built {os.path.relpath(exe, ROOT)}", flush=True)
+        outs.append(exe)
+    return outs
+
+
 def build_all(verbose=False):
     return [build_kernels(verbose), build_core(verbose), build_api(verbose)]
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv)
+    if "--sanitizers" in sys.argv:
+        build_sanitizers(verbose="-v" in sys.argv)
+    else:
+        build_all(verbose="-v" in sys.argv)

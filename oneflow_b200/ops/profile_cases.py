@@ -54,6 +54,30 @@ def case_fmha_bwd():
     return (lambda: K.fmha_bwd(q, k, v, o, d_o, lse, causal=True)), fl, 0
 
 
+def _single_rank_tp(tokens, hidden):
+    """A one-rank tensor-parallel context: the fused GEMM+collective kernels run with their exchange logic compiled in but
+    nothing to exchange, which isolates their main loop and epilogue for a single-GPU capture."""
+    import torch.distributed as dist
+    from ..parallel.tensor_parallel import TPContext
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29655", rank=0, world_size=1, device_id=dev)
+    return TPContext(None, [0], dev, max_tokens=tokens, max_cols=hidden, hidden=hidden)
+
+
+def case_gemm_rs_single_rank():
+    tp = _single_rank_tp(8192, 4096)
+    a, w = _bf(8192, 4096), _bf(4096, 4096, scale=0.02)
+    return (lambda: tp.gemm_rs(a, w)), 2 * 8192 * 4096 * 4096, 0
+
+
+def case_ag_gemm_single_rank():
+    tp = _single_rank_tp(8192, 4096)
+    x, w = _bf(8192, 4096), _bf(4096, 4096, scale=0.02)
+    return (lambda: tp.ag_gemm(x, w)), 2 * 8192 * 4096 * 4096, 0
+
+
 def _conv_case(mode):
     from . import conv as C
     n, h, w, cin, cout = 64, 56, 56, 64, 64

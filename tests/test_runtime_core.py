@@ -195,3 +195,22 @@ def test_record_reader_reports_corrupt_and_truncated_files(tmp_path):
     with pytest.raises(R.CoreError, match="ends inside a record"):
         next(r)
     r.close()
+
+
+def test_host_runtime_selftest_under_sanitizers(tmp_path):
+    """The multi-threaded self-test of the host runtime (executor ordering over a non-atomic counter, concurrent allocator
+    use, store clients with heartbeats, table writers with snapshots, the record prefetch thread) runs clean under
+    ThreadSanitizer and under AddressSanitizer + UBSan."""
+    import subprocess
+    from oneflow_b200 import build as B
+    exes = B.build_sanitizers()
+    assert len(exes) == 2
+    for exe in exes:
+        d = tmp_path / os.path.basename(exe)
+        d.mkdir()
+        env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0 exitcode=66", ASAN_OPTIONS="detect_leaks=1 exitcode=67")
+        r = subprocess.run([exe, str(d)], capture_output=True, text=True, timeout=600, env=env)
+        out = r.stdout + r.stderr
+        assert r.returncode == 0, out[-3000:]
+        assert "core selftest ok" in out
+        assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
