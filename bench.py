@@ -412,8 +412,10 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    host0 = time.perf_counter()
     for _ in range(args.steps):
         loss = train_step(dev_tokens)
+    host_enqueue_ms = (time.perf_counter() - host0) * 1e3       # host time to issue the steps, before any wait for the device
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -474,6 +476,8 @@ def main():
             "gpu_launches": launches if impl != "torch_proxy" else 0,
             "model_tflops_per_gpu": flops * args.steps / (ms / 1e3) / 1e12 / world,
             "final_loss": final_loss,
+            # host time to enqueue a step on rank 0: close to ms_per_step means the step is bound by the host issuing launches
+            "host_enqueue_ms_per_step": host_enqueue_ms / args.steps,
             "kernel_status": list(status),
         }
         print(json.dumps(line))

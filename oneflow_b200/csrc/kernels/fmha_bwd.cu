@@ -10,10 +10,12 @@
 //     dV += P^T dO_i             (MN-major x MN-major)      -> TMEM accumulator
 //     dK += dS^T Q_i             (MN-major x MN-major)      -> TMEM accumulator
 //     dQ_i partial = dS K_j      (K-major  x MN-major)      -> TMEM, then staged in shared memory and added to HBM by TMA (cp.reduce.async.bulk)
-// The 128 compute threads own one query row each: they rebuild P from S and the saved
-// log-sum-exp, form dS = P * (dP - delta) * scale, and publish P / dS (bf16) through one
-// shared buffer in the 128-byte swizzled layout that serves both as K-major and MN-major
-// operand. TMEM: S | dP (reused for the dQ partial) | dV | dK = 512 columns at D = 128.
+// 256 compute threads (two warps per scheduler: one alone issued a fifth of the cycles), two per query row: warps
+// 2..5 take key columns 0..63 of the tile, warps 6..9 columns 64..127 (a warp reaches the TMEM lanes of its own
+// quarter only, so the work is split by columns). They rebuild P from S and the saved log-sum-exp, form
+// dS = P * (dP - delta) * scale, and publish P / dS (bf16) through one shared buffer in the 128-byte swizzled
+// layout that serves both as K-major and MN-major operand; the dQ drain and the dK / dV epilogue are split the
+// same way. TMEM: S | dP (reused for the dQ partial) | dV | dK = 512 columns at D = 128.
 //
 // Reference counterpart: oneflow/user/kernels/scaled_dot_product_attention_grad_kernel.cu
 // (flash-attention library call).
@@ -74,7 +76,7 @@ __device__ __forceinline__ bool compute_sync(uint64_t* bar, uint32_t& parity, vo
 }
 
 template <int D, bool DROP>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmdQ, FmhaBwdParams p) {
@@ -133,13 +135,13 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(dv_done, 1);
-    mbar_init(ds_ready, 128);
+    mbar_init(ds_ready, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 128);
+    mbar_init(dq_drained, 256);
     mbar_init(all_done, 1);
-    mbar_init(stg_bar, 128);
+    mbar_init(stg_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -246,9 +248,12 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (n_iter > 0) {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;          // which 64 key columns of the tile this thread takes
     const int r = quad * 32 + lane;
+    const bool issuer = r == 0 && half == 0;   // the one thread that issues and awaits the dQ bulk reductions
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* pds_row = sPdS + r * 128;
+    uint8_t* pds_row = sPdS + half * CH_BYTES + r * 128;   // 64 columns = one swizzled chunk
+    const int kc0 = k0 + half * 64;            // first key column of this half
     const float kLog2e = 1.4426950408889634f;
     bool ok = true;
     uint32_t stg_parity = 0;
@@ -265,40 +270,40 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool dead_row = !row_ok || lse == -INFINITY;
       const bool need_mask = (p.causal && k0 + 127 > q0 + p.causal_off) || (k0 + 128 > kv_limit);
       const int col_max = p.causal ? min(row_g + p.causal_off, kv_limit - 1) : kv_limit - 1;
-      uint32_t pk[64];  // P, later dS, as packed bf16 pairs for this row
-      uint32_t keep_bits[DROP ? 4 : 1];  // dropout: bit c of word w = column 32 * w + c of this tile is kept
+      uint32_t pk[32];  // P, later dS, as packed bf16 pairs for this row's 64 columns
+      uint32_t keep_bits[DROP ? 2 : 1];  // dropout: bit c of word w = column 32 * w + c of this half is kept
       if (!mbar_wait(s_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       // the previous pair's dQ reduction must have finished reading the staging area (= this P buffer)
       if (t > 0) {
-        if (r == 0) tma_store_wait_read<0>();
+        if (issuer) tma_store_wait_read<0>();
         if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
       }
       {
-        uint32_t v[4][32];
+        uint32_t v[2][32];
         __syncwarp();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_addr + c * 32, v[c]);
+        for (int c = 0; c < 2; ++c) tmem_ld_32x32(tS + lane_addr + half * 64 + c * 32, v[c]);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float p0 = fast_exp2_b(__uint_as_float(v[c][i]) * p.scale_log2e - lse2);
             float p1 = fast_exp2_b(__uint_as_float(v[c][i + 1]) * p.scale_log2e - lse2);
-            if (dead_row || (need_mask && k0 + c * 32 + i > col_max)) p0 = 0.f;
-            if (dead_row || (need_mask && k0 + c * 32 + i + 1 > col_max)) p1 = 0.f;
+            if (dead_row || (need_mask && kc0 + c * 32 + i > col_max)) p0 = 0.f;
+            if (dead_row || (need_mask && kc0 + c * 32 + i + 1 > col_max)) p1 = 0.f;
             pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
           }
       }
       if constexpr (DROP) {
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < 2; ++w) {
           uint32_t bits = 0;
 #pragma unroll
           for (int q4 = 0; q4 < 8; ++q4)
             bits |= dropout_keep4(p.drop, static_cast<uint32_t>(b * p.H + h), static_cast<uint32_t>(row_g),
-                                  static_cast<uint32_t>((k0 + w * 32 + q4 * 4) >> 2)) << (q4 * 4);
+                                  static_cast<uint32_t>((kc0 + w * 32 + q4 * 4) >> 2)) << (q4 * 4);
           keep_bits[w] = bits;
         }
       }
@@ -306,17 +311,16 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // 1 / keep is applied to dV at the end). The buffer is free: the MMAs that read dS of the previous iteration
       // were covered by the dq_full wait below in that iteration.
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        uint8_t* chunk = pds_row + (g >> 3) * CH_BYTES;
+      for (int g = 0; g < 8; ++g) {
         uint32_t w4[4] = {pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]};
         if constexpr (DROP) {
-          // pair q of this 16-byte group holds columns 8 * g + 2 * q and + 1
+          // pair q of this 16-byte group holds columns 8 * g + 2 * q and + 1 of this half
           const uint32_t bits = keep_bits[g >> 2] >> ((g & 3) * 8);
 #pragma unroll
           for (int q = 0; q < 4; ++q)
             w4[q] &= ((bits >> (2 * q)) & 1u ? 0x0000FFFFu : 0u) | ((bits >> (2 * q + 1)) & 1u ? 0xFFFF0000u : 0u);
         }
-        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        *reinterpret_cast<uint4*>(pds_row + ((g ^ (r & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -324,18 +328,17 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // dS = P * (dP - delta) * scale
       if (!mbar_wait(dp_full, ph1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
+      {
         uint32_t v[2][32];
         __syncwarp();
-        tmem_ld_32x32(tdP + lane_addr + hh * 64, v[0]);
-        tmem_ld_32x32(tdP + lane_addr + hh * 64 + 32, v[1]);
+        tmem_ld_32x32(tdP + lane_addr + half * 64, v[0]);
+        tmem_ld_32x32(tdP + lane_addr + half * 64 + 32, v[1]);
         tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const int c = hh * 2 + cc;
+            const int c = cc;
             float2 pp = unpack_bf16x2(pk[c * 16 + (i >> 1)]);
             float g0 = __uint_as_float(v[cc][i]), g1 = __uint_as_float(v[cc][i + 1]);
             if constexpr (DROP) {   // the gradient reaches P only through the kept entries, scaled by 1 / keep
@@ -350,11 +353,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       if (!mbar_wait(dv_done, ph1, abort_flag)) { ok = false; break; }
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        uint8_t* chunk = pds_row + (g >> 3) * CH_BYTES;
-        *reinterpret_cast<uint4*>(chunk + (((g & 7) ^ (r & 7)) << 4)) =
-            make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-      }
+      for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<uint4*>(pds_row + ((g ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -365,29 +365,27 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int hh = 0; hh < D / 64; ++hh) {
         if (hh > 0) {
-          if (r == 0) tma_store_wait_read<0>();
+          if (issuer) tma_store_wait_read<0>();
           if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
         }
-        uint32_t v[2][32];
+        uint32_t v[32];     // this half's 32 of the 64 columns of the slab
         __syncwarp();
-        tmem_ld_32x32(tdP + lane_addr + hh * 64, v[0]);
-        tmem_ld_32x32(tdP + lane_addr + hh * 64 + 32, v[1]);
+        tmem_ld_32x32(tdP + lane_addr + hh * 64 + half * 32, v);
         tmem_wait_ld();
         if (hh == D / 64 - 1) {
           // every column of the dQ partial has left TMEM: the dP region may be overwritten
           tc_fence_before();
           mbar_arrive(dq_drained);
         }
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint8_t* st = sPdS + cc * (128 * 128) + r * 128;
+        {
+          uint8_t* st = sPdS + half * (128 * 128) + r * 128;
 #pragma unroll
           for (int g = 0; g < 8; ++g)
-            *reinterpret_cast<uint4*>(st + ((g ^ (r & 7)) << 4)) = make_uint4(v[cc][4 * g], v[cc][4 * g + 1], v[cc][4 * g + 2], v[cc][4 * g + 3]);
+            *reinterpret_cast<uint4*>(st + ((g ^ (r & 7)) << 4)) = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         }
         fence_proxy_async_smem();
         if (!compute_sync(stg_bar, stg_parity, abort_flag)) { ok = false; break; }
-        if (r == 0) {
+        if (issuer) {
           tma_reduce_add_4d(&tmdQ, sPdS, hh * 64, h, q0, b);
           tma_reduce_add_4d(&tmdQ, sPdS + 128 * 128, hh * 64 + 32, h, q0, b);
           tma_store_commit();
@@ -395,8 +393,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (!ok) break;
     }
-    if (r == 0) tma_store_wait<0>();
-    // dK, dV of this key tile: TMEM lane = key row
+    if (issuer) tma_store_wait<0>();
+    // dK, dV of this key tile: TMEM lane = key row; each half writes its half of the D columns
     if (ok) ok = mbar_wait(all_done, 0, abort_flag);
     if (ok) {
       tc_fence_after();
@@ -409,7 +407,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __nv_bfloat16* dst = which == 0 ? dk_row : dv_row;
         const float osc = (DROP && which == 1) ? p.drop.inv_keep : 1.f;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c0 = 0; c0 < D / 64; ++c0) {
+          const int c = half * (D / 64) + c0;
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(src + lane_addr + c * 32, v);
@@ -501,7 +500,7 @@ static int launch_fmha_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   dim3 grid((p.Sk + 127) / 128, p.Hk, p.B);
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
+  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

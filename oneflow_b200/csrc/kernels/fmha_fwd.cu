@@ -6,9 +6,13 @@
 // One CTA owns a 128-row query tile of one (batch, head). Roles:
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles through a 2-stage ring
 //   warp 1      tcgen05 issuer: S_j = Q K_j^T and O_j = P_j V_j, accumulators in TMEM
-//   warps 2..5  softmax: thread t owns query row t; it reads its whole S row with tcgen05.ld
-//               (no shuffles needed), keeps the running max / sum and writes P_j (bf16) to shared
-//               memory in the 128-byte-swizzled K-major layout the second MMA consumes.
+//   warps 2..9  softmax, two warps per scheduler: query row r is shared by two threads (warps 2..5 take key columns
+//               0..63 of every tile, warps 6..9 columns 64..127; a warp reaches the TMEM lanes of its own quarter
+//               only, so the split is by columns). Each reads its half of the S row with tcgen05.ld, the two exchange
+//               their row maxima through shared memory (one bounded rendezvous per tile), keep identical running
+//               maxima and their own partial sums, and write their half of P_j (bf16) to shared memory in the
+//               128-byte-swizzled K-major layout the second MMA consumes. One softmax warp per scheduler issued
+//               only a third of the cycles (a single warp cannot hide the MUFU and TMEM-load latencies); two do.
 // O accumulates in TMEM across all key tiles (the PV product runs with accumulate on); the exponent
 // reference trails the true running maximum by up to 2^8, so O is only rescaled in TMEM
 // (tcgen05.ld / st) on the rare tiles where a row maximum jumps. S is double-buffered in TMEM so the
@@ -42,7 +46,12 @@ struct FmhaFwdCfg {
   static constexpr int Q_BYTES = BM * D * 2;
   static constexpr int KV_BYTES = BN * D * 2;
   static constexpr int P_BYTES = BM * BN * 2;
-  static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 256 + 1024;
+  static constexpr int BAR_BYTES = 128;                 // 14 mbarriers, the TMEM slot, the abort flag
+  static constexpr int XCHG_BYTES = 2 * 2 * 128 * 4;    // row maxima of the two column halves, one buffer per tile parity
+  // At D = 128 the tiles take 224 KiB of the 227 KiB a CTA may have: the dynamic shared memory is declared 1024-byte
+  // aligned (the kernel has no static shared memory, so it starts the CTA's window) instead of being aligned by hand
+  // with a kilobyte of slack; the kernel checks the alignment and reports a status instead of running if it is not there.
+  static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + BAR_BYTES + XCHG_BYTES;
 };
 
 // ex2.approx: one MUFU op (inputs here are <= ~8, -inf gives 0)
@@ -53,7 +62,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int D, bool DROP>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FmhaFwdParams p) {
   using Cfg = FmhaFwdCfg<D>;
@@ -62,8 +71,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t IDESC_O = make_idesc_bf16(BM, D, 0, 1);
   constexpr int CH_BYTES = 128 * 128;  // one [128 rows x 64 elements] swizzled chunk
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {   // uniform over the CTA: nobody has touched a barrier or TMEM yet
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, (int)kStatusBounds);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::Q_BYTES;            // 2 stages
   uint8_t* sV = sK + 2 * Cfg::KV_BYTES;       // 2 stages
@@ -76,8 +89,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 7;     // [2]
   uint64_t* p_full = bars + 9;     // [2]
   uint64_t* pv_done = bars + 11;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* pair_bar = bars + 13;  // rendezvous of the 256 softmax threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + Cfg::BAR_BYTES);   // [2 parities][2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Heavier (later) causal tiles first.
@@ -99,9 +114,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_full[s], 1);
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
+      mbar_init(&p_full[s], 256);
       mbar_init(&pv_done[s], 1);
     }
+    mbar_init(pair_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -179,31 +195,40 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (n_kv > 0) {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;        // which 64 key columns of every tile this thread takes
     const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
     const int row_g = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     // m_ref is the exponent reference actually used for P and l; it trails the true running maximum by at
     // most kLazy (log2 units) so that the TMEM-resident O only has to be rescaled when the maximum jumps.
+    // Both threads of a row carry the same m_ref (they see the same joint maxima); l_run is this half's sum.
     constexpr float kLazy = 8.0f;
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
+    uint32_t pair_parity = 0;
+    auto pair_sync = [&]() {   // bounded: a thread that gave up elsewhere can never leave the others stuck here
+      mbar_arrive(pair_bar);
+      const bool w = mbar_wait(pair_bar, pair_parity, abort_flag);
+      pair_parity ^= 1;
+      return w;
+    };
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       if (!mbar_wait(&s_full[s], ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int col_base = j * BN;
-      const bool need_mask = (p.causal && col_base + BN - 1 > q0 + p.causal_off) || (col_base + BN > kv_limit);
+      const int col_base = j * BN + half * 64;
+      const bool need_mask = (p.causal && j * BN + BN - 1 > q0 + p.causal_off) || (j * BN + BN > kv_limit);
       const int col_max = p.causal ? min(row_g + p.causal_off, kv_limit - 1) : kv_limit - 1;  // last visible column
-      uint32_t sv[4][32];
+      uint32_t sv[2][32];
       __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_addr + s * BN + c * 32, sv[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32(tS + lane_addr + s * BN + half * 64 + c * 32, sv[c]);
       tmem_wait_ld();
-      // eight independent max chains: a single warp per scheduler cannot hide a 128-long dependent chain
+      // eight independent max chains: a dependent chain of 64 cannot be hidden
       float mxs[8] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float e = __uint_as_float(sv[c][i]) * p.scale_log2e;
@@ -211,7 +236,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           sv[c][i] = __float_as_uint(e);
           mxs[i & 7] = fmaxf(mxs[i & 7], e);
         }
-      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      // joint row maximum of the two halves (buffer = tile parity: the partner may be one tile behind, never two)
+      xchg[(s * 2 + half) * 128 + r] = mx;
+      if (!pair_sync()) { ok = false; break; }
+      mx = fmaxf(mx, xchg[(s * 2 + (half ^ 1)) * 128 + r]);
       // Rescale O (and l) only when some row of the warp moved its maximum by more than kLazy.
       const bool jump = mx > m_ref + kLazy;
       if (__any_sync(0xffffffffu, jump)) {
@@ -220,14 +249,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (j > 0) {
           if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
+          // each half rescales its half of the O columns
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
+            const int cc = half * (D / 32) + c;
             uint32_t o[16];
-            tmem_ld_32x16(tO + lane_addr + c * 16, o);
+            tmem_ld_32x16(tO + lane_addr + cc * 16, o);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x16(tO + lane_addr + c * 16, o);
+            tmem_st_32x16(tO + lane_addr + cc * 16, o);
           }
           tmem_wait_st();
         }
@@ -239,9 +270,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&pv_done[s], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
       }
       float rs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      uint8_t* p_row = sP + s * Cfg::P_BYTES + r * 128;
+      uint8_t* chunk = sP + s * Cfg::P_BYTES + half * CH_BYTES + r * 128;   // 64 columns = one swizzled chunk
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -259,10 +290,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           packed[i >> 1] = pack_bf16x2(pv[0], pv[1]);
           packed[(i >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
         }
-        uint8_t* chunk = p_row + (c >> 1) * CH_BYTES;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int grp = (c & 1) * 4 + g;
+          const int grp = c * 4 + g;
           *reinterpret_cast<uint4*>(chunk + ((grp ^ (r & 7)) << 4)) =
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
@@ -273,17 +303,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(&p_full[s]);
     }
     if (ok) {
+      // The row sum is the sum of the two halves' sums. It travels through the maxima buffer of the OTHER parity than the
+      // last tile's: every thread finished reading that one before it could pass the last tile's rendezvous.
       const int so = (n_kv - 1) & 1;
-      ok = mbar_wait(&pv_done[so], ((n_kv - 1) >> 1) & 1, abort_flag);
+      xchg[(((so ^ 1) * 2) + half) * 128 + r] = l_run;
+      ok = pair_sync();
+      const float l_tot = ok ? l_run + xchg[(((so ^ 1) * 2) + (half ^ 1)) * 128 + r] : 0.f;
+      if (ok) ok = mbar_wait(&pv_done[so], ((n_kv - 1) >> 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
-        const float inv = l_run > 0.f ? (DROP ? p.drop.inv_keep : 1.f) / l_run : 0.f;
+        const float inv = l_tot > 0.f ? (DROP ? p.drop.inv_keep : 1.f) / l_tot : 0.f;
         __nv_bfloat16* orow = p.out + ((static_cast<long long>(b) * p.Sq + row_g) * p.H + h) * D;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
+          const int cc = half * (D / 64) + c;     // each half writes its half of the output columns
           uint32_t v[32];
           __syncwarp();
-          tmem_ld_32x32(tO + lane_addr + c * 32, v);
+          tmem_ld_32x32(tO + lane_addr + cc * 32, v);
           tmem_wait_ld();
           if (row_g < p.Sq) {
 #pragma unroll
@@ -291,15 +327,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               float f[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv;
-              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
+              *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) =
                   make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
                              pack_bf16x2(f[6], f[7]));
             }
           }
         }
-        if (row_g < p.Sq && p.lse)
+        if (half == 0 && row_g < p.Sq && p.lse)
           p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + row_g] =
-              l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+              l_tot > 0.f ? (m_ref + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
       }
     }
   } else {
@@ -335,7 +371,7 @@ static int launch_fmha_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   dim3 grid((p.Sq + 127) / 128, p.H, p.B);
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   OFB_CUDA_OK(cudaGetLastError());
   return 0;
 }

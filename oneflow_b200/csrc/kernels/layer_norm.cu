@@ -34,38 +34,91 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
   b = warp_sum(y);
 }
 
+// (count, mean, M2) of two disjoint sets of values merged into one (Chan et al.): the variance comes out of ONE reduction
+// without the cancellation of E[x^2] - mean^2.
+__device__ __forceinline__ void welford_merge(float& n, float& mean, float& m2, float nb, float meanb, float m2b) {
+  const float nt = n + nb;
+  if (nt > 0.f) {
+    const float delta = meanb - mean;
+    const float fb = nb / nt;
+    mean += delta * fb;
+    m2 += m2b + delta * delta * n * fb;
+  }
+  n = nt;
+}
+
+// Block-wide merge of per-thread (count, mean, M2); `red` holds 3*32 floats. Every thread gets the total.
+__device__ __forceinline__ void block_welford(float& n, float& mean, float& m2, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float nb = __shfl_xor_sync(0xffffffffu, n, o), mb = __shfl_xor_sync(0xffffffffu, mean, o), qb = __shfl_xor_sync(0xffffffffu, m2, o);
+    welford_merge(n, mean, m2, nb, mb, qb);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();   // the previous row's readers of `red` are done
+  if (lane == 0) { red[warp] = n; red[32 + warp] = mean; red[64 + warp] = m2; }
+  __syncthreads();
+  n = lane < nw ? red[lane] : 0.f;
+  mean = lane < nw ? red[32 + lane] : 0.f;
+  m2 = lane < nw ? red[64 + lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float nb = __shfl_xor_sync(0xffffffffu, n, o), mb = __shfl_xor_sync(0xffffffffu, mean, o), qb = __shfl_xor_sync(0xffffffffu, m2, o);
+    welford_merge(n, mean, m2, nb, mb, qb);
+  }
+}
+
+// One CTA per row at a time; the row lives in registers as packed 16-byte vectors. The loads of the CTA's NEXT row are
+// issued before the current row's reduction, so a CTA always has a row in flight while it computes (the reduction and
+// its barriers no longer sit between two dependent HBM round trips); mean and variance come from one merged reduction.
 template <int NV>
 __global__ void __launch_bounds__(NV == 4 ? 1024 : 256)
 layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                       const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols, float eps) {
-  __shared__ float red[64];
+  __shared__ float red[96];
   const int nvec = cols >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  uint4 nxt[NV];
+  auto load_row = [&](int row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * cols);
-    float v[NV][8];
-    float s = 0.f, dummy = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
-      if (vi < nvec) {
-        uint4 p = xr[vi];
-        const uint32_t w[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = unpack_bf16x2(w[j]);
-          v[i][2 * j] = f.x; v[i][2 * j + 1] = f.y;
-          s += f.x + f.y;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
-      }
+      nxt[i] = vi < nvec ? __ldcs(xr + vi) : make_uint4(0, 0, 0, 0);
     }
-    block_sum2(s, dummy, red);
-    const float mean = s / cols;
+  };
+  if (static_cast<int>(blockIdx.x) < rows) load_row(blockIdx.x);
+  // gamma and beta stay in registers (packed) for all of the CTA's rows: fetched per row they cost twice the row's own
+  // bytes in L2 traffic. The 1024-thread form has no registers to spare and reads them per row.
+  constexpr bool kKeepParams = NV < 4;
+  uint4 gq[kKeepParams ? NV : 1], bq[kKeepParams ? NV : 1];
+  if constexpr (kKeepParams) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      const bool in = vi < nvec;
+      gq[i] = (gamma && in) ? __ldg(reinterpret_cast<const uint4*>(gamma) + vi) : make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+      bq[i] = (beta && in) ? __ldg(reinterpret_cast<const uint4*>(beta) + vi) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[NV][8];
+    float s = 0.f, cnt = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * blockDim.x;
+      const uint32_t w[4] = {nxt[i].x, nxt[i].y, nxt[i].z, nxt[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(w[j]);
+        v[i][2 * j] = f.x; v[i][2 * j + 1] = f.y;
+        s += f.x + f.y;
+      }
+      if (vi < nvec) cnt += 8.f;
+    }
+    if (row + static_cast<int>(gridDim.x) < rows) load_row(row + gridDim.x);   // next row in flight under this row's math
+    float mean = cnt > 0.f ? s / cnt : 0.f;
     float q = 0.f;
-    dummy = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = threadIdx.x + i * blockDim.x;
@@ -74,7 +127,7 @@ layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
         for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; q += d * d; }
       }
     }
-    block_sum2(q, dummy, red);
+    block_welford(cnt, mean, q, red);
     const float rstd = rsqrtf(q / cols + eps);
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[row] = mean;
@@ -86,23 +139,34 @@ layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
       const int vi = threadIdx.x + i * blockDim.x;
       if (vi < nvec) {
         float g[8], b[8];
-        if (gamma) {
-          uint4 p = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
-          const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+        if constexpr (kKeepParams) {
+          const uint32_t wg[4] = {gq[i].x, gq[i].y, gq[i].z, gq[i].w};
+          const uint32_t wb[4] = {bq[i].x, bq[i].y, bq[i].z, bq[i].w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); g[2 * j] = f.x; g[2 * j + 1] = f.y; }
+          for (int j = 0; j < 4; ++j) {
+            float2 fg = unpack_bf16x2(wg[j]), fb = unpack_bf16x2(wb[j]);
+            g[2 * j] = fg.x; g[2 * j + 1] = fg.y;
+            b[2 * j] = fb.x; b[2 * j + 1] = fb.y;
+          }
         } else {
+          if (gamma) {
+            uint4 p = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+            const uint32_t w[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] = 1.f;
-        }
-        if (beta) {
-          uint4 p = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
-          const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); g[2 * j] = f.x; g[2 * j + 1] = f.y; }
+          } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); b[2 * j] = f.x; b[2 * j + 1] = f.y; }
-        } else {
+            for (int j = 0; j < 8; ++j) g[j] = 1.f;
+          }
+          if (beta) {
+            uint4 p = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+            const uint32_t w[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) b[j] = 0.f;
+            for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(w[j]); b[2 * j] = f.x; b[2 * j + 1] = f.y; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b[j] = 0.f;
+          }
         }
         uint4 o;
         uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
@@ -110,7 +174,7 @@ layer_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
         for (int j = 0; j < 4; ++j)
           ow[j] = pack_bf16x2((v[i][2 * j] - mean) * rstd * g[2 * j] + b[2 * j],
                               (v[i][2 * j + 1] - mean) * rstd * g[2 * j + 1] + b[2 * j + 1]);
-        yr[vi] = o;
+        __stcs(yr + vi, o);
       }
     }
   }

@@ -342,7 +342,44 @@ _MUL_LIKE = {aten.mul.Tensor, aten.mul_.Tensor, aten.div.Tensor, aten.div_.Tenso
              aten.mul_.Scalar, aten.div_.Scalar}
 
 
+def _pointwise_fast(func, args, kwargs):
+    """The common case without any inference: every tensor operand is a global tensor of ONE logical shape, dtype, placement
+    and SBP (scalars beside them are fine), nothing is a partial sum unless the op is linear in them. The op then runs on
+    the local shards as they are and the result carries the operands' description (gradient accumulation of a residual
+    stream, optimizer arithmetic). Returns NotImplemented when the case does not apply."""
+    first = None
+    for a in args:
+        if isinstance(a, GlobalTensor):
+            if first is None:
+                first = a
+            elif a._placement != first._placement or a._nd_sbp != first._nd_sbp or a.shape != first.shape or a.dtype != first.dtype:
+                return NotImplemented
+        elif isinstance(a, torch.Tensor) or isinstance(a, (list, tuple)):
+            return NotImplemented
+    if first is None or kwargs and any(isinstance(v, torch.Tensor) for v in kwargs.values()):
+        return NotImplemented
+    n_glob = sum(isinstance(a, GlobalTensor) for a in args)
+    if any(s_.kind == "P" for s_ in first._nd_sbp):
+        if not ((func in _ADD_LIKE and n_glob == 2 and "alpha" not in kwargs) or (func in _LINEAR_UNARY and n_glob == 1)):
+            return NotImplemented
+    if func._schema.is_mutable:
+        if not isinstance(args[0], GlobalTensor):
+            return NotImplemented
+        if _in_placement(first._placement):
+            func(*[a._local if isinstance(a, GlobalTensor) else a for a in args], **kwargs)
+        return args[0]
+    if not _in_placement(first._placement):
+        return NotImplemented
+    res = func(*[a._local if isinstance(a, GlobalTensor) else a for a in args], **kwargs)
+    if not isinstance(res, torch.Tensor) or res.shape != first._local.shape:
+        return NotImplemented      # not an element-wise result after all: the general rule decides
+    return wrap(res, first.shape, first._placement, first._nd_sbp)
+
+
 def pointwise_rule(func, args, kwargs):
+    fast = _pointwise_fast(func, args, kwargs)
+    if fast is not NotImplemented:
+        return fast
     gs = _globals(args, kwargs)
     pl = _common_placement(gs)
     try:

@@ -144,6 +144,24 @@ def case_batchnorm_relu():
     return (lambda: N.bn_train_fwd(x, gamma, beta, None, True)), 0, 3 * x.numel() * 2
 
 
+def _ln_inputs():
+    rows, cols = 32768, 4096         # 256 MiB per tensor: every pass streams from HBM
+    return _bf(rows, cols), torch.ones(cols, device="cuda", dtype=torch.bfloat16), torch.zeros(cols, device="cuda", dtype=torch.bfloat16)
+
+
+def case_layer_norm_fwd():
+    x, g, b = _ln_inputs()
+    return (lambda: K.layer_norm_fwd(x, g, b)), 0, 2 * x.numel() * 2
+
+
+def case_layer_norm_bwd():
+    x, g, b = _ln_inputs()
+    y, mean, rstd = K.layer_norm_fwd(x, g, b)
+    dy = _bf(*x.shape, scale=0.1)
+    del y
+    return (lambda: K.layer_norm_bwd(dy, x, g, mean, rstd)), 0, 3 * x.numel() * 2
+
+
 def case_adamw():
     n = 64 << 20
     g = torch.randn(n, device="cuda")
