@@ -23,6 +23,9 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=16384)
     ap.add_argument("--no-p2p", action="store_true")
+    ap.add_argument("--collectives", action="store_true",
+                    help="also time the device collectives (all-reduce, reduce-scatter, all-gather, all-to-all, NVLS all-reduce) "
+                         "against NCCL's at 8 / 64 MB and print bus bandwidths")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -78,7 +81,40 @@ def main():
                                                              _native.stream_ptr()), "p2p_bandwidth")
                 us = timeit(f, iters=10, warm=3)
                 bw[f"{nm}_{ctas}ctas"] = round(nbytes / us / 1e3, 1)
+    coll = {}
+    if args.collectives and world > 1:
+        from oneflow_b200.comm.symmetric import DeviceCollectives, MultimemAllReduce
+        arena2 = SymmetricArena(None, list(range(world)), dev, 4 * (64 << 20) + (1 << 22))
+        dc = DeviceCollectives(arena2, io_bytes=64 << 20, ctas=128)
+        mm = MultimemAllReduce(None, list(range(world)), dev, nbytes=64 << 20)
+        for mb in (8, 64):
+            nel = (mb << 20) // 2
+            xfull = torch.randn(nel, device=dev, dtype=bf)
+            xshard = torch.randn(nel // n, device=dev, dtype=bf)
+            out_full = torch.empty_like(xfull)
+            out_shard = torch.empty_like(xshard)
+            nbytes = nel * 2
+            # bus bandwidth as NCCL's tests define it: algorithm bytes x (2(n-1)/n for all-reduce, (n-1)/n for the others)
+            f_ar, f_1 = 2.0 * (n - 1) / n, (n - 1.0) / n
+
+            def gbs(us, f):
+                return round(nbytes * f / us / 1e3, 1)
+            coll[f"all_reduce_{mb}MB_ours"] = gbs(timeit(lambda: dc.all_reduce(xfull), 10, 3), f_ar)
+            coll[f"all_reduce_{mb}MB_nccl"] = gbs(timeit(lambda: dist.all_reduce(xfull), 10, 3), f_ar)
+            if mm.available:
+                coll[f"all_reduce_{mb}MB_nvls"] = gbs(timeit(lambda: mm.all_reduce(xfull), 10, 3), f_ar)
+            coll[f"reduce_scatter_{mb}MB_ours"] = gbs(timeit(lambda: dc.reduce_scatter(xfull.view(n, -1)), 10, 3), f_1)
+            coll[f"reduce_scatter_{mb}MB_nccl"] = gbs(timeit(lambda: dist.reduce_scatter_tensor(out_shard, xfull), 10, 3), f_1)
+            coll[f"all_gather_{mb}MB_ours"] = gbs(timeit(lambda: dc.all_gather(xshard.view(1, -1)), 10, 3), f_1)
+            coll[f"all_gather_{mb}MB_nccl"] = gbs(timeit(lambda: dist.all_gather_into_tensor(out_full, xshard), 10, 3), f_1)
+            rows = 4096
+            cols = nel // rows
+            xa = xfull.view(rows, cols)[:rows // n].contiguous()          # this rank's row shard of a [rows, cols] tensor
+            coll[f"all_to_all_{mb}MB_ours"] = gbs(timeit(lambda: dc.all_to_all(xa, 0, 1, (rows, cols)), 10, 3), f_1 / n)
+            coll[f"all_to_all_{mb}MB_nccl"] = gbs(timeit(lambda: dist.all_to_all_single(out_full, xfull), 10, 3), f_1)
     status = _native.read_status()
+    if rank == 0 and coll:
+        print("COLLECTIVES_BUS_GBS", json.dumps({"ranks": world, **coll}))
     if rank == 0:
         print("GEMM_COMM_US", json.dumps({"ranks": world, "tokens": T, "hidden": H, "ffn": F, **{k: round(v, 1) for k, v in res.items()},
                                           "kernel_status": list(status)}))

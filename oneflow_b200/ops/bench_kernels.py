@@ -85,9 +85,27 @@ def bench_fmha(batch, seq, heads, dim, causal, iters=10):
     ms_b = time_ms(bwd, iters)
     fl = 4.0 * batch * heads * seq * seq * dim * (0.5 if causal else 1.0)
     pk = peaks()
-    return {"kernel": "fmha_fwd/bwd", "batch": batch, "seq": seq, "heads": heads, "dim": dim, "causal": causal,
-            "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9, "bwd_ms": ms_b, "bwd_tflops": 2.5 * fl / ms_b / 1e9,
-            "fwd_frac_of_" + pk["source"] + "_cublas_burst": fl / ms_f / 1e9 / pk["bf16_tflops"]}
+    res = {"kernel": "fmha_fwd/bwd", "batch": batch, "seq": seq, "heads": heads, "dim": dim, "causal": causal,
+           "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9, "bwd_ms": ms_b, "bwd_tflops": 2.5 * fl / ms_b / 1e9,
+           "fwd_frac_of_" + pk["source"] + "_cublas_burst": fl / ms_f / 1e9 / pk["bf16_tflops"]}
+    # the library kernel on the same box, same inputs, same timing loop (right after ours, so the clocks are comparable)
+    try:
+        from flash_attn import flash_attn_func
+    except Exception:
+        return res
+
+    def fa_fwd(i):
+        t = qkv[i % 4]
+        return flash_attn_func(t[:, :, 0], t[:, :, 1], t[:, :, 2], causal=causal)
+    res["flash_attn_fwd_ms"] = time_ms(fa_fwd, iters)
+    leaf = qkv[0].clone().requires_grad_()
+    o = flash_attn_func(leaf[:, :, 0], leaf[:, :, 1], leaf[:, :, 2], causal=causal)
+
+    def fa_bwd(i):
+        leaf.grad = None
+        o.backward(d_o, retain_graph=True)
+    res["flash_attn_bwd_ms"] = time_ms(fa_bwd, iters)
+    return res
 
 
 def bench_layer_norm(rows, cols, iters=20):
