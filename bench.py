@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument("--workload", default="gpt-6.7b", choices=["gpt-6.7b", "gpt-small", "gpt-tiny", "bert-large", "dlrm", "dlrm-tiny", "resnet50", "resnet-tiny"])
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--global-batch", type=int, default=64)
+    ap.add_argument("--profile-step", default="", metavar="FILE",
+                    help="after the timed regions, run one more step under flow.profiler and write its key_averages table "
+                         "(kernel names, device time, calls, bandwidth) to FILE (rank 0)")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0 = choose from --gpus)")
     ap.add_argument("--pp", type=int, default=0, help="pipeline stages (0 = choose from --gpus)")
     return ap.parse_args()
@@ -450,6 +453,19 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
     status = _native.read_status()
+
+    if args.profile_step:
+        import oneflow_b200 as flow
+        with flow.profiler.profile(record_shapes=False, record_bandwidth_for_cuda=True) as prof:
+            loss = train_step(dev_tokens)
+        barrier()
+        if rank == 0:
+            evs = sorted(prof.key_averages(), key=lambda e: -(e.cuda_time_total or 0.0))
+            total = sum(e.cuda_time_total or 0.0 for e in evs if e.kind == "kernel")
+            with open(args.profile_step, "w") as f:
+                f.write(f"one training step, {world} GPU(s), rank 0; device time of all recorded kernels {total / 1e3:.1f} ms "
+                        "(events bracket each launch on the stream: gaps between launches are not in it)\n")
+                f.write(flow.profiler.Events(evs[:60]).table())
 
     if rank == 0:
         tokens_per_step = args.global_batch * seq

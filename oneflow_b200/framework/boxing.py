@@ -24,6 +24,8 @@ from __future__ import annotations
 import logging
 from typing import List, Sequence, Tuple
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -52,6 +54,12 @@ def _device_coll(group, ranks, device):
     return c
 
 
+# Largest tensor the boxing steps hand to the in-kernel collectives (the exchange region holds 64 MB). As stand-alone calls
+# NCCL's collectives measured faster at 8 MB and 64 MB on two B200s (the device collectives copy their input into the arena
+# first); ONEFLOW_DEVICE_COLL_MAX_BYTES lowers the limit, 0 sends every boxing collective to NCCL.
+_DEVICE_COLL_MAX_BYTES = int(os.environ.get("ONEFLOW_DEVICE_COLL_MAX_BYTES", str(64 << 20)))
+
+
 def _use_device_coll(t, n, staged_fp32=True):
     """The in-kernel collectives take fp32 / bf16 tensors that fit their exchange region: the input region holds 64 MB;
     the two-shot all-reduce also stages an fp32 copy (``staged_fp32``), reduce-scatter / all-gather / all-to-all do not."""
@@ -61,7 +69,7 @@ def _use_device_coll(t, n, staged_fp32=True):
         return False
     from ..ops import _native
     need = t.numel() * (4 if staged_fp32 else t.element_size())
-    return _native.kernels_available() and need <= (64 << 20)
+    return _native.kernels_available() and need <= min(64 << 20, _DEVICE_COLL_MAX_BYTES)
 
 
 # ------------------------------------------------------------------------------------------------ 1-D steps

@@ -81,6 +81,10 @@ def main():
                                                              _native.stream_ptr()), "p2p_bandwidth")
                 us = timeit(f, iters=10, warm=3)
                 bw[f"{nm}_{ctas}ctas"] = round(nbytes / us / 1e3, 1)
+    if rank == 0:
+        print("GEMM_COMM_US", json.dumps({"ranks": world, "tokens": T, "hidden": H, "ffn": F, **{k: round(v, 1) for k, v in res.items()}}), flush=True)
+        if bw:
+            print("P2P_GBS", json.dumps({"ranks": world, **bw}), flush=True)
     coll = {}
     if args.collectives and world > 1:
         from oneflow_b200.comm.symmetric import DeviceCollectives, MultimemAllReduce
@@ -109,17 +113,15 @@ def main():
             coll[f"all_gather_{mb}MB_nccl"] = gbs(timeit(lambda: dist.all_gather_into_tensor(out_full, xshard), 10, 3), f_1)
             rows = 4096
             cols = nel // rows
-            xa = xfull.view(rows, cols)[:rows // n].contiguous()          # this rank's row shard of a [rows, cols] tensor
-            coll[f"all_to_all_{mb}MB_ours"] = gbs(timeit(lambda: dc.all_to_all(xa, 0, 1, (rows, cols)), 10, 3), f_1 / n)
+            # this rank's row shard of a [rows, cols / 64, 64] tensor, re-split along the middle axis
+            xa = xfull.view(rows, cols // 64, 64)[:rows // n].contiguous()
+            coll[f"all_to_all_{mb}MB_ours"] = gbs(timeit(lambda: dc.all_to_all(xa, 0, 1, (rows, cols // 64, 64)), 10, 3), f_1 / n)
             coll[f"all_to_all_{mb}MB_nccl"] = gbs(timeit(lambda: dist.all_to_all_single(out_full, xfull), 10, 3), f_1)
     status = _native.read_status()
     if rank == 0 and coll:
         print("COLLECTIVES_BUS_GBS", json.dumps({"ranks": world, **coll}))
     if rank == 0:
-        print("GEMM_COMM_US", json.dumps({"ranks": world, "tokens": T, "hidden": H, "ffn": F, **{k: round(v, 1) for k, v in res.items()},
-                                          "kernel_status": list(status)}))
-        if bw:
-            print("P2P_GBS", json.dumps({"ranks": world, **bw}))
+        print("KERNEL_STATUS", list(status))
     dist.barrier()
 
 
