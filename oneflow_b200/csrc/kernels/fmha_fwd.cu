@@ -231,12 +231,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = __uint_as_float(sv[c][i]) * p.scale_log2e;
-          if (need_mask && col_base + c * 32 + i > col_max) e = -INFINITY;
-          sv[c][i] = __float_as_uint(e);
+          // the scores stay unscaled here: the scale is positive, so the maximum commutes with it, and the exponent below
+          // applies it inside one fused multiply-add (one instruction per element less)
+          float e = __uint_as_float(sv[c][i]);
+          if (need_mask && col_base + c * 32 + i > col_max) { e = -INFINITY; sv[c][i] = __float_as_uint(e); }
           mxs[i & 7] = fmaxf(mxs[i & 7], e);
         }
       float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      mx *= p.scale_log2e;   // -inf stays -inf
       // joint row maximum of the two halves (buffer = tile parity: the partner may be one tile behind, never two)
       xchg[(s * 2 + half) * 128 + r] = mx;
       if (!pair_sync()) { ok = false; break; }
@@ -278,7 +280,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 32; i += 4) {
           float pv[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(__uint_as_float(sv[c][i + e]) - m_use);  // masked entries are -inf -> 0
+          for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(__uint_as_float(sv[c][i + e]), p.scale_log2e, -m_use));  // masked entries are -inf -> 0
           rs[(i >> 2) & 7] += (pv[0] + pv[1]) + (pv[2] + pv[3]);
           if constexpr (DROP) {
             // the row sum keeps every probability; only what multiplies V is dropped (1 / keep is applied at the end)
@@ -433,6 +435,7 @@ OFB_API int ofb_fmha_fwd_ex(const void* q, const void* k, const void* v, long lo
   if (D != 64 && D != 128) return fail("fmha: head dim must be 64 or 128");
   if (Hk <= 0 || H % Hk) return fail("fmha: the number of query heads must be a multiple of the key/value heads");
   if (B <= 0 || Sq <= 0 || Sk <= 0) return fail("fmha: empty problem");
+  if (!(scale > 0.f)) return fail("fmha: the softmax scale must be positive");   // the kernel takes row maxima before scaling
   CUtensorMap tq, tk, tv;
   if (fmha_tensor_map(&tq, q, B, Sq, H, D, q_row_stride)) return -1;
   if (fmha_tensor_map(&tk, k, B, Sk, Hk, D, kv_row_stride)) return -1;
