@@ -492,6 +492,7 @@ def main():
             "gpu_launches": launches if impl != "torch_proxy" else 0,
             "model_tflops_per_gpu": flops * args.steps / (ms / 1e3) / 1e12 / world,
             "final_loss": final_loss,
+            "peak_device_memory_gb": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 2),
             # host time to enqueue a step on rank 0: close to ms_per_step means the step is bound by the host issuing launches
             "host_enqueue_ms_per_step": host_enqueue_ms / args.steps,
             "kernel_status": list(status),

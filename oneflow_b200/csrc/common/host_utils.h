@@ -54,6 +54,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_tiled_fn() {
+  // The encoder is a driver entry point and needs a current context on the CALLING thread. A thread that has only run this
+  // library's code so far (autograd's device thread whose first work item is one of these kernels) has none bound yet:
+  // the first runtime call that needs one binds the primary context of the thread's device.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {

@@ -264,8 +264,9 @@ class _Linear(torch.autograd.Function):
     """y = act(x W^T + b) + residual on local shards, with the tensor-parallel exchange fused into the products."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, residual, act, plan):
+    def forward(ctx, x, w, bias, residual, act, plan, link=None):
         ctx.plan, ctx.act = plan, act
+        ctx.link = link            # (role, _ActLink) when this call is one half of ``mlp``
         ctx.x_shape, ctx.has_res = tuple(x.shape), residual is not None
         ctx.params = (w, bias)
         g = plan is not None
@@ -315,6 +316,8 @@ class _Linear(torch.autograd.Function):
         else:
             y, aux = _gemm_act(x2, w2, b1, act, r2)
         ctx.save_for_backward(x_saved, w2, aux)
+        if link is not None and link[0] == "producer":
+            link[1].aux, link[1].act = aux, act
         if not g:
             return y.view(out_shape)
         lshape = _local_shape_of(out_shape, plan.pl, plan.out_nd)
@@ -329,8 +332,14 @@ class _Linear(torch.autograd.Function):
         g = plan is not None
         if ctx.skip:
             dxp = GT._placeholder(torch.empty(ctx.x_shape, dtype=dy.dtype, device="meta"), plan.pl, (B_,) * plan.pl.ndim)
-            return dxp, None, None, (dy if ctx.has_res else None), None, None
+            return dxp, None, None, (dy if ctx.has_res else None), None, None, None
         x2, w2, aux = ctx.saved_tensors
+        link = ctx.link
+        # the consumer half of ``mlp``: its input is the producer's activation output and nothing else reads that, so the
+        # activation's gradient rides in the epilogue of this call's data-gradient GEMM
+        fuse = {}
+        if link is not None and link[0] == "consumer" and link[1].aux is not None and link[1].act:
+            fuse = {"aux_in": link[1].aux, "act": link[1].act}
         mode = plan.mode if g else "data"
         dres = dy if ctx.has_res else None
         if g:
@@ -346,13 +355,20 @@ class _Linear(torch.autograd.Function):
         dy2 = dyl.reshape(-1, w2.shape[0]) if mode != "row" or not g else dyl.reshape(-1, dyl.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        if act:
+        if act and not (link is not None and link[0] == "producer" and link[1].fused):
             dy2 = K.bias_act_bwd(aux, None, dy2, act)
+        if link is not None:
+            # the link outlives the nodes' saved tensors (it hangs on the context objects until the whole graph is freed):
+            # drop its reference to the pre-activation values as soon as nobody needs it
+            if link[0] == "producer" or fuse:
+                link[1].aux = None
         nd_w = w._nd_sbp if _is_g(w) else None
         nd_b = bias._nd_sbp if _is_g(bias) else None
         x_nd = None
         if mode == "data":
-            dx2 = _gemm(dy2, w2, b_layout="kn") if ctx.needs_input_grad[0] else None
+            dx2 = _gemm(dy2, w2, b_layout="kn", **fuse) if ctx.needs_input_grad[0] else None
+            if fuse and dx2 is not None:
+                link[1].fused = True
             gw = _wgrad(w, _param_nd(plan, nd_w, None), dy2, x2)
             gb = _bgrad(bias, _param_nd(plan, nd_b, None), dy2)
             x_nd = tuple(plan.out_nd[:]) if g else None
@@ -373,7 +389,7 @@ class _Linear(torch.autograd.Function):
             if thunk is not None:
                 out = GT.wrap_deferred(thunk, _local_shape_of(ctx.x_shape, plan.pl, x_nd), ctx.x_shape, dy2.dtype, dy2.device,
                                        plan.pl, x_nd)
-                return out, gw, gb, dres, None, None
+                return out, gw, gb, dres, None, None, None
         else:  # row
             cur = dy._nd_sbp[plan.axis] if plan.n > 1 else B_
             dy_full = dy2
@@ -383,25 +399,29 @@ class _Linear(torch.autograd.Function):
                 if _fusable(dy2, T, n, w2.shape[1], dy2.shape[1]):
                     tp = tp_context(plan.pl, plan.axis, dy2.device, T, max(dy2.shape[1], 8))
                     _trace("all_gather_gemm", T=T, N=w2.shape[1], K=dy2.shape[1], n=n, grad=True)
-                    dy_full, dx2 = tp.ag_gemm(dy2, w2, b_layout="kn", return_gathered=True)
+                    dy_full, dx2 = tp.ag_gemm(dy2, w2, b_layout="kn", return_gathered=True, **fuse)
                 else:
                     from . import boxing
                     ranks = plan.pl.axis_ranks(plan.axis, GT._rank())
                     dy_full = boxing.s_to_b(dy2, 0, plan.pl.axis_group(plan.axis), ranks, plan.idx, T)
-                    dx2 = _gemm(dy_full, w2, b_layout="kn")
+                    dx2 = _gemm(dy_full, w2, b_layout="kn", **fuse)
+                if fuse:
+                    link[1].fused = True
                 # the bias was added once to the reduced rows: its gradient is the column sum over this rank's rows,
                 # a partial sum over the axis
                 gb = _bgrad(bias, _param_nd(plan, nd_b, None, partial_axis=plan.axis), dy2)
             else:
-                dx2 = _gemm(dy2, w2, b_layout="kn")
+                dx2 = _gemm(dy2, w2, b_layout="kn", **fuse)
+                if fuse:
+                    link[1].fused = True
                 gb = _bgrad(bias, _param_nd(plan, nd_b, None), dy2)
             gw = _wgrad(w, _param_nd(plan, nd_w, plan.axis), dy_full, x2)
             x_nd = tuple(_x_nd_data(plan, axis_sbp=S.split(len(ctx.x_shape) - 1)))
         if dx2 is None:
-            return None, gw, gb, dres, None, None
+            return None, gw, gb, dres, None, None, None
         if not g:
-            return dx2.view(ctx.x_shape), gw, gb, dres, None, None
-        return GT.wrap(dx2.view(_local_shape_of(ctx.x_shape, plan.pl, x_nd)), ctx.x_shape, plan.pl, x_nd), gw, gb, dres, None, None
+            return dx2.view(ctx.x_shape), gw, gb, dres, None, None, None
+        return GT.wrap(dx2.view(_local_shape_of(ctx.x_shape, plan.pl, x_nd)), ctx.x_shape, plan.pl, x_nd), gw, gb, dres, None, None, None
 
 
 def _gemm_act(x2, w2, b1, act, r2):
@@ -448,7 +468,27 @@ def _param_nd(plan, nd_param, model_axis, partial_axis=None):
     return tuple(nd)
 
 
-def linear(x, weight, bias=None, *, act=0, residual=None, out_sbp=None):
+class _ActLink:
+    """What the two halves of ``mlp`` share: the producer's pre-activation values and activation code, and whether the
+    consumer's backward already applied the activation's gradient."""
+    __slots__ = ("aux", "act", "fused")
+
+    def __init__(self):
+        self.aux, self.act, self.fused = None, 0, False
+
+
+def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None, out_sbp=None):
+    """``linear(act(linear(x, w1, b1)), w2, b2) + residual`` as one unit: the hidden activation is private to the call, so
+    in backward the activation's gradient is folded into the epilogue of the second layer's data-gradient GEMM (one pass
+    over the [tokens, ffn] hidden gradient less). SBP handling, fused tensor-parallel products and parameter gradients
+    are those of ``linear`` (column-parallel first layer, row-parallel second layer is the Megatron MLP).
+    Reference: the fused MLP family (oneflow/user/kernels/cublas_fused_mlp_kernel.cu, cublas_bias_add_relu_matmul_grad)."""
+    link = _ActLink()
+    h = linear(x, w1, b1, act=act, _link=("producer", link))
+    return linear(h, w2, b2, residual=residual, out_sbp=out_sbp, _link=("consumer", link))
+
+
+def linear(x, weight, bias=None, *, act=0, residual=None, out_sbp=None, _link=None):
     """``act(x @ weight^T + bias) + residual``.
 
     weight: ``[N, K]``, or ``[G, N, K]`` for G stacked projections (the result then has shape ``[..., G, N]``: a packed
@@ -464,7 +504,7 @@ def linear(x, weight, bias=None, *, act=0, residual=None, out_sbp=None):
                                               if s is not None)
         plan = _plan_linear(x, weight, bias, residual, want_rs)
         if plan is not None and _native(_loc(x), _loc(weight)) and _aligned(weight):
-            return _Linear.apply(x, weight, bias, residual, act, plan)
+            return _Linear.apply(x, weight, bias, residual, act, plan, _link)
         w2 = weight if weight.dim() == 2 else weight.reshape(-1, weight.shape[-1])
         y = torch.nn.functional.linear(x, w2, bias.reshape(-1) if bias is not None and bias.dim() > 1 else bias)
         if weight.dim() == 3:
@@ -472,7 +512,7 @@ def linear(x, weight, bias=None, *, act=0, residual=None, out_sbp=None):
         y = G._act_ref(y, act) if act else y
         return y if residual is None else y + residual
     if x.is_cuda and _native(x, weight) and _aligned(weight) and x.numel() > 0:
-        return _Linear.apply(x, weight, bias, residual, act, None)
+        return _Linear.apply(x, weight, bias, residual, act, None, _link)
     w2 = weight if weight.dim() == 2 else weight.reshape(-1, weight.shape[-1])
     y = torch.nn.functional.linear(x, w2, bias.reshape(-1) if bias is not None and bias.dim() > 1 else bias)
     if weight.dim() == 3:

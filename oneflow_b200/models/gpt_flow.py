@@ -130,8 +130,9 @@ class TransformerLayer(nn.Module):
         a = F.fused_attention_qkv_packed(qkv, seq_len=cfg.seq_len, head_size=cfg.head_dim, causal=cfg.causal)
         x = F.linear(a, self.wo, self.bo, residual=x)                             # GEMM -> reduce-scatter (+bias +residual)
         h = F.layer_norm(x, (cfg.hidden,), self.ln2_w, self.ln2_b, cfg.eps)
-        m = F.linear(h, self.w1, self.b1, act=cfg.act)                            # all-gather -> GEMM -> bias + GELU
-        return F.linear(m, self.w2, self.b2, residual=x)                          # GEMM -> reduce-scatter (+bias +residual)
+        # all-gather -> GEMM -> bias + GELU, then GEMM -> reduce-scatter (+bias +residual); as one unit, so that backward folds
+        # the GELU gradient into the data-gradient GEMM of the second layer
+        return F.mlp(h, self.w1, self.b1, self.w2, self.b2, act=cfg.act, residual=x)
 
 
 class GPTHead(nn.Module):

@@ -17,6 +17,13 @@ def linear(input, weight, bias=None):
     return fused_ops.linear(input, weight, bias)
 
 
+def mlp(input, weight1, bias1, weight2, bias2, act="gelu", residual=None):
+    """``linear(act(linear(input, weight1, bias1)), weight2, bias2) + residual`` as one unit (the hidden activation is
+    private to the call, so its gradient is folded into a GEMM epilogue in backward); SBP-aware like ``linear``."""
+    from ..framework import fused_ops
+    return fused_ops.mlp(input, weight1, bias1, weight2, bias2, act=act, residual=residual)
+
+
 def layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5):
     from ..framework import fused_ops
     return fused_ops.layer_norm(input, normalized_shape, weight, bias, eps)

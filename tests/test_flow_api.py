@@ -278,7 +278,10 @@ def test_load_variable_directory_written_by_the_reference():
     the raw bytes in ``out`` and a text-proto ``meta``). ``flow.load`` must read it as it is (read-only, in place)."""
     import struct
     import oneflow as flow
-    root = "/root/reference/oneflow/api/cpp/tests/graph_test_model/affine_with_parameter"
+    # the reference checkout sits beside this repository (or where ONEFLOW_REFERENCE_ROOT points)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("ONEFLOW_REFERENCE_ROOT", os.path.join(os.path.dirname(repo), "reference"))
+    root = os.path.join(ref, "oneflow", "api", "cpp", "tests", "graph_test_model", "affine_with_parameter")
     if not os.path.isdir(os.path.join(root, "model.a")):
         pytest.skip("the reference tree is not mounted")
     sd = flow.load(root)

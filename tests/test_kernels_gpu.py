@@ -552,3 +552,40 @@ def test_remat_on_cuda_matches_unbounded_run():
     assert torch.allclose(loss, ref)
     for a, p in zip(g_ref, layers.parameters()):
         assert torch.allclose(a, p.grad, atol=1e-6, rtol=1e-5)
+
+
+def test_mlp_unit_folds_the_activation_gradient_into_the_gemm():
+    """fused_ops.mlp == linear(gelu(linear(x))) + residual with the same gradients as the fp32 statement; its backward issues one
+    kernel less than the two separate linears (the GELU gradient rides in the second layer's data-gradient GEMM)."""
+    from oneflow_b200.framework import fused_ops as FO
+    torch.manual_seed(31)
+    T, H, F_ = 512, 256, 1024
+    x = (torch.randn(T, H, device=DEV) * 0.5).to(BF).requires_grad_()
+    w1 = (torch.randn(F_, H, device=DEV) * 0.05).to(BF).requires_grad_()
+    b1 = (torch.randn(F_, device=DEV) * 0.1).to(BF).requires_grad_()
+    w2 = (torch.randn(H, F_, device=DEV) * 0.05).to(BF).requires_grad_()
+    b2 = (torch.randn(H, device=DEV) * 0.1).to(BF).requires_grad_()
+    res = (torch.randn(T, H, device=DEV) * 0.5).to(BF).requires_grad_()
+    gy = torch.randn(T, H, device=DEV).to(BF)
+
+    def run(fused):
+        for t in (x, w1, b1, w2, b2, res):
+            t.grad = None
+        n0 = K.launch_count
+        if fused:
+            y = FO.mlp(x, w1, b1, w2, b2, act="gelu", residual=res)
+        else:
+            y = FO.linear(FO.linear(x, w1, b1, act="gelu"), w2, b2, residual=res)
+        y.backward(gy)
+        return y.detach(), [t.grad.clone() for t in (x, w1, b1, w2, b2, res)], K.launch_count - n0
+    y_f, g_f, n_f = run(True)
+    y_s, g_s, n_s = run(False)
+    assert n_f == n_s - 1, (n_f, n_s)
+    xf, w1f, b1f, w2f, b2f, rf = (t.detach().float().requires_grad_() for t in (x, w1, b1, w2, b2, res))
+    ref = torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(xf, w1f, b1f)), w2f, b2f) + rf
+    ref.backward(gy.float())
+    close(y_f, ref.detach())
+    for got, want in zip(g_f, (xf, w1f, b1f, w2f, b2f, rf)):
+        close(got, want.grad, 2e-2)
+    for a, b in zip(g_f, g_s):
+        close(a, b.float(), 2e-2)
