@@ -585,7 +585,12 @@ def test_mlp_unit_folds_the_activation_gradient_into_the_gemm():
     ref = torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(xf, w1f, b1f)), w2f, b2f) + rf
     ref.backward(gy.float())
     close(y_f, ref.detach())
+
+    def rms(t):
+        return float(t.float().pow(2).mean().sqrt())
+    # gradients pass through two bf16 roundings of [T, ffn]-sized intermediates (one in the folded form): elements that nearly
+    # cancel carry an absolute error of a few percent of the tensor's RMS
     for got, want in zip(g_f, (xf, w1f, b1f, w2f, b2f, rf)):
-        close(got, want.grad, 2e-2)
+        close(got, want.grad, 2e-2, 3e-2 * rms(want.grad))
     for a, b in zip(g_f, g_s):
-        close(a, b.float(), 2e-2)
+        close(a, b.float(), 2e-2, 3e-2 * rms(b))
