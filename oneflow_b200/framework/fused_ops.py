@@ -531,12 +531,14 @@ def _aligned(weight):
 # ------------------------------------------------------------------------------------------------ layer norm
 class _LayerNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, pl, nd):
+    def forward(ctx, x, gamma, beta, eps, pl, nd, passthrough=False):
         ctx.pl, ctx.nd, ctx.shape = pl, nd, tuple(x.shape)
         ctx.params = (gamma, beta)
+        ctx.passthrough = passthrough
         if pl is not None and not _in_pl(pl):
             ctx.skip = True
-            return GT._placeholder(torch.empty(x.shape, dtype=x.dtype, device="meta"), pl, nd)
+            ph = GT._placeholder(torch.empty(x.shape, dtype=x.dtype, device="meta"), pl, nd)
+            return (ph, GT._placeholder(torch.empty(x.shape, dtype=x.dtype, device="meta"), pl, nd)) if passthrough else ph
         ctx.skip = False
         xl = _loc(x)
         x2 = xl.reshape(-1, xl.shape[-1])
@@ -546,15 +548,31 @@ class _LayerNorm(torch.autograd.Function):
         y, mean, rstd = K.layer_norm_fwd(x2, _loc(gamma), _loc(beta), eps)
         ctx.save_for_backward(x2, _loc(gamma), mean, rstd)
         y = y.view(xl.shape)
-        return GT.wrap(y, x.shape, pl, nd) if pl is not None else y
+        yo = GT.wrap(y, x.shape, pl, nd) if pl is not None else y
+        if not passthrough:
+            return yo
+        # the input handed on for the residual branch: whatever gradient reaches it comes back to THIS node, which adds it
+        # inside the LayerNorm backward kernel instead of leaving the sum of the two branches to a separate add
+        xo = GT.wrap(xl.view(xl.shape), x.shape, pl, nd) if pl is not None else xl.view(xl.shape)
+        return yo, xo
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dx_pass=None):
         gamma, beta = ctx.params
         pl, nd = ctx.pl, ctx.nd
         if ctx.skip:
-            return dy, None, None, None, None, None
+            return (dy if dy is not None else dx_pass), None, None, None, None, None, None
         x2, gl, mean, rstd = ctx.saved_tensors
+        addend = None
+        if dx_pass is not None:
+            if pl is not None:
+                dx_pass = GT.rebox(dx_pass, nd)
+            addend = _loc(dx_pass).reshape(x2.shape)
+            if not addend.is_contiguous():
+                addend = addend.contiguous()
+        if dy is None:         # only the passed-through input was used
+            dx = addend.view(_loc(dx_pass).shape)
+            return (GT.wrap(dx, ctx.shape, pl, nd) if pl is not None else dx), None, None, None, None, None, None
         if pl is not None:
             dy = GT.rebox(dy, nd)
         dyl = _loc(dy)
@@ -566,11 +584,11 @@ class _LayerNorm(torch.autograd.Function):
         mg, mb = getattr(gamma, "_main_grad", None), getattr(beta, "_main_grad", None)
         want = gamma is not None and gamma.requires_grad
         if want and mg is not None and mb is not None:
-            dx, _, _ = K.layer_norm_bwd(dy2, x2, gl, mean, rstd, dgamma=mg.view(-1), dbeta=mb.view(-1))
+            dx, _, _ = K.layer_norm_bwd(dy2, x2, gl, mean, rstd, add_to_dx=addend, dgamma=mg.view(-1), dbeta=mb.view(-1))
             gamma._grad_nd_sbp = beta._grad_nd_sbp = pnd
             dg = db = None
         else:
-            dx, dg, db = K.layer_norm_bwd(dy2, x2, gl, mean, rstd, want_param_grads=want)
+            dx, dg, db = K.layer_norm_bwd(dy2, x2, gl, mean, rstd, add_to_dx=addend, want_param_grads=want)
             if want:
                 dg, db = dg.to(gl.dtype), db.to(gl.dtype)
                 if pl is not None:
@@ -581,10 +599,16 @@ class _LayerNorm(torch.autograd.Function):
         dx = dx.view(dyl.shape)
         if pl is not None:
             dx = GT.wrap(dx, ctx.shape, pl, nd)
-        return dx, dg, (db if beta is not None else None), None, None, None
+        return dx, dg, (db if beta is not None else None), None, None, None, None
 
 
-def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+def layer_norm_residual(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+    """``(layer_norm(x), x)`` for a pre-norm residual block: use the returned ``x`` for the residual branch. The gradients of
+    the two branches then meet inside the LayerNorm backward kernel (its ``add_to_dx`` input) instead of in a separate add."""
+    return layer_norm(x, normalized_shape, weight, bias, eps, _passthrough=True)
+
+
+def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5, _passthrough=False):
     """LayerNorm over the last axis on the native kernels (rows may be split on any mesh axis; parameters broadcast);
     other forms go to the ATen path."""
     ns = (normalized_shape,) if isinstance(normalized_shape, int) else tuple(normalized_shape)
@@ -596,10 +620,11 @@ def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
             _kind(x, a, n).kind == "B" or (_kind(x, a, n).kind == "S" and _kind(x, a, n).axis != last) for a, n in enumerate(pl.hierarchy)) \
             and all(_kind(weight, a, n).kind == "B" and _kind(bias, a, n).kind == "B" for a, n in enumerate(pl.hierarchy))
         if ok:
-            return _LayerNorm.apply(x, weight, bias, eps, pl, x._nd_sbp)
+            return _LayerNorm.apply(x, weight, bias, eps, pl, x._nd_sbp, _passthrough)
     elif ok and not _is_g(weight) and _native(x, weight, bias) and (x.is_cuda or x.dtype == torch.bfloat16) and x.numel() > 0:
-        return _LayerNorm.apply(x, weight, bias, eps, None, None)
-    return torch.nn.functional.layer_norm(x, ns, weight, bias, eps)
+        return _LayerNorm.apply(x, weight, bias, eps, None, None, _passthrough)
+    y = torch.nn.functional.layer_norm(x, ns, weight, bias, eps)
+    return (y, x) if _passthrough else y
 
 
 # ------------------------------------------------------------------------------------------------ attention

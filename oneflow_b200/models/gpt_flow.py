@@ -125,11 +125,12 @@ class TransformerLayer(nn.Module):
 
     def forward(self, x):
         cfg = self.cfg
-        h = F.layer_norm(x, (cfg.hidden,), self.ln1_w, self.ln1_b, cfg.eps)
+        # (LayerNorm output, the input again for the residual branch: both gradients meet inside the LayerNorm backward kernel)
+        h, x = F.layer_norm_residual(x, (cfg.hidden,), self.ln1_w, self.ln1_b, cfg.eps)
         qkv = F.linear(h, self.wqkv, self.bqkv)                                   # all-gather -> GEMM, heads split
         a = F.fused_attention_qkv_packed(qkv, seq_len=cfg.seq_len, head_size=cfg.head_dim, causal=cfg.causal)
         x = F.linear(a, self.wo, self.bo, residual=x)                             # GEMM -> reduce-scatter (+bias +residual)
-        h = F.layer_norm(x, (cfg.hidden,), self.ln2_w, self.ln2_b, cfg.eps)
+        h, x = F.layer_norm_residual(x, (cfg.hidden,), self.ln2_w, self.ln2_b, cfg.eps)
         # all-gather -> GEMM -> bias + GELU, then GEMM -> reduce-scatter (+bias +residual); as one unit, so that backward folds
         # the GELU gradient into the data-gradient GEMM of the second layer
         return F.mlp(h, self.w1, self.b1, self.w2, self.b2, act=cfg.act, residual=x)
