@@ -212,11 +212,10 @@ def fused_multi_head_attention_inference_v2(*, query, query_layout="BM(HK)", que
 
 
 def fused_mlp(x, weights, biases, skip_final_activation=False):
-    from .nn.modules.fused_mlp import fused_linear_act
-    n = len(weights)
-    for i, (w, b) in enumerate(zip(weights, biases)):
-        x = fused_linear_act(x, w, b, 0 if (i == n - 1 and skip_final_activation) else 3)
-    return x
+    """Linear + ReLU layers as fused GEMMs (bias and ReLU in the epilogue; in backward every layer folds the previous
+    layer's ReLU gradient into its data-gradient GEMM); local and global tensors (framework/fused_ops.mlp_chain)."""
+    from .framework import fused_ops
+    return fused_ops.mlp_chain(x, list(weights), list(biases), act="relu", skip_final_activation=skip_final_activation)
 
 
 def fused_matmul_bias(x, weight, bias, _add_to_output=None, alpha=1.0, beta=1.0):

@@ -266,7 +266,7 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, residual, act, plan, link=None):
         ctx.plan, ctx.act = plan, act
-        ctx.link = link            # (role, _ActLink) when this call is one half of ``mlp``
+        ctx.link = link            # (link this call produces for, link it consumes) when the call is a layer of ``mlp``
         ctx.x_shape, ctx.has_res = tuple(x.shape), residual is not None
         ctx.params = (w, bias)
         g = plan is not None
@@ -316,8 +316,8 @@ class _Linear(torch.autograd.Function):
         else:
             y, aux = _gemm_act(x2, w2, b1, act, r2)
         ctx.save_for_backward(x_saved, w2, aux)
-        if link is not None and link[0] == "producer":
-            link[1].aux, link[1].act = aux, act
+        if link is not None and link[0] is not None:
+            link[0].aux, link[0].act = aux, act
         if not g:
             return y.view(out_shape)
         lshape = _local_shape_of(out_shape, plan.pl, plan.out_nd)
@@ -338,8 +338,9 @@ class _Linear(torch.autograd.Function):
         # the consumer half of ``mlp``: its input is the producer's activation output and nothing else reads that, so the
         # activation's gradient rides in the epilogue of this call's data-gradient GEMM
         fuse = {}
-        if link is not None and link[0] == "consumer" and link[1].aux is not None and link[1].act:
-            fuse = {"aux_in": link[1].aux, "act": link[1].act}
+        prod, cons = link if link is not None else (None, None)
+        if cons is not None and cons.aux is not None and cons.act:
+            fuse = {"aux_in": cons.aux, "act": cons.act}
         mode = plan.mode if g else "data"
         dres = dy if ctx.has_res else None
         if g:
@@ -355,20 +356,21 @@ class _Linear(torch.autograd.Function):
         dy2 = dyl.reshape(-1, w2.shape[0]) if mode != "row" or not g else dyl.reshape(-1, dyl.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        if act and not (link is not None and link[0] == "producer" and link[1].fused):
+        if act and not (prod is not None and prod.fused):
             dy2 = K.bias_act_bwd(aux, None, dy2, act)
-        if link is not None:
-            # the link outlives the nodes' saved tensors (it hangs on the context objects until the whole graph is freed):
-            # drop its reference to the pre-activation values as soon as nobody needs it
-            if link[0] == "producer" or fuse:
-                link[1].aux = None
+        # a link outlives the nodes' saved tensors (it hangs on the context objects until the whole graph is freed): drop its
+        # reference to the pre-activation values as soon as nobody needs it (the dict above keeps them for this call)
+        if prod is not None:
+            prod.aux = None
+        if cons is not None and fuse:
+            cons.aux = None
         nd_w = w._nd_sbp if _is_g(w) else None
         nd_b = bias._nd_sbp if _is_g(bias) else None
         x_nd = None
         if mode == "data":
             dx2 = _gemm(dy2, w2, b_layout="kn", **fuse) if ctx.needs_input_grad[0] else None
             if fuse and dx2 is not None:
-                link[1].fused = True
+                cons.fused = True
             gw = _wgrad(w, _param_nd(plan, nd_w, None), dy2, x2)
             gb = _bgrad(bias, _param_nd(plan, nd_b, None), dy2)
             x_nd = tuple(plan.out_nd[:]) if g else None
@@ -406,14 +408,14 @@ class _Linear(torch.autograd.Function):
                     dy_full = boxing.s_to_b(dy2, 0, plan.pl.axis_group(plan.axis), ranks, plan.idx, T)
                     dx2 = _gemm(dy_full, w2, b_layout="kn", **fuse)
                 if fuse:
-                    link[1].fused = True
+                    cons.fused = True
                 # the bias was added once to the reduced rows: its gradient is the column sum over this rank's rows,
                 # a partial sum over the axis
                 gb = _bgrad(bias, _param_nd(plan, nd_b, None, partial_axis=plan.axis), dy2)
             else:
                 dx2 = _gemm(dy2, w2, b_layout="kn", **fuse)
                 if fuse:
-                    link[1].fused = True
+                    cons.fused = True
                 gb = _bgrad(bias, _param_nd(plan, nd_b, None), dy2)
             gw = _wgrad(w, _param_nd(plan, nd_w, plan.axis), dy_full, x2)
             x_nd = tuple(_x_nd_data(plan, axis_sbp=S.split(len(ctx.x_shape) - 1)))
@@ -484,8 +486,22 @@ def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None, out_sbp=None):
     are those of ``linear`` (column-parallel first layer, row-parallel second layer is the Megatron MLP).
     Reference: the fused MLP family (oneflow/user/kernels/cublas_fused_mlp_kernel.cu, cublas_bias_add_relu_matmul_grad)."""
     link = _ActLink()
-    h = linear(x, w1, b1, act=act, _link=("producer", link))
-    return linear(h, w2, b2, residual=residual, out_sbp=out_sbp, _link=("consumer", link))
+    h = linear(x, w1, b1, act=act, _link=(link, None))
+    return linear(h, w2, b2, residual=residual, out_sbp=out_sbp, _link=(None, link))
+
+
+def mlp_chain(x, weights, biases, *, act="relu", skip_final_activation=False):
+    """A stack of linear layers with one activation between them (the reference's ``fused_mlp``): every hidden activation is
+    private to the call, so each layer's backward folds the previous layer's activation gradient into its data-gradient GEMM."""
+    n = len(weights)
+    prev = None
+    for i, (w, b) in enumerate(zip(weights, biases)):
+        last = i == n - 1
+        a = 0 if (last and skip_final_activation) else act
+        nxt = _ActLink() if (not last and a) else None
+        x = linear(x, w, b, act=a, _link=(nxt, prev))
+        prev = nxt
+    return x
 
 
 def linear(x, weight, bias=None, *, act=0, residual=None, out_sbp=None, _link=None):

@@ -65,6 +65,12 @@ class FusedMLP(torch.nn.Module):
 
     def forward(self, x):
         n = len(self.weights)
+        rates = list(self.hidden_dropout_rate) + [self.out_dropout_rate]
+        if not self.training or not any(rates):
+            # no dropout between the layers: the whole stack is one chain whose hidden activations are private to it
+            from ...framework import fused_ops
+            return fused_ops.mlp_chain(x, list(self.weights), list(self.biases), act="relu",
+                                       skip_final_activation=self.skip_final_activation)
         for i in range(n):
             last = i == n - 1
             act = 0 if (last and self.skip_final_activation) else 3

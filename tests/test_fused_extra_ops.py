@@ -150,3 +150,39 @@ def test_roi_align_matches_torchvision_including_boxes_past_the_border():
             ref = torchvision.ops.roi_align(x, rois, (5, 5), 0.5, sr, aligned)
             assert torch.allclose(_roi_align_impl(x, rois, (5, 5), 0.5, sr, aligned), ref, atol=1e-5)
             assert torch.allclose(flow.roi_align(x, rois, 0.5, 5, 5, sr, aligned), ref, atol=1e-5)
+
+
+def test_fused_mlp_chain_matches_separate_layers():
+    """flow._C.fused_mlp / nn.FusedMLP (a chain of linear + ReLU layers whose backward folds each ReLU gradient into the next
+    data-gradient GEMM on CUDA) give the values and gradients of the plain layer-by-layer statement."""
+    import torch
+    import oneflow_b200 as flow
+    torch.manual_seed(5)
+    x = torch.randn(6, 16, requires_grad=True)
+    ws = [torch.randn(32, 16, requires_grad=True), torch.randn(24, 32, requires_grad=True), torch.randn(8, 24, requires_grad=True)]
+    bs = [torch.randn(32, requires_grad=True), torch.randn(24, requires_grad=True), torch.randn(8, requires_grad=True)]
+    for skip in (False, True):
+        for t in [x] + ws + bs:
+            t.grad = None
+        y = flow._C.fused_mlp(x, ws, bs, skip_final_activation=skip)
+        y.pow(2).sum().backward()
+        got = [t.grad.clone() for t in [x] + ws + bs]
+        for t in [x] + ws + bs:
+            t.grad = None
+        h = x
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            h = torch.nn.functional.linear(h, w, b)
+            if not (skip and i == 2):
+                h = torch.relu(h)
+        assert torch.allclose(y, h, atol=1e-5)
+        h.pow(2).sum().backward()
+        for a, t in zip(got, [x] + ws + bs):
+            assert torch.allclose(a, t.grad, atol=1e-4)
+    m = flow.nn.FusedMLP(16, [32, 24], 8, skip_final_activation=True)
+    out = m(x.detach())
+    ref = x.detach()
+    for i in range(3):
+        ref = torch.nn.functional.linear(ref, m.weight(i), m.bias(i))
+        if i < 2:
+            ref = torch.relu(ref)
+    assert torch.allclose(out, ref, atol=1e-5)

@@ -204,3 +204,33 @@ def test_branches_graph_on_the_gpu_runtime(tmp_path):
     assert np.abs(outs[1] - ref_scores.detach().numpy().reshape(-1)).max() < 5e-2
     assert g.stats()["streams_used"] == 2
     g.close()
+
+
+class Glu(nn.Module):
+    """Views that need strided copies (chunk halves, a slice of an input, a row select, a transposed output), a tied weight
+    used by an embedding lookup and by a linear layer, softmax output."""
+
+    def __init__(self):
+        super().__init__()
+        self.emb, self.fc, self.ln = nn.Embedding(50, 32), nn.Linear(32, 64), nn.LayerNorm(32)
+
+    def forward(self, ids, y):
+        x = self.emb(ids)
+        a, b = self.fc(x).chunk(2, dim=-1)
+        g = self.ln(a * torch.sigmoid(b) + y[:, 1:, :])
+        logits = F.linear(g[:, -1], self.emb.weight)
+        return torch.softmax(logits, -1), g.transpose(1, 2).contiguous()
+
+
+def test_views_tied_weights_and_two_outputs_on_the_host_runtime(tmp_path):
+    torch.manual_seed(4)
+    m = _bf16_weights(Glu().eval())
+    ids, y = torch.randint(0, 50, (3, 7)), torch.randn(3, 8, 32).bfloat16().float()
+    g, outs = _run_host(m, (ids, y), tmp_path)
+    r1, r2 = m(ids, y)
+    assert np.abs(outs[0] - r1.detach().numpy().reshape(-1)).max() < 3e-2
+    assert np.abs(outs[1] - r2.detach().numpy().reshape(-1)).max() < 3e-2
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("file=") == 5           # embedding table (once, although two operators read it), fc.weight / bias, ln.weight / bias
+    assert text.count("op copy") == 5 and text.count("op embedding") == 1
+    g.close()

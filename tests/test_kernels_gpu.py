@@ -594,3 +594,34 @@ def test_mlp_unit_folds_the_activation_gradient_into_the_gemm():
         close(got, want.grad, 2e-2, 3e-2 * rms(want.grad))
     for a, b in zip(g_f, g_s):
         close(a, b.float(), 2e-2, 3e-2 * rms(b))
+
+
+def test_fused_mlp_chain_on_cuda():
+    """flow._C.fused_mlp on bf16 CUDA tensors: three linear + ReLU layers, each ReLU gradient folded into the next layer's
+    data-gradient GEMM (no separate activation-gradient kernel runs), values and gradients against the fp32 statement."""
+    import oneflow_b200 as flow
+    torch.manual_seed(32)
+    T = 384
+    dims = [256, 512, 384, 128]
+    x = (torch.randn(T, dims[0], device=DEV) * 0.5).to(BF).requires_grad_()
+    ws = [(torch.randn(dims[i + 1], dims[i], device=DEV) * 0.06).to(BF).requires_grad_() for i in range(3)]
+    bs = [(torch.randn(dims[i + 1], device=DEV) * 0.1).to(BF).requires_grad_() for i in range(3)]
+    gy = torch.randn(T, dims[-1], device=DEV).to(BF)
+    n0 = K.launch_count
+    y = flow._C.fused_mlp(x, ws, bs, skip_final_activation=True)
+    y.backward(gy)
+    # 3 forward GEMMs; backward: 3 data-gradient + 3 weight-gradient GEMMs + 3 bias column sums, no activation-gradient kernel
+    assert K.launch_count - n0 == 12, K.launch_count - n0
+    ref_in = [t.detach().float().requires_grad_() for t in [x] + ws + bs]
+    h = ref_in[0]
+    for i in range(3):
+        h = torch.nn.functional.linear(h, ref_in[1 + i], ref_in[4 + i])
+        if i < 2:
+            h = torch.relu(h)
+    h.backward(gy.float())
+    close(y, h.detach())
+
+    def rms(t):
+        return float(t.float().pow(2).mean().sqrt())
+    for got, want in zip([x] + ws + bs, ref_in):
+        close(got.grad, want.grad, 2e-2, 3e-2 * rms(want.grad))
