@@ -612,16 +612,38 @@ def test_fused_mlp_chain_on_cuda():
     y.backward(gy)
     # 3 forward GEMMs; backward: 3 data-gradient + 3 weight-gradient GEMMs + 3 bias column sums, no activation-gradient kernel
     assert K.launch_count - n0 == 12, K.launch_count - n0
+    # fp32 statement that rounds the hidden activations to bf16 where the kernels store them (straight-through for the
+    # gradient): ReLU is discontinuous, so a statement with unrounded hidden values switches a few units per token the other
+    # way (|pre-activation| below the rounding noise of its inputs) and its gradients then differ by several percent of
+    # their RMS on whole rows: measured 10 - 30 % of the elements beyond 3 % of RMS, against none for GELU
     ref_in = [t.detach().float().requires_grad_() for t in [x] + ws + bs]
     h = ref_in[0]
     for i in range(3):
         h = torch.nn.functional.linear(h, ref_in[1 + i], ref_in[4 + i])
         if i < 2:
             h = torch.relu(h)
+            h = h + (h.bfloat16().float() - h).detach()
     h.backward(gy.float())
     close(y, h.detach())
 
     def rms(t):
         return float(t.float().pow(2).mean().sqrt())
+    # even so a hidden value can round to the neighbouring bf16 number in the kernel (other summation order), which now and
+    # then switches a unit of the next layer: up to 1 % of the elements may sit outside the bound, none far outside
     for got, want in zip([x] + ws + bs, ref_in):
-        close(got.grad, want.grad, 2e-2, 3e-2 * rms(want.grad))
+        g, w_ = got.grad.float(), want.grad
+        r = rms(w_)
+        bad = (g - w_).abs() > 3e-2 * r + 2e-2 * w_.abs()
+        assert bad.float().mean().item() < 0.01, bad.float().mean().item()
+        assert (g - w_).abs().max().item() < 0.5 * r
+    # and the folded form equals the layer-by-layer form bit for bit
+    got = [t.grad.clone() for t in [x] + ws + bs]
+    for t in [x] + ws + bs:
+        t.grad = None
+    from oneflow_b200.framework import fused_ops as FO
+    h2 = x
+    for i in range(3):
+        h2 = FO.linear(h2, ws[i], bs[i], act=("relu" if i < 2 else 0))
+    h2.backward(gy)
+    for a, t in zip(got, [x] + ws + bs):
+        assert torch.equal(a, t.grad)
