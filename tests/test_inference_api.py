@@ -234,3 +234,30 @@ def test_views_tied_weights_and_two_outputs_on_the_host_runtime(tmp_path):
     assert text.count("file=") == 5           # embedding table (once, although two operators read it), fc.weight / bias, ln.weight / bias
     assert text.count("op copy") == 5 and text.count("op embedding") == 1
     g.close()
+
+
+def test_cpp_program_links_the_api_and_runs_a_graph(tmp_path):
+    """A C++ program (csrc/api/examples/run_graph.cpp) compiled against oneflow_api.h and libofb_api.so loads an exported
+    transformer block and reproduces what the Python binding computes: the API is usable from C++ as documented."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    api = os.path.join(root, "oneflow_b200", "csrc", "api")
+    lib = os.path.join(root, "oneflow_b200", "lib")
+    exe = str(tmp_path / "run_graph")
+    r = subprocess.run(["g++", "-std=c++17", "-O1", os.path.join(api, "examples", "run_graph.cpp"), "-I", api, "-L", lib, "-lofb_api",
+                        "-lofb_kernels", "-lofb_core", f"-Wl,-rpath,{lib}", "-o", exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    torch.manual_seed(1)
+    m = _bf16_weights(Block().eval())
+    ids = torch.randint(0, 96, (2, 16))
+    d = E.export_graph(m, (ids,), str(tmp_path / "g"))
+    ids.numpy().astype(np.int64).tofile(str(tmp_path / "ids.bin"))
+    r = subprocess.run([exe, d, "-1", str(tmp_path / "ids.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = np.array([float(v) for v in r.stdout.strip().split()], dtype=np.float32)
+    py = E.InferenceGraph(d, device=-1).run(ids.numpy())[0]
+    assert out.shape == py.shape and np.allclose(out, py, rtol=1e-5, atol=1e-5)
+    assert "ops 11" in r.stderr
