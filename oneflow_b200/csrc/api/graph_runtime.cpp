@@ -19,6 +19,8 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <map>
@@ -282,6 +284,17 @@ struct Graph::Impl {
   std::vector<cudaStream_t> streams;
   std::vector<cudaEvent_t> events;             // one per planned operator
   std::unique_ptr<Plan> plan;
+  // GPU only: the plan replayed as one CUDA graph. The first Forward of a plan runs through the scheduler (it also performs
+  // every one-time initialisation the kernels do on first use); the second one records the same launches (same streams,
+  // cross-stream edges as events) into a graph on the calling thread, and from then on a Forward is: copy the inputs into
+  // the plan's own input buffers, one graph launch, copy the outputs out.
+  std::vector<std::shared_ptr<void>> input_bufs;   // per graph input, static addresses
+  cudaGraphExec_t graph_exec = nullptr;
+  cudaEvent_t fork_event = nullptr;
+  std::vector<cudaEvent_t> join_events;
+  int runs_of_plan = 0;
+  int64_t graph_replays = 0;
+  bool graph_disabled = false;
   std::mutex run_mu;
   // per call
   std::vector<void*> bound;                    // per root: address of inputs for the running call
@@ -290,6 +303,9 @@ struct Graph::Impl {
 
   ~Impl() {
     if (executor) ofc_executor_destroy(executor);
+    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    if (fork_event) cudaEventDestroy(fork_event);
+    for (auto e : join_events) cudaEventDestroy(e);
     for (auto e : events) cudaEventDestroy(e);
     for (auto s : streams) cudaStreamDestroy(s);
     for (void* al : allocators) ofc_allocator_destroy(al);
@@ -311,6 +327,7 @@ struct Graph::Impl {
     return b + plan->byte_off[static_cast<size_t>(tensor)];
   }
   void run_op(int index);
+  bool capture_plan();
   void run_op_device(const PlannedOp& p, cudaStream_t s);
   void run_op_host(const PlannedOp& p);
 };
@@ -600,6 +617,25 @@ void Graph::Impl::compile(int64_t rows) {
   if (!executor) {
     executor = ofc_executor_create(n_streams);
     if (!executor) throw std::runtime_error(std::string("executor: ") + ofc_last_error());
+  }
+  if (graph_exec) {
+    cudaGraphExecDestroy(graph_exec);
+    graph_exec = nullptr;
+  }
+  runs_of_plan = 0;
+  graph_replays = 0;
+  input_bufs.clear();
+  if (device >= 0) {
+    for (int t : ir.inputs)
+      input_bufs.push_back(storage_alloc(static_cast<size_t>(numel(p->shape[static_cast<size_t>(t)]) * SizeOf(ir.tensors[static_cast<size_t>(t)].dtype)), device));
+    if (!fork_event) check_cuda(cudaEventCreateWithFlags(&fork_event, cudaEventDisableTiming), "cudaEventCreate");
+    while (static_cast<int>(join_events.size()) < n_streams) {
+      cudaEvent_t e;
+      check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+      join_events.push_back(e);
+    }
+    const char* off = std::getenv("ONEFLOW_API_CUDA_GRAPH");
+    graph_disabled = off && off[0] == '0';
   }
   plan = std::move(p);
 }
@@ -895,6 +931,61 @@ void Graph::Impl::run_op(int index) {
   }
 }
 
+// Records the plan into a CUDA graph: stream 0 is the origin, the other streams fork from it and join it again, every
+// operator is launched on its plan stream after waiting for the events of its cross-stream dependencies. Returns false (and
+// leaves the scheduler path in charge) if anything in the plan cannot be captured.
+bool Graph::Impl::capture_plan() {
+  cudaStream_t s0 = streams[0];
+  std::string why;
+  auto give_up = [&](const std::string& reason) {
+    std::fprintf(stderr, "oneflow_api: the plan is not replayed as a CUDA graph (%s); it keeps running through the scheduler\n", reason.c_str());
+    return false;
+  };
+  cudaError_t rc = cudaStreamBeginCapture(s0, cudaStreamCaptureModeThreadLocal);
+  if (rc != cudaSuccess) {
+    cudaGetLastError();
+    return give_up(std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(rc));
+  }
+  bool ok = true;
+  try {
+    check_cuda(cudaEventRecord(fork_event, s0), "cudaEventRecord");
+    for (size_t s = 1; s < streams.size(); ++s) check_cuda(cudaStreamWaitEvent(streams[s], fork_event, 0), "cudaStreamWaitEvent");
+    for (size_t i = 0; i < plan->ops.size(); ++i) {
+      const PlannedOp& p = plan->ops[i];
+      cudaStream_t s = streams[static_cast<size_t>(p.stream)];
+      for (int d : p.deps)
+        if (plan->ops[static_cast<size_t>(d)].stream != p.stream) check_cuda(cudaStreamWaitEvent(s, events[static_cast<size_t>(d)], 0), "cudaStreamWaitEvent");
+      run_op_device(p, s);
+      check_cuda(cudaEventRecord(events[i], s), "cudaEventRecord");
+    }
+    for (size_t s = 1; s < streams.size(); ++s) {
+      check_cuda(cudaEventRecord(join_events[s], streams[s]), "cudaEventRecord");
+      check_cuda(cudaStreamWaitEvent(s0, join_events[s], 0), "cudaStreamWaitEvent");
+    }
+  } catch (const std::exception& e) {
+    ok = false;
+    why = e.what();
+  }
+  cudaGraph_t g = nullptr;
+  rc = cudaStreamEndCapture(s0, &g);
+  if (rc != cudaSuccess || !g) {
+    cudaGetLastError();
+    return give_up(why.empty() ? std::string("cudaStreamEndCapture: ") + cudaGetErrorString(rc) : why);
+  }
+  if (ok) {
+    rc = cudaGraphInstantiate(&graph_exec, g, 0);
+    if (rc != cudaSuccess) {
+      cudaGetLastError();
+      graph_exec = nullptr;
+      ok = false;
+      why = std::string("cudaGraphInstantiate: ") + cudaGetErrorString(rc);
+    }
+  }
+  cudaGraphDestroy(g);
+  if (!ok || !graph_exec) return give_up(why);
+  return true;
+}
+
 Graph Graph::Load(const std::string& dir, int device, int n_streams) {
   std::ifstream f(dir + "/graph.txt");
   if (!f) throw std::runtime_error("cannot open " + dir + "/graph.txt");
@@ -939,7 +1030,12 @@ Shape Graph::output_shape(int i) const {
 }
 int64_t Graph::in_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs[0])].shape.back(); }
 int64_t Graph::out_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.outputs[0])].shape.back(); }
-PlanStats Graph::stats() const { return impl_->plan ? impl_->plan->stats : PlanStats(); }
+PlanStats Graph::stats() const {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  PlanStats st = impl_->plan ? impl_->plan->stats : PlanStats();
+  st.graph_replays = impl_->graph_replays;
+  return st;
+}
 
 DType Graph::input_dtype(int i) const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs.at(static_cast<size_t>(i)))].dtype; }
 int Graph::device() const { return impl_->device; }
@@ -971,13 +1067,35 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     if (inputs[i].shape().elem_cnt() != numel(plan.shape[static_cast<size_t>(t)]))
       throw std::runtime_error("Forward: input " + std::to_string(i) + " has the wrong number of elements");
     if (inputs[i].device() != im.device) throw std::runtime_error("Forward: input " + std::to_string(i) + " lives on another device");
-    im.bound[static_cast<size_t>(plan.root[static_cast<size_t>(t)])] = inputs[i].data();
+    if (im.device >= 0) {
+      // the plan reads its inputs from buffers of its own (fixed addresses, as a recorded graph needs)
+      check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+      check_cuda(cudaMemcpyAsync(im.input_bufs[i].get(), inputs[i].data(), static_cast<size_t>(inputs[i].shape().elem_cnt() * SizeOf(def.dtype)),
+                                 cudaMemcpyDeviceToDevice, im.streams[0]), "cudaMemcpyAsync");
+      im.bound[static_cast<size_t>(plan.root[static_cast<size_t>(t)])] = im.input_bufs[i].get();
+    } else {
+      im.bound[static_cast<size_t>(plan.root[static_cast<size_t>(t)])] = inputs[i].data();
+    }
   }
   {
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
-  const int n_ops = static_cast<int>(plan.ops.size());
+  bool replayed = false;
+  if (im.device >= 0) {
+    check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");   // inputs are in place before any stream reads them
+    if (!im.graph_disabled && im.runs_of_plan >= 1) {
+      if (!im.graph_exec && !im.capture_plan()) im.graph_disabled = true;
+      if (im.graph_exec) {
+        check_cuda(cudaGraphLaunch(im.graph_exec, im.streams[0]), "cudaGraphLaunch");
+        check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");
+        replayed = true;
+        ++im.graph_replays;
+      }
+    }
+  }
+  ++im.runs_of_plan;
+  const int n_ops = replayed ? 0 : static_cast<int>(plan.ops.size());
   std::vector<TaskArg> args(static_cast<size_t>(n_ops));
   for (int i = 0; i < n_ops; ++i) {
     args[static_cast<size_t>(i)] = TaskArg{&im, i};

@@ -5,7 +5,10 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <stdexcept>
+#include <vector>
 
 #include "graph_runtime.h"
 
@@ -33,6 +36,52 @@ float from_bf16(uint16_t h) {
   return f;
 }
 
+namespace {
+// Free device blocks by (device, size). Lives until the process exits (never destroyed: tensors with static lifetime may
+// return blocks during shutdown). Holds at most kMaxCachedBytes; beyond that a returned block goes back to the driver.
+class DevicePool {
+ public:
+  static constexpr size_t kMaxCachedBytes = size_t(1) << 30;
+  static constexpr size_t kMaxCachedBlock = size_t(64) << 20;   // larger blocks (weights, big arenas) go straight back
+  void* take(int device, size_t bytes) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = free_.find({device, bytes});
+    if (it == free_.end() || it->second.empty()) return nullptr;
+    void* p = it->second.back();
+    it->second.pop_back();
+    cached_ -= bytes;
+    return p;
+  }
+  void give(int device, size_t bytes, void* p) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (bytes <= kMaxCachedBlock && cached_ + bytes <= kMaxCachedBytes) {
+        free_[{device, bytes}].push_back(p);
+        cached_ += bytes;
+        return;
+      }
+    }
+    cudaFree(p);
+  }
+  void release_all() {
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto& kv : free_)
+      for (void* p : kv.second) cudaFree(p);
+    free_.clear();
+    cached_ = 0;
+  }
+
+ private:
+  std::mutex mu_;
+  std::map<std::pair<int, size_t>, std::vector<void*>> free_;
+  size_t cached_ = 0;
+};
+DevicePool& device_pool() {
+  static DevicePool* pool = new DevicePool();
+  return *pool;
+}
+}  // namespace
+
 std::shared_ptr<void> storage_alloc(size_t bytes, int device) {
   if (bytes == 0) bytes = 16;
   if (device < 0) {
@@ -41,10 +90,29 @@ std::shared_ptr<void> storage_alloc(size_t bytes, int device) {
     return std::shared_ptr<void>(p, [](void* q) { std::free(q); });
   }
   check_cuda(cudaSetDevice(device), "cudaSetDevice");
-  void* p = nullptr;
-  check_cuda(cudaMalloc(&p, bytes), "cudaMalloc");
-  return std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+  // Device blocks are recycled: a serving loop allocates the same input and output sizes on every request, and a
+  // cudaMalloc / cudaFree pair costs more than a small graph takes to run. Every user of a block is synchronous with the
+  // host when the block is dropped (Forward returns after its streams are idle, the copies block), so a returned block can
+  // be handed out again at once.
+  DevicePool& pool = device_pool();
+  bytes = (bytes + 511) / 512 * 512;
+  void* p = pool.take(device, bytes);
+  if (!p) {
+    cudaError_t rc = cudaMalloc(&p, bytes);
+    if (rc != cudaSuccess) {
+      cudaGetLastError();
+      pool.release_all();
+      check_cuda(cudaMalloc(&p, bytes), "cudaMalloc");
+    }
+  }
+  return std::shared_ptr<void>(p, [device, bytes](void* q) { device_pool().give(device, bytes, q); });
 }
+
+}  // namespace detail
+
+void EmptyCache() { detail::device_pool().release_all(); }
+
+namespace detail {
 
 void copy_in(void* dst, const void* host, size_t bytes, int device) {
   if (device < 0) std::memcpy(dst, host, bytes);
@@ -173,7 +241,7 @@ int ofb_api_graph_forward(void* g, const float* x, long long rows, float* y) {
 
 int ofb_api_graph_stats(void* g, long long* s) {
   const auto st = static_cast<Graph*>(g)->stats();
-  s[0] = st.n_ops; s[1] = st.n_tensors; s[2] = st.activation_bytes; s[3] = st.arena_bytes; s[4] = st.n_dependencies; s[5] = st.n_streams_used;
+  s[0] = st.n_ops; s[1] = st.n_tensors; s[2] = st.activation_bytes; s[3] = st.arena_bytes; s[4] = st.n_dependencies; s[5] = st.n_streams_used; s[6] = st.graph_replays;
   return 0;
 }
 void ofb_api_graph_free(void* g) { delete static_cast<Graph*>(g); }

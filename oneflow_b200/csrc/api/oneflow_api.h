@@ -75,12 +75,17 @@ class Tensor {
   DType dtype_ = DType::kBFloat16;
 };
 
+// Device blocks of dropped tensors are kept for the next tensor of the same size (up to 1 GiB in blocks of at most
+// 64 MiB each); this returns them to the driver.
+void EmptyCache();
+
 struct PlanStats {
   int64_t n_ops = 0, n_tensors = 0;
   int64_t activation_bytes = 0;   // sum of all activation sizes
   int64_t arena_bytes = 0;        // peak bytes in use at once after sharing (activations + operator workspaces)
   int64_t n_dependencies = 0;
   int n_streams_used = 0;
+  int64_t graph_replays = 0;      // GPU: runs of the current plan that were one CUDA-graph launch
 };
 
 class Graph {
@@ -123,7 +128,7 @@ int ofb_api_graph_num_outputs(void* graph);
 long long ofb_api_graph_input_numel(void* graph, int i);
 int ofb_api_graph_input_is_int64(void* graph, int i);
 long long ofb_api_graph_output_numel(void* graph, int i);
-// stats_out[6]: ops, tensors, activation bytes, arena bytes, dependencies, streams used
+// stats_out[7]: ops, tensors, activation bytes, arena bytes, dependencies, streams used, CUDA-graph replays of the current plan
 int ofb_api_graph_stats(void* graph, long long* stats_out);
 void ofb_api_graph_free(void* graph);
 const char* ofb_api_last_error(void);

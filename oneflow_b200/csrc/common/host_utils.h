@@ -56,10 +56,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 inline EncodeTiledFn encode_tiled_fn() {
   // The encoder is a driver entry point and needs a current context on the CALLING thread. A thread that has only run this
   // library's code so far (autograd's device thread whose first work item is one of these kernels) has none bound yet:
-  // the first runtime call that needs one binds the primary context of the thread's device.
+  // the first runtime call that needs one binds the primary context of the thread's device. That call may come while a
+  // stream capture is open (a thread that records a graph after other threads ran the same kernels eagerly), where
+  // cudaFree counts as unsafe and would invalidate the capture: the thread's capture mode is relaxed around it.
   static thread_local bool context_bound = false;
   if (!context_bound) {
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    cudaThreadExchangeStreamCaptureMode(&mode);
     cudaFree(nullptr);
+    cudaThreadExchangeStreamCaptureMode(&mode);
     context_bound = true;
   }
   static EncodeTiledFn fn = nullptr;

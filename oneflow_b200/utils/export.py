@@ -580,9 +580,9 @@ class InferenceGraph:
         return outs
 
     def stats(self):
-        s = (ctypes.c_longlong * 6)()
+        s = (ctypes.c_longlong * 7)()
         self.lib.ofb_api_graph_stats(ctypes.c_void_p(self.h), s)
-        return dict(zip(("ops", "tensors", "activation_bytes", "arena_bytes", "dependencies", "streams_used"), list(s)))
+        return dict(zip(("ops", "tensors", "activation_bytes", "arena_bytes", "dependencies", "streams_used", "graph_replays"), list(s)))
 
     def close(self):
         if self.h:

@@ -188,6 +188,7 @@ def test_transformer_block_graph_on_the_gpu_runtime(tmp_path):
     assert np.abs(out - host).max() < 0.05 * np.abs(ref).max()
     for _ in range(3):
         assert np.array_equal(g.run(ids.numpy())[0], out)
+    assert g.stats()["graph_replays"] == 3     # every run after the first is one CUDA-graph launch
     g.close()
 
 
@@ -203,6 +204,15 @@ def test_branches_graph_on_the_gpu_runtime(tmp_path):
     assert np.abs(outs[0] - ref_out.detach().numpy().reshape(-1)).max() < 5e-2
     assert np.abs(outs[1] - ref_scores.detach().numpy().reshape(-1)).max() < 5e-2
     assert g.stats()["streams_used"] == 2
+    # replays of the recorded two-stream graph read the inputs of their own call, not those of the recording
+    for seed in (5, 6):
+        torch.manual_seed(seed)
+        x2, y2 = torch.randn(4, 64, 32).bfloat16().float(), torch.randn(4, 64, 32).bfloat16().float()
+        outs2 = g.run(x2.numpy(), y2.numpy())
+        r_out, r_scores = m(x2.clone(), y2.clone())
+        assert np.abs(outs2[0] - r_out.detach().numpy().reshape(-1)).max() < 5e-2
+        assert np.abs(outs2[1] - r_scores.detach().numpy().reshape(-1)).max() < 5e-2
+    assert g.stats()["graph_replays"] == 2
     g.close()
 
 
