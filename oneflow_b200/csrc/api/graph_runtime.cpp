@@ -4,6 +4,7 @@
 //
 // IR text (version 2), one record per line:
 //   tensor <id> <bf16|i64|f32> <input|param|act> <ndim> <d0> ... [file=<raw file>] [alias=<id>] [offset=<elements>]
+//                                                                  [name=<qualified parameter name>: trainable]
 //   op <type> in=<id,id,...> out=<id,...> [key=value ...]          (-1 marks an absent optional input)
 //   input <id> / output <id>                                      (in call order)
 // Tensor ids are dense and operators are listed in a valid execution order. A dimension of -1 is the row count that is
@@ -13,7 +14,7 @@
 // oneflow/core/graph/op_graph.cpp, task_graph.cpp, oneflow/core/job/plan_util.cpp), the memory-sharing pass
 // (oneflow/core/job/intra_job_mem_sharing_util.cpp) and the runtime that launches the plan
 // (oneflow/core/framework/nn_graph.cpp, oneflow/core/lazy/actor/).
-#include "graph_runtime.h"
+#include "graph_impl.h"
 
 #include <cuda_runtime.h>
 
@@ -54,57 +55,6 @@ using namespace detail;
 
 namespace {
 
-// ------------------------------------------------------------------------------------------------ IR
-struct TensorDef {
-  DType dtype = DType::kBFloat16;
-  std::vector<int64_t> shape;
-  int kind = 2;   // 0 input, 1 param, 2 activation
-  std::string file;
-  int alias_of = -1;
-  int64_t alias_off = 0;   // elements into the aliased tensor
-};
-struct OpDef {
-  std::string type;
-  std::vector<int> in, out;
-  std::map<std::string, std::string> attr;
-};
-struct IR {
-  std::vector<TensorDef> tensors;
-  std::vector<OpDef> ops;
-  std::vector<int> inputs, outputs;
-  bool dynamic_rows = false;
-};
-
-std::vector<std::string> split(const std::string& s, char sep) {
-  std::vector<std::string> out;
-  std::string cur;
-  for (char c : s) {
-    if (c == sep) { out.push_back(cur); cur.clear(); }
-    else cur.push_back(c);
-  }
-  out.push_back(cur);
-  return out;
-}
-std::vector<int64_t> int_list(const std::string& s) {
-  std::vector<int64_t> out;
-  if (s.empty()) return out;
-  for (auto& t : split(s, ',')) out.push_back(std::stoll(t));
-  return out;
-}
-int64_t attr_int(const OpDef& op, const char* k, int64_t dflt) {
-  auto it = op.attr.find(k);
-  return it == op.attr.end() ? dflt : std::stoll(it->second);
-}
-double attr_float(const OpDef& op, const char* k, double dflt) {
-  auto it = op.attr.find(k);
-  return it == op.attr.end() ? dflt : std::stod(it->second);
-}
-std::string attr_str(const OpDef& op, const char* k, const std::string& dflt) {
-  auto it = op.attr.find(k);
-  return it == op.attr.end() ? dflt : it->second;
-}
-int act_code(const std::string& a) { return a == "gelu" ? 1 : a == "gelu_tanh" ? 2 : a == "relu" ? 3 : 0; }
-
 IR parse_v2(std::istream& f) {
   IR ir;
   std::string line;
@@ -140,6 +90,7 @@ IR parse_v2(std::istream& f) {
         if (k == "file") t.file = v;
         else if (k == "alias") t.alias_of = std::stoi(v);
         else if (k == "offset") t.alias_off = std::stoll(v);
+        else if (k == "name") t.name = v;
         else throw bad("unknown tensor attribute " + k);
       }
       if (t.alias_of >= id) throw bad("an alias must point to an earlier tensor");
@@ -240,97 +191,8 @@ IR parse_v1(std::istream& f) {
   return ir;
 }
 
-// ------------------------------------------------------------------------------------------------ plan
-struct Range {
-  int64_t key, bytes;
-};
-bool overlaps(const Range& a, const Range& b) { return a.key < b.key + b.bytes && b.key < a.key + a.bytes; }
-
-struct PlannedOp {
-  const OpDef* def = nullptr;
-  std::vector<int> deps;        // indices of earlier operators this one must follow
-  int stream = 0;
-  int64_t workspace_bytes = 0;
-  void* workspace = nullptr;
-  std::vector<Range> reads, writes;
-};
-
-struct Plan {
-  int64_t rows = 0;
-  std::vector<std::vector<int64_t>> shape;     // resolved shapes per tensor
-  std::vector<int> root;                       // storage root per tensor
-  std::vector<int64_t> byte_off;               // byte offset of the tensor inside its root's storage
-  std::vector<void*> base;                     // per root: planned address (activations); null for inputs (bound per call)
-  std::vector<PlannedOp> ops;
-  PlanStats stats;
-};
-
-int64_t numel(const std::vector<int64_t>& s) {
-  int64_t n = 1;
-  for (auto d : s) n *= d;
-  return n;
-}
-
 }  // namespace
 
-struct Graph::Impl {
-  IR ir;
-  std::string dir;
-  int device = 0;
-  int n_streams = 2;
-  std::vector<std::shared_ptr<void>> params;   // per tensor id (params only)
-  std::vector<void*> allocators;              // one pool per stream of the plan
-  void* executor = nullptr;
-  std::vector<cudaStream_t> streams;
-  std::vector<cudaEvent_t> events;             // one per planned operator
-  std::unique_ptr<Plan> plan;
-  // GPU only: the plan replayed as one CUDA graph. The first Forward of a plan runs through the scheduler (it also performs
-  // every one-time initialisation the kernels do on first use); the second one records the same launches (same streams,
-  // cross-stream edges as events) into a graph on the calling thread, and from then on a Forward is: copy the inputs into
-  // the plan's own input buffers, one graph launch, copy the outputs out.
-  std::vector<std::shared_ptr<void>> input_bufs;   // per graph input, static addresses
-  cudaGraphExec_t graph_exec = nullptr;
-  cudaEvent_t fork_event = nullptr;
-  std::vector<cudaEvent_t> join_events;
-  int runs_of_plan = 0;
-  int64_t graph_replays = 0;
-  bool graph_disabled = false;
-  std::mutex run_mu;
-  // per call
-  std::vector<void*> bound;                    // per root: address of inputs for the running call
-  std::mutex err_mu;
-  std::string error;
-
-  ~Impl() {
-    if (executor) ofc_executor_destroy(executor);
-    if (graph_exec) cudaGraphExecDestroy(graph_exec);
-    if (fork_event) cudaEventDestroy(fork_event);
-    for (auto e : join_events) cudaEventDestroy(e);
-    for (auto e : events) cudaEventDestroy(e);
-    for (auto s : streams) cudaStreamDestroy(s);
-    for (void* al : allocators) ofc_allocator_destroy(al);
-  }
-
-  void fail(const std::string& msg) {
-    std::lock_guard<std::mutex> g(err_mu);
-    if (error.empty()) error = msg;
-  }
-  bool failed() {
-    std::lock_guard<std::mutex> g(err_mu);
-    return !error.empty();
-  }
-
-  void compile(int64_t rows);
-  void* addr(int tensor) const {
-    const int r = plan->root[static_cast<size_t>(tensor)];
-    char* b = static_cast<char*>(plan->base[static_cast<size_t>(r)] ? plan->base[static_cast<size_t>(r)] : bound[static_cast<size_t>(r)]);
-    return b + plan->byte_off[static_cast<size_t>(tensor)];
-  }
-  void run_op(int index);
-  bool capture_plan();
-  void run_op_device(const PlannedOp& p, cudaStream_t s);
-  void run_op_host(const PlannedOp& p);
-};
 
 namespace {
 
@@ -343,7 +205,7 @@ int64_t workspace_for(const OpDef& op, const Plan& plan) {
     const auto& q = plan.shape[static_cast<size_t>(op.in[0])];
     return q[0] * q[1] * q[2] * 4;
   }
-  return 0;
+  return train_workspace_for(op, plan);
 }
 
 void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
@@ -366,12 +228,15 @@ void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
     const auto& a = shp(op.in[0]);
     const auto& b = shp(op.in[1]);
     need(a.size() >= 2 && b.size() >= 2, "operands need at least two axes");
-    const bool tb = attr_int(op, "tb", 0) != 0;
-    const int64_t K = a.back(), N = tb ? b[b.size() - 2] : b.back(), Kb = tb ? b.back() : b[b.size() - 2];
+    const bool ta = attr_int(op, "ta", 0) != 0, tb = attr_int(op, "tb", 0) != 0;   // ta: the left operand is stored [.., K, M]
+    const int64_t K = ta ? a[a.size() - 2] : a.back(), M = ta ? a.back() : a[a.size() - 2];
+    const int64_t N = tb ? b[b.size() - 2] : b.back(), Kb = tb ? b.back() : b[b.size() - 2];
     need(K == Kb, "inner dimensions differ");
-    const int64_t batch_a = numel(a) / (a[a.size() - 2] * K), batch_b = numel(b) / (N * K);
+    const int64_t batch_a = numel(a) / (M * K), batch_b = numel(b) / (N * K);
     need(batch_b == 1 || batch_b == batch_a, "batch dimensions differ");
-    need(numel(shp(op.out[0])) == batch_a * a[a.size() - 2] * N, "output size mismatch");
+    need(numel(shp(op.out[0])) == batch_a * M * N, "output size mismatch");
+    need(dt(op.out[0]) == DType::kBFloat16 || dt(op.out[0]) == DType::kFloat, "the output must be bf16 or fp32");
+    need(attr_int(op, "accumulate", 0) == 0 || dt(op.out[0]) == DType::kFloat, "only fp32 outputs accumulate");
   } else if (t == "layer_norm") {
     need(op.in.size() == 3, "needs x, gamma, beta");
     need(numel(shp(op.in[1])) == shp(op.in[0]).back() && numel(shp(op.in[2])) == shp(op.in[0]).back(), "gamma / beta length");
@@ -404,8 +269,8 @@ void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
       out_max += (s[i] - 1) * os[i];
     }
     need(in_max < numel(shp(op.in[0])) && out_max < numel(shp(op.out[0])), "view reaches outside its tensor");
-    need(dt(op.in[0]) == dt(op.out[0]), "dtype mismatch");
-  } else {
+    need(dt(op.in[0]) == dt(op.out[0]) || attr_int(op, "accumulate", 0) != 0, "dtype mismatch");
+  } else if (!check_train_op(op, ir, plan)) {
     throw std::runtime_error("unknown operator type: " + t);
   }
 }
@@ -460,6 +325,8 @@ void Graph::Impl::compile(int64_t rows) {
     }
     for (int t : op.out) {
       const int r = p->root[static_cast<size_t>(t)];
+      const bool update = op.type == "adamw_update" || op.type == "sgd_update";
+      if (update && (root_kind(r) == 1 || root_kind(r) == 3)) continue;   // parameters and optimizer state: persistent, not planned
       if (root_kind(r) != 2) throw std::runtime_error("operator " + op.type + " writes a tensor that is not an activation");
       if (first[static_cast<size_t>(r)] < 0) first[static_cast<size_t>(r)] = i;
       last[static_cast<size_t>(r)] = i;
@@ -507,7 +374,7 @@ void Graph::Impl::compile(int64_t rows) {
   for (int i = 0; i < n_ops; ++i) {
     PlannedOp& po = p->ops[static_cast<size_t>(i)];
     for (int t : po.def->in)
-      if (t >= 0 && root_kind(p->root[static_cast<size_t>(t)]) != 1) po.reads.push_back(virtual_range(t));   // parameters never change
+      if (t >= 0 && (ir.training || root_kind(p->root[static_cast<size_t>(t)]) != 1)) po.reads.push_back(virtual_range(t));   // inference: parameters never change
     for (int t : po.def->out) po.writes.push_back(virtual_range(t));
   }
   {
@@ -582,7 +449,7 @@ void Graph::Impl::compile(int64_t rows) {
     po.reads.clear();
     po.writes.clear();
     for (int t : po.def->in)
-      if (t >= 0 && root_kind(p->root[static_cast<size_t>(t)]) != 1) po.reads.push_back(range_of(t));
+      if (t >= 0 && (ir.training || root_kind(p->root[static_cast<size_t>(t)]) != 1)) po.reads.push_back(range_of(t));
     for (int t : po.def->out) po.writes.push_back(range_of(t));
     if (po.workspace) po.writes.push_back(Range{reinterpret_cast<int64_t>(po.workspace), po.workspace_bytes});
     if (po.workspace) ofc_allocator_free(al, po.workspace);
@@ -635,13 +502,14 @@ void Graph::Impl::compile(int64_t rows) {
       join_events.push_back(e);
     }
     const char* off = std::getenv("ONEFLOW_API_CUDA_GRAPH");
-    graph_disabled = off && off[0] == '0';
+    graph_disabled = ir.training || (off && off[0] == '0');   // a training step takes step-dependent values at launch
   }
   plan = std::move(p);
 }
 
 // ------------------------------------------------------------------------------------------------ operators on the GPU
 void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
+  if (run_train_op_device(p, s)) return;
   const OpDef& op = *p.def;
   auto shp = [&](int t) -> const std::vector<int64_t>& { return plan->shape[static_cast<size_t>(t)]; };
   auto ok = [&](int rc) {
@@ -665,17 +533,22 @@ void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
   } else if (t == "matmul") {
     const auto& as = shp(op.in[0]);
     const auto& bs = shp(op.in[1]);
-    const bool tb = attr_int(op, "tb", 0) != 0;
-    const int64_t M = as[as.size() - 2], K = as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
+    const bool ta = attr_int(op, "ta", 0) != 0, tb = attr_int(op, "tb", 0) != 0;
+    const int64_t M = ta ? as.back() : as[as.size() - 2], K = ta ? as[as.size() - 2] : as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
     const int64_t batch = numel(as) / (M * K), batch_b = numel(bs) / (N * K);
+    const bool wide = ir.tensors[static_cast<size_t>(op.out[0])].dtype == DType::kFloat;
     for (int64_t b = 0; b < batch; ++b) {
       OfbGemmArgs a;
       std::memset(&a, 0, sizeof(a));
-      a.A = static_cast<char*>(addr(op.in[0])) + b * M * K * 2; a.lda = K;
+      a.A = static_cast<char*>(addr(op.in[0])) + b * M * K * 2;
+      a.lda = ta ? M : K;
+      a.a_mn_major = ta ? 1 : 0;
       a.B = static_cast<char*>(addr(op.in[1])) + (batch_b == 1 ? 0 : b) * N * K * 2;
       a.ldb = tb ? K : N;
       a.b_mn_major = tb ? 0 : 1;
-      a.C = static_cast<char*>(addr(op.out[0])) + b * M * N * 2; a.ldc = N;
+      a.C = static_cast<char*>(addr(op.out[0])) + b * M * N * (wide ? 4 : 2); a.ldc = N;
+      a.out_fp32 = wide ? 1 : 0;
+      a.accumulate = attr_int(op, "accumulate", 0) != 0 ? 1 : 0;
       a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
       a.alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
       ok(ofb_gemm_bf16(&a, s));
@@ -683,7 +556,7 @@ void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
   } else if (t == "layer_norm") {
     const auto& x = shp(op.in[0]);
     const int64_t cols = x.back(), rows = numel(x) / cols;
-    float* mean = static_cast<float*>(p.workspace);
+    float* mean = op.out.size() > 1 ? static_cast<float*>(addr(op.out[1])) : static_cast<float*>(p.workspace);   // kept for the backward pass
     ok(ofb_layer_norm_fwd(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), addr(op.out[0]), mean, mean + rows, static_cast<int>(rows),
                           static_cast<int>(cols), static_cast<float>(attr_float(op, "eps", 1e-5)), s));
   } else if (t == "embedding") {
@@ -705,7 +578,8 @@ void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
     const auto& q = shp(op.in[0]);
     const auto& k = shp(op.in[1]);
     const int64_t qs = attr_int(op, "q_stride", q[2] * q[3]), ks = attr_int(op, "kv_stride", k[2] * k[3]);
-    ok(ofb_fmha_fwd_ex(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), qs, ks, addr(op.out[0]), static_cast<float*>(p.workspace), nullptr,
+    float* lse = op.out.size() > 1 ? static_cast<float*>(addr(op.out[1])) : static_cast<float*>(p.workspace);   // kept for the backward pass
+    ok(ofb_fmha_fwd_ex(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), qs, ks, addr(op.out[0]), lse, nullptr,
                        static_cast<int>(q[0]), static_cast<int>(q[1]), static_cast<int>(k[1]), static_cast<int>(q[2]), static_cast<int>(k[2]),
                        static_cast<int>(q[3]), static_cast<int>(attr_int(op, "causal", 0)),
                        static_cast<float>(attr_float(op, "scale", 1.0 / std::sqrt(static_cast<double>(q[3])))), 0.f, 0ull, 0u, s));
@@ -753,6 +627,7 @@ float host_binary(float a, float b, int op) {
 }  // namespace
 
 void Graph::Impl::run_op_host(const PlannedOp& p) {
+  if (run_train_op_host(p)) return;
   const OpDef& op = *p.def;
   auto shp = [&](int t) -> const std::vector<int64_t>& { return plan->shape[static_cast<size_t>(t)]; };
   const std::string& t = op.type;
@@ -779,10 +654,11 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
   } else if (t == "matmul") {
     const auto& as = shp(op.in[0]);
     const auto& bs = shp(op.in[1]);
-    const bool tb = attr_int(op, "tb", 0) != 0;
-    const int64_t M = as[as.size() - 2], K = as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
+    const bool ta = attr_int(op, "ta", 0) != 0, tb = attr_int(op, "tb", 0) != 0;
+    const int64_t M = ta ? as.back() : as[as.size() - 2], K = ta ? as[as.size() - 2] : as.back(), N = tb ? bs[bs.size() - 2] : bs.back();
     const int64_t batch = numel(as) / (M * K), batch_b = numel(bs) / (N * K);
     const float alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
+    const bool wide = ir.tensors[static_cast<size_t>(op.out[0])].dtype == DType::kFloat, accumulate = attr_int(op, "accumulate", 0) != 0;
     const void *a = addr(op.in[0]), *b = addr(op.in[1]);
     void* y = addr(op.out[0]);
     for (int64_t bi = 0; bi < batch; ++bi) {
@@ -790,8 +666,14 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
       for (int64_t m = 0; m < M; ++m)
         for (int64_t n = 0; n < N; ++n) {
           float acc = 0.f;
-          for (int64_t k = 0; k < K; ++k) acc += ldb(a, ao + m * K + k) * (tb ? ldb(b, bo + n * K + k) : ldb(b, bo + k * N + n));
-          stb(y, yo + m * N + n, acc * alpha);
+          for (int64_t k = 0; k < K; ++k)
+            acc += (ta ? ldb(a, ao + k * M + m) : ldb(a, ao + m * K + k)) * (tb ? ldb(b, bo + n * K + k) : ldb(b, bo + k * N + n));
+          if (wide) {
+            float* yf = static_cast<float*>(y) + yo + m * N + n;
+            *yf = (accumulate ? *yf : 0.f) + acc * alpha;
+          } else {
+            stb(y, yo + m * N + n, acc * alpha);
+          }
         }
     }
   } else if (t == "layer_norm") {
@@ -809,6 +691,11 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
         var += d * d;
       }
       const float rstd = 1.f / std::sqrt(static_cast<float>(var / static_cast<double>(cols)) + eps);
+      if (op.out.size() > 1) {   // kept for the backward pass
+        float* st = static_cast<float*>(addr(op.out[1]));
+        st[r] = static_cast<float>(mean);
+        st[rows + r] = rstd;
+      }
       for (int64_t c = 0; c < cols; ++c)
         stb(y, r * cols + c, (ldb(xp, r * cols + c) - static_cast<float>(mean)) * rstd * ldb(g, c) + ldb(b, c));
     }
@@ -878,6 +765,7 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
             for (int64_t d = 0; d < D; ++d) acc[static_cast<size_t>(d)] += e * ldb(vp, (b * Sk + j) * ks + hk * D + d);
           }
           for (int64_t d = 0; d < D; ++d) stb(y, ((b * Sq + i) * H + h) * D + d, vis > 0 ? acc[static_cast<size_t>(d)] / sum : 0.f);
+          if (op.out.size() > 1) static_cast<float*>(addr(op.out[1]))[(b * H + h) * Sq + i] = vis > 0 ? mx + std::log(sum) : 0.f;   // kept for the backward pass
         }
       }
   } else if (t == "copy") {
@@ -986,18 +874,24 @@ bool Graph::Impl::capture_plan() {
   return true;
 }
 
-Graph Graph::Load(const std::string& dir, int device, int n_streams) {
+namespace {
+std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n_streams, const TrainOptions* train) {
   std::ifstream f(dir + "/graph.txt");
   if (!f) throw std::runtime_error("cannot open " + dir + "/graph.txt");
   std::string line;
   std::getline(f, line);
-  auto impl = std::make_shared<Impl>();
+  auto impl = std::make_shared<Graph::Impl>();
   impl->dir = dir;
   impl->device = device;
   impl->n_streams = std::max(1, std::min(n_streams, 16));
   if (line.rfind("oneflow_b200 graph v2", 0) == 0) impl->ir = parse_v2(f);
   else if (line.rfind("oneflow_b200 inference graph v1", 0) == 0) impl->ir = parse_v1(f);
   else throw std::runtime_error("not an exported graph: " + dir);
+  if (train) {
+    append_training_ops(impl->ir, *train);
+    impl->train = *train;
+    impl->graph_disabled = true;   // the update operator takes step-dependent values (learning rate, bias corrections) at launch
+  }
   // parameters
   impl->params.resize(impl->ir.tensors.size());
   for (size_t i = 0; i < impl->ir.tensors.size(); ++i) {
@@ -1011,12 +905,63 @@ Graph Graph::Load(const std::string& dir, int device, int n_streams) {
     if (static_cast<size_t>(pf.gcount()) != bytes) throw std::runtime_error("short read: " + t.file);
     impl->params[i] = storage_alloc(bytes, device);
     copy_in(impl->params[i].get(), host.data(), bytes, device);
+    // optimizer state that starts as a copy of this parameter (fp32 master weights)
+    for (size_t j = 0; j < impl->ir.tensors.size(); ++j) {
+      const TensorDef& st = impl->ir.tensors[j];
+      if (st.kind != 3 || st.init_from != static_cast<int>(i)) continue;
+      const size_t n = static_cast<size_t>(numel(t.shape));
+      std::vector<float> wide(n);
+      for (size_t k = 0; k < n; ++k) wide[k] = from_bf16(reinterpret_cast<const uint16_t*>(host.data())[k]);
+      impl->params[j] = storage_alloc(n * 4, device);
+      copy_in(impl->params[j].get(), wide.data(), n * 4, device);
+    }
+  }
+  for (size_t j = 0; j < impl->ir.tensors.size(); ++j) {
+    const TensorDef& st = impl->ir.tensors[j];
+    if (st.kind != 3 || st.init_from >= 0) continue;
+    const size_t bytes = static_cast<size_t>(numel(st.shape) * SizeOf(st.dtype));
+    std::vector<char> zeros(bytes, 0);
+    impl->params[j] = storage_alloc(bytes, device);
+    copy_in(impl->params[j].get(), zeros.data(), bytes, device);
   }
   if (!impl->ir.dynamic_rows) impl->compile(0);
+  return impl;
+}
+}  // namespace
+
+Graph Graph::Load(const std::string& dir, int device, int n_streams) {
   Graph g;
-  g.impl_ = impl;
+  g.impl_ = load_impl(dir, device, n_streams, nullptr);
   return g;
 }
+
+Graph Graph::LoadTraining(const std::string& dir, const TrainOptions& options, int device, int n_streams) {
+  Graph g;
+  g.impl_ = load_impl(dir, device, n_streams, &options);
+  return g;
+}
+
+int Graph::num_parameters() const { return static_cast<int>(impl_->ir.trainable.size()); }
+std::string Graph::parameter_name(int i) const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.trainable.at(static_cast<size_t>(i)))].name; }
+int64_t Graph::parameter_numel(int i) const { return numel(impl_->ir.tensors[static_cast<size_t>(impl_->ir.trainable.at(static_cast<size_t>(i)))].shape); }
+std::vector<float> Graph::parameter(int i) const {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  const int m = impl_->ir.masters.at(static_cast<size_t>(i));
+  const size_t n = static_cast<size_t>(numel(impl_->ir.tensors[static_cast<size_t>(m)].shape));
+  std::vector<float> out(n);
+  if (impl_->device >= 0) check_cuda(cudaSetDevice(impl_->device), "cudaSetDevice");
+  copy_out(out.data(), impl_->params[static_cast<size_t>(m)].get(), n * 4, impl_->device);
+  return out;
+}
+void Graph::set_learning_rate(float lr) {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  impl_->train.lr = lr;
+}
+int64_t Graph::steps() const {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  return impl_->train_steps;
+}
+std::string Graph::dump() const { return ir_to_text(impl_->ir); }
 
 int Graph::num_inputs() const { return static_cast<int>(impl_->ir.inputs.size()); }
 int Graph::num_outputs() const { return static_cast<int>(impl_->ir.outputs.size()); }
@@ -1028,8 +973,14 @@ Shape Graph::output_shape(int i) const {
   const int t = impl_->ir.outputs.at(static_cast<size_t>(i));
   return Shape(impl_->plan ? impl_->plan->shape[static_cast<size_t>(t)] : impl_->ir.tensors[static_cast<size_t>(t)].shape);
 }
-int64_t Graph::in_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs[0])].shape.back(); }
-int64_t Graph::out_features() const { return impl_->ir.tensors[static_cast<size_t>(impl_->ir.outputs[0])].shape.back(); }
+int64_t Graph::in_features() const {
+  const auto& s = impl_->ir.tensors[static_cast<size_t>(impl_->ir.inputs[0])].shape;
+  return s.empty() ? 1 : s.back();
+}
+int64_t Graph::out_features() const {
+  const auto& s = impl_->ir.tensors[static_cast<size_t>(impl_->ir.outputs[0])].shape;
+  return s.empty() ? 1 : s.back();   // a scalar output (a loss) counts as one feature
+}
 PlanStats Graph::stats() const {
   std::lock_guard<std::mutex> g(impl_->run_mu);
   PlanStats st = impl_->plan ? impl_->plan->stats : PlanStats();
@@ -1081,6 +1032,7 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
+  if (im.ir.training) ++im.train_steps;   // the update operator of this call sees the 1-based step number
   bool replayed = false;
   if (im.device >= 0) {
     check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");   // inputs are in place before any stream reads them

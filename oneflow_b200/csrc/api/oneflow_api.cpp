@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -245,4 +246,60 @@ int ofb_api_graph_stats(void* g, long long* s) {
   return 0;
 }
 void ofb_api_graph_free(void* g) { delete static_cast<Graph*>(g); }
+
+void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2, float eps,
+                                  float weight_decay, float momentum) {
+  try {
+    oneflow_api::TrainOptions o;
+    o.optimizer = optimizer ? optimizer : "adamw";
+    o.lr = lr; o.beta1 = beta1; o.beta2 = beta2; o.eps = eps; o.weight_decay = weight_decay; o.momentum = momentum;
+    return new Graph(Graph::LoadTraining(dir, o, device, n_streams));
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return nullptr;
+  }
+}
+int ofb_api_graph_num_parameters(void* g) { return static_cast<Graph*>(g)->num_parameters(); }
+const char* ofb_api_graph_parameter_name(void* g, int i) {
+  static thread_local std::string name;
+  try {
+    name = static_cast<Graph*>(g)->parameter_name(i);
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return nullptr;
+  }
+  return name.c_str();
+}
+long long ofb_api_graph_parameter_numel(void* g, int i) {
+  try {
+    return static_cast<Graph*>(g)->parameter_numel(i);
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_parameter_read(void* g, int i, float* out) {
+  try {
+    const auto v = static_cast<Graph*>(g)->parameter(i);
+    std::memcpy(out, v.data(), v.size() * sizeof(float));
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_set_lr(void* g, float lr) {
+  static_cast<Graph*>(g)->set_learning_rate(lr);
+  return 0;
+}
+long long ofb_api_graph_steps(void* g) { return static_cast<Graph*>(g)->steps(); }
+long long ofb_api_graph_dump(void* g, char* buf, long long cap) {
+  const std::string text = static_cast<Graph*>(g)->dump();
+  if (buf && cap > 0) {
+    const size_t n = std::min(static_cast<size_t>(cap - 1), text.size());
+    std::memcpy(buf, text.data(), n);
+    buf[n] = 0;
+  }
+  return static_cast<long long>(text.size());
+}
 }

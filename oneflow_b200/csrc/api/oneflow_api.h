@@ -88,9 +88,26 @@ struct PlanStats {
   int64_t graph_replays = 0;      // GPU: runs of the current plan that were one CUDA-graph launch
 };
 
+// Optimizer of a training graph (Graph::LoadTraining). "adamw" keeps fp32 master weights and both moments per parameter,
+// "sgd" fp32 master weights and, with momentum > 0, a momentum buffer; the bf16 parameters the forward operators read are
+// rewritten from the master weights by the same update operator.
+struct TrainOptions {
+  std::string optimizer = "adamw";
+  float lr = 1e-3f;
+  float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f;
+  float weight_decay = 0.f;
+  float momentum = 0.f;
+};
+
 class Graph {
  public:
   static Graph Load(const std::string& dir, int device = 0, int n_streams = 2);
+  // The same exported graph as a TRAINING step. Its first output must be a scalar loss (a cross_entropy or mse operator).
+  // Loading appends the backward operators of everything between the named (trainable) parameters and the loss, and one
+  // optimizer update operator; the whole step is then compiled like an inference graph (liveness, memory sharing across
+  // forward and backward, dependencies, streams). Each Forward call runs one step: forward, backward, update; it returns
+  // the graph's outputs (the loss first) as computed BEFORE the update.
+  static Graph LoadTraining(const std::string& dir, const TrainOptions& options, int device = 0, int n_streams = 2);
   Tensor Forward(const Tensor& input) const;
   std::vector<Tensor> Forward(const std::vector<Tensor>& inputs) const;
   int64_t in_features() const;    // last axis of the first input
@@ -104,6 +121,16 @@ class Graph {
   // Graphs exported without a batch size (the layer-list form) are compiled for a row count on first use, or here.
   void BindRows(int64_t rows);
   PlanStats stats() const;
+  // Training graphs: the trainable parameters in export order, their current values (fp32 master weights), the learning
+  // rate of the following steps, the number of steps taken, and the operator list after the backward pass was appended
+  // (the IR text format, for inspection).
+  int num_parameters() const;
+  std::string parameter_name(int i) const;
+  int64_t parameter_numel(int i) const;
+  std::vector<float> parameter(int i) const;
+  void set_learning_rate(float lr);
+  int64_t steps() const;
+  std::string dump() const;
   struct Impl;
 
  private:
@@ -130,6 +157,17 @@ int ofb_api_graph_input_is_int64(void* graph, int i);
 long long ofb_api_graph_output_numel(void* graph, int i);
 // stats_out[7]: ops, tensors, activation bytes, arena bytes, dependencies, streams used, CUDA-graph replays of the current plan
 int ofb_api_graph_stats(void* graph, long long* stats_out);
+// Training graphs (oneflow_api::Graph::LoadTraining); optimizer: "adamw" or "sgd".
+void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
+                                  float eps, float weight_decay, float momentum);
+int ofb_api_graph_num_parameters(void* graph);
+const char* ofb_api_graph_parameter_name(void* graph, int i);
+long long ofb_api_graph_parameter_numel(void* graph, int i);
+int ofb_api_graph_parameter_read(void* graph, int i, float* out);
+int ofb_api_graph_set_lr(void* graph, float lr);
+long long ofb_api_graph_steps(void* graph);
+// Writes the operator list (IR text) into buf (at most cap bytes, zero-terminated); returns the full length.
+long long ofb_api_graph_dump(void* graph, char* buf, long long cap);
 void ofb_api_graph_free(void* graph);
 const char* ofb_api_last_error(void);
 }

@@ -8,6 +8,10 @@ GELU and LayerNorm layers and writes ``graph.txt`` plus one raw bf16 file per pa
 Linear is folded into that layer's GEMM epilogue. ``InferenceGraph`` loads such a directory through the C ABI of
 ``libofb_api.so`` (what a C++ program does with ``oneflow_api::Graph::Load``).
 
+A module whose forward returns a scalar loss (``F.cross_entropy`` / ``F.mse_loss`` or the loss modules) exports the same way
+(use ``fuse=False``); ``TrainingGraph`` loads it as a training step: the C++ side appends the backward and optimizer operators
+and compiles forward, backward and update into one plan.
+
 Reference: oneflow/api/cpp (Graph::Load of a saved nn.Graph), python/oneflow/framework/check_point_v2.py save(..., save_as_external_data)."""
 from __future__ import annotations
 
@@ -114,6 +118,12 @@ class _GraphEmitter(torch.fx.Interpreter):
         self.keep = []             # tensors kept alive so that storage pointers stay unique
         self.alias_cache = {}
         self.copy_cache = {}
+        # parameters that own their whole storage and take gradients: named in the IR, which makes them trainable there
+        self.param_names = {}
+        for name, prm in gm.named_parameters():
+            if prm.requires_grad and prm.dtype.is_floating_point and prm.storage_offset() == 0 and \
+                    prm.untyped_storage().nbytes() == prm.numel() * prm.element_size():
+                self.param_names.setdefault(prm.untyped_storage().data_ptr(), name)
 
     # ---- IR helpers
     @staticmethod
@@ -154,7 +164,8 @@ class _GraphEmitter(torch.fx.Interpreter):
             _write_bf16(os.path.join(self.dir, name), whole)
         else:
             whole.to(torch.int64).cpu().numpy().tofile(os.path.join(self.dir, name))
-        rid = self._new_tensor(self._dtype(real), "param", [n_storage], f"file={name}")
+        pname = self.param_names.get(real.untyped_storage().data_ptr())
+        rid = self._new_tensor(self._dtype(real), "param", [n_storage], f"file={name}" + (f" name={pname}" if pname else ""))
         self.keep.append(real)
         self.roots[real.untyped_storage().data_ptr()] = rid
         return rid
@@ -328,6 +339,33 @@ class _GraphEmitter(torch.fx.Interpreter):
                    kv_stride=ks)
         return y_ir.transpose(1, 2)
 
+    def _scalar_result(self, y):
+        """A fresh fp32 scalar activation (loss values): (IR id, the tensor that stands for the node)."""
+        real = y.detach().to(torch.float32).reshape(1).clone()
+        rid = self._new_tensor("f32", "act", [1])
+        self.keep.append(real)
+        self.roots[real.untyped_storage().data_ptr()] = rid
+        return rid, real.reshape(())
+
+    def _cross_entropy(self, logits, target, y, weight=None, ignore_index=-100, reduction="mean", label_smoothing=0.0):
+        if logits.dim() != 2 or target.dim() != 1 or target.dtype != torch.int64:
+            raise ValueError("cross_entropy is exported for [rows, classes] logits and int64 class targets [rows]")
+        if weight is not None or reduction != "mean" or label_smoothing:
+            raise ValueError("cross_entropy is exported with mean reduction, no class weights and no label smoothing")
+        ins = [self._operand(logits), self._operand(target)]
+        out, y = self._scalar_result(y)
+        # the mean runs over all rows; a row whose target is ignore_index adds nothing to the loss or the gradient
+        self._emit("cross_entropy", ins, out, ignore_index=int(ignore_index))
+        return y
+
+    def _mse(self, a, b, y, reduction="mean"):
+        if tuple(a.shape) != tuple(b.shape) or reduction != "mean":
+            raise ValueError("mse_loss is exported for equal shapes and mean reduction")
+        ins = [self._operand(a), self._operand(b)]
+        out, y = self._scalar_result(y)
+        self._emit("mse", ins, out)
+        return y
+
     def _cat(self, tensors, dim, y):
         y = y.contiguous()
         if y.untyped_storage().data_ptr() in self.roots:
@@ -394,6 +432,10 @@ class _GraphEmitter(torch.fx.Interpreter):
                     return self._unary(a[0], y, fn, inplace=inplace)
             if isinstance(m, torch.nn.Softmax):
                 return self._softmax(a[0], m.dim, y)
+            if isinstance(m, torch.nn.CrossEntropyLoss):
+                return self._cross_entropy(a[0], a[1], y, m.weight, m.ignore_index, m.reduction, m.label_smoothing)
+            if isinstance(m, torch.nn.MSELoss):
+                return self._mse(a[0], a[1], y, m.reduction)
             raise ValueError(f"cannot export module of type {type(m).__name__}")
         n = name
         if n in _INPLACE:
@@ -424,6 +466,11 @@ class _GraphEmitter(torch.fx.Interpreter):
             if (a[4] if len(a) > 4 else kw.get("dropout_p", 0.0)):
                 raise ValueError("attention dropout has no place in an inference graph")
             return self._sdpa(a[0], a[1], a[2], y, a[5] if len(a) > 5 else kw.get("is_causal", False), kw.get("scale"))
+        if n == "cross_entropy":
+            return self._cross_entropy(a[0], a[1], y, a[2] if len(a) > 2 else kw.get("weight"), kw.get("ignore_index", -100),
+                                       kw.get("reduction", "mean"), kw.get("label_smoothing", 0.0))
+        if n == "mse_loss":
+            return self._mse(a[0], a[1], y, kw.get("reduction", "mean"))
         if n in ("cat", "concat"):
             return self._cat(list(a[0]), int(a[1] if len(a) > 1 else kw.get("dim", 0)) % y.dim(), y)
         if n in ("reshape", "contiguous", "clone", "flatten", "to", "float", "type_as", "dropout", "expand_as"):
@@ -538,7 +585,9 @@ class InferenceGraph:
         lib.ofb_api_last_error.restype = ctypes.c_char_p
         for fn in ("ofb_api_graph_in_features", "ofb_api_graph_out_features", "ofb_api_graph_input_numel", "ofb_api_graph_output_numel"):
             getattr(lib, fn).restype = ctypes.c_longlong
-        self.h = lib.ofb_api_graph_load_ex(directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams))
+        lib.ofb_api_graph_load_training.restype = ctypes.c_void_p
+        load = getattr(self, "_load", None)
+        self.h = load(lib) if load else lib.ofb_api_graph_load_ex(directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams))
         if not self.h:
             raise RuntimeError(lib.ofb_api_last_error().decode())
         h = ctypes.c_void_p(self.h)
@@ -588,3 +637,52 @@ class InferenceGraph:
         if self.h:
             self.lib.ofb_api_graph_free(ctypes.c_void_p(self.h))
             self.h = None
+
+
+class TrainingGraph(InferenceGraph):
+    """An exported graph whose first output is a scalar loss, loaded as a training step (``oneflow_api::Graph::LoadTraining``):
+    reverse-mode differentiation of the operator IR, gradient buffers planned together with the activations, one fused
+    optimizer operator ("adamw" or "sgd") over fp32 master weights. ``step(*inputs)`` runs forward, backward and update and
+    returns the loss (computed before the update); ``parameters()`` reads the fp32 master weights back by parameter name."""
+
+    def __init__(self, directory, device=0, n_streams=2, optimizer="adamw", lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                 momentum=0.0):
+        self._load = lambda lib: lib.ofb_api_graph_load_training(
+            directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams), optimizer.encode(), ctypes.c_float(lr),
+            ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_float(momentum))
+        super().__init__(directory, device, n_streams)
+        lib = self.lib
+        lib.ofb_api_graph_parameter_name.restype = ctypes.c_char_p
+        lib.ofb_api_graph_parameter_numel.restype = ctypes.c_longlong
+        lib.ofb_api_graph_steps.restype = ctypes.c_longlong
+        lib.ofb_api_graph_dump.restype = ctypes.c_longlong
+
+    def step(self, *inputs):
+        outs = self.run(*inputs)
+        return float(outs[0][0])
+
+    @property
+    def steps(self):
+        return int(self.lib.ofb_api_graph_steps(ctypes.c_void_p(self.h)))
+
+    def set_lr(self, lr):
+        self.lib.ofb_api_graph_set_lr(ctypes.c_void_p(self.h), ctypes.c_float(lr))
+
+    def parameters(self):
+        h = ctypes.c_void_p(self.h)
+        out = {}
+        for i in range(self.lib.ofb_api_graph_num_parameters(h)):
+            name = self.lib.ofb_api_graph_parameter_name(h, ctypes.c_int(i)).decode()
+            buf = np.empty(self.lib.ofb_api_graph_parameter_numel(h, ctypes.c_int(i)), dtype=np.float32)
+            if self.lib.ofb_api_graph_parameter_read(h, ctypes.c_int(i), buf.ctypes.data_as(ctypes.c_void_p)) != 0:
+                raise RuntimeError(self.lib.ofb_api_last_error().decode())
+            out[name] = buf
+        return out
+
+    def dump(self):
+        """The operator list after the backward pass was appended, in the IR text format."""
+        h = ctypes.c_void_p(self.h)
+        n = self.lib.ofb_api_graph_dump(h, None, ctypes.c_longlong(0))
+        buf = ctypes.create_string_buffer(n + 1)
+        self.lib.ofb_api_graph_dump(h, buf, ctypes.c_longlong(n + 1))
+        return buf.value.decode()

@@ -1,0 +1,200 @@
+"""Training through the native graph compiler: an exported forward graph that ends in a loss is differentiated in C++
+(csrc/api/graph_autodiff.cpp), compiled into one plan with its backward and optimizer operators, and run by the same
+executor as inference graphs. The host runtime is compared with PyTorch autograd; the GPU runtime with the host runtime."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from oneflow_b200.utils import export as E
+
+from test_inference_api import Block, _bf16_weights
+
+
+class Mlp(nn.Module):
+    def __init__(self, d_in=32, d_h=64, classes=16):
+        super().__init__()
+        self.fc1, self.ln, self.fc2 = nn.Linear(d_in, d_h), nn.LayerNorm(d_h), nn.Linear(d_h, classes)
+
+    def forward(self, x, y):
+        return F.cross_entropy(self.fc2(self.ln(F.gelu(self.fc1(x)))), y)
+
+
+class TiedLM(nn.Module):
+    """Embedding + position table + one pre-LN transformer layer; the output projection shares the embedding table."""
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.block = Block(**kw)
+        self.block.head.weight = self.block.emb.weight
+
+    def forward(self, ids, targets):
+        logits = self.block(ids)
+        return F.cross_entropy(logits.view(-1, logits.shape[-1]), targets.view(-1))
+
+
+def _grads_by_unit_sgd(module, inputs, directory, device=-1):
+    """One SGD step with lr 1 and no momentum: parameter before - parameter after = the gradient the graph computed."""
+    d = E.export_graph(module, inputs, directory, fuse=False)
+    g = E.TrainingGraph(d, device=device, optimizer="sgd", lr=1.0)
+    before = g.parameters()
+    loss = g.step(*[t.numpy() for t in inputs])
+    after = g.parameters()
+    g.close()
+    return loss, {k: before[k] - after[k] for k in before}
+
+
+def _check_grads(module, grads, rel=3e-2):
+    for name, p in module.named_parameters():
+        ref = p.grad.detach().numpy().reshape(-1)
+        scale = np.abs(ref).max() + 1e-6
+        assert np.abs(grads[name] - ref).max() <= rel * scale, name
+
+
+def test_mlp_gradients_and_sgd_trajectory_match_autograd(tmp_path):
+    torch.manual_seed(0)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    loss, grads = _grads_by_unit_sgd(m, (x, y), str(tmp_path / "unit"))
+    ref = m(x, y)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    _check_grads(m, grads)
+    # several steps against torch.optim.SGD with momentum
+    m.zero_grad()
+    d = E.export_graph(m, (x, y), str(tmp_path / "run"), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.1, momentum=0.9)
+    opt = torch.optim.SGD(m.parameters(), lr=0.1, momentum=0.9)
+    for _ in range(8):
+        ref = m(x, y)
+        opt.zero_grad()
+        ref.backward()
+        opt.step()
+        assert abs(g.step(x.numpy(), y.numpy()) - float(ref.detach())) < 3e-2 * max(abs(float(ref.detach())), 0.1)
+    assert g.steps == 8
+    ps = g.parameters()
+    for name, p in m.named_parameters():
+        assert np.abs(ps[name] - p.detach().numpy().reshape(-1)).max() < 2e-2, name
+    g.close()
+
+
+def test_tied_transformer_block_gradients_match_autograd(tmp_path):
+    """Attention backward through the packed projection, two embedding tables (one broadcast over the batch), residual
+    streams with several consumers, and a table that is both looked up and used as the output projection."""
+    torch.manual_seed(1)
+    m = _bf16_weights(TiedLM(d=64, heads=1, vocab=96, seq=16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    loss, grads = _grads_by_unit_sgd(m, (ids, tgt), str(tmp_path))
+    ref = m(ids, tgt)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    assert "block.emb.weight" in grads and "block.head.weight" not in grads      # one parameter, two uses
+    _check_grads(m, grads, rel=5e-2)
+
+
+def test_adamw_loss_falls_like_torch(tmp_path):
+    torch.manual_seed(2)
+    m = _bf16_weights(TiedLM(d=64, heads=1, vocab=96, seq=16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.01)
+    text = g.dump()
+    assert text.count("op attention_bwd") == 1 and text.count("op adamw_update") == 1 and text.count("op embedding_bwd") == 2
+    assert "dq_stride=192" in text            # the three gradients go straight into the packed projection's gradient
+    st = g.stats()
+    assert st["arena_bytes"] < st["activation_bytes"]          # forward activations, gradients and temporaries share memory
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2, weight_decay=0.01)
+    ours, theirs = [], []
+    for _ in range(6):
+        ref = m(ids, tgt)
+        opt.zero_grad()
+        ref.backward()
+        opt.step()
+        theirs.append(float(ref.detach()))
+        ours.append(g.step(ids.numpy(), tgt.numpy()))
+    assert ours[-1] < 0.05 * ours[0]
+    for a, b in zip(ours[:4], theirs[:4]):
+        assert abs(a - b) < 0.05 * max(abs(b), 1.0)
+    g.set_lr(0.0)
+    before = g.parameters()
+    g.step(ids.numpy(), tgt.numpy())
+    after = g.parameters()
+    assert all(np.array_equal(before[k], after[k] * 1.0) or np.abs(before[k] - after[k]).max() < 1e-12 for k in before)
+    g.close()
+
+
+def test_mse_and_parameter_free_paths(tmp_path):
+    class Reg(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = nn.Linear(16, 32), nn.Linear(32, 8)
+
+        def forward(self, x, t):
+            return F.mse_loss(self.b(torch.tanh(self.a(x))) * 0.5, t)
+
+    torch.manual_seed(3)
+    m = _bf16_weights(Reg())
+    x, t = torch.randn(8, 16).bfloat16().float(), torch.randn(8, 8).bfloat16().float()
+    loss, grads = _grads_by_unit_sgd(m, (x, t), str(tmp_path))
+    ref = m(x, t)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    _check_grads(m, grads)
+
+
+def test_what_cannot_be_differentiated_is_refused_with_the_operator_named(tmp_path):
+    class InPlace(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = nn.Linear(16, 16)
+
+        def forward(self, x, y):
+            h = self.fc(x)
+            h.relu_()
+            return F.cross_entropy(h, y)
+
+    m = _bf16_weights(InPlace())
+    x, y = torch.randn(4, 16), torch.randint(0, 16, (4,))
+    d = E.export_graph(m, (x, y), str(tmp_path / "inplace"), fuse=False)
+    with pytest.raises(RuntimeError, match="in place"):
+        E.TrainingGraph(d, device=-1)
+    m2 = _bf16_weights(Mlp())
+    x2, y2 = torch.randn(24, 32), torch.randint(0, 16, (24,))
+    d2 = E.export_graph(m2, (x2, y2), str(tmp_path / "fused"), fuse=True)       # gelu folded into fc1's epilogue
+    with pytest.raises(RuntimeError, match="fuse=False"):
+        E.TrainingGraph(d2, device=-1)
+    d3 = E.export_graph(_bf16_weights(nn.Sequential(nn.Linear(8, 8))), (torch.randn(2, 8),), str(tmp_path / "noloss"))
+    with pytest.raises(RuntimeError, match="scalar fp32 loss"):
+        E.TrainingGraph(d3, device=-1)
+    # the same directories still load as inference graphs (the loss is just an output)
+    out = E.InferenceGraph(d2, device=-1).run(x2.numpy(), y2.numpy())[0]
+    assert abs(out[0] - float(m2(x2.bfloat16().float(), y2))) < 5e-2
+
+
+@pytest.mark.gpu
+def test_training_step_on_the_gpu_runtime_matches_the_host_runtime(tmp_path):
+    """The same plan on the sm_100a kernels: tcgen05 GEMMs for data and weight gradients (fp32 accumulation into the
+    gradient buffers), fused attention backward writing into the packed projection gradient, LayerNorm backward, fused
+    cross entropy, the multi-tensor AdamW; compared step by step with the host implementation of the same operators."""
+    torch.manual_seed(4)
+    m = _bf16_weights(TiedLM(d=128, heads=2, vocab=256, seq=128))
+    ids, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path), fuse=False)
+    loss_h, grads_h = _grads_by_unit_sgd(m, (ids, tgt), str(tmp_path / "h"), device=-1)
+    loss_d, grads_d = _grads_by_unit_sgd(m, (ids, tgt), str(tmp_path / "d"), device=0)
+    assert abs(loss_h - loss_d) < 1e-2 * abs(loss_h)
+    for k in grads_h:
+        assert np.abs(grads_h[k] - grads_d[k]).max() <= 5e-2 * (np.abs(grads_h[k]).max() + 1e-6), k
+    host = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=3e-3)
+    dev = E.TrainingGraph(d, device=0, optimizer="adamw", lr=3e-3)
+    assert dev.stats()["streams_used"] == 2
+    lh = [host.step(ids.numpy(), tgt.numpy()) for _ in range(5)]
+    ld = [dev.step(ids.numpy(), tgt.numpy()) for _ in range(5)]
+    assert ld[-1] < ld[0]
+    for a, b in zip(lh, ld):
+        assert abs(a - b) < 5e-2 * max(abs(a), 1.0)
+    host.close()
+    dev.close()
