@@ -22,7 +22,10 @@ namespace oneflow_api {
 
 namespace {
 
-enum class Mode { kNone, kDirect, kDirectStrided, kAccumulate };
+// kResidualLayerNorm: the pre-LN residual pattern, x read by a LayerNorm and (later) by a same-shape addition. The addition's
+// part of dx is its own output gradient; the LayerNorm backward kernel adds it while it writes dx, so the storage needs
+// neither a zero fill nor an accumulate pass.
+enum class Mode { kNone, kDirect, kDirectStrided, kAccumulate, kResidualLayerNorm };
 
 struct Use {
   int op, slot, tensor;
@@ -64,6 +67,7 @@ struct Builder {
   std::vector<int> grad_root;   // forward root -> gradient root, or -1
   std::vector<Mode> mode;
   std::vector<char> requires_grad, reaches_loss;
+  std::map<int, int> pending_add;   // kResidualLayerNorm roots: the addition's output gradient, waiting for the LayerNorm backward
 
   Builder(IR& i, const TrainOptions& o) : ir(i), opt(o) {}
 
@@ -129,7 +133,7 @@ struct Builder {
     const bool param = ir.tensors[static_cast<size_t>(r)].kind == 1;
     const int g = new_root(param ? DType::kFloat : DType::kBFloat16, count(r));
     grad_root[static_cast<size_t>(r)] = g;
-    if (mode[static_cast<size_t>(r)] != Mode::kDirect) emit("fill", {}, {g}, {{"value", "0"}});
+    if (mode[static_cast<size_t>(r)] != Mode::kDirect && mode[static_cast<size_t>(r)] != Mode::kResidualLayerNorm) emit("fill", {}, {g}, {{"value", "0"}});
     return g;
   }
   bool has_grad(int t) const { return grad_root[static_cast<size_t>(root(t))] >= 0; }
@@ -144,7 +148,7 @@ struct Builder {
     const int r = root(t);
     Target tg;
     tg.tensor = t;
-    if (mode[static_cast<size_t>(r)] == Mode::kDirect) {
+    if (mode[static_cast<size_t>(r)] == Mode::kDirect || mode[static_cast<size_t>(r)] == Mode::kResidualLayerNorm) {
       tg.out = grad_of(t);
     } else if (ir.tensors[static_cast<size_t>(r)].kind == 1 && op_adds_fp32) {
       tg.out = grad_of(t);
@@ -168,7 +172,13 @@ struct Builder {
   // the gradient of t is scale * src (src contiguous, same element count)
   void pass_grad(int t, int src, double scale = 1.0) {
     const int r = root(t);
-    if (mode[static_cast<size_t>(r)] == Mode::kDirect) {
+    const bool same_type = ir.tensors[static_cast<size_t>(root(src))].dtype == (ir.tensors[static_cast<size_t>(r)].kind == 1 ? DType::kFloat : DType::kBFloat16);
+    if (mode[static_cast<size_t>(r)] == Mode::kResidualLayerNorm) {
+      pending_add[r] = src;
+    } else if (mode[static_cast<size_t>(r)] == Mode::kDirect && scale == 1.0 && same_type && whole(t) && whole(src) && grad_root[static_cast<size_t>(r)] < 0) {
+      // the gradient IS the source: both are complete and read-only from here on, so the storage is shared instead of copied
+      grad_root[static_cast<size_t>(r)] = root(src);
+    } else if (mode[static_cast<size_t>(r)] == Mode::kDirect) {
       emit("cast", {src}, {grad_of(t)}, {{"scale", fstr(scale)}});
     } else if (scale == 1.0) {
       accumulate_into(t, src);
@@ -275,6 +285,19 @@ void Builder::run() {
     if (u.size() == 1 && first.type != "copy" && whole(u[0].tensor)) {
       mode[r] = Mode::kDirect;
       continue;
+    }
+    if (u.size() == 2) {
+      const Use* ln = nullptr;
+      const Use* add = nullptr;
+      for (const Use& x : u) {
+        const OpDef& o = ir.ops[static_cast<size_t>(x.op)];
+        if (o.type == "layer_norm" && x.slot == 0) ln = &x;
+        if (o.type == "binary" && attr_int(o, "fn", 0) == 0 && attr_int(o, "bmode", 0) == 0) add = &x;
+      }
+      if (ln && add && add->op > ln->op && whole(ln->tensor) && whole(add->tensor)) {
+        mode[r] = Mode::kResidualLayerNorm;
+        continue;
+      }
     }
     bool one_attention = first.type == "attention";
     for (const Use& x : u) one_attention = one_attention && x.op == u[0].op;
@@ -444,7 +467,12 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
       outs.push_back(dg);
       outs.push_back(db);
     }
-    emit("layer_norm_bwd", {dy, x, gamma, stats}, outs, {{"accumulate", native ? "1" : "0"}});
+    std::vector<int> ins = {dy, x, gamma, stats};
+    if (mode[static_cast<size_t>(root(x))] == Mode::kResidualLayerNorm) {
+      if (!pending_add.count(root(x))) refuse(op, "the residual addition that shares its input produced no gradient");
+      ins.push_back(pending_add.at(root(x)));   // added to dx by the same kernel
+    }
+    emit("layer_norm_bwd", ins, outs, {{"accumulate", native ? "1" : "0"}});
     if (wants(x)) finish(tx);
   } else if (t == "embedding") {
     const int ids = in(0), table = in(1);

@@ -143,6 +143,10 @@ struct Graph::Impl {
   // training graphs: hyper-parameters read by the update operator at launch time, steps taken so far
   TrainOptions train;
   int64_t train_steps = 0;
+  // GPU: {learning rate, 1 - beta1^t, 1 - beta2^t} of the running step, refreshed before every step through pinned host
+  // memory; the update operator reads them on the device, so a recorded step stays valid from one step to the next
+  float* step_scalars = nullptr;
+  float* step_scalars_host = nullptr;
   std::mutex run_mu;
   // per call
   std::vector<void*> bound;                    // per root: address of inputs for the running call
@@ -151,6 +155,8 @@ struct Graph::Impl {
 
   ~Impl() {
     if (executor) ofc_executor_destroy(executor);
+    if (step_scalars) cudaFree(step_scalars);
+    if (step_scalars_host) cudaFreeHost(step_scalars_host);
     if (graph_exec) cudaGraphExecDestroy(graph_exec);
     if (fork_event) cudaEventDestroy(fork_event);
     for (auto e : join_events) cudaEventDestroy(e);

@@ -502,7 +502,7 @@ void Graph::Impl::compile(int64_t rows) {
       join_events.push_back(e);
     }
     const char* off = std::getenv("ONEFLOW_API_CUDA_GRAPH");
-    graph_disabled = ir.training || (off && off[0] == '0');   // a training step takes step-dependent values at launch
+    graph_disabled = off && off[0] == '0';
   }
   plan = std::move(p);
 }
@@ -890,7 +890,11 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
   if (train) {
     append_training_ops(impl->ir, *train);
     impl->train = *train;
-    impl->graph_disabled = true;   // the update operator takes step-dependent values (learning rate, bias corrections) at launch
+    if (device >= 0) {
+      check_cuda(cudaSetDevice(device), "cudaSetDevice");
+      check_cuda(cudaMalloc(&impl->step_scalars, 4 * sizeof(float)), "cudaMalloc");
+      check_cuda(cudaMallocHost(&impl->step_scalars_host, 4 * sizeof(float)), "cudaMallocHost");
+    }
   }
   // parameters
   impl->params.resize(impl->ir.tensors.size());
@@ -1032,7 +1036,17 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
-  if (im.ir.training) ++im.train_steps;   // the update operator of this call sees the 1-based step number
+  if (im.ir.training) {
+    ++im.train_steps;   // the update operator of this call sees the 1-based step number
+    if (im.device >= 0) {
+      im.step_scalars_host[0] = im.train.lr;
+      im.step_scalars_host[1] = 1.f - std::pow(im.train.beta1, static_cast<float>(im.train_steps));
+      im.step_scalars_host[2] = 1.f - std::pow(im.train.beta2, static_cast<float>(im.train_steps));
+      im.step_scalars_host[3] = 0.f;
+      // on stream 0, which is synchronised below before anything of the step starts
+      check_cuda(cudaMemcpyAsync(im.step_scalars, im.step_scalars_host, 4 * sizeof(float), cudaMemcpyHostToDevice, im.streams[0]), "cudaMemcpyAsync");
+    }
+  }
   bool replayed = false;
   if (im.device >= 0) {
     check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");   // inputs are in place before any stream reads them

@@ -7,7 +7,8 @@
 //   copy accumulate=1   out[view] += in[view] (the backward of every view copy; bf16 or fp32 on either side)
 //   column_sum      out[c] += sum over rows of in[r, c]              (fp32 out; bias gradients)
 //   unary_bwd       dx = dy * fn'(x)
-//   layer_norm_bwd  (dy, x, gamma, stats) -> dx [, dgamma, dbeta]     (fp32 parameter gradients, added when accumulate=1)
+//   layer_norm_bwd  (dy, x, gamma, stats [, add_to_dx]) -> dx [, dgamma, dbeta]   (fp32 parameter gradients, added when
+//                   accumulate=1; add_to_dx is the residual branch's gradient, added while dx is written)
 //   softmax_bwd     (y, dy) -> dx = scale * y * (dy - sum(dy * y))
 //   attention_bwd   (q, k, v, o, do, lse) -> dq, dk, dv, each written through a token stride
 //   embedding_bwd   (ids, dy) -> table gradient (fp32, scatter-add)
@@ -51,6 +52,9 @@ int ofb_xent_grad(const void* logits, const long long* labels, const float* merg
 int ofb_multi_tensor_adamw(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms, float* const* vs,
                            const long long* sizes, int grad_is_bf16, float lr, float beta1, float beta2, float eps, float weight_decay, float l2,
                            float scale, float bc1, float bc2, const float* lr_ptr, const float* scale_ptr, const long long* skip_if, void* stream);
+int ofb_multi_tensor_adamw_dev(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms, float* const* vs,
+                               const long long* sizes, int grad_is_bf16, float beta1, float beta2, float eps, float weight_decay, const float* step,
+                               void* stream);
 int ofb_multi_tensor_sgd(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms, const long long* sizes,
                          int grad_is_bf16, float lr, float momentum, float dampening, int nesterov, int maximize, float weight_decay, float l1,
                          float l2, float scale, const float* lr_ptr, const float* scale_ptr, const long long* skip_if, void* stream);
@@ -124,7 +128,8 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
   } else if (t == "unary_bwd") {
     need(op.in.size() == 2 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]), "x, dy and dx of the same length");
   } else if (t == "layer_norm_bwd") {
-    need(op.in.size() == 4 && (op.out.size() == 1 || op.out.size() == 3), "(dy, x, gamma, stats) -> dx [, dgamma, dbeta]");
+    need((op.in.size() == 4 || op.in.size() == 5) && (op.out.size() == 1 || op.out.size() == 3), "(dy, x, gamma, stats [, add_to_dx]) -> dx [, dgamma, dbeta]");
+    if (op.in.size() == 5) need(n(op.in[4]) == n(op.in[1]) && dt(op.in[4]) == DType::kBFloat16, "the tensor added to dx must match x");
     const int64_t cols = shp(op.in[1]).back(), rows = n(op.in[1]) / cols;
     need(n(op.in[0]) == n(op.in[1]) && n(op.out[0]) == n(op.in[1]) && n(op.in[2]) == cols && n(op.in[3]) == 2 * rows && dt(op.in[3]) == DType::kFloat,
          "shape mismatch");
@@ -252,7 +257,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       s2 /= static_cast<float>(cols);
       for (int64_t c = 0; c < cols; ++c) {
         const float xh = (ldb(x, r * cols + c) - mean) * rstd, g = ldb(dy, r * cols + c) * ldb(gamma, c);
-        stb(dx, r * cols + c, rstd * (g - s1 - xh * s2));
+        stb(dx, r * cols + c, rstd * (g - s1 - xh * s2) + (op.in.size() > 4 ? ldb(addr(op.in[4]), r * cols + c) : 0.f));
       }
     }
     if (params) {
@@ -426,7 +431,7 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
     const int64_t cols = shp(op.in[1]).back(), rows = n(op.in[1]) / cols;
     const float* stats = static_cast<const float*>(addr(op.in[3]));
     const bool params = op.out.size() == 3;
-    ok(ofb_layer_norm_bwd(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), stats, stats + rows, nullptr, addr(op.out[0]),
+    ok(ofb_layer_norm_bwd(addr(op.in[0]), addr(op.in[1]), addr(op.in[2]), stats, stats + rows, op.in.size() > 4 ? addr(op.in[4]) : nullptr, addr(op.out[0]),
                           params ? static_cast<float*>(addr(op.out[1])) : nullptr, params ? static_cast<float*>(addr(op.out[2])) : nullptr,
                           static_cast<float*>(p.workspace), attr_int(op, "accumulate", 0) != 0 ? 1 : 0, static_cast<int>(rows), static_cast<int>(cols), s));
   } else if (t == "softmax_bwd") {
@@ -462,7 +467,6 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
   } else if (t == "adamw_update" || t == "sgd_update") {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
-    const float bc1 = 1.f - std::pow(train.beta1, static_cast<float>(train_steps)), bc2 = 1.f - std::pow(train.beta2, static_cast<float>(train_steps));
     for (int64_t first = 0; first < np; first += 48) {   // the multi-tensor kernels take 48 tensors per launch
       const int cnt = static_cast<int>(std::min<int64_t>(48, np - first));
       std::vector<void*> grads, copies;
@@ -477,12 +481,13 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
         if (states >= 2) s2.push_back(static_cast<float*>(addr(op.out[static_cast<size_t>(3 * np) + e])));
         sizes.push_back(n(op.in[e]));
       }
+      // learning rate and bias corrections come from the device (refreshed before every step), nothing here depends on the step
       if (adam)
-        ok(ofb_multi_tensor_adamw(cnt, grads.data(), masters.data(), copies.data(), s1.data(), s2.data(), sizes.data(), 0, train.lr, train.beta1,
-                                  train.beta2, train.eps, train.weight_decay, 0.f, 1.f, bc1, bc2, nullptr, nullptr, nullptr, s));
+        ok(ofb_multi_tensor_adamw_dev(cnt, grads.data(), masters.data(), copies.data(), s1.data(), s2.data(), sizes.data(), 0, train.beta1,
+                                      train.beta2, train.eps, train.weight_decay, step_scalars, s));
       else
-        ok(ofb_multi_tensor_sgd(cnt, grads.data(), masters.data(), copies.data(), states >= 1 ? s1.data() : nullptr, sizes.data(), 0, train.lr,
-                                train.momentum, 0.f, 0, 0, train.weight_decay, 0.f, 0.f, 1.f, nullptr, nullptr, nullptr, s));
+        ok(ofb_multi_tensor_sgd(cnt, grads.data(), masters.data(), copies.data(), states >= 1 ? s1.data() : nullptr, sizes.data(), 0, 0.f,
+                                train.momentum, 0.f, 0, 0, train.weight_decay, 0.f, 0.f, 1.f, step_scalars, nullptr, nullptr, s));
     }
   } else {
     return false;

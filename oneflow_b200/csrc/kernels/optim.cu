@@ -43,6 +43,8 @@ struct OptimHyper {
   const float* lr_ptr;      // overrides lr when non-null
   const float* scale_ptr;   // multiplies scale when non-null (e.g. 1/loss_scale or clip factor)
   const long long* skip_if; // skip the whole update when *skip_if != 0
+  const float* bc_ptr;      // {bc1, bc2} on the device: overrides the two values above when non-null, so that a step
+                            // captured in a CUDA graph sees the bias corrections of the step it is replayed for
 };
 
 __device__ __forceinline__ int find_tensor(const TensorTable& t, int chunk) {
@@ -63,6 +65,7 @@ __global__ void __launch_bounds__(512) multi_tensor_update_kernel(const __grid_c
   if (h.skip_if && *h.skip_if != 0) return;
   const float lr = h.lr_ptr ? *h.lr_ptr : h.lr;
   const float scale = h.scale * (h.scale_ptr ? *h.scale_ptr : 1.f);
+  const float bc1 = h.bc_ptr ? h.bc_ptr[0] : h.bc1, bc2 = h.bc_ptr ? h.bc_ptr[1] : h.bc2;
   for (int chunk = blockIdx.x; chunk < tab.first_chunk[tab.n]; chunk += gridDim.x) {
     const int ti = find_tensor(tab, chunk);
     const long long base = static_cast<long long>(chunk - tab.first_chunk[ti]) * tab.chunk;
@@ -107,8 +110,8 @@ __global__ void __launch_bounds__(512) multi_tensor_update_kernel(const __grid_c
         if (MODE == 0) {
           m4[j] = h.beta1 * m4[j] + (1.f - h.beta1) * g;
           v4[j] = h.beta2 * v4[j] + (1.f - h.beta2) * g * g;
-          const float denom = sqrtf(v4[j]) / sqrtf(h.bc2) + h.eps;
-          wv[j] = wv[j] - (lr / h.bc1) * (m4[j] / denom) - lr * h.weight_decay * wv[j];
+          const float denom = sqrtf(v4[j]) / sqrtf(bc2) + h.eps;
+          wv[j] = wv[j] - (lr / bc1) * (m4[j] / denom) - lr * h.weight_decay * wv[j];
         } else {
           if (mm) {
             m4[j] = h.momentum * m4[j] + (1.f - h.dampening) * g;
@@ -224,10 +227,33 @@ static int build_table(TensorTable& tab, int n, void* const* grads, float* const
 
 using namespace ofb;
 
+static int adamw_launch(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,
+                        float* const* vs, const long long* sizes, int grad_is_bf16, float lr, float beta1, float beta2, float eps,
+                        float weight_decay, float l2, float scale, float bc1, float bc2, const float* lr_ptr, const float* scale_ptr,
+                        const long long* skip_if, const float* bc_ptr, void* stream);
+
 OFB_API int ofb_multi_tensor_adamw(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,
                                    float* const* vs, const long long* sizes, int grad_is_bf16, float lr, float beta1,
                                    float beta2, float eps, float weight_decay, float l2, float scale, float bc1, float bc2,
                                    const float* lr_ptr, const float* scale_ptr, const long long* skip_if, void* stream) {
+  return adamw_launch(n, grads, masters, copies, ms, vs, sizes, grad_is_bf16, lr, beta1, beta2, eps, weight_decay, l2, scale, bc1, bc2,
+                      lr_ptr, scale_ptr, skip_if, nullptr, stream);
+}
+
+// The same update with the step-dependent scalars on the device: step[0] = learning rate, step[1] = 1 - beta1^t,
+// step[2] = 1 - beta2^t. Nothing in the launch depends on the step number, so it can be recorded in a CUDA graph.
+OFB_API int ofb_multi_tensor_adamw_dev(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,
+                                       float* const* vs, const long long* sizes, int grad_is_bf16, float beta1, float beta2, float eps,
+                                       float weight_decay, const float* step, void* stream) {
+  if (!step) return fail("multi_tensor_adamw_dev: the step scalars are required");
+  return adamw_launch(n, grads, masters, copies, ms, vs, sizes, grad_is_bf16, 0.f, beta1, beta2, eps, weight_decay, 0.f, 1.f, 1.f, 1.f, step,
+                      nullptr, nullptr, step + 1, stream);
+}
+
+static int adamw_launch(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,
+                        float* const* vs, const long long* sizes, int grad_is_bf16, float lr, float beta1, float beta2, float eps,
+                        float weight_decay, float l2, float scale, float bc1, float bc2, const float* lr_ptr, const float* scale_ptr,
+                        const long long* skip_if, const float* bc_ptr, void* stream) {
   TensorTable tab;
   const int chunks = build_table(tab, n, grads, masters, copies, ms, vs, sizes);
   if (chunks < 0) return -1;
@@ -236,6 +262,7 @@ OFB_API int ofb_multi_tensor_adamw(int n, void* const* grads, float* const* mast
   std::memset(&h, 0, sizeof(h));
   h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.weight_decay = weight_decay; h.l2 = l2; h.scale = scale;
   h.bc1 = bc1; h.bc2 = bc2; h.grad_is_bf16 = grad_is_bf16; h.lr_ptr = lr_ptr; h.scale_ptr = scale_ptr; h.skip_if = skip_if;
+  h.bc_ptr = bc_ptr;
   const int grid = chunks < 148 * 4 ? chunks : 148 * 4;
   multi_tensor_update_kernel<0><<<grid, 512, 0, (cudaStream_t)stream>>>(tab, h);
   OFB_CUDA_OK(cudaGetLastError());

@@ -194,6 +194,7 @@ def test_training_step_on_the_gpu_runtime_matches_the_host_runtime(tmp_path):
     lh = [host.step(ids.numpy(), tgt.numpy()) for _ in range(5)]
     ld = [dev.step(ids.numpy(), tgt.numpy()) for _ in range(5)]
     assert ld[-1] < ld[0]
+    assert dev.stats()["graph_replays"] == 4      # the whole step (forward, backward, update) is one CUDA-graph launch from the second on
     for a, b in zip(lh, ld):
         assert abs(a - b) < 5e-2 * max(abs(a), 1.0)
     host.close()
