@@ -589,6 +589,7 @@ void append_training_ops(IR& ir, const TrainOptions& options) {
 std::string ir_to_text(const IR& ir) {
   std::ostringstream ss;
   ss << "oneflow_b200 graph v2\n";
+  for (const auto& p : ir.pass_report) ss << "# pass " << p.first << " fired=" << p.second << '\n';
   for (size_t i = 0; i < ir.tensors.size(); ++i) {
     const TensorDef& t = ir.tensors[i];
     ss << "tensor " << i << ' ' << (t.dtype == DType::kBFloat16 ? "bf16" : t.dtype == DType::kInt64 ? "i64" : "f32") << ' '

@@ -43,7 +43,13 @@ struct IR {
   bool training = false;
   std::vector<int> trainable;   // parameter roots that get updated, in export order
   std::vector<int> masters;     // their fp32 master-weight state tensors
+  std::vector<std::pair<std::string, int>> pass_report;   // rewriting passes that ran and how often each fired
 };
+
+// The rewriting passes (graph_passes.cpp), in their fixed order; returns (pass name, times it fired).
+std::vector<std::pair<std::string, int>> run_graph_passes(IR& ir);
+// d fn(x) / dx for the unary function codes (graph_train_ops.cpp).
+float host_unary_grad(float x, int fn, float alpha);
 
 // Appends to a forward IR whose first output is a scalar loss: the backward operators, gradient buffers and one optimizer
 // update operator (graph_autodiff.cpp). Throws std::runtime_error with the offending operator for anything it cannot

@@ -1,0 +1,160 @@
+// Rewriting passes over the operator IR, run in a fixed order after a graph is loaded (and, for training graphs, after the
+// backward operators were appended) and before the plan compiler sees it. Each pass is a peephole over operators and the
+// storages ("roots") they touch; a pass only fires when the intermediate it removes has no other reader or writer.
+//
+//   fuse_activation_forward   linear -> gelu / relu            =>  linear with the activation in the GEMM epilogue; when a
+//                                                                   backward operator still reads the pre-activation, the
+//                                                                   epilogue also stores it (second output)
+//   fuse_activation_backward  matmul -> unary_bwd(pre-act, .)  =>  matmul whose epilogue multiplies by act'(pre-activation):
+//                                                                   the data-gradient GEMM of the NEXT layer produces the
+//                                                                   gradient w.r.t. the pre-activation directly
+//   drop_dead_operators       operators none of whose outputs is read by an operator or returned
+//
+// ONEFLOW_API_PASSES=0 switches all of them off (the unfused plan is the reference the tests compare with).
+//
+// Reference counterparts: the ordered pass list of LazyJobBuildAndInferCtx::Complete (oneflow/core/job/job_build_and_infer_ctx.cpp),
+// fuse patterns such as fused_bias_add_gelu (oneflow/ir/lib/OneFlow/PDLL/, oneflow/core/job_rewriter/fuse_*_pass.cpp) and
+// dead-code elimination on the job (oneflow/core/job_rewriter/prune_*_pass.cpp).
+#include <algorithm>
+#include <cstdlib>
+#include <set>
+
+#include "graph_impl.h"
+
+namespace oneflow_api {
+
+namespace {
+
+struct View {
+  const IR& ir;
+  explicit View(const IR& i) : ir(i) {}
+  int root(int t) const {
+    while (ir.tensors[static_cast<size_t>(t)].alias_of >= 0) t = ir.tensors[static_cast<size_t>(t)].alias_of;
+    return t;
+  }
+  int64_t offset(int t) const {
+    int64_t off = 0;
+    while (ir.tensors[static_cast<size_t>(t)].alias_of >= 0) {
+      off += ir.tensors[static_cast<size_t>(t)].alias_off;
+      t = ir.tensors[static_cast<size_t>(t)].alias_of;
+    }
+    return off;
+  }
+  int64_t count(int t) const { return numel(ir.tensors[static_cast<size_t>(t)].shape); }
+  bool whole(int t) const { return offset(t) == 0 && count(t) == count(root(t)); }
+};
+
+// operator indices that read / write each root, in order
+struct Touches {
+  std::vector<std::vector<int>> readers, writers;
+  std::set<int> returned;
+  Touches(const IR& ir, const View& v) : readers(ir.tensors.size()), writers(ir.tensors.size()) {
+    for (size_t i = 0; i < ir.ops.size(); ++i) {
+      for (int t : ir.ops[i].in)
+        if (t >= 0) readers[static_cast<size_t>(v.root(t))].push_back(static_cast<int>(i));
+      for (int t : ir.ops[i].out) writers[static_cast<size_t>(v.root(t))].push_back(static_cast<int>(i));
+    }
+    for (int t : ir.outputs) returned.insert(v.root(t));
+  }
+};
+
+const char* act_name(int64_t fn) { return fn == 1 ? "gelu" : fn == 2 ? "gelu_tanh" : fn == 3 ? "relu" : nullptr; }
+
+bool fuse_activation_forward(IR& ir) {
+  const View v(ir);
+  const Touches tc(ir, v);
+  for (size_t i = 0; i < ir.ops.size(); ++i) {
+    OpDef& lin = ir.ops[i];
+    if (lin.type != "linear" || lin.out.size() != 1 || attr_str(lin, "act", "none") != "none") continue;
+    if (lin.in.size() > 3 && lin.in[3] >= 0) continue;   // the epilogue applies the activation before the residual
+    const int h = v.root(lin.out[0]);
+    if (!v.whole(lin.out[0]) || tc.returned.count(h) || tc.writers[static_cast<size_t>(h)].size() != 1) continue;
+    int act_op = -1;
+    bool other = false, saved = false;
+    for (int r : tc.readers[static_cast<size_t>(h)]) {
+      const OpDef& o = ir.ops[static_cast<size_t>(r)];
+      if (o.type == "unary" && act_op < 0 && act_name(attr_int(o, "fn", 0)) && v.whole(o.in[0]) && v.root(o.out[0]) != h) act_op = r;
+      else if (o.type == "unary_bwd" && v.root(o.in[0]) == h && v.root(o.in[1]) != h) saved = true;   // reads the pre-activation
+      else if (o.type == "matmul" && o.in.size() == 3 && v.root(o.in[2]) == h && v.root(o.in[0]) != h && v.root(o.in[1]) != h) saved = true;
+      else other = true;
+    }
+    if (act_op < 0 || other || act_op < static_cast<int>(i)) continue;
+    const OpDef act = ir.ops[static_cast<size_t>(act_op)];
+    if (!v.whole(act.out[0]) || tc.writers[static_cast<size_t>(v.root(act.out[0]))].size() != 1) continue;
+    lin.attr["act"] = act_name(attr_int(act, "fn", 0));
+    const int pre = lin.out[0];
+    lin.out = {act.out[0]};
+    if (saved) lin.out.push_back(pre);
+    ir.ops.erase(ir.ops.begin() + act_op);
+    return true;
+  }
+  return false;
+}
+
+bool fuse_activation_backward(IR& ir) {
+  const View v(ir);
+  const Touches tc(ir, v);
+  for (size_t i = 0; i < ir.ops.size(); ++i) {
+    OpDef& mm = ir.ops[i];
+    if (mm.type != "matmul" || mm.in.size() != 2 || mm.out.size() != 1 || attr_int(mm, "ta", 0) != 0 || attr_int(mm, "accumulate", 0) != 0) continue;
+    if (ir.tensors[static_cast<size_t>(mm.out[0])].dtype != DType::kBFloat16 || ir.tensors[static_cast<size_t>(mm.in[0])].shape.size() != 2) continue;
+    const int t = v.root(mm.out[0]);
+    if (!v.whole(mm.out[0]) || tc.returned.count(t) || tc.writers[static_cast<size_t>(t)].size() != 1 || tc.readers[static_cast<size_t>(t)].size() != 1) continue;
+    const int j = tc.readers[static_cast<size_t>(t)][0];
+    const OpDef ub = ir.ops[static_cast<size_t>(j)];
+    if (ub.type != "unary_bwd" || j < static_cast<int>(i) || !act_name(attr_int(ub, "fn", 0))) continue;
+    if (v.root(ub.in[1]) != t || !v.whole(ub.in[1]) || v.root(ub.in[0]) == t || !v.whole(ub.in[0]) || !v.whole(ub.out[0])) continue;
+    if (tc.writers[static_cast<size_t>(v.root(ub.out[0]))].size() != 1) continue;
+    mm.in.push_back(ub.in[0]);
+    mm.attr["act_grad"] = act_name(attr_int(ub, "fn", 0));
+    mm.out = {ub.out[0]};
+    ir.ops.erase(ir.ops.begin() + j);
+    return true;
+  }
+  return false;
+}
+
+bool drop_dead_operators(IR& ir) {
+  const View v(ir);
+  const Touches tc(ir, v);
+  for (size_t i = ir.ops.size(); i-- > 0;) {
+    const OpDef& op = ir.ops[i];
+    if (op.type == "adamw_update" || op.type == "sgd_update") continue;
+    bool live = false;
+    for (int t : op.out) {
+      const int r = v.root(t);
+      if (tc.returned.count(r)) live = true;
+      for (int reader : tc.readers[static_cast<size_t>(r)])
+        if (reader > static_cast<int>(i)) live = true;
+    }
+    if (live) continue;
+    ir.ops.erase(ir.ops.begin() + static_cast<long>(i));
+    return true;
+  }
+  return false;
+}
+
+}  // namespace
+
+std::vector<std::pair<std::string, int>> run_graph_passes(IR& ir) {
+  std::vector<std::pair<std::string, int>> report;
+  const char* off = std::getenv("ONEFLOW_API_PASSES");
+  if (off && off[0] == '0') return report;
+  struct Pass {
+    const char* name;
+    bool (*fn)(IR&);
+  };
+  // backward first: the forward pass must see which pre-activations a fused data-gradient GEMM still reads
+  const Pass passes[] = {{"fuse_activation_backward", fuse_activation_backward},
+                         {"fuse_activation_forward", fuse_activation_forward},
+                         {"drop_dead_operators", drop_dead_operators}};
+  for (const Pass& p : passes) {
+    if (!ir.training && std::string(p.name) != "drop_dead_operators" && std::string(p.name) != "fuse_activation_forward") continue;
+    int fired = 0;
+    while (fired < 100000 && p.fn(ir)) ++fired;
+    report.emplace_back(p.name, fired);
+  }
+  return report;
+}
+
+}  // namespace oneflow_api

@@ -224,10 +224,13 @@ void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
     if (op.in.size() > 2 && op.in[2] >= 0) need(numel(shp(op.in[2])) == w[0], "bias must have N elements");
     if (op.in.size() > 3 && op.in[3] >= 0) need(numel(shp(op.in[3])) == numel(shp(op.out[0])), "residual must match the output");
   } else if (t == "matmul") {
-    need(op.in.size() == 2, "needs two inputs");
+    need(op.in.size() == 2 || op.in.size() == 3, "needs two inputs (and optionally the pre-activation whose derivative scales the result)");
     const auto& a = shp(op.in[0]);
     const auto& b = shp(op.in[1]);
     need(a.size() >= 2 && b.size() >= 2, "operands need at least two axes");
+    if (op.in.size() == 3)
+      need(a.size() == 2 && numel(shp(op.in[2])) == numel(shp(op.out[0])) && act_code(attr_str(op, "act_grad", "none")) != 0 && dt(op.out[0]) == DType::kBFloat16,
+           "act_grad needs a 2-D left operand, a pre-activation of the output's size and a bf16 output");
     const bool ta = attr_int(op, "ta", 0) != 0, tb = attr_int(op, "tb", 0) != 0;   // ta: the left operand is stored [.., K, M]
     const int64_t K = ta ? a[a.size() - 2] : a.back(), M = ta ? a.back() : a[a.size() - 2];
     const int64_t N = tb ? b[b.size() - 2] : b.back(), Kb = tb ? b.back() : b[b.size() - 2];
@@ -528,6 +531,7 @@ void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
     if (op.in.size() > 3 && op.in[3] >= 0) { a.residual = addr(op.in[3]); a.ldr = N; }
     a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
     a.act = act_code(attr_str(op, "act", "none"));
+    if (op.out.size() > 1) { a.aux_out = addr(op.out[1]); a.ld_aux = N; }   // the pre-activation, kept for the backward pass
     a.alpha = 1.f;
     ok(ofb_gemm_bf16(&a, s));
   } else if (t == "matmul") {
@@ -549,6 +553,7 @@ void Graph::Impl::run_op_device(const PlannedOp& p, cudaStream_t s) {
       a.C = static_cast<char*>(addr(op.out[0])) + b * M * N * (wide ? 4 : 2); a.ldc = N;
       a.out_fp32 = wide ? 1 : 0;
       a.accumulate = attr_int(op, "accumulate", 0) != 0 ? 1 : 0;
+      if (op.in.size() > 2) { a.aux_in = addr(op.in[2]); a.ld_aux = N; a.act = act_code(attr_str(op, "act_grad", "none")); }   // result *= act'(pre-activation)
       a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
       a.alpha = static_cast<float>(attr_float(op, "alpha", 1.0));
       ok(ofb_gemm_bf16(&a, s));
@@ -646,6 +651,7 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
         float acc = 0.f;
         for (int64_t k = 0; k < K; ++k) acc += xr[static_cast<size_t>(k)] * ldb(wt, n * K + k);
         if (bias) acc += ldb(bias, n);
+        if (op.out.size() > 1) stb(addr(op.out[1]), m * N + n, acc);   // the pre-activation, kept for the backward pass
         if (act) acc = host_unary(acc, act, 1.f);
         if (res) acc += ldb(res, m * N + n);
         stb(y, m * N + n, acc);
@@ -671,6 +677,8 @@ void Graph::Impl::run_op_host(const PlannedOp& p) {
           if (wide) {
             float* yf = static_cast<float*>(y) + yo + m * N + n;
             *yf = (accumulate ? *yf : 0.f) + acc * alpha;
+          } else if (op.in.size() > 2) {
+            stb(y, yo + m * N + n, acc * alpha * host_unary_grad(ldb(addr(op.in[2]), yo + m * N + n), act_code(attr_str(op, "act_grad", "none")), 1.f));
           } else {
             stb(y, yo + m * N + n, acc * alpha);
           }
@@ -896,6 +904,7 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
       check_cuda(cudaMallocHost(&impl->step_scalars_host, 4 * sizeof(float)), "cudaMallocHost");
     }
   }
+  impl->ir.pass_report = run_graph_passes(impl->ir);
   // parameters
   impl->params.resize(impl->ir.tensors.size());
   for (size_t i = 0; i < impl->ir.tensors.size(); ++i) {

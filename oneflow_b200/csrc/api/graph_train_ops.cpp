@@ -74,7 +74,9 @@ inline void st(void* p, DType dt, int64_t i, float v) {
 inline float ldb(const void* p, int64_t i) { return from_bf16(static_cast<const uint16_t*>(p)[i]); }
 inline void stb(void* p, int64_t i, float v) { static_cast<uint16_t*>(p)[i] = to_bf16(v); }
 
-float unary_grad(float x, int fn, float alpha) {
+}  // namespace
+
+float host_unary_grad(float x, int fn, float alpha) {
   switch (fn) {
     case 0: return alpha;
     case 1: return 0.5f * (1.f + std::erf(x * 0.7071067811865476f)) + x * 0.3989422804014327f * std::exp(-0.5f * x * x);
@@ -102,6 +104,10 @@ float unary_grad(float x, int fn, float alpha) {
     default: return 1.f;
   }
 }
+
+namespace {
+
+inline float unary_grad(float x, int fn, float alpha) { return host_unary_grad(x, fn, alpha); }
 
 bool is_float_type(DType d) { return d == DType::kBFloat16 || d == DType::kFloat; }
 

@@ -199,3 +199,46 @@ def test_training_step_on_the_gpu_runtime_matches_the_host_runtime(tmp_path):
         assert abs(a - b) < 5e-2 * max(abs(a), 1.0)
     host.close()
     dev.close()
+
+
+def test_rewriting_passes_fuse_the_activation_into_both_gemms_and_keep_the_numbers(tmp_path, monkeypatch):
+    """linear -> gelu becomes one GEMM that also stores the pre-activation; the next layer's data-gradient GEMM multiplies by
+    gelu' of it in its epilogue, so neither the activation nor its derivative is a pass of its own. The unfused plan
+    (passes switched off) is the reference."""
+    torch.manual_seed(5)
+    m = _bf16_weights(TiedLM(d=64, heads=1, vocab=96, seq=16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path), fuse=False)
+    fused = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.5)
+    text = fused.dump()
+    assert "# pass fuse_activation_backward fired=1" in text and "# pass fuse_activation_forward fired=1" in text
+    assert "act=gelu" in text and "act_grad=gelu" in text and "op unary" not in text
+    monkeypatch.setenv("ONEFLOW_API_PASSES", "0")
+    plain = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.5)
+    monkeypatch.delenv("ONEFLOW_API_PASSES")
+    assert "op unary_bwd" in plain.dump() and "act_grad" not in plain.dump()
+    assert fused.stats()["ops"] < plain.stats()["ops"]
+    before = fused.parameters()
+    a, b = fused.step(ids.numpy(), tgt.numpy()), plain.step(ids.numpy(), tgt.numpy())
+    assert abs(a - b) < 1e-3 * max(abs(b), 1.0)                    # the forward pass computes the same numbers
+    pf, pp = fused.parameters(), plain.parameters()
+    for k in pf:                                                    # one step: the parameter deltas are lr * gradient
+        gf, gp = before[k] - pf[k], before[k] - pp[k]
+        assert np.abs(gf - gp).max() <= 3e-2 * (np.abs(gp).max() + 1e-6), k
+    for _ in range(2):
+        a, b = fused.step(ids.numpy(), tgt.numpy()), plain.step(ids.numpy(), tgt.numpy())
+        assert abs(a - b) < 5e-2 * max(abs(b), 1.0)
+    fused.close()
+    plain.close()
+
+
+def test_inference_graph_exported_unfused_is_fused_at_load_time(tmp_path):
+    torch.manual_seed(6)
+    m = _bf16_weights(nn.Sequential(nn.Linear(32, 64), nn.GELU(), nn.Linear(64, 16), nn.ReLU()))
+    x = torch.randn(8, 32).bfloat16().float()
+    d = E.export_graph(m, (x,), str(tmp_path), fuse=False)
+    g = E.InferenceGraph(d, device=-1)
+    assert g.stats()["ops"] == 2                      # two GEMMs, activations in their epilogues
+    out = g.run(x.numpy())[0]
+    assert np.abs(out - m(x).detach().numpy().reshape(-1)).max() < 3e-2
+    g.close()
