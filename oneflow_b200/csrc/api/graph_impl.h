@@ -127,6 +127,7 @@ inline int64_t numel(const std::vector<int64_t>& s) {
 struct Graph::Impl {
   IR ir;
   std::string dir;
+  std::string graph_text;   // graph.txt as loaded (Save writes it back unchanged)
   int device = 0;
   int n_streams = 2;
   std::vector<std::shared_ptr<void>> params;   // per tensor id (params only)

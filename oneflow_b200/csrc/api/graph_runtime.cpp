@@ -889,6 +889,12 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
   std::string line;
   std::getline(f, line);
   auto impl = std::make_shared<Graph::Impl>();
+  {
+    std::ifstream whole(dir + "/graph.txt", std::ios::binary);
+    std::ostringstream text;
+    text << whole.rdbuf();
+    impl->graph_text = text.str();
+  }
   impl->dir = dir;
   impl->device = device;
   impl->n_streams = std::max(1, std::min(n_streams, 16));
@@ -975,6 +981,89 @@ int64_t Graph::steps() const {
   return impl_->train_steps;
 }
 std::string Graph::dump() const { return ir_to_text(impl_->ir); }
+
+namespace {
+constexpr uint64_t kTrainStateMagic = 0x31545354464f4eull;   // "NOFTST1"
+void write_file(const std::string& path, const void* data, size_t bytes) {
+  std::ofstream f(path, std::ios::binary | std::ios::trunc);
+  if (!f) throw std::runtime_error("cannot write " + path);
+  f.write(static_cast<const char*>(data), static_cast<std::streamsize>(bytes));
+  if (!f) throw std::runtime_error("short write: " + path);
+}
+}  // namespace
+
+void Graph::Save(const std::string& dir) const {
+  Impl& im = *impl_;
+  std::lock_guard<std::mutex> g(im.run_mu);
+  if (im.device >= 0) check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+  write_file(dir + "/graph.txt", im.graph_text.data(), im.graph_text.size());
+  std::vector<char> host;
+  for (size_t i = 0; i < im.ir.tensors.size(); ++i) {
+    const TensorDef& t = im.ir.tensors[i];
+    if (t.kind != 1 || t.alias_of >= 0) continue;
+    host.resize(static_cast<size_t>(numel(t.shape) * SizeOf(t.dtype)));
+    copy_out(host.data(), im.params[i].get(), host.size(), im.device);
+    write_file(dir + "/" + t.file, host.data(), host.size());
+  }
+  if (!im.ir.training) return;
+  // train_state.bin: magic, steps, number of state tensors, then per state tensor (in IR order) its length and fp32 data
+  std::vector<char> blob;
+  auto put = [&](const void* p, size_t n) { blob.insert(blob.end(), static_cast<const char*>(p), static_cast<const char*>(p) + n); };
+  uint64_t n_state = 0;
+  for (const TensorDef& t : im.ir.tensors) n_state += t.kind == 3 ? 1 : 0;
+  const uint64_t steps = static_cast<uint64_t>(im.train_steps);
+  put(&kTrainStateMagic, 8);
+  put(&steps, 8);
+  put(&n_state, 8);
+  for (size_t i = 0; i < im.ir.tensors.size(); ++i) {
+    const TensorDef& t = im.ir.tensors[i];
+    if (t.kind != 3) continue;
+    const uint64_t n = static_cast<uint64_t>(numel(t.shape));
+    host.resize(n * 4);
+    copy_out(host.data(), im.params[i].get(), host.size(), im.device);
+    put(&n, 8);
+    put(host.data(), host.size());
+  }
+  write_file(dir + "/train_state.bin", blob.data(), blob.size());
+}
+
+void Graph::Restore(const std::string& dir) {
+  Impl& im = *impl_;
+  std::lock_guard<std::mutex> g(im.run_mu);
+  if (!im.ir.training) throw std::runtime_error("Restore: not a training graph");
+  std::ifstream f(dir + "/train_state.bin", std::ios::binary);
+  if (!f) throw std::runtime_error("cannot open " + dir + "/train_state.bin");
+  uint64_t magic = 0, steps = 0, n_state = 0;
+  f.read(reinterpret_cast<char*>(&magic), 8);
+  f.read(reinterpret_cast<char*>(&steps), 8);
+  f.read(reinterpret_cast<char*>(&n_state), 8);
+  if (!f || magic != kTrainStateMagic) throw std::runtime_error("train_state.bin: not a training state file");
+  uint64_t have = 0;
+  for (const TensorDef& t : im.ir.tensors) have += t.kind == 3 ? 1 : 0;
+  if (have != n_state) throw std::runtime_error("train_state.bin: holds " + std::to_string(n_state) + " state tensors, the graph has " + std::to_string(have) + " (another optimizer?)");
+  if (im.device >= 0) check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+  std::vector<char> host;
+  // read everything first, apply after: a truncated file leaves the graph untouched
+  std::vector<std::vector<char>> staged;
+  for (size_t i = 0; i < im.ir.tensors.size(); ++i) {
+    const TensorDef& t = im.ir.tensors[i];
+    if (t.kind != 3) continue;
+    uint64_t n = 0;
+    f.read(reinterpret_cast<char*>(&n), 8);
+    if (!f || n != static_cast<uint64_t>(numel(t.shape))) throw std::runtime_error("train_state.bin: state tensor " + std::to_string(staged.size()) + " has another length or the file is truncated");
+    host.resize(n * 4);
+    f.read(host.data(), static_cast<std::streamsize>(host.size()));
+    if (static_cast<size_t>(f.gcount()) != host.size()) throw std::runtime_error("train_state.bin: truncated");
+    staged.push_back(host);
+  }
+  size_t k = 0;
+  for (size_t i = 0; i < im.ir.tensors.size(); ++i) {
+    if (im.ir.tensors[i].kind != 3) continue;
+    copy_in(im.params[i].get(), staged[k].data(), staged[k].size(), im.device);
+    ++k;
+  }
+  im.train_steps = static_cast<int64_t>(steps);
+}
 
 int Graph::num_inputs() const { return static_cast<int>(impl_->ir.inputs.size()); }
 int Graph::num_outputs() const { return static_cast<int>(impl_->ir.outputs.size()); }

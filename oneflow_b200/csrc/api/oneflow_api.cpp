@@ -292,6 +292,24 @@ int ofb_api_graph_set_lr(void* g, float lr) {
   static_cast<Graph*>(g)->set_learning_rate(lr);
   return 0;
 }
+int ofb_api_graph_save(void* g, const char* dir) {
+  try {
+    static_cast<Graph*>(g)->Save(dir);
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_restore(void* g, const char* dir) {
+  try {
+    static_cast<Graph*>(g)->Restore(dir);
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
 long long ofb_api_graph_steps(void* g) { return static_cast<Graph*>(g)->steps(); }
 long long ofb_api_graph_dump(void* g, char* buf, long long cap) {
   const std::string text = static_cast<Graph*>(g)->dump();

@@ -128,6 +128,11 @@ class Graph {
   std::string parameter_name(int i) const;
   int64_t parameter_numel(int i) const;
   std::vector<float> parameter(int i) const;
+  // Save writes a directory that loads again (graph.txt and every parameter file, the trainable ones with their current
+  // values) plus, for training graphs, train_state.bin: step count, fp32 master weights and optimizer state. Restore reads
+  // train_state.bin back into a training graph loaded from such a directory, so that training continues bit for bit.
+  void Save(const std::string& dir) const;
+  void Restore(const std::string& dir);
   void set_learning_rate(float lr);
   int64_t steps() const;
   std::string dump() const;
@@ -165,6 +170,8 @@ const char* ofb_api_graph_parameter_name(void* graph, int i);
 long long ofb_api_graph_parameter_numel(void* graph, int i);
 int ofb_api_graph_parameter_read(void* graph, int i, float* out);
 int ofb_api_graph_set_lr(void* graph, float lr);
+int ofb_api_graph_save(void* graph, const char* dir);
+int ofb_api_graph_restore(void* graph, const char* dir);
 long long ofb_api_graph_steps(void* graph);
 // Writes the operator list (IR text) into buf (at most cap bytes, zero-terminated); returns the full length.
 long long ofb_api_graph_dump(void* graph, char* buf, long long cap);

@@ -668,6 +668,18 @@ class TrainingGraph(InferenceGraph):
     def set_lr(self, lr):
         self.lib.ofb_api_graph_set_lr(ctypes.c_void_p(self.h), ctypes.c_float(lr))
 
+    def save(self, directory):
+        """Writes a directory that loads again (for inference, or with ``restore`` for training that continues bit for bit)."""
+        os.makedirs(directory, exist_ok=True)
+        if self.lib.ofb_api_graph_save(ctypes.c_void_p(self.h), directory.encode()) != 0:
+            raise RuntimeError(self.lib.ofb_api_last_error().decode())
+        return directory
+
+    def restore(self, directory):
+        """Step count, fp32 master weights and optimizer state from ``directory/train_state.bin`` (written by ``save``)."""
+        if self.lib.ofb_api_graph_restore(ctypes.c_void_p(self.h), directory.encode()) != 0:
+            raise RuntimeError(self.lib.ofb_api_last_error().decode())
+
     def parameters(self):
         h = ctypes.c_void_p(self.h)
         out = {}

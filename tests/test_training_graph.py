@@ -242,3 +242,39 @@ def test_inference_graph_exported_unfused_is_fused_at_load_time(tmp_path):
     out = g.run(x.numpy())[0]
     assert np.abs(out - m(x).detach().numpy().reshape(-1)).max() < 3e-2
     g.close()
+
+
+def test_save_and_restore_continue_training_bit_for_bit(tmp_path):
+    torch.manual_seed(7)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path / "export"), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.1)
+    for _ in range(3):
+        g.step(x.numpy(), y.numpy())
+    saved = g.save(str(tmp_path / "ckpt"))
+    after = [g.step(x.numpy(), y.numpy()) for _ in range(3)]
+    final = g.parameters()
+    g.close()
+    # the saved directory is a graph of its own: as inference it computes the loss of the saved weights
+    assert abs(E.InferenceGraph(saved, device=-1).run(x.numpy(), y.numpy())[0][0] - after[0]) < 1e-6
+    r = E.TrainingGraph(saved, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.1)
+    r.restore(saved)
+    assert r.steps == 3
+    assert [r.step(x.numpy(), y.numpy()) for _ in range(3)] == after
+    again = r.parameters()
+    assert all(np.array_equal(final[k], again[k]) for k in final)
+    r.close()
+    # without restore the moments start from zero and the master weights from the rounded bf16 files: another trajectory
+    cold = E.TrainingGraph(saved, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.1)
+    assert [cold.step(x.numpy(), y.numpy()) for _ in range(3)] != after
+    # a state file of another optimizer is refused, and the graph stays usable
+    sgd = E.TrainingGraph(saved, device=-1, optimizer="sgd", lr=1e-2)
+    with pytest.raises(RuntimeError, match="another optimizer"):
+        sgd.restore(saved)
+    (tmp_path / "ckpt" / "train_state.bin").write_bytes((tmp_path / "ckpt" / "train_state.bin").read_bytes()[:-100])
+    with pytest.raises(RuntimeError, match="truncated"):
+        cold.restore(saved)
+    cold.step(x.numpy(), y.numpy())
+    cold.close()
+    sgd.close()
