@@ -131,9 +131,14 @@ struct Builder {
   int grad_storage(int r) {
     if (grad_root[static_cast<size_t>(r)] >= 0) return grad_root[static_cast<size_t>(r)];
     const bool param = ir.tensors[static_cast<size_t>(r)].kind == 1;
-    const int g = new_root(param ? DType::kFloat : DType::kBFloat16, count(r));
+    // with gradient accumulation a parameter gradient outlives the call: persistent storage, cleared on the first micro-batch only
+    const bool persistent = param && opt.accumulation_steps > 1;
+    const int g = new_root(param ? DType::kFloat : DType::kBFloat16, count(r), persistent ? 3 : 2);
     grad_root[static_cast<size_t>(r)] = g;
-    if (mode[static_cast<size_t>(r)] != Mode::kDirect && mode[static_cast<size_t>(r)] != Mode::kResidualLayerNorm) emit("fill", {}, {g}, {{"value", "0"}});
+    if (mode[static_cast<size_t>(r)] != Mode::kDirect && mode[static_cast<size_t>(r)] != Mode::kResidualLayerNorm) {
+      OpDef& f = emit("fill", {}, {g}, {{"value", "0"}});
+      if (persistent) f.attr["when"] = "first";
+    }
     return g;
   }
   bool has_grad(int t) const { return grad_root[static_cast<size_t>(root(t))] >= 0; }
@@ -200,6 +205,8 @@ struct Builder {
 void Builder::run() {
   if (ir.dynamic_rows) throw std::runtime_error("training graph: export with static shapes (export_graph), not the layer-list form");
   if (opt.optimizer != "adamw" && opt.optimizer != "sgd") throw std::runtime_error("training graph: optimizer must be \"adamw\" or \"sgd\"");
+  if (opt.accumulation_steps < 1 || opt.accumulation_steps > 65536) throw std::runtime_error("training graph: accumulation_steps must be between 1 and 65536");
+  if (opt.clip_grad_norm < 0.f) throw std::runtime_error("training graph: clip_grad_norm must not be negative");
   const size_t nt = ir.tensors.size();
   const int n_ops = static_cast<int>(ir.ops.size());
   grad_root.assign(nt, -1);
@@ -337,7 +344,21 @@ void Builder::run() {
   outs.insert(outs.end(), masters.begin(), masters.end());
   outs.insert(outs.end(), s1.begin(), s1.end());
   outs.insert(outs.end(), s2.begin(), s2.end());
-  emit(adam ? "adamw_update" : "sgd_update", grads, outs, {{"n", std::to_string(params.size())}, {"states", std::to_string((s1.empty() ? 0 : 1) + (s2.empty() ? 0 : 1))}});
+  std::map<std::string, std::string> when;
+  if (opt.accumulation_steps > 1) when["when"] = "last";
+  std::vector<int> update_in = grads;
+  std::map<std::string, std::string> uattr = {{"n", std::to_string(params.size())}, {"states", std::to_string((s1.empty() ? 0 : 1) + (s2.empty() ? 0 : 1))}};
+  if (opt.clip_grad_norm > 0.f) {
+    // {sum of squares, non-finite count, clip factor, norm}; the update reads the factor on the device
+    const int clip = new_root(DType::kFloat, 4);
+    std::map<std::string, std::string> cattr = when;
+    cattr["max_norm"] = fstr(opt.clip_grad_norm);
+    emit("grad_clip", grads, {clip}, cattr);
+    update_in.push_back(clip);
+    uattr["clip"] = "1";
+  }
+  uattr.insert(when.begin(), when.end());
+  emit(adam ? "adamw_update" : "sgd_update", update_in, outs, uattr);
 
   for (auto& op : out_ops) ir.ops.push_back(std::move(op));
   ir.training = true;
@@ -350,6 +371,7 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
   if (t == "cross_entropy") {
     // the forward operator writes d loss / d logits (already divided by the row count) beside the loss
     const int logits = in(0);
+    if (opt.accumulation_steps > 1) fwd.attr["grad_scale"] = fstr(1.0 / opt.accumulation_steps);
     if (mode[static_cast<size_t>(root(logits))] == Mode::kDirect) {
       fwd.out.push_back(grad_of(logits));
     } else {
@@ -364,7 +386,7 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
     const int a = in(0), b = in(1);
     const int diff = new_root(DType::kBFloat16, count(a));
     emit("binary", {alias(root(a), abs_off(a), {count(a)}), alias(root(b), abs_off(b), {count(b)})}, {diff}, {{"fn", "1"}, {"bmode", "0"}, {"cols", "1"}});
-    const double g = 2.0 / static_cast<double>(count(a));
+    const double g = 2.0 / static_cast<double>(count(a)) / static_cast<double>(opt.accumulation_steps);
     if (wants(a)) pass_grad(a, diff, g);
     if (wants(b)) pass_grad(b, diff, -g);
     return;

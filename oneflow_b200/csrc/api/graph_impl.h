@@ -141,10 +141,14 @@ struct Graph::Impl {
   // cross-stream edges as events) into a graph on the calling thread, and from then on a Forward is: copy the inputs into
   // the plan's own input buffers, one graph launch, copy the outputs out.
   std::vector<std::shared_ptr<void>> input_bufs;   // per graph input, static addresses
-  cudaGraphExec_t graph_exec = nullptr;
+  // One recorded graph per kind of call: bit 0 = first micro-batch of an optimizer step, bit 1 = last one (operators marked
+  // when=first / when=last only run then). Without gradient accumulation every call is kind 3.
+  cudaGraphExec_t graph_exec[4] = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t fork_event = nullptr;
   std::vector<cudaEvent_t> join_events;
-  int runs_of_plan = 0;
+  int runs_of_plan[4] = {0, 0, 0, 0};
+  int micro_step = 0;     // position inside the current optimizer step
+  int call_kind = 3;      // of the running call
   int64_t graph_replays = 0;
   bool graph_disabled = false;
   // training graphs: hyper-parameters read by the update operator at launch time, steps taken so far
@@ -164,7 +168,8 @@ struct Graph::Impl {
     if (executor) ofc_executor_destroy(executor);
     if (step_scalars) cudaFree(step_scalars);
     if (step_scalars_host) cudaFreeHost(step_scalars_host);
-    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    for (auto ge : graph_exec)
+      if (ge) cudaGraphExecDestroy(ge);
     if (fork_event) cudaEventDestroy(fork_event);
     for (auto e : join_events) cudaEventDestroy(e);
     for (auto e : events) cudaEventDestroy(e);
@@ -186,6 +191,12 @@ struct Graph::Impl {
     const int r = plan->root[static_cast<size_t>(tensor)];
     char* b = static_cast<char*>(plan->base[static_cast<size_t>(r)] ? plan->base[static_cast<size_t>(r)] : bound[static_cast<size_t>(r)]);
     return b + plan->byte_off[static_cast<size_t>(tensor)];
+  }
+  // operators marked when=first / when=last are skipped on the other micro-batches
+  bool op_enabled(const OpDef& op) const {
+    auto it = op.attr.find("when");
+    if (it == op.attr.end()) return true;
+    return it->second == "first" ? (call_kind & 1) != 0 : (call_kind & 2) != 0;
   }
   void run_op(int index);
   bool capture_plan();

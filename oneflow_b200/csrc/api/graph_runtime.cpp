@@ -330,6 +330,7 @@ void Graph::Impl::compile(int64_t rows) {
       const int r = p->root[static_cast<size_t>(t)];
       const bool update = op.type == "adamw_update" || op.type == "sgd_update";
       if (update && (root_kind(r) == 1 || root_kind(r) == 3)) continue;   // parameters and optimizer state: persistent, not planned
+      if (ir.training && root_kind(r) == 3) continue;                    // gradient accumulators that outlive the call
       if (root_kind(r) != 2) throw std::runtime_error("operator " + op.type + " writes a tensor that is not an activation");
       if (first[static_cast<size_t>(r)] < 0) first[static_cast<size_t>(r)] = i;
       last[static_cast<size_t>(r)] = i;
@@ -488,11 +489,11 @@ void Graph::Impl::compile(int64_t rows) {
     executor = ofc_executor_create(n_streams);
     if (!executor) throw std::runtime_error(std::string("executor: ") + ofc_last_error());
   }
-  if (graph_exec) {
-    cudaGraphExecDestroy(graph_exec);
-    graph_exec = nullptr;
+  for (int k = 0; k < 4; ++k) {
+    if (graph_exec[k]) cudaGraphExecDestroy(graph_exec[k]);
+    graph_exec[k] = nullptr;
+    runs_of_plan[k] = 0;
   }
-  runs_of_plan = 0;
   graph_replays = 0;
   input_bufs.clear();
   if (device >= 0) {
@@ -812,7 +813,7 @@ void Graph::Impl::run_op(int index) {
   const PlannedOp& p = plan->ops[static_cast<size_t>(index)];
   try {
     if (device < 0) {
-      run_op_host(p);
+      if (op_enabled(*p.def)) run_op_host(p);
       return;
     }
     check_cuda(cudaSetDevice(device), "cudaSetDevice");
@@ -820,7 +821,7 @@ void Graph::Impl::run_op(int index) {
     // the scheduler ran every dependency's host side already, so its event has been recorded
     for (int d : p.deps)
       if (plan->ops[static_cast<size_t>(d)].stream != p.stream) check_cuda(cudaStreamWaitEvent(s, events[static_cast<size_t>(d)], 0), "cudaStreamWaitEvent");
-    run_op_device(p, s);
+    if (op_enabled(*p.def)) run_op_device(p, s);
     check_cuda(cudaEventRecord(events[static_cast<size_t>(index)], s), "cudaEventRecord");
   } catch (const std::exception& e) {
     fail(e.what());
@@ -851,7 +852,7 @@ bool Graph::Impl::capture_plan() {
       cudaStream_t s = streams[static_cast<size_t>(p.stream)];
       for (int d : p.deps)
         if (plan->ops[static_cast<size_t>(d)].stream != p.stream) check_cuda(cudaStreamWaitEvent(s, events[static_cast<size_t>(d)], 0), "cudaStreamWaitEvent");
-      run_op_device(p, s);
+      if (op_enabled(*p.def)) run_op_device(p, s);
       check_cuda(cudaEventRecord(events[i], s), "cudaEventRecord");
     }
     for (size_t s = 1; s < streams.size(); ++s) {
@@ -869,16 +870,16 @@ bool Graph::Impl::capture_plan() {
     return give_up(why.empty() ? std::string("cudaStreamEndCapture: ") + cudaGetErrorString(rc) : why);
   }
   if (ok) {
-    rc = cudaGraphInstantiate(&graph_exec, g, 0);
+    rc = cudaGraphInstantiate(&graph_exec[call_kind], g, 0);
     if (rc != cudaSuccess) {
       cudaGetLastError();
-      graph_exec = nullptr;
+      graph_exec[call_kind] = nullptr;
       ok = false;
       why = std::string("cudaGraphInstantiate: ") + cudaGetErrorString(rc);
     }
   }
   cudaGraphDestroy(g);
-  if (!ok || !graph_exec) return give_up(why);
+  if (!ok || !graph_exec[call_kind]) return give_up(why);
   return true;
 }
 
@@ -1006,6 +1007,7 @@ void Graph::Save(const std::string& dir) const {
     write_file(dir + "/" + t.file, host.data(), host.size());
   }
   if (!im.ir.training) return;
+  if (im.micro_step != 0) throw std::runtime_error("Save: " + std::to_string(im.micro_step) + " micro-batches of the running optimizer step are accumulated; save between steps");
   // train_state.bin: magic, steps, number of state tensors, then per state tensor (in IR order) its length and fp32 data
   std::vector<char> blob;
   auto put = [&](const void* p, size_t n) { blob.insert(blob.end(), static_cast<const char*>(p), static_cast<const char*>(p) + n); };
@@ -1134,8 +1136,11 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
+  im.call_kind = 3;
   if (im.ir.training) {
-    ++im.train_steps;   // the update operator of this call sees the 1-based step number
+    const int k = std::max(1, im.train.accumulation_steps);
+    im.call_kind = (im.micro_step == 0 ? 1 : 0) | (im.micro_step == k - 1 ? 2 : 0);
+    if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
     if (im.device >= 0) {
       im.step_scalars_host[0] = im.train.lr;
       im.step_scalars_host[1] = 1.f - std::pow(im.train.beta1, static_cast<float>(im.train_steps));
@@ -1148,17 +1153,18 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
   bool replayed = false;
   if (im.device >= 0) {
     check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");   // inputs are in place before any stream reads them
-    if (!im.graph_disabled && im.runs_of_plan >= 1) {
-      if (!im.graph_exec && !im.capture_plan()) im.graph_disabled = true;
-      if (im.graph_exec) {
-        check_cuda(cudaGraphLaunch(im.graph_exec, im.streams[0]), "cudaGraphLaunch");
+    if (!im.graph_disabled && im.runs_of_plan[im.call_kind] >= 1) {
+      if (!im.graph_exec[im.call_kind] && !im.capture_plan()) im.graph_disabled = true;
+      if (im.graph_exec[im.call_kind]) {
+        check_cuda(cudaGraphLaunch(im.graph_exec[im.call_kind], im.streams[0]), "cudaGraphLaunch");
         check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");
         replayed = true;
         ++im.graph_replays;
       }
     }
   }
-  ++im.runs_of_plan;
+  ++im.runs_of_plan[im.call_kind];
+  if (im.ir.training) im.micro_step = (im.call_kind & 2) ? 0 : im.micro_step + 1;
   const int n_ops = replayed ? 0 : static_cast<int>(plan.ops.size());
   std::vector<TaskArg> args(static_cast<size_t>(n_ops));
   for (int i = 0; i < n_ops; ++i) {

@@ -14,7 +14,9 @@
 //   embedding_bwd   (ids, dy) -> table gradient (fp32, scatter-add)
 //   cross_entropy   (logits, targets) -> mean loss [, d loss / d logits]
 //   mse             (a, b) -> mean squared difference
-//   adamw_update / sgd_update   gradients -> parameters (bf16), fp32 master weights and optimizer state, in place
+//   grad_clip       gradients -> {sum of squares, non-finite count, clip factor, global norm}
+//   adamw_update / sgd_update   gradients [, clip] -> parameters (bf16), fp32 master weights and optimizer state, in place
+// Operators marked when=first / when=last run only on the first / last micro-batch of an optimizer step (gradient accumulation).
 //
 // Reference counterparts: oneflow/user/kernels/{layer_norm_gpu_kernel.cu, softmax_kernel.cpp, sparse_softmax_cross_entropy_kernel.cu,
 // unsorted_segment_sum_kernel.cpp, reduce_kernel.cpp, model_update_kernels.cpp}, oneflow/user/ops/*_grad*.
@@ -54,7 +56,10 @@ int ofb_multi_tensor_adamw(int n, void* const* grads, float* const* masters, voi
                            float scale, float bc1, float bc2, const float* lr_ptr, const float* scale_ptr, const long long* skip_if, void* stream);
 int ofb_multi_tensor_adamw_dev(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms, float* const* vs,
                                const long long* sizes, int grad_is_bf16, float beta1, float beta2, float eps, float weight_decay, const float* step,
-                               void* stream);
+                               const float* scale_ptr, void* stream);
+int ofb_sqsum_scratch_floats(void);
+int ofb_multi_tensor_sqsum(int n, void* const* grads, const long long* sizes, int grad_is_bf16, float* scratch, float* out, int accumulate, void* stream);
+int ofb_clip_factor(const float* sq_and_bad, float max_norm, float* factor, long long* found_inf, float* total_norm, void* stream);
 int ofb_multi_tensor_sgd(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms, const long long* sizes,
                          int grad_is_bf16, float lr, float momentum, float dampening, int nesterov, int maximize, float weight_decay, float l1,
                          float l2, float scale, const float* lr_ptr, const float* scale_ptr, const long long* skip_if, void* stream);
@@ -160,9 +165,13 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
   } else if (t == "mse") {
     need(op.in.size() == 2 && n(op.in[0]) == n(op.in[1]) && dt(op.in[0]) == DType::kBFloat16 && dt(op.in[1]) == DType::kBFloat16, "two bf16 inputs of the same length");
     need(dt(op.out[0]) == DType::kFloat && n(op.out[0]) == 1, "a scalar fp32 loss");
+  } else if (t == "grad_clip") {
+    need(!op.in.empty() && op.out.size() == 1 && n(op.out[0]) == 4 && dt(op.out[0]) == DType::kFloat, "gradients -> four fp32 values");
+    for (int g : op.in) need(dt(g) == DType::kFloat, "fp32 gradients");
   } else if (t == "adamw_update" || t == "sgd_update") {
-    const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
-    need(np > 0 && static_cast<int64_t>(op.in.size()) == np && static_cast<int64_t>(op.out.size()) == np * (2 + states), "n gradients -> n parameters, n master copies, n * states state tensors");
+    const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0), clip = attr_int(op, "clip", 0);
+    need(np > 0 && static_cast<int64_t>(op.in.size()) == np + clip && static_cast<int64_t>(op.out.size()) == np * (2 + states), "n gradients [+ clip] -> n parameters, n master copies, n * states state tensors");
+    if (clip) need(n(op.in[static_cast<size_t>(np)]) == 4 && dt(op.in[static_cast<size_t>(np)]) == DType::kFloat, "the clip record is four fp32 values");
     need(t == "adamw_update" ? states == 2 : states <= 1, "state tensors per parameter");
     for (int64_t i = 0; i < np; ++i) {
       const int64_t len = n(op.in[static_cast<size_t>(i)]);
@@ -192,6 +201,7 @@ int64_t train_workspace_for(const OpDef& op, const Plan& plan) {
     return rows * 16 + (op.out.size() > 1 ? 0 : numel(shp(op.in[0])) * 2);
   }
   if (op.type == "mse") return static_cast<int64_t>(ofb_graph_mse_parts()) * 4;
+  if (op.type == "grad_clip") return static_cast<int64_t>(ofb_sqsum_scratch_floats()) * 4;
   return 0;
 }
 
@@ -348,6 +358,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
   } else if (t == "cross_entropy") {
     const int64_t cols = shp(op.in[0]).back(), rows = n(op.in[1]);
     const int64_t ignore = attr_int(op, "ignore_index", -100);
+    const float grad_scale = static_cast<float>(attr_float(op, "grad_scale", 1.0));   // 1 / accumulation steps
     const void* x = addr(op.in[0]);
     const int64_t* y = static_cast<const int64_t*>(addr(op.in[1]));
     void* dx = op.out.size() > 1 ? addr(op.out[1]) : nullptr;
@@ -360,7 +371,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       if (live) total += std::log(sum) + mx - ldb(x, r * cols + y[r]);
       if (dx)
         for (int64_t c = 0; c < cols; ++c)
-          stb(dx, r * cols + c, live ? (std::exp(ldb(x, r * cols + c) - mx) / sum - (c == y[r] ? 1.f : 0.f)) / static_cast<float>(rows) : 0.f);
+          stb(dx, r * cols + c, live ? (std::exp(ldb(x, r * cols + c) - mx) / sum - (c == y[r] ? 1.f : 0.f)) * grad_scale / static_cast<float>(rows) : 0.f);
     }
     static_cast<float*>(addr(op.out[0]))[0] = static_cast<float>(total / static_cast<double>(rows));
   } else if (t == "mse") {
@@ -371,9 +382,25 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       total += d * d;
     }
     static_cast<float*>(addr(op.out[0]))[0] = static_cast<float>(total / static_cast<double>(n(op.in[0])));
+  } else if (t == "grad_clip") {
+    double sq = 0.0, bad = 0.0;
+    for (int g : op.in) {
+      const float* p = static_cast<const float*>(addr(g));
+      for (int64_t e = 0; e < n(g); ++e) {
+        if (!std::isfinite(p[e])) bad += 1.0;
+        else sq += static_cast<double>(p[e]) * p[e];
+      }
+    }
+    const float max_norm = static_cast<float>(attr_float(op, "max_norm", 0.0)), norm = static_cast<float>(std::sqrt(sq));
+    float* out = static_cast<float*>(addr(op.out[0]));
+    out[0] = static_cast<float>(sq);
+    out[1] = static_cast<float>(bad);
+    out[2] = max_norm > 0.f ? std::min(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+    out[3] = norm;
   } else if (t == "adamw_update" || t == "sgd_update") {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
+    const float gscale = attr_int(op, "clip", 0) ? static_cast<const float*>(addr(op.in[static_cast<size_t>(np)]))[2] : 1.f;
     const float lr = train.lr, b1 = train.beta1, b2 = train.beta2, wd = train.weight_decay;
     const float bc1 = 1.f - std::pow(b1, static_cast<float>(train_steps)), bc2 = 1.f - std::pow(b2, static_cast<float>(train_steps));
     for (int64_t i = 0; i < np; ++i) {
@@ -383,7 +410,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       float* s1 = states >= 1 ? static_cast<float*>(addr(op.out[static_cast<size_t>(2 * np + i)])) : nullptr;
       float* s2 = states >= 2 ? static_cast<float*>(addr(op.out[static_cast<size_t>(3 * np + i)])) : nullptr;
       for (int64_t e = 0; e < n(op.in[static_cast<size_t>(i)]); ++e) {
-        float grad = g[e];
+        float grad = g[e] * gscale;
         if (adam) {
           s1[e] = b1 * s1[e] + (1.f - b1) * grad;
           s2[e] = b2 * s2[e] + (1.f - b2) * grad * grad;
@@ -466,13 +493,28 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
     const long long* labels = static_cast<const long long*>(addr(op.in[1]));
     ok(ofb_xent_stats(addr(op.in[0]), labels, stats, static_cast<int>(rows), static_cast<int>(cols), cols, 0, s));
     ok(ofb_xent_grad(addr(op.in[0]), labels, stats, row_loss, dx, static_cast<int>(rows), static_cast<int>(cols), cols, 0,
-                     1.f / static_cast<float>(rows), attr_int(op, "ignore_index", -100), s));
+                     static_cast<float>(attr_float(op, "grad_scale", 1.0)) / static_cast<float>(rows), attr_int(op, "ignore_index", -100), s));
     ok(ofb_graph_sum_f32(row_loss, static_cast<float*>(addr(op.out[0])), rows, 1.f / static_cast<float>(rows), s));
   } else if (t == "mse") {
     ok(ofb_graph_mse(addr(op.in[0]), addr(op.in[1]), static_cast<float*>(addr(op.out[0])), static_cast<float*>(p.workspace), n(op.in[0]), s));
+  } else if (t == "grad_clip") {
+    float* out = static_cast<float*>(addr(op.out[0]));
+    const int64_t ng = static_cast<int64_t>(op.in.size());
+    for (int64_t first = 0; first < ng; first += 48) {
+      const int cnt = static_cast<int>(std::min<int64_t>(48, ng - first));
+      std::vector<void*> grads;
+      std::vector<long long> sizes;
+      for (int i = 0; i < cnt; ++i) {
+        grads.push_back(addr(op.in[static_cast<size_t>(first + i)]));
+        sizes.push_back(n(op.in[static_cast<size_t>(first + i)]));
+      }
+      ok(ofb_multi_tensor_sqsum(cnt, grads.data(), sizes.data(), 0, static_cast<float*>(p.workspace), out, first > 0 ? 1 : 0, s));
+    }
+    ok(ofb_clip_factor(out, static_cast<float>(attr_float(op, "max_norm", 0.0)), out + 2, nullptr, out + 3, s));
   } else if (t == "adamw_update" || t == "sgd_update") {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
+    const float* gscale = attr_int(op, "clip", 0) ? static_cast<const float*>(addr(op.in[static_cast<size_t>(np)])) + 2 : nullptr;
     for (int64_t first = 0; first < np; first += 48) {   // the multi-tensor kernels take 48 tensors per launch
       const int cnt = static_cast<int>(std::min<int64_t>(48, np - first));
       std::vector<void*> grads, copies;
@@ -490,10 +532,10 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
       // learning rate and bias corrections come from the device (refreshed before every step), nothing here depends on the step
       if (adam)
         ok(ofb_multi_tensor_adamw_dev(cnt, grads.data(), masters.data(), copies.data(), s1.data(), s2.data(), sizes.data(), 0, train.beta1,
-                                      train.beta2, train.eps, train.weight_decay, step_scalars, s));
+                                      train.beta2, train.eps, train.weight_decay, step_scalars, gscale, s));
       else
         ok(ofb_multi_tensor_sgd(cnt, grads.data(), masters.data(), copies.data(), states >= 1 ? s1.data() : nullptr, sizes.data(), 0, 0.f,
-                                train.momentum, 0.f, 0, 0, train.weight_decay, 0.f, 0.f, 1.f, step_scalars, nullptr, nullptr, s));
+                                train.momentum, 0.f, 0, 0, train.weight_decay, 0.f, 0.f, 1.f, step_scalars, gscale, nullptr, s));
     }
   } else {
     return false;

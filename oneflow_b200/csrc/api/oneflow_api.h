@@ -97,6 +97,11 @@ struct TrainOptions {
   float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f;
   float weight_decay = 0.f;
   float momentum = 0.f;
+  // > 0: the gradients are scaled by min(1, clip_grad_norm / (global L2 norm + 1e-6)) before the update.
+  float clip_grad_norm = 0.f;
+  // k > 1: every Forward call is one micro-batch; its gradients (of loss / k) are added to persistent fp32 buffers and the
+  // optimizer runs on every k-th call.
+  int accumulation_steps = 1;
 };
 
 class Graph {
@@ -165,6 +170,8 @@ int ofb_api_graph_stats(void* graph, long long* stats_out);
 // Training graphs (oneflow_api::Graph::LoadTraining); optimizer: "adamw" or "sgd".
 void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                   float eps, float weight_decay, float momentum);
+void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
+                                     float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps);
 int ofb_api_graph_num_parameters(void* graph);
 const char* ofb_api_graph_parameter_name(void* graph, int i);
 long long ofb_api_graph_parameter_numel(void* graph, int i);

@@ -241,13 +241,14 @@ OFB_API int ofb_multi_tensor_adamw(int n, void* const* grads, float* const* mast
 }
 
 // The same update with the step-dependent scalars on the device: step[0] = learning rate, step[1] = 1 - beta1^t,
-// step[2] = 1 - beta2^t. Nothing in the launch depends on the step number, so it can be recorded in a CUDA graph.
+// step[2] = 1 - beta2^t; scale_ptr (optional) multiplies the gradients (a clip factor). Nothing in the launch depends on the
+// step number, so it can be recorded in a CUDA graph.
 OFB_API int ofb_multi_tensor_adamw_dev(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,
                                        float* const* vs, const long long* sizes, int grad_is_bf16, float beta1, float beta2, float eps,
-                                       float weight_decay, const float* step, void* stream) {
+                                       float weight_decay, const float* step, const float* scale_ptr, void* stream) {
   if (!step) return fail("multi_tensor_adamw_dev: the step scalars are required");
   return adamw_launch(n, grads, masters, copies, ms, vs, sizes, grad_is_bf16, 0.f, beta1, beta2, eps, weight_decay, 0.f, 1.f, 1.f, 1.f, step,
-                      nullptr, nullptr, step + 1, stream);
+                      scale_ptr, nullptr, step + 1, stream);
 }
 
 static int adamw_launch(int n, void* const* grads, float* const* masters, void* const* copies, float* const* ms,

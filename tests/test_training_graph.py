@@ -313,3 +313,76 @@ def test_cpp_program_trains_through_the_api_and_saves_a_loadable_directory(tmp_p
     saved_loss = E.InferenceGraph(str(tmp_path / "out"), device=-1).run(x.numpy(), y.numpy())[0][0]
     assert abs(saved_loss - ours[12]) < 2e-2 * max(ours[12], 0.05)           # weights were stored as bf16
     g.close()
+
+
+def test_gradient_clipping_matches_clip_grad_norm(tmp_path):
+    torch.manual_seed(9)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float() * 3, torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=1.0, clip_grad_norm=0.25)
+    assert "op grad_clip" in g.dump() and "clip=1" in g.dump()
+    before = g.parameters()
+    g.step(x.numpy(), y.numpy())
+    after = g.parameters()
+    m(x, y).backward()
+    total = torch.nn.utils.clip_grad_norm_(m.parameters(), 0.25)
+    assert float(total) > 0.25                                     # the clip is active
+    ours = np.sqrt(sum(float(((before[k] - after[k]) ** 2).sum()) for k in before))
+    assert abs(ours - 0.25) < 0.01                                 # the applied gradient has the clipped norm
+    for name, p in m.named_parameters():
+        ref = p.grad.numpy().reshape(-1)
+        assert np.abs((before[name] - after[name]) - ref).max() <= 3e-2 * (np.abs(ref).max() + 1e-6), name
+    g.close()
+
+
+def test_gradient_accumulation_over_two_micro_batches_equals_one_large_batch(tmp_path):
+    torch.manual_seed(10)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d_full = E.export_graph(m, (x, y), str(tmp_path / "full"), fuse=False)
+    d_half = E.export_graph(m, (x[:12], y[:12]), str(tmp_path / "half"), fuse=False)
+    full = E.TrainingGraph(d_full, device=-1, optimizer="adamw", lr=1e-2)
+    acc = E.TrainingGraph(d_half, device=-1, optimizer="adamw", lr=1e-2, accumulation_steps=2)
+    text = acc.dump()
+    assert "when=first" in text and "when=last" in text and "grad_scale=0.5" in text
+    start = acc.parameters()
+    for step in range(3):
+        lf = full.step(x.numpy(), y.numpy())
+        l0 = acc.step(x[:12].numpy(), y[:12].numpy())
+        if step == 0:
+            mid = acc.parameters()
+            assert all(np.array_equal(start[k], mid[k]) for k in start)      # no update after the first micro-batch
+            with pytest.raises(RuntimeError, match="save between steps"):
+                acc.save(str(tmp_path / "never"))
+        l1 = acc.step(x[12:].numpy(), y[12:].numpy())
+        assert abs(0.5 * (l0 + l1) - lf) < 2e-2 * max(abs(lf), 0.1)
+    assert acc.steps == 3 and full.steps == 3
+    pf, pa = full.parameters(), acc.parameters()
+    for k in pf:
+        assert np.abs(pf[k] - pa[k]).max() < 1e-2, k
+    full.close()
+    acc.close()
+
+
+@pytest.mark.gpu
+def test_clipping_and_accumulation_on_the_gpu_runtime_match_the_host_runtime(tmp_path):
+    """Every kind of call (first / last micro-batch of a step) is recorded as a CUDA graph of its own; the clip factor and the
+    step scalars are read on the device, so the recordings stay valid from one step to the next."""
+    torch.manual_seed(11)
+    m = _bf16_weights(TiedLM(d=128, heads=2, vocab=256, seq=128))
+    ids, tgt = torch.randint(0, 256, (4, 128)), torch.randint(0, 256, (4, 128))
+    d = E.export_graph(m, (ids[:2], tgt[:2]), str(tmp_path), fuse=False)
+    kw = dict(optimizer="adamw", lr=3e-3, clip_grad_norm=1.0, accumulation_steps=2)
+    host, dev = E.TrainingGraph(d, device=-1, **kw), E.TrainingGraph(d, device=0, **kw)
+    for _ in range(3):
+        for lo in (0, 2):
+            a = host.step(ids[lo:lo + 2].numpy(), tgt[lo:lo + 2].numpy())
+            b = dev.step(ids[lo:lo + 2].numpy(), tgt[lo:lo + 2].numpy())
+            assert abs(a - b) < 5e-2 * max(abs(a), 1.0)
+    assert dev.steps == 3 and dev.stats()["graph_replays"] == 4          # calls 3..6: both kinds replay from their second run on
+    ph, pd = host.parameters(), dev.parameters()
+    for k in ph:
+        assert np.abs(ph[k] - pd[k]).max() < 2e-2, k
+    host.close()
+    dev.close()
