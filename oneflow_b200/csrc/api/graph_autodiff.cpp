@@ -360,6 +360,8 @@ void Builder::run() {
   uattr.insert(when.begin(), when.end());
   emit(adam ? "adamw_update" : "sgd_update", update_in, outs, uattr);
 
+  ir.n_forward_ops = n_ops;
+  ir.recompute_cheap = opt.recompute_cheap_activations;
   for (auto& op : out_ops) ir.ops.push_back(std::move(op));
   ir.training = true;
 }

@@ -43,6 +43,8 @@ struct IR {
   bool training = false;
   std::vector<int> trainable;   // parameter roots that get updated, in export order
   std::vector<int> masters;     // their fp32 master-weight state tensors
+  int n_forward_ops = 0;        // operators before the first backward one
+  bool recompute_cheap = false; // asks the recompute pass to run
   std::vector<std::pair<std::string, int>> pass_report;   // rewriting passes that ran and how often each fired
 };
 

@@ -8,6 +8,10 @@
 //   fuse_activation_backward  matmul -> unary_bwd(pre-act, .)  =>  matmul whose epilogue multiplies by act'(pre-activation):
 //                                                                   the data-gradient GEMM of the NEXT layer produces the
 //                                                                   gradient w.r.t. the pre-activation directly
+//   recompute_cheap_activations (training, on request)  an element-wise operator or LayerNorm of the forward pass whose output
+//                             the backward pass reads, and whose inputs are kept for the backward pass anyway, is run
+//                             again right before its first backward reader; the backward readers use the copy, so the
+//                             original dies with its last forward reader (activation checkpointing for the cheap part)
 //   drop_dead_operators       operators none of whose outputs is read by an operator or returned
 //
 // ONEFLOW_API_PASSES=0 switches all of them off (the unfused plan is the reference the tests compare with).
@@ -60,6 +64,75 @@ struct Touches {
 
 const char* act_name(int64_t fn) { return fn == 1 ? "gelu" : fn == 2 ? "gelu_tanh" : fn == 3 ? "relu" : nullptr; }
 
+bool recompute_cheap_activations(IR& ir) {
+  const View v(ir);
+  const Touches tc(ir, v);
+  const int F = ir.n_forward_ops;
+  auto kept_for_backward = [&](int root, int except_op) {
+    const int kind = ir.tensors[static_cast<size_t>(root)].kind;
+    if (kind == 0 || kind == 1) return true;   // graph inputs and parameters are there anyway
+    for (int r : tc.readers[static_cast<size_t>(root)])
+      if (r >= F && r != except_op) return true;
+    return false;
+  };
+  for (int i = 0; i < F && i < static_cast<int>(ir.ops.size()); ++i) {
+    const OpDef op = ir.ops[static_cast<size_t>(i)];
+    if (op.type != "unary" && op.type != "binary" && op.type != "layer_norm") continue;
+    const int R = v.root(op.out[0]);
+    if (!v.whole(op.out[0]) || tc.returned.count(R) || tc.writers[static_cast<size_t>(R)].size() != 1) continue;
+    int first_reader = -1;
+    for (int r : tc.readers[static_cast<size_t>(R)])
+      if (r >= F && (first_reader < 0 || r < first_reader)) first_reader = r;
+    if (first_reader < 0) continue;
+    bool ok = true;
+    for (int t : op.in) {
+      if (t < 0) continue;
+      const int r = v.root(t);
+      if (r == R || !kept_for_backward(r, -1)) ok = false;
+      for (int w : tc.writers[static_cast<size_t>(r)])
+        if (w > i && w < first_reader) ok = false;   // the input would have changed by then
+    }
+    if (!ok) continue;
+    // the copy: same operator, fresh outputs
+    auto fresh_like = [&](int t) {
+      TensorDef root = ir.tensors[static_cast<size_t>(v.root(t))];
+      root.kind = 2;
+      root.file.clear();
+      root.name.clear();
+      ir.tensors.push_back(root);
+      const int rid = static_cast<int>(ir.tensors.size()) - 1;
+      TensorDef al = ir.tensors[static_cast<size_t>(t)];
+      if (al.alias_of < 0) return rid;
+      al.alias_of = rid;
+      al.alias_off = v.offset(t);
+      ir.tensors.push_back(al);
+      return static_cast<int>(ir.tensors.size()) - 1;
+    };
+    OpDef copy = op;
+    for (int& t : copy.out) t = fresh_like(t);
+    const int new_root = View(ir).root(copy.out[0]);
+    // backward readers switch to the copy
+    std::map<int, int> renamed;
+    for (size_t j = static_cast<size_t>(F); j < ir.ops.size(); ++j)
+      for (int& t : ir.ops[j].in) {
+        if (t < 0 || View(ir).root(t) != R) continue;
+        auto it = renamed.find(t);
+        if (it == renamed.end()) {
+          TensorDef al = ir.tensors[static_cast<size_t>(t)];
+          const int64_t off = View(ir).offset(t);
+          al.alias_of = new_root;
+          al.alias_off = off;
+          ir.tensors.push_back(al);
+          it = renamed.emplace(t, static_cast<int>(ir.tensors.size()) - 1).first;
+        }
+        t = it->second;
+      }
+    ir.ops.insert(ir.ops.begin() + first_reader, copy);
+    return true;
+  }
+  return false;
+}
+
 bool fuse_activation_forward(IR& ir) {
   const View v(ir);
   const Touches tc(ir, v);
@@ -74,8 +147,7 @@ bool fuse_activation_forward(IR& ir) {
     for (int r : tc.readers[static_cast<size_t>(h)]) {
       const OpDef& o = ir.ops[static_cast<size_t>(r)];
       if (o.type == "unary" && act_op < 0 && act_name(attr_int(o, "fn", 0)) && v.whole(o.in[0]) && v.root(o.out[0]) != h) act_op = r;
-      else if (o.type == "unary_bwd" && v.root(o.in[0]) == h && v.root(o.in[1]) != h) saved = true;   // reads the pre-activation
-      else if (o.type == "matmul" && o.in.size() == 3 && v.root(o.in[2]) == h && v.root(o.in[0]) != h && v.root(o.in[1]) != h) saved = true;
+      else if (r > static_cast<int>(i)) saved = true;   // another reader of the pre-activation (backward operators, recomputed copies): keep it stored
       else other = true;
     }
     if (act_op < 0 || other || act_op < static_cast<int>(i)) continue;
@@ -145,6 +217,11 @@ std::vector<std::pair<std::string, int>> run_graph_passes(IR& ir) {
     bool (*fn)(IR&);
   };
   // backward first: the forward pass must see which pre-activations a fused data-gradient GEMM still reads
+  if (ir.training && ir.recompute_cheap) {
+    int fired = 0;
+    while (fired < 100000 && recompute_cheap_activations(ir)) ++fired;
+    report.emplace_back("recompute_cheap_activations", fired);
+  }
   const Pass passes[] = {{"fuse_activation_backward", fuse_activation_backward},
                          {"fuse_activation_forward", fuse_activation_forward},
                          {"drop_dead_operators", drop_dead_operators}};

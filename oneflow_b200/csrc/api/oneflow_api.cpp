@@ -249,12 +249,18 @@ void ofb_api_graph_free(void* g) { delete static_cast<Graph*>(g); }
 
 void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2, float eps,
                                      float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps) {
+  return ofb_api_graph_load_training_flags(dir, device, n_streams, optimizer, lr, beta1, beta2, eps, weight_decay, momentum, clip_grad_norm,
+                                           accumulation_steps, 0);
+}
+void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2, float eps,
+                                        float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps, int flags) {
   try {
     oneflow_api::TrainOptions o;
     o.optimizer = optimizer ? optimizer : "adamw";
     o.lr = lr; o.beta1 = beta1; o.beta2 = beta2; o.eps = eps; o.weight_decay = weight_decay; o.momentum = momentum;
     o.clip_grad_norm = clip_grad_norm;
     o.accumulation_steps = accumulation_steps;
+    o.recompute_cheap_activations = (flags & 1) != 0;
     return new Graph(Graph::LoadTraining(dir, o, device, n_streams));
   } catch (const std::exception& e) {
     oneflow_api::detail::g_error = e.what();

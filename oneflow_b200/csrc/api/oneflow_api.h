@@ -102,6 +102,9 @@ struct TrainOptions {
   // k > 1: every Forward call is one micro-batch; its gradients (of loss / k) are added to persistent fp32 buffers and the
   // optimizer runs on every k-th call.
   int accumulation_steps = 1;
+  // Activation checkpointing for the cheap operators: outputs of element-wise operators and LayerNorms that only the
+  // backward pass still needs are not kept; the backward pass recomputes them from their (kept) inputs.
+  bool recompute_cheap_activations = false;
 };
 
 class Graph {
@@ -172,6 +175,9 @@ void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, co
                                   float eps, float weight_decay, float momentum);
 void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                      float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps);
+// bit 0 of flags: recompute cheap activations in the backward pass
+void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
+                                        float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps, int flags);
 int ofb_api_graph_num_parameters(void* graph);
 const char* ofb_api_graph_parameter_name(void* graph, int i);
 long long ofb_api_graph_parameter_numel(void* graph, int i);
