@@ -56,7 +56,7 @@ std::vector<int> diff_slots(const OpDef& op) {
   if (t == "matmul" || t == "binary" || t == "mse") return {0, 1};
   if (t == "layer_norm" || t == "attention") return {0, 1, 2};
   if (t == "embedding") return {1};
-  if (t == "unary" || t == "softmax" || t == "copy" || t == "cross_entropy") return {0};
+  if (t == "unary" || t == "softmax" || t == "copy" || t == "cross_entropy" || t == "dropout") return {0};
   return {};
 }
 
@@ -545,6 +545,12 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
     const int x = in(0);
     Target tg = target_for(x, false);
     emit("unary_bwd", {x, dy}, {tg.out}, {{"fn", attr_str(op, "fn", "0")}, {"alpha", attr_str(op, "alpha", "1.0")}});
+    finish(tg);
+  } else if (t == "dropout") {
+    // the same mask (same seed, call and operator index) applied to the gradient
+    const int x = in(0);
+    Target tg = target_for(x, false);
+    emit("dropout", {dy}, {tg.out}, {{"p", attr_str(op, "p", "0.5")}, {"index", attr_str(op, "index", "0")}});
     finish(tg);
   } else if (t == "softmax") {
     const int x = in(0);

@@ -160,6 +160,9 @@ struct Graph::Impl {
   // memory; the update operator reads them on the device, so a recorded step stays valid from one step to the next
   float* step_scalars = nullptr;
   float* step_scalars_host = nullptr;
+  // dropout: number of Forward calls so far; on the GPU it follows the four floats above as one 64-bit value
+  uint64_t call_counter = 0;
+  const unsigned long long* call_counter_device() const { return reinterpret_cast<const unsigned long long*>(step_scalars + 4); }
   std::mutex run_mu;
   // per call
   std::vector<void*> bound;                    // per root: address of inputs for the running call

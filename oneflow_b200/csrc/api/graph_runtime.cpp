@@ -907,8 +907,8 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
     impl->train = *train;
     if (device >= 0) {
       check_cuda(cudaSetDevice(device), "cudaSetDevice");
-      check_cuda(cudaMalloc(&impl->step_scalars, 4 * sizeof(float)), "cudaMalloc");
-      check_cuda(cudaMallocHost(&impl->step_scalars_host, 4 * sizeof(float)), "cudaMallocHost");
+      check_cuda(cudaMalloc(&impl->step_scalars, 8 * sizeof(float)), "cudaMalloc");
+      check_cuda(cudaMallocHost(&impl->step_scalars_host, 8 * sizeof(float)), "cudaMallocHost");
     }
   }
   impl->ir.pass_report = run_graph_passes(impl->ir);
@@ -976,6 +976,14 @@ std::vector<float> Graph::parameter(int i) const {
 void Graph::set_learning_rate(float lr) {
   std::lock_guard<std::mutex> g(impl_->run_mu);
   impl_->train.lr = lr;
+}
+void Graph::set_seed(uint64_t seed) {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  impl_->train.seed = seed;
+  for (int k = 0; k < 4; ++k) {   // the seed is a launch argument of the recorded dropout kernels: record again
+    if (impl_->graph_exec[k]) cudaGraphExecDestroy(impl_->graph_exec[k]);
+    impl_->graph_exec[k] = nullptr;
+  }
 }
 int64_t Graph::steps() const {
   std::lock_guard<std::mutex> g(impl_->run_mu);
@@ -1141,13 +1149,15 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     const int k = std::max(1, im.train.accumulation_steps);
     im.call_kind = (im.micro_step == 0 ? 1 : 0) | (im.micro_step == k - 1 ? 2 : 0);
     if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
+    ++im.call_counter;                          // dropout masks are a function of the call number
     if (im.device >= 0) {
       im.step_scalars_host[0] = im.train.lr;
       im.step_scalars_host[1] = 1.f - std::pow(im.train.beta1, static_cast<float>(im.train_steps));
       im.step_scalars_host[2] = 1.f - std::pow(im.train.beta2, static_cast<float>(im.train_steps));
       im.step_scalars_host[3] = 0.f;
+      std::memcpy(im.step_scalars_host + 4, &im.call_counter, 8);
       // on stream 0, which is synchronised below before anything of the step starts
-      check_cuda(cudaMemcpyAsync(im.step_scalars, im.step_scalars_host, 4 * sizeof(float), cudaMemcpyHostToDevice, im.streams[0]), "cudaMemcpyAsync");
+      check_cuda(cudaMemcpyAsync(im.step_scalars, im.step_scalars_host, 8 * sizeof(float), cudaMemcpyHostToDevice, im.streams[0]), "cudaMemcpyAsync");
     }
   }
   bool replayed = false;

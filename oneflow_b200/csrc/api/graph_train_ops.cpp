@@ -14,6 +14,8 @@
 //   embedding_bwd   (ids, dy) -> table gradient (fp32, scatter-add)
 //   cross_entropy   (logits, targets) -> mean loss [, d loss / d logits]
 //   mse             (a, b) -> mean squared difference
+//   dropout         y = x * keep / (1 - p); the mask is a function of (seed, call number, operator index, element), so the
+//                   backward operator is the same operator applied to the gradient and nothing is stored
 //   grad_clip       gradients -> {sum of squares, non-finite count, clip factor, global norm}
 //   adamw_update / sgd_update   gradients [, clip] -> parameters (bf16), fp32 master weights and optimizer state, in place
 // Operators marked when=first / when=last run only on the first / last micro-batch of an optimizer step (gradient accumulation).
@@ -24,6 +26,7 @@
 #include <cstring>
 #include <stdexcept>
 
+#include "../common/dropout_hash.h"
 #include "../kernels/ofb_kernels.h"
 #include "graph_impl.h"
 
@@ -31,6 +34,8 @@ extern "C" {
 int ofb_graph_unary_bwd(const void* x, const void* dy, void* dx, long long n, int fn, float alpha, void* stream);
 int ofb_graph_strided_acc(const void* x, int x_dtype, void* y, int y_dtype, int ndim, const long long* shape, const long long* in_strides,
                           long long in_offset, const long long* out_strides, long long out_offset, void* stream);
+int ofb_graph_dropout(const void* x, void* y, long long n, unsigned long long seed, const unsigned long long* counter, unsigned int op_index,
+                      float p, void* stream);
 int ofb_graph_mse_parts(void);
 int ofb_graph_mse(const void* a, const void* b, float* loss, float* scratch, long long n, void* stream);
 int ofb_graph_sum_f32(const float* x, float* out, long long n, float scale, void* stream);
@@ -136,6 +141,10 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
   } else if (t == "column_sum") {
     need(op.in.size() == 1 && shp(op.in[0]).size() == 2 && dt(op.in[0]) == DType::kBFloat16, "a [rows, cols] bf16 input");
     need(dt(op.out[0]) == DType::kFloat && n(op.out[0]) == shp(op.in[0])[1], "an fp32 output with one element per column");
+  } else if (t == "dropout") {
+    need(op.in.size() == 1 && op.out.size() == 1 && n(op.in[0]) == n(op.out[0]) && dt(op.in[0]) == DType::kBFloat16 && dt(op.out[0]) == DType::kBFloat16,
+         "one bf16 input and output of the same length");
+    need(attr_float(op, "p", 0.5) >= 0.0 && attr_float(op, "p", 0.5) < 1.0, "p must be in [0, 1)");
   } else if (t == "unary_bwd") {
     need(op.in.size() == 2 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]), "x, dy and dx of the same length");
   } else if (t == "layer_norm_bwd") {
@@ -245,6 +254,18 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       float acc = 0.f;
       for (int64_t r = 0; r < rows; ++r) acc += ldb(x, r * cols + c);
       y[c] += acc;
+    }
+  } else if (t == "dropout" && !ir.training) {
+    std::memcpy(addr(op.out[0]), addr(op.in[0]), static_cast<size_t>(n(op.in[0]) * 2));   // evaluation: the identity
+  } else if (t == "dropout") {
+    const float p = static_cast<float>(attr_float(op, "p", 0.5)), scale = 1.f / (1.f - p);
+    const uint64_t base = ofb::dropout_base(train.seed, call_counter, static_cast<uint32_t>(attr_int(op, "index", 0)));
+    const uint32_t thr = ofb::dropout_threshold(p);
+    const void* x = addr(op.in[0]);
+    void* y = addr(op.out[0]);
+    for (int64_t i = 0; i < n(op.in[0]); ++i) {
+      const bool keep = ofb::dropout_keep(ofb::dropout_draw(base, static_cast<uint64_t>(i >> 2)), static_cast<int>(i & 3), thr);
+      stb(y, i, keep ? ldb(x, i) * scale : 0.f);
     }
   } else if (t == "unary_bwd") {
     const int fn = static_cast<int>(attr_int(op, "fn", 0));
@@ -457,6 +478,11 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
                              attr_int(op, "in_offset", 0), c.data(), attr_int(op, "out_offset", 0), s));
   } else if (t == "column_sum") {
     ok(ofb_column_sum(addr(op.in[0]), static_cast<float*>(addr(op.out[0])), static_cast<int>(shp(op.in[0])[0]), static_cast<int>(shp(op.in[0])[1]), s));
+  } else if (t == "dropout" && !ir.training) {
+    check_cuda(cudaMemcpyAsync(addr(op.out[0]), addr(op.in[0]), static_cast<size_t>(n(op.in[0]) * 2), cudaMemcpyDeviceToDevice, s), "cudaMemcpyAsync");
+  } else if (t == "dropout") {
+    ok(ofb_graph_dropout(addr(op.in[0]), addr(op.out[0]), n(op.in[0]), train.seed, call_counter_device(), static_cast<unsigned int>(attr_int(op, "index", 0)),
+                         static_cast<float>(attr_float(op, "p", 0.5)), s));
   } else if (t == "unary_bwd") {
     ok(ofb_graph_unary_bwd(addr(op.in[0]), addr(op.in[1]), addr(op.out[0]), n(op.in[0]), static_cast<int>(attr_int(op, "fn", 0)),
                            static_cast<float>(attr_float(op, "alpha", 1.0)), s));

@@ -322,6 +322,10 @@ int ofb_api_graph_restore(void* g, const char* dir) {
     return -1;
   }
 }
+int ofb_api_graph_set_seed(void* g, unsigned long long seed) {
+  static_cast<Graph*>(g)->set_seed(seed);
+  return 0;
+}
 long long ofb_api_graph_steps(void* g) { return static_cast<Graph*>(g)->steps(); }
 long long ofb_api_graph_dump(void* g, char* buf, long long cap) {
   const std::string text = static_cast<Graph*>(g)->dump();

@@ -105,6 +105,9 @@ struct TrainOptions {
   // Activation checkpointing for the cheap operators: outputs of element-wise operators and LayerNorms that only the
   // backward pass still needs are not kept; the backward pass recomputes them from their (kept) inputs.
   bool recompute_cheap_activations = false;
+  // Seed of the dropout operators (graphs exported in training mode). The mask of an operator is a function of (seed,
+  // number of the call, operator): every call draws new masks, a run with the same seed draws the same sequence.
+  uint64_t seed = 0;
 };
 
 class Graph {
@@ -142,6 +145,7 @@ class Graph {
   void Save(const std::string& dir) const;
   void Restore(const std::string& dir);
   void set_learning_rate(float lr);
+  void set_seed(uint64_t seed);
   int64_t steps() const;
   std::string dump() const;
   struct Impl;
@@ -183,6 +187,7 @@ const char* ofb_api_graph_parameter_name(void* graph, int i);
 long long ofb_api_graph_parameter_numel(void* graph, int i);
 int ofb_api_graph_parameter_read(void* graph, int i, float* out);
 int ofb_api_graph_set_lr(void* graph, float lr);
+int ofb_api_graph_set_seed(void* graph, unsigned long long seed);
 int ofb_api_graph_save(void* graph, const char* dir);
 int ofb_api_graph_restore(void* graph, const char* dir);
 long long ofb_api_graph_steps(void* graph);

@@ -9,12 +9,42 @@
 // oneflow/user/kernels/reduce_kernel.cpp.
 #include <cuda_bf16.h>
 
+#include "../common/dropout_hash.h"
 #include "../common/host_utils.h"
 #include "ofb_kernels.h"
 
 namespace ofb {
 
 using bf16 = __nv_bfloat16;
+
+// y = x * keep / (1 - p); the call counter is read from device memory so that a recorded launch draws a new mask on every
+// replay. 8 elements (two draws) per thread and iteration.
+__global__ void gtr_dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, unsigned long long seed,
+                                   const unsigned long long* __restrict__ counter, unsigned int op_index, float p, bool vec) {
+  const uint64_t base = dropout_base(seed, *counter, op_index);
+  const uint32_t thr = dropout_threshold(p);
+  const float scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long groups8 = (n + 7) / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups8; i += stride) {
+    const uint64_t d0 = dropout_draw(base, 2 * i), d1 = dropout_draw(base, 2 * i + 1);
+    if (vec && i * 8 + 8 <= n) {
+      uint4 q = reinterpret_cast<const uint4*>(x)[i];
+      bf16* e = reinterpret_cast<bf16*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool keep = dropout_keep(j < 4 ? d0 : d1, j & 3, thr);
+        e[j] = __float2bfloat16(keep ? __bfloat162float(e[j]) * scale : 0.f);
+      }
+      reinterpret_cast<uint4*>(y)[i] = q;
+    } else {
+      for (int j = 0; j < 8 && i * 8 + j < n; ++j) {
+        const bool keep = dropout_keep(j < 4 ? d0 : d1, j & 3, thr);
+        y[i * 8 + j] = __float2bfloat16(keep ? __bfloat162float(x[i * 8 + j]) * scale : 0.f);
+      }
+    }
+  }
+}
 
 // d fn(x) / dx for the function codes of ofb_graph_unary
 __device__ __forceinline__ float gtr_unary_grad(float x, int fn, float alpha) {
@@ -150,6 +180,19 @@ static unsigned gtr_grid(long long work) {
 }  // namespace ofb
 
 using namespace ofb;
+
+// y = dropout(x) on n bf16 elements with the counter-based mask of common/dropout_hash.h; `counter` points to the call
+// counter in device memory.
+OFB_API int ofb_graph_dropout(const void* x, void* y, long long n, unsigned long long seed, const unsigned long long* counter,
+                              unsigned int op_index, float p, void* stream) {
+  if (n <= 0) return 0;
+  if (!counter) return fail("graph_dropout: the call counter is required");
+  if (!(p >= 0.f && p <= 1.f)) return fail("graph_dropout: p must be in [0, 1]");
+  const bool vec = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15);
+  gtr_dropout_kernel<<<gtr_grid((n + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, seed, counter, op_index, p, vec);
+  OFB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 // dx = dy * fn'(x) on n bf16 elements; fn and alpha as in ofb_graph_unary.
 OFB_API int ofb_graph_unary_bwd(const void* x, const void* dy, void* dx, long long n, int fn, float alpha, void* stream) {

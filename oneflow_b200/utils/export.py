@@ -119,6 +119,7 @@ class _GraphEmitter(torch.fx.Interpreter):
         self.alias_cache = {}
         self.copy_cache = {}
         # parameters that own their whole storage and take gradients: named in the IR, which makes them trainable there
+        self.n_dropout = 0
         self.param_names = {}
         for name, prm in gm.named_parameters():
             if prm.requires_grad and prm.dtype.is_floating_point and prm.storage_offset() == 0 and \
@@ -339,6 +340,14 @@ class _GraphEmitter(torch.fx.Interpreter):
                    kv_stride=ks)
         return y_ir.transpose(1, 2)
 
+    def _dropout(self, x, y, p):
+        """Only reached when the module is traced in training mode: in evaluation mode dropout hands its input through."""
+        ix = self._operand(x)
+        out, y = self._result(y)
+        self._emit("dropout", [ix], out, p=repr(float(p)), index=self.n_dropout)
+        self.n_dropout += 1
+        return y
+
     def _scalar_result(self, y):
         """A fresh fp32 scalar activation (loss values): (IR id, the tensor that stands for the node)."""
         real = y.detach().to(torch.float32).reshape(1).clone()
@@ -417,6 +426,10 @@ class _GraphEmitter(torch.fx.Interpreter):
             return y
         if not inplace and any(y.untyped_storage().data_ptr() == t.untyped_storage().data_ptr() for t in flat):
             return y                    # a view of a traced tensor (or the tensor itself: dropout in eval mode, .to of the same dtype)
+        if isinstance(module, torch.nn.Dropout) or (module is None and name == "dropout"):
+            p = module.p if module is not None else (a[1] if len(a) > 1 else kw.get("p", 0.5))
+            training = module.training if module is not None else (a[2] if len(a) > 2 else kw.get("training", True))
+            return self._dropout(a[0], y, p) if training and p > 0 else a[0]
         if module is not None:
             m = module
             if isinstance(m, torch.nn.Linear):
@@ -546,14 +559,16 @@ def _fold(ops, outputs, tensor_lines):
     return ops
 
 
-def export_graph(module, example_inputs, directory, fuse=True):
+def export_graph(module, example_inputs, directory, fuse=True, train_mode=False):
     """Records ``module(*example_inputs)`` as an operator graph with the example's shapes and writes it for the C++ runtime.
-    Parameters are stored as bf16 (integer tables as int64). Returns the directory."""
+    Parameters are stored as bf16 (integer tables as int64). Returns the directory. The module is traced in evaluation mode
+    unless ``train_mode`` is set; in training mode dropout layers become dropout operators (a training graph draws a new mask
+    on every step; loaded for inference they hand their input through)."""
     os.makedirs(directory, exist_ok=True)
     if torch.is_tensor(example_inputs):
         example_inputs = (example_inputs,)
     was_training = module.training
-    module.eval()
+    module.train(bool(train_mode))
     try:
         gm = module if isinstance(module, torch.fx.GraphModule) else torch.fx.symbolic_trace(module)
         em = _GraphEmitter(gm, directory)
@@ -650,7 +665,7 @@ class TrainingGraph(InferenceGraph):
     recomputes them in the backward pass (less activation memory, a few more memory-bound kernels)."""
 
     def __init__(self, directory, device=0, n_streams=2, optimizer="adamw", lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
-                 momentum=0.0, clip_grad_norm=0.0, accumulation_steps=1, recompute_cheap_activations=False):
+                 momentum=0.0, clip_grad_norm=0.0, accumulation_steps=1, recompute_cheap_activations=False, seed=0):
         self._load = lambda lib: lib.ofb_api_graph_load_training_flags(
             directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams), optimizer.encode(), ctypes.c_float(lr),
             ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_float(momentum),
@@ -661,6 +676,8 @@ class TrainingGraph(InferenceGraph):
         lib.ofb_api_graph_parameter_numel.restype = ctypes.c_longlong
         lib.ofb_api_graph_steps.restype = ctypes.c_longlong
         lib.ofb_api_graph_dump.restype = ctypes.c_longlong
+        if seed:
+            self.set_seed(seed)
 
     def step(self, *inputs):
         outs = self.run(*inputs)
@@ -669,6 +686,10 @@ class TrainingGraph(InferenceGraph):
     @property
     def steps(self):
         return int(self.lib.ofb_api_graph_steps(ctypes.c_void_p(self.h)))
+
+    def set_seed(self, seed):
+        """Seed of the dropout operators: the mask is a function of (seed, number of the call, operator, element)."""
+        self.lib.ofb_api_graph_set_seed(ctypes.c_void_p(self.h), ctypes.c_ulonglong(seed))
 
     def set_lr(self, lr):
         self.lib.ofb_api_graph_set_lr(ctypes.c_void_p(self.h), ctypes.c_float(lr))

@@ -414,3 +414,94 @@ def test_recomputing_cheap_activations_saves_memory_and_keeps_the_trajectory(tmp
         assert np.abs(pl[k] - pp[k]).max() < 2e-2 * (np.abs(pp[k]).max() + 1e-3), k
     plain.close()
     lean.close()
+
+
+def _dropout_keep(seed, call, op_index, n, p):
+    """The runtime's counter-based mask (csrc/common/dropout_hash.h) restated with numpy's wrapping 64-bit arithmetic."""
+    u = np.uint64
+
+    def mix(z):
+        z = z + u(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> u(30))) * u(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> u(27))) * u(0x94D049BB133111EB)
+        return z ^ (z >> u(31))
+
+    with np.errstate(over="ignore"):
+        base = mix(u(seed) ^ mix(u(call) * u(0xD1B54A32D192ED03) + u(op_index)))
+        idx = np.arange(n, dtype=np.uint64)
+        draw = mix(base + (idx >> u(2)) * u(0x9E3779B97F4A7C15))
+        lane = (draw >> (u(16) * (idx & u(3)))) & u(0xFFFF)
+    return lane >= u(int(p * 65536.0))
+
+
+def test_dropout_draws_a_new_mask_every_call_and_backward_uses_the_same_one(tmp_path):
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.drop, self.fc2 = nn.Linear(32, 64), nn.Dropout(0.25), nn.Linear(64, 16)
+
+        def forward(self, x, y):
+            return F.cross_entropy(self.fc2(F.gelu(self.drop(self.fc1(x)))), y)
+
+    torch.manual_seed(13)
+    m = _bf16_weights(Net())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False, train_mode=True)
+    assert "op dropout" in open(os.path.join(d, "graph.txt")).read()
+    assert m.training                                                   # the caller's mode is put back
+    keep1 = _dropout_keep(77, 1, 0, 24 * 64, 0.25)
+    assert 0.65 < keep1.mean() < 0.85 and not np.array_equal(keep1, _dropout_keep(77, 2, 0, 24 * 64, 0.25))
+    g = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=1.0, seed=77)
+    assert g.dump().count("op dropout") == 2                             # forward, and the same operator on the gradient
+    before = g.parameters()
+    loss1 = g.step(x.numpy(), y.numpy())
+    after = g.parameters()
+    # the same computation in PyTorch with the mask of call 1 written out
+    mask = torch.from_numpy(keep1.reshape(24, 64).astype(np.float32)) / 0.75
+    ref = F.cross_entropy(m.fc2(F.gelu(m.fc1(x) * mask)), y)
+    ref.backward()
+    assert abs(loss1 - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    for name, p in m.named_parameters():
+        r = p.grad.numpy().reshape(-1)
+        assert np.abs((before[name] - after[name]) - r).max() <= 3e-2 * (np.abs(r).max() + 1e-6), name
+    # the second call draws another mask: with lr 0 the weights stay, the loss changes
+    g.set_lr(0.0)
+    a, b = g.step(x.numpy(), y.numpy()), g.step(x.numpy(), y.numpy())
+    assert a != b
+    # loaded for inference the dropout operators hand their input through
+    m.eval()
+    saved = g.save(str(tmp_path / "saved"))
+    out = E.InferenceGraph(saved, device=-1).run(x.numpy(), y.numpy())[0][0]
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            p.copy_(torch.from_numpy(g.parameters()[name]).view_as(p))
+        assert abs(out - float(m(x, y))) < 3e-2 * max(float(m(x, y)), 0.1)
+    g.close()
+
+
+@pytest.mark.gpu
+def test_dropout_on_the_gpu_runtime_drops_the_same_elements_as_the_host_runtime(tmp_path):
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.drop, self.fc2 = nn.Linear(128, 256), nn.Dropout(0.5), nn.Linear(256, 64)
+
+        def forward(self, x, y):
+            return F.cross_entropy(self.fc2(self.drop(F.gelu(self.fc1(x)))), y)
+
+    torch.manual_seed(14)
+    m = _bf16_weights(Net())
+    x, y = torch.randn(256, 128).bfloat16().float(), torch.randint(0, 64, (256,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False, train_mode=True)
+    host = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.05, seed=5)
+    dev = E.TrainingGraph(d, device=0, optimizer="sgd", lr=0.05, seed=5)
+    other = E.TrainingGraph(d, device=0, optimizer="sgd", lr=0.05, seed=6)
+    lh = [host.step(x.numpy(), y.numpy()) for _ in range(4)]
+    ld = [dev.step(x.numpy(), y.numpy()) for _ in range(4)]
+    lo = [other.step(x.numpy(), y.numpy()) for _ in range(4)]
+    assert dev.stats()["graph_replays"] == 3                  # replays read the call number on the device: new masks each time
+    for a, b in zip(lh, ld):
+        assert abs(a - b) < 1e-2 * max(abs(a), 1.0)
+    assert max(abs(a - b) for a, b in zip(ld, lo)) > 1e-3     # another seed, other masks
+    for g in (host, dev, other):
+        g.close()
