@@ -131,6 +131,26 @@ def build_sanitizers(verbose=False):
     return outs
 
 
+def build_api_sanitized(verbose=False):
+    """The graph API's sources (parser, plan compiler, autodiff, passes, host operators) compiled with the C++ training example
+    under AddressSanitizer + UBSan: lib/ofb_api_train_asan. It links the regular kernel and runtime libraries; on the host
+    device (-1) no CUDA code runs."""
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "api", "*.cpp"))) + [os.path.join(CSRC, "api", "examples", "train_graph.cpp")]
+    headers = glob.glob(os.path.join(CSRC, "api", "*.h")) + glob.glob(os.path.join(CSRC, "common", "*.h"))
+    exe = os.path.join(LIB, "ofb_api_train_asan")
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    if not os.path.exists(exe) or any(_newer(s, exe, headers) for s in srcs):
+        cxx = shutil.which("g++") or "g++"
+        _run([cxx, "-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", "-pthread", "-fsanitize=address,undefined",
+              "-fno-sanitize-recover=undefined", "-I", os.path.join(cuda, "include"), "-I", os.path.join(CSRC, "api"), "-o", exe] + srcs +
+             ["-L", LIB, "-lofb_kernels", "-lofb_core", "-L", os.path.join(cuda, "lib64"), "-lcudart", f"-Wl,-rpath,{LIB}"],
+             os.path.join(OBJ, "api_asan.log"))
+        print(f"[build] built {os.path.relpath(exe, ROOT)}", flush=True)
+    return exe
+
+
 def build_all(verbose=False):
     return [build_kernels(verbose), build_core(verbose), build_api(verbose)]
 
@@ -138,5 +158,6 @@ def build_all(verbose=False):
 if __name__ == "__main__":
     if "--sanitizers" in sys.argv:
         build_sanitizers(verbose="-v" in sys.argv)
+        build_api_sanitized(verbose="-v" in sys.argv)
     else:
         build_all(verbose="-v" in sys.argv)

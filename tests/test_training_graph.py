@@ -505,3 +505,31 @@ def test_dropout_on_the_gpu_runtime_drops_the_same_elements_as_the_host_runtime(
     assert max(abs(a - b) for a, b in zip(ld, lo)) > 1e-3     # another seed, other masks
     for g in (host, dev, other):
         g.close()
+
+
+def test_graph_compiler_runs_clean_under_address_and_ub_sanitizers(tmp_path):
+    """Parser, autodiff, the default rewriting passes, plan compiler, host operators and Save: the C++ training example built
+    from the API's sources with -fsanitize=address,undefined trains a two-layer GPT with dropout on the host device."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    from oneflow_b200 import build as B
+    from oneflow_b200.utils.bench_graph_runtime import GPT
+    exe = B.build_api_sanitized()
+    torch.manual_seed(15)
+    m = _bf16_weights(GPT(2, 64, 1, 96, 16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path / "g"), fuse=False, train_mode=True)
+    ids.numpy().astype(np.int64).tofile(str(tmp_path / "ids.bin"))
+    tgt.numpy().astype(np.int64).tofile(str(tmp_path / "tgt.bin"))
+    os.makedirs(str(tmp_path / "out"))
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=0 exitcode=67")
+    r = subprocess.run([exe, d, "-1", "4", "0.01", str(tmp_path / "out"), str(tmp_path / "ids.bin"), str(tmp_path / "tgt.bin")],
+                       capture_output=True, text=True, timeout=600, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
+    losses = [float(v) for v in r.stdout.split()]
+    assert len(losses) == 4 and losses[-1] < losses[0]
+    assert os.path.exists(str(tmp_path / "out" / "train_state.bin"))
