@@ -284,11 +284,15 @@ void Builder::run() {
   for (size_t r = 0; r < nt; ++r) {
     const auto& u = uses[r];
     if (u.empty()) continue;
+    const OpDef& first = ir.ops[static_cast<size_t>(u[0].op)];
     if (ir.tensors[r].kind == 1) {
-      mode[r] = Mode::kAccumulate;
+      // A parameter with one consumer whose backward operator can overwrite (a GEMM, the LayerNorm backward) owns its
+      // gradient: no zero fill, no read-modify-write in the GEMM epilogue. Everything else (tied weights, bias column sums,
+      // embedding scatter-adds, gradients kept across micro-batches) accumulates into a cleared buffer.
+      const bool overwrites = (first.type == "linear" && u[0].slot == 1) || first.type == "matmul" || (first.type == "layer_norm" && u[0].slot >= 1);
+      mode[r] = opt.accumulation_steps == 1 && u.size() == 1 && overwrites && whole(u[0].tensor) ? Mode::kDirect : Mode::kAccumulate;
       continue;
     }
-    const OpDef& first = ir.ops[static_cast<size_t>(u[0].op)];
     if (u.size() == 1 && first.type != "copy" && whole(u[0].tensor)) {
       mode[r] = Mode::kDirect;
       continue;
@@ -477,7 +481,13 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
       const bool gp = wants(gamma) && ir.tensors[static_cast<size_t>(root(gamma))].kind == 1;
       const bool bp = wants(beta) && ir.tensors[static_cast<size_t>(root(beta))].kind == 1;
       if (wants(gamma) != gp || wants(beta) != bp) refuse(op, "scale and shift must be parameters");
-      native = true;
+      // both parameter gradients are written by one kernel call: they overwrite together or accumulate together
+      const bool g_direct = gp && mode[static_cast<size_t>(root(gamma))] == Mode::kDirect, b_direct = bp && mode[static_cast<size_t>(root(beta))] == Mode::kDirect;
+      if (!(g_direct && b_direct)) {
+        if (g_direct) mode[static_cast<size_t>(root(gamma))] = Mode::kAccumulate;
+        if (b_direct) mode[static_cast<size_t>(root(beta))] = Mode::kAccumulate;
+      }
+      native = !(g_direct && b_direct);
       auto scratch = [&] {
         const int s = new_root(DType::kFloat, cols);
         emit("fill", {}, {s}, {{"value", "0"}});
