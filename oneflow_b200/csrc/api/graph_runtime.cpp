@@ -78,9 +78,16 @@ IR parse_v2(std::istream& f) {
       for (int i = 0; i < ndim; ++i) {
         int64_t d;
         ss >> d;
-        if (!ss || d < -1) throw bad("bad dimension");
+        if (!ss || d < -1 || d > (int64_t{1} << 40)) throw bad("bad dimension");
         if (d == -1) ir.dynamic_rows = true;
         t.shape.push_back(d);
+      }
+      {
+        int64_t total = 1;
+        for (auto d : t.shape) {
+          if (d > 0 && total > (int64_t{1} << 40) / d) throw bad("tensor too large");
+          total *= d > 0 ? d : 1;
+        }
       }
       std::string kv;
       while (ss >> kv) {
@@ -214,20 +221,37 @@ void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
   };
   auto shp = [&](int t) -> const std::vector<int64_t>& { return plan.shape[static_cast<size_t>(t)]; };
   auto dt = [&](int t) { return ir.tensors[static_cast<size_t>(t)].dtype; };
+  auto bf16 = [&](std::initializer_list<int> ts) {
+    for (int x : ts)
+      if (x >= 0 && dt(x) != DType::kBFloat16) return false;
+    return true;
+  };
+  // a [rows, heads, D] view read with a token stride stays inside its storage
+  auto strided_view_fits = [&](int x, int64_t rows, int64_t row_elems, int64_t stride) {
+    if (stride < row_elems || rows <= 0) return false;
+    const int r = plan.root[static_cast<size_t>(x)];
+    const int64_t first = plan.byte_off[static_cast<size_t>(x)] / SizeOf(dt(x));
+    return stride <= (int64_t{1} << 40) && first + (rows - 1) * stride + row_elems <= numel(shp(r));
+  };
   const std::string& t = op.type;
+  if (t != "linear")
+    for (int x : op.in) need(x >= 0, "absent input");
   if (t == "linear") {
-    need(op.in.size() >= 2 && op.in[0] >= 0 && op.in[1] >= 0, "needs x and weight");
+    need(op.in.size() >= 2 && op.in.size() <= 4 && op.in[0] >= 0 && op.in[1] >= 0, "needs x and weight (and optionally bias and residual)");
     const auto& x = shp(op.in[0]);
     const auto& w = shp(op.in[1]);
     need(w.size() == 2 && !x.empty() && x.back() == w[1], "weight must be [N, K] with K the last axis of x");
     need(numel(shp(op.out[0])) == numel(x) / w[1] * w[0], "output size mismatch");
     if (op.in.size() > 2 && op.in[2] >= 0) need(numel(shp(op.in[2])) == w[0], "bias must have N elements");
     if (op.in.size() > 3 && op.in[3] >= 0) need(numel(shp(op.in[3])) == numel(shp(op.out[0])), "residual must match the output");
+    need(bf16({op.in[0], op.in[1], op.in.size() > 2 ? op.in[2] : -1, op.in.size() > 3 ? op.in[3] : -1, op.out[0]}), "operands must be bf16");
+    if (op.out.size() > 1) need(op.out.size() == 2 && bf16({op.out[1]}) && numel(shp(op.out[1])) == numel(shp(op.out[0])), "the stored pre-activation must match the output");
   } else if (t == "matmul") {
     need(op.in.size() == 2 || op.in.size() == 3, "needs two inputs (and optionally the pre-activation whose derivative scales the result)");
     const auto& a = shp(op.in[0]);
     const auto& b = shp(op.in[1]);
     need(a.size() >= 2 && b.size() >= 2, "operands need at least two axes");
+    need(bf16({op.in[0], op.in[1], op.in.size() > 2 ? op.in[2] : -1}) && op.out.size() == 1, "bf16 operands, one output");
     if (op.in.size() == 3)
       need(a.size() == 2 && numel(shp(op.in[2])) == numel(shp(op.out[0])) && act_code(attr_str(op, "act_grad", "none")) != 0 && dt(op.out[0]) == DType::kBFloat16,
            "act_grad needs a 2-D left operand, a pre-activation of the output's size and a bf16 output");
@@ -242,37 +266,53 @@ void check_op(const OpDef& op, const IR& ir, const Plan& plan) {
     need(attr_int(op, "accumulate", 0) == 0 || dt(op.out[0]) == DType::kFloat, "only fp32 outputs accumulate");
   } else if (t == "layer_norm") {
     need(op.in.size() == 3, "needs x, gamma, beta");
-    need(numel(shp(op.in[1])) == shp(op.in[0]).back() && numel(shp(op.in[2])) == shp(op.in[0]).back(), "gamma / beta length");
+    need(!shp(op.in[0]).empty() && numel(shp(op.in[1])) == shp(op.in[0]).back() && numel(shp(op.in[2])) == shp(op.in[0]).back(), "gamma / beta length");
+    need(bf16({op.in[0], op.in[1], op.in[2], op.out[0]}) && numel(shp(op.out[0])) == numel(shp(op.in[0])), "bf16 operands; the output matches the input");
+    if (op.out.size() > 1)
+      need(op.out.size() == 2 && dt(op.out[1]) == DType::kFloat && numel(shp(op.out[1])) == 2 * numel(shp(op.in[0])) / shp(op.in[0]).back(), "the statistics are two fp32 values per row");
   } else if (t == "embedding") {
     need(op.in.size() == 2 && dt(op.in[0]) == DType::kInt64 && shp(op.in[1]).size() == 2, "needs int64 ids and a [rows, cols] table");
     need(numel(shp(op.out[0])) == numel(shp(op.in[0])) * shp(op.in[1])[1], "output size mismatch");
+    need(bf16({op.in[1], op.out[0]}) && op.out.size() == 1, "bf16 table and output");
   } else if (t == "binary") {
     need(op.in.size() == 2, "needs two inputs");
     const int64_t n = numel(shp(op.in[0])), nb = numel(shp(op.in[1]));
     const int64_t mode = attr_int(op, "bmode", 0), cols = attr_int(op, "cols", 1);
     need(n == numel(shp(op.out[0])), "the first operand must have the output's shape");
-    need((mode == 0 && nb == n) || (mode == 1 && nb == cols && n % cols == 0) || (mode == 2 && cols > 0 && nb * cols == n), "broadcast description does not match the shapes");
+    need((mode == 0 && nb == n) || (mode == 1 && cols > 0 && nb == cols && n % cols == 0) || (mode == 2 && cols > 0 && nb * cols == n), "broadcast description does not match the shapes");
+    need(bf16({op.in[0], op.in[1], op.out[0]}) && op.out.size() == 1, "bf16 operands");
   } else if (t == "unary" || t == "softmax") {
-    need(op.in.size() == 1 && numel(shp(op.in[0])) == numel(shp(op.out[0])), "shape mismatch");
+    need(op.in.size() == 1 && op.in[0] >= 0 && op.out.size() == 1 && numel(shp(op.in[0])) == numel(shp(op.out[0])), "shape mismatch");
+    need(bf16({op.in[0], op.out[0]}), "bf16 operands");
+    if (t == "softmax") need(!shp(op.in[0]).empty() && shp(op.in[0]).back() > 0, "softmax needs a last axis");
   } else if (t == "attention") {
     need(op.in.size() == 3, "needs q, k, v");
     const auto& q = shp(op.in[0]);
     const auto& k = shp(op.in[1]);
     need(q.size() == 4 && k.size() == 4 && shp(op.in[2]) == k && q[0] == k[0] && q[3] == k[3] && q[2] % k[2] == 0, "q [B,Sq,H,D], k / v [B,Sk,Hk,D]");
     need(numel(shp(op.out[0])) == numel(q), "output size mismatch");
+    need(bf16({op.in[0], op.in[1], op.in[2], op.out[0]}), "bf16 operands");
+    need(strided_view_fits(op.in[0], q[0] * q[1], q[2] * q[3], attr_int(op, "q_stride", q[2] * q[3])) &&
+             strided_view_fits(op.in[1], k[0] * k[1], k[2] * k[3], attr_int(op, "kv_stride", k[2] * k[3])) &&
+             strided_view_fits(op.in[2], k[0] * k[1], k[2] * k[3], attr_int(op, "kv_stride", k[2] * k[3])),
+         "a token stride reaches outside the operand's storage");
+    if (op.out.size() > 1) need(op.out.size() == 2 && dt(op.out[1]) == DType::kFloat && numel(shp(op.out[1])) == q[0] * q[1] * q[2], "the log-sum-exp is one fp32 value per (batch, head, query)");
   } else if (t == "copy") {
     need(op.in.size() == 1, "needs one input");
     const auto s = int_list(attr_str(op, "shape", "")), is = int_list(attr_str(op, "in_strides", "")), os = int_list(attr_str(op, "out_strides", ""));
     need(!s.empty() && s.size() <= 5 && is.size() == s.size() && os.size() == s.size(), "shape / in_strides / out_strides of 1..5 axes");
     // bounds of both views
     int64_t in_max = attr_int(op, "in_offset", 0), out_max = attr_int(op, "out_offset", 0);
+    const int64_t lim = int64_t{1} << 40;
+    need(in_max >= 0 && out_max >= 0 && in_max < lim && out_max < lim && op.out.size() == 1, "negative or absurd offset");
     for (size_t i = 0; i < s.size(); ++i) {
-      need(s[i] > 0 && is[i] >= 0 && os[i] >= 0, "non-positive extent or negative stride");
+      need(s[i] > 0 && is[i] >= 0 && os[i] >= 0 && s[i] < lim && is[i] < lim && os[i] < lim && numel(s) < lim, "non-positive extent, negative stride or absurd size");
       in_max += (s[i] - 1) * is[i];
       out_max += (s[i] - 1) * os[i];
     }
     need(in_max < numel(shp(op.in[0])) && out_max < numel(shp(op.out[0])), "view reaches outside its tensor");
     need(dt(op.in[0]) == dt(op.out[0]) || attr_int(op, "accumulate", 0) != 0, "dtype mismatch");
+    if (attr_int(op, "accumulate", 0) != 0) need(dt(op.in[0]) != DType::kInt64 && dt(op.out[0]) != DType::kInt64, "only bf16 / fp32 views accumulate");
   } else if (!check_train_op(op, ir, plan)) {
     throw std::runtime_error("unknown operator type: " + t);
   }
@@ -295,8 +335,16 @@ void Graph::Impl::compile(int64_t rows) {
         if (rows <= 0) throw std::runtime_error("the graph has an unbound row count");
         d = rows;
       }
+    {
+      int64_t total = 1;
+      for (auto d : p->shape[i]) {
+        if (d < 0 || d > (int64_t{1} << 40) || (d > 0 && total > (int64_t{1} << 40) / d)) throw std::runtime_error("tensor " + std::to_string(i) + ": absurd size");
+        total *= d;
+      }
+    }
     const TensorDef& t = ir.tensors[i];
     if (t.alias_of >= 0) {
+      if (t.alias_off < 0) throw std::runtime_error("tensor " + std::to_string(i) + ": negative alias offset");
       const size_t a = static_cast<size_t>(t.alias_of);
       p->root[i] = p->root[a];
       p->byte_off[i] = p->byte_off[a] + t.alias_off * SizeOf(ir.tensors[a].dtype);
@@ -312,6 +360,23 @@ void Graph::Impl::compile(int64_t rows) {
 
   const int n_ops = static_cast<int>(ir.ops.size());
   p->ops.resize(static_cast<size_t>(n_ops));
+  // every storage of kind "input" that an operator reads must be handed in by the caller
+  {
+    std::vector<char> fed(nt, 0);
+    for (int t : ir.inputs) fed[static_cast<size_t>(p->root[static_cast<size_t>(t)])] = 1;
+    for (const OpDef& op : ir.ops)
+      for (int t : op.in)
+        if (t >= 0 && root_kind(p->root[static_cast<size_t>(t)]) == 0 && !fed[static_cast<size_t>(p->root[static_cast<size_t>(t)])])
+          throw std::runtime_error("operator " + op.type + " reads input tensor " + std::to_string(t) + ", which is not among the graph's inputs");
+    for (int t : ir.inputs) {
+      const int r = p->root[static_cast<size_t>(t)];
+      if (root_kind(r) != 0) throw std::runtime_error("graph input " + std::to_string(t) + " is not a tensor of kind input");
+      // the caller hands in exactly this tensor: it has to be the whole storage the operators may read
+      if (p->byte_off[static_cast<size_t>(t)] != 0 || numel(p->shape[static_cast<size_t>(t)]) != numel(p->shape[static_cast<size_t>(r)]) ||
+          ir.tensors[static_cast<size_t>(t)].dtype != ir.tensors[static_cast<size_t>(r)].dtype)
+        throw std::runtime_error("graph input " + std::to_string(t) + " does not cover its whole storage");
+    }
+  }
   // 1. liveness of activation storages in operator order
   std::vector<int> first(nt, -1), last(nt, -1);
   for (int i = 0; i < n_ops; ++i) {
@@ -903,6 +968,10 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
   else if (line.rfind("oneflow_b200 inference graph v1", 0) == 0) impl->ir = parse_v1(f);
   else throw std::runtime_error("not an exported graph: " + dir);
   if (train) {
+    // the forward graph is compiled once on its own first: that validates every operator (shapes, dtypes, views) before the
+    // differentiation pass indexes into them
+    if (impl->ir.dynamic_rows) throw std::runtime_error("training graph: export with static shapes (export_graph), not the layer-list form");
+    impl->compile(0);
     append_training_ops(impl->ir, *train);
     impl->train = *train;
     if (device >= 0) {
@@ -920,6 +989,10 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
     const size_t bytes = static_cast<size_t>(numel(t.shape) * SizeOf(t.dtype));
     std::ifstream pf(dir + "/" + t.file, std::ios::binary);
     if (!pf) throw std::runtime_error("cannot open " + dir + "/" + t.file);
+    pf.seekg(0, std::ios::end);
+    if (static_cast<int64_t>(pf.tellg()) != static_cast<int64_t>(bytes))
+      throw std::runtime_error(t.file + " holds " + std::to_string(static_cast<int64_t>(pf.tellg())) + " bytes, the graph declares " + std::to_string(bytes));
+    pf.seekg(0, std::ios::beg);
     std::vector<char> host(bytes);
     pf.read(host.data(), static_cast<std::streamsize>(bytes));
     if (static_cast<size_t>(pf.gcount()) != bytes) throw std::runtime_error("short read: " + t.file);

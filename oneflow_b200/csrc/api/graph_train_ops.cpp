@@ -132,6 +132,17 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
   auto dt = [&](int t) { return ir.tensors[static_cast<size_t>(t)].dtype; };
   auto n = [&](int t) { return numel(shp(t)); };
   for (int t : op.in) need(t >= 0, "absent input");
+  auto bf16 = [&](std::initializer_list<int> ts) {
+    for (int x : ts)
+      if (dt(x) != DType::kBFloat16) return false;
+    return true;
+  };
+  auto strided_view_fits = [&](int x, int64_t rows, int64_t row_elems, int64_t stride) {
+    if (stride < row_elems || rows <= 0 || stride > (int64_t{1} << 40)) return false;
+    const int r = plan.root[static_cast<size_t>(x)];
+    const int64_t first = plan.byte_off[static_cast<size_t>(x)] / SizeOf(dt(x));
+    return first + (rows - 1) * stride + row_elems <= numel(shp(r));
+  };
   const std::string& t = op.type;
   if (t == "fill") {
     need(op.in.empty() && op.out.size() == 1 && is_float_type(dt(op.out[0])), "one bf16 / fp32 output, no input");
@@ -146,16 +157,20 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
          "one bf16 input and output of the same length");
     need(attr_float(op, "p", 0.5) >= 0.0 && attr_float(op, "p", 0.5) < 1.0, "p must be in [0, 1)");
   } else if (t == "unary_bwd") {
-    need(op.in.size() == 2 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]), "x, dy and dx of the same length");
+    need(op.in.size() == 2 && op.out.size() == 1 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]) && bf16({op.in[0], op.in[1], op.out[0]}),
+         "bf16 x, dy and dx of the same length");
   } else if (t == "layer_norm_bwd") {
     need((op.in.size() == 4 || op.in.size() == 5) && (op.out.size() == 1 || op.out.size() == 3), "(dy, x, gamma, stats [, add_to_dx]) -> dx [, dgamma, dbeta]");
     if (op.in.size() == 5) need(n(op.in[4]) == n(op.in[1]) && dt(op.in[4]) == DType::kBFloat16, "the tensor added to dx must match x");
     const int64_t cols = shp(op.in[1]).back(), rows = n(op.in[1]) / cols;
-    need(n(op.in[0]) == n(op.in[1]) && n(op.out[0]) == n(op.in[1]) && n(op.in[2]) == cols && n(op.in[3]) == 2 * rows && dt(op.in[3]) == DType::kFloat,
-         "shape mismatch");
+    need(n(op.in[0]) == n(op.in[1]) && n(op.out[0]) == n(op.in[1]) && n(op.in[2]) == cols && n(op.in[3]) == 2 * rows && dt(op.in[3]) == DType::kFloat &&
+             bf16({op.in[0], op.in[1], op.in[2], op.out[0]}),
+         "shape or dtype mismatch");
     if (op.out.size() == 3) need(n(op.out[1]) == cols && n(op.out[2]) == cols && dt(op.out[1]) == DType::kFloat && dt(op.out[2]) == DType::kFloat, "fp32 parameter gradients with one element per column");
   } else if (t == "softmax_bwd") {
-    need(op.in.size() == 2 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]), "y, dy and dx of the same length");
+    need(op.in.size() == 2 && op.out.size() == 1 && n(op.in[0]) == n(op.in[1]) && n(op.in[0]) == n(op.out[0]) && bf16({op.in[0], op.in[1], op.out[0]}) &&
+             !shp(op.in[0]).empty() && shp(op.in[0]).back() > 0,
+         "bf16 y, dy and dx of the same length");
   } else if (t == "attention_bwd") {
     need(op.in.size() == 6 && op.out.size() == 3, "(q, k, v, o, do, lse) -> dq, dk, dv");
     const auto& q = shp(op.in[0]);
@@ -163,9 +178,16 @@ bool check_train_op(const OpDef& op, const IR& ir, const Plan& plan) {
     need(q.size() == 4 && k.size() == 4 && shp(op.in[2]) == k && q[0] == k[0] && q[3] == k[3] && q[2] % k[2] == 0, "q [B,Sq,H,D], k / v [B,Sk,Hk,D]");
     need(n(op.in[3]) == numel(q) && n(op.in[4]) == numel(q) && n(op.in[5]) == q[0] * q[1] * q[2] && dt(op.in[5]) == DType::kFloat, "o / do / lse sizes");
     need(n(op.out[0]) == numel(q) && n(op.out[1]) == numel(k) && n(op.out[2]) == numel(k), "gradient sizes");
+    need(bf16({op.in[0], op.in[1], op.in[2], op.in[3], op.in[4], op.out[0], op.out[1], op.out[2]}), "bf16 operands");
+    const int64_t qr = q[0] * q[1], kr = k[0] * k[1], qe = q[2] * q[3], ke = k[2] * k[3];
+    need(strided_view_fits(op.in[0], qr, qe, attr_int(op, "q_stride", qe)) && strided_view_fits(op.in[1], kr, ke, attr_int(op, "kv_stride", ke)) &&
+             strided_view_fits(op.in[2], kr, ke, attr_int(op, "kv_stride", ke)) && strided_view_fits(op.out[0], qr, qe, attr_int(op, "dq_stride", qe)) &&
+             strided_view_fits(op.out[1], kr, ke, attr_int(op, "dkv_stride", ke)) && strided_view_fits(op.out[2], kr, ke, attr_int(op, "dkv_stride", ke)),
+         "a token stride reaches outside its storage");
   } else if (t == "embedding_bwd") {
     need(op.in.size() == 2 && dt(op.in[0]) == DType::kInt64 && shp(op.in[1]).size() == 2 && shp(op.in[1])[0] == n(op.in[0]), "ids and a [ids, cols] gradient");
-    need(dt(op.out[0]) == DType::kFloat && shp(op.out[0]).size() == 2 && shp(op.out[0])[1] == shp(op.in[1])[1], "an fp32 [rows, cols] table gradient");
+    need(op.out.size() == 1 && dt(op.out[0]) == DType::kFloat && shp(op.out[0]).size() == 2 && shp(op.out[0])[1] == shp(op.in[1])[1] && bf16({op.in[1]}),
+         "a bf16 gradient and an fp32 [rows, cols] table gradient");
   } else if (t == "cross_entropy") {
     need(op.in.size() == 2 && shp(op.in[0]).size() >= 2 && dt(op.in[0]) == DType::kBFloat16 && dt(op.in[1]) == DType::kInt64, "bf16 logits [.., classes] and int64 targets");
     need(n(op.in[1]) * shp(op.in[0]).back() == n(op.in[0]), "one target per row of logits");

@@ -116,10 +116,12 @@ void EmptyCache() { detail::device_pool().release_all(); }
 namespace detail {
 
 void copy_in(void* dst, const void* host, size_t bytes, int device) {
+  if (bytes == 0) return;
   if (device < 0) std::memcpy(dst, host, bytes);
   else check_cuda(cudaMemcpy(dst, host, bytes, cudaMemcpyHostToDevice), "cudaMemcpy");
 }
 void copy_out(void* host, const void* src, size_t bytes, int device) {
+  if (bytes == 0) return;
   if (device < 0) std::memcpy(host, src, bytes);
   else check_cuda(cudaMemcpy(host, src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy");
 }

@@ -533,3 +533,62 @@ def test_graph_compiler_runs_clean_under_address_and_ub_sanitizers(tmp_path):
     losses = [float(v) for v in r.stdout.split()]
     assert len(losses) == 4 and losses[-1] < losses[0]
     assert os.path.exists(str(tmp_path / "out" / "train_state.bin"))
+
+
+def test_damaged_graph_files_are_refused_not_crashed_on(tmp_path):
+    """Random damage to graph.txt (dropped or doubled records, dropped tokens, changed digits, negative and absurd numbers):
+    the sanitized C++ program either trains or reports an error; it never reads or writes out of bounds."""
+    import random
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    from oneflow_b200 import build as B
+    from oneflow_b200.utils.bench_graph_runtime import GPT
+    exe = B.build_api_sanitized()
+    torch.manual_seed(16)
+    m = _bf16_weights(GPT(1, 64, 1, 96, 16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    src = E.export_graph(m, (ids, tgt), str(tmp_path / "g"), fuse=False, train_mode=True)
+    ids.numpy().astype(np.int64).tofile(str(tmp_path / "ids.bin"))
+    tgt.numpy().astype(np.int64).tofile(str(tmp_path / "tgt.bin"))
+    lines = open(os.path.join(src, "graph.txt")).read().splitlines()
+    outcomes = {}
+    for seed in range(80):
+        rnd = random.Random(seed)
+        damaged = list(lines)
+        for _ in range(rnd.randint(1, 3)):
+            i = rnd.randrange(1, len(damaged))
+            toks = damaged[i].split()
+            kind = rnd.randrange(6)
+            if kind == 0 and len(toks) > 2:
+                del toks[rnd.randrange(1, len(toks))]
+            elif kind == 1:
+                j = rnd.randrange(len(toks))
+                toks[j] = "".join(c if not c.isdigit() else str(rnd.randrange(10)) for c in toks[j])
+            elif kind == 2:
+                j = rnd.randrange(len(toks))
+                toks[j] = toks[j].replace("=", "=-", 1) if "=" in toks[j] else "-" + toks[j]
+            elif kind == 3:
+                del damaged[i]
+                continue
+            elif kind == 4:
+                damaged.insert(i, damaged[rnd.randrange(1, len(damaged))])
+                continue
+            else:
+                j = rnd.randrange(len(toks))
+                toks[j] = toks[j] + "9999999999"
+            damaged[i] = " ".join(toks)
+        d = tmp_path / f"damaged{seed}"
+        d.mkdir()
+        for f in os.listdir(src):
+            if f != "graph.txt":
+                os.symlink(os.path.join(src, f), str(d / f))
+        (d / "graph.txt").write_text("\n".join(damaged) + "\n")
+        r = subprocess.run([exe, str(d), "-1", "1", "0.01", "-", str(tmp_path / "ids.bin"), str(tmp_path / "tgt.bin")], capture_output=True,
+                           text=True, timeout=120, env=dict(os.environ, ASAN_OPTIONS="detect_leaks=0 exitcode=67"))
+        assert r.returncode in (0, 1, 2) and "Sanitizer" not in r.stderr and "runtime error" not in r.stderr, (seed, r.stderr[-1500:])
+        if r.returncode != 0:
+            assert "error:" in r.stderr or "short read" in r.stderr or "takes" in r.stderr, (seed, r.stderr[-500:])
+        outcomes[r.returncode] = outcomes.get(r.returncode, 0) + 1
+    assert outcomes.get(1, 0) > 40           # most damage is detected and named
