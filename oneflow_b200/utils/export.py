@@ -512,6 +512,17 @@ class _GraphEmitter(torch.fx.Interpreter):
         return self._handle(target, args, kwargs, super().call_method(target, args, kwargs))
 
 
+class _LeafTracer(torch.fx.Tracer):
+    """Layers the emitter knows by type stay whole, whatever package their class lives in: the flow API's layers subclass the
+    torch ones and dispatch on the tensor kind in ``forward``, which cannot be traced symbolically (and need not be)."""
+
+    _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
+               torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss)
+
+    def is_leaf_module(self, m, qualname):
+        return isinstance(m, self._LEAVES) or super().is_leaf_module(m, qualname)
+
+
 def _fold(ops, outputs, tensor_lines):
     """Peephole fusion: an activation, then a residual addition, that are the only consumer of a linear's result move into its
     GEMM epilogue (bias -> activation -> + residual is the order the kernel applies). The fused operator takes the consumer's
@@ -570,7 +581,11 @@ def export_graph(module, example_inputs, directory, fuse=True, train_mode=False)
     was_training = module.training
     module.train(bool(train_mode))
     try:
-        gm = module if isinstance(module, torch.fx.GraphModule) else torch.fx.symbolic_trace(module)
+        if isinstance(module, torch.fx.GraphModule):
+            gm = module
+        else:
+            tracer = _LeafTracer()
+            gm = torch.fx.GraphModule(module, tracer.trace(module))
         em = _GraphEmitter(gm, directory)
         with torch.no_grad():
             em.run(*[t.detach().cpu() for t in example_inputs])

@@ -592,3 +592,26 @@ def test_damaged_graph_files_are_refused_not_crashed_on(tmp_path):
             assert "error:" in r.stderr or "short read" in r.stderr or "takes" in r.stderr, (seed, r.stderr[-500:])
         outcomes[r.returncode] = outcomes.get(r.returncode, 0) + 1
     assert outcomes.get(1, 0) > 40           # most damage is detected and named
+
+
+def test_layers_of_the_flow_api_export_and_train_natively(tmp_path):
+    """flow.nn layers subclass the torch ones and dispatch on the tensor kind in forward; the exporter keeps them whole."""
+    import oneflow as flow
+
+    class Net(flow.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = flow.nn.Sequential(flow.nn.Linear(32, 64), flow.nn.GELU(), flow.nn.LayerNorm(64), flow.nn.Linear(64, 16))
+
+        def forward(self, x, y):
+            return F.cross_entropy(self.body(x), y)
+
+    torch.manual_seed(17)
+    m = _bf16_weights(Net())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    loss, grads = _grads_by_unit_sgd(m, (x, y), str(tmp_path))
+    ref = m(x, y)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    assert set(grads) == {n for n, _ in m.named_parameters()}
+    _check_grads(m, grads)
