@@ -139,6 +139,15 @@ __device__ __forceinline__ void epi_store_bf16(uint32_t stage, int lane, const f
     epi_sts(epi_addr64(stage, lane, ch), q);
   }
   __syncwarp();
+  // the old values are all read before the first store (see epi_store_f32)
+  uint4 olds[4];
+  if (accumulate) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = it * 8 + (lane >> 2), ch = lane & 3;
+      olds[it] = (r < rows_valid && ch * 8 < cols_valid) ? *reinterpret_cast<const uint4*>(dst + r * ld + ch * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
 #pragma unroll
   for (int it = 0; it < 4; ++it) {
     const int r = it * 8 + (lane >> 2), ch = lane & 3;
@@ -146,7 +155,7 @@ __device__ __forceinline__ void epi_store_bf16(uint32_t stage, int lane, const f
     if (r < rows_valid && ch * 8 < cols_valid) {
       uint4* p = reinterpret_cast<uint4*>(dst + r * ld + ch * 8);
       if (accumulate) {
-        const uint4 old = *p;
+        const uint4 old = olds[it];
         const uint32_t a[4] = {q.x, q.y, q.z, q.w}, b[4] = {old.x, old.y, old.z, old.w};
         uint32_t o[4];
 #pragma unroll
@@ -175,6 +184,17 @@ __device__ __forceinline__ void epi_store_f32(uint32_t stage, int lane, const fl
     epi_sts(epi_addr128(stage, lane, ch), q);
   }
   __syncwarp();
+  // read-add-write: all eight reads of the old values are issued before the first store. Inside one loop the compiler has
+  // to keep every load behind the previous iteration's store (the pointers may alias for all it knows), which makes eight
+  // dependent round trips to memory per chunk; with one output tile per CTA nothing hides them.
+  float4 old[8];
+  if (mode == 1) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + (lane >> 3), ch = lane & 7;
+      old[it] = (r < rows_valid && ch * 4 < cols_valid) ? *reinterpret_cast<const float4*>(dst + r * ld + ch * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int r = it * 4 + (lane >> 3), ch = lane & 7;
@@ -186,8 +206,7 @@ __device__ __forceinline__ void epi_store_f32(uint32_t stage, int lane, const fl
         atomicAdd(p, x);
       } else {
         if (mode == 1) {
-          const float4 old = *p;
-          x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+          x.x += old[it].x; x.y += old[it].y; x.z += old[it].z; x.w += old[it].w;
         }
         *p = x;
       }
