@@ -4,6 +4,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <map>
 #include <memory>
@@ -196,6 +198,16 @@ struct Graph::Impl {
     const int r = plan->root[static_cast<size_t>(tensor)];
     char* b = static_cast<char*>(plan->base[static_cast<size_t>(r)] ? plan->base[static_cast<size_t>(r)] : bound[static_cast<size_t>(r)]);
     return b + plan->byte_off[static_cast<size_t>(tensor)];
+  }
+  // learning rate of optimizer step t (1-based) under the schedule of `train`
+  float scheduled_lr(int64_t t) const {
+    float lr = train.lr;
+    if (train.warmup_steps > 0 && t <= train.warmup_steps) return lr * static_cast<float>(t) / static_cast<float>(train.warmup_steps);
+    if (train.lr_schedule == "constant" || train.decay_steps <= train.warmup_steps) return lr;
+    const double span = static_cast<double>(train.decay_steps - train.warmup_steps);
+    const double x = std::min(1.0, static_cast<double>(t - train.warmup_steps) / span);
+    const double shape = train.lr_schedule == "cosine" ? 0.5 * (1.0 + std::cos(3.14159265358979323846 * x)) : 1.0 - x;
+    return lr * static_cast<float>(train.min_lr_ratio + (1.0 - train.min_lr_ratio) * shape);
   }
   // operators marked when=first / when=last are skipped on the other micro-batches
   bool op_enabled(const OpDef& op) const {

@@ -1050,6 +1050,19 @@ void Graph::set_learning_rate(float lr) {
   std::lock_guard<std::mutex> g(impl_->run_mu);
   impl_->train.lr = lr;
 }
+void Graph::set_lr_schedule(const std::string& kind, int64_t warmup_steps, int64_t decay_steps, float min_lr_ratio) {
+  if (kind != "constant" && kind != "cosine" && kind != "linear") throw std::runtime_error("lr schedule must be \"constant\", \"cosine\" or \"linear\"");
+  if (warmup_steps < 0 || decay_steps < 0 || min_lr_ratio < 0.f || min_lr_ratio > 1.f) throw std::runtime_error("lr schedule: negative step count or ratio outside [0, 1]");
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  impl_->train.lr_schedule = kind;
+  impl_->train.warmup_steps = warmup_steps;
+  impl_->train.decay_steps = decay_steps;
+  impl_->train.min_lr_ratio = min_lr_ratio;
+}
+float Graph::learning_rate() const {
+  std::lock_guard<std::mutex> g(impl_->run_mu);
+  return impl_->scheduled_lr(impl_->train_steps + 1);
+}
 void Graph::set_seed(uint64_t seed) {
   std::lock_guard<std::mutex> g(impl_->run_mu);
   impl_->train.seed = seed;
@@ -1224,7 +1237,7 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
     ++im.call_counter;                          // dropout masks are a function of the call number
     if (im.device >= 0) {
-      im.step_scalars_host[0] = im.train.lr;
+      im.step_scalars_host[0] = im.scheduled_lr(std::max<int64_t>(im.train_steps, 1));
       im.step_scalars_host[1] = 1.f - std::pow(im.train.beta1, static_cast<float>(im.train_steps));
       im.step_scalars_host[2] = 1.f - std::pow(im.train.beta2, static_cast<float>(im.train_steps));
       im.step_scalars_host[3] = 0.f;

@@ -444,7 +444,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
     const float gscale = attr_int(op, "clip", 0) ? static_cast<const float*>(addr(op.in[static_cast<size_t>(np)]))[2] : 1.f;
-    const float lr = train.lr, b1 = train.beta1, b2 = train.beta2, wd = train.weight_decay;
+    const float lr = scheduled_lr(std::max<int64_t>(train_steps, 1)), b1 = train.beta1, b2 = train.beta2, wd = train.weight_decay;
     const float bc1 = 1.f - std::pow(b1, static_cast<float>(train_steps)), bc2 = 1.f - std::pow(b2, static_cast<float>(train_steps));
     for (int64_t i = 0; i < np; ++i) {
       const float* g = static_cast<const float*>(addr(op.in[static_cast<size_t>(i)]));

@@ -324,6 +324,16 @@ int ofb_api_graph_restore(void* g, const char* dir) {
     return -1;
   }
 }
+int ofb_api_graph_set_lr_schedule(void* g, const char* kind, long long warmup_steps, long long decay_steps, float min_lr_ratio) {
+  try {
+    static_cast<Graph*>(g)->set_lr_schedule(kind ? kind : "constant", warmup_steps, decay_steps, min_lr_ratio);
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+float ofb_api_graph_lr(void* g) { return static_cast<Graph*>(g)->learning_rate(); }
 int ofb_api_graph_set_seed(void* g, unsigned long long seed) {
   static_cast<Graph*>(g)->set_seed(seed);
   return 0;

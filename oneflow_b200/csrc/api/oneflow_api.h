@@ -108,6 +108,13 @@ struct TrainOptions {
   // Seed of the dropout operators (graphs exported in training mode). The mask of an operator is a function of (seed,
   // number of the call, operator): every call draws new masks, a run with the same seed draws the same sequence.
   uint64_t seed = 0;
+  // Learning-rate schedule evaluated by the runtime before every optimizer step t = 1, 2, ...: linear warm-up from 0 over
+  // warmup_steps, then "constant", or "cosine" / "linear" decay to min_lr_ratio * lr at decay_steps (and flat after it).
+  // set_learning_rate changes the base rate the schedule scales.
+  std::string lr_schedule = "constant";
+  int64_t warmup_steps = 0;
+  int64_t decay_steps = 0;
+  float min_lr_ratio = 0.f;
 };
 
 class Graph {
@@ -145,6 +152,8 @@ class Graph {
   void Save(const std::string& dir) const;
   void Restore(const std::string& dir);
   void set_learning_rate(float lr);
+  void set_lr_schedule(const std::string& kind, int64_t warmup_steps, int64_t decay_steps, float min_lr_ratio);
+  float learning_rate() const;   // the rate the next optimizer step will use
   void set_seed(uint64_t seed);
   int64_t steps() const;
   std::string dump() const;
@@ -188,6 +197,8 @@ long long ofb_api_graph_parameter_numel(void* graph, int i);
 int ofb_api_graph_parameter_read(void* graph, int i, float* out);
 int ofb_api_graph_set_lr(void* graph, float lr);
 int ofb_api_graph_set_seed(void* graph, unsigned long long seed);
+int ofb_api_graph_set_lr_schedule(void* graph, const char* kind, long long warmup_steps, long long decay_steps, float min_lr_ratio);
+float ofb_api_graph_lr(void* graph);
 int ofb_api_graph_save(void* graph, const char* dir);
 int ofb_api_graph_restore(void* graph, const char* dir);
 long long ofb_api_graph_steps(void* graph);

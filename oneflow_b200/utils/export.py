@@ -702,6 +702,19 @@ class TrainingGraph(InferenceGraph):
     def steps(self):
         return int(self.lib.ofb_api_graph_steps(ctypes.c_void_p(self.h)))
 
+    def set_lr_schedule(self, kind="cosine", warmup_steps=0, decay_steps=0, min_lr_ratio=0.0):
+        """Linear warm-up over ``warmup_steps`` optimizer steps, then "constant", or "cosine" / "linear" decay to
+        ``min_lr_ratio`` times the base rate at ``decay_steps``; evaluated by the runtime before every optimizer step."""
+        if self.lib.ofb_api_graph_set_lr_schedule(ctypes.c_void_p(self.h), kind.encode(), ctypes.c_longlong(warmup_steps),
+                                                  ctypes.c_longlong(decay_steps), ctypes.c_float(min_lr_ratio)) != 0:
+            raise RuntimeError(self.lib.ofb_api_last_error().decode())
+
+    @property
+    def lr(self):
+        """The rate the next optimizer step will use."""
+        self.lib.ofb_api_graph_lr.restype = ctypes.c_float
+        return float(self.lib.ofb_api_graph_lr(ctypes.c_void_p(self.h)))
+
     def set_seed(self, seed):
         """Seed of the dropout operators: the mask is a function of (seed, number of the call, operator, element)."""
         self.lib.ofb_api_graph_set_seed(ctypes.c_void_p(self.h), ctypes.c_ulonglong(seed))

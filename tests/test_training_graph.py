@@ -615,3 +615,38 @@ def test_layers_of_the_flow_api_export_and_train_natively(tmp_path):
     assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
     assert set(grads) == {n for n, _ in m.named_parameters()}
     _check_grads(m, grads)
+
+
+def test_learning_rate_schedule_follows_warmup_and_cosine(tmp_path):
+    import math
+    torch.manual_seed(18)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.2)
+    g.set_lr_schedule("cosine", warmup_steps=2, decay_steps=6, min_lr_ratio=0.1)
+    want = []
+    for t in range(1, 9):
+        if t <= 2:
+            want.append(0.2 * t / 2)
+        else:
+            xx = min(1.0, (t - 2) / 4)
+            want.append(0.2 * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * xx))))
+    got = []
+    opt = torch.optim.SGD(m.parameters(), lr=0.2)
+    for t in range(8):
+        got.append(g.lr)
+        for group in opt.param_groups:
+            group["lr"] = want[t]
+        ref = m(x, y)
+        opt.zero_grad()
+        ref.backward()
+        opt.step()
+        assert abs(g.step(x.numpy(), y.numpy()) - float(ref.detach())) < 3e-2 * max(abs(float(ref.detach())), 0.1)
+    assert np.allclose(got, want, rtol=1e-5)
+    ps = g.parameters()
+    for name, p in m.named_parameters():
+        assert np.abs(ps[name] - p.detach().numpy().reshape(-1)).max() < 2e-2, name
+    with pytest.raises(RuntimeError, match="lr schedule"):
+        g.set_lr_schedule("exponential")
+    g.close()
