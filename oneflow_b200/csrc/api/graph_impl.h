@@ -152,7 +152,8 @@ struct Graph::Impl {
   std::vector<cudaEvent_t> join_events;
   int runs_of_plan[4] = {0, 0, 0, 0};
   int micro_step = 0;     // position inside the current optimizer step
-  int call_kind = 3;      // of the running call
+  int call_kind = 3;      // of the running call; 4 = evaluation (forward operators only, never recorded)
+  std::vector<Tensor> run(const std::vector<Tensor>& inputs, bool evaluate, const Graph& self);
   int64_t graph_replays = 0;
   bool graph_disabled = false;
   // training graphs: hyper-parameters read by the update operator at launch time, steps taken so far
@@ -211,6 +212,7 @@ struct Graph::Impl {
   }
   // operators marked when=first / when=last are skipped on the other micro-batches
   bool op_enabled(const OpDef& op) const {
+    if (call_kind == 4) return op.attr.count("fwd") != 0;
     auto it = op.attr.find("when");
     if (it == op.attr.end()) return true;
     return it->second == "first" ? (call_kind & 1) != 0 : (call_kind & 2) != 0;

@@ -109,6 +109,7 @@ bool recompute_cheap_activations(IR& ir) {
       return static_cast<int>(ir.tensors.size()) - 1;
     };
     OpDef copy = op;
+    copy.attr.erase("fwd");   // the copy belongs to the backward pass: an evaluation call does not run it
     for (int& t : copy.out) t = fresh_like(t);
     const int new_root = View(ir).root(copy.out[0]);
     // backward readers switch to the copy

@@ -1196,12 +1196,15 @@ void Graph::BindRows(int64_t rows) {
 
 Tensor Graph::Forward(const Tensor& input) const { return Forward(std::vector<Tensor>{input}).at(0); }
 
-std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
-  Impl& im = *impl_;
+std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const { return impl_->run(inputs, false, *this); }
+std::vector<Tensor> Graph::Evaluate(const std::vector<Tensor>& inputs) const { return impl_->run(inputs, impl_->ir.training, *this); }
+
+std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, bool evaluate, const Graph& self) {
+  Impl& im = *this;
   std::lock_guard<std::mutex> run_guard(im.run_mu);
   if (inputs.size() != im.ir.inputs.size()) throw std::runtime_error("Forward: wrong number of inputs");
   if (im.ir.dynamic_rows) {
-    const int64_t feat = in_features();
+    const int64_t feat = self.in_features();
     const int64_t rows = inputs[0].shape().elem_cnt() / (feat > 0 ? feat : 1);
     if (!im.plan || im.plan->rows != rows) im.compile(rows);
   }
@@ -1230,8 +1233,8 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
-  im.call_kind = 3;
-  if (im.ir.training) {
+  im.call_kind = evaluate ? 4 : 3;
+  if (im.ir.training && !evaluate) {
     const int k = std::max(1, im.train.accumulation_steps);
     im.call_kind = (im.micro_step == 0 ? 1 : 0) | (im.micro_step == k - 1 ? 2 : 0);
     if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
@@ -1249,7 +1252,7 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
   bool replayed = false;
   if (im.device >= 0) {
     check_cuda(cudaStreamSynchronize(im.streams[0]), "cudaStreamSynchronize");   // inputs are in place before any stream reads them
-    if (!im.graph_disabled && im.runs_of_plan[im.call_kind] >= 1) {
+    if (!im.graph_disabled && im.call_kind < 4 && im.runs_of_plan[im.call_kind] >= 1) {
       if (!im.graph_exec[im.call_kind] && !im.capture_plan()) im.graph_disabled = true;
       if (im.graph_exec[im.call_kind]) {
         check_cuda(cudaGraphLaunch(im.graph_exec[im.call_kind], im.streams[0]), "cudaGraphLaunch");
@@ -1259,8 +1262,8 @@ std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const {
       }
     }
   }
-  ++im.runs_of_plan[im.call_kind];
-  if (im.ir.training) im.micro_step = (im.call_kind & 2) ? 0 : im.micro_step + 1;
+  if (im.call_kind < 4) ++im.runs_of_plan[im.call_kind];
+  if (im.ir.training && !evaluate) im.micro_step = (im.call_kind & 2) ? 0 : im.micro_step + 1;
   const int n_ops = replayed ? 0 : static_cast<int>(plan.ops.size());
   std::vector<TaskArg> args(static_cast<size_t>(n_ops));
   for (int i = 0; i < n_ops; ++i) {

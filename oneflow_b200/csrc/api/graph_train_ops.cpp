@@ -277,7 +277,7 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
       for (int64_t r = 0; r < rows; ++r) acc += ldb(x, r * cols + c);
       y[c] += acc;
     }
-  } else if (t == "dropout" && !ir.training) {
+  } else if (t == "dropout" && (!ir.training || call_kind == 4)) {
     std::memcpy(addr(op.out[0]), addr(op.in[0]), static_cast<size_t>(n(op.in[0]) * 2));   // evaluation: the identity
   } else if (t == "dropout") {
     const float p = static_cast<float>(attr_float(op, "p", 0.5)), scale = 1.f / (1.f - p);
@@ -500,7 +500,7 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
                              attr_int(op, "in_offset", 0), c.data(), attr_int(op, "out_offset", 0), s));
   } else if (t == "column_sum") {
     ok(ofb_column_sum(addr(op.in[0]), static_cast<float*>(addr(op.out[0])), static_cast<int>(shp(op.in[0])[0]), static_cast<int>(shp(op.in[0])[1]), s));
-  } else if (t == "dropout" && !ir.training) {
+  } else if (t == "dropout" && (!ir.training || call_kind == 4)) {
     check_cuda(cudaMemcpyAsync(addr(op.out[0]), addr(op.in[0]), static_cast<size_t>(n(op.in[0]) * 2), cudaMemcpyDeviceToDevice, s), "cudaMemcpyAsync");
   } else if (t == "dropout") {
     ok(ofb_graph_dropout(addr(op.in[0]), addr(op.out[0]), n(op.in[0]), train.seed, call_counter_device(), static_cast<unsigned int>(attr_int(op, "index", 0)),

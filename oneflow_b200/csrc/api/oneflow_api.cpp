@@ -200,7 +200,14 @@ long long ofb_api_graph_input_numel(void* g, int i) { return static_cast<Graph*>
 long long ofb_api_graph_output_numel(void* g, int i) { return static_cast<Graph*>(g)->output_shape(i).elem_cnt(); }
 int ofb_api_graph_input_is_int64(void* g, int i) { return oneflow_api::graph_input_is_int64(*static_cast<Graph*>(g), i) ? 1 : 0; }
 
+static int run_or_evaluate(void* g, const void* const* inputs, int n_in, float* const* outputs, int n_out, bool evaluate);
 int ofb_api_graph_run(void* g, const void* const* inputs, int n_in, float* const* outputs, int n_out) {
+  return run_or_evaluate(g, inputs, n_in, outputs, n_out, false);
+}
+int ofb_api_graph_evaluate(void* g, const void* const* inputs, int n_in, float* const* outputs, int n_out) {
+  return run_or_evaluate(g, inputs, n_in, outputs, n_out, true);
+}
+static int run_or_evaluate(void* g, const void* const* inputs, int n_in, float* const* outputs, int n_out, bool evaluate) {
   try {
     auto* graph = static_cast<Graph*>(g);
     if (n_in != graph->num_inputs() || n_out != graph->num_outputs()) throw std::runtime_error("run: wrong number of inputs or outputs");
@@ -212,7 +219,7 @@ int ofb_api_graph_run(void* g, const void* const* inputs, int n_in, float* const
       else
         in.push_back(Tensor::from_buffer(static_cast<const float*>(inputs[i]), graph->input_shape(i), device));
     }
-    auto out = graph->Forward(in);
+    auto out = evaluate ? graph->Evaluate(in) : graph->Forward(in);
     for (int i = 0; i < n_out; ++i) {
       auto h = out[static_cast<size_t>(i)].to_host();
       std::memcpy(outputs[i], h.data(), h.size() * sizeof(float));

@@ -128,6 +128,9 @@ class Graph {
   static Graph LoadTraining(const std::string& dir, const TrainOptions& options, int device = 0, int n_streams = 2);
   Tensor Forward(const Tensor& input) const;
   std::vector<Tensor> Forward(const std::vector<Tensor>& inputs) const;
+  // Training graphs: the forward operators only, dropout switched off, nothing updated and no counter advanced (a
+  // validation loss between steps). On an inference graph it is Forward.
+  std::vector<Tensor> Evaluate(const std::vector<Tensor>& inputs) const;
   int64_t in_features() const;    // last axis of the first input
   int64_t out_features() const;   // last axis of the first output
   int num_inputs() const;
@@ -183,6 +186,8 @@ int ofb_api_graph_input_is_int64(void* graph, int i);
 long long ofb_api_graph_output_numel(void* graph, int i);
 // stats_out[7]: ops, tensors, activation bytes, arena bytes, dependencies, streams used, CUDA-graph replays of the current plan
 int ofb_api_graph_stats(void* graph, long long* stats_out);
+// As ofb_api_graph_run, through Graph::Evaluate.
+int ofb_api_graph_evaluate(void* graph, const void* const* inputs, int n_inputs, float* const* outputs, int n_outputs);
 // Training graphs (oneflow_api::Graph::LoadTraining); optimizer: "adamw" or "sgd".
 void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                   float eps, float weight_decay, float momentum);

@@ -639,6 +639,9 @@ class InferenceGraph:
 
     def run(self, *inputs):
         """Any number of inputs (float arrays for bf16 inputs, integer arrays for id inputs) -> list of flat fp32 outputs."""
+        return self._call(self.lib.ofb_api_graph_run, inputs)
+
+    def _call(self, entry, inputs):
         h = ctypes.c_void_p(self.h)
         if len(inputs) != self.num_inputs:
             raise ValueError(f"the graph takes {self.num_inputs} inputs")
@@ -653,7 +656,7 @@ class InferenceGraph:
         outs = [np.empty(self.lib.ofb_api_graph_output_numel(h, ctypes.c_int(i)), dtype=np.float32) for i in range(self.num_outputs)]
         in_ptrs = (ctypes.c_void_p * len(bufs))(*[b.ctypes.data for b in bufs])
         out_ptrs = (ctypes.c_void_p * len(outs))(*[o.ctypes.data for o in outs])
-        rc = self.lib.ofb_api_graph_run(h, in_ptrs, ctypes.c_int(len(bufs)), out_ptrs, ctypes.c_int(len(outs)))
+        rc = entry(h, in_ptrs, ctypes.c_int(len(bufs)), out_ptrs, ctypes.c_int(len(outs)))
         if rc != 0:
             raise RuntimeError(self.lib.ofb_api_last_error().decode())
         return outs
@@ -697,6 +700,10 @@ class TrainingGraph(InferenceGraph):
     def step(self, *inputs):
         outs = self.run(*inputs)
         return float(outs[0][0])
+
+    def evaluate(self, *inputs):
+        """The loss (first output) of the current weights on ``inputs``: forward operators only, dropout off, nothing updated."""
+        return float(self._call(self.lib.ofb_api_graph_evaluate, inputs)[0][0])
 
     @property
     def steps(self):

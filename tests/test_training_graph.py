@@ -650,3 +650,38 @@ def test_learning_rate_schedule_follows_warmup_and_cosine(tmp_path):
     with pytest.raises(RuntimeError, match="lr schedule"):
         g.set_lr_schedule("exponential")
     g.close()
+
+
+def test_evaluation_calls_run_the_forward_pass_only(tmp_path):
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.drop, self.fc2 = nn.Linear(32, 64), nn.Dropout(0.5), nn.Linear(64, 16)
+
+        def forward(self, x, y):
+            return F.cross_entropy(self.fc2(self.drop(F.gelu(self.fc1(x)))), y)
+
+    torch.manual_seed(19)
+    m = _bf16_weights(Net())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False, train_mode=True)
+    g = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, accumulation_steps=2, recompute_cheap_activations=True, seed=3)
+    m.eval()
+    before = g.parameters()
+    e0 = g.evaluate(x.numpy(), y.numpy())
+    want = float(m(x, y).detach())
+    assert abs(e0 - want) < 2e-2 * want                                  # dropout is off: the deterministic loss
+    assert g.evaluate(x.numpy(), y.numpy()) == e0 and g.steps == 0
+    assert all(np.array_equal(before[k], v) for k, v in g.parameters().items())
+    # evaluation between the two micro-batches of a step disturbs neither the accumulated gradients nor the mask sequence
+    ref = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, accumulation_steps=2, recompute_cheap_activations=True, seed=3)
+    for _ in range(2):
+        a0 = g.step(x.numpy(), y.numpy())
+        g.evaluate(x.numpy(), y.numpy())
+        a1 = g.step(x.numpy(), y.numpy())
+        assert (a0, a1) == (ref.step(x.numpy(), y.numpy()), ref.step(x.numpy(), y.numpy()))
+    pg, pr = g.parameters(), ref.parameters()
+    assert all(np.array_equal(pg[k], pr[k]) for k in pg)
+    assert g.evaluate(x.numpy(), y.numpy()) < e0
+    g.close()
+    ref.close()
