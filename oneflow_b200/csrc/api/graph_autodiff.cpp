@@ -367,6 +367,7 @@ void Builder::run() {
   ir.n_forward_ops = n_ops;
   for (int i = 0; i < n_ops; ++i) ir.ops[static_cast<size_t>(i)].attr["fwd"] = "1";   // what an evaluation call runs
   ir.recompute_cheap = opt.recompute_cheap_activations;
+  ir.recompute_full = opt.recompute_all_but_residual_stream;
   for (auto& op : out_ops) ir.ops.push_back(std::move(op));
   ir.training = true;
 }

@@ -47,6 +47,7 @@ struct IR {
   std::vector<int> masters;     // their fp32 master-weight state tensors
   int n_forward_ops = 0;        // operators before the first backward one
   bool recompute_cheap = false; // asks the recompute pass to run
+  bool recompute_full = false;  // ... for every operator off the residual stream
   std::vector<std::pair<std::string, int>> pass_report;   // rewriting passes that ran and how often each fired
 };
 

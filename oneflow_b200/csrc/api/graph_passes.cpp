@@ -12,6 +12,9 @@
 //                             the backward pass reads, and whose inputs are kept for the backward pass anyway, is run
 //                             again right before its first backward reader; the backward readers use the copy, so the
 //                             original dies with its last forward reader (activation checkpointing for the cheap part)
+//                             With recompute_all_but_residual_stream the same pass takes every operator (GEMMs and
+//                             attention included) whose result has a single forward reader: only the residual stream
+//                             survives the forward pass, and the copies pull in their producers transitively
 //   drop_dead_operators       operators none of whose outputs is read by an operator or returned
 //
 // ONEFLOW_API_PASSES=0 switches all of them off (the unfused plan is the reference the tests compare with).
@@ -75,11 +78,28 @@ bool recompute_cheap_activations(IR& ir) {
       if (r >= F && r != except_op) return true;
     return false;
   };
-  for (int i = 0; i < F && i < static_cast<int>(ir.ops.size()); ++i) {
+  const bool full = ir.recompute_full;
+  auto forward_readers = [&](int root) {
+    std::set<int> ops;   // an operator that reads several views of the storage (q, k, v) counts once
+    for (int r : tc.readers[static_cast<size_t>(root)])
+      if (r < F) ops.insert(r);
+    return static_cast<int>(ops.size());
+  };
+  // Last forward operator first: by the time an operator is looked at, the copies of its consumers exist, so the set of
+  // backward readers of its result is final and one copy serves them all.
+  for (int i = std::min(F, static_cast<int>(ir.ops.size())) - 1; i >= 0; --i) {
     const OpDef op = ir.ops[static_cast<size_t>(i)];
-    if (op.type != "unary" && op.type != "binary" && op.type != "layer_norm") continue;
+    if (full) {
+      // everything but the loss operators (their results are consumed at once), copies into shared storage and the residual
+      // additions (their results are the checkpoints)
+      if (op.type == "cross_entropy" || op.type == "mse" || op.type == "copy") continue;
+      if (op.type == "binary" && attr_int(op, "fn", 0) == 0 && attr_int(op, "bmode", 0) == 0) continue;
+    } else if (op.type != "unary" && op.type != "binary" && op.type != "layer_norm") {
+      continue;
+    }
     const int R = v.root(op.out[0]);
     if (!v.whole(op.out[0]) || tc.returned.count(R) || tc.writers[static_cast<size_t>(R)].size() != 1) continue;
+    if (full && forward_readers(R) > 1) continue;   // the residual stream: a checkpoint
     int first_reader = -1;
     for (int r : tc.readers[static_cast<size_t>(R)])
       if (r >= F && (first_reader < 0 || r < first_reader)) first_reader = r;
@@ -88,7 +108,7 @@ bool recompute_cheap_activations(IR& ir) {
     for (int t : op.in) {
       if (t < 0) continue;
       const int r = v.root(t);
-      if (r == R || !kept_for_backward(r, -1)) ok = false;
+      if (r == R || (!full && !kept_for_backward(r, -1))) ok = false;
       for (int w : tc.writers[static_cast<size_t>(r)])
         if (w > i && w < first_reader) ok = false;   // the input would have changed by then
     }
@@ -178,6 +198,9 @@ bool fuse_activation_backward(IR& ir) {
     if (ub.type != "unary_bwd" || j < static_cast<int>(i) || !act_name(attr_int(ub, "fn", 0))) continue;
     if (v.root(ub.in[1]) != t || !v.whole(ub.in[1]) || v.root(ub.in[0]) == t || !v.whole(ub.in[0]) || !v.whole(ub.out[0])) continue;
     if (tc.writers[static_cast<size_t>(v.root(ub.out[0]))].size() != 1) continue;
+    bool ready = true;   // the pre-activation must exist where the GEMM runs (a recomputed copy may be produced later)
+    for (int w : tc.writers[static_cast<size_t>(v.root(ub.in[0]))]) ready = ready && w < static_cast<int>(i);
+    if (!ready) continue;
     mm.in.push_back(ub.in[0]);
     mm.attr["act_grad"] = act_name(attr_int(ub, "fn", 0));
     mm.out = {ub.out[0]};
@@ -218,7 +241,7 @@ std::vector<std::pair<std::string, int>> run_graph_passes(IR& ir) {
     bool (*fn)(IR&);
   };
   // backward first: the forward pass must see which pre-activations a fused data-gradient GEMM still reads
-  if (ir.training && ir.recompute_cheap) {
+  if (ir.training && (ir.recompute_cheap || ir.recompute_full)) {
     int fired = 0;
     while (fired < 100000 && recompute_cheap_activations(ir)) ++fired;
     report.emplace_back("recompute_cheap_activations", fired);

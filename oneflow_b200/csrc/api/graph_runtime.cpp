@@ -981,6 +981,10 @@ std::shared_ptr<Graph::Impl> load_impl(const std::string& dir, int device, int n
     }
   }
   impl->ir.pass_report = run_graph_passes(impl->ir);
+  if (const char* dump_to = std::getenv("ONEFLOW_API_DUMP_IR")) {   // the graph as the plan compiler is about to see it
+    std::ofstream out(dump_to, std::ios::trunc);
+    out << ir_to_text(impl->ir);
+  }
   // parameters
   impl->params.resize(impl->ir.tensors.size());
   for (size_t i = 0; i < impl->ir.tensors.size(); ++i) {

@@ -105,6 +105,10 @@ struct TrainOptions {
   // Activation checkpointing for the cheap operators: outputs of element-wise operators and LayerNorms that only the
   // backward pass still needs are not kept; the backward pass recomputes them from their (kept) inputs.
   bool recompute_cheap_activations = false;
+  // Full activation checkpointing: only the residual stream (tensors with more than one forward reader), the inputs and the
+  // loss operator's results are kept; every other forward operator whose result the backward pass needs, GEMMs and attention
+  // included, runs again right before that part of the backward pass.
+  bool recompute_all_but_residual_stream = false;
   // Seed of the dropout operators (graphs exported in training mode). The mask of an operator is a function of (seed,
   // number of the call, operator): every call draws new masks, a run with the same seed draws the same sequence.
   uint64_t seed = 0;
@@ -193,7 +197,7 @@ void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, co
                                   float eps, float weight_decay, float momentum);
 void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                      float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps);
-// bit 0 of flags: recompute cheap activations in the backward pass
+// flags: bit 0 recompute cheap activations in the backward pass, bit 1 recompute everything but the residual stream
 void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                         float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps, int flags);
 int ofb_api_graph_num_parameters(void* graph);

@@ -685,3 +685,30 @@ def test_evaluation_calls_run_the_forward_pass_only(tmp_path):
     assert g.evaluate(x.numpy(), y.numpy()) < e0
     g.close()
     ref.close()
+
+
+def test_full_activation_checkpointing_keeps_only_the_residual_stream(tmp_path):
+    """Every forward operator off the residual stream, GEMMs and attention included, runs again in the backward pass; the
+    copies pull in their producers, each operator is copied once, and the losses stay those of the plain plan."""
+    from oneflow_b200.utils.bench_graph_runtime import GPT
+    torch.manual_seed(20)
+    m = _bf16_weights(GPT(4, 64, 1, 96, 64))
+    ids, tgt = torch.randint(0, 96, (8, 64)), torch.randint(0, 96, (8, 64))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path), fuse=False, train_mode=True)
+    kw = dict(device=-1, optimizer="sgd", lr=2e-2, seed=9)
+    plain = E.TrainingGraph(d, **kw)
+    cheap = E.TrainingGraph(d, recompute_cheap_activations=True, **kw)
+    full = E.TrainingGraph(d, recompute_all_but_residual_stream=True, **kw)
+    assert full.stats()["arena_bytes"] < 0.6 * cheap.stats()["arena_bytes"] < 0.6 * plain.stats()["arena_bytes"]
+    text = full.dump()
+    count = lambda t: sum(1 for line in text.splitlines() if line.startswith("op " + t + " "))
+    assert count("attention") == 2 * 4 and count("attention_bwd") == 4           # each attention once more, not more
+    assert count("embedding") == 2                                                  # the first residual value is a checkpoint
+    for _ in range(3):
+        a, b = full.step(ids.numpy(), tgt.numpy()), plain.step(ids.numpy(), tgt.numpy())
+        assert abs(a - b) < 1e-2 * max(abs(b), 1.0)
+    pf, pp = full.parameters(), plain.parameters()
+    for k in pf:
+        assert np.abs(pf[k] - pp[k]).max() < 2e-2 * (np.abs(pp[k]).max() + 1e-3), k
+    for g in (plain, cheap, full):
+        g.close()
