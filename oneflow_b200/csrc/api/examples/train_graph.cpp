@@ -2,7 +2,7 @@
 // run a number of steps on inputs read from raw files, print the loss of every step, save the result as a directory that
 // loads again (for inference, or to continue training). Built by the tests against libofb_api.so:
 //     g++ -std=c++17 train_graph.cpp -I<csrc/api> -L<lib> -lofb_api -Wl,-rpath,<lib> -o train_graph
-//     ./train_graph <graph dir> <device: -1 host, >= 0 GPU> <steps> <learning rate> <save dir or -> <input file per graph input ...>
+//     ./train_graph [--recompute=cheap|full] <graph dir> <device: -1 host, >= 0 GPU> <steps> <learning rate> <save dir or -> <input file per graph input ...>
 // An input file holds little-endian float32 values (for bf16 graph inputs) or int64 values (for id inputs) in the exported
 // shape; the same batch is used for every step.
 #include <cstdio>
@@ -27,6 +27,12 @@ static std::vector<T> read_file(const std::string& path, int64_t n) {
 }
 
 int main(int argc, char** argv) {
+  std::string recompute;
+  if (argc > 1 && std::string(argv[1]).rfind("--recompute=", 0) == 0) {
+    recompute = std::string(argv[1]).substr(12);
+    --argc;
+    ++argv;
+  }
   if (argc < 7) {
     std::cerr << "usage: train_graph <dir> <device> <steps> <lr> <save dir or -> <input files...>\n";
     return 2;
@@ -36,6 +42,8 @@ int main(int argc, char** argv) {
     oneflow_api::TrainOptions options;
     options.optimizer = "adamw";
     options.lr = static_cast<float>(std::atof(argv[4]));
+    options.recompute_cheap_activations = recompute == "cheap";
+    options.recompute_all_but_residual_stream = recompute == "full";
     oneflow_api::Graph graph = oneflow_api::Graph::LoadTraining(argv[1], options, device, 2);
     if (argc - 6 != graph.num_inputs()) {
       std::cerr << "the graph takes " << graph.num_inputs() << " inputs\n";
