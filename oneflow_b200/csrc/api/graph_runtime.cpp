@@ -341,6 +341,8 @@ void Graph::Impl::compile(int64_t rows) {
         if (d < 0 || d > (int64_t{1} << 40) || (d > 0 && total > (int64_t{1} << 40) / d)) throw std::runtime_error("tensor " + std::to_string(i) + ": absurd size");
         total *= d;
       }
+      // no single tensor can be larger than the memory of the device (180 GB) or of any host this runs on
+      if (total > (int64_t{1} << 38) / SizeOf(ir.tensors[i].dtype)) throw std::runtime_error("tensor " + std::to_string(i) + ": larger than 256 GiB");
     }
     const TensorDef& t = ir.tensors[i];
     if (t.alias_of >= 0) {
@@ -504,6 +506,7 @@ void Graph::Impl::compile(int64_t rows) {
       p->stats.activation_bytes += root_bytes(r);
     }
     po.workspace_bytes = workspace_for(*po.def, *p);
+    if (po.workspace_bytes < 0 || po.workspace_bytes > (int64_t{1} << 38)) throw std::runtime_error("operator " + po.def->type + ": absurd scratch size");
     if (po.workspace_bytes > 0) {
       po.workspace = ofc_allocator_alloc(al, po.workspace_bytes);
       if (!po.workspace) throw std::runtime_error(std::string("allocator: ") + ofc_last_error());
