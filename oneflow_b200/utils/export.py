@@ -234,6 +234,8 @@ class _GraphEmitter(torch.fx.Interpreter):
                 return self._unary(t, y, "add_scalar", -c, inplace)
             if fn == "div" and torch.is_tensor(a):
                 return self._unary(t, y, "scale", 1.0 / c, inplace)
+            if fn == "sub" and not inplace:                      # c - t = (-t) + c
+                return self._unary(self._unary(t, -t, "scale", -1.0), y, "add_scalar", c)
             raise ValueError(f"cannot export scalar {fn} with the tensor on the right")
         if tuple(a.shape) != tuple(y.shape):
             if not inplace and fn in ("add", "mul", "maximum", "minimum") and tuple(b.shape) == tuple(y.shape):
@@ -254,7 +256,12 @@ class _GraphEmitter(torch.fx.Interpreter):
         elif b.dim() == y.dim() and tail and tuple(b.shape[:len(tail)]) == tuple(y.shape[:len(tail)]) and b.numel() == math.prod(tail):
             mode, cols = 2, y.numel() // b.numel()      # one value of b per leading index
         else:
-            raise ValueError(f"cannot export {fn} of shapes {tuple(a.shape)} and {tuple(b.shape)}")
+            # any other broadcast (axes of length 1 in the middle, ...): the expanded operand is materialised by a strided copy
+            try:
+                b = b.expand(y.shape)
+            except RuntimeError:
+                raise ValueError(f"cannot export {fn} of shapes {tuple(a.shape)} and {tuple(b.shape)}") from None
+            mode = 0
         ia, ib = self._operand(a), self._operand(b)
         if inplace:
             if not a.is_contiguous():

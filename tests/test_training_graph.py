@@ -714,3 +714,59 @@ def test_full_activation_checkpointing_keeps_only_the_residual_stream(tmp_path):
         assert np.abs(pf[k] - pp[k]).max() < 2e-2 * (np.abs(pp[k]).max() + 1e-3), k
     for g in (plain, cheap, full):
         g.close()
+
+
+def test_bert_style_classifier_trains_natively(tmp_path):
+    """A second model family through the native compiler: three embedding tables, post-LN encoder layers with the attention
+    written out (matmul, scale, additive padding mask broadcast over heads and queries, softmax, matmul), tanh pooler over the
+    first token, classification loss. Exercises scalar-minus-tensor, the general broadcast, permuted views and a row slice."""
+    import math
+
+    class Layer(nn.Module):
+        def __init__(self, d, h):
+            super().__init__()
+            self.q, self.k, self.v, self.o = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
+            self.ln1, self.ln2, self.fc1, self.fc2, self.h = nn.LayerNorm(d), nn.LayerNorm(d), nn.Linear(d, 4 * d), nn.Linear(4 * d, d), h
+
+        def forward(self, x, bias):
+            B, S, D = x.shape
+            heads = lambda t: t.view(B, S, self.h, D // self.h).transpose(1, 2)
+            q, k, v = heads(self.q(x)), heads(self.k(x)), heads(self.v(x))
+            scores = torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(D // self.h) + bias
+            a = torch.matmul(torch.softmax(scores, -1), v).transpose(1, 2).reshape(B, S, D)
+            x = self.ln1(x + self.o(a))
+            return self.ln2(x + self.fc2(F.gelu(self.fc1(x))))
+
+    class Bert(nn.Module):
+        def __init__(self, layers=2, d=64, h=2, vocab=96, seq=16, classes=4):
+            super().__init__()
+            self.tok, self.pos, self.typ, self.ln = nn.Embedding(vocab, d), nn.Embedding(seq, d), nn.Embedding(2, d), nn.LayerNorm(d)
+            self.layers = nn.ModuleList([Layer(d, h) for _ in range(layers)])
+            self.pool, self.cls = nn.Linear(d, d), nn.Linear(d, classes)
+
+        def forward(self, ids, types, mask, labels):
+            x = self.ln(self.tok(ids) + self.pos(torch.arange(ids.shape[1])) + self.typ(types))
+            bias = (1.0 - mask[:, None, None, :]) * -1e4
+            for layer in self.layers:
+                x = layer(x, bias)
+            return F.cross_entropy(self.cls(torch.tanh(self.pool(x[:, 0]))), labels)
+
+    torch.manual_seed(21)
+    m = _bf16_weights(Bert())
+    ids, types, labels = torch.randint(0, 96, (4, 16)), torch.randint(0, 2, (4, 16)), torch.randint(0, 4, (4,))
+    mask = (torch.rand(4, 16) > 0.2).float()
+    mask[:, 0] = 1
+    loss, grads = _grads_by_unit_sgd(m, (ids, types, mask, labels), str(tmp_path))
+    ref = m(ids, types, mask, labels)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for name, p in m.named_parameters():
+        r = p.grad.numpy().reshape(-1)
+        # key biases shift every score of a row alike: their true gradient is zero, what is left is rounding
+        tol = 3e-2 * (np.abs(r).max() + 1e-6) if ".k.bias" not in name else 1e-3 * scale
+        assert np.abs(grads[name] - r).max() <= tol, name
+    g = E.TrainingGraph(str(tmp_path), device=-1, optimizer="adamw", lr=3e-3)
+    losses = [g.step(ids.numpy(), types.numpy(), mask.numpy(), labels.numpy()) for _ in range(8)]
+    assert losses[-1] < 0.5 * losses[0]
+    g.close()
