@@ -770,3 +770,25 @@ def test_bert_style_classifier_trains_natively(tmp_path):
     losses = [g.step(ids.numpy(), types.numpy(), mask.numpy(), labels.numpy()) for _ in range(8)]
     assert losses[-1] < 0.5 * losses[0]
     g.close()
+
+
+def test_the_compiled_step_is_deterministic_and_can_be_dumped(tmp_path, monkeypatch):
+    """Two loads of one directory give the same operator list, the same plan statistics and, on the host runtime, the same
+    bits; ONEFLOW_API_DUMP_IR writes the list the plan compiler sees."""
+    torch.manual_seed(22)
+    m = _bf16_weights(TiedLM(d=64, heads=1, vocab=96, seq=16))
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    d = E.export_graph(m, (ids, tgt), str(tmp_path / "g"), fuse=False, train_mode=True)
+    monkeypatch.setenv("ONEFLOW_API_DUMP_IR", str(tmp_path / "ir.txt"))
+    a = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, clip_grad_norm=1.0, recompute_cheap_activations=True, seed=4)
+    monkeypatch.delenv("ONEFLOW_API_DUMP_IR")
+    b = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, clip_grad_norm=1.0, recompute_cheap_activations=True, seed=4, n_streams=1)
+    assert a.dump() == b.dump() == open(str(tmp_path / "ir.txt")).read()
+    sa, sb = a.stats(), b.stats()
+    assert sa["ops"] == sb["ops"] and sa["activation_bytes"] == sb["activation_bytes"] and (sa["streams_used"], sb["streams_used"]) == (2, 1)
+    # one stream or two, the numbers are the same: the dependency edges order everything that shares data or memory
+    assert [a.step(ids.numpy(), tgt.numpy()) for _ in range(4)] == [b.step(ids.numpy(), tgt.numpy()) for _ in range(4)]
+    pa, pb = a.parameters(), b.parameters()
+    assert all(np.array_equal(pa[k], pb[k]) for k in pa)
+    a.close()
+    b.close()
