@@ -53,18 +53,21 @@ def _copies(nbytes_per_set):
     return max(2, math.ceil((256 << 20) / max(nbytes_per_set, 1)))
 
 
-def bench_gemm(m, n, k, layout="mk,nk", iters=20, bn=0, bias=False, act=0):
+def bench_gemm(m, n, k, layout="mk,nk", iters=20, bn=0, bias=False, act=0, out_f32=False, accumulate=False):
     al, bl = layout.split(",")
     dev, dt = "cuda", torch.bfloat16
     nset = min(_copies((m * k + n * k + m * n) * 2), 8)
     As = [torch.randn((m, k) if al == "mk" else (k, m), device=dev, dtype=dt) for _ in range(nset)]
     Bs = [torch.randn((n, k) if bl == "nk" else (k, n), device=dev, dtype=dt) for _ in range(nset)]
-    out = torch.empty(m, n, device=dev, dtype=dt)
+    odt = torch.float32 if out_f32 else dt
+    outs = [torch.zeros(m, n, device=dev, dtype=odt) for _ in range(nset if accumulate else 1)]   # accumulation reads the output too
     b = torch.randn(n, device=dev, dtype=dt) if bias else None
-    ms = time_ms(lambda i: G.gemm(As[i % nset], Bs[i % nset], a_layout=al, b_layout=bl, out=out, bn=bn, bias=b, act=act), iters)
+    ms = time_ms(lambda i: G.gemm(As[i % nset], Bs[i % nset], a_layout=al, b_layout=bl, out=outs[i % len(outs)], out_dtype=odt, bn=bn, bias=b,
+                                  act=act, accumulate=accumulate), iters)
     tf = 2.0 * m * n * k / ms / 1e9
     pk = peaks()
-    return {"kernel": "gemm_bf16_tcgen05", "m": m, "n": n, "k": k, "layout": layout, "bn": bn, "ms": ms, "tflops": tf,
+    return {"kernel": "gemm_bf16_tcgen05", "m": m, "n": n, "k": k, "layout": layout, "bn": bn, "out": "f32" if out_f32 else "bf16",
+            "accumulate": bool(accumulate), "ms": ms, "tflops": tf,
             "frac_of_" + pk["source"] + "_cublas_burst": tf / pk["bf16_tflops"]}
 
 
@@ -165,6 +168,8 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--layout", default="mk,nk")
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--out-f32", action="store_true", help="gemm: fp32 output (weight-gradient form)")
+    ap.add_argument("--accumulate", action="store_true", help="gemm: C += A B (read-add-write epilogue)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=2048)
@@ -178,7 +183,7 @@ def main():
     a = ap.parse_args()
     out = []
     if a.kernel in ("gemm",):
-        out.append(bench_gemm(a.m, a.n, a.k, a.layout, a.iters, a.bn))
+        out.append(bench_gemm(a.m, a.n, a.k, a.layout, a.iters, a.bn, out_f32=a.out_f32, accumulate=a.accumulate))
     if a.kernel in ("fmha",):
         out.append(bench_fmha(a.batch, a.seq, a.heads, a.dim, a.causal, a.iters))
     if a.kernel in ("layer_norm",):
