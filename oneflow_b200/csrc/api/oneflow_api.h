@@ -1,4 +1,4 @@
-// C++ inference API: load an exported network and run it without Python.
+// C++ graph API: load an exported network and run it, or train it, without Python.
 //
 //   #include "oneflow_api.h"
 //   auto graph = oneflow_api::Graph::Load("model_dir");            // reads graph.txt + raw weight files, compiles a plan
@@ -21,7 +21,14 @@
 //     on its producer's stream, independent branches go to other streams; on the GPU each stream is a CUDA stream and
 //     cross-stream dependencies are CUDA events.
 // `device` >= 0 runs the sm_100a kernels of libofb_kernels on that GPU; device = -1 runs a plain host implementation of
-// the same operators (fp32 arithmetic, bf16 storage), which is what the tests without a GPU use.
+// the same operators (fp32 arithmetic, bf16 storage), which is what the tests without a GPU use. From its second run on a
+// plan on the GPU is replayed as one CUDA graph.
+//
+// Training: `Graph::LoadTraining(dir, options)` takes a graph whose first output is a scalar loss, appends the backward and
+// optimizer operators (graph_autodiff.cpp), rewrites the result (graph_passes.cpp: activation and activation-gradient into
+// GEMM epilogues, optional recomputation, dead operators) and compiles forward + backward + update into one plan; every
+// Forward call is then one training step (TrainOptions below: optimizer, clipping, accumulation, checkpointing, dropout
+// seed, learning-rate schedule; Evaluate, Save / Restore, parameter read-back on Graph).
 //
 // Reference counterpart: oneflow/api/cpp/ (oneflow_api::Tensor, Shape, Graph::Load(dir) running a saved nn.Graph through
 // the job -> plan compiler and the actor runtime).
