@@ -610,8 +610,37 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
   } else if (t == "copy") {
     const int x = in(0);
     const auto is = int_list(attr_str(op, "in_strides", "")), sh = int_list(attr_str(op, "shape", ""));
-    for (size_t d = 0; d < sh.size(); ++d)
-      if (sh[d] > 1 && is[d] == 0) refuse(op, "reads a broadcast (zero-stride) view; its gradient is not built");
+    bool broadcast = false;
+    for (size_t d = 0; d < sh.size(); ++d) broadcast = broadcast || (sh[d] > 1 && is[d] == 0);
+    if (broadcast) {
+      // A source repeated over leading axes (a class token or a table expanded over the batch): its gradient is the sum of
+      // the output gradient over those axes. The output gradient's view is gathered into a [repeats, block] matrix, summed
+      // over its rows in fp32 and added to the source's gradient. Broadcasts in inner axes are not built.
+      size_t k = 0;
+      while (k < sh.size() && (sh[k] == 1 || is[k] == 0)) ++k;
+      int64_t rows = 1, cols = 1, expect = 1;
+      for (size_t d = 0; d < k; ++d) rows *= sh[d];
+      bool dense = true;
+      for (size_t d = sh.size(); d-- > k;) {
+        if (sh[d] > 1 && is[d] != expect) dense = false;
+        expect *= sh[d];
+        cols *= sh[d];
+      }
+      if (!dense || k == sh.size()) refuse(op, "reads a view that is broadcast in an inner axis; its gradient is not built");
+      const int gathered = new_root(DType::kBFloat16, rows * cols);
+      std::vector<int64_t> dense_strides(sh.size(), 1);
+      for (size_t d = sh.size() - 1; d-- > 0;) dense_strides[d] = dense_strides[d + 1] * sh[d + 1];
+      emit("copy", {root(dy)}, {gathered},
+           {{"shape", attr_str(op, "shape", "")}, {"in_strides", attr_str(op, "out_strides", "")},
+            {"in_offset", std::to_string(attr_int(op, "out_offset", 0) + abs_off(y))}, {"out_strides", join(dense_strides)}, {"out_offset", "0"}});
+      const int summed = new_root(DType::kFloat, cols);
+      emit("fill", {}, {summed}, {{"value", "0"}});
+      emit("column_sum", {view2d(gathered, rows, cols)}, {summed});
+      emit("copy", {summed}, {grad_storage(root(x))},
+           {{"shape", std::to_string(cols)}, {"in_strides", "1"}, {"in_offset", "0"}, {"out_strides", "1"},
+            {"out_offset", std::to_string(attr_int(op, "in_offset", 0) + abs_off(x))}, {"accumulate", "1"}});
+      return;
+    }
     emit("copy", {root(dy)}, {grad_storage(root(x))},
          {{"shape", attr_str(op, "shape", "")}, {"in_strides", attr_str(op, "out_strides", "")},
           {"in_offset", std::to_string(attr_int(op, "out_offset", 0) + abs_off(y))}, {"out_strides", attr_str(op, "in_strides", "")},

@@ -792,3 +792,52 @@ def test_the_compiled_step_is_deterministic_and_can_be_dumped(tmp_path, monkeypa
     assert all(np.array_equal(pa[k], pb[k]) for k in pa)
     a.close()
     b.close()
+
+
+def test_vit_style_classifier_trains_natively(tmp_path):
+    """A third model family: patch projection, a class token broadcast over the batch and concatenated in front, a learned
+    position table added with a leading broadcast axis, bidirectional attention, classification from the class token. The
+    class token's gradient is a sum over the batch axis of a strided view of the concatenation's gradient."""
+
+    class Block(nn.Module):
+        def __init__(self, d, heads):
+            super().__init__()
+            self.ln1, self.qkv, self.proj = nn.LayerNorm(d), nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.ln2, self.fc1, self.fc2, self.heads = nn.LayerNorm(d), nn.Linear(d, 4 * d), nn.Linear(4 * d, d), heads
+
+        def forward(self, x):
+            B, S, _ = x.shape
+            q, k, v = self.qkv(self.ln1(x)).view(B, S, 3, self.heads, -1).unbind(2)
+            a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+            x = x + self.proj(a.transpose(1, 2).reshape(B, S, -1))
+            return x + self.fc2(F.gelu(self.fc1(self.ln2(x))))
+
+    class ViT(nn.Module):
+        def __init__(self, d=64, patches=15, patch_dim=48, classes=8):
+            super().__init__()
+            self.embed = nn.Linear(patch_dim, d)
+            self.cls = nn.Parameter(torch.randn(1, 1, d) * 0.1)
+            self.pos = nn.Parameter(torch.randn(1, patches + 1, d) * 0.1)
+            self.blocks = nn.ModuleList([Block(d, 1) for _ in range(2)])
+            self.ln, self.head = nn.LayerNorm(d), nn.Linear(d, classes)
+
+        def forward(self, patches, labels):
+            x = self.embed(patches)
+            x = torch.cat([self.cls.expand(x.shape[0], -1, -1), x], dim=1) + self.pos
+            for block in self.blocks:
+                x = block(x)
+            return F.cross_entropy(self.head(self.ln(x)[:, 0]), labels)
+
+    torch.manual_seed(23)
+    m = _bf16_weights(ViT())
+    patches, labels = torch.randn(4, 15, 48).bfloat16().float(), torch.randint(0, 8, (4,))
+    loss, grads = _grads_by_unit_sgd(m, (patches, labels), str(tmp_path))
+    ref = m(patches, labels)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    assert float(m.embed.weight.grad.abs().max()) > 0 and float(m.cls.grad.abs().max()) > 0
+    _check_grads(m, grads)
+    g = E.TrainingGraph(str(tmp_path), device=-1, optimizer="adamw", lr=3e-3)
+    losses = [g.step(patches.numpy(), labels.numpy()) for _ in range(8)]
+    assert losses[-1] < 0.5 * losses[0]
+    g.close()
