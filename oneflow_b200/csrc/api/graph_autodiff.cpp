@@ -132,7 +132,7 @@ struct Builder {
     if (grad_root[static_cast<size_t>(r)] >= 0) return grad_root[static_cast<size_t>(r)];
     const bool param = ir.tensors[static_cast<size_t>(r)].kind == 1;
     // with gradient accumulation a parameter gradient outlives the call: persistent storage, cleared on the first micro-batch only
-    const bool persistent = param && opt.accumulation_steps > 1;
+    const bool persistent = param && (opt.accumulation_steps > 1 || opt.external_gradient_reduction);
     const int g = new_root(param ? DType::kFloat : DType::kBFloat16, count(r), persistent ? 3 : 2);
     grad_root[static_cast<size_t>(r)] = g;
     if (mode[static_cast<size_t>(r)] != Mode::kDirect && mode[static_cast<size_t>(r)] != Mode::kResidualLayerNorm) {
@@ -290,7 +290,8 @@ void Builder::run() {
       // gradient: no zero fill, no read-modify-write in the GEMM epilogue. Everything else (tied weights, bias column sums,
       // embedding scatter-adds, gradients kept across micro-batches) accumulates into a cleared buffer.
       const bool overwrites = (first.type == "linear" && u[0].slot == 1) || first.type == "matmul" || (first.type == "layer_norm" && u[0].slot >= 1);
-      mode[r] = opt.accumulation_steps == 1 && u.size() == 1 && overwrites && whole(u[0].tensor) ? Mode::kDirect : Mode::kAccumulate;
+      const bool kept_across_calls = opt.accumulation_steps > 1 || opt.external_gradient_reduction;
+      mode[r] = !kept_across_calls && u.size() == 1 && overwrites && whole(u[0].tensor) ? Mode::kDirect : Mode::kAccumulate;
       continue;
     }
     if (u.size() == 1 && first.type != "copy" && whole(u[0].tensor)) {
@@ -344,12 +345,13 @@ void Builder::run() {
   if (kept.empty()) throw std::runtime_error("training graph: no trainable parameter is connected to the loss");
   ir.trainable = kept;
   ir.masters = masters;
+  ir.grad_tensors = grads;
   std::vector<int> outs = params;
   outs.insert(outs.end(), masters.begin(), masters.end());
   outs.insert(outs.end(), s1.begin(), s1.end());
   outs.insert(outs.end(), s2.begin(), s2.end());
   std::map<std::string, std::string> when;
-  if (opt.accumulation_steps > 1) when["when"] = "last";
+  if (opt.accumulation_steps > 1 || opt.external_gradient_reduction) when["when"] = "last";
   std::vector<int> update_in = grads;
   std::map<std::string, std::string> uattr = {{"n", std::to_string(params.size())}, {"states", std::to_string((s1.empty() ? 0 : 1) + (s2.empty() ? 0 : 1))}};
   if (opt.clip_grad_norm > 0.f) {

@@ -45,6 +45,7 @@ struct IR {
   bool training = false;
   std::vector<int> trainable;   // parameter roots that get updated, in export order
   std::vector<int> masters;     // their fp32 master-weight state tensors
+  std::vector<int> grad_tensors;  // their fp32 gradient buffers (persistent only with accumulation or external reduction)
   int n_forward_ops = 0;        // operators before the first backward one
   bool recompute_cheap = false; // asks the recompute pass to run
   bool recompute_full = false;  // ... for every operator off the residual stream
@@ -153,8 +154,9 @@ struct Graph::Impl {
   std::vector<cudaEvent_t> join_events;
   int runs_of_plan[4] = {0, 0, 0, 0};
   int micro_step = 0;     // position inside the current optimizer step
-  int call_kind = 3;      // of the running call; 4 = evaluation (forward operators only, never recorded)
-  std::vector<Tensor> run(const std::vector<Tensor>& inputs, bool evaluate, const Graph& self);
+  int call_kind = 3;      // of the running call; 4 = evaluation (forward operators only), 8 = update only; neither is recorded
+  enum RunMode { kStep = 0, kEvaluate = 1, kUpdateOnly = 2 };
+  std::vector<Tensor> run(const std::vector<Tensor>& inputs, int mode, const Graph& self);
   int64_t graph_replays = 0;
   bool graph_disabled = false;
   // training graphs: hyper-parameters read by the update operator at launch time, steps taken so far
@@ -215,6 +217,7 @@ struct Graph::Impl {
   bool op_enabled(const OpDef& op) const {
     if (call_kind == 4) return op.attr.count("fwd") != 0;
     auto it = op.attr.find("when");
+    if (call_kind == 8) return it != op.attr.end() && it->second == "last";
     if (it == op.attr.end()) return true;
     return it->second == "first" ? (call_kind & 1) != 0 : (call_kind & 2) != 0;
   }

@@ -1203,13 +1203,41 @@ void Graph::BindRows(int64_t rows) {
 
 Tensor Graph::Forward(const Tensor& input) const { return Forward(std::vector<Tensor>{input}).at(0); }
 
-std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const { return impl_->run(inputs, false, *this); }
-std::vector<Tensor> Graph::Evaluate(const std::vector<Tensor>& inputs) const { return impl_->run(inputs, impl_->ir.training, *this); }
+std::vector<Tensor> Graph::Forward(const std::vector<Tensor>& inputs) const { return impl_->run(inputs, Impl::kStep, *this); }
+std::vector<Tensor> Graph::Evaluate(const std::vector<Tensor>& inputs) const {
+  return impl_->run(inputs, impl_->ir.training ? Impl::kEvaluate : Impl::kStep, *this);
+}
+void Graph::ApplyUpdate() {
+  if (!impl_->ir.training || !impl_->train.external_gradient_reduction) throw std::runtime_error("ApplyUpdate: the graph was not loaded with external_gradient_reduction");
+  impl_->run({}, Impl::kUpdateOnly, *this);
+}
+std::vector<float> Graph::gradient(int i) const {
+  Impl& im = *impl_;
+  std::lock_guard<std::mutex> g(im.run_mu);
+  if (!im.train.external_gradient_reduction) throw std::runtime_error("gradient: the graph was not loaded with external_gradient_reduction");
+  const int t = im.ir.grad_tensors.at(static_cast<size_t>(i));
+  std::vector<float> out(static_cast<size_t>(numel(im.ir.tensors[static_cast<size_t>(t)].shape)));
+  if (im.device >= 0) check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+  copy_out(out.data(), im.params[static_cast<size_t>(t)].get(), out.size() * 4, im.device);
+  return out;
+}
+void Graph::set_gradient(int i, const float* values, int64_t count) {
+  Impl& im = *impl_;
+  std::lock_guard<std::mutex> g(im.run_mu);
+  if (!im.train.external_gradient_reduction) throw std::runtime_error("set_gradient: the graph was not loaded with external_gradient_reduction");
+  const int t = im.ir.grad_tensors.at(static_cast<size_t>(i));
+  if (count != numel(im.ir.tensors[static_cast<size_t>(t)].shape)) throw std::runtime_error("set_gradient: wrong number of elements");
+  if (im.device >= 0) check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
+  copy_in(im.params[static_cast<size_t>(t)].get(), values, static_cast<size_t>(count) * 4, im.device);
+}
 
-std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, bool evaluate, const Graph& self) {
+std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, int mode, const Graph& self) {
   Impl& im = *this;
   std::lock_guard<std::mutex> run_guard(im.run_mu);
-  if (inputs.size() != im.ir.inputs.size()) throw std::runtime_error("Forward: wrong number of inputs");
+  const bool evaluate = mode == kEvaluate, update_only = mode == kUpdateOnly;
+  if (update_only && im.micro_step == 0) throw std::runtime_error("ApplyUpdate: no gradients have been accumulated since the last update");
+  if (!update_only && inputs.size() != im.ir.inputs.size()) throw std::runtime_error("Forward: wrong number of inputs");
+  if (im.device >= 0) check_cuda(cudaSetDevice(im.device), "cudaSetDevice");
   if (im.ir.dynamic_rows) {
     const int64_t feat = self.in_features();
     const int64_t rows = inputs[0].shape().elem_cnt() / (feat > 0 ? feat : 1);
@@ -1240,12 +1268,18 @@ std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, bool eva
     std::lock_guard<std::mutex> g(im.err_mu);
     im.error.clear();
   }
-  im.call_kind = evaluate ? 4 : 3;
+  im.call_kind = evaluate ? 4 : (update_only ? 8 : 3);
   if (im.ir.training && !evaluate) {
     const int k = std::max(1, im.train.accumulation_steps);
-    im.call_kind = (im.micro_step == 0 ? 1 : 0) | (im.micro_step == k - 1 ? 2 : 0);
-    if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
-    ++im.call_counter;                          // dropout masks are a function of the call number
+    if (update_only) {
+      ++im.train_steps;
+    } else if (im.train.external_gradient_reduction) {
+      im.call_kind = im.micro_step == 0 ? 1 : 0;   // never the updating kind: ApplyUpdate does that
+    } else {
+      im.call_kind = (im.micro_step == 0 ? 1 : 0) | (im.micro_step == k - 1 ? 2 : 0);
+      if (im.call_kind & 2) ++im.train_steps;   // the update operator of this call sees the 1-based step number
+    }
+    if (!update_only) ++im.call_counter;        // dropout masks are a function of the call number
     if (im.device >= 0) {
       im.step_scalars_host[0] = im.scheduled_lr(std::max<int64_t>(im.train_steps, 1));
       im.step_scalars_host[1] = 1.f - std::pow(im.train.beta1, static_cast<float>(im.train_steps));
@@ -1270,7 +1304,7 @@ std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, bool eva
     }
   }
   if (im.call_kind < 4) ++im.runs_of_plan[im.call_kind];
-  if (im.ir.training && !evaluate) im.micro_step = (im.call_kind & 2) ? 0 : im.micro_step + 1;
+  if (im.ir.training && !evaluate) im.micro_step = (update_only || (im.call_kind & 2)) ? 0 : im.micro_step + 1;
   const int n_ops = replayed ? 0 : static_cast<int>(plan.ops.size());
   std::vector<TaskArg> args(static_cast<size_t>(n_ops));
   for (int i = 0; i < n_ops; ++i) {
@@ -1288,6 +1322,7 @@ std::vector<Tensor> Graph::Impl::run(const std::vector<Tensor>& inputs, bool eva
   }
   if (im.failed()) throw std::runtime_error(im.error);
   std::vector<Tensor> outs;
+  if (update_only) return outs;
   for (int t : im.ir.outputs) {
     const TensorDef& def = im.ir.tensors[static_cast<size_t>(t)];
     Tensor o = Tensor::empty(Shape(plan.shape[static_cast<size_t>(t)]), im.device, def.dtype);

@@ -271,6 +271,7 @@ void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_strea
     o.accumulation_steps = accumulation_steps;
     o.recompute_cheap_activations = (flags & 1) != 0;
     o.recompute_all_but_residual_stream = (flags & 2) != 0;
+    o.external_gradient_reduction = (flags & 4) != 0;
     return new Graph(Graph::LoadTraining(dir, o, device, n_streams));
   } catch (const std::exception& e) {
     oneflow_api::detail::g_error = e.what();
@@ -304,6 +305,34 @@ int ofb_api_graph_parameter_read(void* g, int i, float* out) {
   try {
     const auto v = static_cast<Graph*>(g)->parameter(i);
     std::memcpy(out, v.data(), v.size() * sizeof(float));
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_gradient_read(void* g, int i, float* out) {
+  try {
+    const auto v = static_cast<Graph*>(g)->gradient(i);
+    std::memcpy(out, v.data(), v.size() * sizeof(float));
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_gradient_write(void* g, int i, const float* values, long long count) {
+  try {
+    static_cast<Graph*>(g)->set_gradient(i, values, count);
+    return 0;
+  } catch (const std::exception& e) {
+    oneflow_api::detail::g_error = e.what();
+    return -1;
+  }
+}
+int ofb_api_graph_apply_update(void* g) {
+  try {
+    static_cast<Graph*>(g)->ApplyUpdate();
     return 0;
   } catch (const std::exception& e) {
     oneflow_api::detail::g_error = e.what();

@@ -119,6 +119,11 @@ struct TrainOptions {
   // Seed of the dropout operators (graphs exported in training mode). The mask of an operator is a function of (seed,
   // number of the call, operator): every call draws new masks, a run with the same seed draws the same sequence.
   uint64_t seed = 0;
+  // Data parallelism (or any other treatment of the gradients) outside the graph: Forward runs forward and backward only
+  // and adds into persistent fp32 gradient buffers (cleared on the first call after an update); the caller reads them with
+  // gradient(i), reduces them across ranks, writes them back with set_gradient(i, ...) and calls ApplyUpdate(), which runs
+  // clipping and the optimizer. accumulation_steps still scales the loss gradient (micro-batches per update).
+  bool external_gradient_reduction = false;
   // Learning-rate schedule evaluated by the runtime before every optimizer step t = 1, 2, ...: linear warm-up from 0 over
   // warmup_steps, then "constant", or "cosine" / "linear" decay to min_lr_ratio * lr at decay_steps (and flat after it).
   // set_learning_rate changes the base rate the schedule scales.
@@ -142,6 +147,11 @@ class Graph {
   // Training graphs: the forward operators only, dropout switched off, nothing updated and no counter advanced (a
   // validation loss between steps). On an inference graph it is Forward.
   std::vector<Tensor> Evaluate(const std::vector<Tensor>& inputs) const;
+  // Graphs loaded with external_gradient_reduction: the accumulated gradient of trainable parameter i (fp32), and the
+  // optimizer step on whatever the gradient buffers hold now.
+  std::vector<float> gradient(int i) const;
+  void set_gradient(int i, const float* values, int64_t count);
+  void ApplyUpdate();
   int64_t in_features() const;    // last axis of the first input
   int64_t out_features() const;   // last axis of the first output
   int num_inputs() const;
@@ -204,13 +214,17 @@ void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, co
                                   float eps, float weight_decay, float momentum);
 void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                      float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps);
-// flags: bit 0 recompute cheap activations in the backward pass, bit 1 recompute everything but the residual stream
+// flags: bit 0 recompute cheap activations in the backward pass, bit 1 recompute everything but the residual stream,
+// bit 2 external gradient reduction (ofb_api_graph_gradient_read / _write / ofb_api_graph_apply_update)
 void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                         float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps, int flags);
 int ofb_api_graph_num_parameters(void* graph);
 const char* ofb_api_graph_parameter_name(void* graph, int i);
 long long ofb_api_graph_parameter_numel(void* graph, int i);
 int ofb_api_graph_parameter_read(void* graph, int i, float* out);
+int ofb_api_graph_gradient_read(void* graph, int i, float* out);
+int ofb_api_graph_gradient_write(void* graph, int i, const float* values, long long count);
+int ofb_api_graph_apply_update(void* graph);
 int ofb_api_graph_set_lr(void* graph, float lr);
 int ofb_api_graph_set_seed(void* graph, unsigned long long seed);
 int ofb_api_graph_set_lr_schedule(void* graph, const char* kind, long long warmup_steps, long long decay_steps, float min_lr_ratio);

@@ -689,15 +689,19 @@ class TrainingGraph(InferenceGraph):
     ``recompute_cheap_activations`` drops the outputs of element-wise operators and LayerNorms after the forward pass and
     recomputes them in the backward pass (less activation memory, a few more memory-bound kernels);
     ``recompute_all_but_residual_stream`` keeps only the residual stream and runs every other forward operator again in the
-    backward pass (full activation checkpointing: about a third more compute for the smallest activation footprint)."""
+    backward pass (full activation checkpointing: about a third more compute for the smallest activation footprint).
+    With ``external_gradient_reduction`` a ``step`` runs forward and backward only; ``gradients()`` / ``set_gradients()`` give
+    access to the accumulated fp32 gradients, ``all_reduce_gradients()`` averages them over a torch.distributed group (data
+    parallelism), ``apply_update()`` runs clipping and the optimizer."""
 
     def __init__(self, directory, device=0, n_streams=2, optimizer="adamw", lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  momentum=0.0, clip_grad_norm=0.0, accumulation_steps=1, recompute_cheap_activations=False, seed=0,
-                 recompute_all_but_residual_stream=False):
+                 recompute_all_but_residual_stream=False, external_gradient_reduction=False):
         self._load = lambda lib: lib.ofb_api_graph_load_training_flags(
             directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams), optimizer.encode(), ctypes.c_float(lr),
             ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_float(momentum),
-            ctypes.c_float(clip_grad_norm), ctypes.c_int(accumulation_steps), ctypes.c_int((1 if recompute_cheap_activations else 0) | (2 if recompute_all_but_residual_stream else 0)))
+            ctypes.c_float(clip_grad_norm), ctypes.c_int(accumulation_steps), ctypes.c_int((1 if recompute_cheap_activations else 0) | (2 if recompute_all_but_residual_stream else 0) |
+                         (4 if external_gradient_reduction else 0)))
         super().__init__(directory, device, n_streams)
         lib = self.lib
         lib.ofb_api_graph_parameter_name.restype = ctypes.c_char_p
@@ -749,6 +753,48 @@ class TrainingGraph(InferenceGraph):
     def restore(self, directory):
         """Step count, fp32 master weights and optimizer state from ``directory/train_state.bin`` (written by ``save``)."""
         if self.lib.ofb_api_graph_restore(ctypes.c_void_p(self.h), directory.encode()) != 0:
+            raise RuntimeError(self.lib.ofb_api_last_error().decode())
+
+    def _parameter_names(self):
+        h = ctypes.c_void_p(self.h)
+        return [self.lib.ofb_api_graph_parameter_name(h, ctypes.c_int(i)).decode() for i in range(self.lib.ofb_api_graph_num_parameters(h))]
+
+    def gradients(self):
+        """The accumulated fp32 gradients by parameter name (graphs loaded with ``external_gradient_reduction``)."""
+        h = ctypes.c_void_p(self.h)
+        out = {}
+        for i, name in enumerate(self._parameter_names()):
+            buf = np.empty(self.lib.ofb_api_graph_parameter_numel(h, ctypes.c_int(i)), dtype=np.float32)
+            if self.lib.ofb_api_graph_gradient_read(h, ctypes.c_int(i), buf.ctypes.data_as(ctypes.c_void_p)) != 0:
+                raise RuntimeError(self.lib.ofb_api_last_error().decode())
+            out[name] = buf
+        return out
+
+    def set_gradients(self, grads):
+        h = ctypes.c_void_p(self.h)
+        for i, name in enumerate(self._parameter_names()):
+            if name not in grads:
+                continue
+            a = np.ascontiguousarray(np.asarray(grads[name], dtype=np.float32).reshape(-1))
+            if self.lib.ofb_api_graph_gradient_write(h, ctypes.c_int(i), a.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(a.size)) != 0:
+                raise RuntimeError(self.lib.ofb_api_last_error().decode())
+
+    def all_reduce_gradients(self, group=None):
+        """Averages the gradients over the ranks of a torch.distributed group: one flat buffer, one collective."""
+        import torch.distributed as dist
+        grads = self.gradients()
+        names = list(grads)
+        flat = torch.from_numpy(np.concatenate([grads[n] for n in names]))
+        dist.all_reduce(flat, group=group)
+        flat /= dist.get_world_size(group)
+        out, at = {}, 0
+        for n in names:
+            out[n] = flat[at:at + grads[n].size].numpy()
+            at += grads[n].size
+        self.set_gradients(out)
+
+    def apply_update(self):
+        if self.lib.ofb_api_graph_apply_update(ctypes.c_void_p(self.h)) != 0:
             raise RuntimeError(self.lib.ofb_api_last_error().decode())
 
     def parameters(self):

@@ -538,11 +538,55 @@ def rank_divergence(tmp):
     CP.barrier("end", world, 30)
 
 
+def native_data_parallel(tmp):
+    """The native graph compiler under data parallelism: every rank runs forward and backward of its shard of the batch in
+    its own compiled plan, the fp32 gradients are averaged over the ranks by one collective outside the graph, every rank
+    applies the same update. The result equals one plan over the whole batch."""
+    import numpy as np
+    import torch.nn.functional as F
+    from oneflow_b200.utils import export as E
+    rank, world = flow.env.get_rank(), flow.env.get_world_size()
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.ln, self.fc2 = torch.nn.Linear(32, 64), torch.nn.LayerNorm(64), torch.nn.Linear(64, 16)
+
+        def forward(self, x, y):
+            return F.cross_entropy(self.fc2(self.ln(F.gelu(self.fc1(x)))), y)
+
+    torch.manual_seed(0)
+    m = Net()
+    for prm in m.parameters():
+        prm.data = prm.data.bfloat16().float()
+    x, y = torch.randn(16 * world, 32).bfloat16().float(), torch.randint(0, 16, (16 * world,))
+    lo, hi = 16 * rank, 16 * (rank + 1)
+    shard = E.export_graph(m, (x[lo:hi], y[lo:hi]), os.path.join(tmp, f"shard{rank}"), fuse=False)
+    whole = E.export_graph(m, (x, y), os.path.join(tmp, f"whole{rank}"), fuse=False)
+    kw = dict(device=-1, optimizer="adamw", lr=1e-2, clip_grad_norm=1.0)
+    g = E.TrainingGraph(shard, external_gradient_reduction=True, **kw)
+    ref = E.TrainingGraph(whole, **kw)
+    for _ in range(4):
+        g.step(x[lo:hi].numpy(), y[lo:hi].numpy())
+        g.all_reduce_gradients()
+        g.apply_update()
+        ref.step(x.numpy(), y.numpy())
+    mine, want = g.parameters(), ref.parameters()
+    for k in want:
+        assert np.abs(mine[k] - want[k]).max() < 1e-2, (k, float(np.abs(mine[k] - want[k]).max()))
+    # every rank holds the same weights, bit for bit
+    flat = torch.from_numpy(np.concatenate([mine[k] for k in sorted(mine)]))
+    gathered = [torch.empty_like(flat) for _ in range(world)]
+    torch.distributed.all_gather(gathered, flat)
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+    assert g.evaluate(x[lo:hi].numpy(), y[lo:hi].numpy()) > 0
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     tmp = sys.argv[2] if len(sys.argv) > 2 else "/tmp"
     {"mlp_config1": mlp_config1, "boxing": boxing_exhaustive, "global_ops": global_ops, "graph_features": graph_features,
-     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers, "embedding_stages": embedding_stages, "rank_divergence": rank_divergence}[case](tmp)
+     "ddp_comm": ddp_and_comm, "auto_parallel": auto_parallel_graph, "data_readers": data_readers, "embedding_stages": embedding_stages, "rank_divergence": rank_divergence, "native_dp": native_data_parallel}[case](tmp)
     if case != "rank_divergence":
         flow.comm.barrier()
     if flow.env.get_rank() == 0:

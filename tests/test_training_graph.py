@@ -841,3 +841,45 @@ def test_vit_style_classifier_trains_natively(tmp_path):
     losses = [g.step(patches.numpy(), labels.numpy()) for _ in range(8)]
     assert losses[-1] < 0.5 * losses[0]
     g.close()
+
+
+def test_external_gradient_reduction_reproduces_the_large_batch_step(tmp_path):
+    """Two graphs stand for two data-parallel ranks: each runs forward and backward on its half of the batch, the gradients
+    are averaged outside the graphs, each applies the update. Both end where one graph with the whole batch ends."""
+    torch.manual_seed(24)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d_full = E.export_graph(m, (x, y), str(tmp_path / "full"), fuse=False)
+    d_half = E.export_graph(m, (x[:12], y[:12]), str(tmp_path / "half"), fuse=False)
+    kw = dict(device=-1, optimizer="adamw", lr=1e-2, clip_grad_norm=0.5)
+    full = E.TrainingGraph(d_full, **kw)
+    ranks = [E.TrainingGraph(d_half, external_gradient_reduction=True, **kw) for _ in range(2)]
+    with pytest.raises(RuntimeError, match="no gradients"):
+        ranks[0].apply_update()
+    with pytest.raises(RuntimeError, match="external_gradient_reduction"):
+        full.gradients()
+    for _ in range(3):
+        lf = full.step(x.numpy(), y.numpy())
+        losses = [ranks[0].step(x[:12].numpy(), y[:12].numpy()), ranks[1].step(x[12:].numpy(), y[12:].numpy())]
+        assert abs(0.5 * sum(losses) - lf) < 2e-2 * max(abs(lf), 0.1)
+        before = ranks[0].parameters()
+        grads = [r.gradients() for r in ranks]
+        mean = {k: 0.5 * (grads[0][k] + grads[1][k]) for k in grads[0]}
+        for r in ranks:
+            r.set_gradients(mean)
+            r.apply_update()
+        assert any(not np.array_equal(before[k], v) for k, v in ranks[0].parameters().items())
+    assert ranks[0].steps == 3
+    p0, p1, pf = ranks[0].parameters(), ranks[1].parameters(), full.parameters()
+    for k in pf:
+        assert np.array_equal(p0[k], p1[k])
+        assert np.abs(p0[k] - pf[k]).max() < 1e-2, k
+    for g in ranks + [full]:
+        g.close()
+
+
+def test_native_data_parallel_on_two_cpu_ranks():
+    """Two processes (gloo): per-rank compiled plans, gradients averaged by one collective, identical weights on both ranks and
+    the same result as one plan over the whole batch (tests/flow_worker.py: native_data_parallel)."""
+    from test_flow_api import launch
+    launch("native_dp", 2)
