@@ -24,6 +24,9 @@ def main(argv=None):
         print("tensor substrate: torch", torch.__version__)
         print("native kernel library (sm_100a):", _native.lib_path("libofb_kernels.so"), "built" if _native.kernels_available() else "MISSING")
         print("native runtime library:", _native.lib_path("libofb_core.so"), "built" if _native.core_available() else "MISSING")
+        import os
+        api = _native.lib_path("libofb_api.so")
+        print("graph compiler / C++ API library:", api, "built" if os.path.exists(api) else "MISSING")
         print("gpus:", torch.cuda.device_count(), [torch.cuda.get_device_name(i) for i in range(torch.cuda.device_count())])
     return 0
 
