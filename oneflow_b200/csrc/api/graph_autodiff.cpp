@@ -56,7 +56,7 @@ std::vector<int> diff_slots(const OpDef& op) {
   if (t == "matmul" || t == "binary" || t == "mse") return {0, 1};
   if (t == "layer_norm" || t == "attention") return {0, 1, 2};
   if (t == "embedding") return {1};
-  if (t == "unary" || t == "softmax" || t == "copy" || t == "cross_entropy" || t == "dropout") return {0};
+  if (t == "unary" || t == "softmax" || t == "copy" || t == "cross_entropy" || t == "dropout" || t == "column_sum" || t == "cast") return {0};
   return {};
 }
 
@@ -266,7 +266,10 @@ void Builder::run() {
         if (!requires_grad[static_cast<size_t>(r)] || !reaches_loss[static_cast<size_t>(r)]) continue;
         for (int in : op.in)
           if (in >= 0 && root(in) == r) refuse(op, "works in place on a tensor the backward pass needs; export the module without in-place operators");
-        if (writer[static_cast<size_t>(r)] >= 0 && (op.type != "copy" || ir.ops[static_cast<size_t>(writer[static_cast<size_t>(r)])].type != "copy"))
+        // several writers are fine when they build one value together: copies into slices (concatenation), a zero fill
+        // followed by column sums into it (a reduction)
+        auto builds_jointly = [](const std::string& ty) { return ty == "copy" || ty == "fill" || ty == "column_sum"; };
+        if (writer[static_cast<size_t>(r)] >= 0 && !(builds_jointly(op.type) && builds_jointly(ir.ops[static_cast<size_t>(writer[static_cast<size_t>(r)])].type)))
           refuse(op, "rewrites a tensor another operator produced");
         writer[static_cast<size_t>(r)] = i;
       }
@@ -294,7 +297,7 @@ void Builder::run() {
       mode[r] = !kept_across_calls && u.size() == 1 && overwrites && whole(u[0].tensor) ? Mode::kDirect : Mode::kAccumulate;
       continue;
     }
-    if (u.size() == 1 && first.type != "copy" && whole(u[0].tensor)) {
+    if (u.size() == 1 && first.type != "copy" && first.type != "column_sum" && whole(u[0].tensor)) {
       mode[r] = Mode::kDirect;
       continue;
     }
@@ -560,6 +563,15 @@ void Builder::backward_of(const OpDef& op, OpDef& fwd) {
     Target tg = target_for(x, false);
     emit("unary_bwd", {x, dy}, {tg.out}, {{"fn", attr_str(op, "fn", "0")}, {"alpha", attr_str(op, "alpha", "1.0")}});
     finish(tg);
+  } else if (t == "column_sum") {
+    // every row of the [rows, cols] input receives the gradient of its column's sum: a copy that repeats dy over the rows
+    const int x = in(0);
+    const std::vector<int64_t> xs = shape(x);
+    emit("copy", {root(dy)}, {grad_storage(root(x))},
+         {{"shape", join(xs)}, {"in_strides", join({0, 1})}, {"in_offset", std::to_string(abs_off(dy))}, {"out_strides", join({xs[1], 1})},
+          {"out_offset", std::to_string(abs_off(x))}, {"accumulate", "1"}});
+  } else if (t == "cast") {
+    pass_grad(in(0), dy, attr_float(op, "scale", 1.0));
   } else if (t == "dropout") {
     // the same mask (same seed, call and operator index) applied to the gradient
     const int x = in(0);

@@ -355,6 +355,33 @@ class _GraphEmitter(torch.fx.Interpreter):
         self.n_dropout += 1
         return y
 
+    def _reduce(self, x, dim, y, mean):
+        """Sum or mean over one axis that is not the last: per leading index a column sum of a [reduced, rest] matrix into an
+        fp32 buffer, then one cast (with 1 / reduced for the mean) to the bf16 result."""
+        if isinstance(dim, (tuple, list)):
+            if len(dim) != 1:
+                raise ValueError("reductions over several axes cannot be exported")
+            dim = dim[0]
+        dim = dim % x.dim()
+        if dim == x.dim() - 1:
+            raise ValueError("reductions over the last axis cannot be exported")
+        outer, red, rest = math.prod(x.shape[:dim]), x.shape[dim], math.prod(x.shape[dim + 1:])
+        if outer > 64:
+            raise ValueError("reductions with more than 64 leading indices cannot be exported")
+        ix = self._operand(x)                                         # contiguous [outer, red, rest]
+        root = int(self.tensors[ix].split("alias=")[1].split()[0]) if "alias=" in self.tensors[ix] else ix
+        base = int(self.tensors[ix].split("offset=")[1].split()[0]) if "offset=" in self.tensors[ix] else 0
+        acc = self._new_tensor("f32", "act", [outer * rest])
+        self.copy_cache.clear()
+        self.ops.append({"type": "fill", "in": [], "out": [acc], "attr": {"value": 0}})
+        for b in range(outer):
+            src = self._alias(root, base + b * red * rest, (red, rest))
+            dst = self._new_tensor("f32", "act", [rest], f"alias={acc} offset={b * rest}")
+            self.ops.append({"type": "column_sum", "in": [src], "out": [dst], "attr": {}})
+        out, y = self._result(y)
+        self.ops.append({"type": "cast", "in": [acc], "out": [out], "attr": {"scale": repr(1.0 / red if mean else 1.0)}})
+        return y
+
     def _scalar_result(self, y):
         """A fresh fp32 scalar activation (loss values): (IR id, the tensor that stands for the node)."""
         real = y.detach().to(torch.float32).reshape(1).clone()
@@ -486,6 +513,8 @@ class _GraphEmitter(torch.fx.Interpreter):
             if (a[4] if len(a) > 4 else kw.get("dropout_p", 0.0)):
                 raise ValueError("attention dropout has no place in an inference graph")
             return self._sdpa(a[0], a[1], a[2], y, a[5] if len(a) > 5 else kw.get("is_causal", False), kw.get("scale"))
+        if n in ("mean", "sum") and torch.is_tensor(y) and y.dim() > 0 and (len(a) > 1 or "dim" in kw):
+            return self._reduce(a[0], a[1] if len(a) > 1 else kw["dim"], y, n == "mean")
         if n == "cross_entropy":
             return self._cross_entropy(a[0], a[1], y, a[2] if len(a) > 2 else kw.get("weight"), kw.get("ignore_index", -100),
                                        kw.get("reduction", "mean"), kw.get("label_smoothing", 0.0))

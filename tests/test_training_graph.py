@@ -883,3 +883,30 @@ def test_native_data_parallel_on_two_cpu_ranks():
     the same result as one plan over the whole batch (tests/flow_worker.py: native_data_parallel)."""
     from test_flow_api import launch
     launch("native_dp", 2)
+
+
+def test_mean_pooling_over_the_sequence_exports_and_differentiates(tmp_path):
+    """x.mean(dim=1) lowers to a zero fill, one column sum per batch index into an fp32 buffer and a scaling cast; backward
+    repeats the gradient over the reduced axis with a zero-stride copy."""
+    class Pooled(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb, self.fc, self.head = nn.Embedding(50, 32), nn.Linear(32, 32), nn.Linear(32, 8)
+
+        def forward(self, ids, labels):
+            h = torch.tanh(self.fc(self.emb(ids)))          # [B, S, 32]
+            return F.cross_entropy(self.head(h.mean(dim=1) + h.sum(1) * 0.125), labels)
+
+    torch.manual_seed(25)
+    m = _bf16_weights(Pooled())
+    ids, labels = torch.randint(0, 50, (6, 9)), torch.randint(0, 8, (6,))
+    loss, grads = _grads_by_unit_sgd(m, (ids, labels), str(tmp_path))
+    ref = m(ids, labels)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    _check_grads(m, grads)
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("op column_sum") == 12 and text.count("op cast") == 2
+    # the same directory as an inference graph
+    out = E.InferenceGraph(str(tmp_path), device=-1).run(ids.numpy(), labels.numpy())[0][0]
+    assert abs(out - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
