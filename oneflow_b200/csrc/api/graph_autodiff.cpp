@@ -349,25 +349,55 @@ void Builder::run() {
   ir.trainable = kept;
   ir.masters = masters;
   ir.grad_tensors = grads;
-  std::vector<int> outs = params;
-  outs.insert(outs.end(), masters.begin(), masters.end());
-  outs.insert(outs.end(), s1.begin(), s1.end());
-  outs.insert(outs.end(), s2.begin(), s2.end());
   std::map<std::string, std::string> when;
   if (opt.accumulation_steps > 1 || opt.external_gradient_reduction) when["when"] = "last";
-  std::vector<int> update_in = grads;
-  std::map<std::string, std::string> uattr = {{"n", std::to_string(params.size())}, {"states", std::to_string((s1.empty() ? 0 : 1) + (s2.empty() ? 0 : 1))}};
+  // parameter groups: with decay_matrices_only, parameters that are only ever used as vectors (biases, LayerNorm scale and
+  // shift) form a second group that the optimizer does not decay
+  std::vector<char> is_matrix(params.size(), 1);
+  if (opt.decay_matrices_only) {
+    for (size_t i = 0; i < params.size(); ++i) {
+      size_t axes = 1;
+      for (size_t t = 0; t < ir.tensors.size(); ++t)
+        if (ir.tensors[t].alias_of >= 0 && root(static_cast<int>(t)) == params[i]) {
+          size_t real = 0;
+          for (auto dim : ir.tensors[t].shape) real += dim > 1 ? 1 : 0;
+          axes = std::max(axes, real);
+        }
+      is_matrix[i] = axes >= 2 ? 1 : 0;
+    }
+  }
+  int clip = -1;
   if (opt.clip_grad_norm > 0.f) {
     // {sum of squares, non-finite count, clip factor, norm}; the update reads the factor on the device
-    const int clip = new_root(DType::kFloat, 4);
+    clip = new_root(DType::kFloat, 4);
     std::map<std::string, std::string> cattr = when;
     cattr["max_norm"] = fstr(opt.clip_grad_norm);
     emit("grad_clip", grads, {clip}, cattr);
-    update_in.push_back(clip);
-    uattr["clip"] = "1";
   }
-  uattr.insert(when.begin(), when.end());
-  emit(adam ? "adamw_update" : "sgd_update", update_in, outs, uattr);
+  for (int group = 1; group >= 0; --group) {
+    std::vector<int> gin, gp, gm, g1, g2;
+    for (size_t i = 0; i < params.size(); ++i) {
+      if (is_matrix[i] != group) continue;
+      gin.push_back(grads[i]);
+      gp.push_back(params[i]);
+      gm.push_back(masters[i]);
+      if (!s1.empty()) g1.push_back(s1[i]);
+      if (!s2.empty()) g2.push_back(s2[i]);
+    }
+    if (gp.empty()) continue;
+    std::vector<int> outs = gp;
+    outs.insert(outs.end(), gm.begin(), gm.end());
+    outs.insert(outs.end(), g1.begin(), g1.end());
+    outs.insert(outs.end(), g2.begin(), g2.end());
+    std::map<std::string, std::string> uattr = {{"n", std::to_string(gp.size())}, {"states", std::to_string((s1.empty() ? 0 : 1) + (s2.empty() ? 0 : 1))},
+                                                {"decay", group ? "1" : "0"}};
+    if (clip >= 0) {
+      gin.push_back(clip);
+      uattr["clip"] = "1";
+    }
+    uattr.insert(when.begin(), when.end());
+    emit(adam ? "adamw_update" : "sgd_update", gin, outs, uattr);
+  }
 
   ir.n_forward_ops = n_ops;
   for (int i = 0; i < n_ops; ++i) ir.ops[static_cast<size_t>(i)].attr["fwd"] = "1";   // what an evaluation call runs

@@ -444,7 +444,8 @@ bool Graph::Impl::run_train_op_host(const PlannedOp& p) {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
     const float gscale = attr_int(op, "clip", 0) ? static_cast<const float*>(addr(op.in[static_cast<size_t>(np)]))[2] : 1.f;
-    const float lr = scheduled_lr(std::max<int64_t>(train_steps, 1)), b1 = train.beta1, b2 = train.beta2, wd = train.weight_decay;
+    const float lr = scheduled_lr(std::max<int64_t>(train_steps, 1)), b1 = train.beta1, b2 = train.beta2;
+    const float wd = attr_int(op, "decay", 1) != 0 ? train.weight_decay : 0.f;   // the group of vectors is not decayed
     const float bc1 = 1.f - std::pow(b1, static_cast<float>(train_steps)), bc2 = 1.f - std::pow(b2, static_cast<float>(train_steps));
     for (int64_t i = 0; i < np; ++i) {
       const float* g = static_cast<const float*>(addr(op.in[static_cast<size_t>(i)]));
@@ -563,6 +564,7 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
     const int64_t np = attr_int(op, "n", 0), states = attr_int(op, "states", 0);
     const bool adam = t == "adamw_update";
     const float* gscale = attr_int(op, "clip", 0) ? static_cast<const float*>(addr(op.in[static_cast<size_t>(np)])) + 2 : nullptr;
+    const float wd = attr_int(op, "decay", 1) != 0 ? train.weight_decay : 0.f;   // the group of vectors is not decayed
     for (int64_t first = 0; first < np; first += 48) {   // the multi-tensor kernels take 48 tensors per launch
       const int cnt = static_cast<int>(std::min<int64_t>(48, np - first));
       std::vector<void*> grads, copies;
@@ -580,10 +582,10 @@ bool Graph::Impl::run_train_op_device(const PlannedOp& p, cudaStream_t s) {
       // learning rate and bias corrections come from the device (refreshed before every step), nothing here depends on the step
       if (adam)
         ok(ofb_multi_tensor_adamw_dev(cnt, grads.data(), masters.data(), copies.data(), s1.data(), s2.data(), sizes.data(), 0, train.beta1,
-                                      train.beta2, train.eps, train.weight_decay, step_scalars, gscale, s));
+                                      train.beta2, train.eps, wd, step_scalars, gscale, s));
       else
         ok(ofb_multi_tensor_sgd(cnt, grads.data(), masters.data(), copies.data(), states >= 1 ? s1.data() : nullptr, sizes.data(), 0, 0.f,
-                                train.momentum, 0.f, 0, 0, train.weight_decay, 0.f, 0.f, 1.f, step_scalars, gscale, nullptr, s));
+                                train.momentum, 0.f, 0, 0, wd, 0.f, 0.f, 1.f, step_scalars, gscale, nullptr, s));
     }
   } else {
     return false;

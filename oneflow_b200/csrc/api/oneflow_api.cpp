@@ -272,6 +272,7 @@ void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_strea
     o.recompute_cheap_activations = (flags & 1) != 0;
     o.recompute_all_but_residual_stream = (flags & 2) != 0;
     o.external_gradient_reduction = (flags & 4) != 0;
+    o.decay_matrices_only = (flags & 8) != 0;
     return new Graph(Graph::LoadTraining(dir, o, device, n_streams));
   } catch (const std::exception& e) {
     oneflow_api::detail::g_error = e.what();

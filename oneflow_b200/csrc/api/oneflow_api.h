@@ -103,6 +103,9 @@ struct TrainOptions {
   float lr = 1e-3f;
   float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f;
   float weight_decay = 0.f;
+  // true: weight decay only on parameters used with two or more axes (weight matrices, tables); biases and LayerNorm
+  // scales / shifts go into a second update operator without decay.
+  bool decay_matrices_only = false;
   float momentum = 0.f;
   // > 0: the gradients are scaled by min(1, clip_grad_norm / (global L2 norm + 1e-6)) before the update.
   float clip_grad_norm = 0.f;
@@ -214,7 +217,8 @@ void* ofb_api_graph_load_training(const char* dir, int device, int n_streams, co
                                   float eps, float weight_decay, float momentum);
 void* ofb_api_graph_load_training_ex(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                      float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps);
-// flags: bit 0 recompute cheap activations in the backward pass, bit 1 recompute everything but the residual stream,
+// flags: bit 0 recompute cheap activations in the backward pass, bit 1 recompute everything but the residual stream, bit 3
+// weight decay on matrices only,
 // bit 2 external gradient reduction (ofb_api_graph_gradient_read / _write / ofb_api_graph_apply_update)
 void* ofb_api_graph_load_training_flags(const char* dir, int device, int n_streams, const char* optimizer, float lr, float beta1, float beta2,
                                         float eps, float weight_decay, float momentum, float clip_grad_norm, int accumulation_steps, int flags);

@@ -719,18 +719,19 @@ class TrainingGraph(InferenceGraph):
     recomputes them in the backward pass (less activation memory, a few more memory-bound kernels);
     ``recompute_all_but_residual_stream`` keeps only the residual stream and runs every other forward operator again in the
     backward pass (full activation checkpointing: about a third more compute for the smallest activation footprint).
+    ``decay_matrices_only`` keeps weight decay off biases and LayerNorm parameters (a second update operator).
     With ``external_gradient_reduction`` a ``step`` runs forward and backward only; ``gradients()`` / ``set_gradients()`` give
     access to the accumulated fp32 gradients, ``all_reduce_gradients()`` averages them over a torch.distributed group (data
     parallelism), ``apply_update()`` runs clipping and the optimizer."""
 
     def __init__(self, directory, device=0, n_streams=2, optimizer="adamw", lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  momentum=0.0, clip_grad_norm=0.0, accumulation_steps=1, recompute_cheap_activations=False, seed=0,
-                 recompute_all_but_residual_stream=False, external_gradient_reduction=False):
+                 recompute_all_but_residual_stream=False, external_gradient_reduction=False, decay_matrices_only=False):
         self._load = lambda lib: lib.ofb_api_graph_load_training_flags(
             directory.encode(), ctypes.c_int(device), ctypes.c_int(n_streams), optimizer.encode(), ctypes.c_float(lr),
             ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_float(momentum),
             ctypes.c_float(clip_grad_norm), ctypes.c_int(accumulation_steps), ctypes.c_int((1 if recompute_cheap_activations else 0) | (2 if recompute_all_but_residual_stream else 0) |
-                         (4 if external_gradient_reduction else 0)))
+                         (4 if external_gradient_reduction else 0) | (8 if decay_matrices_only else 0)))
         super().__init__(directory, device, n_streams)
         lib = self.lib
         lib.ofb_api_graph_parameter_name.restype = ctypes.c_char_p

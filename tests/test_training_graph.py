@@ -910,3 +910,32 @@ def test_mean_pooling_over_the_sequence_exports_and_differentiates(tmp_path):
     # the same directory as an inference graph
     out = E.InferenceGraph(str(tmp_path), device=-1).run(ids.numpy(), labels.numpy())[0][0]
     assert abs(out - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+
+
+def test_weight_decay_on_matrices_only_matches_torch_parameter_groups(tmp_path):
+    torch.manual_seed(26)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False)
+    g = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.5, decay_matrices_only=True, clip_grad_norm=10.0)
+    text = g.dump()
+    assert text.count("op adamw_update") == 2 and "decay=0" in text and "decay=1" in text
+    opt = torch.optim.AdamW([{"params": [p for p in m.parameters() if p.dim() >= 2], "weight_decay": 0.5},
+                             {"params": [p for p in m.parameters() if p.dim() < 2], "weight_decay": 0.0}], lr=1e-2)
+    for _ in range(5):
+        ref = m(x, y)
+        opt.zero_grad()
+        ref.backward()
+        opt.step()
+        assert abs(g.step(x.numpy(), y.numpy()) - float(ref.detach())) < 3e-2 * max(abs(float(ref.detach())), 0.1)
+    ps = g.parameters()
+    for name, p in m.named_parameters():
+        assert np.abs(ps[name] - p.detach().numpy().reshape(-1)).max() < 2.5e-2, name
+    # the strong decay shows on the matrices and must not show on the vectors: compare with a run that decays everything
+    h = E.TrainingGraph(d, device=-1, optimizer="adamw", lr=1e-2, weight_decay=0.5)
+    for _ in range(5):
+        h.step(x.numpy(), y.numpy())
+    ph = h.parameters()
+    assert np.abs(ph["ln.weight"]).mean() < np.abs(ps["ln.weight"]).mean() - 0.01
+    g.close()
+    h.close()
