@@ -838,6 +838,16 @@ class TrainingGraph(InferenceGraph):
             out[name] = buf
         return out
 
+    def copy_parameters_to(self, module):
+        """Writes the trained fp32 master weights back into ``module``'s parameters (matched by name), so that the module
+        can go on in Python: evaluation, another export, a state_dict checkpoint."""
+        trained = self.parameters()
+        with torch.no_grad():
+            for name, prm in module.named_parameters():
+                if name in trained:
+                    prm.copy_(torch.from_numpy(trained[name]).view_as(prm).to(prm.dtype))
+        return module
+
     def dump(self):
         """The operator list after the backward pass was appended, in the IR text format."""
         h = ctypes.c_void_p(self.h)
@@ -845,3 +855,12 @@ class TrainingGraph(InferenceGraph):
         buf = ctypes.create_string_buffer(n + 1)
         self.lib.ofb_api_graph_dump(h, buf, ctypes.c_longlong(n + 1))
         return buf.value.decode()
+
+
+def compile_training(module, example_inputs, directory=None, device=0, **options):
+    """Export ``module`` (its forward returns the loss) in training mode and load it as a ``TrainingGraph``: the one call that
+    takes a PyTorch / flow module to a natively compiled training step. ``options`` are ``TrainingGraph``'s."""
+    import tempfile
+    directory = directory or tempfile.mkdtemp(prefix="oneflow_graph_")
+    export_graph(module, example_inputs, directory, fuse=False, train_mode=True)
+    return TrainingGraph(directory, device=device, **options)

@@ -939,3 +939,19 @@ def test_weight_decay_on_matrices_only_matches_torch_parameter_groups(tmp_path):
     assert np.abs(ph["ln.weight"]).mean() < np.abs(ps["ln.weight"]).mean() - 0.01
     g.close()
     h.close()
+
+
+def test_compile_training_and_parameters_back_into_the_module(tmp_path):
+    torch.manual_seed(27)
+    m = _bf16_weights(Mlp())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    before = float(m(x, y).detach())
+    g = E.compile_training(m, (x, y), str(tmp_path), device=-1, optimizer="adamw", lr=1e-2)
+    for _ in range(10):
+        g.step(x.numpy(), y.numpy())
+    want = g.evaluate(x.numpy(), y.numpy())
+    g.copy_parameters_to(m)
+    m.eval()
+    after = float(m(x, y).detach())
+    assert after < 0.7 * before and abs(after - want) < 3e-2 * max(want, 0.05)      # the module now computes what the graph trained
+    g.close()
