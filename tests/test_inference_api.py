@@ -271,3 +271,45 @@ def test_cpp_program_links_the_api_and_runs_a_graph(tmp_path):
     py = E.InferenceGraph(d, device=-1).run(ids.numpy())[0]
     assert out.shape == py.shape and np.allclose(out, py, rtol=1e-5, atol=1e-5)
     assert "ops 11" in r.stderr
+
+
+def test_compile_from_torch_runs_a_module_through_cached_native_plans(tmp_path):
+    """oneflow.framework.infer_compiler: the wrapper exports per input signature, caches the loaded graphs, lets attribute
+    access through to the wrapped module, and saves / loads the exported directories."""
+    from oneflow.framework.infer_compiler import DeployableModule, compile_from_torch
+    torch.manual_seed(1)
+    m = _bf16_weights(Block().eval())
+    dm = compile_from_torch(m, options={"size": 2})
+    assert isinstance(dm, DeployableModule) and compile_from_torch(dm) is dm
+    ids = torch.randint(0, 96, (2, 16))
+    out = dm(ids)
+    ref = m(ids).detach()
+    assert out.shape == ref.shape and float((out - ref).abs().max()) < 0.05 * float(ref.abs().max())
+    assert dm.heads == m.heads and set(dm.state_dict()) == set(m.state_dict())          # attributes and weights of the module
+    first = dm.get_graph()
+    assert torch.equal(dm(ids), out) and dm.get_graph() is first                         # same signature: the cached plan
+    ids3 = torch.randint(0, 96, (3, 16))
+    assert dm(ids3).shape == (3, 16, 96) and dm.get_graph() is not first                 # another batch size: another plan
+    saved = dm.save_graph(str(tmp_path / "saved"))
+    fresh = compile_from_torch(m).load_graph(os.path.join(saved, "graph0"), (ids,), run_warmup=True)
+    assert torch.equal(fresh(ids), out)
+    eager = compile_from_torch(m, use_graph=False)
+    assert torch.equal(eager(ids), m(ids))
+
+
+def test_torch_compile_backend_on_the_native_runtime():
+    from oneflow.framework.infer_compiler import oneflow_backend
+    torch.manual_seed(2)
+    mlp = _bf16_weights(nn.Sequential(nn.Linear(32, 64), nn.GELU(), nn.LayerNorm(64), nn.Linear(64, 16)).eval())
+    x = torch.randn(8, 32).bfloat16().float()
+    compiled = torch.compile(mlp, backend=oneflow_backend)
+    with torch.no_grad():
+        y = compiled(x)
+        assert float((y - mlp(x)).abs().max()) < 3e-2
+
+        class Odd(nn.Module):                       # an operator the exporter does not know: that graph runs eagerly
+            def forward(self, t):
+                return torch.sin(t) * 2
+
+        odd = torch.compile(Odd(), backend=oneflow_backend)
+        assert torch.allclose(odd(x), torch.sin(x) * 2)
