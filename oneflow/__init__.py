@@ -46,15 +46,23 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
     def find_spec(self, fullname, path=None, target=None):
         if not fullname.startswith("oneflow.") or fullname == "oneflow.__main__":
             return None
-        if _resolve(fullname[len("oneflow."):]) is None:
+        mod = _resolve(fullname[len("oneflow."):])
+        if mod is None:
             return None
-        return importlib.machinery.ModuleSpec(fullname, self)
+        # a real package stays one (``python -m oneflow.<package>`` then looks for its __main__)
+        return importlib.machinery.ModuleSpec(fullname, self, is_package=bool(getattr(mod, "__path__", None)))
 
     def create_module(self, spec):
         return _resolve(spec.name[len("oneflow."):])
 
     def exec_module(self, module):
         pass
+
+    def get_code(self, fullname):
+        """For ``python -m oneflow.<package>``: the code object of the module this name stands for."""
+        mod = _resolve(fullname[len("oneflow."):])
+        loader = getattr(getattr(mod, "__spec__", None), "loader", None)
+        return loader.get_code(mod.__name__) if loader is not None and hasattr(loader, "get_code") else None
 
 
 sys.meta_path.insert(0, _AliasFinder())    # ahead of the path finder: one module object per file, under both names

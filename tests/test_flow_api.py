@@ -415,3 +415,26 @@ def test_remat_evicts_under_a_budget_and_recomputes_for_backward():
     finally:
         flow.remat.set_small_pieces_optimization(old)
     assert flow.remat.parse_size("1.5GB") == int(1.5 * 2 ** 30)
+
+
+def test_autoprof_profiles_a_script_into_a_csv(tmp_path):
+    """python -m oneflow.autoprof script.py: one CSV row per operator and input shape, a summary table on stdout; the alias
+    package keeps real packages as packages so that ``python -m oneflow.<package>`` finds their __main__."""
+    script = tmp_path / "work.py"
+    script.write_text("import oneflow as flow\nx = flow.randn(64, 128)\nw = flow.randn(128, 256)\n"
+                      "for _ in range(3):\n    y = flow.nn.functional.gelu(flow.matmul(x, w))\nprint('ran', tuple(y.shape))\n")
+    env = dict(os.environ, ONEFLOW_PROFILE_CSV=str(tmp_path / "ops"), PYTHONPATH=ROOT)
+    p = subprocess.run([sys.executable, "-m", "oneflow.autoprof", str(script)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=300, cwd=str(tmp_path), env=env)
+    assert p.returncode == 0 and "ran (64, 256)" in p.stdout and "aten::mm" in p.stdout, p.stdout[-3000:]
+    import csv
+    rows = list(csv.DictReader(open(str(tmp_path / "ops.csv"))))
+    mm = [r for r in rows if r["op"] == "aten::mm"]
+    assert len(mm) == 1 and mm[0]["count"] == "3" and "(64,128)" in mm[0]["input_shapes"].replace(" ", "")
+    import oneflow as flow
+    assert flow.support.env_var_util.parse_boolean_from_env("ONEFLOW_SURELY_UNSET_VARIABLE", True) is True
+    os.environ["ONEFLOW_TEST_BOOL"] = "off"
+    assert flow.support.env_var_util.parse_boolean_from_env("ONEFLOW_TEST_BOOL", True) is False
+    os.environ.pop("ONEFLOW_TEST_BOOL")
+    t = torch.arange(6.0)
+    assert torch.equal(flow.utils.dlpack.from_dlpack(flow.utils.dlpack.to_dlpack(t)), t)
