@@ -42,7 +42,7 @@ boxing = framework.boxing
 _SUBMODULES = ["nn", "nn.functional", "nn.graph", "nn.parallel", "nn.utils", "nn.init", "optim", "optim.lr_scheduler", "comm",
                "env", "sbp", "amp", "autograd", "utils", "utils.data", "distributed", "distributed.launch", "one_embedding",
                "profiler", "cuda", "backends", "mock_torch", "framework", "models", "ops", "parallel", "_C", "remat", "sysconfig",
-               "unittest", "asyncs", "hub", "multiprocessing", "fx", "version", "support", "autoprof"]
+               "unittest", "asyncs", "hub", "multiprocessing", "fx", "version", "support", "autoprof", "model", "data", "experimental"]
 
 __all__ = ["sbp", "placement", "GlobalTensor", "to_global", "to_local", "Tensor", "tensor", "zeros", "ones", "empty", "full",
            "randn", "rand", "randint", "randperm", "arange", "eye", "linspace", "from_numpy", "save", "load", "nn", "optim",

@@ -438,3 +438,89 @@ def test_autoprof_profiles_a_script_into_a_csv(tmp_path):
     os.environ.pop("ONEFLOW_TEST_BOOL")
     t = torch.arange(6.0)
     assert torch.equal(flow.utils.dlpack.from_dlpack(flow.utils.dlpack.to_dlpack(t)), t)
+
+
+def test_model_fit_runs_training_validation_checkpoints_and_callbacks(tmp_path):
+    import numpy as np
+    import oneflow as flow
+
+    class Data(flow.model.NumpyDataModule):
+        def forward(self, step_idx=0, optimizer_idx=0):
+            rng = np.random.default_rng(step_idx % 4)
+            x = rng.standard_normal((16, 8)).astype(np.float32)
+            return x, (x.sum(1, keepdims=True) > 0).astype(np.float32)
+
+    class Net(flow.model.Model):
+        def __init__(self):
+            super().__init__()
+            self.fc = flow.nn.Linear(8, 1)
+
+        def forward(self, x):
+            return self.fc(x)
+
+        def training_step(self, batch, optimizer_idx=0):
+            x, y = batch
+            return flow.nn.functional.binary_cross_entropy_with_logits(self(x), y), "extra"
+
+        def validation_step(self, batch):
+            x, y = batch
+            return ((self(x) > 0).float() == y).float().mean()
+
+        def configure_optimizers(self):
+            return flow.optim.SGD(self.parameters(), lr=0.5)
+
+    class Log(flow.model.Callback):
+        def __init__(self):
+            self.train, self.val = [], []
+
+        def on_training_step_end(self, outputs, step_idx=0, optimizer_idx=0):
+            self.train.append(float(outputs[0].detach()))
+
+        def on_validation_step_end(self, outputs, step_idx=0):
+            self.val.append((step_idx, float(outputs)))
+
+    flow.manual_seed(0)
+    net, log = Net(), Log()
+    train, val, ckpt = flow.model.TrainingConfig(), flow.model.ValidationConfig(), flow.model.CheckpointConfig()
+    train.config_data(Data())
+    val.config_data(Data())
+    val.config_step_interval(10)
+    ckpt.config_save(str(tmp_path), step_interval=20)
+    net.fit(training_config=train, validation_config=val, checkpoint_config=ckpt, callbacks=log, max_steps=40)
+    assert len(log.train) == 40 and log.train[-1] < 0.6 * log.train[0]
+    assert [s for s, _ in log.val] == [9, 19, 29, 39] and log.val[-1][1] > 0.85
+    assert sorted(os.listdir(str(tmp_path))) == ["step_20", "step_40"]
+    again, load = Net(), flow.model.CheckpointConfig()
+    load.config_load(str(tmp_path / "step_40"))
+    again.fit(checkpoint_config=load, max_steps=0)
+    assert torch.equal(again.fc.weight, net.fc.weight)
+    with pytest.raises(ValueError, match="DataModule"):
+        bad = flow.model.TrainingConfig()
+        Net().fit(training_config=bad, max_steps=1)
+
+    class NoStep(flow.model.Model):
+        def configure_optimizers(self):
+            return None
+
+    with pytest.raises(NotImplementedError, match="training_step"):
+        NoStep().fit(training_config=train, max_steps=1)
+
+
+def test_load_mnist_reads_local_idx_files(tmp_path):
+    import gzip
+    import struct
+    import numpy as np
+    import oneflow as flow
+    rng = np.random.default_rng(0)
+    for stem, n in (("train", 250), ("t10k", 120)):
+        images = rng.integers(0, 256, (n, 28, 28), dtype=np.uint8)
+        labels = rng.integers(0, 10, (n,), dtype=np.uint8)
+        with gzip.open(str(tmp_path / f"{stem}-images-idx3-ubyte.gz"), "wb") as f:
+            f.write(struct.pack(">HBBIII", 0, 8, 3, n, 28, 28) + images.tobytes())
+        with open(str(tmp_path / f"{stem}-labels-idx1-ubyte"), "wb") as f:
+            f.write(struct.pack(">HBBI", 0, 8, 1, n) + labels.tobytes())
+    (xtr, ytr), (xte, yte) = flow.data.load_mnist(100, 50, data_dir=str(tmp_path))
+    assert len(xtr) == 2 and xtr[0].shape == (100, 1, 28, 28) and xtr[0].dtype == np.float32 and 0.0 <= xtr[0].min() and xtr[0].max() <= 1.0
+    assert len(yte) == 2 and yte[0].shape == (50,) and yte[0].dtype == np.int32
+    with pytest.raises(FileNotFoundError, match="nothing is downloaded"):
+        flow.data.load_mnist(data_dir=str(tmp_path / "empty"))
