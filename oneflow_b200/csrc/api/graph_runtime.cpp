@@ -1073,6 +1073,7 @@ float Graph::learning_rate() const {
 void Graph::set_seed(uint64_t seed) {
   std::lock_guard<std::mutex> g(impl_->run_mu);
   impl_->train.seed = seed;
+  if (impl_->device >= 0) check_cuda(cudaSetDevice(impl_->device), "cudaSetDevice");
   for (int k = 0; k < 4; ++k) {   // the seed is a launch argument of the recorded dropout kernels: record again
     if (impl_->graph_exec[k]) cudaGraphExecDestroy(impl_->graph_exec[k]);
     impl_->graph_exec[k] = nullptr;
