@@ -177,6 +177,7 @@ struct Graph::Impl {
 
   ~Impl() {
     if (executor) ofc_executor_destroy(executor);
+    if (device >= 0) cudaSetDevice(device);   // the streams, events and graphs below belong to that device
     if (step_scalars) cudaFree(step_scalars);
     if (step_scalars_host) cudaFreeHost(step_scalars_host);
     for (auto ge : graph_exec)
