@@ -382,6 +382,28 @@ class _GraphEmitter(torch.fx.Interpreter):
         self.ops.append({"type": "cast", "in": [acc], "out": [out], "attr": {"scale": repr(1.0 / red if mean else 1.0)}})
         return y
 
+    def _multihead_attention(self, m, a, kw):
+        """nn.MultiheadAttention as packed projection -> fused attention -> output projection. Exported for self-attention on
+        batch-first inputs without masks and without the averaged attention weights (``need_weights=False``)."""
+        q, k, v = a[0], (a[1] if len(a) > 1 else kw.get("key")), (a[2] if len(a) > 2 else kw.get("value"))
+        if not (q is k and k is v) or not m.batch_first or not m._qkv_same_embed_dim or m.bias_k is not None or m.add_zero_attn:
+            raise ValueError("MultiheadAttention is exported for batch-first self-attention (query is key is value)")
+        if kw.get("need_weights", a[4] if len(a) > 4 else True) or kw.get("attn_mask") is not None or kw.get("key_padding_mask") is not None:
+            raise ValueError("MultiheadAttention is exported with need_weights=False and without masks (is_causal is honoured)")
+        if m.training and m.dropout > 0:
+            raise ValueError("attention dropout inside MultiheadAttention cannot be exported")
+        B, S, E = q.shape
+        H, D = m.num_heads, E // m.num_heads
+        with torch.no_grad():
+            packed = self._linear(q, m.in_proj_weight, m.in_proj_bias, F.linear(q, m.in_proj_weight, m.in_proj_bias))
+            qh, kh, vh = (t.transpose(1, 2) for t in packed.view(B, S, 3, H, D).unbind(2))
+            causal = bool(kw.get("is_causal", False))
+            att = self._sdpa(qh, kh, vh, F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal), causal, None)
+            merged = att.transpose(1, 2)
+            merged = self._handle("reshape", (merged, (B, S, E)), {}, merged.reshape(B, S, E))
+            out = self._linear(merged, m.out_proj.weight, m.out_proj.bias, F.linear(merged, m.out_proj.weight, m.out_proj.bias))
+        return out, None
+
     def _scalar_result(self, y):
         """A fresh fp32 scalar activation (loss values): (IR id, the tensor that stands for the node)."""
         real = y.detach().to(torch.float32).reshape(1).clone()
@@ -452,6 +474,8 @@ class _GraphEmitter(torch.fx.Interpreter):
         for x in list(a) + list(kw.values()):
             flat += [t for t in (x if isinstance(x, (tuple, list)) else (x,)) if torch.is_tensor(t)]
         inplace = name in _INPLACE or bool(getattr(module, "inplace", False))
+        if isinstance(module, torch.nn.MultiheadAttention):
+            return self._multihead_attention(module, a, kw)          # returns (output, None)
         if not torch.is_tensor(y):
             if isinstance(y, (tuple, list)):
                 for r in y:
@@ -553,7 +577,7 @@ class _LeafTracer(torch.fx.Tracer):
     torch ones and dispatch on the tensor kind in ``forward``, which cannot be traced symbolically (and need not be)."""
 
     _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
-               torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss)
+               torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss, torch.nn.MultiheadAttention)
 
     def is_leaf_module(self, m, qualname):
         return isinstance(m, self._LEAVES) or super().is_leaf_module(m, qualname)

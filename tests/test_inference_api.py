@@ -313,3 +313,36 @@ def test_torch_compile_backend_on_the_native_runtime():
 
         odd = torch.compile(Odd(), backend=oneflow_backend)
         assert torch.allclose(odd(x), torch.sin(x) * 2)
+
+
+def test_multihead_attention_module_exports_as_fused_attention(tmp_path):
+    class Enc(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln, self.mha, self.out = nn.LayerNorm(64), nn.MultiheadAttention(64, 1, batch_first=True), nn.Linear(64, 8)
+
+        def forward(self, x):
+            h = self.ln(x)
+            a, _ = self.mha(h, h, h, need_weights=False)
+            return self.out(x + a)
+
+    torch.manual_seed(3)
+    m = _bf16_weights(Enc().eval())
+    x = torch.randn(2, 16, 64).bfloat16().float()
+    g, outs = _run_host(m, (x,), tmp_path)
+    ref = m(x).detach().numpy().reshape(-1)
+    assert np.abs(outs[0] - ref).max() < 3e-2 * max(np.abs(ref).max(), 1.0)
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("op attention") == 1 and "q_stride=192" in text          # q, k, v read in place from the packed projection
+    g.close()
+
+    class Weights(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mha = nn.MultiheadAttention(64, 1, batch_first=True)
+
+        def forward(self, x):
+            return self.mha(x, x, x)[0]
+
+    with pytest.raises(Exception, match="need_weights=False"):
+        E.export_graph(Weights().eval(), (x,), str(tmp_path / "w"))

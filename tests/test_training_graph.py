@@ -955,3 +955,30 @@ def test_compile_training_and_parameters_back_into_the_module(tmp_path):
     after = float(m(x, y).detach())
     assert after < 0.7 * before and abs(after - want) < 3e-2 * max(want, 0.05)      # the module now computes what the graph trained
     g.close()
+
+
+def test_multihead_attention_module_trains_natively(tmp_path):
+    class Enc(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln, self.mha, self.out = nn.LayerNorm(64), nn.MultiheadAttention(64, 1, batch_first=True), nn.Linear(64, 8)
+
+        def forward(self, x, y):
+            h = self.ln(x)
+            a, _ = self.mha(h, h, h, need_weights=False)
+            return F.cross_entropy(self.out(x + a)[:, 0], y)
+
+    torch.manual_seed(28)
+    m = _bf16_weights(Enc())
+    x, y = torch.randn(4, 16, 64).bfloat16().float(), torch.randint(0, 8, (4,))
+    loss, grads = _grads_by_unit_sgd(m, (x, y), str(tmp_path))
+    ref = m(x, y)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    assert "mha.in_proj_weight" in grads and "mha.out_proj.weight" in grads
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for name, p in m.named_parameters():
+        r = p.grad.numpy().reshape(-1)
+        # the key third of the packed bias shifts all scores of a row alike: zero true gradient, rounding is what is left
+        tol = 3e-2 * (np.abs(r).max() + 1e-6) if name != "mha.in_proj_bias" else 3e-2 * (np.abs(r).max() + 1e-6) + 1e-3 * scale
+        assert np.abs(grads[name] - r).max() <= tol, name
