@@ -404,6 +404,49 @@ class _GraphEmitter(torch.fx.Interpreter):
             out = self._linear(merged, m.out_proj.weight, m.out_proj.bias, F.linear(merged, m.out_proj.weight, m.out_proj.bias))
         return out, None
 
+    def _encoder_layer(self, m, x, causal=False):
+        """nn.TransformerEncoderLayer written out with the emitter's own operators (its forward cannot be traced: fast-path
+        checks on concrete tensors). Batch-first, no masks, relu / gelu feed-forward; pre- or post-norm."""
+        if not m.self_attn.batch_first:
+            raise ValueError("TransformerEncoderLayer is exported with batch_first=True")
+        act = m.activation
+        name = "relu" if act in (F.relu, torch.relu) or isinstance(act, torch.nn.ReLU) else \
+            "gelu" if act is F.gelu or isinstance(act, torch.nn.GELU) else None
+        if name is None:
+            raise ValueError("TransformerEncoderLayer is exported with relu or gelu as its activation")
+        drop = lambda d, h: self._dropout(h, F.dropout(h, d.p, True), d.p) if m.training and d.p > 0 else h
+        norm = lambda n, h: self._layer_norm(h, n.normalized_shape, n.weight, n.bias, n.eps, n(h))
+        add = lambda p, q: self._binary(p, q, p + q, "add")
+
+        def attend(h):
+            return drop(m.dropout1, self._multihead_attention(m.self_attn, (h, h, h), {"need_weights": False, "is_causal": causal})[0])
+
+        def feed_forward(h):
+            h1 = self._linear(h, m.linear1.weight, m.linear1.bias, F.linear(h, m.linear1.weight, m.linear1.bias))
+            h2 = drop(m.dropout, self._unary(h1, F.relu(h1) if name == "relu" else F.gelu(h1), name))
+            return drop(m.dropout2, self._linear(h2, m.linear2.weight, m.linear2.bias, F.linear(h2, m.linear2.weight, m.linear2.bias)))
+
+        with torch.no_grad():
+            if m.norm_first:
+                x = add(x, attend(norm(m.norm1, x)))
+                return add(x, feed_forward(norm(m.norm2, x)))
+            x = norm(m.norm1, add(x, attend(x)))
+            return norm(m.norm2, add(x, feed_forward(x)))
+
+    def _encoder(self, m, a, kw):
+        if kw.get("mask") is not None or kw.get("src_mask") is not None or kw.get("src_key_padding_mask") is not None or len(a) > 1 and a[1] is not None:
+            raise ValueError("transformer encoders are exported without masks (is_causal is honoured)")
+        causal = bool(kw.get("is_causal", False))
+        x = a[0]
+        if isinstance(m, torch.nn.TransformerEncoderLayer):
+            return self._encoder_layer(m, x, causal)
+        for layer in m.layers:
+            x = self._encoder_layer(layer, x, causal)
+        if m.norm is not None:
+            with torch.no_grad():
+                x = self._layer_norm(x, m.norm.normalized_shape, m.norm.weight, m.norm.bias, m.norm.eps, m.norm(x))
+        return x
+
     def _scalar_result(self, y):
         """A fresh fp32 scalar activation (loss values): (IR id, the tensor that stands for the node)."""
         real = y.detach().to(torch.float32).reshape(1).clone()
@@ -476,6 +519,8 @@ class _GraphEmitter(torch.fx.Interpreter):
         inplace = name in _INPLACE or bool(getattr(module, "inplace", False))
         if isinstance(module, torch.nn.MultiheadAttention):
             return self._multihead_attention(module, a, kw)          # returns (output, None)
+        if isinstance(module, (torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder)):
+            return self._encoder(module, a, kw)
         if not torch.is_tensor(y):
             if isinstance(y, (tuple, list)):
                 for r in y:
@@ -577,7 +622,8 @@ class _LeafTracer(torch.fx.Tracer):
     torch ones and dispatch on the tensor kind in ``forward``, which cannot be traced symbolically (and need not be)."""
 
     _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
-               torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss, torch.nn.MultiheadAttention)
+               torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss, torch.nn.MultiheadAttention,
+               torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder)
 
     def is_leaf_module(self, m, qualname):
         return isinstance(m, self._LEAVES) or super().is_leaf_module(m, qualname)

@@ -982,3 +982,32 @@ def test_multihead_attention_module_trains_natively(tmp_path):
         # the key third of the packed bias shifts all scores of a row alike: zero true gradient, rounding is what is left
         tol = 3e-2 * (np.abs(r).max() + 1e-6) if name != "mha.in_proj_bias" else 3e-2 * (np.abs(r).max() + 1e-6) + 1e-3 * scale
         assert np.abs(grads[name] - r).max() <= tol, name
+
+
+@pytest.mark.parametrize("norm_first", [True, False])
+def test_torch_transformer_encoder_exports_and_trains_natively(tmp_path, norm_first):
+    """nn.TransformerEncoder / nn.TransformerEncoderLayer (whose forward cannot be traced) are written out by the exporter:
+    packed projection, fused attention, feed-forward, pre- or post-norm; gradients against autograd."""
+    class Tagger(nn.Module):
+        def __init__(self):
+            super().__init__()
+            layer = nn.TransformerEncoderLayer(64, 1, 128, dropout=0.0, activation="gelu", batch_first=True, norm_first=norm_first)
+            self.emb, self.enc, self.head = nn.Embedding(50, 64), nn.TransformerEncoder(layer, 2, norm=nn.LayerNorm(64), enable_nested_tensor=False), nn.Linear(64, 8)
+
+        def forward(self, ids, labels):
+            return F.cross_entropy(self.head(self.enc(self.emb(ids))).view(-1, 8), labels.view(-1))
+
+    torch.manual_seed(29)
+    m = _bf16_weights(Tagger())
+    ids, labels = torch.randint(0, 50, (3, 16)), torch.randint(0, 8, (3, 16))
+    loss, grads = _grads_by_unit_sgd(m, (ids, labels), str(tmp_path))
+    ref = m(ids, labels)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for name, p in m.named_parameters():
+        r = p.grad.numpy().reshape(-1)
+        extra = 1e-3 * scale if name.endswith("in_proj_bias") else 0.0       # the key third has zero true gradient
+        assert np.abs(grads[name] - r).max() <= 3e-2 * (np.abs(r).max() + 1e-6) + extra, name
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("op attention") == 2 and text.count("op layer_norm") == 5
