@@ -383,11 +383,12 @@ class _GraphEmitter(torch.fx.Interpreter):
         return y
 
     def _multihead_attention(self, m, a, kw):
-        """nn.MultiheadAttention as packed projection -> fused attention -> output projection. Exported for self-attention on
-        batch-first inputs without masks and without the averaged attention weights (``need_weights=False``)."""
+        """nn.MultiheadAttention as packed projection -> fused attention -> output projection: self-attention (query is key is
+        value: one GEMM for q, k, v) or cross-attention (key is value: one GEMM for q, one for k and v, both reading row slices
+        of the packed weight in place). Batch-first inputs, no masks, no averaged attention weights (``need_weights=False``)."""
         q, k, v = a[0], (a[1] if len(a) > 1 else kw.get("key")), (a[2] if len(a) > 2 else kw.get("value"))
-        if not (q is k and k is v) or not m.batch_first or not m._qkv_same_embed_dim or m.bias_k is not None or m.add_zero_attn:
-            raise ValueError("MultiheadAttention is exported for batch-first self-attention (query is key is value)")
+        if k is not v or not m.batch_first or not m._qkv_same_embed_dim or m.bias_k is not None or m.add_zero_attn:
+            raise ValueError("MultiheadAttention is exported for batch-first inputs with key is value (self- or cross-attention)")
         if kw.get("need_weights", a[4] if len(a) > 4 else True) or kw.get("attn_mask") is not None or kw.get("key_padding_mask") is not None:
             raise ValueError("MultiheadAttention is exported with need_weights=False and without masks (is_causal is honoured)")
         if m.training and m.dropout > 0:
@@ -395,8 +396,17 @@ class _GraphEmitter(torch.fx.Interpreter):
         B, S, E = q.shape
         H, D = m.num_heads, E // m.num_heads
         with torch.no_grad():
-            packed = self._linear(q, m.in_proj_weight, m.in_proj_bias, F.linear(q, m.in_proj_weight, m.in_proj_bias))
-            qh, kh, vh = (t.transpose(1, 2) for t in packed.view(B, S, 3, H, D).unbind(2))
+            w, bias = m.in_proj_weight, m.in_proj_bias
+            part = lambda t, lo, hi: None if t is None else t[lo:hi]
+            if q is k:
+                packed = self._linear(q, w, bias, F.linear(q, w, bias))
+                qh, kh, vh = (t.transpose(1, 2) for t in packed.view(B, S, 3, H, D).unbind(2))
+            else:
+                Sk = k.shape[1]
+                qp = self._linear(q, w[:E], part(bias, 0, E), F.linear(q, w[:E], part(bias, 0, E)))
+                kv = self._linear(k, w[E:], part(bias, E, 3 * E), F.linear(k, w[E:], part(bias, E, 3 * E)))
+                qh = qp.view(B, S, H, D).transpose(1, 2)
+                kh, vh = (t.transpose(1, 2) for t in kv.view(B, Sk, 2, H, D).unbind(2))
             causal = bool(kw.get("is_causal", False))
             att = self._sdpa(qh, kh, vh, F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal), causal, None)
             merged = att.transpose(1, 2)
@@ -433,10 +443,57 @@ class _GraphEmitter(torch.fx.Interpreter):
             x = norm(m.norm1, add(x, attend(x)))
             return norm(m.norm2, add(x, feed_forward(x)))
 
+    def _decoder_layer(self, m, x, memory, causal):
+        """nn.TransformerDecoderLayer: (causal) self-attention, cross-attention over ``memory``, feed-forward."""
+        if not m.self_attn.batch_first:
+            raise ValueError("TransformerDecoderLayer is exported with batch_first=True")
+        act = m.activation
+        name = "relu" if act in (F.relu, torch.relu) or isinstance(act, torch.nn.ReLU) else \
+            "gelu" if act is F.gelu or isinstance(act, torch.nn.GELU) else None
+        if name is None:
+            raise ValueError("TransformerDecoderLayer is exported with relu or gelu as its activation")
+        drop = lambda d, h: self._dropout(h, F.dropout(h, d.p, True), d.p) if m.training and d.p > 0 else h
+        norm = lambda n, h: self._layer_norm(h, n.normalized_shape, n.weight, n.bias, n.eps, n(h))
+        add = lambda p, q: self._binary(p, q, p + q, "add")
+        own = lambda h: drop(m.dropout1, self._multihead_attention(m.self_attn, (h, h, h), {"need_weights": False, "is_causal": causal})[0])
+        cross = lambda h: drop(m.dropout2, self._multihead_attention(m.multihead_attn, (h, memory, memory), {"need_weights": False})[0])
+
+        def feed_forward(h):
+            h1 = self._linear(h, m.linear1.weight, m.linear1.bias, F.linear(h, m.linear1.weight, m.linear1.bias))
+            h2 = drop(m.dropout, self._unary(h1, F.relu(h1) if name == "relu" else F.gelu(h1), name))
+            return drop(m.dropout3, self._linear(h2, m.linear2.weight, m.linear2.bias, F.linear(h2, m.linear2.weight, m.linear2.bias)))
+
+        with torch.no_grad():
+            if m.norm_first:
+                x = add(x, own(norm(m.norm1, x)))
+                x = add(x, cross(norm(m.norm2, x)))
+                return add(x, feed_forward(norm(m.norm3, x)))
+            x = norm(m.norm1, add(x, own(x)))
+            x = norm(m.norm2, add(x, cross(x)))
+            return norm(m.norm3, add(x, feed_forward(x)))
+
+    def _decoder(self, m, a, kw):
+        x, memory = a[0], (a[1] if len(a) > 1 else kw.get("memory"))
+        causal = bool(kw.get("tgt_is_causal", False))
+        tgt_mask = kw.get("tgt_mask", a[2] if len(a) > 2 else None)
+        # torch wants the square mask beside the tgt_is_causal hint; the hint is what is exported (the fused kernel masks itself)
+        if (tgt_mask is not None and not causal) or any(kw.get(key) is not None for key in ("memory_mask", "tgt_key_padding_mask", "memory_key_padding_mask")) \
+                or (len(a) > 3 and any(t is not None for t in a[3:])):
+            raise ValueError("transformer decoders are exported without explicit masks (tgt_mask together with tgt_is_causal=True is the causal mask)")
+        if isinstance(m, torch.nn.TransformerDecoderLayer):
+            return self._decoder_layer(m, x, memory, causal)
+        for layer in m.layers:
+            x = self._decoder_layer(layer, x, memory, causal)
+        if m.norm is not None:
+            with torch.no_grad():
+                x = self._layer_norm(x, m.norm.normalized_shape, m.norm.weight, m.norm.bias, m.norm.eps, m.norm(x))
+        return x
+
     def _encoder(self, m, a, kw):
-        if kw.get("mask") is not None or kw.get("src_mask") is not None or kw.get("src_key_padding_mask") is not None or len(a) > 1 and a[1] is not None:
-            raise ValueError("transformer encoders are exported without masks (is_causal is honoured)")
         causal = bool(kw.get("is_causal", False))
+        mask = kw.get("mask", kw.get("src_mask", a[1] if len(a) > 1 else None))
+        if (mask is not None and not causal) or kw.get("src_key_padding_mask") is not None or (len(a) > 2 and a[2] is not None):
+            raise ValueError("transformer encoders are exported without explicit masks (a mask together with is_causal=True is the causal mask)")
         x = a[0]
         if isinstance(m, torch.nn.TransformerEncoderLayer):
             return self._encoder_layer(m, x, causal)
@@ -521,6 +578,8 @@ class _GraphEmitter(torch.fx.Interpreter):
             return self._multihead_attention(module, a, kw)          # returns (output, None)
         if isinstance(module, (torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder)):
             return self._encoder(module, a, kw)
+        if isinstance(module, (torch.nn.TransformerDecoderLayer, torch.nn.TransformerDecoder)):
+            return self._decoder(module, a, kw)
         if not torch.is_tensor(y):
             if isinstance(y, (tuple, list)):
                 for r in y:
@@ -623,7 +682,7 @@ class _LeafTracer(torch.fx.Tracer):
 
     _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
                torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss, torch.nn.MultiheadAttention,
-               torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder)
+               torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder, torch.nn.TransformerDecoderLayer, torch.nn.TransformerDecoder)
 
     def is_leaf_module(self, m, qualname):
         return isinstance(m, self._LEAVES) or super().is_leaf_module(m, qualname)

@@ -1011,3 +1011,42 @@ def test_torch_transformer_encoder_exports_and_trains_natively(tmp_path, norm_fi
         assert np.abs(grads[name] - r).max() <= 3e-2 * (np.abs(r).max() + 1e-6) + extra, name
     text = open(os.path.join(str(tmp_path), "graph.txt")).read()
     assert text.count("op attention") == 2 and text.count("op layer_norm") == 5
+
+
+def test_encoder_decoder_with_cross_attention_trains_natively(tmp_path):
+    """A sequence-to-sequence model from torch's own building blocks: encoder over the source, decoder with causal
+    self-attention and cross-attention over the encoder's output (query from one sequence, keys / values from another of a
+    different length: two GEMMs reading row slices of the packed projection weight), tied nothing, token-level loss."""
+    class Seq2Seq(nn.Module):
+        def __init__(self):
+            super().__init__()
+            # gelu: with relu a pre-activation near zero falls on different sides in bf16 and in the fp32 reference, and the
+            # gradient of that unit is all or nothing
+            enc = nn.TransformerEncoderLayer(64, 1, 128, dropout=0.0, activation="gelu", batch_first=True, norm_first=True)
+            dec = nn.TransformerDecoderLayer(64, 1, 128, dropout=0.0, activation="gelu", batch_first=True, norm_first=True)
+            self.src, self.tgt = nn.Embedding(40, 64), nn.Embedding(40, 64)
+            self.encoder = nn.TransformerEncoder(enc, 1, enable_nested_tensor=False)
+            self.decoder = nn.TransformerDecoder(dec, 1, norm=nn.LayerNorm(64))
+            self.head = nn.Linear(64, 40)
+
+        def forward(self, src, tgt_in, tgt_out):
+            memory = self.encoder(self.src(src))
+            mask = nn.Transformer.generate_square_subsequent_mask(tgt_in.shape[1])
+            h = self.decoder(self.tgt(tgt_in), memory, tgt_mask=mask, tgt_is_causal=True)
+            return F.cross_entropy(self.head(h).view(-1, 40), tgt_out.view(-1))
+
+    torch.manual_seed(30)
+    m = _bf16_weights(Seq2Seq())
+    src, tgt_in, tgt_out = torch.randint(0, 40, (2, 24)), torch.randint(0, 40, (2, 16)), torch.randint(0, 40, (2, 16))
+    loss, grads = _grads_by_unit_sgd(m, (src, tgt_in, tgt_out), str(tmp_path))
+    ref = m(src, tgt_in, tgt_out)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for name, p in m.named_parameters():
+        r = p.grad.numpy().reshape(-1)
+        # the encoder's gradients arrive through the cross-attention as bf16 activation gradients: small against the decoder's,
+        # so their rounding is measured against the largest gradient of the model as well
+        assert np.abs(grads[name] - r).max() <= 3e-2 * (np.abs(r).max() + 1e-6) + 1e-3 * scale, name
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("op attention") == 3
