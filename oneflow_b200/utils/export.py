@@ -580,6 +580,14 @@ class _GraphEmitter(torch.fx.Interpreter):
             return self._encoder(module, a, kw)
         if isinstance(module, (torch.nn.TransformerDecoderLayer, torch.nn.TransformerDecoder)):
             return self._decoder(module, a, kw)
+        if isinstance(module, torch.nn.Transformer):                 # encoder over src, decoder over tgt and the encoder's output
+            if not module.batch_first:
+                raise ValueError("nn.Transformer is exported with batch_first=True")
+            src, tgt = a[0], (a[1] if len(a) > 1 else kw.get("tgt"))
+            memory = self._encoder(module.encoder, (src,), {"mask": kw.get("src_mask"), "is_causal": kw.get("src_is_causal", False),
+                                                             "src_key_padding_mask": kw.get("src_key_padding_mask")})
+            return self._decoder(module.decoder, (tgt, memory), {k: kw.get(k) for k in ("tgt_mask", "memory_mask", "tgt_key_padding_mask",
+                                                                                         "memory_key_padding_mask", "tgt_is_causal")})
         if not torch.is_tensor(y):
             if isinstance(y, (tuple, list)):
                 for r in y:

@@ -346,3 +346,26 @@ def test_multihead_attention_module_exports_as_fused_attention(tmp_path):
 
     with pytest.raises(Exception, match="need_weights=False"):
         E.export_graph(Weights().eval(), (x,), str(tmp_path / "w"))
+
+
+def test_torch_transformer_model_exports(tmp_path):
+    """nn.Transformer (encoder-decoder) as one leaf: both stacks are written out by the exporter."""
+    class Translator(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.core = nn.Transformer(d_model=64, nhead=1, num_encoder_layers=1, num_decoder_layers=2, dim_feedforward=128, dropout=0.0,
+                                       activation="gelu", batch_first=True, norm_first=True)
+            self.src, self.tgt, self.head = nn.Embedding(40, 64), nn.Embedding(40, 64), nn.Linear(64, 40)
+
+        def forward(self, src, tgt):
+            mask = nn.Transformer.generate_square_subsequent_mask(tgt.shape[1])
+            return self.head(self.core(self.src(src), self.tgt(tgt), tgt_mask=mask, tgt_is_causal=True))
+
+    torch.manual_seed(4)
+    m = _bf16_weights(Translator().eval())
+    src, tgt = torch.randint(0, 40, (2, 24)), torch.randint(0, 40, (2, 16))
+    g, outs = _run_host(m, (src, tgt), tmp_path)
+    ref = m(src, tgt).detach().numpy().reshape(-1)
+    assert np.abs(outs[0] - ref).max() < 4e-2 * max(np.abs(ref).max(), 1.0)
+    assert open(os.path.join(str(tmp_path), "graph.txt")).read().count("op attention") == 1 + 2 * 2
+    g.close()
