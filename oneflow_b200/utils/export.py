@@ -840,9 +840,21 @@ class InferenceGraph:
         return dict(zip(("ops", "tensors", "activation_bytes", "arena_bytes", "dependencies", "streams_used", "graph_replays"), list(s)))
 
     def close(self):
-        if self.h:
+        if getattr(self, "h", None):
             self.lib.ofb_api_graph_free(ctypes.c_void_p(self.h))
             self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class TrainingGraph(InferenceGraph):
