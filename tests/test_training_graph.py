@@ -1050,3 +1050,54 @@ def test_encoder_decoder_with_cross_attention_trains_natively(tmp_path):
         assert np.abs(grads[name] - r).max() <= 3e-2 * (np.abs(r).max() + 1e-6) + 1e-3 * scale, name
     text = open(os.path.join(str(tmp_path), "graph.txt")).read()
     assert text.count("op attention") == 3
+
+
+def test_modern_decoder_block_with_rope_swiglu_and_grouped_query_attention_trains_natively(tmp_path):
+    """Rotary position embedding (slices, negation, concatenation, broadcast tables), a gated SiLU feed-forward (chunk views),
+    grouped-query attention (two query heads per key / value head) and bias-free projections: all on operators the IR already
+    has, gradients against autograd."""
+    def rope(t, cos, sin):            # t [B, heads, S, D]
+        h = t.shape[-1] // 2
+        rot = torch.cat([-t[..., h:], t[..., :h]], dim=-1)
+        return t * cos + rot * sin
+    class Block(nn.Module):
+        def __init__(s, d=64, heads=2, kv_heads=1, seq=16):
+            super().__init__()
+            s.h, s.hk, s.dh = heads, kv_heads, d // heads
+            s.ln1, s.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            s.wq, s.wkv, s.wo = nn.Linear(d, d, bias=False), nn.Linear(d, 2 * kv_heads * s.dh, bias=False), nn.Linear(d, d, bias=False)
+            s.gate_up, s.down = nn.Linear(d, 2 * 128, bias=False), nn.Linear(128, d, bias=False)
+            pos = torch.arange(seq)[:, None] * (1.0 / 10000 ** (torch.arange(0, s.dh, 2) / s.dh))[None, :]
+            s.register_buffer("cos", torch.cat([pos.cos(), pos.cos()], -1))
+            s.register_buffer("sin", torch.cat([pos.sin(), pos.sin()], -1))
+        def forward(s, x):
+            B, S, D = x.shape
+            h = s.ln1(x)
+            q = s.wq(h).view(B, S, s.h, s.dh).transpose(1, 2)
+            k, v = s.wkv(h).view(B, S, 2, s.hk, s.dh).unbind(2)
+            k, v = k.transpose(1, 2), v.transpose(1, 2)
+            q, k = rope(q, s.cos, s.sin), rope(k, s.cos, s.sin)
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            x = x + s.wo(a.transpose(1, 2).reshape(B, S, D))
+            g, u = s.gate_up(s.ln2(x)).chunk(2, dim=-1)
+            return x + s.down(F.silu(g) * u)
+    class LM(nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.emb, s.blocks, s.ln, s.head = nn.Embedding(96, 64), nn.ModuleList([Block(), Block()]), nn.LayerNorm(64), nn.Linear(64, 96, bias=False)
+        def forward(s, ids, tgt):
+            x = s.emb(ids)
+            for b in s.blocks:
+                x = b(x)
+            return F.cross_entropy(s.head(s.ln(x)).view(-1, 96), tgt.view(-1))
+
+    torch.manual_seed(31)
+    m = _bf16_weights(LM())
+    ids, tgt = torch.randint(0, 96, (2, 16)), torch.randint(0, 96, (2, 16))
+    loss, grads = _grads_by_unit_sgd(m, (ids, tgt), str(tmp_path))
+    ref = m(ids, tgt)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    _check_grads(m, grads)
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert text.count("op attention") == 2 and "fn=6" in text           # fused attention with grouped heads; silu
