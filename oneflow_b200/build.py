@@ -151,6 +151,26 @@ def build_api_sanitized(verbose=False):
     return exe
 
 
+def build_api_thread_sanitized(verbose=False):
+    """The same program under ThreadSanitizer, with the host runtime's sources compiled in (the scheduler's worker threads are
+    what runs the operators of a plan): lib/ofb_api_train_tsan."""
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "api", "*.cpp"))) + [os.path.join(CSRC, "api", "examples", "train_graph.cpp")] + \
+        sorted(glob.glob(os.path.join(CSRC, "core", "*.cpp")))
+    headers = glob.glob(os.path.join(CSRC, "api", "*.h")) + glob.glob(os.path.join(CSRC, "common", "*.h")) + glob.glob(os.path.join(CSRC, "core", "*.h"))
+    exe = os.path.join(LIB, "ofb_api_train_tsan")
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    if not os.path.exists(exe) or any(_newer(s, exe, headers) for s in srcs):
+        cxx = shutil.which("g++") or "g++"
+        _run([cxx, "-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", "-pthread", "-fsanitize=thread", "-I", os.path.join(cuda, "include"),
+              "-I", os.path.join(CSRC, "api"), "-o", exe] + srcs +
+             ["-L", LIB, "-lofb_kernels", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lrt", "-ldl", f"-Wl,-rpath,{LIB}"],
+             os.path.join(OBJ, "api_tsan.log"))
+        print(f"[build] built {os.path.relpath(exe, ROOT)}", flush=True)
+    return exe
+
+
 def build_all(verbose=False):
     return [build_kernels(verbose), build_core(verbose), build_api(verbose)]
 
@@ -159,5 +179,6 @@ if __name__ == "__main__":
     if "--sanitizers" in sys.argv:
         build_sanitizers(verbose="-v" in sys.argv)
         build_api_sanitized(verbose="-v" in sys.argv)
+        build_api_thread_sanitized(verbose="-v" in sys.argv)
     else:
         build_all(verbose="-v" in sys.argv)

@@ -507,7 +507,7 @@ def test_dropout_on_the_gpu_runtime_drops_the_same_elements_as_the_host_runtime(
         g.close()
 
 
-def test_graph_compiler_runs_clean_under_address_and_ub_sanitizers(tmp_path):
+def test_graph_compiler_runs_clean_under_address_ub_and_thread_sanitizers(tmp_path):
     """Parser, autodiff, the rewriting passes (default list, cheap recompute, full checkpointing), plan compiler, host
     operators and Save: the C++ training example built from the API's sources with -fsanitize=address,undefined trains a
     two-layer GPT with dropout on the host device."""
@@ -526,12 +526,16 @@ def test_graph_compiler_runs_clean_under_address_and_ub_sanitizers(tmp_path):
     tgt.numpy().astype(np.int64).tofile(str(tmp_path / "tgt.bin"))
     os.makedirs(str(tmp_path / "out"))
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=0 exitcode=67")
-    for mode in ([], ["--recompute=cheap"], ["--recompute=full"]):
-        r = subprocess.run([exe] + mode + [d, "-1", "4", "0.01", str(tmp_path / "out"), str(tmp_path / "ids.bin"), str(tmp_path / "tgt.bin")],
+    runs = [(exe, mode) for mode in ([], ["--recompute=cheap"], ["--recompute=full"])]
+    # and once under ThreadSanitizer with the scheduler's sources compiled in: two plan streams = two worker threads
+    runs.append((B.build_api_thread_sanitized(), []))
+    env["TSAN_OPTIONS"] = "halt_on_error=0 exitcode=66"
+    for program, mode in runs:
+        r = subprocess.run([program] + mode + [d, "-1", "4", "0.01", str(tmp_path / "out"), str(tmp_path / "ids.bin"), str(tmp_path / "tgt.bin")],
                            capture_output=True, text=True, timeout=600, env=env)
         out = r.stdout + r.stderr
         assert r.returncode == 0, out[-3000:]
-        assert "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
+        assert "AddressSanitizer" not in out and "ThreadSanitizer" not in out and "runtime error" not in out, out[-3000:]
         losses = [float(v) for v in r.stdout.split()]
         assert len(losses) == 4 and losses[-1] < losses[0]
         assert os.path.exists(str(tmp_path / "out" / "train_state.bin"))
