@@ -289,6 +289,23 @@ class _GraphEmitter(torch.fx.Interpreter):
         self._emit("layer_norm", ins, out, eps=repr(float(eps)))
         return y
 
+    def _rms_norm(self, x, shape, w, eps, y):
+        """RMSNorm on the LayerNorm kernels: over [x, -x] the mean is zero and the variance is mean(x^2), so the first half of
+        LayerNorm([x, -x]) with unit scale and zero shift is x / sqrt(mean(x^2) + eps); the learned scale is a broadcast
+        multiplication afterwards (its gradient a column sum). Twice the row length through the normalisation, no new kernel."""
+        if len(shape) != 1:
+            raise ValueError("only RMSNorm over the last dimension can be exported")
+        n = int(shape[0])
+        eps = float(eps) if eps is not None else float(torch.finfo(x.dtype).eps)
+        with torch.no_grad():
+            neg = self._unary(x, -x, "scale", -1.0)
+            both = self._cat([x, neg], x.dim() - 1, torch.cat([x, neg], dim=-1))
+            normed = self._layer_norm(both, (2 * n,), torch.ones(2 * n), torch.zeros(2 * n), eps, F.layer_norm(both, (2 * n,), None, None, eps))
+            half = normed[..., :n]
+            if w is None:
+                return self._unary(half, y, "scale", 1.0)
+            return self._binary(half, w, y, "mul")
+
     def _embedding(self, ids, table, y):
         ins = [self._operand(ids), self._operand(table)]
         out, y = self._result(y)
@@ -608,6 +625,8 @@ class _GraphEmitter(torch.fx.Interpreter):
                 return self._layer_norm(a[0], m.normalized_shape, m.weight, m.bias, m.eps, y)
             if isinstance(m, torch.nn.Embedding):
                 return self._embedding(a[0], m.weight, y)
+            if isinstance(m, torch.nn.RMSNorm):
+                return self._rms_norm(a[0], m.normalized_shape, m.weight, m.eps, y)
             if isinstance(m, torch.nn.GELU):
                 return self._unary(a[0], y, "gelu_tanh" if m.approximate == "tanh" else "gelu")
             for cls, fn in ((torch.nn.ReLU, "relu"), (torch.nn.Tanh, "tanh"), (torch.nn.Sigmoid, "sigmoid"), (torch.nn.SiLU, "silu")):
@@ -631,6 +650,8 @@ class _GraphEmitter(torch.fx.Interpreter):
                                     a[4] if len(a) > 4 else kw.get("eps", 1e-5), y)
         if n == "embedding":
             return self._embedding(a[0], a[1], y)
+        if n == "rms_norm":
+            return self._rms_norm(a[0], a[1], a[2] if len(a) > 2 else kw.get("weight"), a[3] if len(a) > 3 else kw.get("eps"), y)
         if n == "gelu":
             return self._unary(a[0], y, "gelu_tanh" if kw.get("approximate", "none") == "tanh" else "gelu")
         if n in ("relu", "tanh", "sigmoid", "silu", "exp", "rsqrt", "square"):
@@ -688,7 +709,7 @@ class _LeafTracer(torch.fx.Tracer):
     """Layers the emitter knows by type stay whole, whatever package their class lives in: the flow API's layers subclass the
     torch ones and dispatch on the tensor kind in ``forward``, which cannot be traced symbolically (and need not be)."""
 
-    _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
+    _LEAVES = (torch.nn.Linear, torch.nn.LayerNorm, torch.nn.RMSNorm, torch.nn.Embedding, torch.nn.GELU, torch.nn.ReLU, torch.nn.Tanh, torch.nn.Sigmoid,
                torch.nn.SiLU, torch.nn.Softmax, torch.nn.Dropout, torch.nn.CrossEntropyLoss, torch.nn.MSELoss, torch.nn.MultiheadAttention,
                torch.nn.TransformerEncoderLayer, torch.nn.TransformerEncoder, torch.nn.TransformerDecoderLayer, torch.nn.TransformerDecoder)
 

@@ -1105,3 +1105,28 @@ def test_modern_decoder_block_with_rope_swiglu_and_grouped_query_attention_train
     _check_grads(m, grads)
     text = open(os.path.join(str(tmp_path), "graph.txt")).read()
     assert text.count("op attention") == 2 and "fn=6" in text           # fused attention with grouped heads; silu
+
+
+def test_rms_norm_exports_onto_the_layer_norm_kernels_and_trains(tmp_path):
+    """RMSNorm(x) = first half of LayerNorm([x, -x]) with unit scale and zero shift, times the learned scale."""
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb, self.n1, self.fc, self.n2, self.head = nn.Embedding(50, 64), nn.RMSNorm(64, eps=1e-6), nn.Linear(64, 64), nn.RMSNorm(64), nn.Linear(64, 8)
+
+        def forward(self, ids, labels):
+            h = self.emb(ids)
+            h = h + F.silu(self.fc(self.n1(h)))
+            return F.cross_entropy(self.head(F.rms_norm(self.n2(h), (64,)))[:, 0], labels)
+
+    torch.manual_seed(32)
+    m = _bf16_weights(Net())
+    with torch.no_grad():
+        m.n1.weight.mul_(torch.linspace(0.5, 1.5, 64))
+    ids, labels = torch.randint(0, 50, (4, 12)), torch.randint(0, 8, (4,))
+    loss, grads = _grads_by_unit_sgd(m, (ids, labels), str(tmp_path))
+    ref = m(ids, labels)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    assert "n1.weight" in grads and "n2.weight" in grads
+    _check_grads(m, grads)
