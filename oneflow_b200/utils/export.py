@@ -120,6 +120,7 @@ class _GraphEmitter(torch.fx.Interpreter):
         self.copy_cache = {}
         # parameters that own their whole storage and take gradients: named in the IR, which makes them trainable there
         self.n_dropout = 0
+        self.pending_log_softmax = {}     # storage of a log_softmax result -> the logits it was computed from
         self.param_names = {}
         for name, prm in gm.named_parameters():
             if prm.requires_grad and prm.dtype.is_floating_point and prm.storage_offset() == 0 and \
@@ -151,6 +152,8 @@ class _GraphEmitter(torch.fx.Interpreter):
         return rid
 
     def _root(self, real):
+        if real.untyped_storage().data_ptr() in self.pending_log_softmax:
+            raise ValueError("log_softmax is exported only as the input of nll_loss (the pair becomes one cross_entropy operator)")
         rid = self.roots.get(real.untyped_storage().data_ptr())
         if rid is None:
             rid = self._constant(real)
@@ -672,6 +675,19 @@ class _GraphEmitter(torch.fx.Interpreter):
             return self._sdpa(a[0], a[1], a[2], y, a[5] if len(a) > 5 else kw.get("is_causal", False), kw.get("scale"))
         if n in ("mean", "sum") and torch.is_tensor(y) and y.dim() > 0 and (len(a) > 1 or "dim" in kw):
             return self._reduce(a[0], a[1] if len(a) > 1 else kw["dim"], y, n == "mean")
+        if n == "log_softmax":
+            x, dim = a[0], (a[1] if len(a) > 1 else kw.get("dim", -1))
+            if x.dim() != 2 or dim % 2 != 1:
+                raise ValueError("log_softmax is exported over the class axis of [rows, classes] logits, as the input of nll_loss")
+            self.keep.append(y)
+            self.pending_log_softmax[y.untyped_storage().data_ptr()] = x
+            return y
+        if n == "nll_loss":
+            logits = self.pending_log_softmax.get(a[0].untyped_storage().data_ptr())   # stays registered: any other reader is refused
+            if logits is None:
+                raise ValueError("nll_loss is exported on the result of log_softmax only")
+            return self._cross_entropy(logits, a[1], y, a[2] if len(a) > 2 else kw.get("weight"), kw.get("ignore_index", -100),
+                                       kw.get("reduction", "mean"), 0.0)
         if n == "cross_entropy":
             return self._cross_entropy(a[0], a[1], y, a[2] if len(a) > 2 else kw.get("weight"), kw.get("ignore_index", -100),
                                        kw.get("reduction", "mean"), kw.get("label_smoothing", 0.0))
@@ -688,6 +704,8 @@ class _GraphEmitter(torch.fx.Interpreter):
             self.keep.append(flat_copy)
             self.roots[flat_copy.untyped_storage().data_ptr()] = root
             return flat_copy.reshape(y.shape)
+        if any(t.untyped_storage().data_ptr() in self.pending_log_softmax for t in flat):
+            raise ValueError("log_softmax is exported only as the input of nll_loss (the pair becomes one cross_entropy operator)")
         if all(t.untyped_storage().data_ptr() not in self.roots or self._kind(self.roots[t.untyped_storage().data_ptr()]) == "param" for t in flat):
             y = y.contiguous()
             self._constant(y)           # built from constants only (position ids, tables of fixed shape, ...)

@@ -1130,3 +1130,37 @@ def test_rms_norm_exports_onto_the_layer_norm_kernels_and_trains(tmp_path):
     assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
     assert "n1.weight" in grads and "n2.weight" in grads
     _check_grads(m, grads)
+
+
+def test_log_softmax_followed_by_nll_loss_becomes_one_cross_entropy_operator(tmp_path):
+    class Classic(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.fc2 = nn.Linear(32, 64), nn.Linear(64, 16)
+
+        def forward(self, x, y):
+            return F.nll_loss(F.log_softmax(self.fc2(torch.relu(self.fc1(x))), dim=1), y)
+
+    torch.manual_seed(33)
+    m = _bf16_weights(Classic())
+    x, y = torch.randn(24, 32).bfloat16().float(), torch.randint(0, 16, (24,))
+    d = E.export_graph(m, (x, y), str(tmp_path), fuse=False)
+    text = open(os.path.join(d, "graph.txt")).read()
+    assert text.count("op cross_entropy") == 1 and "log_softmax" not in text
+    g = E.TrainingGraph(d, device=-1, optimizer="sgd", lr=0.1)
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+    for _ in range(5):
+        ref = m(x, y)
+        opt.zero_grad()
+        ref.backward()
+        opt.step()
+        assert abs(g.step(x.numpy(), y.numpy()) - float(ref.detach())) < 3e-2 * max(abs(float(ref.detach())), 0.1)
+    g.close()
+
+    class Leaks(nn.Module):
+        def forward(self, x, y):
+            lp = F.log_softmax(x, dim=1)
+            return F.nll_loss(lp, y) + lp.sum() * 0.0
+
+    with pytest.raises(Exception, match="only as the input of nll_loss"):
+        E.export_graph(Leaks(), (torch.randn(4, 8), torch.randint(0, 8, (4,))), str(tmp_path / "leak"))
