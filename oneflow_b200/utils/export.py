@@ -661,6 +661,17 @@ class _GraphEmitter(torch.fx.Interpreter):
             return self._unary(a[0], y, n)
         if n == "neg":
             return self._unary(a[0], y, "scale", -1.0)
+        if n == "pow" and not torch.is_tensor(a[1] if len(a) > 1 else kw.get("exponent")):
+            p = a[1] if len(a) > 1 else kw.get("exponent")
+            if p == 2:
+                return self._unary(a[0], y, "square")
+            if p == 1:
+                return self._unary(a[0], y, "scale", 1.0)
+            if p == -0.5:
+                return self._unary(a[0], y, "rsqrt")
+            if p == 3:                                           # x^3 = x^2 * x
+                return self._binary(self._unary(a[0], a[0] * a[0], "square"), a[0], y, "mul")
+            raise ValueError(f"cannot export pow with exponent {p} (2, 3, 1 and -0.5 are)")
         if n in ("add", "sub", "mul", "truediv", "div", "maximum", "minimum"):
             return self._binary(a[0], a[1], y, "div" if n == "truediv" else n)
         if n in ("matmul", "bmm", "mm"):

@@ -1164,3 +1164,28 @@ def test_log_softmax_followed_by_nll_loss_becomes_one_cross_entropy_operator(tmp
 
     with pytest.raises(Exception, match="only as the input of nll_loss"):
         E.export_graph(Leaks(), (torch.randn(4, 8), torch.randint(0, 8, (4,))), str(tmp_path / "leak"))
+
+
+def test_classic_image_classifier_with_flatten_powers_and_nll_loss(tmp_path):
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = nn.Sequential(nn.Flatten(), nn.Linear(64, 32), nn.ReLU(), nn.Identity(), nn.Linear(32, 16))
+
+        def forward(self, img, y):
+            z = self.body(img)
+            return F.nll_loss(F.log_softmax(z ** 2 * 0.5 + z.pow(3) * 0.01, dim=1), y)
+
+    torch.manual_seed(34)
+    m = _bf16_weights(Net())
+    img, y = torch.randn(8, 1, 8, 8).bfloat16().float(), torch.randint(0, 16, (8,))
+    loss, grads = _grads_by_unit_sgd(m, (img, y), str(tmp_path))
+    ref = m(img, y)
+    ref.backward()
+    assert abs(loss - float(ref.detach())) < 2e-2 * abs(float(ref.detach()))
+    scale = max(float(p.grad.abs().max()) for p in m.parameters())
+    for name, p in m.named_parameters():          # relu: units whose pre-activation is near zero may fall on the other side in bf16
+        r = p.grad.numpy().reshape(-1)
+        assert np.abs(grads[name] - r).max() <= 5e-2 * (np.abs(r).max() + 1e-6) + 5e-3 * scale, name
+    with pytest.raises(Exception, match="exponent"):
+        E.export_graph(type("P", (nn.Module,), {"forward": lambda self, x: x ** 1.5})(), (torch.rand(2, 8),), str(tmp_path / "p"))
