@@ -661,6 +661,10 @@ class _GraphEmitter(torch.fx.Interpreter):
             return self._unary(a[0], y, n)
         if n == "neg":
             return self._unary(a[0], y, "scale", -1.0)
+        if n == "sqrt":                                          # sqrt(x) = x * rsqrt(x)
+            return self._binary(a[0], self._unary(a[0], torch.rsqrt(a[0]), "rsqrt"), y, "mul")
+        if n == "clamp" and (a[1] if len(a) > 1 else kw.get("min")) == 0 and (a[2] if len(a) > 2 else kw.get("max")) is None:
+            return self._unary(a[0], y, "relu")
         if n == "pow" and not torch.is_tensor(a[1] if len(a) > 1 else kw.get("exponent")):
             p = a[1] if len(a) > 1 else kw.get("exponent")
             if p == 2:

@@ -369,3 +369,17 @@ def test_torch_transformer_model_exports(tmp_path):
     assert np.abs(outs[0] - ref).max() < 4e-2 * max(np.abs(ref).max(), 1.0)
     assert open(os.path.join(str(tmp_path), "graph.txt")).read().count("op attention") == 1 + 2 * 2
     g.close()
+
+
+def test_sqrt_and_clamp_at_zero_export_as_compositions(tmp_path):
+    class M(nn.Module):
+        def forward(self, x):
+            return torch.sqrt(x * x + 1.0) + x.clamp(min=0) + torch.clamp(x, 0)
+
+    x = torch.randn(4, 16).bfloat16().float()
+    g, outs = _run_host(M(), (x,), tmp_path)
+    ref = M()(x).numpy().reshape(-1)
+    assert np.abs(outs[0] - ref).max() < 2e-2 * np.abs(ref).max()
+    text = open(os.path.join(str(tmp_path), "graph.txt")).read()
+    assert "fn=9" in text and text.count("fn=3") == 2            # rsqrt; relu twice
+    g.close()
