@@ -383,3 +383,59 @@ def test_sqrt_and_clamp_at_zero_export_as_compositions(tmp_path):
     text = open(os.path.join(str(tmp_path), "graph.txt")).read()
     assert "fn=9" in text and text.count("fn=3") == 2            # rsqrt; relu twice
     g.close()
+
+
+def test_decode_step_with_key_value_cache_matches_the_full_forward(tmp_path):
+    """Serving with a cache needs nothing special from the runtime: the decode step is a module of its own whose inputs and
+    outputs include the cache tensors (one query position attends the cached keys plus its own: Sq = 1, Sk = S)."""
+    class Attn(nn.Module):
+        def __init__(self, d=64, vocab=96, seq=16):
+            super().__init__()
+            self.emb, self.pos, self.ln = nn.Embedding(vocab, d), nn.Embedding(seq, d), nn.LayerNorm(d)
+            self.q, self.kv, self.o, self.head = nn.Linear(d, d), nn.Linear(d, 2 * d), nn.Linear(d, d), nn.Linear(d, vocab)
+
+        def full(self, ids):                                          # [B, S] -> logits of the last position, and the cache
+            B, S = ids.shape
+            x = self.emb(ids) + self.pos(torch.arange(S))
+            h = self.ln(x)
+            k, v = self.kv(h).view(B, S, 2, 1, -1).unbind(2)
+            a = F.scaled_dot_product_attention(self.q(h).view(B, S, 1, -1).transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+            x = x + self.o(a.transpose(1, 2).reshape(B, S, -1))
+            return self.head(x[:, -1]), k.contiguous(), v.contiguous()
+
+    class Prefill(nn.Module):
+        def __init__(self, net):
+            super().__init__()
+            self.net = net
+
+        def forward(self, ids):
+            return self.net.full(ids)
+
+    class Decode(nn.Module):
+        def __init__(self, net, position):
+            super().__init__()
+            self.net, self.position = net, position
+
+        def forward(self, token, k_cache, v_cache):                  # token [B, 1]; caches [B, S, 1, D]
+            net, B = self.net, token.shape[0]
+            x = net.emb(token) + net.pos(torch.full((1,), self.position))
+            h = net.ln(x)
+            k_new, v_new = net.kv(h).view(B, 1, 2, 1, -1).unbind(2)
+            k, v = torch.cat([k_cache, k_new], dim=1), torch.cat([v_cache, v_new], dim=1)
+            a = F.scaled_dot_product_attention(net.q(h).view(B, 1, 1, -1).transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+            x = x + net.o(a.transpose(1, 2).reshape(B, 1, -1))
+            return net.head(x[:, -1]), k, v
+
+    torch.manual_seed(5)
+    net = _bf16_weights(Attn().eval())
+    ids = torch.randint(0, 96, (2, 12))
+    want = net.full(ids)[0].detach().numpy().reshape(-1)
+    pre = E.InferenceGraph(E.export_graph(Prefill(net), (ids[:, :11],), str(tmp_path / "prefill")), device=-1)
+    _, k_cache, v_cache = pre.run(ids[:, :11].numpy())
+    k0, v0 = torch.from_numpy(k_cache).view(2, 11, 1, 64), torch.from_numpy(v_cache).view(2, 11, 1, 64)
+    dec = E.InferenceGraph(E.export_graph(Decode(net, 11), (ids[:, 11:], k0, v0), str(tmp_path / "decode")), device=-1)
+    logits, k1, v1 = dec.run(ids[:, 11:].numpy(), k0.numpy(), v0.numpy())
+    assert np.abs(logits - want).max() < 3e-2 * np.abs(want).max()
+    assert k1.size == 2 * 12 * 64 and np.array_equal(k1.reshape(2, 12, 64)[:, :11], k_cache.reshape(2, 11, 64))
+    pre.close()
+    dec.close()
